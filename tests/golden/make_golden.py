@@ -1,0 +1,152 @@
+"""Generate the golden fixtures in this directory from the REFERENCE's own code.
+
+Run once in a container that has the reference tree (default ``/root/reference``,
+override with ``DAISY_REFERENCE_ROOT``) and, for the KDA fixture, the third-party
+``flash-linear-attention`` package:
+
+    python tests/golden/make_golden.py
+
+It imports ``models.daisy.attention.CausalSelfAttention``, ``inference.kv_cache.KVCache``
+and ``models.daisy.daisy_core.build_attn_mask`` from the reference, runs them in fp32
+on the CPU exactly the way the reference's tests do (``tests/test_attention.py:6-13``:
+weights cast to fp32, W_o re-initialised non-zero), and stores inputs and outputs as
+``.npz``.  The fixtures travel with the repository; the reference does not.
+"""
+import os
+import sys
+
+import numpy as np
+import torch
+
+REF = os.environ.get("DAISY_REFERENCE_ROOT", "/root/reference")
+HERE = os.path.dirname(os.path.abspath(__file__))
+os.environ["DISABLE_O_ZERO_INIT"] = "1"
+sys.path.insert(0, REF)
+
+from models.daisy.attention import CausalSelfAttention, _apply_rope   # noqa: E402
+from models.daisy.daisy_core import build_attn_mask                   # noqa: E402
+from models.daisy.functional import norm                              # noqa: E402
+from inference.kv_cache import KVCache                                # noqa: E402
+
+EOS = 50256
+
+
+def make_attn(dim, heads, head_dim, seed):
+    torch.manual_seed(seed)
+    attn = CausalSelfAttention(dim=dim, num_heads=heads, head_dim=head_dim)
+    attn.qkvo_w = torch.nn.Parameter(attn.qkvo_w.float())
+    with torch.no_grad():
+        attn.qkvo_w.normal_(mean=0.0, std=dim ** -0.5)
+    return attn.eval()
+
+
+def mask_for(T, window):
+    ids = torch.zeros(1, T, dtype=torch.long)          # no EOS -> single document
+    return build_attn_mask(ids, window, EOS)
+
+
+@torch.no_grad()
+def csa_prefill_case():
+    B, T, H, D, W = 2, 96, 2, 128, 40
+    dim = H * D
+    attn = make_attn(dim, H, D, seed=0)
+    x = torch.randn(B, T, dim)
+    m = mask_for(T, W)
+    y_fwd = attn.forward(x, None, attn_mask=m)
+    y, k, v = attn.prefill(x, None, attn_mask=m)
+    assert torch.equal(y, y_fwd)
+    np.savez_compressed(os.path.join(HERE, "csa_prefill_small.npz"),
+                        x=x.numpy(), qkvo_w=attn.qkvo_w.detach().numpy(), window=W, heads=H, head_dim=D,
+                        y=y.numpy(), k=k.contiguous().numpy(), v=v.contiguous().numpy())
+
+
+@torch.no_grad()
+def csa_step_case():
+    """Step chain through the reference KVCache: capacity 8, window 4 and window 12 (> capacity),
+    21 tokens from an empty cache; then prefill of 13 tokens + bulk_write_packed + 8 steps."""
+    B, H, D, CAP, T = 1, 2, 128, 8, 21
+    dim = H * D
+    attn = make_attn(dim, H, D, seed=1)
+    x = torch.randn(B, T, dim)
+    out = dict(x=x.numpy(), qkvo_w=attn.qkvo_w.detach().numpy(), heads=H, head_dim=D, cap=CAP)
+    for window in (4, 12):
+        cache = KVCache(L=1, B=B, H=H, W=CAP, D=D, device="cpu", dtype=torch.float32)
+        ys, ks = [], []
+        for t in range(T):
+            kc, vc = cache.view(0)
+            y, k, v = attn.step(x[:, t:t + 1], kc, vc, pos=cache.t, ve=None, window=window)
+            cache.write(0, k, v)
+            cache.advance()
+            ys.append(y); ks.append(k)
+        out[f"y_steps_w{window}"] = torch.cat(ys, 1).numpy()
+        out[f"k_steps_w{window}"] = torch.cat(ks, 1).numpy()
+        out[f"ring_k_w{window}"] = cache.k[0].numpy()
+    # prefill + bulk write + steps (window 4)
+    window, P = 4, 13
+    y_p, k_p, v_p = attn.prefill(x[:, :P], None, attn_mask=mask_for(P, window))
+    cache = KVCache(L=1, B=B, H=H, W=CAP, D=D, device="cpu", dtype=torch.float32)
+    cache.bulk_write_packed(torch.stack([k_p[None], v_p[None]]), P)
+    ys = []
+    for t in range(P, T):
+        kc, vc = cache.view(0)
+        y, k, v = attn.step(x[:, t:t + 1], kc, vc, pos=cache.t, ve=None, window=window)
+        cache.write(0, k, v)
+        cache.advance()
+        ys.append(y)
+    out["y_prefill13_w4"] = y_p.numpy()
+    out["y_after_bulk_w4"] = torch.cat(ys, 1).numpy()
+    np.savez_compressed(os.path.join(HERE, "csa_step_small.npz"), **out)
+
+
+@torch.no_grad()
+def swa_inner_case():
+    """Inner functions on post-projection q,k,v with a full base-10000 RoPE table
+    (the benchmark configs name base 10000; the reference module hard-codes 1024):
+    norm -> _apply_rope -> SDPA(attn_mask, scale=0.12), as models/daisy/attention.py:121-125,145."""
+    B, T, H, D, W = 1, 200, 2, 128, 64
+    g = torch.Generator().manual_seed(2)
+    q, k, v = (torch.randn(B, T, H, D, generator=g) for _ in range(3))
+    freq = (1.0 / 10000.0) ** torch.linspace(0, 1, steps=D // 2, dtype=torch.float32)
+    theta = torch.einsum("i,j->ij", torch.arange(T, dtype=torch.float32), freq)
+    cos, sin = theta.cos(), theta.sin()
+    qn, kn, vn = norm(q), norm(k), norm(v)
+    qn = _apply_rope(qn, cos[None, :, None, :], sin[None, :, None, :])
+    kn = _apply_rope(kn, cos[None, :, None, :], sin[None, :, None, :])
+    y = torch.nn.functional.scaled_dot_product_attention(
+        qn.transpose(1, 2), kn.transpose(1, 2), vn.transpose(1, 2), is_causal=False,
+        attn_mask=mask_for(T, W), scale=0.12).transpose(1, 2)
+    np.savez_compressed(os.path.join(HERE, "swa_inner_small.npz"),
+                        q=q.numpy(), k=k.numpy(), v=v.numpy(), cos=cos.numpy(), sin=sin.numpy(), window=W,
+                        y=y.contiguous().numpy(), kn=kn.numpy(), vn=vn.numpy())
+
+
+@torch.no_grad()
+def kda_case():
+    """Third-party naive recurrence (fla.ops.kda.naive.naive_recurrent_kda, fla 0.5.1) on
+    bf16-representable inputs; q,k are L2-normalised before the call with the same formula
+    the chunk kernel applies when use_qk_l2norm_in_kernel=True."""
+    import fla
+    from fla.ops.kda.naive import naive_recurrent_kda
+    B, T, H, K, V = 1, 96, 2, 128, 128
+    g_ = torch.Generator().manual_seed(3)
+    bf = lambda t: t.bfloat16().float()
+    q, k, v = (bf(torch.randn(B, T, H, K, generator=g_)) for _ in range(3))
+    g = torch.nn.functional.logsigmoid(torch.randn(B, T, H, K, generator=g_))
+    beta = torch.sigmoid(torch.randn(B, T, H, generator=g_))
+    h0 = 0.1 * torch.randn(B, H, K, V, generator=g_)
+    l2 = lambda t: t * torch.rsqrt(t.pow(2).sum(-1, keepdim=True) + 1e-6)
+    o, s = naive_recurrent_kda(l2(q), l2(k), v, g, beta, output_final_state=True)
+    o2, s2 = naive_recurrent_kda(l2(q), l2(k), v, g, beta, initial_state=h0.clone(), output_final_state=True)
+    np.savez_compressed(os.path.join(HERE, "kda_naive_small.npz"),
+                        q=q.numpy(), k=k.numpy(), v=v.numpy(), g=g.numpy(), beta=beta.numpy(), h0=h0.numpy(),
+                        o=o.numpy(), s=s.numpy(), o_h0=o2.numpy(), s_h0=s2.numpy(), fla_version=fla.__version__)
+
+
+if __name__ == "__main__":
+    csa_prefill_case()
+    csa_step_case()
+    swa_inner_case()
+    kda_case()
+    for f in sorted(os.listdir(HERE)):
+        if f.endswith(".npz"):
+            print(f, os.path.getsize(os.path.join(HERE, f)))

@@ -1,0 +1,122 @@
+"""The CPU oracle against fixtures produced by the reference's own code
+(tests/golden/make_golden.py).  These pin the oracle; the GPU parity tests then
+compare the CUDA path with the oracle."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import swa, kda
+
+
+def _load(golden_dir, name):
+    z = np.load(os.path.join(golden_dir, name))
+    return {k: (torch.from_numpy(z[k]) if z[k].ndim else z[k].item()) for k in z.files}
+
+
+def test_csa_prefill_matches_reference(golden_dir):
+    g = _load(golden_dir, "csa_prefill_small.npz")
+    H, D, W = int(g["heads"]), int(g["head_dim"]), int(g["window"])
+    cos, sin = swa.rope_tables(D, g["x"].shape[1])
+    y, k, v = swa.csa_prefill(g["x"], g["qkvo_w"], H, D, W, cos, sin)
+    assert (y - g["y"]).abs().max().item() < 2e-5
+    assert (k - g["k"]).abs().max().item() < 1e-5
+    assert (v - g["v"]).abs().max().item() < 1e-5
+
+
+@pytest.mark.parametrize("window", [4, 12])
+def test_csa_step_chain_matches_reference(golden_dir, window):
+    g = _load(golden_dir, "csa_step_small.npz")
+    H, D, CAP = int(g["heads"]), int(g["head_dim"]), int(g["cap"])
+    x = g["x"]
+    T = x.shape[1]
+    cos, sin = swa.rope_tables(D, T)
+    cache = swa.RingKVCache(1, 1, H, CAP, D)
+    ys, ks = [], []
+    for t in range(T):
+        kc, vc = cache.view(0)
+        y, k, v = swa.csa_step(x[:, t:t + 1], g["qkvo_w"], H, D, kc, vc, cache.t, window, cos, sin)
+        cache.write(0, k, v)
+        cache.advance()
+        ys.append(y); ks.append(k)
+    assert (torch.cat(ys, 1) - g[f"y_steps_w{window}"]).abs().max().item() < 2e-5
+    assert (torch.cat(ks, 1) - g[f"k_steps_w{window}"]).abs().max().item() < 1e-5
+    assert (cache.k[0] - g[f"ring_k_w{window}"]).abs().max().item() < 1e-5
+
+
+def test_csa_bulk_write_then_steps(golden_dir):
+    g = _load(golden_dir, "csa_step_small.npz")
+    H, D, CAP = int(g["heads"]), int(g["head_dim"]), int(g["cap"])
+    x = g["x"]
+    T, P, window = x.shape[1], 13, 4
+    cos, sin = swa.rope_tables(D, T)
+    y_p, k_p, v_p = swa.csa_prefill(x[:, :P], g["qkvo_w"], H, D, window, cos, sin)
+    assert (y_p - g["y_prefill13_w4"]).abs().max().item() < 2e-5
+    cache = swa.RingKVCache(1, 1, H, CAP, D)
+    cache.bulk_write_packed(torch.stack([k_p[None], v_p[None]]), P)
+    ys = []
+    for t in range(P, T):
+        kc, vc = cache.view(0)
+        y, k, v = swa.csa_step(x[:, t:t + 1], g["qkvo_w"], H, D, kc, vc, cache.t, window, cos, sin)
+        cache.write(0, k, v)
+        cache.advance()
+        ys.append(y)
+    assert (torch.cat(ys, 1) - g["y_after_bulk_w4"]).abs().max().item() < 2e-5
+
+
+def test_swa_inner_base10000(golden_dir):
+    g = _load(golden_dir, "swa_inner_small.npz")
+    y, kn, vn = swa.swa_prefill(g["q"], g["k"], g["v"], g["cos"], g["sin"], int(g["window"]), block=64)
+    assert (y - g["y"]).abs().max().item() < 2e-5
+    assert (kn.permute(0, 2, 1, 3) - g["kn"]).abs().max().item() < 1e-5
+    assert (vn.permute(0, 2, 1, 3) - g["vn"]).abs().max().item() < 1e-5
+
+
+def test_blockwise_equals_dense_mask():
+    torch.manual_seed(0)
+    B, T, H, D, W = 1, 150, 1, 16, 37
+    q, k, v = (torch.randn(B, T, H, D) for _ in range(3))
+    a = swa.attend_windowed(q, k, v, W, block=32)
+    b = swa.attend_windowed(q, k, v, W, block=1000)
+    assert (a - b).abs().max().item() < 1e-5
+    # per-token definition: keys max(0, t+1-W) .. t  (reference tests/test_attention.py:66-67)
+    t = 100
+    s = (q[0, t, 0] @ k[0, t + 1 - W:t + 1, 0].T) * swa.ATTN_SCALE
+    ref = torch.softmax(s, -1) @ v[0, t + 1 - W:t + 1, 0]
+    assert (a[0, t, 0] - ref).abs().max().item() < 1e-5
+
+
+def test_kda_matches_third_party_naive(golden_dir):
+    g = _load(golden_dir, "kda_naive_small.npz")
+    o, s = kda.kda_recurrent(g["q"], g["k"], g["v"], g["g"], g["beta"])
+    assert (o - g["o"]).abs().max().item() < 1e-5
+    assert (s - g["s"]).abs().max().item() < 1e-5
+    o, s = kda.kda_recurrent(g["q"], g["k"], g["v"], g["g"], g["beta"], initial_state=g["h0"])
+    assert (o - g["o_h0"]).abs().max().item() < 1e-5
+    assert (s - g["s_h0"]).abs().max().item() < 1e-5
+
+
+def test_kv_cache_view_order_and_contract():
+    """Ported from the reference's tests/test_kv_cache.py:105-133 (integer fills, wrap order)."""
+    W, steps, L, B, H, D = 4, 6, 2, 1, 3, 5
+    cache = swa.RingKVCache(L, B, H, W, D)
+    for t in range(steps):
+        for layer in range(L):
+            assert cache.view(layer)[0].size(1) == min(t, W)
+        new = torch.full((B, H, 1, D), float(t))
+        for layer in range(L):
+            cache.write(layer, new, new)
+        for layer in range(L):
+            got = cache.view(layer)[0][0, :, 0, 0].to(torch.int64).tolist()
+            n = min(t + 1, W)
+            assert got == list(range(max(0, t - n + 1), t + 1))
+        cache.advance()
+
+
+def test_work_counts():
+    assert swa.window_pairs(1024, 512) == 393472
+    assert swa.prefill_flops(8, 8192, 16, 128, 2048) == pytest.approx(9.6214e11, rel=1e-4)
+    assert swa.prefill_flops(1, 65536, 16, 128, 8192) == pytest.approx(4.1232e12, rel=1e-4)
+    assert swa.decode_bytes(64, 16, 128, 4095) == pytest.approx(2.1485e9, rel=1e-4)
+    assert kda.kda_bytes_per_token_head() == 1540
