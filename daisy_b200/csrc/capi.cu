@@ -1,0 +1,57 @@
+// Library-level entry points and host helpers shared by the kernels' launchers.
+#include "common.cuh"
+
+extern "C" int daisy_b200_version(void) { return DAISY_B200_VERSION; }
+
+extern "C" const char* daisy_b200_strerror(int code) {
+  switch (code) {
+    case DAISY_OK: return "ok";
+    case DAISY_EINVAL: return "invalid argument";
+    case DAISY_EUNSUPPORTED: return "unsupported shape (head_dim must be 128; KDA needs K=V=128, chunk=64)";
+    case DAISY_EALIGN: return "pointer or stride not 16-byte aligned";
+    case DAISY_EWORKSPACE: return "workspace too small";
+    case DAISY_ECUDA: return "CUDA call failed";
+    case DAISY_ETIMEOUT: return "device-side bounded wait ran out";
+    case DAISY_ENODEV: return "no sm_100 CUDA device";
+    default: return "unknown daisy_b200 status";
+  }
+}
+
+extern "C" int daisy_b200_sm_count(void) {
+  int dev = 0, n = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) { (void)cudaGetLastError(); return 0; }
+  if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) { (void)cudaGetLastError(); return 0; }
+  return n;
+}
+
+namespace daisy_host {
+
+EncodeTiledFn get_encode_tiled() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn) return fn;
+  void* p = nullptr;
+  cudaDriverEntryPointQueryResult q;
+  if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+      q != cudaDriverEntryPointSuccess) {
+    (void)cudaGetLastError();
+    return nullptr;
+  }
+  fn = reinterpret_cast<EncodeTiledFn>(p);
+  return fn;
+}
+
+int make_tmap_bf16_3d(CUtensorMap* m, const void* base, uint64_t n0, uint64_t n1, uint64_t n2,
+                      uint64_t s1_bytes, uint64_t s2_bytes, uint32_t b0, uint32_t b1) {
+  EncodeTiledFn enc = get_encode_tiled();
+  if (!enc) return DAISY_ECUDA;
+  cuuint64_t dims[3] = {n0, n1, n2};
+  cuuint64_t strides[2] = {s1_bytes, s2_bytes};
+  cuuint32_t box[3] = {b0, b1, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = enc(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? DAISY_OK : DAISY_ECUDA;
+}
+
+}  // namespace daisy_host

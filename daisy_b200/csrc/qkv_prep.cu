@@ -1,0 +1,126 @@
+// q/k/v preparation (RMS norm + RoPE + [B,T,H,D] -> [B,H,T,D]) and ring-buffer row copies.
+// Both are pure HBM streaming kernels: one half-warp per 256-byte row, 16 bytes per lane.
+#include "rowops.cuh"
+
+namespace daisy {
+
+struct PrepTensor {
+  const __nv_bfloat16* in;
+  __nv_bfloat16* out;
+  int64_t sb, st, sh;
+  int do_norm, do_rope;
+};
+struct PrepParams {
+  PrepTensor t[3];
+  const float* cos;
+  const float* sin;
+  int B, T, H;
+  float eps;
+};
+
+__global__ void __launch_bounds__(256) qkv_prep_kernel(const PrepParams p) {
+  const PrepTensor& ten = p.t[blockIdx.y];
+  if (ten.in == nullptr) return;
+  const int lane = threadIdx.x & 31, sub = lane & 15;
+  const int64_t rows = (int64_t)p.B * p.T * p.H;
+  int64_t row = ((int64_t)blockIdx.x * 256 + threadIdx.x) >> 4;
+  const bool live = row < rows;
+  if (!live) row = rows - 1;                      // keep the warp converged for the shuffles
+  const int h = (int)(row % p.H);
+  const int64_t bt = row / p.H;
+  const int t = (int)(bt % p.T);
+  const int b = (int)(bt / p.T);
+  const __nv_bfloat16* src = ten.in + b * ten.sb + t * ten.st + h * ten.sh + 8 * sub;
+  float x[8];
+  unpack8(ld_stream16(src), x);
+  norm_rope_row8(x, sub, ten.do_norm, ten.do_rope, p.eps, p.cos + (int64_t)t * 64, p.sin + (int64_t)t * 64);
+  if (live) {
+    __nv_bfloat16* dst = ten.out + (((int64_t)b * p.H + h) * p.T + t) * DAISY_HEAD_DIM + 8 * sub;
+    *reinterpret_cast<uint4*>(dst) = pack8(x);
+  }
+}
+
+struct RingCopyParams {
+  char* ring; char* lin;
+  int64_t r_sb, r_sh, r_sr, l_sb, l_sh, l_sr;   // in bytes
+  int B, H, cap, n, row_bytes, to_ring;
+  int64_t first_pos;
+};
+
+__global__ void __launch_bounds__(256) ring_copy_kernel(const RingCopyParams p) {
+  const int chunks = p.row_bytes >> 4;                       // 16-byte chunks per row
+  const int64_t total = (int64_t)p.B * p.H * p.n * chunks;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int c = (int)(i % chunks);
+    int64_t r = i / chunks;
+    const int row = (int)(r % p.n); r /= p.n;
+    const int h = (int)(r % p.H);
+    const int b = (int)(r / p.H);
+    const int slot = (int)((p.first_pos + row) % p.cap);
+    char* a = p.ring + b * p.r_sb + h * p.r_sh + (int64_t)slot * p.r_sr + 16 * c;
+    char* l = p.lin + b * p.l_sb + h * p.l_sh + (int64_t)row * p.l_sr + 16 * c;
+    if (p.to_ring) *reinterpret_cast<uint4*>(a) = *reinterpret_cast<const uint4*>(l);
+    else           *reinterpret_cast<uint4*>(l) = *reinterpret_cast<const uint4*>(a);
+  }
+}
+
+}  // namespace daisy
+
+using namespace daisy;
+
+static int check_in(const void* p, int64_t sb, int64_t st, int64_t sh) {
+  if (!p) return DAISY_OK;
+  if (!daisy_aligned16(p) || (sb & 7) || (st & 7) || (sh & 7)) return DAISY_EALIGN;
+  return DAISY_OK;
+}
+
+extern "C" int daisy_b200_qkv_prep(const void* q, const void* k, const void* v,
+                                   int64_t q_sb, int64_t q_st, int64_t q_sh,
+                                   int64_t k_sb, int64_t k_st, int64_t k_sh,
+                                   int64_t v_sb, int64_t v_st, int64_t v_sh,
+                                   const float* cos, const float* sin,
+                                   void* q_out, void* k_out, void* v_out,
+                                   int B, int T, int H, int D, float eps, unsigned flags, void* stream) {
+  if (B <= 0 || T <= 0 || H <= 0) return DAISY_EINVAL;
+  if (D != DAISY_HEAD_DIM) return DAISY_EUNSUPPORTED;
+  if ((q == nullptr) != (q_out == nullptr) || (k == nullptr) != (k_out == nullptr) || (v == nullptr) != (v_out == nullptr))
+    return DAISY_EINVAL;
+  if (!q && !k && !v) return DAISY_EINVAL;
+  if ((flags & DAISY_ROPE) && (!cos || !sin)) return DAISY_EINVAL;
+  int rc;
+  if ((rc = check_in(q, q_sb, q_st, q_sh)) || (rc = check_in(k, k_sb, k_st, k_sh)) || (rc = check_in(v, v_sb, v_st, v_sh))) return rc;
+  if (!daisy_aligned16(q_out) || !daisy_aligned16(k_out) || !daisy_aligned16(v_out)) return DAISY_EALIGN;
+  if ((flags & DAISY_ROPE) && (!daisy_aligned16(cos) || !daisy_aligned16(sin))) return DAISY_EALIGN;
+  PrepParams p;
+  p.t[0] = {(const __nv_bfloat16*)q, (__nv_bfloat16*)q_out, q_sb, q_st, q_sh, (flags & DAISY_NORM_Q) ? 1 : 0, (flags & DAISY_ROPE) ? 1 : 0};
+  p.t[1] = {(const __nv_bfloat16*)k, (__nv_bfloat16*)k_out, k_sb, k_st, k_sh, (flags & DAISY_NORM_K) ? 1 : 0, (flags & DAISY_ROPE) ? 1 : 0};
+  p.t[2] = {(const __nv_bfloat16*)v, (__nv_bfloat16*)v_out, v_sb, v_st, v_sh, (flags & DAISY_NORM_V) ? 1 : 0, 0};
+  p.cos = cos; p.sin = sin; p.B = B; p.T = T; p.H = H; p.eps = eps;
+  const int64_t rows = (int64_t)B * T * H;
+  dim3 grid((unsigned)((rows + 15) / 16), 3, 1);
+  qkv_prep_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(p);
+  DAISY_CHECK_LAUNCH();
+  return DAISY_OK;
+}
+
+extern "C" int daisy_b200_ring_copy_rows(void* ring, int64_t r_sb, int64_t r_sh, int64_t r_sr,
+                                         void* lin, int64_t l_sb, int64_t l_sh, int64_t l_sr,
+                                         int B, int H, int D, int cap, int64_t first_pos, int n,
+                                         int elem_bytes, int to_ring, void* stream) {
+  if (!ring || !lin || B <= 0 || H <= 0 || D <= 0 || cap <= 0 || n < 0 || first_pos < 0) return DAISY_EINVAL;
+  if (elem_bytes != 2 && elem_bytes != 4) return DAISY_EINVAL;
+  if (n > cap) return DAISY_EINVAL;                          // rows would alias in the ring
+  if (n == 0) return DAISY_OK;
+  const int64_t e = elem_bytes;
+  if (((int64_t)D * e) & 15) return DAISY_EALIGN;
+  if (!daisy_aligned16(ring) || !daisy_aligned16(lin)) return DAISY_EALIGN;
+  const int64_t s[6] = {r_sb * e, r_sh * e, r_sr * e, l_sb * e, l_sh * e, l_sr * e};
+  for (int i = 0; i < 6; ++i) if (s[i] & 15) return DAISY_EALIGN;
+  RingCopyParams p{(char*)ring, (char*)lin, s[0], s[1], s[2], s[3], s[4], s[5], B, H, cap, n, (int)(D * e), to_ring, first_pos};
+  const int64_t total = (int64_t)B * H * n * (p.row_bytes >> 4);
+  int blocks = (int)((total + 255) / 256);
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  ring_copy_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>(p);
+  DAISY_CHECK_LAUNCH();
+  return DAISY_OK;
+}

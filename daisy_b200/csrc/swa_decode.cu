@@ -1,0 +1,263 @@
+// Sliding-window decode step over a ring-buffer KV cache: split-KV partial pass + combine pass.
+//
+// HBM-bound: per (batch, head) the step reads r context rows of K and of V (256 bytes each) once.
+// Pass 1 (grid = splits x H x B, 128 threads): each half-warp owns one 256-byte row per load
+// instruction (16 bytes per lane, two adjacent rows per warp instruction -> 512 contiguous bytes),
+// eight rows of K and of V are in flight per warp before any is consumed, the ring is indexed in
+// place (slot = start + i, minus cap on wrap), scores are reduced with xor-shuffles inside the
+// half-warp and folded into a running (max, sum, acc[128]) in the exp2 domain.  Pass 2 (grid = H x B)
+// normalises/rotates the new token's q,k,v, merges the split partials with the new row's own score,
+// writes the output and stores the new k,v row into the ring -- after every read of pass 1 has
+// completed, so a window larger than the ring capacity still sees the row it is about to overwrite.
+#include "rowops.cuh"
+
+namespace daisy {
+
+#define DEC_NEG (-1.0e30f)
+
+struct DecodeParams {
+  const __nv_bfloat16 *q, *k, *v;
+  int64_t q_sb, q_sh, k_sb, k_sh, v_sb, v_sh;
+  __nv_bfloat16 *kc, *vc;
+  int64_t c_sb, c_sh, c_sr;
+  int start_slot, r, cap, new_slot;
+  const float *cos_row, *sin_row;
+  __nv_bfloat16* out;
+  int64_t o_sb, o_sh;
+  __nv_bfloat16 *k_new_out, *v_new_out;
+  int B, H;
+  float qscale, eps;
+  unsigned flags;
+  float* ws_acc;   // [B,H,splits,128]
+  float* ws_ml;    // [B,H,splits,2]
+  int splits, rows_per_split;
+};
+
+__global__ void __launch_bounds__(128) swa_decode_partial_kernel(const DecodeParams p) {
+  const int s = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, hw = lane >> 4, sub = lane & 15;
+
+  float qf[8];
+  unpack8(*reinterpret_cast<const uint4*>(p.q + b * p.q_sb + h * p.q_sh + 8 * sub), qf);
+  norm_rope_row8(qf, sub, p.flags & DAISY_NORM_Q, p.flags & DAISY_ROPE, p.eps, p.cos_row, p.sin_row);
+#pragma unroll
+  for (int e = 0; e < 8; ++e) qf[e] *= p.qscale;
+
+  const int i0 = s * p.rows_per_split;
+  const int i1 = min(p.r, i0 + p.rows_per_split);
+  const __nv_bfloat16* kbase = p.kc + b * p.c_sb + h * p.c_sh + 8 * sub;
+  const __nv_bfloat16* vbase = p.vc + b * p.c_sb + h * p.c_sh + 8 * sub;
+
+  float m = DEC_NEG, l = 0.f, acc[8];
+#pragma unroll
+  for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+
+  for (int base = i0 + warp * 8; base < i1; base += 32) {
+    uint4 kk[4], vv[4];
+    bool valid[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int row = base + 2 * j + hw;
+      valid[j] = row < i1;
+      int slot = p.start_slot + (valid[j] ? row : i0);
+      if (slot >= p.cap) slot -= p.cap;
+      kk[j] = ld_stream16(kbase + (int64_t)slot * p.c_sr);
+      vv[j] = ld_stream16(vbase + (int64_t)slot * p.c_sr);
+    }
+    float sc[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float kf[8];
+      unpack8(kk[j], kf);
+      float d = 0.f;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) d = fmaf(qf[e], kf[e], d);
+      d = halfwarp_sum(d);
+      sc[j] = valid[j] ? d : -INFINITY;
+    }
+    const float mn = fmaxf(fmaxf(m, fmaxf(sc[0], sc[1])), fmaxf(sc[2], sc[3]));
+    const float alpha = fast_exp2(m - mn);
+    float pj[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) pj[j] = fast_exp2(sc[j] - mn);
+    l = l * alpha + (pj[0] + pj[1]) + (pj[2] + pj[3]);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc[e] *= alpha;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float vf[8];
+      unpack8(vv[j], vf);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[e] = fmaf(pj[j], vf[e], acc[e]);
+    }
+    m = mn;
+  }
+
+  // merge the two half-warps
+  {
+    const float om = __shfl_xor_sync(0xffffffffu, m, 16);
+    const float ol = __shfl_xor_sync(0xffffffffu, l, 16);
+    const float M = fmaxf(m, om);
+    const float a = fast_exp2(m - M), c = fast_exp2(om - M);
+    l = l * a + ol * c;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      const float oa = __shfl_xor_sync(0xffffffffu, acc[e], 16);
+      acc[e] = acc[e] * a + oa * c;
+    }
+    m = M;
+  }
+  __shared__ float sm_m[4], sm_l[4];
+  __shared__ __align__(16) float sm_acc[4][DAISY_HEAD_DIM];
+  if (hw == 0) {
+    *reinterpret_cast<float4*>(&sm_acc[warp][8 * sub]) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+    *reinterpret_cast<float4*>(&sm_acc[warp][8 * sub + 4]) = make_float4(acc[4], acc[5], acc[6], acc[7]);
+    if (sub == 0) { sm_m[warp] = m; sm_l[warp] = l; }
+  }
+  __syncthreads();
+  const int d = threadIdx.x;
+  const float M = fmaxf(fmaxf(sm_m[0], sm_m[1]), fmaxf(sm_m[2], sm_m[3]));
+  float a = 0.f, L = 0.f;
+#pragma unroll
+  for (int w = 0; w < 4; ++w) {
+    const float f = fast_exp2(sm_m[w] - M);
+    a = fmaf(f, sm_acc[w][d], a);
+    L = fmaf(f, sm_l[w], L);
+  }
+  const int64_t slot = ((int64_t)b * p.H + h) * p.splits + s;
+  p.ws_acc[slot * DAISY_HEAD_DIM + d] = a;
+  if (d == 0) { p.ws_ml[slot * 2] = M; p.ws_ml[slot * 2 + 1] = L; }
+}
+
+__device__ __forceinline__ float block128_sum(float x, float* red) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) x += __shfl_xor_sync(0xffffffffu, x, o);
+  __syncthreads();                                   // protect `red` from the previous use
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = x;
+  __syncthreads();
+  return (red[0] + red[1]) + (red[2] + red[3]);
+}
+
+__global__ void __launch_bounds__(128) swa_decode_combine_kernel(const DecodeParams p) {
+  const int h = blockIdx.x, b = blockIdx.y, d = threadIdx.x;
+  __shared__ float red[4];
+  __shared__ float xq[DAISY_HEAD_DIM], xk[DAISY_HEAD_DIM];
+  float q = __bfloat162float(p.q[b * p.q_sb + h * p.q_sh + d]);
+  float k = __bfloat162float(p.k[b * p.k_sb + h * p.k_sh + d]);
+  float v = __bfloat162float(p.v[b * p.v_sb + h * p.v_sh + d]);
+  const float inv_d = 1.0f / DAISY_HEAD_DIM;
+  if (p.flags & DAISY_NORM_Q) q *= rsqrtf(block128_sum(q * q, red) * inv_d + p.eps);
+  if (p.flags & DAISY_NORM_K) k *= rsqrtf(block128_sum(k * k, red) * inv_d + p.eps);
+  if (p.flags & DAISY_NORM_V) v *= rsqrtf(block128_sum(v * v, red) * inv_d + p.eps);
+  if (p.flags & DAISY_ROPE) {
+    xq[d] = q; xk[d] = k;
+    __syncthreads();
+    const float c = p.cos_row[d & 63], sn = p.sin_row[d & 63];
+    const float sgn = d < 64 ? 1.f : -1.f;
+    q = q * c + sgn * xq[d ^ 64] * sn;
+    k = k * c + sgn * xk[d ^ 64] * sn;
+  }
+  // the new row is used at the precision it will have in the cache
+  const __nv_bfloat16 kb = __float2bfloat16_rn(k), vb = __float2bfloat16_rn(v);
+  k = __bfloat162float(kb); v = __bfloat162float(vb);
+  const float s_self = block128_sum(q * p.qscale * k, red);
+
+  const int64_t base = ((int64_t)b * p.H + h) * p.splits;
+  float M = s_self;
+  for (int s = 0; s < p.splits; ++s) M = fmaxf(M, p.ws_ml[(base + s) * 2]);
+  float w = fast_exp2(s_self - M);
+  float num = w * v, den = w;
+  for (int s = 0; s < p.splits; ++s) {
+    const float f = fast_exp2(p.ws_ml[(base + s) * 2] - M);
+    num = fmaf(f, p.ws_acc[(base + s) * DAISY_HEAD_DIM + d], num);
+    den = fmaf(f, p.ws_ml[(base + s) * 2 + 1], den);
+  }
+  p.out[b * p.o_sb + h * p.o_sh + d] = __float2bfloat16_rn(num / den);
+  const int64_t row = ((int64_t)b * p.H + h) * DAISY_HEAD_DIM + d;
+  if (p.k_new_out) p.k_new_out[row] = kb;
+  if (p.v_new_out) p.v_new_out[row] = vb;
+  if (p.flags & DAISY_WRITE_RING) {
+    p.kc[b * p.c_sb + h * p.c_sh + (int64_t)p.new_slot * p.c_sr + d] = kb;
+    p.vc[b * p.c_sb + h * p.c_sh + (int64_t)p.new_slot * p.c_sr + d] = vb;
+  }
+}
+
+}  // namespace daisy
+
+using namespace daisy;
+
+extern "C" int daisy_b200_swa_decode_splits(int B, int H, int ctx_rows, int sm_count) {
+  if (B <= 0 || H <= 0 || ctx_rows <= 0) return 1;
+  if (sm_count <= 0) sm_count = 148;
+  const int64_t bh = (int64_t)B * H;
+  const int64_t target = (int64_t)sm_count * 16;            // 16 CTAs of 128 threads fit on one SM
+  int64_t splits = (target + bh - 1) / bh;
+  const int64_t max_by_rows = ctx_rows / 128 > 0 ? ctx_rows / 128 : 1;   // >= 4 loop trips per CTA
+  if (splits > max_by_rows) splits = max_by_rows;
+  if (splits > 64) splits = 64;
+  if (splits < 1) splits = 1;
+  return (int)splits;
+}
+
+extern "C" size_t daisy_b200_swa_decode_workspace_bytes(int B, int H, int D, int splits) {
+  if (B <= 0 || H <= 0 || D <= 0 || splits <= 0) return 0;
+  return (size_t)B * H * splits * (D + 2) * sizeof(float);
+}
+
+extern "C" int daisy_b200_swa_decode_step(const void* q_new, const void* k_new, const void* v_new,
+                                          int64_t q_sb, int64_t q_sh, int64_t k_sb, int64_t k_sh,
+                                          int64_t v_sb, int64_t v_sh,
+                                          void* kcache, void* vcache, int64_t c_sb, int64_t c_sh, int64_t c_sr,
+                                          int64_t t, int cap, int window,
+                                          const float* cos_row, const float* sin_row,
+                                          void* out, int64_t o_sb, int64_t o_sh,
+                                          void* k_new_out, void* v_new_out,
+                                          int B, int H, int D, float scale, float eps, unsigned flags,
+                                          void* workspace, size_t workspace_bytes, int splits,
+                                          int* status_word, void* stream) {
+  (void)status_word;
+  if (!q_new || !k_new || !v_new || !out || B <= 0 || H <= 0 || t < 0 || cap < 0 || splits <= 0) return DAISY_EINVAL;
+  if (D != DAISY_HEAD_DIM) return DAISY_EUNSUPPORTED;
+  if (B > 65535 || H > 65535) return DAISY_EUNSUPPORTED;
+  if ((flags & DAISY_ROPE) && (!cos_row || !sin_row)) return DAISY_EINVAL;
+  if ((flags & DAISY_WRITE_RING) && cap == 0) return DAISY_EINVAL;
+  int64_t r = t < cap ? t : cap;
+  if (window > 0 && r > (int64_t)window - 1) r = window - 1;
+  if ((r > 0 || (flags & DAISY_WRITE_RING)) && (!kcache || !vcache)) return DAISY_EINVAL;
+  if (!workspace) return DAISY_EINVAL;
+  if (workspace_bytes < daisy_b200_swa_decode_workspace_bytes(B, H, D, splits)) return DAISY_EWORKSPACE;
+  if (!daisy_aligned16(q_new) || !daisy_aligned16(k_new) || !daisy_aligned16(v_new) || !daisy_aligned16(workspace) ||
+      ((q_sb | q_sh | k_sb | k_sh | v_sb | v_sh) & 7))
+    return DAISY_EALIGN;
+  if (r > 0 && (!daisy_aligned16(kcache) || !daisy_aligned16(vcache) || ((c_sb | c_sh | c_sr) & 7))) return DAISY_EALIGN;
+  if ((flags & DAISY_ROPE) && (!daisy_aligned16(cos_row) || !daisy_aligned16(sin_row))) return DAISY_EALIGN;
+
+  DecodeParams p;
+  p.q = (const __nv_bfloat16*)q_new; p.k = (const __nv_bfloat16*)k_new; p.v = (const __nv_bfloat16*)v_new;
+  p.q_sb = q_sb; p.q_sh = q_sh; p.k_sb = k_sb; p.k_sh = k_sh; p.v_sb = v_sb; p.v_sh = v_sh;
+  p.kc = (__nv_bfloat16*)kcache; p.vc = (__nv_bfloat16*)vcache;
+  p.c_sb = c_sb; p.c_sh = c_sh; p.c_sr = c_sr;
+  p.r = (int)r; p.cap = cap;
+  p.start_slot = cap > 0 ? (int)((t - r) % cap) : 0;
+  p.new_slot = cap > 0 ? (int)(t % cap) : 0;
+  p.cos_row = cos_row; p.sin_row = sin_row;
+  p.out = (__nv_bfloat16*)out; p.o_sb = o_sb; p.o_sh = o_sh;
+  p.k_new_out = (__nv_bfloat16*)k_new_out; p.v_new_out = (__nv_bfloat16*)v_new_out;
+  p.B = B; p.H = H;
+  p.qscale = scale * 1.4426950408889634f;
+  p.eps = eps; p.flags = flags;
+  p.ws_acc = (float*)workspace;
+  p.ws_ml = p.ws_acc + (size_t)B * H * splits * DAISY_HEAD_DIM;
+  p.splits = splits;
+  int rps = (int)((r + splits - 1) / splits);
+  rps = (rps + 31) / 32 * 32;                                 // whole 32-row CTA iterations
+  if (rps == 0) rps = 32;
+  p.rows_per_split = rps;
+
+  cudaStream_t st = (cudaStream_t)stream;
+  swa_decode_partial_kernel<<<dim3(splits, H, B), 128, 0, st>>>(p);
+  DAISY_CHECK_LAUNCH();
+  swa_decode_combine_kernel<<<dim3(H, B), 128, 0, st>>>(p);
+  DAISY_CHECK_LAUNCH();
+  return DAISY_OK;
+}

@@ -1,0 +1,466 @@
+// Sliding-window causal softmax attention, prefill form, on tcgen05 tensor cores.
+//
+// One CTA owns 256 consecutive query rows of one (batch, head): two 128-row streams that share
+// every K/V tile.  Roles (320 threads):
+//   warps 0-3   softmax of stream 0 (thread = query row = TMEM lane)
+//   warps 4-7   softmax of stream 1
+//   warp  8     TMA producer: Q tiles once, then K_j, V_j tiles into a ring of 32 KB buffers
+//   warp  9     MMA issuer (one thread): S_s = Q_s K_j^T (smem x smem), O_s += P_s V_j (TMEM x smem)
+// TMEM (512 columns): S_0 [0,128) S_1 [128,256) O_0 [256,384) O_1 [384,512), fp32.  P_s (bf16,
+// two keys per column) overwrites the first 64 columns of S_s once S_s has been read.
+// Softmax is online in the exp2 domain with a lazily refreshed reference maximum: the accumulator
+// is rescaled only when the running maximum has grown by more than 8 (a factor 256), so most
+// iterations touch O only through the tensor core.  KV tiles wholly outside the window are never
+// loaded; the two partially visible tile classes (causal diagonal, trailing window edge) go through
+// the same element-wise predicate 0 <= q - k < window.
+// All mbarrier waits are bounded; a wait that runs out raises an abort flag that every role polls,
+// the CTA drains to its teardown, frees TMEM and reports DAISY_ETIMEOUT through the status word.
+#include "common.cuh"
+
+namespace daisy {
+
+constexpr int BM = 128;
+constexpr int BN = 128;
+constexpr int NSTAGE = 4;
+constexpr int TILE_BYTES = BM * DAISY_HEAD_DIM * 2;      // 32768
+constexpr int HALF_BYTES = TILE_BYTES / 2;               // one [128 x 64] swizzled box
+constexpr int PREFILL_THREADS = 320;
+constexpr int SMEM_TILES = (2 + NSTAGE) * TILE_BYTES;
+constexpr int PREFILL_SMEM = 1024 + SMEM_TILES + 256;
+constexpr float NEG_BIG = -1.0e30f;
+
+struct PrefillParams {
+  __nv_bfloat16* out;
+  int64_t o_sb, o_st, o_sh;
+  int T, H, window;
+  float scale_log2;
+  int* status;
+};
+
+struct PrefillBarriers {
+  uint64_t q_full[2];
+  uint64_t kv_full[NSTAGE];
+  uint64_t kv_empty[NSTAGE];
+  uint64_t s_full[2];
+  uint64_t p_full[2];
+  uint64_t o_full[2];
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+__device__ __forceinline__ bool key_visible(int q, int k, int window) {
+  return (k <= q) && (window <= 0 || k > q - window);
+}
+
+__global__ void __launch_bounds__(PREFILL_THREADS, 1)
+swa_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                   const __grid_constant__ CUtensorMap tm_v, const PrefillParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* q_tiles = smem;
+  uint8_t* kv_tiles = smem + 2 * TILE_BYTES;
+  PrefillBarriers* bars = reinterpret_cast<PrefillBarriers*>(smem + SMEM_TILES);
+  volatile int* abort_flag = &bars->abort_flag;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int h = blockIdx.y, b = blockIdx.z;
+  const int bh = b * p.H + h;
+  const int T = p.T, window = p.window;
+
+  // per-stream geometry
+  int q0[2], jlo_s[2], jhi_s[2];
+  bool valid[2];
+#pragma unroll
+  for (int s = 0; s < 2; ++s) {
+    q0[s] = (blockIdx.x * 2 + s) * BM;
+    valid[s] = q0[s] < T;
+    const int klo = window > 0 ? max(0, q0[s] - window + 1) : 0;
+    jlo_s[s] = valid[s] ? klo / BN : 1;
+    jhi_s[s] = valid[s] ? min(q0[s] + BM - 1, T - 1) / BN : 0;
+  }
+  const int jlo = jlo_s[0];
+  const int jhi = valid[1] ? jhi_s[1] : jhi_s[0];
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&bars->q_full[s], 1);
+      mbar_init(&bars->s_full[s], 1);
+      mbar_init(&bars->p_full[s], 128);
+      mbar_init(&bars->o_full[s], 1);
+    }
+    for (int i = 0; i < NSTAGE; ++i) { mbar_init(&bars->kv_full[i], 1); mbar_init(&bars->kv_empty[i], 1); }
+    bars->abort_flag = 0;
+    mbar_init_fence();
+  }
+  if (warp == 9) {
+    tmem_alloc(&bars->tmem_base, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = bars->tmem_base;
+
+  if (warp == 8) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      prefetch_tmap(&tm_q); prefetch_tmap(&tm_k); prefetch_tmap(&tm_v);
+      for (int s = 0; s < 2; ++s) {
+        if (!valid[s]) continue;
+        mbar_expect_tx(&bars->q_full[s], TILE_BYTES);
+        tma_load_3d(q_tiles + s * TILE_BYTES, &tm_q, &bars->q_full[s], 0, q0[s], bh);
+        tma_load_3d(q_tiles + s * TILE_BYTES + HALF_BYTES, &tm_q, &bars->q_full[s], 64, q0[s], bh);
+      }
+      int n = 0;
+      bool ok = true;
+      for (int j = jlo; j <= jhi && ok; ++j) {
+        for (int kv = 0; kv < 2; ++kv, ++n) {
+          const int stage = n % NSTAGE;
+          const uint32_t ph = (n / NSTAGE) & 1;
+          if (!mbar_wait(&bars->kv_empty[stage], ph ^ 1, abort_flag, p.status, 1)) { ok = false; break; }
+          uint8_t* dst = kv_tiles + stage * TILE_BYTES;
+          const CUtensorMap* tm = kv ? &tm_v : &tm_k;
+          mbar_expect_tx(&bars->kv_full[stage], TILE_BYTES);
+          tma_load_3d(dst, tm, &bars->kv_full[stage], 0, j * BN, bh);
+          tma_load_3d(dst + HALF_BYTES, tm, &bars->kv_full[stage], 64, j * BN, bh);
+        }
+      }
+    }
+  } else if (warp == 9) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc_qk = umma_idesc_bf16(BM, BN, 0, 0);
+      constexpr uint32_t idesc_pv = umma_idesc_bf16(BM, DAISY_HEAD_DIM, 0, 1);
+      const uint32_t q_addr = smem_u32(q_tiles), kv_addr = smem_u32(kv_tiles);
+      bool ok = true;
+      for (int j = jlo; j <= jhi + 1 && ok; ++j) {
+#pragma unroll
+        for (int s = 0; s < 2; ++s) {
+          if (!valid[s]) continue;
+          const uint32_t s_tmem = tmem_base + s * 128;
+          const uint32_t o_tmem = tmem_base + 256 + s * 128;
+          // O_s += P_s(j-1) V_{j-1}
+          if (j - 1 >= jlo_s[s] && j - 1 <= jhi_s[s]) {
+            const int it = j - 1 - jlo_s[s];
+            const int n = 2 * (j - 1 - jlo) + 1;
+            const int stage = n % NSTAGE;
+            if (!mbar_wait(&bars->p_full[s], it & 1, abort_flag, p.status, 2)) { ok = false; break; }
+            if (!mbar_wait(&bars->kv_full[stage], (n / NSTAGE) & 1, abort_flag, p.status, 3)) { ok = false; break; }
+            tc_fence_after();
+            const uint32_t v_addr = kv_addr + stage * TILE_BYTES;
+#pragma unroll
+            for (int k = 0; k < BN / 16; ++k) {
+              const uint64_t bdesc = umma_desc_sw128(v_addr + k * 2048, HALF_BYTES, 1024);
+              umma_ts(o_tmem, s_tmem + k * 8, bdesc, idesc_pv, (it > 0 || k > 0) ? 1u : 0u);
+            }
+            const bool other_uses = (s == 0) && valid[1] && (j - 1 >= jlo_s[1]) && (j - 1 <= jhi_s[1]);
+            if (!other_uses) tc_commit(&bars->kv_empty[stage]);
+            if (j - 1 == jhi_s[s]) tc_commit(&bars->o_full[s]);
+          }
+          // S_s = Q_s K_j^T
+          if (j >= jlo_s[s] && j <= jhi_s[s]) {
+            const int it = j - jlo_s[s];
+            const int n = 2 * (j - jlo);
+            const int stage = n % NSTAGE;
+            if (it == 0 && !mbar_wait(&bars->q_full[s], 0, abort_flag, p.status, 4)) { ok = false; break; }
+            if (!mbar_wait(&bars->kv_full[stage], (n / NSTAGE) & 1, abort_flag, p.status, 5)) { ok = false; break; }
+            tc_fence_after();
+            const uint32_t qa = q_addr + s * TILE_BYTES, ka = kv_addr + stage * TILE_BYTES;
+#pragma unroll
+            for (int k = 0; k < DAISY_HEAD_DIM / 16; ++k) {
+              const uint32_t off = (k >> 2) * HALF_BYTES + (k & 3) * 32;
+              umma_ss(s_tmem, umma_desc_sw128(qa + off, 16, 1024), umma_desc_sw128(ka + off, 16, 1024), idesc_qk,
+                      k > 0 ? 1u : 0u);
+            }
+            tc_commit(&bars->s_full[s]);
+            const bool other_uses = (s == 0) && valid[1] && (j >= jlo_s[1]) && (j <= jhi_s[1]);
+            if (!other_uses) tc_commit(&bars->kv_empty[stage]);
+          }
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ softmax + epilogue
+    const int s = warp >> 2, quarter = warp & 3;
+    if (valid[s]) {
+      const int row = quarter * 32 + lane;
+      const int q_row = q0[s] + row;
+      const uint32_t lane_off = (uint32_t)(quarter * 32) << 16;
+      const uint32_t s_tmem = tmem_base + lane_off + s * 128;
+      const uint32_t o_tmem = tmem_base + lane_off + 256 + s * 128;
+      const float c2 = p.scale_log2;
+      float m_ref = NEG_BIG, l = 0.f;
+      bool ok = true;
+      uint32_t r[32];
+      for (int j = jlo_s[s]; j <= jhi_s[s]; ++j) {
+        const int it = j - jlo_s[s];
+        ok = __all_sync(0xffffffffu, mbar_wait(&bars->s_full[s], it & 1, abort_flag, p.status, 6));
+        if (!ok) break;
+        tc_fence_after();
+        const int k0 = j * BN;
+        const bool full_tile = (k0 + BN - 1 <= q0[s]) && (window <= 0 || k0 > q0[s] + BM - 1 - window);
+        // pass 1: row maximum
+        float mx = -INFINITY;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          tmem_ld32(s_tmem + 32 * c, r);
+          tc_wait_ld();
+          if (full_tile) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(r[i]));
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              if (key_visible(q_row, k0 + 32 * c + i, window)) mx = fmaxf(mx, __uint_as_float(r[i]));
+          }
+        }
+        const float m_new = fmaxf(m_ref, mx * c2);
+        if (it == 0) {
+          m_ref = m_new;
+        } else if (__any_sync(0xffffffffu, m_new - m_ref > 8.0f)) {
+          const float alpha = fast_exp2(m_ref - m_new);
+          m_ref = m_new;
+          l *= alpha;
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            tmem_ld32(o_tmem + 32 * c, r);
+            tc_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+            tmem_st32(o_tmem + 32 * c, r);
+          }
+        }
+        // pass 2: P = exp2(S * c2 - m_ref), row sum, bf16 P into TMEM over S
+        float rowsum = 0.f;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          tmem_ld32(s_tmem + 32 * c, r);
+          tc_wait_ld();
+          uint32_t pk[16];
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+            float x0 = fmaf(__uint_as_float(r[i]), c2, -m_ref);
+            float x1 = fmaf(__uint_as_float(r[i + 1]), c2, -m_ref);
+            if (!full_tile) {
+              if (!key_visible(q_row, k0 + 32 * c + i, window)) x0 = -INFINITY;
+              if (!key_visible(q_row, k0 + 32 * c + i + 1, window)) x1 = -INFINITY;
+            }
+            const float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
+            rowsum += p0 + p1;
+            pk[i >> 1] = pack_bf16(p0, p1);
+          }
+          tmem_st16(s_tmem + 16 * c, pk);
+        }
+        l += rowsum;
+        tc_wait_st();
+        tc_fence_before();
+        mbar_arrive(&bars->p_full[s]);
+      }
+      if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&bars->o_full[s], 0, abort_flag, p.status, 7));
+      if (ok) {
+        tc_fence_after();
+        const float inv = 1.0f / l;
+        __nv_bfloat16* dst = p.out + b * p.o_sb + (int64_t)q_row * p.o_st + h * p.o_sh;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          tmem_ld32(o_tmem + 32 * c, r);
+          tc_wait_ld();
+          if (q_row < T) {
+#pragma unroll
+            for (int i = 0; i < 32; i += 8) {
+              uint4 o;
+              o.x = pack_bf16(__uint_as_float(r[i]) * inv, __uint_as_float(r[i + 1]) * inv);
+              o.y = pack_bf16(__uint_as_float(r[i + 2]) * inv, __uint_as_float(r[i + 3]) * inv);
+              o.z = pack_bf16(__uint_as_float(r[i + 4]) * inv, __uint_as_float(r[i + 5]) * inv);
+              o.w = pack_bf16(__uint_as_float(r[i + 6]) * inv, __uint_as_float(r[i + 7]) * inv);
+              *reinterpret_cast<uint4*>(dst + 32 * c + i) = o;
+            }
+          }
+        }
+      }
+    }
+  }
+
+  // ------------------------------------------------------------------ teardown
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 9) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Tensor-core self-test: C[128,128] = A[128,K] x B in the three operand forms the kernel above uses.
+struct SelftestParams { const __nv_bfloat16* a; float* c; int K, mode; int* status; };
+
+__global__ void __launch_bounds__(128, 1)
+umma_selftest_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
+                     const SelftestParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* a_tile = smem;
+  uint8_t* b_tile = smem + TILE_BYTES;
+  struct Bars { uint64_t full, done; uint32_t tmem_base; int abort_flag; };
+  Bars* bars = reinterpret_cast<Bars*>(smem + 2 * TILE_BYTES);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int K = p.K, mode = p.mode;
+  const int nhalf = K / 64;
+
+  if (threadIdx.x == 0) {
+    mbar_init(&bars->full, 1); mbar_init(&bars->done, 1); bars->abort_flag = 0;
+    mbar_init_fence();
+  }
+  if (warp == 0) { tmem_alloc(&bars->tmem_base, 256); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = bars->tmem_base;
+  const uint32_t lane_off = (uint32_t)(warp * 32) << 16;
+  const int row = warp * 32 + lane;
+  // mode 0/1: A is [128 rows, K] in K-major boxes of 64 columns (128 rows each, 16 KB apart).
+  // mode 0: B is [128 rows(N), K] the same way.  mode 1/2: B is [K rows, 128 cols(N)]: two boxes of
+  // [K rows x 64 cols], K*128 bytes apart.
+  const uint32_t b_half = (mode == 0) ? HALF_BYTES : (uint32_t)K * 128u;
+  if (threadIdx.x == 0) {
+    uint32_t bytes = (mode == 2 ? 0 : 128 * K * 2) + 128 * K * 2;
+    mbar_expect_tx(&bars->full, bytes);
+    if (mode != 2)
+      for (int hlf = 0; hlf < nhalf; ++hlf) tma_load_3d(a_tile + hlf * HALF_BYTES, &tm_a, &bars->full, 64 * hlf, 0, 0);
+    if (mode == 0)
+      for (int hlf = 0; hlf < nhalf; ++hlf) tma_load_3d(b_tile + hlf * HALF_BYTES, &tm_b, &bars->full, 64 * hlf, 0, 0);
+    else
+      for (int hlf = 0; hlf < 2; ++hlf) tma_load_3d(b_tile + hlf * b_half, &tm_b, &bars->full, 64 * hlf, 0, 0);
+  }
+  bool ok = true;
+  if (mode == 2) {
+    // A row -> TMEM columns [128, 128 + K/2) as packed bf16 pairs
+    const uint32_t* arow = reinterpret_cast<const uint32_t*>(p.a + (int64_t)row * K);
+    for (int c = 0; c < K / 32; ++c) {
+      uint32_t pk[16];
+#pragma unroll
+      for (int i = 0; i < 16; ++i) pk[i] = arow[16 * c + i];
+      tmem_st16(tmem_base + lane_off + 128 + 16 * c, pk);
+    }
+    tc_wait_st();
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    ok = mbar_wait(&bars->full, 0, &bars->abort_flag, p.status, 1);
+    if (ok) {
+      tc_fence_after();
+      const uint32_t aa = smem_u32(a_tile), ba = smem_u32(b_tile);
+      const uint32_t idesc = umma_idesc_bf16(128, 128, 0, mode == 0 ? 0 : 1);
+      for (int k = 0; k < K / 16; ++k) {
+        const uint32_t koff = (k >> 2) * HALF_BYTES + (k & 3) * 32;
+        const uint64_t bdesc = (mode == 0) ? umma_desc_sw128(ba + koff, 16, 1024)
+                                           : umma_desc_sw128(ba + k * 2048, b_half, 1024);
+        if (mode == 2) umma_ts(tmem_base, tmem_base + 128 + 8 * k, bdesc, idesc, k > 0);
+        else           umma_ss(tmem_base, umma_desc_sw128(aa + koff, 16, 1024), bdesc, idesc, k > 0);
+      }
+      tc_commit(&bars->done);
+    }
+  }
+  ok = __all_sync(0xffffffffu, mbar_wait(&bars->done, 0, &bars->abort_flag, p.status, 2));
+  if (ok) {
+    tc_fence_after();
+    uint32_t r[32];
+    for (int c = 0; c < 4; ++c) {
+      tmem_ld32(tmem_base + lane_off + 32 * c, r);
+      tc_wait_ld();
+      for (int i = 0; i < 32; ++i) p.c[row * 128 + 32 * c + i] = __uint_as_float(r[i]);
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) { tc_fence_after(); tmem_dealloc(tmem_base, 256); }
+}
+
+}  // namespace daisy
+
+using namespace daisy;
+
+static int ensure_smem_attr() {
+  static bool done = false;
+  if (done) return DAISY_OK;
+  if (cudaFuncSetAttribute(swa_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PREFILL_SMEM) != cudaSuccess) return DAISY_ECUDA;
+  if (cudaFuncSetAttribute(umma_selftest_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 1024 + 2 * TILE_BYTES + 64) != cudaSuccess) return DAISY_ECUDA;
+  done = true;
+  return DAISY_OK;
+}
+
+extern "C" int daisy_b200_swa_attend(const void* q, const void* k, const void* v,
+                                     void* out, int64_t o_sb, int64_t o_st, int64_t o_sh,
+                                     int B, int T, int H, int D, int window, float scale,
+                                     int* status_word, void* stream) {
+  if (!q || !k || !v || !out || B <= 0 || T <= 0 || H <= 0 || !(scale > 0.f)) return DAISY_EINVAL;
+  if (D != DAISY_HEAD_DIM) return DAISY_EUNSUPPORTED;
+  if (B > 65535 || H > 65535) return DAISY_EUNSUPPORTED;
+  if (!daisy_aligned16(q) || !daisy_aligned16(k) || !daisy_aligned16(v) || !daisy_aligned16(out) || ((o_sb | o_st | o_sh) & 7))
+    return DAISY_EALIGN;
+  if (ensure_smem_attr() != DAISY_OK) { (void)cudaGetLastError(); return DAISY_ECUDA; }
+  CUtensorMap tq, tk, tv;
+  const uint64_t s1 = (uint64_t)D * 2, s2 = (uint64_t)T * D * 2, bh = (uint64_t)B * H;
+  int rc;
+  if ((rc = daisy_host::make_tmap_bf16_3d(&tq, q, D, T, bh, s1, s2, 64, BM)) != DAISY_OK) return rc;
+  if ((rc = daisy_host::make_tmap_bf16_3d(&tk, k, D, T, bh, s1, s2, 64, BN)) != DAISY_OK) return rc;
+  if ((rc = daisy_host::make_tmap_bf16_3d(&tv, v, D, T, bh, s1, s2, 64, BN)) != DAISY_OK) return rc;
+  PrefillParams p;
+  p.out = (__nv_bfloat16*)out; p.o_sb = o_sb; p.o_st = o_st; p.o_sh = o_sh;
+  p.T = T; p.H = H; p.window = window;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  p.status = status_word;
+  dim3 grid((T + 2 * BM - 1) / (2 * BM), H, B);
+  swa_prefill_kernel<<<grid, PREFILL_THREADS, PREFILL_SMEM, (cudaStream_t)stream>>>(tq, tk, tv, p);
+  DAISY_CHECK_LAUNCH();
+  return DAISY_OK;
+}
+
+static size_t align1k(size_t x) { return (x + 1023) & ~size_t(1023); }
+
+extern "C" size_t daisy_b200_swa_prefill_workspace_bytes(int B, int T, int H, int D) {
+  if (B <= 0 || T <= 0 || H <= 0 || D <= 0) return 0;
+  return 3 * align1k((size_t)B * T * H * D * 2);
+}
+
+extern "C" int daisy_b200_swa_prefill_fwd(const void* q, const void* k, const void* v,
+                                          int64_t q_sb, int64_t q_st, int64_t q_sh,
+                                          int64_t k_sb, int64_t k_st, int64_t k_sh,
+                                          int64_t v_sb, int64_t v_st, int64_t v_sh,
+                                          const float* cos, const float* sin,
+                                          void* out, int64_t o_sb, int64_t o_st, int64_t o_sh,
+                                          void* k_out, void* v_out,
+                                          int B, int T, int H, int D, int window, float scale, float eps,
+                                          unsigned flags, void* workspace, size_t workspace_bytes,
+                                          int* status_word, void* stream) {
+  if (!q || !k || !v || !out || !workspace || B <= 0 || T <= 0 || H <= 0) return DAISY_EINVAL;
+  if (D != DAISY_HEAD_DIM) return DAISY_EUNSUPPORTED;
+  if (workspace_bytes < daisy_b200_swa_prefill_workspace_bytes(B, T, H, D)) return DAISY_EWORKSPACE;
+  if (reinterpret_cast<uintptr_t>(workspace) & 255) return DAISY_EALIGN;
+  const size_t one = align1k((size_t)B * T * H * D * 2);
+  char* ws = (char*)workspace;
+  void* qp = ws;
+  void* kp = k_out ? k_out : (void*)(ws + one);
+  void* vp = v_out ? v_out : (void*)(ws + 2 * one);
+  int rc = daisy_b200_qkv_prep(q, k, v, q_sb, q_st, q_sh, k_sb, k_st, k_sh, v_sb, v_st, v_sh, cos, sin, qp, kp, vp,
+                               B, T, H, D, eps, flags & DAISY_QKV_DEFAULT, stream);
+  if (rc != DAISY_OK) return rc;
+  return daisy_b200_swa_attend(qp, kp, vp, out, o_sb, o_st, o_sh, B, T, H, D, window, scale, status_word, stream);
+}
+
+extern "C" int daisy_b200_selftest_umma(const void* a, const void* b, float* c, int K, int mode,
+                                        int* status_word, void* stream) {
+  if (!a || !b || !c || (K != 64 && K != 128) || mode < 0 || mode > 2) return DAISY_EINVAL;
+  if (ensure_smem_attr() != DAISY_OK) { (void)cudaGetLastError(); return DAISY_ECUDA; }
+  CUtensorMap ta, tb;
+  int rc;
+  if ((rc = daisy_host::make_tmap_bf16_3d(&ta, a, K, 128, 1, (uint64_t)K * 2, (uint64_t)K * 256, 64, 128)) != DAISY_OK) return rc;
+  if (mode == 0) rc = daisy_host::make_tmap_bf16_3d(&tb, b, K, 128, 1, (uint64_t)K * 2, (uint64_t)K * 256, 64, 128);
+  else           rc = daisy_host::make_tmap_bf16_3d(&tb, b, 128, K, 1, 256, (uint64_t)K * 256, 64, K);
+  if (rc != DAISY_OK) return rc;
+  SelftestParams p{(const __nv_bfloat16*)a, c, K, mode, status_word};
+  umma_selftest_kernel<<<1, 128, 1024 + 2 * TILE_BYTES + 64, (cudaStream_t)stream>>>(ta, tb, p);
+  DAISY_CHECK_LAUNCH();
+  return DAISY_OK;
+}

@@ -1,0 +1,228 @@
+"""Tensor-level wrappers over the C ABI: torch supplies device memory and the stream, nothing else.
+
+Every function requires CUDA tensors and calls into ``libdaisy_b200.so``; there is no CPU path.
+"""
+from __future__ import annotations
+
+from typing import Optional, Tuple
+
+import torch
+
+from . import _lib
+from ._lib import (NORM_Q, NORM_K, NORM_V, ROPE, QKV_DEFAULT, WRITE_RING, KDA_L2NORM_QK, KDA_OUT_FP32)
+
+ATTN_SCALE = 0.12            # reference models/daisy/attention.py:88
+
+_status_words = {}
+
+
+def _stream(t: torch.Tensor) -> int:
+    return torch.cuda.current_stream(t.device).cuda_stream
+
+
+def status_word(device) -> torch.Tensor:
+    """Per-device int32 word that kernels write a DAISY_E* code into when a bounded wait runs out."""
+    dev = torch.device(device)
+    key = dev.index if dev.index is not None else torch.cuda.current_device()
+    if key not in _status_words:
+        _status_words[key] = torch.zeros(1, dtype=torch.int32, device=torch.device("cuda", key))
+    return _status_words[key]
+
+
+def check_device_status(device) -> None:
+    """Synchronise and raise if any kernel reported a device-side error since the last check."""
+    w = status_word(device)
+    code = int(w.item())
+    if code != 0:
+        w.zero_()
+        raise _lib.DaisyB200Error(code, "device-side status")
+
+
+def _req(t: torch.Tensor, name: str, dtype=torch.bfloat16):
+    if not t.is_cuda:
+        raise ValueError(f"{name} must be a CUDA tensor (daisy_b200 has no CPU path)")
+    if t.dtype != dtype:
+        raise TypeError(f"{name} must be {dtype}, got {t.dtype}")
+    if t.stride(-1) != 1:
+        raise ValueError(f"{name} must be contiguous in its last dimension")
+
+
+def _f32c(t: torch.Tensor, name: str) -> torch.Tensor:
+    if not t.is_cuda or t.dtype != torch.float32 or not t.is_contiguous():
+        raise ValueError(f"{name} must be a contiguous float32 CUDA tensor")
+    return t
+
+
+def qkv_prep(q, k, v, cos, sin, eps: float, flags: int = QKV_DEFAULT):
+    """RMS-norm / RoPE raw ``[B,T,H,D]`` projections into ``[B,H,T,D]``-contiguous tensors."""
+    for n, t in (("q", q), ("k", k), ("v", v)):
+        _req(t, n)
+    B, T, H, D = q.shape
+    cos, sin = _f32c(cos, "cos"), _f32c(sin, "sin")
+    assert cos.shape[0] >= T and cos.shape[1] == D // 2
+    outs = [torch.empty(B, H, T, D, dtype=torch.bfloat16, device=q.device) for _ in range(3)]
+    rc = _lib.lib().daisy_b200_qkv_prep(
+        q.data_ptr(), k.data_ptr(), v.data_ptr(),
+        q.stride(0), q.stride(1), q.stride(2), k.stride(0), k.stride(1), k.stride(2),
+        v.stride(0), v.stride(1), v.stride(2), cos.data_ptr(), sin.data_ptr(),
+        outs[0].data_ptr(), outs[1].data_ptr(), outs[2].data_ptr(), B, T, H, D, eps, flags, _stream(q))
+    _lib.check(rc, "daisy_b200_qkv_prep")
+    return tuple(outs)
+
+
+def swa_attend(q_bhtd, k_bhtd, v_bhtd, window: Optional[int], scale: float = ATTN_SCALE,
+               out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Windowed causal attention on prepared ``[B,H,T,D]`` tensors; returns ``[B,T,H,D]``."""
+    for n, t in (("q", q_bhtd), ("k", k_bhtd), ("v", v_bhtd)):
+        _req(t, n)
+        if not t.is_contiguous():
+            raise ValueError(f"{n} must be [B,H,T,D] contiguous")
+    B, H, T, D = q_bhtd.shape
+    if out is None:
+        out = torch.empty(B, T, H, D, dtype=torch.bfloat16, device=q_bhtd.device)
+    rc = _lib.lib().daisy_b200_swa_attend(
+        q_bhtd.data_ptr(), k_bhtd.data_ptr(), v_bhtd.data_ptr(), out.data_ptr(),
+        out.stride(0), out.stride(1), out.stride(2), B, T, H, D, int(window or 0), scale,
+        status_word(q_bhtd.device).data_ptr(), _stream(q_bhtd))
+    _lib.check(rc, "daisy_b200_swa_attend")
+    return out
+
+
+def swa_prefill(q, k, v, cos, sin, window: Optional[int], scale: float = ATTN_SCALE, eps: float = 1.1920929e-07,
+                flags: int = QKV_DEFAULT, workspace: Optional[torch.Tensor] = None,
+                out: Optional[torch.Tensor] = None, k_out=None, v_out=None
+                ) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """Raw projections ``[B,T,H,D]`` -> ``(y [B,T,H,D], k' [B,H,T,D], v' [B,H,T,D])``."""
+    for n, t in (("q", q), ("k", k), ("v", v)):
+        _req(t, n)
+    B, T, H, D = q.shape
+    cos, sin = _f32c(cos, "cos"), _f32c(sin, "sin")
+    assert cos.shape[0] >= T and cos.shape[1] == D // 2
+    L = _lib.lib()
+    need = L.daisy_b200_swa_prefill_workspace_bytes(B, T, H, D)
+    if workspace is None:
+        workspace = torch.empty(need, dtype=torch.uint8, device=q.device)
+    if out is None:
+        out = torch.empty(B, T, H, D, dtype=torch.bfloat16, device=q.device)
+    if k_out is None:
+        k_out = torch.empty(B, H, T, D, dtype=torch.bfloat16, device=q.device)
+    if v_out is None:
+        v_out = torch.empty(B, H, T, D, dtype=torch.bfloat16, device=q.device)
+    rc = L.daisy_b200_swa_prefill_fwd(
+        q.data_ptr(), k.data_ptr(), v.data_ptr(),
+        q.stride(0), q.stride(1), q.stride(2), k.stride(0), k.stride(1), k.stride(2),
+        v.stride(0), v.stride(1), v.stride(2), cos.data_ptr(), sin.data_ptr(),
+        out.data_ptr(), out.stride(0), out.stride(1), out.stride(2), k_out.data_ptr(), v_out.data_ptr(),
+        B, T, H, D, int(window or 0), scale, eps, flags, workspace.data_ptr(), workspace.numel(),
+        status_word(q.device).data_ptr(), _stream(q))
+    _lib.check(rc, "daisy_b200_swa_prefill_fwd")
+    return out, k_out, v_out
+
+
+def decode_splits(B: int, H: int, ctx_rows: int) -> int:
+    L = _lib.lib()
+    return L.daisy_b200_swa_decode_splits(B, H, ctx_rows, L.daisy_b200_sm_count())
+
+
+def swa_decode_step(q_new, k_new, v_new, kcache, vcache, t: int, cap: int, window: Optional[int],
+                    cos_row, sin_row, scale: float = ATTN_SCALE, eps: float = 1.1920929e-07,
+                    flags: int = QKV_DEFAULT, write_ring: bool = False, splits: Optional[int] = None,
+                    workspace: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
+                    return_new_kv: bool = True):
+    """One decode step.  ``q_new,k_new,v_new`` raw ``[B,1,H,D]``; ``kcache,vcache`` logical ``[B,H,cap,D]``
+    (any batch/head/row strides, D contiguous) holding token p in row ``p % cap``; ``t`` tokens are in it.
+    Returns ``(y [B,1,H,D], k' [B,1,H,D] or None, v' or None)``."""
+    for n, x in (("q_new", q_new), ("k_new", k_new), ("v_new", v_new)):
+        _req(x, n)
+    B, one, H, D = q_new.shape
+    assert one == 1
+    L = _lib.lib()
+    r = min(t, cap)
+    if window is not None and window > 0:
+        r = min(r, window - 1)
+    if splits is None:
+        splits = decode_splits(B, H, r)
+    need = L.daisy_b200_swa_decode_workspace_bytes(B, H, D, splits)
+    if workspace is None:
+        workspace = torch.empty(need, dtype=torch.uint8, device=q_new.device)
+    if out is None:
+        out = torch.empty(B, 1, H, D, dtype=torch.bfloat16, device=q_new.device)
+    k_o = torch.empty(B, 1, H, D, dtype=torch.bfloat16, device=q_new.device) if return_new_kv else None
+    v_o = torch.empty(B, 1, H, D, dtype=torch.bfloat16, device=q_new.device) if return_new_kv else None
+    if kcache is not None:
+        _req(kcache, "kcache"); _req(vcache, "vcache")
+        assert kcache.shape == vcache.shape and kcache.stride() == vcache.stride()
+        kc_ptr, vc_ptr = kcache.data_ptr(), vcache.data_ptr()
+        c_sb, c_sh, c_sr = kcache.stride(0), kcache.stride(1), kcache.stride(2)
+    else:
+        kc_ptr = vc_ptr = None
+        c_sb = c_sh = c_sr = 0
+    if flags & ROPE:
+        cos_row, sin_row = _f32c(cos_row, "cos_row"), _f32c(sin_row, "sin_row")
+    f = flags | (WRITE_RING if write_ring else 0)
+    rc = L.daisy_b200_swa_decode_step(
+        q_new.data_ptr(), k_new.data_ptr(), v_new.data_ptr(),
+        q_new.stride(0), q_new.stride(2), k_new.stride(0), k_new.stride(2), v_new.stride(0), v_new.stride(2),
+        kc_ptr, vc_ptr, c_sb, c_sh, c_sr, int(t), int(cap), int(window or 0),
+        cos_row.data_ptr() if cos_row is not None else None, sin_row.data_ptr() if sin_row is not None else None,
+        out.data_ptr(), out.stride(0), out.stride(2),
+        k_o.data_ptr() if k_o is not None else None, v_o.data_ptr() if v_o is not None else None,
+        B, H, D, scale, eps, f, workspace.data_ptr(), workspace.numel(), splits,
+        status_word(q_new.device).data_ptr(), _stream(q_new))
+    _lib.check(rc, "daisy_b200_swa_decode_step")
+    return out, k_o, v_o
+
+
+def ring_copy_rows(ring_bhcd, lin_bhnd, first_pos: int, to_ring: bool) -> None:
+    """Copy rows between a ring ``[B,H,cap,D]`` and a chronological ``[B,H,n,D]`` tensor (any strides
+    with D contiguous): row i of ``lin`` <-> ring row ``(first_pos + i) % cap``."""
+    assert ring_bhcd.is_cuda and lin_bhnd.is_cuda and ring_bhcd.dtype == lin_bhnd.dtype
+    assert ring_bhcd.stride(-1) == 1 and lin_bhnd.stride(-1) == 1
+    B, H, cap, D = ring_bhcd.shape
+    n = lin_bhnd.shape[2]
+    assert lin_bhnd.shape == (B, H, n, D)
+    rc = _lib.lib().daisy_b200_ring_copy_rows(
+        ring_bhcd.data_ptr(), ring_bhcd.stride(0), ring_bhcd.stride(1), ring_bhcd.stride(2),
+        lin_bhnd.data_ptr(), lin_bhnd.stride(0), lin_bhnd.stride(1), lin_bhnd.stride(2),
+        B, H, D, cap, int(first_pos), n, ring_bhcd.element_size(), 1 if to_ring else 0, _stream(ring_bhcd))
+    _lib.check(rc, "daisy_b200_ring_copy_rows")
+
+
+def kda_chunk_fwd(q, k, v, g, beta, scale: Optional[float] = None, initial_state=None,
+                  output_final_state: bool = False, l2norm_qk: bool = True, out_fp32: bool = False):
+    """KDA chunked forward.  ``q,k [B,T,H,K]`` ``v [B,T,H,V]`` bf16; ``g [B,T,H,K]`` fp32 log-decay; ``beta
+    [B,T,H]`` fp32; state ``[B,H,K,V]`` fp32.  Returns ``(o [B,T,H,V], final_state or None)``."""
+    for n, t in (("q", q), ("k", k), ("v", v)):
+        _req(t, n)
+        if not t.is_contiguous():
+            raise ValueError(f"{n} must be contiguous")
+    g, beta = _f32c(g, "g"), _f32c(beta, "beta")
+    B, T, H, K = q.shape
+    V = v.shape[-1]
+    L = _lib.lib()
+    o = torch.empty(B, T, H, V, dtype=torch.float32 if out_fp32 else torch.bfloat16, device=q.device)
+    hT = torch.empty(B, H, K, V, dtype=torch.float32, device=q.device) if output_final_state else None
+    if initial_state is not None:
+        initial_state = _f32c(initial_state, "initial_state")
+    need = L.daisy_b200_kda_workspace_bytes(B, T, H, K, V)
+    ws = torch.empty(max(need, 16), dtype=torch.uint8, device=q.device)
+    flags = (KDA_L2NORM_QK if l2norm_qk else 0) | (KDA_OUT_FP32 if out_fp32 else 0)
+    rc = L.daisy_b200_kda_chunk_fwd(
+        q.data_ptr(), k.data_ptr(), v.data_ptr(), g.data_ptr(), beta.data_ptr(),
+        initial_state.data_ptr() if initial_state is not None else None, o.data_ptr(),
+        hT.data_ptr() if hT is not None else None, B, T, H, K, V, 64,
+        float(scale) if scale is not None else 0.0, flags, ws.data_ptr(), ws.numel(),
+        status_word(q.device).data_ptr(), _stream(q))
+    _lib.check(rc, "daisy_b200_kda_chunk_fwd")
+    return o, hT
+
+
+def selftest_umma(a: torch.Tensor, b: torch.Tensor, mode: int) -> torch.Tensor:
+    """C[128,128] fp32 = A[128,K] x B (B is [128,K] for mode 0, [K,128] for modes 1 and 2)."""
+    _req(a, "a"); _req(b, "b")
+    K = a.shape[1]
+    c = torch.zeros(128, 128, dtype=torch.float32, device=a.device)
+    rc = _lib.lib().daisy_b200_selftest_umma(a.contiguous().data_ptr(), b.contiguous().data_ptr(), c.data_ptr(), K, mode,
+                                             status_word(a.device).data_ptr(), _stream(a))
+    _lib.check(rc, "daisy_b200_selftest_umma")
+    return c

@@ -1,0 +1,182 @@
+/*
+ * daisy_b200 -- C ABI of the B200 (sm_100a) attention hot path.
+ *
+ * Every entry point takes plain pointers, sizes and a CUDA stream handle
+ * (cudaStream_t passed as void*).  Unless its comment says otherwise an entry
+ * point allocates no device memory and never synchronises: it validates its
+ * arguments on the host, enqueues kernels on `stream` and returns.  Return
+ * value: DAISY_OK (0) or a negative DAISY_E* code; daisy_b200_strerror() maps it
+ * to text.  Device-side problems (a bounded wait that ran out) are reported
+ * asynchronously through `status_word`, a caller-owned int in device memory
+ * that kernels only ever write a non-zero DAISY_E* code into (the caller zeroes
+ * it and reads it after synchronising).  `status_word` may be NULL.
+ *
+ * All tensors are bf16 unless stated; strides are in ELEMENTS.  head_dim D must
+ * be 128.  The citations name the reference (jonathanmiddleton/daisy) code each
+ * entry point stands in for.
+ */
+#ifndef DAISY_B200_H
+#define DAISY_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define DAISY_B200_VERSION 100
+
+/* status codes */
+#define DAISY_OK            0
+#define DAISY_EINVAL       -1   /* bad argument (null pointer, non-positive size, bad flag)        */
+#define DAISY_EUNSUPPORTED -2   /* shape the kernels do not implement (head_dim != 128, ...)       */
+#define DAISY_EALIGN       -3   /* pointer or stride not 16-byte aligned                            */
+#define DAISY_EWORKSPACE   -4   /* workspace too small                                              */
+#define DAISY_ECUDA        -5   /* a CUDA runtime/driver call failed (launch, tensor-map encode)   */
+#define DAISY_ETIMEOUT     -6   /* device side: a bounded barrier wait ran out (status_word only)  */
+#define DAISY_ENODEV       -7   /* no CUDA device / not an sm_100 device                            */
+
+/* transform flags (what is applied to raw projected q,k,v on load) */
+#define DAISY_NORM_Q     1u     /* weightless RMS norm over D, eps given by the caller             */
+#define DAISY_NORM_K     2u
+#define DAISY_NORM_V     4u
+#define DAISY_ROPE       8u     /* rotate halves (x[:D/2], x[D/2:]) of q and k by cos/sin tables    */
+#define DAISY_QKV_DEFAULT 15u
+#define DAISY_WRITE_RING 16u    /* decode: store the new k,v row into ring slot t % cap            */
+/* KDA flags */
+#define DAISY_KDA_L2NORM_QK 1u  /* L2-normalise q and k over K inside the kernel (eps 1e-6)         */
+#define DAISY_KDA_OUT_FP32  2u  /* `o` is float32 instead of bf16                                   */
+
+int         daisy_b200_version(void);
+const char* daisy_b200_strerror(int code);
+/* Number of SMs of the current device (0 if there is none). */
+int         daisy_b200_sm_count(void);
+
+/* ---------------------------------------------------------------------------------------------
+ * q/k/v preparation: RMS-norm q,k,v over D and RoPE q,k, writing [B,H,T,D]-contiguous copies.
+ * Replaces the elementwise tail of CausalSelfAttention._calc_qkv
+ * (models/daisy/attention.py:121-125; norm = models/daisy/functional.py:6-7;
+ * _apply_rope = models/daisy/attention.py:16-20).
+ *   q,k,v      raw projections, logical [B,T,H,D], strides (s_b,s_t,s_h) each, D contiguous
+ *   cos,sin    float32 [T, D/2], row t = position of token t
+ *   *_out      [B,H,T,D] contiguous; any of the three pairs (in,out) may be NULL together
+ */
+int daisy_b200_qkv_prep(const void* q, const void* k, const void* v,
+                        int64_t q_sb, int64_t q_st, int64_t q_sh,
+                        int64_t k_sb, int64_t k_st, int64_t k_sh,
+                        int64_t v_sb, int64_t v_st, int64_t v_sh,
+                        const float* cos, const float* sin,
+                        void* q_out, void* k_out, void* v_out,
+                        int B, int T, int H, int D, float eps, unsigned flags, void* stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * Sliding-window causal softmax attention, prefill form.
+ * Replaces CausalSelfAttention._sdpa_common between the two projections
+ * (models/daisy/attention.py:141-148) with the mask of build_attn_mask
+ * (models/daisy/daisy_core.py:53-69, single document): key k is visible to query q iff
+ * 0 <= q - k < window; window <= 0 means plain causal.  Also produces what prefill()
+ * returns for the cache (models/daisy/attention.py:173-179).
+ *   q,k,v      raw projections, logical [B,T,H,D] with strides as above
+ *   out        [B,T,H,D] with strides (o_sb,o_st,o_sh)
+ *   k_out,v_out  normalised/rotated k and v, [B,H,T,D] contiguous; may be NULL (then the
+ *              copies live in the workspace only)
+ *   workspace  daisy_b200_swa_prefill_workspace_bytes(B,T,H,D) bytes, 256-byte aligned
+ */
+size_t daisy_b200_swa_prefill_workspace_bytes(int B, int T, int H, int D);
+int daisy_b200_swa_prefill_fwd(const void* q, const void* k, const void* v,
+                               int64_t q_sb, int64_t q_st, int64_t q_sh,
+                               int64_t k_sb, int64_t k_st, int64_t k_sh,
+                               int64_t v_sb, int64_t v_st, int64_t v_sh,
+                               const float* cos, const float* sin,
+                               void* out, int64_t o_sb, int64_t o_st, int64_t o_sh,
+                               void* k_out, void* v_out,
+                               int B, int T, int H, int D, int window, float scale, float eps,
+                               unsigned flags, void* workspace, size_t workspace_bytes,
+                               int* status_word, void* stream);
+
+/* The attention core alone on already-prepared [B,H,T,D]-contiguous q,k,v (what
+ * F.scaled_dot_product_attention(q_,k_,v_,attn_mask=M,scale=...) computes at
+ * models/daisy/attention.py:145). */
+int daisy_b200_swa_attend(const void* q_bhtd, const void* k_bhtd, const void* v_bhtd,
+                          void* out, int64_t o_sb, int64_t o_st, int64_t o_sh,
+                          int B, int T, int H, int D, int window, float scale,
+                          int* status_word, void* stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * Sliding-window decode step over a ring-buffer KV cache, split-KV.
+ * Replaces CausalSelfAttention.step between the projections (models/daisy/attention.py:183-200)
+ * together with KVCache.view / KVCache.write for one layer (inference/kv_cache.py:26-51):
+ * the ring is read in place, no chronological copy is made.
+ *   q_new,k_new,v_new  raw projections of the new token, logical [B,1,H,D], strides (s_b,s_h)
+ *   kcache,vcache      one layer of the ring, logical [B,H,cap,D], strides (c_sb,c_sh,c_sr);
+ *                      token p lives in row p % cap (inference/kv_cache.py:47-50)
+ *   t                  tokens already in the ring (KVCache.t); the new token has index t
+ *   window             attends the last r = min(t, cap, window-1) ring rows plus the new row
+ *                      (models/daisy/attention.py:192-195); window <= 0: r = min(t, cap)
+ *   cos_row,sin_row    float32 [D/2], the RoPE table row of position `pos` (= t in the Generator)
+ *   out                [B,1,H,D] with strides (o_sb,o_sh)
+ *   k_new_out,v_new_out  normalised/rotated new row, [B,1,H,D] contiguous, may be NULL
+ *   flags              transform flags | DAISY_WRITE_RING
+ *   workspace          daisy_b200_swa_decode_workspace_bytes(B,H,D,splits) bytes (float partials)
+ *   splits             KV splits per (b,h); daisy_b200_swa_decode_splits() suggests a value
+ * A plain chronological context [B,n,H,D] is the special case cap = n, t = n, strides of that
+ * view, without DAISY_WRITE_RING.
+ */
+int    daisy_b200_swa_decode_splits(int B, int H, int ctx_rows, int sm_count);
+size_t daisy_b200_swa_decode_workspace_bytes(int B, int H, int D, int splits);
+int daisy_b200_swa_decode_step(const void* q_new, const void* k_new, const void* v_new,
+                               int64_t q_sb, int64_t q_sh, int64_t k_sb, int64_t k_sh,
+                               int64_t v_sb, int64_t v_sh,
+                               void* kcache, void* vcache, int64_t c_sb, int64_t c_sh, int64_t c_sr,
+                               int64_t t, int cap, int window,
+                               const float* cos_row, const float* sin_row,
+                               void* out, int64_t o_sb, int64_t o_sh,
+                               void* k_new_out, void* v_new_out,
+                               int B, int H, int D, float scale, float eps, unsigned flags,
+                               void* workspace, size_t workspace_bytes, int splits,
+                               int* status_word, void* stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * Ring-buffer row copies for one layer (KVCache.view when wrapped, inference/kv_cache.py:36-42,
+ * and KVCache.bulk_write_packed, inference/kv_cache.py:57-68).
+ *   ring  logical [B,H,cap,D] strides (r_sb,r_sh,r_sr);  lin  logical [B,H,n,D] strides
+ *   (l_sb,l_sh,l_sr); row i of `lin` <-> ring row (first_pos + i) % cap.
+ *   to_ring != 0 copies lin -> ring, else ring -> lin.  elem_bytes is 2 or 4.
+ */
+int daisy_b200_ring_copy_rows(void* ring, int64_t r_sb, int64_t r_sh, int64_t r_sr,
+                              void* lin, int64_t l_sb, int64_t l_sh, int64_t l_sr,
+                              int B, int H, int D, int cap, int64_t first_pos, int n,
+                              int elem_bytes, int to_ring, void* stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * Kimi delta attention, chunked forward.  Replaces the call
+ * chunk_kda(q,k,v,g,beta,initial_state,output_final_state,use_qk_l2norm_in_kernel=True)
+ * at models/daisy/attention_kimi.py:133-134 (third-party flash-linear-attention kernel).
+ *   q,k [B,T,H,K] bf16, v [B,T,H,V] bf16, g [B,T,H,K] float32 log-decay (<= 0),
+ *   beta [B,T,H] float32, h0 / hT [B,H,K,V] float32 (nullable), o [B,T,H,V] bf16
+ *   (float32 with DAISY_KDA_OUT_FP32); all contiguous.  K = V = 128, chunk = 64.
+ *   scale <= 0 selects K^-1/2.
+ */
+size_t daisy_b200_kda_workspace_bytes(int B, int T, int H, int K, int V);
+int daisy_b200_kda_chunk_fwd(const void* q, const void* k, const void* v, const float* g,
+                             const float* beta, const float* h0, void* o, float* hT,
+                             int B, int T, int H, int K, int V, int chunk, float scale,
+                             unsigned flags, void* workspace, size_t workspace_bytes,
+                             int* status_word, void* stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * Self-test of the tensor-core building blocks (no reference counterpart): C[128,128] float32 =
+ * A[128,K] x B, through TMA-staged swizzled shared memory, tcgen05.mma and a TMEM read-back.
+ *   mode 0: B given as [128,K] row-major (K-major operand, the Q K^T form)
+ *   mode 1: B given as [K,128] row-major (MN-major operand, the P V form), A from shared memory
+ *   mode 2: as mode 1 but A is first written to TMEM as packed bf16 (the P-in-TMEM form)
+ * K must be a multiple of 64 and <= 128.  Used by the GPU tests only.
+ */
+int daisy_b200_selftest_umma(const void* a, const void* b, float* c, int K, int mode,
+                             int* status_word, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* DAISY_B200_H */

@@ -135,8 +135,9 @@ def decode_step(q_new, k_new, v_new, k_ctx, v_ctx, pos: int, window: Optional[in
     ``[B,n,H,D]`` (already normalised/rotated rows, as stored in the cache).  Uses
     the last ``r = min(n, window-1)`` context rows plus the new row.  Returns
     ``(y [B,1,H,D], k' [B,1,H,D], v' [B,1,H,D])``."""
-    qn, kn, vn = qkv_transform(q_new, k_new, v_new, cos_td[pos:pos + 1], sin_td[pos:pos + 1], eps,
-                               norm_q, norm_k, norm_v, rope)
+    c = cos_td[pos:pos + 1] if rope else None
+    s = sin_td[pos:pos + 1] if rope else None
+    qn, kn, vn = qkv_transform(q_new, k_new, v_new, c, s, eps, norm_q, norm_k, norm_v, rope)
     n = k_ctx.size(1)
     r = n if window is None else min(n, max(window - 1, 0))
     K = torch.cat([k_ctx[:, n - r:n].float(), kn], 1).permute(0, 2, 1, 3)   # [B,H,r+1,D]

@@ -1,0 +1,192 @@
+"""B200CausalSelfAttention / B200KVCache as drop-ins: the reference's own test scenarios
+(tests/test_attention.py, tests/test_causal_self_attention_equivalence.py, tests/test_kv_cache.py,
+tests/test_generator.py cache contract) re-stated for head_dim 128 on the GPU, plus the
+reference-generated fixtures."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from gpu_util import assert_close_bf16
+from oracle import swa
+
+pytestmark = pytest.mark.gpu
+
+
+def _module(dim, H, D, w=None, eps=None):
+    os.environ["DISABLE_O_ZERO_INIT"] = "1"
+    from daisy_b200 import B200CausalSelfAttention
+    m = B200CausalSelfAttention(dim=dim, num_heads=H, head_dim=D).cuda().eval()
+    if w is not None:
+        with torch.no_grad():
+            m.qkvo_w.copy_(w.to(m.qkvo_w.dtype))
+    if eps is not None:
+        m.norm_eps = eps
+    return m
+
+
+def _fixture(golden_dir, name):
+    z = np.load(os.path.join(golden_dir, name))
+    return {k: (torch.from_numpy(z[k]) if z[k].ndim else z[k].item()) for k in z.files}
+
+
+def test_prefill_matches_reference_fixture(golden_dir):
+    from daisy_b200 import WindowMask
+    g = _fixture(golden_dir, "csa_prefill_small.npz")
+    H, D, W = int(g["heads"]), int(g["head_dim"]), int(g["window"])
+    m = _module(H * D, H, D, g["qkvo_w"], eps=swa.FP32_EPS)
+    x = g["x"].bfloat16().cuda()
+    with torch.inference_mode():
+        y, k, v = m.prefill(x, None, attn_mask=WindowMask(W))
+        y_fwd = m.forward(x, None, attn_mask=WindowMask(W))
+    assert torch.equal(y, y_fwd)
+    assert k.shape == g["k"].shape and v.shape == g["v"].shape
+    # oracle on the bf16-rounded weights/activations the module actually sees
+    cos, sin = swa.rope_tables(D, x.shape[1])
+    y_o, k_o, v_o = swa.csa_prefill(x.float().cpu(), g["qkvo_w"].bfloat16().float(), H, D, W, cos, sin)
+    assert_close_bf16(y, y_o, "y vs oracle(bf16 weights)")
+    assert_close_bf16(k, k_o, "k", max_tol=4e-2)
+    assert_close_bf16(v, v_o, "v", max_tol=4e-2)
+    # and against the reference's own fp32 output
+    assert_close_bf16(y, g["y"], "y vs reference fp32", max_tol=4e-2, mean_tol=4e-3)
+
+
+@pytest.mark.parametrize("window", [4, 12])
+@pytest.mark.parametrize("fused", [False, True])
+def test_step_chain_matches_reference_fixture(golden_dir, window, fused):
+    """21 tokens from an empty cache of capacity 8 (window 4, and window 12 > capacity)."""
+    from daisy_b200 import B200KVCache
+    g = _fixture(golden_dir, "csa_step_small.npz")
+    H, D, CAP = int(g["heads"]), int(g["head_dim"]), int(g["cap"])
+    m = _module(H * D, H, D, g["qkvo_w"], eps=swa.FP32_EPS)
+    x = g["x"].bfloat16().cuda()
+    T = x.shape[1]
+    cache = B200KVCache(L=1, B=1, H=H, W=CAP, D=D, device="cuda", dtype=torch.bfloat16)
+    ys = []
+    with torch.inference_mode():
+        for t in range(T):
+            if fused:
+                y, k, v = m.step_ring(x[:, t:t + 1], cache, 0, cache.t, None, window)
+            else:
+                kc, vc = cache.view(0)
+                assert kc.size(1) == min(t, CAP)
+                y, k, v = m.step(x[:, t:t + 1], kc, vc, pos=cache.t, ve=None, window=window)
+                cache.write(0, k, v)
+            cache.advance()
+            ys.append(y)
+    y = torch.cat(ys, 1)
+    assert_close_bf16(y, g[f"y_steps_w{window}"], f"steps w={window}", max_tol=4e-2, mean_tol=4e-3)
+    assert_close_bf16(cache.k[0], g[f"ring_k_w{window}"], "ring contents", max_tol=4e-2)
+
+
+def test_bulk_write_then_steps_matches_reference_fixture(golden_dir):
+    from daisy_b200 import B200KVCache, WindowMask
+    g = _fixture(golden_dir, "csa_step_small.npz")
+    H, D, CAP = int(g["heads"]), int(g["head_dim"]), int(g["cap"])
+    m = _module(H * D, H, D, g["qkvo_w"], eps=swa.FP32_EPS)
+    x = g["x"].bfloat16().cuda()
+    T, P, window = x.shape[1], 13, 4
+    with torch.inference_mode():
+        y_p, k_p, v_p = m.prefill(x[:, :P], None, attn_mask=WindowMask(window))
+        assert_close_bf16(y_p, g["y_prefill13_w4"], "prefill", max_tol=4e-2, mean_tol=4e-3)
+        cache = B200KVCache(L=1, B=1, H=H, W=CAP, D=D, device="cuda")
+        cache.bulk_write_packed(torch.stack([k_p[None], v_p[None]]), P)
+        ys = []
+        for t in range(P, T):
+            y, _, _ = m.step_ring(x[:, t:t + 1], cache, 0, cache.t, None, window)
+            cache.advance()
+            ys.append(y)
+    assert_close_bf16(torch.cat(ys, 1), g["y_after_bulk_w4"], "after bulk", max_tol=4e-2, mean_tol=4e-3)
+
+
+@pytest.mark.parametrize("T,W", [(128, 128), (131, 128)])
+def test_forward_equals_step(T, W):
+    """tests/test_causal_self_attention_equivalence.py:15-52: full forward == token-by-token step."""
+    from daisy_b200 import WindowMask
+    torch.manual_seed(0)
+    H, D = 2, 128
+    m = _module(H * D, H, D)
+    x = torch.randn(1, T, H * D, device="cuda", dtype=torch.bfloat16)
+    with torch.inference_mode():
+        y_full = m.forward(x, None, attn_mask=WindowMask(W))
+        K = torch.empty(1, 0, H, D, device="cuda", dtype=torch.bfloat16)
+        V = torch.empty(1, 0, H, D, device="cuda", dtype=torch.bfloat16)
+        ys = []
+        for pos in range(T):
+            y, k, v = m.step(x[:, pos:pos + 1], k_ctx=K, v_ctx=V, pos=pos, ve=None, window=W)
+            K, V = torch.cat([K, k], 1), torch.cat([V, v], 1)
+            ys.append(y)
+    y_step = torch.cat(ys, 1)
+    assert y_full.shape == y_step.shape
+    assert torch.allclose(y_full.float(), y_step.float(), atol=2e-2, rtol=2e-2), \
+        f"max_err={(y_full.float() - y_step.float()).abs().max().item()}"
+
+
+def test_value_embedding_gate():
+    from daisy_b200 import B200CausalSelfAttention, WindowMask
+    os.environ["DISABLE_O_ZERO_INIT"] = "1"
+    torch.manual_seed(1)
+    H, D, T, W = 2, 128, 70, 32
+    m = B200CausalSelfAttention(H * D, H, D, receives_ve=True, layer_idx=2).cuda().eval()
+    m.norm_eps = swa.FP32_EPS
+    x = torch.randn(1, T, H * D, device="cuda", dtype=torch.bfloat16)
+    ve = torch.randn(1, T, H * D, device="cuda", dtype=torch.bfloat16)
+    with torch.inference_mode():
+        y = m.forward(x, ve, attn_mask=WindowMask(W))
+    # oracle: models/daisy/attention.py:129-139 (gate after the norm, before attention)
+    w = m.qkvo_w.detach().float().cpu()
+    q, k, v = swa.project_qkv(x.float().cpu(), w, H, D)
+    cos, sin = swa.rope_tables(D, T)
+    qn, kn, vn = swa.qkv_transform(q, k, v, cos, sin, swa.FP32_EPS)
+    gate = torch.sigmoid(m.g_ve.detach().float().cpu())
+    vn = gate * vn + (1 - gate) * ve.float().cpu().view_as(vn)
+    y_o = swa.attend_windowed(qn, kn, vn, W).reshape(1, T, H * D) @ w[3].t()
+    assert_close_bf16(y, y_o, "ve gate", max_tol=4e-2, mean_tol=4e-3)
+
+
+# ----------------------------------------------------------------------------- KV cache (tests/test_kv_cache.py)
+
+def test_kvcache_empty_view_and_reset():
+    from daisy_b200 import B200KVCache
+    L, B, H, W, D = 2, 2, 2, 3, 128
+    c = B200KVCache(L, B, H, W, D, device="cuda", dtype=torch.float32)
+    k, v = c.view(1)
+    assert k.shape == (B, 0, H, D) and v.shape == (B, 0, H, D)
+    for i in range(2):
+        c.write(0, torch.full((B, H, 1, D), 30.0 + i, device="cuda"), torch.full((B, H, 1, D), 1030.0 + i, device="cuda"))
+        c.advance()
+    c.reset_history()
+    assert c.t == 0 and c.view(0)[0].shape == (B, 0, H, D)
+
+
+@pytest.mark.parametrize("W,steps", [(4, 3), (3, 5)])
+def test_kvcache_write_and_view_order(W, steps):
+    from daisy_b200 import B200KVCache
+    L, B, H, D = 1, 2, 2, 128
+    c = B200KVCache(L, B, H, W, D, device="cuda", dtype=torch.float32)
+    vals = [20.0 + i for i in range(steps)]
+    for val in vals:
+        c.write(0, torch.full((B, H, 1, D), val, device="cuda"), torch.full((B, H, 1, D), val + 1000, device="cuda"))
+        c.advance()
+    k, v = c.view(0)
+    exp = vals[-W:]
+    assert k.shape == (B, len(exp), H, D)
+    assert k[0, :, 0, 0].tolist() == exp and v[1, :, 1, 5].tolist() == [e + 1000 for e in exp]
+
+
+def test_kvcache_accepts_b1hd_and_contract():
+    from daisy_b200 import B200KVCache
+    L, B, H, W, D, steps = 2, 1, 3, 4, 128, 6
+    c = B200KVCache(L, B, H, W, D, device="cuda", dtype=torch.bfloat16)
+    for t in range(steps):
+        for layer in range(L):
+            assert c.view(layer)[0].size(1) == min(t, W)
+        new = torch.full((B, 1, H, D), float(t), device="cuda", dtype=torch.bfloat16)   # [B,1,H,D] form
+        for layer in range(L):
+            c.write(layer, new, new)
+        for layer in range(L):
+            got = c.view(layer)[0][0, :, 0, 0].to(torch.int64).tolist()
+            n = min(t + 1, W)
+            assert got == list(range(max(0, t - n + 1), t + 1))
+        c.advance()
