@@ -1,0 +1,400 @@
+#!/usr/bin/env python
+"""Benchmark of the daisy_b200 attention hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
+
+Headline (the JSON line's metric/value): windowed causal prefill TFLOP/s on
+B=8, T=8192, 16 heads x 128, window 2048, bf16 -- one "step" = q/k/v preparation (RMS norm + RoPE)
+plus the windowed attention over one synthetic batch.  The same line carries the decode workload
+(batch 64, 16 x 128, ring capacity 32768, window 4096: tokens/s and HBM GB/s) and, when built, the KDA
+workload as sub-objects, each with its own roofline.  Multi-GPU (torchrun, one rank per GPU) is weak
+scaling: every rank runs the same per-GPU workload on its own shard of independent sequences, no
+collective on the data path; an NCCL all-gather reassembles the outputs after the timed region.
+
+`--impl reference` times the CPU oracle (the fp32 restatement of the reference's PyTorch path) on a
+bounded sample of the same workload with all host threads.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+PREFILL_C2 = dict(B=8, T=8192, H=16, D=128, window=2048)
+PREFILL_C4 = dict(B=1, T=65536, H=16, D=128, window=8192)
+DECODE_C3 = dict(B=64, H=16, D=128, cap=32768, window=4096, steps=256)
+KDA_C5 = dict(B=4, T=16384, H=16, K=128, V=128, chunk=64)
+# reduced copies of the same kernels for profiler captures (inputs still larger than L2, < 3 GB resident)
+PREFILL_SMALL = dict(B=2, T=8192, H=16, D=128, window=2048)
+DECODE_SMALL = dict(B=4, H=16, D=128, cap=32768, window=4096, steps=4)
+ROPE_BASE = 10000.0     # the benchmark configs name base 10000 (the module default is 1024, half-truncated)
+
+
+# ----------------------------------------------------------------------------- helpers
+
+def measured_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        with open(p) as f:
+            d = json.load(f)
+        return dict(hbm_gbs=float(d["hbm_gbs"]), bf16_tflops=float(d["bf16_tflops"]), which="measured")
+    return dict(hbm_gbs=6650.0, bf16_tflops=1590.0, which="fallback")
+
+
+class ClockSampler:
+    """nvidia-smi clock/throttle samples taken while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.proc = index, None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-i", str(self.index), "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out, _ = self.proc.communicate()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in out.strip().splitlines():
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1])); mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for n, v in zip(names, f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        busy = [x for x in sm if x > 0]
+        return {"sm_mhz": statistics.median(busy) if busy else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def dist_env():
+    ws = int(os.environ.get("WORLD_SIZE", "1"))
+    return ws, int(os.environ.get("RANK", "0")), int(os.environ.get("LOCAL_RANK", "0"))
+
+
+def rope_full(D, T, device):
+    from oracle import swa
+    cos, sin = swa.rope_tables(D, T, base=ROPE_BASE, truncate=False)
+    return cos.to(device), sin.to(device)
+
+
+def timed_steps(step, steps, warmup, dist):
+    """W warm-up steps, then K steps between barrier+synchronize on both sides; device time by CUDA
+    events on the launching stream; MAX over ranks."""
+    for _ in range(warmup):
+        step()
+    torch.cuda.synchronize()
+    if dist is not None:
+        dist.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    if dist is not None:
+        dist.barrier()
+    ms = e0.elapsed_time(e1)
+    if dist is not None:
+        t = torch.tensor([ms], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    return ms
+
+
+# ----------------------------------------------------------------------------- our arm: prefill
+
+def run_prefill(cfg, steps, warmup, dist, rank, world, peaks, name, lean=False):
+    from daisy_b200 import ops, _lib
+    from oracle import swa
+    B, T, H, D, W = cfg["B"], cfg["T"], cfg["H"], cfg["D"], cfg["window"]
+    dev = torch.device("cuda", torch.cuda.current_device())
+    g = torch.Generator(device=dev).manual_seed(1234 + rank)
+    q, k, v = (torch.randn(B, T, H, D, device=dev, generator=g).bfloat16() for _ in range(3))
+    cos, sin = rope_full(D, T, dev)
+    L = _lib.lib()
+    ws = torch.empty(L.daisy_b200_swa_prefill_workspace_bytes(B, T, H, D), dtype=torch.uint8, device=dev)
+    out = torch.empty(B, T, H, D, dtype=torch.bfloat16, device=dev)
+    k_out = torch.empty(B, H, T, D, dtype=torch.bfloat16, device=dev)
+    v_out = torch.empty_like(k_out)
+    flops = swa.prefill_flops(B, T, H, D, W)
+
+    def step():
+        ops.swa_prefill(q, k, v, cos, sin, W, eps=swa.FP32_EPS, workspace=ws, out=out, k_out=k_out, v_out=v_out)
+
+    sampler = ClockSampler(dev.index or 0)
+    sampler.start()
+    ms = timed_steps(step, steps, warmup, dist)
+    clocks = sampler.stop()
+    ops.check_device_status(dev)
+
+    if lean:                                                 # profiler capture: the timed loop only
+        return {"name": name, "ms_per_step": ms / steps, "tflops": world * flops / (ms / steps * 1e-3) / 1e12,
+                "clocks": clocks, "launches_per_step": 2, "roofline": None, "e2e": None,
+                "config": {"workload": f"{name}: B={B} T={T} H={H} D={D} window={W} (profiler capture case)"}}
+    # dominant kernel alone (attention on prepared tensors), CUDA events around each launch
+    qp, kp, vp = ops.qkv_prep(q, k, v, cos, sin, swa.FP32_EPS)
+    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
+    for _ in range(warmup):
+        ops.swa_attend(qp, kp, vp, W, out=out)
+    torch.cuda.synchronize()
+    for a, b in ev:
+        a.record(); ops.swa_attend(qp, kp, vp, W, out=out); b.record()
+    torch.cuda.synchronize()
+    k_ms = sum(a.elapsed_time(b) for a, b in ev) / steps
+    del qp, kp, vp
+
+    # end to end through the public call with host buffers
+    hq, hk, hv = (x.cpu().pin_memory() for x in (q, k, v))
+    hout = torch.empty(out.shape, dtype=out.dtype).pin_memory()
+
+    def e2e_step():
+        q.copy_(hq, non_blocking=True); k.copy_(hk, non_blocking=True); v.copy_(hv, non_blocking=True)
+        step()
+        hout.copy_(out, non_blocking=True)
+
+    e2e_steps = max(2, min(steps, 5))
+    e2e_ms = timed_steps(e2e_step, e2e_steps, 1, dist)
+    in_bytes = 3 * q.numel() * 2
+    out_bytes = out.numel() * 2
+
+    if dist is not None:                                      # reassemble outputs (verification only)
+        gathered = [torch.empty_like(out) for _ in range(world)]
+        dist.all_gather(gathered, out)
+        assert all(torch.isfinite(x[:, :64].float()).all() for x in gathered)
+        del gathered
+    finite = bool(torch.isfinite(out.float()).all())
+    ach = flops / (k_ms * 1e-3) / 1e12
+    return {
+        "name": name, "ms_per_step": ms / steps, "tflops": world * flops / (ms / steps * 1e-3) / 1e12,
+        "clocks": clocks, "finite": finite, "launches_per_step": 2,
+        "roofline": {"bound": "tensor", "achieved": ach, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
+                     "frac": ach / peaks["bf16_tflops"], "traffic": None, "kernel": "swa_prefill_kernel",
+                     "kernel_ms": k_ms, "peak_source": peaks["which"] + " (burst cuBLAS bf16)"},
+        "e2e": {"value": world * flops / (e2e_ms / e2e_steps * 1e-3) / 1e12, "unit": "TFLOP/s",
+                "h2d_bytes_per_step": in_bytes, "d2h_bytes_per_step": out_bytes},
+        "config": {"workload": f"{name}: B={B} T={T} H={H} D={D} window={W} causal, RMS-norm q,k,v + RoPE base "
+                               f"{int(ROPE_BASE)} fused in the step", "per_gpu_batch": B, "global_batch": B * world,
+                   "parallelism": f"dp{world} (independent sequences per GPU, no collective)",
+                   "l2": "inputs (768 MiB q,k,v) exceed L2"},
+    }
+
+
+# ----------------------------------------------------------------------------- our arm: decode
+
+def run_decode(cfg, warmup, dist, rank, world, peaks, lean=False):
+    from daisy_b200 import ops, _lib
+    from oracle import swa
+    B, H, D, cap, W, nsteps = cfg["B"], cfg["H"], cfg["D"], cfg["cap"], cfg["window"], cfg["steps"]
+    dev = torch.device("cuda", torch.cuda.current_device())
+    g = torch.Generator(device=dev).manual_seed(4321 + rank)
+    kc = torch.empty(B, H, cap, D, dtype=torch.bfloat16, device=dev)
+    vc = torch.empty_like(kc)
+    for b in range(B):
+        kc[b] = torch.randn(H, cap, D, device=dev, generator=g).bfloat16()
+        vc[b] = torch.randn(H, cap, D, device=dev, generator=g).bfloat16()
+    nq = nsteps + warmup
+    qs, ks, vs = (torch.randn(nq, B, 1, H, D, device=dev, generator=g).bfloat16() for _ in range(3))
+    cos, sin = rope_full(D, cap + nq + 128, dev)
+    L = _lib.lib()
+    splits = ops.decode_splits(B, H, W - 1)
+    ws = torch.empty(L.daisy_b200_swa_decode_workspace_bytes(B, H, D, splits), dtype=torch.uint8, device=dev)
+    out = torch.empty(nq, B, 1, H, D, dtype=torch.bfloat16, device=dev)
+    state = {"t": cap, "i": 0}                       # ring already full: every step wraps
+
+    def step():
+        t, i = state["t"], state["i"]
+        ops.swa_decode_step(qs[i], ks[i], vs[i], kc, vc, t, cap, W, cos[t], sin[t], eps=swa.FP32_EPS,
+                            write_ring=True, splits=splits, workspace=ws, out=out[i], return_new_kv=False)
+        state["t"], state["i"] = t + 1, i + 1
+
+    ms = timed_steps(step, nsteps, warmup, dist)
+    ops.check_device_status(dev)
+    per = ms / nsteps
+    byts = swa.decode_bytes(B, H, D, W - 1)
+    gbs = byts / (per * 1e-3) / 1e9
+    if lean:
+        return {"name": "decode", "ms_per_step": per, "tokens_per_s": world * B / (per * 1e-3), "hbm_gbs": gbs,
+                "steps": nsteps, "launches_per_step": 2, "roofline": None, "e2e": None,
+                "config": {"workload": f"decode: batch {B} x {H} x {D}, capacity {cap}, window {W} (profiler capture case)"}}
+    # e2e: the step's host inputs (new q,k,v rows) in, the output row back, cache resident
+    hq, hk, hv = (x[:8].cpu().pin_memory() for x in (qs, ks, vs))
+    hout = torch.empty(out[0].shape, dtype=out.dtype).pin_memory()
+    state["i"] = 0
+
+    def e2e_step():
+        i = state["i"] % 8
+        qs[i].copy_(hq[i], non_blocking=True); ks[i].copy_(hk[i], non_blocking=True); vs[i].copy_(hv[i], non_blocking=True)
+        state["i"] = i
+        step()
+        hout.copy_(out[i], non_blocking=True)
+        torch.cuda.current_stream().synchronize()           # the token must reach the host before the next one
+
+    e2e_ms = timed_steps(e2e_step, 64, 2, dist)
+    if dist is not None:
+        gathered = [torch.empty_like(out[0]) for _ in range(world)]
+        dist.all_gather(gathered, out[0])
+    return {"name": "decode_c3", "ms_per_step": per, "tokens_per_s": world * B / (per * 1e-3), "hbm_gbs": world * gbs,
+            "splits": splits, "steps": nsteps, "launches_per_step": 2, "finite": bool(torch.isfinite(out.float()).all()),
+            "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                         "frac": gbs / peaks["hbm_gbs"], "traffic": None, "kernel": "swa_decode_partial_kernel",
+                         "peak_source": peaks["which"] + " (copy bandwidth)", "frac_of_8TBs": gbs / 8000.0},
+            "e2e": {"value": world * B / (e2e_ms / 64 * 1e-3), "unit": "tokens/s",
+                    "h2d_bytes_per_step": 3 * B * H * D * 2, "d2h_bytes_per_step": B * H * D * 2},
+            "config": {"workload": f"decode_c3: batch {B} x {H} heads x {D}, ring capacity {cap}, window {W}, "
+                                   f"{nsteps} steps from t={cap} (ring wraps every step)", "per_gpu_batch": B}}
+
+
+# ----------------------------------------------------------------------------- CPU baseline / reference arm
+
+def cpu_prefill_sample(cfg, threads=None):
+    """The fp32 oracle on ONE batch row (all heads) of the prefill workload."""
+    from oracle import swa
+    if threads:
+        torch.set_num_threads(threads)
+    T, H, D, W = cfg["T"], cfg["H"], cfg["D"], cfg["window"]
+    Tcap = min(T, 8192)
+    g = torch.Generator().manual_seed(7)
+    q, k, v = (torch.randn(1, Tcap, H, D, generator=g).bfloat16().float() for _ in range(3))
+    cos, sin = swa.rope_tables(D, Tcap, base=ROPE_BASE, truncate=False)
+    t0 = time.perf_counter()
+    y, _, _ = swa.swa_prefill(q, k, v, cos, sin, W, block=256)
+    dt = time.perf_counter() - t0
+    fl = swa.prefill_flops(1, Tcap, H, D, W)
+    return {"value": fl / dt / 1e12, "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": "port",
+            "sample": f"1 of {cfg['B']} batch rows, T={Tcap}, all {H} heads, fp32 oracle, {dt:.1f} s"}, dt, fl
+
+
+def run_reference(args, world, rank):
+    if rank != 0:
+        return
+    cfg = PREFILL_C2
+    vals, fl = [], None
+    for _ in range(args.warmup if args.warmup < 2 else 1):
+        cpu_prefill_sample(cfg)
+    n = max(1, min(args.steps, 3))
+    for _ in range(n):
+        cb, dt, fl = cpu_prefill_sample(cfg)
+        vals.append(dt)
+    dt = sum(vals) / len(vals)
+    val = fl / dt / 1e12
+    cb["value"] = val
+    line = {"impl": "reference", "metric": "windowed prefill TFLOP/s", "value": val, "unit": "TFLOP/s", "n_gpus": args.gpus,
+            "steps": n, "warmup": 1, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "fp32", "data": "synthetic",
+            "config": {"workload": f"prefill_c2: B={cfg['B']} T={cfg['T']} H={cfg['H']} D={cfg['D']} window={cfg['window']}"
+                                   " (each step = bounded sample: one batch row)"},
+            "cpu_baseline": cb,
+            "e2e": {"value": val, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line), flush=True)
+
+
+# ----------------------------------------------------------------------------- main
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="all", choices=["all", "prefill_c2", "prefill_c4", "decode_c3", "kda_c5", "prefill_small", "decode_small"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    world, rank, local = dist_env()
+    if args.impl == "reference":
+        run_reference(args, world, rank)
+        return
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: daisy_b200 has no CPU path (use --impl reference for the CPU oracle)")
+    warm = max(3, args.warmup)
+    torch.cuda.set_device(local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist_mod
+        dist_mod.init_process_group("nccl", device_id=torch.device("cuda", local))
+        dist = dist_mod
+    peaks = measured_peaks()
+    res, extra = None, {}
+    want = args.workload
+    if want in ("all", "prefill_c2"):
+        res = run_prefill(PREFILL_C2, args.steps, warm, dist, rank, world, peaks, "prefill_c2")
+    if want == "prefill_small":
+        res = run_prefill(PREFILL_SMALL, args.steps, args.warmup, dist, rank, world, peaks, "prefill_small", lean=True)
+    if want == "decode_small":
+        res = run_decode(DECODE_SMALL, args.warmup, dist, rank, world, peaks, lean=True)
+    if want == "prefill_c4":
+        res = run_prefill(PREFILL_C4, max(2, args.steps // 4), warm, dist, rank, world, peaks, "prefill_c4")
+    if want in ("all", "decode_c3"):
+        torch.cuda.empty_cache()
+        d = run_decode(DECODE_C3, warm, dist, rank, world, peaks)
+        if res is None:
+            res = d
+        else:
+            extra["decode"] = d
+    if want in ("all", "kda_c5"):
+        try:
+            from bench_kda import run_kda          # present once the KDA kernels are built
+        except ImportError:
+            run_kda = None
+        if run_kda is not None:
+            torch.cuda.empty_cache()
+            kd = run_kda(KDA_C5, args.steps, warm, dist, rank, world, peaks, timed_steps)
+            if res is None:
+                res = kd
+            else:
+                extra["kda"] = kd
+    if rank == 0:
+        is_prefill = res["name"].startswith("prefill")
+        line = {
+            "metric": "windowed prefill TFLOP/s" if is_prefill else res["name"],
+            "value": res["tflops"] if is_prefill else res.get("tokens_per_s", res.get("value")),
+            "unit": "TFLOP/s" if is_prefill else res.get("unit", "tokens/s"),
+            "n_gpus": world, "steps": args.steps if is_prefill else res.get("steps", args.steps), "warmup": warm,
+            "ms_per_step": res["ms_per_step"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "bf16", "data": "synthetic", "config": res["config"], "clocks": res.get("clocks"),
+            "roofline": res["roofline"], "e2e": res["e2e"],
+            "gpu_launches": res["launches_per_step"] * (args.steps if is_prefill else res.get("steps", args.steps)),
+        }
+        if world == 1 and not args.no_cpu_baseline and not want.endswith("_small"):
+            line["cpu_baseline"] = cpu_prefill_sample(PREFILL_C2)[0]
+        else:
+            line["cpu_baseline"] = None
+        for k_, v_ in extra.items():
+            line[k_] = {kk: vv for kk, vv in v_.items() if kk not in ("name",)}
+        print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
