@@ -191,7 +191,7 @@ swa_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       const float c2 = p.scale_log2;
       float m_ref = NEG_BIG, l = 0.f;
       bool ok = true;
-      uint32_t r[32];
+      uint32_t r[128];
       for (int j = jlo_s[s]; j <= jhi_s[s]; ++j) {
         const int it = j - jlo_s[s];
         ok = __all_sync(0xffffffffu, mbar_wait(&bars->s_full[s], it & 1, abort_flag, p.status, 6));
@@ -199,20 +199,31 @@ swa_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         tc_fence_after();
         const int k0 = j * BN;
         const bool full_tile = (k0 + BN - 1 <= q0[s]) && (window <= 0 || k0 > q0[s] + BM - 1 - window);
-        // pass 1: row maximum
-        float mx = -INFINITY;
+        // whole S row into registers
+        tmem_ld32(s_tmem, r);
+        tmem_ld32(s_tmem + 32, r + 32);
+        tmem_ld32(s_tmem + 64, r + 64);
+        tmem_ld32(s_tmem + 96, r + 96);
+        tc_wait_ld();
+        if (!full_tile) {
+          // column i of this tile is visible iff lo < i <= hi
+          const int hi = q_row - k0;
+          const int lo = window > 0 ? q_row - window - k0 : -1;
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          tmem_ld32(s_tmem + 32 * c, r);
-          tc_wait_ld();
-          if (full_tile) {
+          for (int i = 0; i < 128; ++i)
+            if (!(i > lo && i <= hi)) r[i] = 0xff800000u;              // -inf
+        }
+        float mx;
+        {
+          float m0 = -INFINITY, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
 #pragma unroll
-            for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(r[i]));
-          } else {
-#pragma unroll
-            for (int i = 0; i < 32; ++i)
-              if (key_visible(q_row, k0 + 32 * c + i, window)) mx = fmaxf(mx, __uint_as_float(r[i]));
+          for (int i = 0; i < 32; i += 2) {
+            m0 = fmax3(m0, __uint_as_float(r[i]), __uint_as_float(r[i + 1]));
+            m1 = fmax3(m1, __uint_as_float(r[32 + i]), __uint_as_float(r[33 + i]));
+            m2 = fmax3(m2, __uint_as_float(r[64 + i]), __uint_as_float(r[65 + i]));
+            m3 = fmax3(m3, __uint_as_float(r[96 + i]), __uint_as_float(r[97 + i]));
           }
+          mx = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
         }
         const float m_new = fmaxf(m_ref, mx * c2);
         if (it == 0) {
@@ -221,35 +232,41 @@ swa_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
           const float alpha = fast_exp2(m_ref - m_new);
           m_ref = m_new;
           l *= alpha;
-#pragma unroll
-          for (int c = 0; c < 4; ++c) {
-            tmem_ld32(o_tmem + 32 * c, r);
+          uint32_t t16[16];
+#pragma unroll 1
+          for (int c = 0; c < 8; ++c) {
+            tmem_ld16(o_tmem + 16 * c, t16);
             tc_wait_ld();
 #pragma unroll
-            for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
-            tmem_st32(o_tmem + 32 * c, r);
+            for (int i = 0; i < 16; ++i) t16[i] = __float_as_uint(__uint_as_float(t16[i]) * alpha);
+            tmem_st16(o_tmem + 16 * c, t16);
           }
         }
-        // pass 2: P = exp2(S * c2 - m_ref), row sum, bf16 P into TMEM over S
-        float rowsum = 0.f;
+        // P = exp2(S * c2 - m_ref) as bf16 into TMEM over S; row sum in fp32
+        const uint64_t c2p = pack2f(c2, c2), nm = pack2f(-m_ref, -m_ref);
+        uint64_t sum_a = pack2f(0.f, 0.f), sum_b = sum_a;
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
-          tmem_ld32(s_tmem + 32 * c, r);
-          tc_wait_ld();
           uint32_t pk[16];
 #pragma unroll
-          for (int i = 0; i < 32; i += 2) {
-            float x0 = fmaf(__uint_as_float(r[i]), c2, -m_ref);
-            float x1 = fmaf(__uint_as_float(r[i + 1]), c2, -m_ref);
-            if (!full_tile) {
-              if (!key_visible(q_row, k0 + 32 * c + i, window)) x0 = -INFINITY;
-              if (!key_visible(q_row, k0 + 32 * c + i + 1, window)) x1 = -INFINITY;
-            }
-            const float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
-            rowsum += p0 + p1;
+          for (int i = 0; i < 32; i += 4) {
+            float x0, x1, x2, x3;
+            unpack2f(ffma2(pack2f(__uint_as_float(r[32 * c + i]), __uint_as_float(r[32 * c + i + 1])), c2p, nm), x0, x1);
+            unpack2f(ffma2(pack2f(__uint_as_float(r[32 * c + i + 2]), __uint_as_float(r[32 * c + i + 3])), c2p, nm), x2, x3);
+            const float p0 = fast_exp2(x0), p1 = fast_exp2(x1), p2 = fast_exp2(x2), p3 = fast_exp2(x3);
+            sum_a = fadd2(sum_a, pack2f(p0, p1));
+            sum_b = fadd2(sum_b, pack2f(p2, p3));
             pk[i >> 1] = pack_bf16(p0, p1);
+            pk[(i >> 1) + 1] = pack_bf16(p2, p3);
           }
           tmem_st16(s_tmem + 16 * c, pk);
+        }
+        float rowsum;
+        {
+          float a0, a1, b0, b1;
+          unpack2f(sum_a, a0, a1);
+          unpack2f(sum_b, b0, b1);
+          rowsum = (a0 + a1) + (b0 + b1);
         }
         l += rowsum;
         tc_wait_st();
