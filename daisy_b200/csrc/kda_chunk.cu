@@ -68,15 +68,24 @@ struct KdaIntraParams {
   int l2norm;
 };
 
+#ifdef KDA_PHASE_TIMING
+__device__ long long kda_phase_clk[16];
+#define KDA_MARK(n) do { __syncthreads(); if (threadIdx.x == 0 && blockIdx.x == 1 && blockIdx.y == 0 && blockIdx.z == 0) kda_phase_clk[n] = clock64(); } while (0)
+#else
+#define KDA_MARK(n)
+#endif
+
 constexpr int LDA = 65;    // padded row (floats) of the fp32 [64 x 64] matrices
+constexpr int LDG = KD + 4;     // padded row (floats) of G: fragment gathers (8 rows x 4 column pairs) hit 32 banks
+constexpr int LDR = KD + 8;     // padded row (bf16) of the raw k / q tiles, same reason
 struct KdaIntraSmem {
-  float G[KC][KD];                 // cumulative log-decay; later the W staging image
-  __nv_bfloat16 kraw[KC][KD];      // later (with qraw) the U0^T staging image
-  __nv_bfloat16 qraw[KC][KD];
+  float G[KC][LDG];                // cumulative log-decay; later the W staging image
+  __nv_bfloat16 kraw[KC][LDR];     // later (with qraw) the U0^T staging image
+  __nv_bfloat16 qraw[KC][LDR];
   __nv_bfloat16 vraw[KC][KD];
   float Akk[KC][LDA];
   float Tm[KC][LDA];
-  float Wt[16][LDA];               // scratch of the block forward substitution
+  float Wt[16][3 * 16 + 1];        // scratch of the block forward substitution
   __half Aqk[KC][LDT];
   __half XT[KD][LDT];              // (beta k e^G)^T
   __half YT[KD][LDT];              // (beta v)^T
@@ -92,32 +101,46 @@ __global__ void __launch_bounds__(256, 1) kda_intra_kernel(const KdaIntraParams 
   const int rows = min(KC, p.T - t0);
   uint8_t* rec = p.ws + ((size_t)(b * p.H + h) * p.NC + chunk) * REC_BYTES;
 
-  // ---- P0: load the chunk (rows beyond T are zero: g = 0, beta = 0, q = k = v = 0)
+  KDA_MARK(0);
+  // ---- P0: load the chunk (rows beyond T are zero: g = 0, beta = 0, q = k = v = 0).  All of a thread's
+  //           16-byte loads are issued before the first store so that ~20 are in flight per thread.
   {
     const size_t tok0 = ((size_t)b * p.T + t0) * p.H + h;          // token row index into [B,T,H,*]
-    for (int idx = tid; idx < KC * 16; idx += 256) {               // 16-byte chunks of the bf16 tiles
-      const int r = idx >> 4, c8 = (idx & 15) * 8;
-      uint4 zq = make_uint4(0, 0, 0, 0), zk = zq, zv = zq;
+    uint4 rq_[4], rk_[4], rv_[4], rg_[8];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {                                  // 16-byte chunks of the bf16 tiles
+      const int idx = tid + u * 256, r = idx >> 4, c8 = (idx & 15) * 8;
+      rq_[u] = rk_[u] = rv_[u] = make_uint4(0, 0, 0, 0);
       if (r < rows) {
         const size_t off = (tok0 + (size_t)r * p.H) * KD + c8;
-        zq = ld_stream16(p.q + off); zk = ld_stream16(p.k + off); zv = ld_stream16(p.v + off);
+        rq_[u] = ld_stream16(p.q + off); rk_[u] = ld_stream16(p.k + off); rv_[u] = ld_stream16(p.v + off);
       }
-      *reinterpret_cast<uint4*>(&sm.qraw[r][c8]) = zq;
-      *reinterpret_cast<uint4*>(&sm.kraw[r][c8]) = zk;
-      *reinterpret_cast<uint4*>(&sm.vraw[r][c8]) = zv;
     }
-    for (int idx = tid; idx < KC * 32; idx += 256) {               // 16-byte chunks of the fp32 gate tile
-      const int r = idx >> 5, c4 = (idx & 31) * 4;
-      uint4 z = make_uint4(0, 0, 0, 0);
-      if (r < rows) z = ld_stream16(p.g + (tok0 + (size_t)r * p.H) * KD + c4);
-      *reinterpret_cast<uint4*>(&sm.G[r][c4]) = z;
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {                                  // 16-byte chunks of the fp32 gate tile
+      const int idx = tid + u * 256, r = idx >> 5, c4 = (idx & 31) * 4;
+      rg_[u] = make_uint4(0, 0, 0, 0);
+      if (r < rows) rg_[u] = ld_stream16(p.g + (tok0 + (size_t)r * p.H) * KD + c4);
     }
     if (tid < KC) sm.beta[tid] = tid < rows ? p.beta[tok0 + (size_t)tid * p.H] : 0.f;
     for (int idx = tid; idx < KC * LDT / 2; idx += 256) reinterpret_cast<uint32_t*>(&sm.Aqk[0][0])[idx] = 0u;
     for (int idx = tid; idx < KC * LDA; idx += 256) { (&sm.Akk[0][0])[idx] = 0.f; (&sm.Tm[0][0])[idx] = 0.f; }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int idx = tid + u * 256, r = idx >> 4, c8 = (idx & 15) * 8;
+      *reinterpret_cast<uint4*>(&sm.qraw[r][c8]) = rq_[u];
+      *reinterpret_cast<uint4*>(&sm.kraw[r][c8]) = rk_[u];
+      *reinterpret_cast<uint4*>(&sm.vraw[r][c8]) = rv_[u];
+    }
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      const int idx = tid + u * 256, r = idx >> 5, c4 = (idx & 31) * 4;
+      *reinterpret_cast<uint4*>(&sm.G[r][c4]) = rg_[u];
+    }
   }
   __syncthreads();
 
+  KDA_MARK(1);
   // ---- P1: cumulative gates (threads 0-127, one channel each) and L2 norms (threads 128-255)
   if (tid < KD) {
     float acc = 0.f;
@@ -140,6 +163,7 @@ __global__ void __launch_bounds__(256, 1) kda_intra_kernel(const KdaIntraParams 
   }
   __syncthreads();
 
+  KDA_MARK(2);
   // ---- P2: element-wise images: q~ and k~^T and e^{G_C} straight to the workspace, X^T and Y^T to smem
   for (int idx = tid; idx < KC * 16; idx += 256) {                 // q~[i][8 channels]
     const int i = idx >> 4, c8 = (idx & 15) * 8;
@@ -177,7 +201,11 @@ __global__ void __launch_bounds__(256, 1) kda_intra_kernel(const KdaIntraParams 
     if (j8 == 0) reinterpret_cast<float*>(rec + OFF_D)[c] = __expf(gc);
   }
 
-  // ---- P3a: diagonal 16x16 blocks, exact e^{G_i - G_j} per (pair, channel); warp = (block, row parity)
+  KDA_MARK(3);
+  // ---- P3a: diagonal 16x16 blocks, exact e^{G_i - G_j} per (pair, channel); warp = (block, row parity).
+  //           Lanes split the 128 channels (4 each); the up-to-16 (kk, qk) partial sums of one row are
+  //           reduced across the warp with a halving butterfly (31 shuffles for 32 values), after which
+  //           lane l holds pair value l: l < 16 -> kk partial of column l, l >= 16 -> qk of column l - 16.
   {
     const int I = warp >> 1, par = warp & 1;
     const int c4 = lane * 4;
@@ -190,26 +218,45 @@ __global__ void __launch_bounds__(256, 1) kda_intra_kernel(const KdaIntraParams 
         qi[e] = __bfloat162float(sm.qraw[i][c4 + e]) * sm.rq[i];
         gi[e] = sm.G[i][c4 + e];
       }
-      for (int jj = 0; jj <= ii; ++jj) {
-        const int j = I * 16 + jj;
+      float part[32];
+#pragma unroll
+      for (int jj = 0; jj < 16; ++jj) {
+        // branch-free so the 16 columns overlap; columns above the diagonal are discarded below
         float pk = 0.f, pq = 0.f;
+        const int j = I * 16 + jj;
+        const float rkj = sm.rk[j];
+        const uint2 kj2 = *reinterpret_cast<const uint2*>(&sm.kraw[j][c4]);
+        const float4 gj = *reinterpret_cast<const float4*>(&sm.G[j][c4]);
+        const float kj[4] = {bf16_lo(kj2.x), bf16_hi(kj2.x), bf16_lo(kj2.y), bf16_hi(kj2.y)};
+        const float gjv[4] = {gj.x, gj.y, gj.z, gj.w};
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-          const float w = __bfloat162float(sm.kraw[j][c4 + e]) * sm.rk[j] * __expf(gi[e] - sm.G[j][c4 + e]);
+          const float w = kj[e] * rkj * __expf(fminf(gi[e] - gjv[e], 0.f));
           pk = fmaf(ki[e], w, pk); pq = fmaf(qi[e], w, pq);
         }
+        part[jj] = pk; part[16 + jj] = pq;
+      }
+      // butterfly: after the step with offset o, lanes with (lane & o) keep the upper half of the values
 #pragma unroll
-        for (int o = 16; o > 0; o >>= 1) {
-          pk += __shfl_xor_sync(0xffffffffu, pk, o);
-          pq += __shfl_xor_sync(0xffffffffu, pq, o);
+      for (int o = 16, n = 32; o > 0; o >>= 1, n >>= 1) {
+        const bool up = (lane & o) != 0;
+#pragma unroll
+        for (int x = 0; x < n / 2; ++x) {
+          const float mine = up ? part[x + n / 2] : part[x];
+          const float give = up ? part[x] : part[x + n / 2];
+          part[x] = mine + __shfl_xor_sync(0xffffffffu, give, o);
         }
-        if (lane == 0) {
-          if (jj < ii) sm.Akk[i][j] = sm.beta[i] * pk;
-          sm.Aqk[i][j] = __float2half_rn(p.scale * pq);
-        }
+      }
+      // lane l now owns value index l (bit o of the index == bit o of the lane at every step)
+      const int jj = lane & 15;
+      if (jj <= ii) {
+        const int j = I * 16 + jj;
+        if (lane < 16) { if (jj < ii) sm.Akk[i][j] = sm.beta[i] * part[0]; }
+        else sm.Aqk[i][j] = __float2half_rn(p.scale * part[0]);
       }
     }
   }
+  KDA_MARK(4);
   // ---- P3b: off-diagonal blocks (I > J) on tensor cores; left factor e^{G_i - r_I}, right e^{r_I - G_j},
   //           r_I = G at the last row before block I, so both are <= 1.  Warps 0-5 take one block each.
   if (warp < 6) {
@@ -259,6 +306,7 @@ __global__ void __launch_bounds__(256, 1) kda_intra_kernel(const KdaIntraParams 
   }
   __syncthreads();
 
+  KDA_MARK(5);
   // ---- P4: T = (I + A_kk)^-1, fp32.  (a) the four 16x16 diagonal blocks by forward substitution
   if (warp < 4 && lane < 16) {
     const int base = warp * 16;
@@ -274,33 +322,45 @@ __global__ void __launch_bounds__(256, 1) kda_intra_kernel(const KdaIntraParams 
     for (int i = 0; i < 16; ++i) sm.Tm[base + i][base + lane] = t[i];
   }
   __syncthreads();
-  //      (b) block rows 1..3:  T_{I,:} = -T_II * (A_{I,<I} T_{<I,<I}); thread = (row r, column lane cc)
+  KDA_MARK(6);
+  //      (b) block rows 1..3:  T_{I,<I} = -T_II * (A_{I,<I} T_{<I,<I}); thread = (row r, column lane cc),
+  //          up to three 16-column blocks each.  T is zero above its diagonal, so the inner sums run over
+  //          fixed ranges and unroll.
   {
     const int r = tid >> 4, cc = tid & 15;
     for (int I = 1; I < 4; ++I) {
-      float w[3];
+      float w[3] = {0.f, 0.f, 0.f};
+      const float* arow = &sm.Akk[I * 16 + r][0];
+      for (int mb = 0; mb < I; ++mb) {
 #pragma unroll
-      for (int cb = 0; cb < 3; ++cb) {
-        w[cb] = 0.f;
-        if (cb < I) {
-          const int col = cb * 16 + cc;
-          float s = 0.f;
-          for (int m = col; m < I * 16; ++m) s = fmaf(sm.Akk[I * 16 + r][m], sm.Tm[m][col], s);
-          w[cb] = s;
+        for (int mm = 0; mm < 16; ++mm) {
+          const int m = mb * 16 + mm;
+          const float a = arow[m];
+#pragma unroll
+          for (int cb = 0; cb < 3; ++cb)
+            if (cb <= mb) w[cb] = fmaf(a, sm.Tm[m][cb * 16 + cc], w[cb]);
         }
       }
-      for (int cb = 0; cb < I; ++cb) {
-        __syncthreads();
-        sm.Wt[r][cc] = w[cb];
-        __syncthreads();
-        float s = 0.f;
-        for (int m = 0; m <= r; ++m) s = fmaf(sm.Tm[I * 16 + r][I * 16 + m], sm.Wt[m][cc], s);
-        sm.Tm[I * 16 + r][cb * 16 + cc] = -s;
+      __syncthreads();
+#pragma unroll
+      for (int cb = 0; cb < 3; ++cb) sm.Wt[r][cb * 16 + cc] = w[cb];
+      __syncthreads();
+      float s[3] = {0.f, 0.f, 0.f};
+      const float* trow = &sm.Tm[I * 16 + r][I * 16];
+#pragma unroll
+      for (int m = 0; m < 16; ++m) {
+        const float tv = trow[m];                                  // zero for m > r
+#pragma unroll
+        for (int cb = 0; cb < 3; ++cb) s[cb] = fmaf(tv, sm.Wt[m][cb * 16 + cc], s[cb]);
       }
+#pragma unroll
+      for (int cb = 0; cb < 3; ++cb)
+        if (cb < I) sm.Tm[I * 16 + r][cb * 16 + cc] = -s[cb];
       __syncthreads();
     }
   }
 
+  KDA_MARK(7);
   // ---- P5: W = T X  (warp = row block I x channel half) and U0^T = Y^T T^T (warp = 16 V rows), fp16 MMAs.
   //          G and kraw/qraw are dead: they become the staging images.
   __half* w_img = reinterpret_cast<__half*>(&sm.G[0][0]);          // [64][136]
@@ -360,6 +420,7 @@ __global__ void __launch_bounds__(256, 1) kda_intra_kernel(const KdaIntraParams 
   }
   __syncthreads();
 
+  KDA_MARK(8);
   // ---- P6: staged images -> workspace, 16 bytes per thread per store
   for (int idx = tid; idx < KC * LDW * 2 / 16; idx += 256)
     reinterpret_cast<uint4*>(rec + OFF_W)[idx] = reinterpret_cast<const uint4*>(w_img)[idx];
@@ -367,7 +428,12 @@ __global__ void __launch_bounds__(256, 1) kda_intra_kernel(const KdaIntraParams 
     reinterpret_cast<uint4*>(rec + OFF_UT)[idx] = reinterpret_cast<const uint4*>(u_img)[idx];
   for (int idx = tid; idx < KC * LDT * 2 / 16; idx += 256)
     reinterpret_cast<uint4*>(rec + OFF_AQK)[idx] = reinterpret_cast<const uint4*>(&sm.Aqk[0][0])[idx];
+  KDA_MARK(9);
 }
+
+#ifdef KDA_PHASE_TIMING
+extern "C" __global__ void kda_phase_dump(long long* out) { if (threadIdx.x < 16) out[threadIdx.x] = kda_phase_clk[threadIdx.x]; }
+#endif
 
 // =============================================================================================
 // inter-chunk state kernel
@@ -554,6 +620,10 @@ __global__ void __launch_bounds__(32 * (NW + 1), 1) kda_state_kernel(const KdaSt
 }  // namespace daisy
 
 using namespace daisy;
+
+#ifdef KDA_PHASE_TIMING
+extern "C" void daisy_b200_kda_phase_dump(long long* out, void* stream) { kda_phase_dump<<<1, 32, 0, (cudaStream_t)stream>>>(out); }
+#endif
 
 extern "C" size_t daisy_b200_kda_workspace_bytes(int B, int T, int H, int K, int V) {
   if (B <= 0 || T <= 0 || H <= 0 || K != KD || V != KD) return 0;
