@@ -95,6 +95,13 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
+def shard_bounds(n: int, world: int, rank: int):
+    """Contiguous split of n independent units (batch rows, heads, batch x heads) over the ranks."""
+    base, rem = divmod(n, world)
+    lo = rank * base + min(rank, rem)
+    return lo, lo + base + (1 if rank < rem else 0)
+
+
 def dist_env():
     ws = int(os.environ.get("WORLD_SIZE", "1"))
     return ws, int(os.environ.get("RANK", "0")), int(os.environ.get("LOCAL_RANK", "0"))
@@ -144,7 +151,7 @@ def run_prefill(cfg, steps, warmup, dist, rank, world, peaks, name, lean=False):
     L = _lib.lib()
     ws = torch.empty(L.daisy_b200_swa_prefill_workspace_bytes(B, T, H, D), dtype=torch.uint8, device=dev)
     out = torch.empty(B, T, H, D, dtype=torch.bfloat16, device=dev)
-    k_out = torch.empty(B, H, T, D, dtype=torch.bfloat16, device=dev)
+    k_out = torch.empty(B, T, H, D, dtype=torch.bfloat16, device=dev)
     v_out = torch.empty_like(k_out)
     flops = swa.prefill_flops(B, T, H, D, W)
 

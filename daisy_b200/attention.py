@@ -120,8 +120,9 @@ class B200CausalSelfAttention(nn.Module):
             torch._assert(ve is not None, "ve must be provided when receives_ve=True")
             qp, kp, vp = ops.qkv_prep(q, k, v, cos, sin, self.norm_eps)
             g = torch.sigmoid(self.g_ve).to(vp.dtype)
-            vp = g * vp + (1.0 - g) * ve.view(B, T, self.num_heads, self.head_dim).transpose(1, 2).to(vp.dtype)
-            y = ops.swa_attend(qp, kp, vp.contiguous(), window, self.attn_scale)
+            vp = g * vp + (1.0 - g) * ve.view(B, T, self.num_heads, self.head_dim).to(vp.dtype)
+            y = ops.swa_attend(qp, kp, vp, window, self.attn_scale)
+            qp, kp, vp = qp.transpose(1, 2), kp.transpose(1, 2), vp.transpose(1, 2)
         else:
             y, kp, vp = ops.swa_prefill(q, k, v, cos, sin, window, self.attn_scale, self.norm_eps)
             qp = None
@@ -138,7 +139,8 @@ class B200CausalSelfAttention(nn.Module):
         """Returns ``(y [B,T,dim], k [B,H,T,D], v [B,H,T,D])`` (models/daisy/attention.py:173-179)."""
         y, k, v, q = self._attend(x, ve, self._window_of(attn_mask))
         if debug:
-            self.last_q, self.last_k = q, k.transpose(1, 2)
+            self.last_q = None if q is None else q.transpose(1, 2)
+            self.last_k = k.transpose(1, 2)
         return y, k, v
 
     def step(self, x, k_ctx: Optional[Tensor], v_ctx: Optional[Tensor], pos: int, ve: Optional[Tensor],

@@ -54,4 +54,18 @@ int make_tmap_bf16_3d(CUtensorMap* m, const void* base, uint64_t n0, uint64_t n1
   return r == CUDA_SUCCESS ? DAISY_OK : DAISY_ECUDA;
 }
 
+int make_tmap_bf16_dthb(CUtensorMap* m, const void* base, uint64_t D, uint64_t T, uint64_t H, uint64_t B,
+                        uint64_t st_bytes, uint64_t sh_bytes, uint64_t sb_bytes, uint32_t b0, uint32_t b1) {
+  EncodeTiledFn enc = get_encode_tiled();
+  if (!enc) return DAISY_ECUDA;
+  cuuint64_t dims[4] = {D, T, H, B};
+  cuuint64_t strides[3] = {st_bytes, sh_bytes, sb_bytes};
+  cuuint32_t box[4] = {b0, b1, 1, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = enc(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? DAISY_OK : DAISY_ECUDA;
+}
+
 }  // namespace daisy_host

@@ -109,6 +109,11 @@ __device__ __forceinline__ void tma_load_3d(void* smem_dst, const CUtensorMap* m
       "cp.async.bulk.tensor.3d.shared::cta.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
       ::"r"(smem_u32(smem_dst)), "l"(m), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(z) : "memory");
 }
+__device__ __forceinline__ void tma_load_4d(void* smem_dst, const CUtensorMap* m, uint64_t* bar, int x, int y, int z, int w) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cta.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+      ::"r"(smem_u32(smem_dst)), "l"(m), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(z), "r"(w) : "memory");
+}
 __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* m, uint64_t* bar, int x, int y) {
   asm volatile(
       "cp.async.bulk.tensor.2d.shared::cta.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
@@ -168,6 +173,56 @@ __device__ __forceinline__ void umma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64
       "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
       "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
       ::"r"(d_tmem), "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+
+// Same two products with the descriptors given as (lo, hi) 32-bit halves: the issuing thread keeps the
+// constant high halves in registers and only adds small offsets to the low halves (start address >> 4),
+// so one MMA costs a handful of scalar instructions instead of rebuilding two 64-bit descriptors.
+__device__ __forceinline__ void umma_ss_lh(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo, uint32_t b_hi,
+                                           uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+      "mov.b64 da, {%1, %2};\n\tmov.b64 db, {%3, %4};\n\t"
+      "setp.ne.b32 p, %6, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n\t}"
+      ::"r"(d_tmem), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_ts_lh(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo, uint32_t b_hi,
+                                           uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t.reg .b64 db;\n\t"
+      "mov.b64 db, {%2, %3};\n\t"
+      "setp.ne.b32 p, %5, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n\t}"
+      ::"r"(d_tmem), "r"(a_tmem), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate) : "memory");
+}
+
+// Predicated forms for a warp that runs the issue loop convergently: every lane executes the surrounding
+// (warp-uniform) control flow and address arithmetic, which lets the compiler keep descriptors in uniform
+// registers; only the elected lane (`leader` != 0) actually issues.
+__device__ __forceinline__ void umma_ss_lh_p(uint32_t leader, uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo,
+                                             uint32_t b_hi, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\t.reg .b64 da, db;\n\t"
+      "mov.b64 da, {%1, %2};\n\tmov.b64 db, {%3, %4};\n\t"
+      "setp.ne.b32 p, %6, 0;\n\tsetp.ne.b32 q, %7, 0;\n\t"
+      "@q tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n\t}"
+      ::"r"(d_tmem), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate), "r"(leader) : "memory");
+}
+__device__ __forceinline__ void umma_ts_lh_p(uint32_t leader, uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo, uint32_t b_hi,
+                                             uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\t.reg .b64 db;\n\t"
+      "mov.b64 db, {%2, %3};\n\t"
+      "setp.ne.b32 p, %5, 0;\n\tsetp.ne.b32 q, %6, 0;\n\t"
+      "@q tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n\t}"
+      ::"r"(d_tmem), "r"(a_tmem), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate), "r"(leader) : "memory");
+}
+__device__ __forceinline__ void tc_commit_p(uint32_t leader, uint64_t* bar) {
+  asm volatile(
+      "{\n\t.reg .pred q;\n\tsetp.ne.b32 q, %1, 0;\n\t"
+      "@q tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t}"
+      ::"r"(smem_u32(bar)), "r"(leader) : "memory");
 }
 
 // TMEM <-> registers, 32 lanes x 32-bit, N consecutive columns per thread (thread i of warp w
@@ -244,6 +299,30 @@ __device__ __forceinline__ uint64_t fmul2(uint64_t a, uint64_t b) {
   return d;
 }
 
+// 2^x for a pair of floats on the FMA/ALU pipes instead of the MUFU: round-to-nearest split x = n + f with
+// the 1.5*2^23 trick, degree-3 minimax polynomial for 2^f on [-0.5, 0.5] (relative error 7.5e-5, far below
+// the bf16 rounding the result goes through), then n is added into the exponent field.  x is clamped to
+// >= -125 so the exponent cannot wrap; -inf therefore yields ~2^-125, harmless as an attention weight.
+__device__ __forceinline__ uint64_t exp2_poly2(uint64_t x2) {
+  float x0, x1;
+  unpack2f(x2, x0, x1);
+  x0 = fmaxf(x0, -125.f); x1 = fmaxf(x1, -125.f);
+  const uint64_t xc = pack2f(x0, x1);
+  const uint64_t magic = pack2f(12582912.f, 12582912.f);
+  const uint64_t t = fadd2(xc, magic);
+  const uint64_t n = fadd2(t, pack2f(-12582912.f, -12582912.f));
+  const uint64_t f = ffma2(n, pack2f(-1.f, -1.f), xc);
+  uint64_t pl = ffma2(f, pack2f(0.05517164617776871f, 0.05517164617776871f), pack2f(0.2426111251115799f, 0.2426111251115799f));
+  pl = ffma2(pl, f, pack2f(0.6932609677314758f, 0.6932609677314758f));
+  pl = ffma2(pl, f, pack2f(0.9999280571937561f, 0.9999280571937561f));
+  float t0, t1, p0, p1;
+  unpack2f(t, t0, t1);
+  unpack2f(pl, p0, p1);
+  const uint32_t r0 = __float_as_uint(p0) + (__float_as_uint(t0) << 23);
+  const uint32_t r1 = __float_as_uint(p1) + (__float_as_uint(t1) << 23);
+  return pack2f(__uint_as_float(r0), __uint_as_float(r1));
+}
+
 __device__ __forceinline__ bool elect_one() {
   uint32_t pred;
   asm volatile(
@@ -269,5 +348,10 @@ EncodeTiledFn get_encode_tiled();
 // (b0,b1,1), 128-byte swizzle (b0 * 2 bytes must be 128), zero fill out of bounds.
 int make_tmap_bf16_3d(CUtensorMap* m, const void* base, uint64_t n0, uint64_t n1, uint64_t n2,
                       uint64_t s1_bytes, uint64_t s2_bytes, uint32_t b0, uint32_t b1);
+
+// bf16 tensor addressed as (d, t, h, b) with d contiguous and byte strides for t, h, b; box
+// (b0, b1, 1, 1), 128-byte swizzle, zero fill out of bounds.  Covers [B,T,H,D] and [B,H,T,D] alike.
+int make_tmap_bf16_dthb(CUtensorMap* m, const void* base, uint64_t D, uint64_t T, uint64_t H, uint64_t B,
+                        uint64_t st_bytes, uint64_t sh_bytes, uint64_t sb_bytes, uint32_t b0, uint32_t b1);
 
 }  // namespace daisy_host

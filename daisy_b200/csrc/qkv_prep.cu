@@ -16,27 +16,73 @@ struct PrepParams {
   const float* sin;
   int B, T, H;
   float eps;
+  int out_bthd;
 };
 
+constexpr int PREP_ROWS = 4;     // rows per half-warp: independent loads in flight per lane
+
+// Lane `sub` of a half-warp owns elements [4 sub, 4 sub + 4) and [64 + 4 sub, 64 + 4 sub + 4) of a row: the
+// two halves RoPE pairs together, so the rotation needs no shuffle and one float4 of cos and of sin.
 __global__ void __launch_bounds__(256) qkv_prep_kernel(const PrepParams p) {
   const PrepTensor& ten = p.t[blockIdx.y];
   if (ten.in == nullptr) return;
   const int lane = threadIdx.x & 31, sub = lane & 15;
-  const int64_t rows = (int64_t)p.B * p.T * p.H;
-  int64_t row = ((int64_t)blockIdx.x * 256 + threadIdx.x) >> 4;
-  const bool live = row < rows;
-  if (!live) row = rows - 1;                      // keep the warp converged for the shuffles
-  const int h = (int)(row % p.H);
-  const int64_t bt = row / p.H;
-  const int t = (int)(bt % p.T);
-  const int b = (int)(bt / p.T);
-  const __nv_bfloat16* src = ten.in + b * ten.sb + t * ten.st + h * ten.sh + 8 * sub;
-  float x[8];
-  unpack8(ld_stream16(src), x);
-  norm_rope_row8(x, sub, ten.do_norm, ten.do_rope, p.eps, p.cos + (int64_t)t * 64, p.sin + (int64_t)t * 64);
-  if (live) {
-    __nv_bfloat16* dst = ten.out + (((int64_t)b * p.H + h) * p.T + t) * DAISY_HEAD_DIM + 8 * sub;
-    *reinterpret_cast<uint4*>(dst) = pack8(x);
+  // 32-bit row arithmetic (the host refuses B*T*H >= 2^31): one division pair per thread, then increments
+  const uint32_t rows = (uint32_t)p.B * p.T * p.H;
+  const uint32_t row0 = ((blockIdx.x * 256u + threadIdx.x) >> 4) * PREP_ROWS;
+  uint2 lo[PREP_ROWS], hi[PREP_ROWS];
+  int hh[PREP_ROWS], tt[PREP_ROWS], bb[PREP_ROWS];
+  bool live[PREP_ROWS];
+  const uint32_t fast = p.out_bthd ? (uint32_t)p.H : (uint32_t)p.T;   // extent of the fastest row index
+  const uint32_t mid = p.out_bthd ? (uint32_t)p.T : (uint32_t)p.H;
+  const uint32_t rc = min(row0, rows - 1);
+  uint32_t i_fast = rc % fast, rest = rc / fast;
+  uint32_t i_mid = rest % mid, i_b = rest / mid;
+#pragma unroll
+  for (int u = 0; u < PREP_ROWS; ++u) {
+    live[u] = row0 + u < rows;
+    // rows numbered (b, t, h) when the output keeps [B,T,H,D] (both streams contiguous), else (b, h, t)
+    hh[u] = p.out_bthd ? (int)i_fast : (int)i_mid;
+    tt[u] = p.out_bthd ? (int)i_mid : (int)i_fast;
+    bb[u] = (int)i_b;
+    if (row0 + u + 1 < rows) {                     // advance; past the end the last row is repeated
+      if (++i_fast == fast) { i_fast = 0; if (++i_mid == mid) { i_mid = 0; ++i_b; } }
+    }
+    const __nv_bfloat16* src = ten.in + bb[u] * ten.sb + tt[u] * ten.st + hh[u] * ten.sh + 4 * sub;
+    asm volatile("ld.global.nc.L1::no_allocate.v2.u32 {%0,%1}, [%2];" : "=r"(lo[u].x), "=r"(lo[u].y) : "l"(src));
+    asm volatile("ld.global.nc.L1::no_allocate.v2.u32 {%0,%1}, [%2];" : "=r"(hi[u].x), "=r"(hi[u].y) : "l"(src + 64));
+  }
+#pragma unroll
+  for (int u = 0; u < PREP_ROWS; ++u) {
+    float x1[4] = {bf16_lo(lo[u].x), bf16_hi(lo[u].x), bf16_lo(lo[u].y), bf16_hi(lo[u].y)};
+    float x2[4] = {bf16_lo(hi[u].x), bf16_hi(hi[u].x), bf16_lo(hi[u].y), bf16_hi(hi[u].y)};
+    if (ten.do_norm) {
+      float ss = 0.f;
+#pragma unroll
+      for (int e = 0; e < 4; ++e) ss += x1[e] * x1[e] + x2[e] * x2[e];
+      ss = halfwarp_sum(ss);
+      const float r = rsqrtf(ss * (1.0f / DAISY_HEAD_DIM) + p.eps);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) { x1[e] *= r; x2[e] *= r; }
+    }
+    if (ten.do_rope) {
+      const float4 c4 = *reinterpret_cast<const float4*>(p.cos + (int64_t)tt[u] * 64 + 4 * sub);
+      const float4 s4 = *reinterpret_cast<const float4*>(p.sin + (int64_t)tt[u] * 64 + 4 * sub);
+      const float c[4] = {c4.x, c4.y, c4.z, c4.w}, s[4] = {s4.x, s4.y, s4.z, s4.w};
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float a = x1[e], b2 = x2[e];
+        x1[e] = a * c[e] + b2 * s[e];
+        x2[e] = b2 * c[e] - a * s[e];
+      }
+    }
+    if (live[u]) {
+      const int64_t orow = p.out_bthd ? ((int64_t)bb[u] * p.T + tt[u]) * p.H + hh[u]
+                                      : ((int64_t)bb[u] * p.H + hh[u]) * p.T + tt[u];
+      __nv_bfloat16* dst = ten.out + orow * DAISY_HEAD_DIM + 4 * sub;
+      *reinterpret_cast<uint2*>(dst) = make_uint2(pack_bf16(x1[0], x1[1]), pack_bf16(x1[2], x1[3]));
+      *reinterpret_cast<uint2*>(dst + 64) = make_uint2(pack_bf16(x2[0], x2[1]), pack_bf16(x2[2], x2[3]));
+    }
   }
 }
 
@@ -83,6 +129,7 @@ extern "C" int daisy_b200_qkv_prep(const void* q, const void* k, const void* v,
                                    int B, int T, int H, int D, float eps, unsigned flags, void* stream) {
   if (B <= 0 || T <= 0 || H <= 0) return DAISY_EINVAL;
   if (D != DAISY_HEAD_DIM) return DAISY_EUNSUPPORTED;
+  if ((int64_t)B * T * H >= (int64_t)1 << 31) return DAISY_EUNSUPPORTED;
   if ((q == nullptr) != (q_out == nullptr) || (k == nullptr) != (k_out == nullptr) || (v == nullptr) != (v_out == nullptr))
     return DAISY_EINVAL;
   if (!q && !k && !v) return DAISY_EINVAL;
@@ -96,8 +143,9 @@ extern "C" int daisy_b200_qkv_prep(const void* q, const void* k, const void* v,
   p.t[1] = {(const __nv_bfloat16*)k, (__nv_bfloat16*)k_out, k_sb, k_st, k_sh, (flags & DAISY_NORM_K) ? 1 : 0, (flags & DAISY_ROPE) ? 1 : 0};
   p.t[2] = {(const __nv_bfloat16*)v, (__nv_bfloat16*)v_out, v_sb, v_st, v_sh, (flags & DAISY_NORM_V) ? 1 : 0, 0};
   p.cos = cos; p.sin = sin; p.B = B; p.T = T; p.H = H; p.eps = eps;
+  p.out_bthd = (flags & DAISY_OUT_BTHD) ? 1 : 0;
   const int64_t rows = (int64_t)B * T * H;
-  dim3 grid((unsigned)((rows + 15) / 16), 3, 1);
+  dim3 grid((unsigned)((rows + 16 * PREP_ROWS - 1) / (16 * PREP_ROWS)), 3, 1);
   qkv_prep_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(p);
   DAISY_CHECK_LAUNCH();
   return DAISY_OK;

@@ -21,7 +21,7 @@ namespace daisy {
 
 constexpr int BM = 128;
 constexpr int BN = 128;
-constexpr int NSTAGE = 4;
+constexpr int NSTAGE = 5;
 constexpr int TILE_BYTES = BM * DAISY_HEAD_DIM * 2;      // 32768
 constexpr int HALF_BYTES = TILE_BYTES / 2;               // one [128 x 64] swizzled box
 constexpr int PREFILL_THREADS = 320;
@@ -32,13 +32,14 @@ constexpr float NEG_BIG = -1.0e30f;
 struct PrefillParams {
   __nv_bfloat16* out;
   int64_t o_sb, o_st, o_sh;
-  int T, H, window;
+  int T, H, B, window;
   float scale_log2;
   int* status;
 };
 
 struct PrefillBarriers {
   uint64_t q_full[2];
+  uint64_t q_empty[2];
   uint64_t kv_full[NSTAGE];
   uint64_t kv_empty[NSTAGE];
   uint64_t s_full[2];
@@ -52,6 +53,48 @@ __device__ __forceinline__ bool key_visible(int q, int k, int window) {
   return (k <= q) && (window <= 0 || k > q - window);
 }
 
+#ifdef PREFILL_TIMING
+__device__ long long prefill_clk[32];
+#define PT_DECL long long pt_t0 = 0, pt_acc[8] = {0, 0, 0, 0, 0, 0, 0, 0}; const bool pt_on = (blockIdx.x == 3)
+#define PT_START() do { if (pt_on) pt_t0 = clock64(); } while (0)
+#define PT_LAP(i) do { if (pt_on) { long long t_ = clock64(); pt_acc[i] += t_ - pt_t0; pt_t0 = t_; } } while (0)
+#define PT_FLUSH(base, cond) do { if (pt_on && (cond)) { for (int i_ = 0; i_ < 8; ++i_) prefill_clk[(base) + i_] = pt_acc[i_]; } } while (0)
+#else
+#define PT_DECL
+#define PT_START()
+#define PT_LAP(i)
+#define PT_FLUSH(base, cond)
+#endif
+
+// Geometry of one work item: 256 query rows (two streams) of one (batch, head).
+struct ItemGeom {
+  int b, h;
+  int q0[2], jlo_s[2], jhi_s[2];
+  bool valid[2];
+  int jlo, jhi;
+};
+__device__ __forceinline__ ItemGeom item_geom(int item, int nq, int H, int T, int window) {
+  ItemGeom g;
+  const int qp = item % nq, bh = item / nq;
+  g.h = bh % H; g.b = bh / H;
+#pragma unroll
+  for (int s = 0; s < 2; ++s) {
+    g.q0[s] = (qp * 2 + s) * BM;
+    g.valid[s] = g.q0[s] < T;
+    const int klo = window > 0 ? max(0, g.q0[s] - window + 1) : 0;
+    g.jlo_s[s] = g.valid[s] ? klo / BN : 1;
+    g.jhi_s[s] = g.valid[s] ? min(g.q0[s] + BM - 1, T - 1) / BN : 0;
+  }
+  g.jlo = g.jlo_s[0];
+  g.jhi = g.valid[1] ? g.jhi_s[1] : g.jhi_s[0];
+  return g;
+}
+
+// Persistent: CTA c walks items c, c + gridDim.x, ...; item = (batch*H + head) * nq + q-pair, so the CTAs
+// running at any moment share a handful of (batch, head) K/V streams in L2.  Barrier phases are kept as
+// running counters per role, so the K/V ring, the Q buffers and the TMEM accumulators carry over from
+// one item to the next: the producer prefetches the next item's Q and K while the softmax warps are
+// still writing the previous item's output.
 __global__ void __launch_bounds__(PREFILL_THREADS, 1)
 swa_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                    const __grid_constant__ CUtensorMap tm_v, const PrefillParams p) {
@@ -63,27 +106,14 @@ swa_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
   volatile int* abort_flag = &bars->abort_flag;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int h = blockIdx.y, b = blockIdx.z;
-  const int bh = b * p.H + h;
   const int T = p.T, window = p.window;
-
-  // per-stream geometry
-  int q0[2], jlo_s[2], jhi_s[2];
-  bool valid[2];
-#pragma unroll
-  for (int s = 0; s < 2; ++s) {
-    q0[s] = (blockIdx.x * 2 + s) * BM;
-    valid[s] = q0[s] < T;
-    const int klo = window > 0 ? max(0, q0[s] - window + 1) : 0;
-    jlo_s[s] = valid[s] ? klo / BN : 1;
-    jhi_s[s] = valid[s] ? min(q0[s] + BM - 1, T - 1) / BN : 0;
-  }
-  const int jlo = jlo_s[0];
-  const int jhi = valid[1] ? jhi_s[1] : jhi_s[0];
+  const int nq = (T + 2 * BM - 1) / (2 * BM);
+  const int n_items = nq * p.H * p.B;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < 2; ++s) {
       mbar_init(&bars->q_full[s], 1);
+      mbar_init(&bars->q_empty[s], 1);
       mbar_init(&bars->s_full[s], 1);
       mbar_init(&bars->p_full[s], 128);
       mbar_init(&bars->o_full[s], 1);
@@ -105,106 +135,151 @@ swa_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
       prefetch_tmap(&tm_q); prefetch_tmap(&tm_k); prefetch_tmap(&tm_v);
-      for (int s = 0; s < 2; ++s) {
-        if (!valid[s]) continue;
-        mbar_expect_tx(&bars->q_full[s], TILE_BYTES);
-        tma_load_3d(q_tiles + s * TILE_BYTES, &tm_q, &bars->q_full[s], 0, q0[s], bh);
-        tma_load_3d(q_tiles + s * TILE_BYTES + HALF_BYTES, &tm_q, &bars->q_full[s], 64, q0[s], bh);
-      }
-      int n = 0;
+      int n = 0;                         // K/V tiles loaded so far (ring position)
+      uint32_t qn[2] = {0, 0};           // Q tiles loaded so far per stream
       bool ok = true;
-      for (int j = jlo; j <= jhi && ok; ++j) {
-        for (int kv = 0; kv < 2; ++kv, ++n) {
-          const int stage = n % NSTAGE;
-          const uint32_t ph = (n / NSTAGE) & 1;
-          if (!mbar_wait(&bars->kv_empty[stage], ph ^ 1, abort_flag, p.status, 1)) { ok = false; break; }
-          uint8_t* dst = kv_tiles + stage * TILE_BYTES;
-          const CUtensorMap* tm = kv ? &tm_v : &tm_k;
-          mbar_expect_tx(&bars->kv_full[stage], TILE_BYTES);
-          tma_load_3d(dst, tm, &bars->kv_full[stage], 0, j * BN, bh);
-          tma_load_3d(dst + HALF_BYTES, tm, &bars->kv_full[stage], 64, j * BN, bh);
+      for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
+        const ItemGeom g = item_geom(item, nq, p.H, T, window);
+        for (int s = 0; s < 2 && ok; ++s) {
+          if (!g.valid[s]) continue;
+          if (!mbar_wait(&bars->q_empty[s], (qn[s] & 1) ^ 1, abort_flag, p.status, 9)) { ok = false; break; }
+          ++qn[s];
+          mbar_expect_tx(&bars->q_full[s], TILE_BYTES);
+          tma_load_4d(q_tiles + s * TILE_BYTES, &tm_q, &bars->q_full[s], 0, g.q0[s], g.h, g.b);
+          tma_load_4d(q_tiles + s * TILE_BYTES + HALF_BYTES, &tm_q, &bars->q_full[s], 64, g.q0[s], g.h, g.b);
+        }
+        for (int j = g.jlo; j <= g.jhi && ok; ++j) {
+          for (int kv = 0; kv < 2; ++kv, ++n) {
+            const int stage = n % NSTAGE;
+            const uint32_t ph = (n / NSTAGE) & 1;
+            if (!mbar_wait(&bars->kv_empty[stage], ph ^ 1, abort_flag, p.status, 1)) { ok = false; break; }
+            uint8_t* dst = kv_tiles + stage * TILE_BYTES;
+            const CUtensorMap* tm = kv ? &tm_v : &tm_k;
+            mbar_expect_tx(&bars->kv_full[stage], TILE_BYTES);
+            tma_load_4d(dst, tm, &bars->kv_full[stage], 0, j * BN, g.h, g.b);
+            tma_load_4d(dst + HALF_BYTES, tm, &bars->kv_full[stage], 64, j * BN, g.h, g.b);
+          }
         }
       }
     }
   } else if (warp == 9) {
-    // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
+    // ------------------------------------------------------------------ MMA issuer (one thread)
+    // Issue order per K/V tile j:  PV_0(j-1) QK_0(j) PV_1(j-1) QK_1(j).  While softmax 0 works on S_0(j) the
+    // tensor core runs stream 1's pair and vice versa.  (Splitting the issue over one thread per stream was
+    // measured slower: the two streams drift into phase and compete for the same softmax slots.)
+    // The whole warp walks the loop (uniform control flow and descriptor arithmetic); the tcgen05 instructions
+    // themselves are predicated on one elected lane.
+    {
+      const uint32_t leader = elect_one() ? 1u : 0u;
       constexpr uint32_t idesc_qk = umma_idesc_bf16(BM, BN, 0, 0);
       constexpr uint32_t idesc_pv = umma_idesc_bf16(BM, DAISY_HEAD_DIM, 0, 1);
-      const uint32_t q_addr = smem_u32(q_tiles), kv_addr = smem_u32(kv_tiles);
+      // descriptor halves: low = start address >> 4 | LBO field, high = SBO | version | swizzle (constant)
+      const uint64_t qd = umma_desc_sw128(smem_u32(q_tiles), 16, 1024);        // K-major operands of Q K^T
+      const uint64_t kd = umma_desc_sw128(smem_u32(kv_tiles), 16, 1024);
+      const uint64_t vd = umma_desc_sw128(smem_u32(kv_tiles), HALF_BYTES, 1024);   // MN-major V of P V
+      const uint32_t q_lo0 = (uint32_t)qd, k_lo0 = (uint32_t)kd, qk_hi = (uint32_t)(qd >> 32);
+      const uint32_t v_lo0 = (uint32_t)vd, v_hi = (uint32_t)(vd >> 32);
+      int n_base = 0;                    // ring position of this item's first K tile
+      uint32_t n_pv[2] = {0, 0};         // P tiles consumed so far per stream (phase of p_full)
+      uint32_t n_q[2] = {0, 0};          // Q tiles consumed so far per stream (phase of q_full)
       bool ok = true;
-      for (int j = jlo; j <= jhi + 1 && ok; ++j) {
+      PT_DECL;
+      PT_START();
+      for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
+        const ItemGeom g = item_geom(item, nq, p.H, T, window);
+        for (int j = g.jlo; j <= g.jhi + 1 && ok; ++j) {
 #pragma unroll
-        for (int s = 0; s < 2; ++s) {
-          if (!valid[s]) continue;
-          const uint32_t s_tmem = tmem_base + s * 128;
-          const uint32_t o_tmem = tmem_base + 256 + s * 128;
-          // O_s += P_s(j-1) V_{j-1}
-          if (j - 1 >= jlo_s[s] && j - 1 <= jhi_s[s]) {
-            const int it = j - 1 - jlo_s[s];
-            const int n = 2 * (j - 1 - jlo) + 1;
-            const int stage = n % NSTAGE;
-            if (!mbar_wait(&bars->p_full[s], it & 1, abort_flag, p.status, 2)) { ok = false; break; }
-            if (!mbar_wait(&bars->kv_full[stage], (n / NSTAGE) & 1, abort_flag, p.status, 3)) { ok = false; break; }
-            tc_fence_after();
-            const uint32_t v_addr = kv_addr + stage * TILE_BYTES;
+          for (int s = 0; s < 2; ++s) {
+            if (!g.valid[s]) continue;
+            const uint32_t s_tmem = tmem_base + s * 128;
+            const uint32_t o_tmem = tmem_base + 256 + s * 128;
+            // O_s += P_s(j-1) V_{j-1}
+            if (j - 1 >= g.jlo_s[s] && j - 1 <= g.jhi_s[s]) {
+              const int n = n_base + 2 * (j - 1 - g.jlo) + 1;
+              const int stage = n % NSTAGE;
+              PT_LAP(0);
+              if (!__all_sync(0xffffffffu, mbar_wait(&bars->p_full[s], n_pv[s] & 1, abort_flag, p.status, 2))) { ok = false; break; }
+              ++n_pv[s];
+              PT_LAP(1);
+              if (!__all_sync(0xffffffffu, mbar_wait(&bars->kv_full[stage], (n / NSTAGE) & 1, abort_flag, p.status, 3))) { ok = false; break; }
+              PT_LAP(2);
+              tc_fence_after();
+              const uint32_t v_lo = v_lo0 + stage * (TILE_BYTES >> 4);
+              const bool first = (j - 1 == g.jlo_s[s]);             // first PV of the item overwrites O_s
+              umma_ts_lh_p(leader, o_tmem, s_tmem, v_lo, v_hi, idesc_pv, first ? 0u : 1u);
 #pragma unroll
-            for (int k = 0; k < BN / 16; ++k) {
-              const uint64_t bdesc = umma_desc_sw128(v_addr + k * 2048, HALF_BYTES, 1024);
-              umma_ts(o_tmem, s_tmem + k * 8, bdesc, idesc_pv, (it > 0 || k > 0) ? 1u : 0u);
+              for (int k = 1; k < BN / 16; ++k)
+                umma_ts_lh_p(leader, o_tmem, s_tmem + k * 8, v_lo + k * (2048 >> 4), v_hi, idesc_pv, 1u);
+              const bool other_uses = (s == 0) && g.valid[1] && (j - 1 >= g.jlo_s[1]) && (j - 1 <= g.jhi_s[1]);
+              if (!other_uses) tc_commit_p(leader, &bars->kv_empty[stage]);
+              if (j - 1 == g.jhi_s[s]) tc_commit_p(leader, &bars->o_full[s]);
             }
-            const bool other_uses = (s == 0) && valid[1] && (j - 1 >= jlo_s[1]) && (j - 1 <= jhi_s[1]);
-            if (!other_uses) tc_commit(&bars->kv_empty[stage]);
-            if (j - 1 == jhi_s[s]) tc_commit(&bars->o_full[s]);
-          }
-          // S_s = Q_s K_j^T
-          if (j >= jlo_s[s] && j <= jhi_s[s]) {
-            const int it = j - jlo_s[s];
-            const int n = 2 * (j - jlo);
-            const int stage = n % NSTAGE;
-            if (it == 0 && !mbar_wait(&bars->q_full[s], 0, abort_flag, p.status, 4)) { ok = false; break; }
-            if (!mbar_wait(&bars->kv_full[stage], (n / NSTAGE) & 1, abort_flag, p.status, 5)) { ok = false; break; }
-            tc_fence_after();
-            const uint32_t qa = q_addr + s * TILE_BYTES, ka = kv_addr + stage * TILE_BYTES;
+            // S_s = Q_s K_j^T
+            if (j >= g.jlo_s[s] && j <= g.jhi_s[s]) {
+              const int n = n_base + 2 * (j - g.jlo);
+              const int stage = n % NSTAGE;
+              PT_LAP(3);
+              if (j == g.jlo_s[s]) {
+                if (!__all_sync(0xffffffffu, mbar_wait(&bars->q_full[s], n_q[s] & 1, abort_flag, p.status, 4))) { ok = false; break; }
+                ++n_q[s];
+              }
+              if (!__all_sync(0xffffffffu, mbar_wait(&bars->kv_full[stage], (n / NSTAGE) & 1, abort_flag, p.status, 5))) { ok = false; break; }
+              PT_LAP(4);
+              tc_fence_after();
+              const uint32_t q_lo = q_lo0 + s * (TILE_BYTES >> 4);
+              const uint32_t k_lo = k_lo0 + stage * (TILE_BYTES >> 4);
 #pragma unroll
-            for (int k = 0; k < DAISY_HEAD_DIM / 16; ++k) {
-              const uint32_t off = (k >> 2) * HALF_BYTES + (k & 3) * 32;
-              umma_ss(s_tmem, umma_desc_sw128(qa + off, 16, 1024), umma_desc_sw128(ka + off, 16, 1024), idesc_qk,
-                      k > 0 ? 1u : 0u);
+              for (int k = 0; k < DAISY_HEAD_DIM / 16; ++k) {
+                const uint32_t off = ((k >> 2) * HALF_BYTES + (k & 3) * 32) >> 4;
+                umma_ss_lh_p(leader, s_tmem, q_lo + off, qk_hi, k_lo + off, qk_hi, idesc_qk, k > 0 ? 1u : 0u);
+              }
+              tc_commit_p(leader, &bars->s_full[s]);
+              if (j == g.jhi_s[s]) tc_commit_p(leader, &bars->q_empty[s]);     // Q_s may be overwritten by the next item
+              const bool other_uses = (s == 0) && g.valid[1] && (j >= g.jlo_s[1]) && (j <= g.jhi_s[1]);
+              if (!other_uses) tc_commit_p(leader, &bars->kv_empty[stage]);
             }
-            tc_commit(&bars->s_full[s]);
-            const bool other_uses = (s == 0) && valid[1] && (j >= jlo_s[1]) && (j <= jhi_s[1]);
-            if (!other_uses) tc_commit(&bars->kv_empty[stage]);
           }
         }
+        n_base += 2 * (g.jhi - g.jlo + 1);
       }
+      PT_LAP(5);
+      PT_FLUSH(16, lane == 0);
     }
   } else {
     // ------------------------------------------------------------------ softmax + epilogue
     const int s = warp >> 2, quarter = warp & 3;
-    if (valid[s]) {
-      const int row = quarter * 32 + lane;
-      const int q_row = q0[s] + row;
-      const uint32_t lane_off = (uint32_t)(quarter * 32) << 16;
-      const uint32_t s_tmem = tmem_base + lane_off + s * 128;
-      const uint32_t o_tmem = tmem_base + lane_off + 256 + s * 128;
-      const float c2 = p.scale_log2;
+    const int row = quarter * 32 + lane;
+    const uint32_t lane_off = (uint32_t)(quarter * 32) << 16;
+    const uint32_t s_tmem = tmem_base + lane_off + s * 128;
+    const uint32_t o_tmem = tmem_base + lane_off + 256 + s * 128;
+    const float c2 = p.scale_log2;
+    uint32_t n_s = 0, n_o = 0;           // S tiles / O tiles consumed so far (phases of s_full, o_full)
+    bool ok = true;
+    uint32_t r[128];
+    PT_DECL;
+    PT_START();
+    for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
+      const ItemGeom g = item_geom(item, nq, p.H, T, window);
+      if (!g.valid[s]) continue;
+      const int q0 = g.q0[s];
+      const int q_row = q0 + row;
       float m_ref = NEG_BIG, l = 0.f;
-      bool ok = true;
-      uint32_t r[128];
-      for (int j = jlo_s[s]; j <= jhi_s[s]; ++j) {
-        const int it = j - jlo_s[s];
-        ok = __all_sync(0xffffffffu, mbar_wait(&bars->s_full[s], it & 1, abort_flag, p.status, 6));
+      for (int j = g.jlo_s[s]; j <= g.jhi_s[s]; ++j) {
+        const bool first = (j == g.jlo_s[s]);
+        ok = __all_sync(0xffffffffu, mbar_wait(&bars->s_full[s], n_s & 1, abort_flag, p.status, 6));
         if (!ok) break;
+        ++n_s;
+        PT_LAP(0);
         tc_fence_after();
         const int k0 = j * BN;
-        const bool full_tile = (k0 + BN - 1 <= q0[s]) && (window <= 0 || k0 > q0[s] + BM - 1 - window);
+        const bool full_tile = (k0 + BN - 1 <= q0) && (window <= 0 || k0 > q0 + BM - 1 - window);
         // whole S row into registers
         tmem_ld32(s_tmem, r);
         tmem_ld32(s_tmem + 32, r + 32);
         tmem_ld32(s_tmem + 64, r + 64);
         tmem_ld32(s_tmem + 96, r + 96);
         tc_wait_ld();
+        PT_LAP(1);
         if (!full_tile) {
           // column i of this tile is visible iff lo < i <= hi
           const int hi = q_row - k0;
@@ -226,7 +301,7 @@ swa_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
           mx = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
         }
         const float m_new = fmaxf(m_ref, mx * c2);
-        if (it == 0) {
+        if (first) {
           m_ref = m_new;
         } else if (__any_sync(0xffffffffu, m_new - m_ref > 8.0f)) {
           const float alpha = fast_exp2(m_ref - m_new);
@@ -242,6 +317,7 @@ swa_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
             tmem_st16(o_tmem + 16 * c, t16);
           }
         }
+        PT_LAP(2);
         // P = exp2(S * c2 - m_ref) as bf16 into TMEM over S; row sum in fp32
         const uint64_t c2p = pack2f(c2, c2), nm = pack2f(-m_ref, -m_ref);
         uint64_t sum_a = pack2f(0.f, 0.f), sum_b = sum_a;
@@ -250,12 +326,23 @@ swa_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
           uint32_t pk[16];
 #pragma unroll
           for (int i = 0; i < 32; i += 4) {
-            float x0, x1, x2, x3;
-            unpack2f(ffma2(pack2f(__uint_as_float(r[32 * c + i]), __uint_as_float(r[32 * c + i + 1])), c2p, nm), x0, x1);
-            unpack2f(ffma2(pack2f(__uint_as_float(r[32 * c + i + 2]), __uint_as_float(r[32 * c + i + 3])), c2p, nm), x2, x3);
-            const float p0 = fast_exp2(x0), p1 = fast_exp2(x1), p2 = fast_exp2(x2), p3 = fast_exp2(x3);
+            const uint64_t xa = ffma2(pack2f(__uint_as_float(r[32 * c + i]), __uint_as_float(r[32 * c + i + 1])), c2p, nm);
+            const uint64_t xb = ffma2(pack2f(__uint_as_float(r[32 * c + i + 2]), __uint_as_float(r[32 * c + i + 3])), c2p, nm);
+            float x0, x1, p2, p3;
+            unpack2f(xa, x0, x1);
+            const float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
+            uint64_t pb;
+            if ((i & 4) == 4) {                                    // one pair in four goes to the FMA pipes
+              pb = exp2_poly2(xb);
+              unpack2f(pb, p2, p3);
+            } else {
+              float x2, x3;
+              unpack2f(xb, x2, x3);
+              p2 = fast_exp2(x2); p3 = fast_exp2(x3);
+              pb = pack2f(p2, p3);
+            }
             sum_a = fadd2(sum_a, pack2f(p0, p1));
-            sum_b = fadd2(sum_b, pack2f(p2, p3));
+            sum_b = fadd2(sum_b, pb);
             pk[i >> 1] = pack_bf16(p0, p1);
             pk[(i >> 1) + 1] = pack_bf16(p2, p3);
           }
@@ -269,15 +356,21 @@ swa_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
           rowsum = (a0 + a1) + (b0 + b1);
         }
         l += rowsum;
+        PT_LAP(3);
         tc_wait_st();
         tc_fence_before();
         mbar_arrive(&bars->p_full[s]);
+        PT_LAP(4);
       }
-      if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&bars->o_full[s], 0, abort_flag, p.status, 7));
+      if (ok) {
+        ok = __all_sync(0xffffffffu, mbar_wait(&bars->o_full[s], n_o & 1, abort_flag, p.status, 7));
+        ++n_o;
+      }
+      PT_LAP(5);
       if (ok) {
         tc_fence_after();
         const float inv = 1.0f / l;
-        __nv_bfloat16* dst = p.out + b * p.o_sb + (int64_t)q_row * p.o_st + h * p.o_sh;
+        __nv_bfloat16* dst = p.out + g.b * p.o_sb + (int64_t)q_row * p.o_st + g.h * p.o_sh;
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
           tmem_ld32(o_tmem + 32 * c, r);
@@ -294,8 +387,14 @@ swa_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
             }
           }
         }
+        // the next item's first PV overwrites O_s only after this warp's P of that item has been signalled,
+        // i.e. after these loads: program order of this warp is the guard
+        tc_fence_before();
       }
+      PT_LAP(6);
     }
+    PT_FLUSH(0, threadIdx.x == 0);
+    PT_FLUSH(8, threadIdx.x == 128);
   }
 
   // ------------------------------------------------------------------ teardown
@@ -398,6 +497,11 @@ umma_selftest_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_cons
 
 using namespace daisy;
 
+#ifdef PREFILL_TIMING
+__global__ void prefill_clk_dump(long long* out) { if (threadIdx.x < 32) out[threadIdx.x] = prefill_clk[threadIdx.x]; }
+extern "C" void daisy_b200_prefill_clk_dump(long long* out, void* stream) { prefill_clk_dump<<<1, 32, 0, (cudaStream_t)stream>>>(out); }
+#endif
+
 static int ensure_smem_attr() {
   static bool done = false;
   if (done) return DAISY_OK;
@@ -408,27 +512,37 @@ static int ensure_smem_attr() {
 }
 
 extern "C" int daisy_b200_swa_attend(const void* q, const void* k, const void* v,
+                                     int64_t q_sb, int64_t q_st, int64_t q_sh,
+                                     int64_t k_sb, int64_t k_st, int64_t k_sh,
+                                     int64_t v_sb, int64_t v_st, int64_t v_sh,
                                      void* out, int64_t o_sb, int64_t o_st, int64_t o_sh,
                                      int B, int T, int H, int D, int window, float scale,
                                      int* status_word, void* stream) {
   if (!q || !k || !v || !out || B <= 0 || T <= 0 || H <= 0 || !(scale > 0.f)) return DAISY_EINVAL;
   if (D != DAISY_HEAD_DIM) return DAISY_EUNSUPPORTED;
-  if (B > 65535 || H > 65535) return DAISY_EUNSUPPORTED;
-  if (!daisy_aligned16(q) || !daisy_aligned16(k) || !daisy_aligned16(v) || !daisy_aligned16(out) || ((o_sb | o_st | o_sh) & 7))
+  if (!daisy_aligned16(q) || !daisy_aligned16(k) || !daisy_aligned16(v) || !daisy_aligned16(out) || ((o_sb | o_st | o_sh) & 7) ||
+      ((q_sb | q_st | q_sh | k_sb | k_st | k_sh | v_sb | v_st | v_sh) & 7))
     return DAISY_EALIGN;
+  if (q_st <= 0 || k_st <= 0 || v_st <= 0 || q_sh < 0 || k_sh < 0 || v_sh < 0 || q_sb < 0 || k_sb < 0 || v_sb < 0) return DAISY_EINVAL;
   if (ensure_smem_attr() != DAISY_OK) { (void)cudaGetLastError(); return DAISY_ECUDA; }
   CUtensorMap tq, tk, tv;
-  const uint64_t s1 = (uint64_t)D * 2, s2 = (uint64_t)T * D * 2, bh = (uint64_t)B * H;
   int rc;
-  if ((rc = daisy_host::make_tmap_bf16_3d(&tq, q, D, T, bh, s1, s2, 64, BM)) != DAISY_OK) return rc;
-  if ((rc = daisy_host::make_tmap_bf16_3d(&tk, k, D, T, bh, s1, s2, 64, BN)) != DAISY_OK) return rc;
-  if ((rc = daisy_host::make_tmap_bf16_3d(&tv, v, D, T, bh, s1, s2, 64, BN)) != DAISY_OK) return rc;
+  // a size-1 dimension may come with any stride; the encoder wants a non-zero multiple of 16 bytes
+  auto sb = [](int64_t s, int n) { return (uint64_t)((n == 1 || s == 0) ? 16 : s * 2); };
+  if ((rc = daisy_host::make_tmap_bf16_dthb(&tq, q, D, T, H, B, q_st * 2, sb(q_sh, H), sb(q_sb, B), 64, BM)) != DAISY_OK) return rc;
+  if ((rc = daisy_host::make_tmap_bf16_dthb(&tk, k, D, T, H, B, k_st * 2, sb(k_sh, H), sb(k_sb, B), 64, BN)) != DAISY_OK) return rc;
+  if ((rc = daisy_host::make_tmap_bf16_dthb(&tv, v, D, T, H, B, v_st * 2, sb(v_sh, H), sb(v_sb, B), 64, BN)) != DAISY_OK) return rc;
   PrefillParams p;
   p.out = (__nv_bfloat16*)out; p.o_sb = o_sb; p.o_st = o_st; p.o_sh = o_sh;
-  p.T = T; p.H = H; p.window = window;
+  p.T = T; p.H = H; p.B = B; p.window = window;
   p.scale_log2 = scale * 1.4426950408889634f;
   p.status = status_word;
-  dim3 grid((T + 2 * BM - 1) / (2 * BM), H, B);
+  const int64_t items = (int64_t)((T + 2 * BM - 1) / (2 * BM)) * H * B;
+  if (items >= (int64_t)1 << 31) return DAISY_EUNSUPPORTED;
+  static int sms = 0;                      // one process drives one device
+  if (sms <= 0) sms = daisy_b200_sm_count();
+  if (sms <= 0) return DAISY_ENODEV;
+  dim3 grid((unsigned)(items < sms ? items : sms), 1, 1);
   swa_prefill_kernel<<<grid, PREFILL_THREADS, PREFILL_SMEM, (cudaStream_t)stream>>>(tq, tk, tv, p);
   DAISY_CHECK_LAUNCH();
   return DAISY_OK;
@@ -460,10 +574,17 @@ extern "C" int daisy_b200_swa_prefill_fwd(const void* q, const void* k, const vo
   void* qp = ws;
   void* kp = k_out ? k_out : (void*)(ws + one);
   void* vp = v_out ? v_out : (void*)(ws + 2 * one);
+  // prepared tensors keep the [B,T,H,D] memory order of the projections (a pure streaming pass); the
+  // attention kernel's tensor maps take any token/head/batch strides
+  const unsigned pf = (flags & DAISY_QKV_DEFAULT) | ((flags & DAISY_KV_BHTD) ? 0u : DAISY_OUT_BTHD);
   int rc = daisy_b200_qkv_prep(q, k, v, q_sb, q_st, q_sh, k_sb, k_st, k_sh, v_sb, v_st, v_sh, cos, sin, qp, kp, vp,
-                               B, T, H, D, eps, flags & DAISY_QKV_DEFAULT, stream);
+                               B, T, H, D, eps, pf, stream);
   if (rc != DAISY_OK) return rc;
-  return daisy_b200_swa_attend(qp, kp, vp, out, o_sb, o_st, o_sh, B, T, H, D, window, scale, status_word, stream);
+  const int64_t HD = (int64_t)H * D, TD = (int64_t)T * D;
+  int64_t sb_ = (int64_t)T * HD, st_ = HD, sh_ = D;
+  if (flags & DAISY_KV_BHTD) { st_ = D; sh_ = TD; }
+  return daisy_b200_swa_attend(qp, kp, vp, sb_, st_, sh_, sb_, st_, sh_, sb_, st_, sh_, out, o_sb, o_st, o_sh,
+                               B, T, H, D, window, scale, status_word, stream);
 }
 
 extern "C" int daisy_b200_selftest_umma(const void* a, const void* b, float* c, int K, int mode,

@@ -9,7 +9,8 @@ from typing import Optional, Tuple
 import torch
 
 from . import _lib
-from ._lib import (NORM_Q, NORM_K, NORM_V, ROPE, QKV_DEFAULT, WRITE_RING, KDA_L2NORM_QK, KDA_OUT_FP32)
+from ._lib import (NORM_Q, NORM_K, NORM_V, ROPE, QKV_DEFAULT, WRITE_RING, OUT_BTHD, KV_BHTD, KDA_L2NORM_QK,
+                   KDA_OUT_FP32)
 
 ATTN_SCALE = 0.12            # reference models/daisy/attention.py:88
 
@@ -53,37 +54,44 @@ def _f32c(t: torch.Tensor, name: str) -> torch.Tensor:
     return t
 
 
-def qkv_prep(q, k, v, cos, sin, eps: float, flags: int = QKV_DEFAULT):
-    """RMS-norm / RoPE raw ``[B,T,H,D]`` projections into ``[B,H,T,D]``-contiguous tensors."""
+def qkv_prep(q, k, v, cos, sin, eps: float, flags: int = QKV_DEFAULT, bhtd: bool = False):
+    """RMS-norm / RoPE raw ``[B,T,H,D]`` projections.  Returns three ``[B,T,H,D]`` contiguous tensors, or
+    ``[B,H,T,D]`` contiguous ones with ``bhtd=True``."""
     for n, t in (("q", q), ("k", k), ("v", v)):
         _req(t, n)
     B, T, H, D = q.shape
-    cos, sin = _f32c(cos, "cos"), _f32c(sin, "sin")
-    assert cos.shape[0] >= T and cos.shape[1] == D // 2
-    outs = [torch.empty(B, H, T, D, dtype=torch.bfloat16, device=q.device) for _ in range(3)]
+    if flags & ROPE:
+        cos, sin = _f32c(cos, "cos"), _f32c(sin, "sin")
+        assert cos.shape[0] >= T and cos.shape[1] == D // 2
+    shape = (B, H, T, D) if bhtd else (B, T, H, D)
+    outs = [torch.empty(shape, dtype=torch.bfloat16, device=q.device) for _ in range(3)]
     rc = _lib.lib().daisy_b200_qkv_prep(
         q.data_ptr(), k.data_ptr(), v.data_ptr(),
         q.stride(0), q.stride(1), q.stride(2), k.stride(0), k.stride(1), k.stride(2),
-        v.stride(0), v.stride(1), v.stride(2), cos.data_ptr(), sin.data_ptr(),
-        outs[0].data_ptr(), outs[1].data_ptr(), outs[2].data_ptr(), B, T, H, D, eps, flags, _stream(q))
+        v.stride(0), v.stride(1), v.stride(2), cos.data_ptr() if cos is not None else None,
+        sin.data_ptr() if sin is not None else None,
+        outs[0].data_ptr(), outs[1].data_ptr(), outs[2].data_ptr(), B, T, H, D, eps,
+        flags | (0 if bhtd else OUT_BTHD), _stream(q))
     _lib.check(rc, "daisy_b200_qkv_prep")
     return tuple(outs)
 
 
-def swa_attend(q_bhtd, k_bhtd, v_bhtd, window: Optional[int], scale: float = ATTN_SCALE,
+def swa_attend(q, k, v, window: Optional[int], scale: float = ATTN_SCALE,
                out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """Windowed causal attention on prepared ``[B,H,T,D]`` tensors; returns ``[B,T,H,D]``."""
-    for n, t in (("q", q_bhtd), ("k", k_bhtd), ("v", v_bhtd)):
+    """Windowed causal attention on prepared tensors of logical shape ``[B,T,H,D]`` (any batch / token /
+    head strides, D contiguous); returns ``[B,T,H,D]``."""
+    for n, t in (("q", q), ("k", k), ("v", v)):
         _req(t, n)
-        if not t.is_contiguous():
-            raise ValueError(f"{n} must be [B,H,T,D] contiguous")
-    B, H, T, D = q_bhtd.shape
+    B, T, H, D = q.shape
+    assert k.shape == q.shape and v.shape == q.shape
     if out is None:
-        out = torch.empty(B, T, H, D, dtype=torch.bfloat16, device=q_bhtd.device)
+        out = torch.empty(B, T, H, D, dtype=torch.bfloat16, device=q.device)
     rc = _lib.lib().daisy_b200_swa_attend(
-        q_bhtd.data_ptr(), k_bhtd.data_ptr(), v_bhtd.data_ptr(), out.data_ptr(),
+        q.data_ptr(), k.data_ptr(), v.data_ptr(),
+        q.stride(0), q.stride(1), q.stride(2), k.stride(0), k.stride(1), k.stride(2),
+        v.stride(0), v.stride(1), v.stride(2), out.data_ptr(),
         out.stride(0), out.stride(1), out.stride(2), B, T, H, D, int(window or 0), scale,
-        status_word(q_bhtd.device).data_ptr(), _stream(q_bhtd))
+        status_word(q.device).data_ptr(), _stream(q))
     _lib.check(rc, "daisy_b200_swa_attend")
     return out
 
@@ -92,7 +100,9 @@ def swa_prefill(q, k, v, cos, sin, window: Optional[int], scale: float = ATTN_SC
                 flags: int = QKV_DEFAULT, workspace: Optional[torch.Tensor] = None,
                 out: Optional[torch.Tensor] = None, k_out=None, v_out=None
                 ) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
-    """Raw projections ``[B,T,H,D]`` -> ``(y [B,T,H,D], k' [B,H,T,D], v' [B,H,T,D])``."""
+    """Raw projections ``[B,T,H,D]`` -> ``(y [B,T,H,D], k' [B,H,T,D], v' [B,H,T,D])``.  Like the reference's
+    ``prefill`` the returned k', v' are ``[B,H,T,D]``-shaped views of ``[B,T,H,D]`` memory; pass
+    ``k_out``/``v_out`` as ``[B,T,H,D]`` contiguous buffers to reuse storage."""
     for n, t in (("q", q), ("k", k), ("v", v)):
         _req(t, n)
     B, T, H, D = q.shape
@@ -105,9 +115,10 @@ def swa_prefill(q, k, v, cos, sin, window: Optional[int], scale: float = ATTN_SC
     if out is None:
         out = torch.empty(B, T, H, D, dtype=torch.bfloat16, device=q.device)
     if k_out is None:
-        k_out = torch.empty(B, H, T, D, dtype=torch.bfloat16, device=q.device)
+        k_out = torch.empty(B, T, H, D, dtype=torch.bfloat16, device=q.device)
     if v_out is None:
-        v_out = torch.empty(B, H, T, D, dtype=torch.bfloat16, device=q.device)
+        v_out = torch.empty(B, T, H, D, dtype=torch.bfloat16, device=q.device)
+    assert k_out.shape == (B, T, H, D) and k_out.is_contiguous() and v_out.shape == (B, T, H, D) and v_out.is_contiguous()
     rc = L.daisy_b200_swa_prefill_fwd(
         q.data_ptr(), k.data_ptr(), v.data_ptr(),
         q.stride(0), q.stride(1), q.stride(2), k.stride(0), k.stride(1), k.stride(2),
@@ -116,7 +127,7 @@ def swa_prefill(q, k, v, cos, sin, window: Optional[int], scale: float = ATTN_SC
         B, T, H, D, int(window or 0), scale, eps, flags, workspace.data_ptr(), workspace.numel(),
         status_word(q.device).data_ptr(), _stream(q))
     _lib.check(rc, "daisy_b200_swa_prefill_fwd")
-    return out, k_out, v_out
+    return out, k_out.transpose(1, 2), v_out.transpose(1, 2)
 
 
 def decode_splits(B: int, H: int, ctx_rows: int) -> int:

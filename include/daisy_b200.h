@@ -44,6 +44,8 @@ extern "C" {
 #define DAISY_ROPE       8u     /* rotate halves (x[:D/2], x[D/2:]) of q and k by cos/sin tables    */
 #define DAISY_QKV_DEFAULT 15u
 #define DAISY_WRITE_RING 16u    /* decode: store the new k,v row into ring slot t % cap            */
+#define DAISY_OUT_BTHD   32u    /* qkv_prep: outputs keep the [B,T,H,D] memory order (default [B,H,T,D]) */
+#define DAISY_KV_BHTD    64u    /* swa_prefill_fwd: k_out/v_out memory order [B,H,T,D] (default [B,T,H,D]) */
 /* KDA flags */
 #define DAISY_KDA_L2NORM_QK 1u  /* L2-normalise q and k over K inside the kernel (eps 1e-6)         */
 #define DAISY_KDA_OUT_FP32  2u  /* `o` is float32 instead of bf16                                   */
@@ -60,7 +62,8 @@ int         daisy_b200_sm_count(void);
  * _apply_rope = models/daisy/attention.py:16-20).
  *   q,k,v      raw projections, logical [B,T,H,D], strides (s_b,s_t,s_h) each, D contiguous
  *   cos,sin    float32 [T, D/2], row t = position of token t
- *   *_out      [B,H,T,D] contiguous; any of the three pairs (in,out) may be NULL together
+ *   *_out      [B,H,T,D] contiguous, or [B,T,H,D] contiguous with DAISY_OUT_BTHD (a pure streaming
+ *              pass); any of the three pairs (in,out) may be NULL together
  */
 int daisy_b200_qkv_prep(const void* q, const void* k, const void* v,
                         int64_t q_sb, int64_t q_st, int64_t q_sh,
@@ -79,8 +82,9 @@ int daisy_b200_qkv_prep(const void* q, const void* k, const void* v,
  * returns for the cache (models/daisy/attention.py:173-179).
  *   q,k,v      raw projections, logical [B,T,H,D] with strides as above
  *   out        [B,T,H,D] with strides (o_sb,o_st,o_sh)
- *   k_out,v_out  normalised/rotated k and v, [B,H,T,D] contiguous; may be NULL (then the
- *              copies live in the workspace only)
+ *   k_out,v_out  normalised/rotated k and v; memory order [B,T,H,D] (what the reference returns: a
+ *              [B,H,T,D]-shaped view of that memory) or, with DAISY_KV_BHTD, [B,H,T,D] contiguous;
+ *              may be NULL (then the copies live in the workspace only)
  *   workspace  daisy_b200_swa_prefill_workspace_bytes(B,T,H,D) bytes, 256-byte aligned
  */
 size_t daisy_b200_swa_prefill_workspace_bytes(int B, int T, int H, int D);
@@ -95,10 +99,13 @@ int daisy_b200_swa_prefill_fwd(const void* q, const void* k, const void* v,
                                unsigned flags, void* workspace, size_t workspace_bytes,
                                int* status_word, void* stream);
 
-/* The attention core alone on already-prepared [B,H,T,D]-contiguous q,k,v (what
- * F.scaled_dot_product_attention(q_,k_,v_,attn_mask=M,scale=...) computes at
- * models/daisy/attention.py:145). */
-int daisy_b200_swa_attend(const void* q_bhtd, const void* k_bhtd, const void* v_bhtd,
+/* The attention core alone on already-prepared q,k,v, logical [B,T,H,D] with strides
+ * (s_b,s_t,s_h), D contiguous -- any memory order (what F.scaled_dot_product_attention(q_,k_,v_,
+ * attn_mask=M,scale=...) computes at models/daisy/attention.py:145). */
+int daisy_b200_swa_attend(const void* q, const void* k, const void* v,
+                          int64_t q_sb, int64_t q_st, int64_t q_sh,
+                          int64_t k_sb, int64_t k_st, int64_t k_sh,
+                          int64_t v_sb, int64_t v_st, int64_t v_sh,
                           void* out, int64_t o_sb, int64_t o_st, int64_t o_sh,
                           int B, int T, int H, int D, int window, float scale,
                           int* status_word, void* stream);

@@ -22,7 +22,10 @@ def test_qkv_prep_matches_oracle():
     qn, kn, vn = swa.qkv_transform(q.float().cpu(), k.float().cpu(), v.float().cpu(), cos, sin, swa.FP32_EPS)
     qp, kp, vp = ops.qkv_prep(q, k, v, cos.cuda(), sin.cuda(), swa.FP32_EPS)
     for got, ref, n in ((qp, qn, "q"), (kp, kn, "k"), (vp, vn, "v")):
-        assert_close_bf16(got, ref.permute(0, 2, 1, 3), n)
+        assert got.shape == (B, T, H, D)
+        assert_close_bf16(got, ref, n)
+    qb, kb, vb = ops.qkv_prep(q, k, v, cos.cuda(), sin.cuda(), swa.FP32_EPS, bhtd=True)
+    assert qb.shape == (B, H, T, D) and torch.equal(qb, qp.transpose(1, 2)) and torch.equal(vb, vp.transpose(1, 2))
 
 
 @pytest.mark.parametrize("T,window", [(1, None), (5, 3), (63, 16), (128, None), (128, 128), (129, 128), (131, 128),
@@ -79,7 +82,9 @@ def test_attend_large_logits_rescale_path():
     v = torch.randn(B, T, H, D, generator=g)
     q, k, v = (x.bfloat16().cuda() for x in (q, k, v))
     y_ref = swa.attend_windowed(q.float().cpu(), k.float().cpu(), v.float().cpu(), window, scale=0.5)
-    y = ops.swa_attend(q.transpose(1, 2).contiguous(), k.transpose(1, 2).contiguous(), v.transpose(1, 2).contiguous(),
-                       window, scale=0.5)
+    y = ops.swa_attend(q, k, v, window, scale=0.5)
+    # the same tensors in [B,H,T,D] memory order reach the kernel through different strides
+    yb = ops.swa_attend(*(x.transpose(1, 2).contiguous().transpose(1, 2) for x in (q, k, v)), window, scale=0.5)
+    assert torch.equal(y, yb)
     ops.check_device_status(q.device)
     assert_close_bf16(y, y_ref, "rescale", max_tol=4e-2, mean_tol=4e-3)

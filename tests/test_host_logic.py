@@ -1,0 +1,108 @@
+"""Host-side logic that needs no GPU: ring index arithmetic, mask descriptor parsing, module construction,
+and the sharding arithmetic of the multi-GPU bench (world_size-2 gloo)."""
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from oracle import swa
+
+
+def test_ring_segment_matches_reference_view():
+    from daisy_b200 import ring_segment
+    for W in (1, 3, 4, 8):
+        c = swa.RingKVCache(1, 1, 1, W, 2)
+        for t in range(3 * W + 2):
+            for staged in (False, True):
+                first, n = ring_segment(t, staged, W)
+                assert n == min(t + staged, W) and first == t + staged - n
+            k = torch.full((1, 1, 1, 2), float(t))
+            kc, _ = c.view(0)
+            first, n = ring_segment(c.t, False, W)
+            assert kc[0, :, 0, 0].tolist() == [float(x) for x in range(first, first + n)]
+            c.write(0, k, k)
+            kc, _ = c.view(0)
+            first, n = ring_segment(c.t, True, W)
+            assert kc[0, :, 0, 0].tolist() == [float(x) for x in range(first, first + n)]
+            c.advance()
+
+
+def test_module_construction_and_mask_parsing(monkeypatch):
+    monkeypatch.setenv("DISABLE_O_ZERO_INIT", "")
+    from daisy_b200 import B200CausalSelfAttention, WindowMask
+    m = B200CausalSelfAttention(256, 2, 128, max_seq_len=64)
+    assert m.qkvo_w.shape == (4, 256, 256) and m.qkvo_w.dtype == torch.bfloat16
+    assert float(m.qkvo_w[3].abs().max()) == 0.0               # W_o zero-initialised like the reference
+    assert m.attn_scale == 0.12 and m.num_heads == 2 and m.head_dim == 128
+    cos, sin = swa.rope_tables(128, 64)
+    assert torch.equal(m.rotary.cos, cos) and torch.equal(m.rotary.sin, sin)
+    assert m._window_of(None) is None and m._window_of(WindowMask(5)) == 5 and m._window_of(7) == 7
+    with pytest.raises(TypeError):
+        m._window_of(torch.zeros(1, 1, 4, 4))
+    with pytest.raises(Exception):
+        B200CausalSelfAttention(128, 2, 64)                    # head_dim must be 128
+    g = B200CausalSelfAttention(256, 2, 128, receives_ve=True, layer_idx=2, max_seq_len=8)
+    assert abs(float(g.g_ve) + 1.5163) < 1e-6
+
+
+def test_cpu_tensors_are_rejected():
+    from daisy_b200 import ops, B200KVCache
+    x = torch.zeros(1, 4, 2, 128, dtype=torch.bfloat16)
+    with pytest.raises(ValueError, match="no CPU path"):
+        ops.qkv_prep(x, x, x, torch.zeros(4, 64), torch.zeros(4, 64), 1e-6)
+    with pytest.raises(ValueError, match="no CPU path"):
+        B200KVCache(1, 1, 2, 4, 128, device="cpu")
+
+
+def _free_port():
+    s = socket.socket(); s.bind(("127.0.0.1", 0)); p = s.getsockname()[1]; s.close()
+    return p
+
+
+def _shard_worker(rank, world, port, q):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from bench import shard_bounds
+    # independent (batch) units are sharded with no data-path collective; outputs are all-gathered afterwards
+    B, T, H, D = 6, 16, 2, 8
+    g = torch.Generator().manual_seed(0)
+    qkv = torch.randn(3, B, T, H, D, generator=g)
+    lo, hi = shard_bounds(B, world, rank)
+    y_local = swa.attend_windowed(qkv[0, lo:hi], qkv[1, lo:hi], qkv[2, lo:hi], 5)
+    parts = [torch.empty(shard_bounds(B, world, r)[1] - shard_bounds(B, world, r)[0], T, H, D) for r in range(world)]
+    dist.all_gather(parts, y_local) if len({p.shape for p in parts}) == 1 else dist.all_gather_object(parts, y_local)
+    t = torch.tensor([float(rank + 1)])
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)                    # the bench's max-over-ranks timing reduction
+    if rank == 0:
+        y = torch.cat(parts, 0)
+        y_ref = swa.attend_windowed(qkv[0], qkv[1], qkv[2], 5)
+        q.put((float((y - y_ref).abs().max()), float(t)))
+    dist.destroy_process_group()
+
+
+def test_two_rank_gloo_sharding():
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_shard_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    err, tmax = q.get(timeout=120)
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    assert err < 1e-6 and tmax == 2.0
+
+
+def test_shard_bounds_cover_everything():
+    from bench import shard_bounds
+    for n in (1, 7, 8, 64):
+        for w in (1, 2, 4, 8):
+            spans = [shard_bounds(n, w, r) for r in range(w)]
+            assert spans[0][0] == 0 and spans[-1][1] == n
+            assert all(a[1] == b[0] for a, b in zip(spans, spans[1:]))
+            sizes = [b - a for a, b in spans]
+            assert max(sizes) - min(sizes) <= 1
