@@ -281,6 +281,56 @@ def run_decode(cfg, warmup, dist, rank, world, peaks, lean=False):
                                    f"{nsteps} steps from t={cap} (ring wraps every step)", "per_gpu_batch": B}}
 
 
+# ----------------------------------------------------------------------------- our arm: KDA
+
+def run_kda(cfg, steps, warmup, dist, rank, world, peaks):
+    from daisy_b200 import ops
+    from oracle import kda as okda
+    B, T, H, K = cfg["B"], cfg["T"], cfg["H"], cfg["K"]
+    dev = torch.device("cuda", torch.cuda.current_device())
+    g_ = torch.Generator(device=dev).manual_seed(99 + rank)
+    q, k, v = (torch.randn(B, T, H, K, device=dev, generator=g_).bfloat16() for _ in range(3))
+    g = torch.nn.functional.logsigmoid(torch.randn(B, T, H, K, device=dev, generator=g_))
+    beta = torch.sigmoid(torch.randn(B, T, H, device=dev, generator=g_))
+    res = {}
+
+    def step():
+        res["o"], _ = ops.kda_chunk_fwd(q, k, v, g, beta, None, None, False, l2norm_qk=True)
+
+    ms = timed_steps(step, steps, warmup, dist)
+    ops.check_device_status(dev)
+    per = ms / steps
+    th = B * T * H
+    byts = th * okda.kda_bytes_per_token_head(K, K)
+    gbs = byts / (per * 1e-3) / 1e9
+    # e2e: host tensors in, output back
+    hq, hk, hv, hg, hb = (x.cpu().pin_memory() for x in (q, k, v, g, beta))
+    ho = torch.empty(res["o"].shape, dtype=res["o"].dtype).pin_memory()
+
+    def e2e_step():
+        for d_, h_ in ((q, hq), (k, hk), (v, hv), (g, hg), (beta, hb)):
+            d_.copy_(h_, non_blocking=True)
+        step()
+        ho.copy_(res["o"], non_blocking=True)
+
+    e2e_ms = timed_steps(e2e_step, 3, 1, dist) / 3
+    if dist is not None:
+        gathered = [torch.empty_like(res["o"]) for _ in range(world)]
+        dist.all_gather(gathered, res["o"])
+        del gathered
+    return {"name": "kda_c5", "ms_per_step": per, "value": world * th / (per * 1e-3), "unit": "token-heads/s",
+            "hbm_gbs": world * gbs, "tflops": world * th * okda.kda_flops_per_token_head(K, K) / (per * 1e-3) / 1e12,
+            "steps": steps, "launches_per_step": 2, "finite": bool(torch.isfinite(res["o"].float()).all()),
+            "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                         "frac": gbs / peaks["hbm_gbs"], "traffic": None,
+                         "kernel": "kda_intra_kernel + kda_state_kernel (one call)",
+                         "peak_source": peaks["which"] + " (copy bandwidth)"},
+            "e2e": {"value": world * th / (e2e_ms * 1e-3), "unit": "token-heads/s",
+                    "h2d_bytes_per_step": th * (3 * K * 2 + K * 4 + 4), "d2h_bytes_per_step": th * K * 2},
+            "config": {"workload": f"kda_c5: B={B} T={T} H={H} K=V={K} chunk=64, L2-normalised q,k, "
+                                   "g=logsigmoid(N(0,1)), beta=sigmoid(N(0,1)), bf16 I/O, fp32 state", "per_gpu_batch": B}}
+
+
 # ----------------------------------------------------------------------------- CPU baseline / reference arm
 
 def cpu_prefill_sample(cfg, threads=None):
@@ -368,17 +418,12 @@ def main():
         else:
             extra["decode"] = d
     if want in ("all", "kda_c5"):
-        try:
-            from bench_kda import run_kda          # present once the KDA kernels are built
-        except ImportError:
-            run_kda = None
-        if run_kda is not None:
-            torch.cuda.empty_cache()
-            kd = run_kda(KDA_C5, args.steps, warm, dist, rank, world, peaks, timed_steps)
-            if res is None:
-                res = kd
-            else:
-                extra["kda"] = kd
+        torch.cuda.empty_cache()
+        kd = run_kda(KDA_C5, args.steps, warm, dist, rank, world, peaks)
+        if res is None:
+            res = kd
+        else:
+            extra["kda"] = kd
     if rank == 0:
         is_prefill = res["name"].startswith("prefill")
         line = {
