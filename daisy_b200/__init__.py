@@ -2,6 +2,7 @@
 and KDA, as hand-written CUDA behind the reference's CausalSelfAttention / KVCache / chunk_kda API."""
 from .attention import B200CausalSelfAttention, WindowMask, Rotary   # noqa: F401
 from .kv_cache import B200KVCache, ring_segment                       # noqa: F401
+from .generate import StepRunner                                      # noqa: F401
 from . import ops                                                      # noqa: F401
 
-__all__ = ["B200CausalSelfAttention", "B200KVCache", "WindowMask", "Rotary", "ring_segment", "ops"]
+__all__ = ["B200CausalSelfAttention", "B200KVCache", "WindowMask", "Rotary", "ring_segment", "StepRunner", "ops"]

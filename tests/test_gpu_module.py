@@ -190,3 +190,29 @@ def test_kvcache_accepts_b1hd_and_contract():
             n = min(t + 1, W)
             assert got == list(range(max(0, t - n + 1), t + 1))
         c.advance()
+
+
+def test_step_runner_matches_layerwise_oracle():
+    """Generator-style orchestration (inference/generate.py:220-248) over two layers: prefill 40 tokens into a
+    capacity-32 ring, then 12 fused steps; every step equals the oracle's prefill of the whole prefix."""
+    from daisy_b200 import B200CausalSelfAttention, StepRunner
+    os.environ["DISABLE_O_ZERO_INIT"] = "1"
+    torch.manual_seed(3)
+    H, D, W, P, N = 2, 128, 24, 40, 12
+    layers = [B200CausalSelfAttention(H * D, H, D).cuda().eval() for _ in range(2)]
+    for m in layers:
+        m.norm_eps = swa.FP32_EPS
+        with torch.no_grad():
+            m.qkvo_w.mul_(4.0)                      # keep activations O(1) through two layers
+    x = torch.randn(1, P + N, H * D, device="cuda", dtype=torch.bfloat16)
+    run = StepRunner(layers, window=W, cache_capacity=32)
+    y_p = run._prefill(x[:, :P])
+    ys = [run._step(x[:, P + i:P + i + 1]) for i in range(N)]
+    assert run.cache.t == P + N
+    # oracle: full prefill of all P+N tokens through both layers in fp32 on the bf16 weights
+    cos, sin = swa.rope_tables(D, P + N)
+    h = x.float().cpu()
+    for m in layers:
+        h, _, _ = swa.csa_prefill(h.bfloat16().float(), m.qkvo_w.detach().float().cpu(), H, D, W, cos, sin)
+    assert_close_bf16(y_p, h[:, :P], "prefill part", max_tol=6e-2, mean_tol=6e-3)
+    assert_close_bf16(torch.cat(ys, 1), h[:, P:], "stepped part", max_tol=6e-2, mean_tol=6e-3)
