@@ -32,6 +32,10 @@ SIGNATURES = {
     "daisy_b200_swa_decode_step": (_i, [_vp] * 3 + [_i64] * 6 + [_vp] * 2 + [_i64] * 3 + [_i64, _i, _i] +
                                    [_vp] * 2 + [_vp, _i64, _i64] + [_vp] * 2 + [_i] * 3 + [_f, _f, _u] +
                                    [_vp, _sz, _i, _vp, _vp]),
+    "daisy_b200_swa_decode_static_capacity": (_sz, []),
+    "daisy_b200_swa_decode_step_static": (_i, [_vp] * 3 + [_i64] * 6 + [_vp] * 2 + [_i64] * 3 + [_i64, _i, _i] +
+                                          [_vp] * 2 + [_vp, _i64, _i64] + [_vp] * 2 + [_i] * 3 + [_f, _f, _u] +
+                                          [_i, _vp, _vp]),
     "daisy_b200_ring_copy_rows": (_i, [_vp] + [_i64] * 3 + [_vp] + [_i64] * 3 + [_i] * 4 + [_i64] + [_i] * 3 + [_vp]),
     "daisy_b200_kda_workspace_bytes": (_sz, [_i] * 5),
     "daisy_b200_kda_chunk_fwd": (_i, [_vp] * 8 + [_i] * 6 + [_f, _u, _vp, _sz, _vp, _vp]),

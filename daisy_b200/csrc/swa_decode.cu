@@ -261,3 +261,50 @@ extern "C" int daisy_b200_swa_decode_step(const void* q_new, const void* k_new, 
   DAISY_CHECK_LAUNCH();
   return DAISY_OK;
 }
+
+// ---------------------------------------------------------------------------------------------
+// Decode step for callers that must not allocate.
+//
+// Some hosts of this library cannot call cudaMalloc at all: code running between cudaStreamBeginCapture and
+// EndCapture of someone else's stream, plugins inside a serving process whose memory is owned entirely by
+// a pool allocator that forbids driver allocations after start-up, or a C/Go/Rust embedding that only holds
+// the q/k/v and cache pointers it was handed.  The split-KV decode needs a few MB of scratch for its
+// per-split partial results; here that scratch is a fixed array inside the library image, so the caller
+// passes inputs and outputs only.
+//
+// The array lives in every GPU context that loads the library until the process exits.  Its device address
+// is looked up once per device (cudaGetSymbolAddress with that device current) on the first call made on
+// that device; make that first call outside any stream capture.  All calls on a device share the one array:
+// two calls whose kernels can overlap on the GPU (different streams, no ordering) race on it.  Nothing in it
+// has to be zero at entry -- every partial slot a call reads is written by that same call first.
+constexpr int DECODE_STATIC_SLOTS = 4096;                       // (batch x heads x splits) partials: 2.1 MB
+static __device__ __align__(256) float g_decode_scratch[DECODE_STATIC_SLOTS * (DAISY_HEAD_DIM + 2)];
+
+extern "C" size_t daisy_b200_swa_decode_static_capacity(void) { return (size_t)DECODE_STATIC_SLOTS; }
+
+extern "C" int daisy_b200_swa_decode_step_static(const void* q_new, const void* k_new, const void* v_new,
+                                                 int64_t q_sb, int64_t q_sh, int64_t k_sb, int64_t k_sh,
+                                                 int64_t v_sb, int64_t v_sh,
+                                                 void* kcache, void* vcache, int64_t c_sb, int64_t c_sh, int64_t c_sr,
+                                                 int64_t t, int cap, int window,
+                                                 const float* cos_row, const float* sin_row,
+                                                 void* out, int64_t o_sb, int64_t o_sh,
+                                                 void* k_new_out, void* v_new_out,
+                                                 int B, int H, int D, float scale, float eps, unsigned flags,
+                                                 int splits, int* status_word, void* stream) {
+  if (B <= 0 || H <= 0 || splits <= 0) return DAISY_EINVAL;
+  if ((int64_t)B * H * splits > DECODE_STATIC_SLOTS) return DAISY_EWORKSPACE;   // beyond the built-in scratch
+  constexpr int MAX_DEV = 64;
+  static float* scratch_addr[MAX_DEV] = {nullptr};
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= MAX_DEV) { (void)cudaGetLastError(); return DAISY_ENODEV; }
+  if (!scratch_addr[dev]) {
+    // In host code the array's name is only a handle; the kernels need its address on THIS device.
+    float* ptr = nullptr;
+    if (cudaGetSymbolAddress((void**)&ptr, g_decode_scratch) != cudaSuccess || !ptr) { (void)cudaGetLastError(); return DAISY_ECUDA; }
+    scratch_addr[dev] = ptr;
+  }
+  return daisy_b200_swa_decode_step(q_new, k_new, v_new, q_sb, q_sh, k_sb, k_sh, v_sb, v_sh, kcache, vcache, c_sb, c_sh, c_sr,
+                                    t, cap, window, cos_row, sin_row, out, o_sb, o_sh, k_new_out, v_new_out, B, H, D, scale,
+                                    eps, flags, scratch_addr[dev], sizeof(g_decode_scratch), splits, status_word, stream);
+}

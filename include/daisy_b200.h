@@ -144,6 +144,25 @@ int daisy_b200_swa_decode_step(const void* q_new, const void* k_new, const void*
                                void* workspace, size_t workspace_bytes, int splits,
                                int* status_word, void* stream);
 
+/* The same decode step for callers that cannot allocate device memory (no counterpart in the reference;
+ * it exists for embedders: code inside a stream capture, plugins under a pool allocator that forbids
+ * cudaMalloc after start-up, FFI hosts that only hold the tensors they were given).  The split partials go
+ * to a fixed 2.1 MB array inside the library instead of a caller workspace, so B * H * splits must not exceed
+ * daisy_b200_swa_decode_static_capacity() (4096) -- beyond that the call returns DAISY_EWORKSPACE.  The first
+ * call on each device resolves the array's device address (make it before any stream capture).  The array is
+ * shared by all calls on a device: calls that may overlap on the GPU race.  Allocates nothing, ever. */
+size_t daisy_b200_swa_decode_static_capacity(void);
+int daisy_b200_swa_decode_step_static(const void* q_new, const void* k_new, const void* v_new,
+                                      int64_t q_sb, int64_t q_sh, int64_t k_sb, int64_t k_sh,
+                                      int64_t v_sb, int64_t v_sh,
+                                      void* kcache, void* vcache, int64_t c_sb, int64_t c_sh, int64_t c_sr,
+                                      int64_t t, int cap, int window,
+                                      const float* cos_row, const float* sin_row,
+                                      void* out, int64_t o_sb, int64_t o_sh,
+                                      void* k_new_out, void* v_new_out,
+                                      int B, int H, int D, float scale, float eps, unsigned flags,
+                                      int splits, int* status_word, void* stream);
+
 /* ---------------------------------------------------------------------------------------------
  * Ring-buffer row copies for one layer (KVCache.view when wrapped, inference/kv_cache.py:36-42,
  * and KVCache.bulk_write_packed, inference/kv_cache.py:57-68).
