@@ -36,6 +36,7 @@ KDA_C5 = dict(B=4, T=16384, H=16, K=128, V=128, chunk=64)
 # reduced copies of the same kernels for profiler captures (inputs still larger than L2, < 3 GB resident)
 PREFILL_SMALL = dict(B=2, T=8192, H=16, D=128, window=2048)
 DECODE_SMALL = dict(B=4, H=16, D=128, cap=32768, window=4096, steps=4)
+KDA_SMALL = dict(B=1, T=8192, H=16, K=128, V=128, chunk=64)
 ROPE_BASE = 10000.0     # the benchmark configs name base 10000 (the module default is 1024, half-truncated)
 
 
@@ -283,7 +284,7 @@ def run_decode(cfg, warmup, dist, rank, world, peaks, lean=False):
 
 # ----------------------------------------------------------------------------- our arm: KDA
 
-def run_kda(cfg, steps, warmup, dist, rank, world, peaks):
+def run_kda(cfg, steps, warmup, dist, rank, world, peaks, lean=False):
     from daisy_b200 import ops
     from oracle import kda as okda
     B, T, H, K = cfg["B"], cfg["T"], cfg["H"], cfg["K"]
@@ -303,6 +304,10 @@ def run_kda(cfg, steps, warmup, dist, rank, world, peaks):
     th = B * T * H
     byts = th * okda.kda_bytes_per_token_head(K, K)
     gbs = byts / (per * 1e-3) / 1e9
+    if lean:
+        return {"name": "kda", "ms_per_step": per, "value": world * th / (per * 1e-3), "unit": "token-heads/s", "steps": steps,
+                "launches_per_step": 2, "roofline": None, "e2e": None,
+                "config": {"workload": f"kda: B={B} T={T} H={H} K=V={K} (profiler capture case)"}}
     # e2e: host tensors in, output back
     hq, hk, hv, hg, hb = (x.cpu().pin_memory() for x in (q, k, v, g, beta))
     ho = torch.empty(res["o"].shape, dtype=res["o"].dtype).pin_memory()
@@ -383,7 +388,7 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="all", choices=["all", "prefill_c2", "prefill_c4", "decode_c3", "kda_c5", "prefill_small", "decode_small"])
+    ap.add_argument("--workload", default="all", choices=["all", "prefill_c2", "prefill_c4", "decode_c3", "kda_c5", "prefill_small", "decode_small", "kda_small"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
     world, rank, local = dist_env()
@@ -408,6 +413,8 @@ def main():
         res = run_prefill(PREFILL_SMALL, args.steps, args.warmup, dist, rank, world, peaks, "prefill_small", lean=True)
     if want == "decode_small":
         res = run_decode(DECODE_SMALL, args.warmup, dist, rank, world, peaks, lean=True)
+    if want == "kda_small":
+        res = run_kda(KDA_SMALL, args.steps, args.warmup, dist, rank, world, peaks, lean=True)
     if want == "prefill_c4":
         res = run_prefill(PREFILL_C4, max(2, args.steps // 4), warm, dist, rank, world, peaks, "prefill_c4")
     if want in ("all", "decode_c3"):
