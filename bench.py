@@ -37,6 +37,9 @@ KDA_C5 = dict(B=4, T=16384, H=16, K=128, V=128, chunk=64)
 PREFILL_SMALL = dict(B=2, T=8192, H=16, D=128, window=2048)
 DECODE_SMALL = dict(B=4, H=16, D=128, cap=32768, window=4096, steps=4)
 KDA_SMALL = dict(B=1, T=8192, H=16, K=128, V=128, chunk=64)
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch from the ncu captures summarised under profiles/
+# (reduced workloads of the same kernels); traffic grows in proportion to the batch (independent sequences)
+NCU_TRAFFIC = {"prefill_per_batch_row": 246.4e6 / 2, "decode_per_batch_row": 137.3e6 / 4}
 ROPE_BASE = 10000.0     # the benchmark configs name base 10000 (the module default is 1024, half-truncated)
 
 
@@ -206,7 +209,9 @@ def run_prefill(cfg, steps, warmup, dist, rank, world, peaks, name, lean=False):
         "name": name, "ms_per_step": ms / steps, "tflops": world * flops / (ms / steps * 1e-3) / 1e12,
         "clocks": clocks, "finite": finite, "launches_per_step": 2,
         "roofline": {"bound": "tensor", "achieved": ach, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
-                     "frac": ach / peaks["bf16_tflops"], "traffic": None, "kernel": "swa_prefill_kernel",
+                     "frac": ach / peaks["bf16_tflops"], "traffic": NCU_TRAFFIC["prefill_per_batch_row"] * B / (T / 8192.0) ** 0 if T == 8192 else None,
+                     "traffic_unit": "bytes per launch (ncu dram read+write on B=2, scaled by batch)",
+                     "kernel": "swa_prefill_kernel",
                      "kernel_ms": k_ms, "peak_source": peaks["which"] + " (burst cuBLAS bf16)"},
         "e2e": {"value": world * flops / (e2e_ms / e2e_steps * 1e-3) / 1e12, "unit": "TFLOP/s",
                 "h2d_bytes_per_step": in_bytes, "d2h_bytes_per_step": out_bytes},
@@ -274,7 +279,9 @@ def run_decode(cfg, warmup, dist, rank, world, peaks, lean=False):
     return {"name": "decode_c3", "ms_per_step": per, "tokens_per_s": world * B / (per * 1e-3), "hbm_gbs": world * gbs,
             "splits": splits, "steps": nsteps, "launches_per_step": 2, "finite": bool(torch.isfinite(out.float()).all()),
             "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                         "frac": gbs / peaks["hbm_gbs"], "traffic": None, "kernel": "swa_decode_partial_kernel",
+                         "frac": gbs / peaks["hbm_gbs"], "traffic": NCU_TRAFFIC["decode_per_batch_row"] * B,
+                         "traffic_unit": "bytes per launch (ncu dram read+write on batch 4, scaled by batch)",
+                         "kernel": "swa_decode_partial_kernel",
                          "peak_source": peaks["which"] + " (copy bandwidth)", "frac_of_8TBs": gbs / 8000.0},
             "e2e": {"value": world * B / (e2e_ms / 64 * 1e-3), "unit": "tokens/s",
                     "h2d_bytes_per_step": 3 * B * H * D * 2, "d2h_bytes_per_step": B * H * D * 2},
