@@ -209,7 +209,7 @@ def run_prefill(cfg, steps, warmup, dist, rank, world, peaks, name, lean=False):
         "name": name, "ms_per_step": ms / steps, "tflops": world * flops / (ms / steps * 1e-3) / 1e12,
         "clocks": clocks, "finite": finite, "launches_per_step": 2,
         "roofline": {"bound": "tensor", "achieved": ach, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
-                     "frac": ach / peaks["bf16_tflops"], "traffic": NCU_TRAFFIC["prefill_per_batch_row"] * B / (T / 8192.0) ** 0 if T == 8192 else None,
+                     "frac": ach / peaks["bf16_tflops"], "traffic": (NCU_TRAFFIC["prefill_per_batch_row"] * B if (T, W) == (8192, 2048) else None),
                      "traffic_unit": "bytes per launch (ncu dram read+write on B=2, scaled by batch)",
                      "kernel": "swa_prefill_kernel",
                      "kernel_ms": k_ms, "peak_source": peaks["which"] + " (burst cuBLAS bf16)"},
