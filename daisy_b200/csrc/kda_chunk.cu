@@ -71,8 +71,12 @@ struct KdaIntraParams {
 #ifdef KDA_PHASE_TIMING
 __device__ long long kda_phase_clk[16];
 #define KDA_MARK(n) do { __syncthreads(); if (threadIdx.x == 0 && blockIdx.x == 1 && blockIdx.y == 0 && blockIdx.z == 0) kda_phase_clk[n] = clock64(); } while (0)
+#define KDA_LAP(n) do { if (threadIdx.x == 0 && blockIdx.x == 1 && blockIdx.y == 0 && blockIdx.z == 0) { long long t_ = clock64(); kda_phase_clk[n] += t_ - kda_lap_t; kda_lap_t = t_; } } while (0)
+#define KDA_LAP_DECL long long kda_lap_t = clock64(); if (threadIdx.x == 0 && blockIdx.x == 1 && blockIdx.y == 0 && blockIdx.z == 0) { kda_phase_clk[10] = kda_phase_clk[11] = kda_phase_clk[12] = kda_phase_clk[13] = 0; }
 #else
 #define KDA_MARK(n)
+#define KDA_LAP(n)
+#define KDA_LAP_DECL
 #endif
 
 constexpr int LDA = 65;    // padded row (floats) of the fp32 [64 x 64] matrices
@@ -87,6 +91,8 @@ struct KdaIntraSmem {
   float Tm[KC][LDA];
   float Wt[16][3 * 16 + 1];        // scratch of the block forward substitution
   __half Aqk[KC][LDT];
+  __half Mk[KC][LDW];              // one level's Gram operands: k * e^{-|G - r|}
+  __half Mq[KC][LDW];              //                             q * e^{-|G - r|} on upper rows, else 0
   __half XT[KD][LDT];              // (beta k e^G)^T
   __half YT[KD][LDT];              // (beta v)^T
   float rq[KC], rk[KC], beta[KC];
@@ -202,109 +208,144 @@ __global__ void __launch_bounds__(256, 1) kda_intra_kernel(const KdaIntraParams 
   }
 
   KDA_MARK(3);
-  // ---- P3a: diagonal 16x16 blocks, exact e^{G_i - G_j} per (pair, channel); warp = (block, row parity).
-  //           Lanes split the 128 channels (4 each); the up-to-16 (kk, qk) partial sums of one row are
-  //           reduced across the warp with a halving butterfly (31 shuffles for 32 values), after which
-  //           lane l holds pair value l: l < 16 -> kk partial of column l, l >= 16 -> qk of column l - 16.
+  // ---- P3: both gated Gram matrices on tensor cores, one binary level at a time.
+  // Level s in {32,16,8,4,2,1}: tokens fall into groups of 2s; rows in the upper half of a group (i & s) pair
+  // with columns in the lower half of the same group, and every pair i > j belongs to exactly one level (the
+  // highest bit in which i and j differ).  With r = G at the last row of the lower half,
+  //     e^{G_i - G_j} = e^{G_i - r} * e^{r - G_j},   both exponents <= 0,
+  // so each row gets ONE factor per level, e^{-|G_i - r|}: upper rows carry it as the left operand, lower rows as
+  // the right operand.  Mk = k * factor (all rows), Mq = q * factor (upper rows, else 0) are staged as fp16 and
+  // the level's blocks are plain m16n8k16 products; no exponent is ever positive, whatever the gate values.
   {
-    const int I = warp >> 1, par = warp & 1;
-    const int c4 = lane * 4;
-    for (int ii = par; ii < 16; ii += 2) {
-      const int i = I * 16 + ii;
-      float ki[4], qi[4], gi[4];
+    const int brow = tid >> 2, bq = (tid & 3) * 8;                   // build: row and channels bq + 32 k .. + 8 (conflict-free)
+    // this thread's 32 normalised k and q values and cumulative gates stay in registers across the six levels
+    float kn[32], qn[32], gi[32];
+    {
+      const float rkb = sm.rk[brow], rqb = sm.rq[brow];
+      float dot = 0.f;
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        ki[e] = __bfloat162float(sm.kraw[i][c4 + e]) * sm.rk[i];
-        qi[e] = __bfloat162float(sm.qraw[i][c4 + e]) * sm.rq[i];
-        gi[e] = sm.G[i][c4 + e];
-      }
-      float part[32];
+      for (int kq = 0; kq < 4; ++kq) {
+        const int c = bq + 32 * kq;
+        float kf[8], qf[8];
+        unpack8(*reinterpret_cast<const uint4*>(&sm.kraw[brow][c]), kf);
+        unpack8(*reinterpret_cast<const uint4*>(&sm.qraw[brow][c]), qf);
+        const float4 g0 = *reinterpret_cast<const float4*>(&sm.G[brow][c]);
+        const float4 g1 = *reinterpret_cast<const float4*>(&sm.G[brow][c + 4]);
+        const float gg[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
 #pragma unroll
-      for (int jj = 0; jj < 16; ++jj) {
-        // branch-free so the 16 columns overlap; columns above the diagonal are discarded below
-        float pk = 0.f, pq = 0.f;
-        const int j = I * 16 + jj;
-        const float rkj = sm.rk[j];
-        const uint2 kj2 = *reinterpret_cast<const uint2*>(&sm.kraw[j][c4]);
-        const float4 gj = *reinterpret_cast<const float4*>(&sm.G[j][c4]);
-        const float kj[4] = {bf16_lo(kj2.x), bf16_hi(kj2.x), bf16_lo(kj2.y), bf16_hi(kj2.y)};
-        const float gjv[4] = {gj.x, gj.y, gj.z, gj.w};
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const float w = kj[e] * rkj * __expf(fminf(gi[e] - gjv[e], 0.f));
-          pk = fmaf(ki[e], w, pk); pq = fmaf(qi[e], w, pq);
-        }
-        part[jj] = pk; part[16 + jj] = pq;
-      }
-      // butterfly: after the step with offset o, lanes with (lane & o) keep the upper half of the values
-#pragma unroll
-      for (int o = 16, n = 32; o > 0; o >>= 1, n >>= 1) {
-        const bool up = (lane & o) != 0;
-#pragma unroll
-        for (int x = 0; x < n / 2; ++x) {
-          const float mine = up ? part[x + n / 2] : part[x];
-          const float give = up ? part[x] : part[x + n / 2];
-          part[x] = mine + __shfl_xor_sync(0xffffffffu, give, o);
+        for (int e = 0; e < 8; ++e) {
+          kn[8 * kq + e] = kf[e] * rkb; qn[8 * kq + e] = qf[e] * rqb; gi[8 * kq + e] = gg[e];
+          dot = fmaf(kn[8 * kq + e], qn[8 * kq + e], dot);
         }
       }
-      // lane l now owns value index l (bit o of the index == bit o of the lane at every step)
-      const int jj = lane & 15;
-      if (jj <= ii) {
-        const int j = I * 16 + jj;
-        if (lane < 16) { if (jj < ii) sm.Akk[i][j] = sm.beta[i] * part[0]; }
-        else sm.Aqk[i][j] = __float2half_rn(p.scale * part[0]);
+      dot += __shfl_xor_sync(0xffffffffu, dot, 1);                   // diagonal of A_qk: q_i . k_i, no decay
+      dot += __shfl_xor_sync(0xffffffffu, dot, 2);
+      if ((tid & 3) == 0) sm.Aqk[brow][brow] = __float2half_rn(p.scale * dot);
+    }
+    KDA_LAP_DECL;
+#pragma unroll 1
+    for (int ls = 5; ls >= 0; --ls) {
+      const int s = 1 << ls;                                         // shifts and masks below: s is a power of two
+      // -- build the level's operands
+      {
+        const bool upper = (brow & s) != 0;
+        const int ref = (brow & ~(2 * s - 1)) + s - 1;
+#pragma unroll
+        for (int kq = 0; kq < 4; ++kq) {
+          const int c = bq + 32 * kq;
+          const float4 r0 = *reinterpret_cast<const float4*>(&sm.G[ref][c]);
+          const float4 r1 = *reinterpret_cast<const float4*>(&sm.G[ref][c + 4]);
+          const float gr[8] = {r0.x, r0.y, r0.z, r0.w, r1.x, r1.y, r1.z, r1.w};
+          uint32_t mk[4], mq[4];
+#pragma unroll
+          for (int e = 0; e < 8; e += 2) {
+            const float f0 = __expf(-fabsf(gi[8 * kq + e] - gr[e])), f1 = __expf(-fabsf(gi[8 * kq + e + 1] - gr[e + 1]));
+            mk[e >> 1] = pack_h2(kn[8 * kq + e] * f0, kn[8 * kq + e + 1] * f1);
+            mq[e >> 1] = upper ? pack_h2(qn[8 * kq + e] * f0, qn[8 * kq + e + 1] * f1) : 0u;
+          }
+          *reinterpret_cast<uint4*>(&sm.Mk[brow][c]) = make_uint4(mk[0], mk[1], mk[2], mk[3]);
+          *reinterpret_cast<uint4*>(&sm.Mq[brow][c]) = make_uint4(mq[0], mq[1], mq[2], mq[3]);
+        }
       }
+      KDA_LAP(10);
+      __syncthreads();
+      KDA_LAP(11);
+      // -- the level's blocks.  A tile = 16 rows x 8 columns; for s <= 8 one 16-row tile spans 8/s groups and
+      //    its 8 columns are the lower halves of those groups (column n -> group n / s, offset n % s).
+      {
+        int mrow, ncol0, which;                                      // which: 0 = A_kk, 1 = A_qk, 2 = both
+        bool active = true;
+        if (s == 32) { mrow = 32 + 16 * (warp >> 2); ncol0 = 8 * (warp & 3); which = 2; }
+        else if (s == 16) { const int c = warp & 3; mrow = 16 + 32 * (c >> 1); ncol0 = 32 * (c >> 1) + 8 * (c & 1); which = warp >> 2; }
+        else { mrow = 16 * (warp & 3); ncol0 = mrow; which = warp >> 2; }
+        (void)active;
+        // column (token) held by this lane's B fragment, and validity of this lane's four outputs
+        const int nb = g8;                                           // B fragment: n = lane >> 2
+        const int jb = (s >= 8) ? ncol0 + nb : mrow + ((nb >> ls) << (ls + 1)) + (nb & (s - 1));
+        float acc_k[4] = {0.f, 0.f, 0.f, 0.f}, acc_q[4] = {0.f, 0.f, 0.f, 0.f};
+        float acc_k2[4] = {0.f, 0.f, 0.f, 0.f}, acc_q2[4] = {0.f, 0.f, 0.f, 0.f};   // odd k-steps: two independent chains
+        const int i0 = mrow + g8, i1 = i0 + 8;
+        // all fragments first (independent shared-memory loads), then the products
+        uint32_t bf[KD / 16][2], af[KD / 16][4];
+        const __half* arow0 = (which == 1) ? &sm.Mq[i0][0] : &sm.Mk[i0][0];
+        const __half* arow1 = (which == 1) ? &sm.Mq[i1][0] : &sm.Mk[i1][0];
+#pragma unroll
+        for (int ks = 0; ks < KD / 16; ++ks) {
+          const int c = ks * 16 + 2 * t4;
+          bf[ks][0] = *reinterpret_cast<const uint32_t*>(&sm.Mk[jb][c]);
+          bf[ks][1] = *reinterpret_cast<const uint32_t*>(&sm.Mk[jb][c + 8]);
+          af[ks][0] = *reinterpret_cast<const uint32_t*>(&arow0[c]);
+          af[ks][1] = *reinterpret_cast<const uint32_t*>(&arow1[c]);
+          af[ks][2] = *reinterpret_cast<const uint32_t*>(&arow0[c + 8]);
+          af[ks][3] = *reinterpret_cast<const uint32_t*>(&arow1[c + 8]);
+        }
+        float* accA = (which == 1) ? acc_q : acc_k;
+        float* accB = (which == 1) ? acc_q2 : acc_k2;
+#pragma unroll
+        for (int ks = 0; ks < KD / 16; ks += 2) {
+          mma_f16(accA, af[ks], bf[ks][0], bf[ks][1]);
+          mma_f16(accB, af[ks + 1], bf[ks + 1][0], bf[ks + 1][1]);
+        }
+        if (which == 2) {                                            // level 32: this warp also owns the A_qk tile
+#pragma unroll
+          for (int ks = 0; ks < KD / 16; ++ks) {
+            const int c = ks * 16 + 2 * t4;
+            af[ks][0] = *reinterpret_cast<const uint32_t*>(&sm.Mq[i0][c]);
+            af[ks][1] = *reinterpret_cast<const uint32_t*>(&sm.Mq[i1][c]);
+            af[ks][2] = *reinterpret_cast<const uint32_t*>(&sm.Mq[i0][c + 8]);
+            af[ks][3] = *reinterpret_cast<const uint32_t*>(&sm.Mq[i1][c + 8]);
+          }
+#pragma unroll
+          for (int ks = 0; ks < KD / 16; ks += 2) {
+            mma_f16(acc_q, af[ks], bf[ks][0], bf[ks][1]);
+            mma_f16(acc_q2, af[ks + 1], bf[ks + 1][0], bf[ks + 1][1]);
+          }
+        }
+#pragma unroll
+        for (int x = 0; x < 4; ++x) { acc_k[x] += acc_k2[x]; acc_q[x] += acc_q2[x]; }
+        // outputs: rows i0 (acc[0],acc[1]) and i1 (acc[2],acc[3]), tile columns 2 t4, 2 t4 + 1
+#pragma unroll
+        for (int x = 0; x < 4; ++x) {
+          const int i = (x < 2) ? i0 : i1;
+          const int n = 2 * t4 + (x & 1);
+          int j; bool ok;
+          if (s >= 16) { j = ncol0 + n; ok = true; }
+          else {
+            const int r = i - mrow;
+            j = mrow + ((n >> ls) << (ls + 1)) + (n & (s - 1));
+            ok = ((r >> (ls + 1)) == (n >> ls)) && ((r & s) != 0);
+          }
+          if (ok) {
+            if (which != 1) sm.Akk[i][j] = sm.beta[i] * acc_k[x];
+            if (which != 0) sm.Aqk[i][j] = __float2half_rn(p.scale * acc_q[x]);
+          }
+        }
+      }
+      KDA_LAP(12);
+      __syncthreads();
+      KDA_LAP(13);
     }
   }
-  KDA_MARK(4);
-  // ---- P3b: off-diagonal blocks (I > J) on tensor cores; left factor e^{G_i - r_I}, right e^{r_I - G_j},
-  //           r_I = G at the last row before block I, so both are <= 1.  Warps 0-5 take one block each.
-  if (warp < 6) {
-    const int I = warp < 1 ? 1 : (warp < 3 ? 2 : 3);
-    const int J = warp < 1 ? 0 : (warp < 3 ? warp - 1 : warp - 3);
-    const int ir = I * 16 - 1;
-    float akk[2][4] = {{0, 0, 0, 0}, {0, 0, 0, 0}}, aqk[2][4] = {{0, 0, 0, 0}, {0, 0, 0, 0}};
-    const int i0 = I * 16 + g8, i1 = i0 + 8;
-    const float rk0 = sm.rk[i0], rk1 = sm.rk[i1], rq0 = sm.rq[i0], rq1 = sm.rq[i1];
-    for (int ks = 0; ks < KD / 16; ++ks) {
-      uint32_t ak[4], aq[4];
-#pragma unroll
-      for (int hh = 0; hh < 2; ++hh) {                              // column halves: c, c+8
-        const int c = ks * 16 + hh * 8 + 2 * t4;
-        const float r0 = sm.G[ir][c], r1 = sm.G[ir][c + 1];
-        const float e00 = __expf(sm.G[i0][c] - r0), e01 = __expf(sm.G[i0][c + 1] - r1);
-        const float e10 = __expf(sm.G[i1][c] - r0), e11 = __expf(sm.G[i1][c + 1] - r1);
-        ak[hh * 2 + 0] = pack_h2(__bfloat162float(sm.kraw[i0][c]) * rk0 * e00, __bfloat162float(sm.kraw[i0][c + 1]) * rk0 * e01);
-        ak[hh * 2 + 1] = pack_h2(__bfloat162float(sm.kraw[i1][c]) * rk1 * e10, __bfloat162float(sm.kraw[i1][c + 1]) * rk1 * e11);
-        aq[hh * 2 + 0] = pack_h2(__bfloat162float(sm.qraw[i0][c]) * rq0 * e00, __bfloat162float(sm.qraw[i0][c + 1]) * rq0 * e01);
-        aq[hh * 2 + 1] = pack_h2(__bfloat162float(sm.qraw[i1][c]) * rq1 * e10, __bfloat162float(sm.qraw[i1][c + 1]) * rq1 * e11);
-      }
-#pragma unroll
-      for (int nt = 0; nt < 2; ++nt) {
-        const int j = J * 16 + nt * 8 + g8;
-        const float rkj = sm.rk[j];
-        uint32_t bb[2];
-#pragma unroll
-        for (int hh = 0; hh < 2; ++hh) {
-          const int c = ks * 16 + hh * 8 + 2 * t4;
-          bb[hh] = pack_h2(__bfloat162float(sm.kraw[j][c]) * rkj * __expf(sm.G[ir][c] - sm.G[j][c]),
-                           __bfloat162float(sm.kraw[j][c + 1]) * rkj * __expf(sm.G[ir][c + 1] - sm.G[j][c + 1]));
-        }
-        mma_f16(akk[nt], ak, bb[0], bb[1]);
-        mma_f16(aqk[nt], aq, bb[0], bb[1]);
-      }
-    }
-    const float b0 = sm.beta[i0], b1 = sm.beta[i1];
-#pragma unroll
-    for (int nt = 0; nt < 2; ++nt) {
-      const int j = J * 16 + nt * 8 + 2 * t4;
-      sm.Akk[i0][j] = b0 * akk[nt][0]; sm.Akk[i0][j + 1] = b0 * akk[nt][1];
-      sm.Akk[i1][j] = b1 * akk[nt][2]; sm.Akk[i1][j + 1] = b1 * akk[nt][3];
-      *reinterpret_cast<uint32_t*>(&sm.Aqk[i0][j]) = pack_h2(p.scale * aqk[nt][0], p.scale * aqk[nt][1]);
-      *reinterpret_cast<uint32_t*>(&sm.Aqk[i1][j]) = pack_h2(p.scale * aqk[nt][2], p.scale * aqk[nt][3]);
-    }
-  }
-  __syncthreads();
 
   KDA_MARK(5);
   // ---- P4: T = (I + A_kk)^-1, fp32.  (a) the four 16x16 diagonal blocks by forward substitution
