@@ -12,7 +12,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "libdaisy_b200.so")
 
 OK, EINVAL, EUNSUPPORTED, EALIGN, EWORKSPACE, ECUDA, ETIMEOUT, ENODEV = 0, -1, -2, -3, -4, -5, -6, -7
-NORM_Q, NORM_K, NORM_V, ROPE, QKV_DEFAULT, WRITE_RING, OUT_BTHD, KV_BHTD = 1, 2, 4, 8, 15, 16, 32, 64
+NORM_Q, NORM_K, NORM_V, ROPE, QKV_DEFAULT, WRITE_RING, OUT_BTHD, KV_BHTD, Q_IN_KERNEL = 1, 2, 4, 8, 15, 16, 32, 64, 128
 KDA_L2NORM_QK, KDA_OUT_FP32 = 1, 2
 
 _vp, _i, _i64, _f, _u, _sz = C.c_void_p, C.c_int, C.c_int64, C.c_float, C.c_uint, C.c_size_t

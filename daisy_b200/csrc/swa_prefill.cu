@@ -21,13 +21,17 @@ namespace daisy {
 
 constexpr int BM = 128;
 constexpr int BN = 128;
-constexpr int NSTAGE = 5;
+constexpr int NSTAGE = 3;              // K/V ring stages (32 KB each)
+constexpr int NQBUF = 2;               // Q double buffer: the next item's Q lands while this item computes
 constexpr int TILE_BYTES = BM * DAISY_HEAD_DIM * 2;      // 32768
 constexpr int HALF_BYTES = TILE_BYTES / 2;               // one [128 x 64] swizzled box
 constexpr int PREFILL_THREADS = 320;
-constexpr int SMEM_TILES = (2 + NSTAGE) * TILE_BYTES;
+constexpr int SMEM_TILES = (2 * NQBUF + NSTAGE) * TILE_BYTES;
 constexpr int PREFILL_SMEM = 1024 + SMEM_TILES + 256;
 constexpr float NEG_BIG = -1.0e30f;
+#ifndef POLY_HALF
+#define POLY_HALF 0                      // 1: every second pair of exponentials by polynomial; 0: one pair in four
+#endif
 
 struct PrefillParams {
   __nv_bfloat16* out;
@@ -35,11 +39,17 @@ struct PrefillParams {
   int T, H, B, window;
   float scale_log2;
   int* status;
+  // raw-Q mode: the kernel RMS-normalises and rotates the Q tile in shared memory before the first product
+  const float* cos;
+  const float* sin;
+  float eps;
+  int q_norm, q_rope;
 };
 
 struct PrefillBarriers {
-  uint64_t q_full[2];
-  uint64_t q_empty[2];
+  uint64_t q_full[2][NQBUF];
+  uint64_t q_empty[2][NQBUF];
+  uint64_t q_ready[2][NQBUF];
   uint64_t kv_full[NSTAGE];
   uint64_t kv_empty[NSTAGE];
   uint64_t s_full[2];
@@ -95,13 +105,14 @@ __device__ __forceinline__ ItemGeom item_geom(int item, int nq, int H, int T, in
 // running counters per role, so the K/V ring, the Q buffers and the TMEM accumulators carry over from
 // one item to the next: the producer prefetches the next item's Q and K while the softmax warps are
 // still writing the previous item's output.
+template <bool QRAW>
 __global__ void __launch_bounds__(PREFILL_THREADS, 1)
 swa_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                    const __grid_constant__ CUtensorMap tm_v, const PrefillParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* q_tiles = smem;
-  uint8_t* kv_tiles = smem + 2 * TILE_BYTES;
+  uint8_t* kv_tiles = smem + 2 * NQBUF * TILE_BYTES;
   PrefillBarriers* bars = reinterpret_cast<PrefillBarriers*>(smem + SMEM_TILES);
   volatile int* abort_flag = &bars->abort_flag;
 
@@ -112,8 +123,7 @@ swa_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < 2; ++s) {
-      mbar_init(&bars->q_full[s], 1);
-      mbar_init(&bars->q_empty[s], 1);
+      for (int qb = 0; qb < NQBUF; ++qb) { mbar_init(&bars->q_full[s][qb], 1); mbar_init(&bars->q_empty[s][qb], 1); mbar_init(&bars->q_ready[s][qb], 128); }
       mbar_init(&bars->s_full[s], 1);
       mbar_init(&bars->p_full[s], 128);
       mbar_init(&bars->o_full[s], 1);
@@ -138,16 +148,24 @@ swa_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       int n = 0;                         // K/V tiles loaded so far (ring position)
       uint32_t qn[2] = {0, 0};           // Q tiles loaded so far per stream
       bool ok = true;
+      // Q tiles run one item ahead of the K/V stream (double buffer), so the softmax warps can prepare the
+      // next item's Q while the current item is still computing.
+      auto load_q = [&](int it_item) {
+        const ItemGeom gq = item_geom(it_item, nq, p.H, T, window);
+        for (int s = 0; s < 2 && ok; ++s) {
+          if (!gq.valid[s]) continue;
+          const int qb = qn[s] % NQBUF;
+          if (!mbar_wait(&bars->q_empty[s][qb], ((qn[s] / NQBUF) & 1) ^ 1, abort_flag, p.status, 9)) { ok = false; break; }
+          ++qn[s];
+          uint8_t* qdst = q_tiles + (qb * 2 + s) * TILE_BYTES;
+          mbar_expect_tx(&bars->q_full[s][qb], TILE_BYTES);
+          tma_load_4d(qdst, &tm_q, &bars->q_full[s][qb], 0, gq.q0[s], gq.h, gq.b);
+          tma_load_4d(qdst + HALF_BYTES, &tm_q, &bars->q_full[s][qb], 64, gq.q0[s], gq.h, gq.b);
+        }
+      };
+      if ((int)blockIdx.x < n_items) load_q(blockIdx.x);
       for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
         const ItemGeom g = item_geom(item, nq, p.H, T, window);
-        for (int s = 0; s < 2 && ok; ++s) {
-          if (!g.valid[s]) continue;
-          if (!mbar_wait(&bars->q_empty[s], (qn[s] & 1) ^ 1, abort_flag, p.status, 9)) { ok = false; break; }
-          ++qn[s];
-          mbar_expect_tx(&bars->q_full[s], TILE_BYTES);
-          tma_load_4d(q_tiles + s * TILE_BYTES, &tm_q, &bars->q_full[s], 0, g.q0[s], g.h, g.b);
-          tma_load_4d(q_tiles + s * TILE_BYTES + HALF_BYTES, &tm_q, &bars->q_full[s], 64, g.q0[s], g.h, g.b);
-        }
         for (int j = g.jlo; j <= g.jhi && ok; ++j) {
           for (int kv = 0; kv < 2; ++kv, ++n) {
             const int stage = n % NSTAGE;
@@ -159,6 +177,9 @@ swa_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
             tma_load_4d(dst, tm, &bars->kv_full[stage], 0, j * BN, g.h, g.b);
             tma_load_4d(dst + HALF_BYTES, tm, &bars->kv_full[stage], 64, j * BN, g.h, g.b);
           }
+          // next item's Q: after this item's first K/V tiles are on their way (its buffer was released when the
+          // previous item issued its last Q K^T, which the ring has long passed by now)
+          if (j == g.jlo && item + (int)gridDim.x < n_items) load_q(item + gridDim.x);
         }
       }
     }
@@ -220,13 +241,15 @@ swa_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
               const int stage = n % NSTAGE;
               PT_LAP(3);
               if (j == g.jlo_s[s]) {
-                if (!__all_sync(0xffffffffu, mbar_wait(&bars->q_full[s], n_q[s] & 1, abort_flag, p.status, 4))) { ok = false; break; }
+                const uint32_t qb = n_q[s] % NQBUF;
+                if (!__all_sync(0xffffffffu, mbar_wait(QRAW ? &bars->q_ready[s][qb] : &bars->q_full[s][qb], (n_q[s] / NQBUF) & 1, abort_flag, p.status, 4))) { ok = false; break; }
                 ++n_q[s];
               }
               if (!__all_sync(0xffffffffu, mbar_wait(&bars->kv_full[stage], (n / NSTAGE) & 1, abort_flag, p.status, 5))) { ok = false; break; }
               PT_LAP(4);
               tc_fence_after();
-              const uint32_t q_lo = q_lo0 + s * (TILE_BYTES >> 4);
+              const uint32_t q_buf = (n_q[s] - 1) % NQBUF;              // the buffer this item's Q_s sits in
+              const uint32_t q_lo = q_lo0 + (q_buf * 2 + s) * (TILE_BYTES >> 4);
               const uint32_t k_lo = k_lo0 + stage * (TILE_BYTES >> 4);
 #pragma unroll
               for (int k = 0; k < DAISY_HEAD_DIM / 16; ++k) {
@@ -234,7 +257,7 @@ swa_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
                 umma_ss_lh_p(leader, s_tmem, q_lo + off, qk_hi, k_lo + off, qk_hi, idesc_qk, k > 0 ? 1u : 0u);
               }
               tc_commit_p(leader, &bars->s_full[s]);
-              if (j == g.jhi_s[s]) tc_commit_p(leader, &bars->q_empty[s]);     // Q_s may be overwritten by the next item
+              if (j == g.jhi_s[s]) tc_commit_p(leader, &bars->q_empty[s][q_buf]);     // Q_s may be overwritten by the next item
               const bool other_uses = (s == 0) && g.valid[1] && (j >= g.jlo_s[1]) && (j <= g.jhi_s[1]);
               if (!other_uses) tc_commit_p(leader, &bars->kv_empty[stage]);
             }
@@ -253,9 +276,59 @@ swa_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     const uint32_t s_tmem = tmem_base + lane_off + s * 128;
     const uint32_t o_tmem = tmem_base + lane_off + 256 + s * 128;
     const float c2 = p.scale_log2;
-    uint32_t n_s = 0, n_o = 0;           // S tiles / O tiles consumed so far (phases of s_full, o_full)
+    uint32_t n_s = 0, n_o = 0, n_qs = 0; // S tiles / O tiles / Q tiles consumed so far (phases of s_full, o_full, q_full)
     bool ok = true;
     uint32_t r[128];
+    bool q_prepared = false;
+    // Raw-Q mode: RMS norm over the row and half-rotation RoPE at position `qrow`, in place in the 128-byte-
+    // swizzled Q tile (thread = row; chunk c of row r sits at r*128 + ((c ^ r) & 7)*16 of box c >> 3).  Uses
+    // the S register buffer as scratch, so it runs between two softmax tiles.
+    auto prepare_q = [&](int qrow) -> bool {
+      const uint32_t qb = n_qs % NQBUF;
+      if (!__all_sync(0xffffffffu, mbar_wait(&bars->q_full[s][qb], (n_qs / NQBUF) & 1, abort_flag, p.status, 12))) return false;
+      ++n_qs;
+      uint8_t* qt = q_tiles + (qb * 2 + s) * TILE_BYTES + row * 128;
+      const int sw = row & 7;
+      uint4* rq = reinterpret_cast<uint4*>(r);
+      float ss = 0.f;
+#pragma unroll
+      for (int c = 0; c < 16; ++c) {
+        rq[c] = *reinterpret_cast<const uint4*>(qt + (c >> 3) * HALF_BYTES + (((c & 7) ^ sw) << 4));
+        float f[8];
+        unpack8(rq[c], f);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) ss = fmaf(f[e], f[e], ss);
+      }
+      const float rs = p.q_norm ? rsqrtf(ss * (1.0f / DAISY_HEAD_DIM) + p.eps) : 1.f;
+      const int pos = min(qrow, T - 1);
+      const float* cr = p.cos + (int64_t)pos * 64;
+      const float* sr = p.sin + (int64_t)pos * 64;
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        float x1[8], x2[8];
+        unpack8(rq[c], x1);
+        unpack8(rq[c + 8], x2);
+        float cs[8] = {1.f, 1.f, 1.f, 1.f, 1.f, 1.f, 1.f, 1.f}, sn[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        if (p.q_rope) {
+          const float4 c0 = *reinterpret_cast<const float4*>(cr + 8 * c), c1 = *reinterpret_cast<const float4*>(cr + 8 * c + 4);
+          const float4 s0 = *reinterpret_cast<const float4*>(sr + 8 * c), s1 = *reinterpret_cast<const float4*>(sr + 8 * c + 4);
+          cs[0] = c0.x; cs[1] = c0.y; cs[2] = c0.z; cs[3] = c0.w; cs[4] = c1.x; cs[5] = c1.y; cs[6] = c1.z; cs[7] = c1.w;
+          sn[0] = s0.x; sn[1] = s0.y; sn[2] = s0.z; sn[3] = s0.w; sn[4] = s1.x; sn[5] = s1.y; sn[6] = s1.z; sn[7] = s1.w;
+        }
+        float y1[8], y2[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          const float a = x1[e] * rs, b2 = x2[e] * rs;
+          y1[e] = a * cs[e] + b2 * sn[e];
+          y2[e] = b2 * cs[e] - a * sn[e];
+        }
+        *reinterpret_cast<uint4*>(qt + (((c & 7) ^ sw) << 4)) = pack8(y1);
+        *reinterpret_cast<uint4*>(qt + HALF_BYTES + (((c & 7) ^ sw) << 4)) = pack8(y2);
+      }
+      fence_proxy_async();                                              // generic-proxy writes -> visible to the MMA's reads
+      mbar_arrive(&bars->q_ready[s][qb]);
+      return true;
+    };
     PT_DECL;
     PT_START();
     for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
@@ -263,6 +336,21 @@ swa_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       if (!g.valid[s]) continue;
       const int q0 = g.q0[s];
       const int q_row = q0 + row;
+      if (QRAW && !q_prepared) {
+        ok = prepare_q(q_row);
+        if (!ok) break;
+      }
+      q_prepared = false;
+      // the next item's Q is prepared inside this item's loop (second iteration), in time these warps would
+      // otherwise spend waiting for the tensor core
+      const int item_next = item + gridDim.x;
+      bool next_valid = false;
+      int q_row_next = 0;
+      if (QRAW && item_next < n_items) {
+        const ItemGeom gn = item_geom(item_next, nq, p.H, T, window);
+        next_valid = gn.valid[s];
+        q_row_next = gn.q0[s] + row;
+      }
       float m_ref = NEG_BIG, l = 0.f;
       for (int j = g.jlo_s[s]; j <= g.jhi_s[s]; ++j) {
         const bool first = (j == g.jlo_s[s]);
@@ -332,7 +420,7 @@ swa_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
             unpack2f(xa, x0, x1);
             const float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
             uint64_t pb;
-            if ((i & 4) == 4) {                                    // one pair in four goes to the FMA pipes
+            if (POLY_HALF || (i & 4) == 4) {                       // a share of the pairs goes to the FMA pipes
               pb = exp2_poly2(xb);
               unpack2f(pb, p2, p3);
             } else {
@@ -361,6 +449,11 @@ swa_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         tc_fence_before();
         mbar_arrive(&bars->p_full[s]);
         PT_LAP(4);
+        if (QRAW && next_valid && !q_prepared && j == g.jlo_s[s] + 1) {
+          ok = prepare_q(q_row_next);
+          if (!ok) break;
+          q_prepared = true;
+        }
       }
       if (ok) {
         ok = __all_sync(0xffffffffu, mbar_wait(&bars->o_full[s], n_o & 1, abort_flag, p.status, 7));
@@ -505,25 +598,30 @@ extern "C" void daisy_b200_prefill_clk_dump(long long* out, void* stream) { pref
 static int ensure_smem_attr() {
   static bool done = false;
   if (done) return DAISY_OK;
-  if (cudaFuncSetAttribute(swa_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PREFILL_SMEM) != cudaSuccess) return DAISY_ECUDA;
+  if (cudaFuncSetAttribute(swa_prefill_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, PREFILL_SMEM) != cudaSuccess) return DAISY_ECUDA;
+  if (cudaFuncSetAttribute(swa_prefill_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, PREFILL_SMEM) != cudaSuccess) return DAISY_ECUDA;
   if (cudaFuncSetAttribute(umma_selftest_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 1024 + 2 * TILE_BYTES + 64) != cudaSuccess) return DAISY_ECUDA;
   done = true;
   return DAISY_OK;
 }
 
-extern "C" int daisy_b200_swa_attend(const void* q, const void* k, const void* v,
-                                     int64_t q_sb, int64_t q_st, int64_t q_sh,
-                                     int64_t k_sb, int64_t k_st, int64_t k_sh,
-                                     int64_t v_sb, int64_t v_st, int64_t v_sh,
-                                     void* out, int64_t o_sb, int64_t o_st, int64_t o_sh,
-                                     int B, int T, int H, int D, int window, float scale,
-                                     int* status_word, void* stream) {
+// Shared launcher.  `qt` non-null: q is the RAW projection and the kernel normalises / rotates it on load.
+struct QTransform { const float* cos; const float* sin; float eps; int norm, rope; };
+
+static int launch_attend(const void* q, const void* k, const void* v,
+                         int64_t q_sb, int64_t q_st, int64_t q_sh, int64_t k_sb, int64_t k_st, int64_t k_sh,
+                         int64_t v_sb, int64_t v_st, int64_t v_sh,
+                         void* out, int64_t o_sb, int64_t o_st, int64_t o_sh,
+                         int B, int T, int H, int D, int window, float scale, const QTransform* qt,
+                         int* status_word, void* stream) {
   if (!q || !k || !v || !out || B <= 0 || T <= 0 || H <= 0 || !(scale > 0.f)) return DAISY_EINVAL;
   if (D != DAISY_HEAD_DIM) return DAISY_EUNSUPPORTED;
   if (!daisy_aligned16(q) || !daisy_aligned16(k) || !daisy_aligned16(v) || !daisy_aligned16(out) || ((o_sb | o_st | o_sh) & 7) ||
       ((q_sb | q_st | q_sh | k_sb | k_st | k_sh | v_sb | v_st | v_sh) & 7))
     return DAISY_EALIGN;
   if (q_st <= 0 || k_st <= 0 || v_st <= 0 || q_sh < 0 || k_sh < 0 || v_sh < 0 || q_sb < 0 || k_sb < 0 || v_sb < 0) return DAISY_EINVAL;
+  if (qt && qt->rope && (!qt->cos || !qt->sin)) return DAISY_EINVAL;
+  if (qt && qt->rope && (!daisy_aligned16(qt->cos) || !daisy_aligned16(qt->sin))) return DAISY_EALIGN;
   if (ensure_smem_attr() != DAISY_OK) { (void)cudaGetLastError(); return DAISY_ECUDA; }
   CUtensorMap tq, tk, tv;
   int rc;
@@ -537,22 +635,38 @@ extern "C" int daisy_b200_swa_attend(const void* q, const void* k, const void* v
   p.T = T; p.H = H; p.B = B; p.window = window;
   p.scale_log2 = scale * 1.4426950408889634f;
   p.status = status_word;
+  p.cos = qt ? qt->cos : nullptr; p.sin = qt ? qt->sin : nullptr;
+  p.eps = qt ? qt->eps : 0.f; p.q_norm = qt ? qt->norm : 0; p.q_rope = qt ? qt->rope : 0;
   const int64_t items = (int64_t)((T + 2 * BM - 1) / (2 * BM)) * H * B;
   if (items >= (int64_t)1 << 31) return DAISY_EUNSUPPORTED;
   static int sms = 0;                      // one process drives one device
   if (sms <= 0) sms = daisy_b200_sm_count();
   if (sms <= 0) return DAISY_ENODEV;
   dim3 grid((unsigned)(items < sms ? items : sms), 1, 1);
-  swa_prefill_kernel<<<grid, PREFILL_THREADS, PREFILL_SMEM, (cudaStream_t)stream>>>(tq, tk, tv, p);
+  if (qt && (qt->norm || qt->rope))
+    swa_prefill_kernel<true><<<grid, PREFILL_THREADS, PREFILL_SMEM, (cudaStream_t)stream>>>(tq, tk, tv, p);
+  else
+    swa_prefill_kernel<false><<<grid, PREFILL_THREADS, PREFILL_SMEM, (cudaStream_t)stream>>>(tq, tk, tv, p);
   DAISY_CHECK_LAUNCH();
   return DAISY_OK;
+}
+
+extern "C" int daisy_b200_swa_attend(const void* q, const void* k, const void* v,
+                                     int64_t q_sb, int64_t q_st, int64_t q_sh,
+                                     int64_t k_sb, int64_t k_st, int64_t k_sh,
+                                     int64_t v_sb, int64_t v_st, int64_t v_sh,
+                                     void* out, int64_t o_sb, int64_t o_st, int64_t o_sh,
+                                     int B, int T, int H, int D, int window, float scale,
+                                     int* status_word, void* stream) {
+  return launch_attend(q, k, v, q_sb, q_st, q_sh, k_sb, k_st, k_sh, v_sb, v_st, v_sh, out, o_sb, o_st, o_sh,
+                       B, T, H, D, window, scale, nullptr, status_word, stream);
 }
 
 static size_t align1k(size_t x) { return (x + 1023) & ~size_t(1023); }
 
 extern "C" size_t daisy_b200_swa_prefill_workspace_bytes(int B, int T, int H, int D) {
   if (B <= 0 || T <= 0 || H <= 0 || D <= 0) return 0;
-  return 3 * align1k((size_t)B * T * H * D * 2);
+  return 3 * align1k((size_t)B * T * H * D * 2);       // slots: q', k', v' -- the latter two only when k_out/v_out are NULL
 }
 
 extern "C" int daisy_b200_swa_prefill_fwd(const void* q, const void* k, const void* v,
@@ -571,20 +685,29 @@ extern "C" int daisy_b200_swa_prefill_fwd(const void* q, const void* k, const vo
   if (reinterpret_cast<uintptr_t>(workspace) & 255) return DAISY_EALIGN;
   const size_t one = align1k((size_t)B * T * H * D * 2);
   char* ws = (char*)workspace;
-  void* qp = ws;
   void* kp = k_out ? k_out : (void*)(ws + one);
   void* vp = v_out ? v_out : (void*)(ws + 2 * one);
-  // prepared tensors keep the [B,T,H,D] memory order of the projections (a pure streaming pass); the
-  // attention kernel's tensor maps take any token/head/batch strides
+  // K and V are prepared once (they are outputs anyway: the cache rows) and keep the [B,T,H,D] memory order
+  // of the projections, a pure streaming pass.  Q is either prepared in the same pass (default) or, with
+  // DAISY_Q_IN_KERNEL, consumed raw: the attention kernel then normalises and rotates each Q tile in shared
+  // memory one item ahead of its use.  Measured on C2 the in-kernel form is slower (1.46 ms vs 1.33 ms per
+  // step: the transform competes with the softmax warps for issue slots and L2 latency), so it is opt-in.
+  const bool q_in_kernel = (flags & DAISY_Q_IN_KERNEL) != 0;
+  void* qp = ws;
   const unsigned pf = (flags & DAISY_QKV_DEFAULT) | ((flags & DAISY_KV_BHTD) ? 0u : DAISY_OUT_BTHD);
-  int rc = daisy_b200_qkv_prep(q, k, v, q_sb, q_st, q_sh, k_sb, k_st, k_sh, v_sb, v_st, v_sh, cos, sin, qp, kp, vp,
-                               B, T, H, D, eps, pf, stream);
+  int rc = daisy_b200_qkv_prep(q_in_kernel ? nullptr : q, k, v, q_sb, q_st, q_sh, k_sb, k_st, k_sh, v_sb, v_st, v_sh, cos, sin,
+                               q_in_kernel ? nullptr : qp, kp, vp, B, T, H, D, eps, pf, stream);
   if (rc != DAISY_OK) return rc;
   const int64_t HD = (int64_t)H * D, TD = (int64_t)T * D;
   int64_t sb_ = (int64_t)T * HD, st_ = HD, sh_ = D;
   if (flags & DAISY_KV_BHTD) { st_ = D; sh_ = TD; }
-  return daisy_b200_swa_attend(qp, kp, vp, sb_, st_, sh_, sb_, st_, sh_, sb_, st_, sh_, out, o_sb, o_st, o_sh,
-                               B, T, H, D, window, scale, status_word, stream);
+  if (q_in_kernel) {
+    QTransform qt{cos, sin, eps, (flags & DAISY_NORM_Q) ? 1 : 0, (flags & DAISY_ROPE) ? 1 : 0};
+    return launch_attend(q, kp, vp, q_sb, q_st, q_sh, sb_, st_, sh_, sb_, st_, sh_, out, o_sb, o_st, o_sh,
+                         B, T, H, D, window, scale, &qt, status_word, stream);
+  }
+  return launch_attend(qp, kp, vp, sb_, st_, sh_, sb_, st_, sh_, sb_, st_, sh_, out, o_sb, o_st, o_sh,
+                       B, T, H, D, window, scale, nullptr, status_word, stream);
 }
 
 extern "C" int daisy_b200_selftest_umma(const void* a, const void* b, float* c, int K, int mode,

@@ -9,7 +9,7 @@ from typing import Optional, Tuple
 import torch
 
 from . import _lib
-from ._lib import (NORM_Q, NORM_K, NORM_V, ROPE, QKV_DEFAULT, WRITE_RING, OUT_BTHD, KV_BHTD, KDA_L2NORM_QK,
+from ._lib import (NORM_Q, NORM_K, NORM_V, ROPE, QKV_DEFAULT, WRITE_RING, OUT_BTHD, KV_BHTD, Q_IN_KERNEL, KDA_L2NORM_QK,
                    KDA_OUT_FP32)
 
 ATTN_SCALE = 0.12            # reference models/daisy/attention.py:88

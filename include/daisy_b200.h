@@ -46,6 +46,7 @@ extern "C" {
 #define DAISY_WRITE_RING 16u    /* decode: store the new k,v row into ring slot t % cap            */
 #define DAISY_OUT_BTHD   32u    /* qkv_prep: outputs keep the [B,T,H,D] memory order (default [B,H,T,D]) */
 #define DAISY_KV_BHTD    64u    /* swa_prefill_fwd: k_out/v_out memory order [B,H,T,D] (default [B,T,H,D]) */
+#define DAISY_Q_IN_KERNEL 128u  /* swa_prefill_fwd: normalise / rotate Q inside the attention kernel (on load) */
 /* KDA flags */
 #define DAISY_KDA_L2NORM_QK 1u  /* L2-normalise q and k over K inside the kernel (eps 1e-6)         */
 #define DAISY_KDA_OUT_FP32  2u  /* `o` is float32 instead of bf16                                   */
