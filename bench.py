@@ -184,17 +184,20 @@ def run_prefill(cfg, steps, warmup, dist, rank, world, peaks, name, lean=False):
     k_ms = sum(a.elapsed_time(b) for a, b in ev) / steps
     del qp, kp, vp
 
-    # end to end through the public call with host buffers
+    # end to end through the public host-buffer call: pinned host q,k,v in, pinned host result out, every step;
+    # batch rows stream through copy-in / kernels / copy-out on three CUDA streams
+    from daisy_b200.host_api import HostPrefill
     hq, hk, hv = (x.cpu().pin_memory() for x in (q, k, v))
     hout = torch.empty(out.shape, dtype=out.dtype).pin_memory()
+    host_call = HostPrefill(T, H, D, device=dev, rows_per_chunk=1)
 
     def e2e_step():
-        q.copy_(hq, non_blocking=True); k.copy_(hk, non_blocking=True); v.copy_(hv, non_blocking=True)
-        step()
-        hout.copy_(out, non_blocking=True)
+        host_call(hq, hk, hv, cos, sin, W, hout, eps=swa.FP32_EPS)
 
     e2e_steps = max(2, min(steps, 5))
     e2e_ms = timed_steps(e2e_step, e2e_steps, 1, dist)
+    torch.cuda.synchronize()
+    e2e_same = bool(torch.equal(hout, out.cpu()))             # same inputs -> the host path must reproduce `out`
     in_bytes = 3 * q.numel() * 2
     out_bytes = out.numel() * 2
 
@@ -214,7 +217,8 @@ def run_prefill(cfg, steps, warmup, dist, rank, world, peaks, name, lean=False):
                      "kernel": "swa_prefill_kernel",
                      "kernel_ms": k_ms, "peak_source": peaks["which"] + " (burst cuBLAS bf16)"},
         "e2e": {"value": world * flops / (e2e_ms / e2e_steps * 1e-3) / 1e12, "unit": "TFLOP/s",
-                "h2d_bytes_per_step": in_bytes, "d2h_bytes_per_step": out_bytes},
+                "h2d_bytes_per_step": in_bytes, "d2h_bytes_per_step": out_bytes,
+                "matches_device_result": e2e_same, "api": "daisy_b200.host_api.HostPrefill"},
         "config": {"workload": f"{name}: B={B} T={T} H={H} D={D} window={W} causal, RMS-norm q,k,v + RoPE base "
                                f"{int(ROPE_BASE)} fused in the step", "per_gpu_batch": B, "global_batch": B * world,
                    "parallelism": f"dp{world} (independent sequences per GPU, no collective)",

@@ -216,3 +216,24 @@ def test_step_runner_matches_layerwise_oracle():
         h, _, _ = swa.csa_prefill(h.bfloat16().float(), m.qkvo_w.detach().float().cpu(), H, D, W, cos, sin)
     assert_close_bf16(y_p, h[:, :P], "prefill part", max_tol=6e-2, mean_tol=6e-3)
     assert_close_bf16(torch.cat(ys, 1), h[:, P:], "stepped part", max_tol=6e-2, mean_tol=6e-3)
+
+
+def test_host_buffer_prefill_equals_device_call():
+    """HostPrefill (pinned host tensors, three-stream pipeline over batch rows) == the device-resident call."""
+    from daisy_b200 import ops
+    from daisy_b200.host_api import HostPrefill
+    B, T, H, D, W = 5, 260, 2, 128, 100
+    g = torch.Generator().manual_seed(8)
+    hq, hk, hv = (torch.randn(B, T, H, D, generator=g).bfloat16().pin_memory() for _ in range(3))
+    cos, sin = swa.rope_tables(D, T)
+    cos, sin = cos.cuda(), sin.cuda()
+    y_dev, k_dev, _ = ops.swa_prefill(hq.cuda(), hk.cuda(), hv.cuda(), cos, sin, W)
+    for rows in (1, 2):
+        hout = torch.zeros(B, T, H, D, dtype=torch.bfloat16).pin_memory()
+        hk_out, hv_out = torch.zeros_like(hout).pin_memory(), torch.zeros_like(hout).pin_memory()
+        call = HostPrefill(T, H, D, rows_per_chunk=rows, return_kv=True)
+        call(hq, hk, hv, cos, sin, W, hout, hk_out, hv_out)
+        call(hq, hk, hv, cos, sin, W, hout, hk_out, hv_out)          # staging reuse
+        torch.cuda.synchronize()
+        assert torch.equal(hout, y_dev.cpu())
+        assert torch.equal(hk_out.transpose(1, 2), k_dev.cpu())
