@@ -105,7 +105,7 @@ __device__ __forceinline__ ItemGeom item_geom(int item, int nq, int H, int T, in
 // running counters per role, so the K/V ring, the Q buffers and the TMEM accumulators carry over from
 // one item to the next: the producer prefetches the next item's Q and K while the softmax warps are
 // still writing the previous item's output.
-template <bool QRAW>
+template <bool QRAW, bool BOUNDED>
 __global__ void __launch_bounds__(PREFILL_THREADS, 1)
 swa_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                    const __grid_constant__ CUtensorMap tm_v, const PrefillParams p) {
@@ -219,10 +219,11 @@ swa_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
               const int n = n_base + 2 * (j - 1 - g.jlo) + 1;
               const int stage = n % NSTAGE;
               PT_LAP(0);
-              if (!__all_sync(0xffffffffu, mbar_wait(&bars->p_full[s], n_pv[s] & 1, abort_flag, p.status, 2))) { ok = false; break; }
+              if (!mbar_wait(&bars->p_full[s], n_pv[s] & 1, abort_flag, p.status, 2)) { ok = false; break; }
               ++n_pv[s];
               PT_LAP(1);
-              if (!__all_sync(0xffffffffu, mbar_wait(&bars->kv_full[stage], (n / NSTAGE) & 1, abort_flag, p.status, 3))) { ok = false; break; }
+              const bool v_seen = (s == 1) && g.valid[0] && (j - 1 >= g.jlo_s[0]) && (j - 1 <= g.jhi_s[0]);   // stream 0 waited on V_{j-1}
+              if (!v_seen && !mbar_wait(&bars->kv_full[stage], (n / NSTAGE) & 1, abort_flag, p.status, 3)) { ok = false; break; }
               PT_LAP(2);
               tc_fence_after();
               const uint32_t v_lo = v_lo0 + stage * (TILE_BYTES >> 4);
@@ -242,10 +243,11 @@ swa_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
               PT_LAP(3);
               if (j == g.jlo_s[s]) {
                 const uint32_t qb = n_q[s] % NQBUF;
-                if (!__all_sync(0xffffffffu, mbar_wait(QRAW ? &bars->q_ready[s][qb] : &bars->q_full[s][qb], (n_q[s] / NQBUF) & 1, abort_flag, p.status, 4))) { ok = false; break; }
+                if (!mbar_wait(QRAW ? &bars->q_ready[s][qb] : &bars->q_full[s][qb], (n_q[s] / NQBUF) & 1, abort_flag, p.status, 4)) { ok = false; break; }
                 ++n_q[s];
               }
-              if (!__all_sync(0xffffffffu, mbar_wait(&bars->kv_full[stage], (n / NSTAGE) & 1, abort_flag, p.status, 5))) { ok = false; break; }
+              const bool k_seen = (s == 1) && g.valid[0] && (j >= g.jlo_s[0]) && (j <= g.jhi_s[0]);           // stream 0 waited on K_j
+              if (!k_seen && !mbar_wait(&bars->kv_full[stage], (n / NSTAGE) & 1, abort_flag, p.status, 5)) { ok = false; break; }
               PT_LAP(4);
               tc_fence_after();
               const uint32_t q_buf = (n_q[s] - 1) % NQBUF;              // the buffer this item's Q_s sits in
@@ -351,7 +353,7 @@ swa_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         next_valid = gn.valid[s];
         q_row_next = gn.q0[s] + row;
       }
-      float m_ref = NEG_BIG, l = 0.f;
+      float m_ref = NEG_BIG, l = 0.f, pend = 0.f;   // pend: how far the reference is known to lag (applied before the next P)
       for (int j = g.jlo_s[s]; j <= g.jhi_s[s]; ++j) {
         const bool first = (j == g.jlo_s[s]);
         ok = __all_sync(0xffffffffu, mbar_wait(&bars->s_full[s], n_s & 1, abort_flag, p.status, 6));
@@ -376,8 +378,14 @@ swa_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
           for (int i = 0; i < 128; ++i)
             if (!(i > lo && i <= hi)) r[i] = 0xff800000u;              // -inf
         }
-        float mx;
-        {
+        // Reference maximum.  General inputs: row max of every tile first, accumulator rescaled lazily (only when
+        // the maximum grew by more than 8).  BOUNDED inputs (RMS-normalised q and k, so |logit| <= scale*D and
+        // 2^x cannot overflow whatever the reference): only an item's first tile pays for the max pass; later
+        // tiles exponentiate against the current reference at once, the largest P of the row is tracked on the
+        // side, and a reference that turned out stale by more than 2^8 is raised before the NEXT tile.
+        float m_tgt = m_ref + pend;                                  // BOUNDED: reference the previous tile asked for
+        const bool need_max = first || !BOUNDED || __any_sync(0xffffffffu, m_ref == NEG_BIG);   // warp-uniform
+        if (need_max) {
           float m0 = -INFINITY, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
 #pragma unroll
           for (int i = 0; i < 32; i += 2) {
@@ -386,14 +394,13 @@ swa_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
             m2 = fmax3(m2, __uint_as_float(r[64 + i]), __uint_as_float(r[65 + i]));
             m3 = fmax3(m3, __uint_as_float(r[96 + i]), __uint_as_float(r[97 + i]));
           }
-          mx = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
+          m_tgt = fmaxf(m_tgt, fmaxf(fmaxf(m0, m1), fmaxf(m2, m3)) * c2);
         }
-        const float m_new = fmaxf(m_ref, mx * c2);
         if (first) {
-          m_ref = m_new;
-        } else if (__any_sync(0xffffffffu, m_new - m_ref > 8.0f)) {
-          const float alpha = fast_exp2(m_ref - m_new);
-          m_ref = m_new;
+          m_ref = m_tgt;
+        } else if (__any_sync(0xffffffffu, m_tgt - m_ref > 8.0f)) {
+          const float alpha = fast_exp2(m_ref - m_tgt);              // 0 for rows that had seen nothing yet
+          m_ref = m_tgt;
           l *= alpha;
           uint32_t t16[16];
 #pragma unroll 1
@@ -405,10 +412,12 @@ swa_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
             tmem_st16(o_tmem + 16 * c, t16);
           }
         }
+        pend = 0.f;
         PT_LAP(2);
         // P = exp2(S * c2 - m_ref) as bf16 into TMEM over S; row sum in fp32
         const uint64_t c2p = pack2f(c2, c2), nm = pack2f(-m_ref, -m_ref);
         uint64_t sum_a = pack2f(0.f, 0.f), sum_b = sum_a;
+        uint32_t pmax2 = 0u;                                         // running max of the packed bf16 P (both halves)
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
           uint32_t pk[16];
@@ -433,6 +442,11 @@ swa_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
             sum_b = fadd2(sum_b, pb);
             pk[i >> 1] = pack_bf16(p0, p1);
             pk[(i >> 1) + 1] = pack_bf16(p2, p3);
+            // P >= 0, so bf16 bit patterns order like unsigned integers
+            if (BOUNDED) {
+              const uint32_t a = pk[i >> 1], b2 = pk[(i >> 1) + 1];
+              pmax2 = max(pmax2, max(max(a & 0xffff0000u, b2 & 0xffff0000u), max(a << 16, b2 << 16)));
+            }
           }
           tmem_st16(s_tmem + 16 * c, pk);
         }
@@ -442,6 +456,10 @@ swa_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
           unpack2f(sum_a, a0, a1);
           unpack2f(sum_b, b0, b1);
           rowsum = (a0 + a1) + (b0 + b1);
+        }
+        if (BOUNDED) {                                               // largest P = 2^(how far the reference lags)
+          const float pmaxf = __uint_as_float(pmax2);
+          pend = pmaxf > 256.f ? __log2f(pmaxf) : 0.f;
         }
         l += rowsum;
         PT_LAP(3);
@@ -598,8 +616,10 @@ extern "C" void daisy_b200_prefill_clk_dump(long long* out, void* stream) { pref
 static int ensure_smem_attr() {
   static bool done = false;
   if (done) return DAISY_OK;
-  if (cudaFuncSetAttribute(swa_prefill_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, PREFILL_SMEM) != cudaSuccess) return DAISY_ECUDA;
-  if (cudaFuncSetAttribute(swa_prefill_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, PREFILL_SMEM) != cudaSuccess) return DAISY_ECUDA;
+  if (cudaFuncSetAttribute(swa_prefill_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, PREFILL_SMEM) != cudaSuccess) return DAISY_ECUDA;
+  if (cudaFuncSetAttribute(swa_prefill_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, PREFILL_SMEM) != cudaSuccess) return DAISY_ECUDA;
+  if (cudaFuncSetAttribute(swa_prefill_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, PREFILL_SMEM) != cudaSuccess) return DAISY_ECUDA;
+  if (cudaFuncSetAttribute(swa_prefill_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, PREFILL_SMEM) != cudaSuccess) return DAISY_ECUDA;
   if (cudaFuncSetAttribute(umma_selftest_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 1024 + 2 * TILE_BYTES + 64) != cudaSuccess) return DAISY_ECUDA;
   done = true;
   return DAISY_OK;
@@ -612,7 +632,7 @@ static int launch_attend(const void* q, const void* k, const void* v,
                          int64_t q_sb, int64_t q_st, int64_t q_sh, int64_t k_sb, int64_t k_st, int64_t k_sh,
                          int64_t v_sb, int64_t v_st, int64_t v_sh,
                          void* out, int64_t o_sb, int64_t o_st, int64_t o_sh,
-                         int B, int T, int H, int D, int window, float scale, const QTransform* qt,
+                         int B, int T, int H, int D, int window, float scale, const QTransform* qt, bool bounded_qk,
                          int* status_word, void* stream) {
   if (!q || !k || !v || !out || B <= 0 || T <= 0 || H <= 0 || !(scale > 0.f)) return DAISY_EINVAL;
   if (D != DAISY_HEAD_DIM) return DAISY_EUNSUPPORTED;
@@ -643,10 +663,14 @@ static int launch_attend(const void* q, const void* k, const void* v,
   if (sms <= 0) sms = daisy_b200_sm_count();
   if (sms <= 0) return DAISY_ENODEV;
   dim3 grid((unsigned)(items < sms ? items : sms), 1, 1);
-  if (qt && (qt->norm || qt->rope))
-    swa_prefill_kernel<true><<<grid, PREFILL_THREADS, PREFILL_SMEM, (cudaStream_t)stream>>>(tq, tk, tv, p);
-  else
-    swa_prefill_kernel<false><<<grid, PREFILL_THREADS, PREFILL_SMEM, (cudaStream_t)stream>>>(tq, tk, tv, p);
+  const bool raw = qt && (qt->norm || qt->rope);
+  // with RMS-normalised q and k every logit is bounded by scale * D: 2^(logit - reference) cannot overflow
+  const bool bounded = bounded_qk && scale * 1.4426950408889634f * (float)D <= 60.f;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (raw && bounded)       swa_prefill_kernel<true, true><<<grid, PREFILL_THREADS, PREFILL_SMEM, st>>>(tq, tk, tv, p);
+  else if (raw)             swa_prefill_kernel<true, false><<<grid, PREFILL_THREADS, PREFILL_SMEM, st>>>(tq, tk, tv, p);
+  else if (bounded)         swa_prefill_kernel<false, true><<<grid, PREFILL_THREADS, PREFILL_SMEM, st>>>(tq, tk, tv, p);
+  else                      swa_prefill_kernel<false, false><<<grid, PREFILL_THREADS, PREFILL_SMEM, st>>>(tq, tk, tv, p);
   DAISY_CHECK_LAUNCH();
   return DAISY_OK;
 }
@@ -659,7 +683,7 @@ extern "C" int daisy_b200_swa_attend(const void* q, const void* k, const void* v
                                      int B, int T, int H, int D, int window, float scale,
                                      int* status_word, void* stream) {
   return launch_attend(q, k, v, q_sb, q_st, q_sh, k_sb, k_st, k_sh, v_sb, v_st, v_sh, out, o_sb, o_st, o_sh,
-                       B, T, H, D, window, scale, nullptr, status_word, stream);
+                       B, T, H, D, window, scale, nullptr, false, status_word, stream);
 }
 
 static size_t align1k(size_t x) { return (x + 1023) & ~size_t(1023); }
@@ -693,6 +717,7 @@ extern "C" int daisy_b200_swa_prefill_fwd(const void* q, const void* k, const vo
   // memory one item ahead of its use.  Measured on C2 the in-kernel form is slower (1.46 ms vs 1.33 ms per
   // step: the transform competes with the softmax warps for issue slots and L2 latency), so it is opt-in.
   const bool q_in_kernel = (flags & DAISY_Q_IN_KERNEL) != 0;
+  const bool bounded_qk = (flags & DAISY_NORM_Q) && (flags & DAISY_NORM_K);
   void* qp = ws;
   const unsigned pf = (flags & DAISY_QKV_DEFAULT) | ((flags & DAISY_KV_BHTD) ? 0u : DAISY_OUT_BTHD);
   int rc = daisy_b200_qkv_prep(q_in_kernel ? nullptr : q, k, v, q_sb, q_st, q_sh, k_sb, k_st, k_sh, v_sb, v_st, v_sh, cos, sin,
@@ -704,10 +729,10 @@ extern "C" int daisy_b200_swa_prefill_fwd(const void* q, const void* k, const vo
   if (q_in_kernel) {
     QTransform qt{cos, sin, eps, (flags & DAISY_NORM_Q) ? 1 : 0, (flags & DAISY_ROPE) ? 1 : 0};
     return launch_attend(q, kp, vp, q_sb, q_st, q_sh, sb_, st_, sh_, sb_, st_, sh_, out, o_sb, o_st, o_sh,
-                         B, T, H, D, window, scale, &qt, status_word, stream);
+                         B, T, H, D, window, scale, &qt, bounded_qk, status_word, stream);
   }
   return launch_attend(qp, kp, vp, sb_, st_, sh_, sb_, st_, sh_, sb_, st_, sh_, out, o_sb, o_st, o_sh,
-                       B, T, H, D, window, scale, nullptr, status_word, stream);
+                       B, T, H, D, window, scale, nullptr, bounded_qk, status_word, stream);
 }
 
 extern "C" int daisy_b200_selftest_umma(const void* a, const void* b, float* c, int K, int mode,
