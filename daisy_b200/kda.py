@@ -29,20 +29,3 @@ def chunk_kda(q, k, v, g, beta, scale: Optional[float] = None, initial_state: Op
     o, hT = ops.kda_chunk_fwd(q, k, v, g, beta, scale, initial_state, output_final_state,
                               l2norm_qk=use_qk_l2norm_in_kernel, out_fp32=out_fp32)
     return o, hT
-
-
-def smoke_kda() -> None:
-    """One small KDA forward on cuda:0 against the fp32 token recurrence."""
-    from oracle import kda as okda
-    g_ = torch.Generator().manual_seed(0)
-    B, T, H, K = 1, 160, 2, 128
-    q, k, v = (torch.randn(B, T, H, K, generator=g_).bfloat16() for _ in range(3))
-    g = torch.nn.functional.logsigmoid(torch.randn(B, T, H, K, generator=g_))
-    beta = torch.sigmoid(torch.randn(B, T, H, generator=g_))
-    o_ref, s_ref = okda.kda_recurrent(q.float(), k.float(), v.float(), g, beta)
-    o, s = chunk_kda(q.cuda(), k.cuda(), v.cuda(), g.cuda(), beta.cuda(), output_final_state=True,
-                     use_qk_l2norm_in_kernel=True, out_fp32=True)
-    ops.check_device_status("cuda")
-    rel = ((o.cpu() - o_ref).norm() / o_ref.norm()).item()
-    rel_s = ((s.cpu() - s_ref).norm() / s_ref.norm()).item()
-    assert rel < 1e-3 and rel_s < 1e-3, ("kda", rel, rel_s)
