@@ -98,7 +98,9 @@ struct KdaIntraSmem {
   float rq[KC], rk[KC], beta[KC];
 };
 
-__global__ void __launch_bounds__(256, 1) kda_intra_kernel(const KdaIntraParams p) {
+constexpr int KDA_INTRA_THREADS = 512;   // 16 warps: one 200 KB CTA per SM, so latency is hidden by warps, not by CTAs
+
+__global__ void __launch_bounds__(KDA_INTRA_THREADS, 1) kda_intra_kernel(const KdaIntraParams p) {
   extern __shared__ __align__(128) uint8_t kda_smem_raw[];
   KdaIntraSmem& sm = *reinterpret_cast<KdaIntraSmem*>(kda_smem_raw);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g8 = lane >> 2, t4 = lane & 3;
@@ -112,10 +114,10 @@ __global__ void __launch_bounds__(256, 1) kda_intra_kernel(const KdaIntraParams 
   //           16-byte loads are issued before the first store so that ~20 are in flight per thread.
   {
     const size_t tok0 = ((size_t)b * p.T + t0) * p.H + h;          // token row index into [B,T,H,*]
-    uint4 rq_[4], rk_[4], rv_[4], rg_[8];
+    uint4 rq_[2], rk_[2], rv_[2], rg_[4];
 #pragma unroll
-    for (int u = 0; u < 4; ++u) {                                  // 16-byte chunks of the bf16 tiles
-      const int idx = tid + u * 256, r = idx >> 4, c8 = (idx & 15) * 8;
+    for (int u = 0; u < 2; ++u) {                                  // 16-byte chunks of the bf16 tiles
+      const int idx = tid + u * KDA_INTRA_THREADS, r = idx >> 4, c8 = (idx & 15) * 8;
       rq_[u] = rk_[u] = rv_[u] = make_uint4(0, 0, 0, 0);
       if (r < rows) {
         const size_t off = (tok0 + (size_t)r * p.H) * KD + c8;
@@ -123,55 +125,60 @@ __global__ void __launch_bounds__(256, 1) kda_intra_kernel(const KdaIntraParams 
       }
     }
 #pragma unroll
-    for (int u = 0; u < 8; ++u) {                                  // 16-byte chunks of the fp32 gate tile
-      const int idx = tid + u * 256, r = idx >> 5, c4 = (idx & 31) * 4;
+    for (int u = 0; u < 4; ++u) {                                  // 16-byte chunks of the fp32 gate tile
+      const int idx = tid + u * KDA_INTRA_THREADS, r = idx >> 5, c4 = (idx & 31) * 4;
       rg_[u] = make_uint4(0, 0, 0, 0);
       if (r < rows) rg_[u] = ld_stream16(p.g + (tok0 + (size_t)r * p.H) * KD + c4);
     }
     if (tid < KC) sm.beta[tid] = tid < rows ? p.beta[tok0 + (size_t)tid * p.H] : 0.f;
-    for (int idx = tid; idx < KC * LDT / 2; idx += 256) reinterpret_cast<uint32_t*>(&sm.Aqk[0][0])[idx] = 0u;
-    for (int idx = tid; idx < KC * LDA; idx += 256) { (&sm.Akk[0][0])[idx] = 0.f; (&sm.Tm[0][0])[idx] = 0.f; }
+    for (int idx = tid; idx < KC * LDT / 2; idx += KDA_INTRA_THREADS) reinterpret_cast<uint32_t*>(&sm.Aqk[0][0])[idx] = 0u;
+    for (int idx = tid; idx < KC * LDA; idx += KDA_INTRA_THREADS) { (&sm.Akk[0][0])[idx] = 0.f; (&sm.Tm[0][0])[idx] = 0.f; }
 #pragma unroll
-    for (int u = 0; u < 4; ++u) {
-      const int idx = tid + u * 256, r = idx >> 4, c8 = (idx & 15) * 8;
+    for (int u = 0; u < 2; ++u) {
+      const int idx = tid + u * KDA_INTRA_THREADS, r = idx >> 4, c8 = (idx & 15) * 8;
       *reinterpret_cast<uint4*>(&sm.qraw[r][c8]) = rq_[u];
       *reinterpret_cast<uint4*>(&sm.kraw[r][c8]) = rk_[u];
       *reinterpret_cast<uint4*>(&sm.vraw[r][c8]) = rv_[u];
     }
 #pragma unroll
-    for (int u = 0; u < 8; ++u) {
-      const int idx = tid + u * 256, r = idx >> 5, c4 = (idx & 31) * 4;
+    for (int u = 0; u < 4; ++u) {
+      const int idx = tid + u * KDA_INTRA_THREADS, r = idx >> 5, c4 = (idx & 31) * 4;
       *reinterpret_cast<uint4*>(&sm.G[r][c4]) = rg_[u];
     }
   }
   __syncthreads();
 
   KDA_MARK(1);
-  // ---- P1: cumulative gates (threads 0-127, one channel each) and L2 norms (threads 128-255)
+  // ---- P1: cumulative gates (threads 0-127, one channel each) and L2 norms (threads 128-383)
   if (tid < KD) {
     float acc = 0.f;
 #pragma unroll 8
     for (int i = 0; i < KC; ++i) { acc += sm.G[i][tid]; sm.G[i][tid] = acc; }
-  } else {
-    const int r = (tid - KD) >> 1, half = tid & 1;
-    float sq = 0.f, sk = 0.f;
+  } else if (tid < KD + 4 * KC) {
+    const int r = (tid - KD) >> 2, quarter = tid & 3;                // four threads per row, 32 channels each
+    float sq = 0.f, sk = 0.f, dqk = 0.f;
 #pragma unroll 8
-    for (int c = 0; c < 64; ++c) {
-      const float xq = __bfloat162float(sm.qraw[r][half * 64 + c]), xk = __bfloat162float(sm.kraw[r][half * 64 + c]);
-      sq = fmaf(xq, xq, sq); sk = fmaf(xk, xk, sk);
+    for (int c = 0; c < 32; ++c) {
+      const float xq = __bfloat162float(sm.qraw[r][quarter * 32 + c]), xk = __bfloat162float(sm.kraw[r][quarter * 32 + c]);
+      sq = fmaf(xq, xq, sq); sk = fmaf(xk, xk, sk); dqk = fmaf(xq, xk, dqk);
     }
-    sq += __shfl_xor_sync(0xffffffffu, sq, 1);
-    sk += __shfl_xor_sync(0xffffffffu, sk, 1);
-    if (half == 0) {
-      sm.rq[r] = p.l2norm ? rsqrtf(sq + 1e-6f) : 1.f;
-      sm.rk[r] = p.l2norm ? rsqrtf(sk + 1e-6f) : 1.f;
+#pragma unroll
+    for (int o = 1; o <= 2; o <<= 1) {
+      sq += __shfl_xor_sync(0xffffffffu, sq, o);
+      sk += __shfl_xor_sync(0xffffffffu, sk, o);
+      dqk += __shfl_xor_sync(0xffffffffu, dqk, o);
+    }
+    if (quarter == 0) {
+      const float a = p.l2norm ? rsqrtf(sq + 1e-6f) : 1.f, c = p.l2norm ? rsqrtf(sk + 1e-6f) : 1.f;
+      sm.rq[r] = a; sm.rk[r] = c;
+      sm.Aqk[r][r] = __float2half_rn(p.scale * a * c * dqk);         // diagonal of A_qk: q_i . k_i, no decay
     }
   }
   __syncthreads();
 
   KDA_MARK(2);
   // ---- P2: element-wise images: q~ and k~^T and e^{G_C} straight to the workspace, X^T and Y^T to smem
-  for (int idx = tid; idx < KC * 16; idx += 256) {                 // q~[i][8 channels]
+  for (int idx = tid; idx < KC * 16; idx += KDA_INTRA_THREADS) {                 // q~[i][8 channels]
     const int i = idx >> 4, c8 = (idx & 15) * 8;
     const float rs = sm.rq[i] * p.scale;
     uint32_t o[4];
@@ -183,7 +190,7 @@ __global__ void __launch_bounds__(256, 1) kda_intra_kernel(const KdaIntraParams 
     }
     *reinterpret_cast<uint4*>(rec + OFF_Q + ((size_t)i * LDW + c8) * 2) = make_uint4(o[0], o[1], o[2], o[3]);
   }
-  for (int idx = tid; idx < KD * 8; idx += 256) {                  // (channel c, 8 tokens)
+  for (int idx = tid; idx < KD * 8; idx += KDA_INTRA_THREADS) {                  // (channel c, 8 tokens)
     const int c = idx & (KD - 1), j8 = (idx >> 7) * 8;
     const float gc = sm.G[KC - 1][c];
     uint32_t kt[4], xt[4], yt[4];
@@ -217,15 +224,17 @@ __global__ void __launch_bounds__(256, 1) kda_intra_kernel(const KdaIntraParams 
   // the right operand.  Mk = k * factor (all rows), Mq = q * factor (upper rows, else 0) are staged as fp16 and
   // the level's blocks are plain m16n8k16 products; no exponent is ever positive, whatever the gate values.
   {
-    const int brow = tid >> 2, bq = (tid & 3) * 8;                   // build: row and channels bq + 32 k .. + 8 (conflict-free)
-    // this thread's 32 normalised k and q values and cumulative gates stay in registers across the six levels
-    float kn[32], qn[32], gi[32];
+    // build mapping: lanes 0-7 of a warp take 8 consecutive rows at the same channels, so every 8-lane phase of a
+    // 16-byte shared-memory access spreads over all banks (row strides are 4 banks apart).  Two warps share
+    // eight rows; a thread owns channels bq + 64 k .. + 8 (k = 0, 1).
+    const int brow = (warp >> 1) * 8 + (lane & 7), bq = ((lane >> 3) + 4 * (warp & 1)) * 8;
+    // this thread's 16 normalised k and q values and cumulative gates stay in registers across the six levels
+    float kn[16], qn[16], gi[16];
     {
       const float rkb = sm.rk[brow], rqb = sm.rq[brow];
-      float dot = 0.f;
 #pragma unroll
-      for (int kq = 0; kq < 4; ++kq) {
-        const int c = bq + 32 * kq;
+      for (int kq = 0; kq < 2; ++kq) {
+        const int c = bq + 64 * kq;
         float kf[8], qf[8];
         unpack8(*reinterpret_cast<const uint4*>(&sm.kraw[brow][c]), kf);
         unpack8(*reinterpret_cast<const uint4*>(&sm.qraw[brow][c]), qf);
@@ -233,14 +242,8 @@ __global__ void __launch_bounds__(256, 1) kda_intra_kernel(const KdaIntraParams 
         const float4 g1 = *reinterpret_cast<const float4*>(&sm.G[brow][c + 4]);
         const float gg[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
 #pragma unroll
-        for (int e = 0; e < 8; ++e) {
-          kn[8 * kq + e] = kf[e] * rkb; qn[8 * kq + e] = qf[e] * rqb; gi[8 * kq + e] = gg[e];
-          dot = fmaf(kn[8 * kq + e], qn[8 * kq + e], dot);
-        }
+        for (int e = 0; e < 8; ++e) { kn[8 * kq + e] = kf[e] * rkb; qn[8 * kq + e] = qf[e] * rqb; gi[8 * kq + e] = gg[e]; }
       }
-      dot += __shfl_xor_sync(0xffffffffu, dot, 1);                   // diagonal of A_qk: q_i . k_i, no decay
-      dot += __shfl_xor_sync(0xffffffffu, dot, 2);
-      if ((tid & 3) == 0) sm.Aqk[brow][brow] = __float2half_rn(p.scale * dot);
     }
     KDA_LAP_DECL;
 #pragma unroll 1
@@ -251,8 +254,8 @@ __global__ void __launch_bounds__(256, 1) kda_intra_kernel(const KdaIntraParams 
         const bool upper = (brow & s) != 0;
         const int ref = (brow & ~(2 * s - 1)) + s - 1;
 #pragma unroll
-        for (int kq = 0; kq < 4; ++kq) {
-          const int c = bq + 32 * kq;
+        for (int kq = 0; kq < 2; ++kq) {
+          const int c = bq + 64 * kq;
           const float4 r0 = *reinterpret_cast<const float4*>(&sm.G[ref][c]);
           const float4 r1 = *reinterpret_cast<const float4*>(&sm.G[ref][c + 4]);
           const float gr[8] = {r0.x, r0.y, r0.z, r0.w, r1.x, r1.y, r1.z, r1.w};
@@ -273,12 +276,15 @@ __global__ void __launch_bounds__(256, 1) kda_intra_kernel(const KdaIntraParams 
       // -- the level's blocks.  A tile = 16 rows x 8 columns; for s <= 8 one 16-row tile spans 8/s groups and
       //    its 8 columns are the lower halves of those groups (column n -> group n / s, offset n % s).
       {
-        int mrow, ncol0, which;                                      // which: 0 = A_kk, 1 = A_qk, 2 = both
-        bool active = true;
-        if (s == 32) { mrow = 32 + 16 * (warp >> 2); ncol0 = 8 * (warp & 3); which = 2; }
-        else if (s == 16) { const int c = warp & 3; mrow = 16 + 32 * (c >> 1); ncol0 = 32 * (c >> 1) + 8 * (c & 1); which = warp >> 2; }
-        else { mrow = 16 * (warp & 3); ncol0 = mrow; which = warp >> 2; }
-        (void)active;
+        // 16 warps: level 32 has 8 tiles per matrix (warp -> tile w & 7, matrix w >> 3); the other levels have 4
+        // (warp -> tile w & 3, matrix (w >> 2) & 1) and keep warps 8-15 free for the next build
+        int mrow, ncol0;
+        const int which = (s == 32) ? (warp >> 3) : ((warp >> 2) & 1);      // 0 = A_kk, 1 = A_qk
+        const bool active = (s == 32) || warp < 8;
+        if (s == 32) { const int c = warp & 7; mrow = 32 + 16 * (c >> 2); ncol0 = 8 * (c & 3); }
+        else if (s == 16) { const int c = warp & 3; mrow = 16 + 32 * (c >> 1); ncol0 = 32 * (c >> 1) + 8 * (c & 1); }
+        else { mrow = 16 * (warp & 3); ncol0 = mrow; }
+        if (active) {
         // column (token) held by this lane's B fragment, and validity of this lane's four outputs
         const int nb = g8;                                           // B fragment: n = lane >> 2
         const int jb = (s >= 8) ? ncol0 + nb : mrow + ((nb >> ls) << (ls + 1)) + (nb & (s - 1));
@@ -306,21 +312,6 @@ __global__ void __launch_bounds__(256, 1) kda_intra_kernel(const KdaIntraParams 
           mma_f16(accA, af[ks], bf[ks][0], bf[ks][1]);
           mma_f16(accB, af[ks + 1], bf[ks + 1][0], bf[ks + 1][1]);
         }
-        if (which == 2) {                                            // level 32: this warp also owns the A_qk tile
-#pragma unroll
-          for (int ks = 0; ks < KD / 16; ++ks) {
-            const int c = ks * 16 + 2 * t4;
-            af[ks][0] = *reinterpret_cast<const uint32_t*>(&sm.Mq[i0][c]);
-            af[ks][1] = *reinterpret_cast<const uint32_t*>(&sm.Mq[i1][c]);
-            af[ks][2] = *reinterpret_cast<const uint32_t*>(&sm.Mq[i0][c + 8]);
-            af[ks][3] = *reinterpret_cast<const uint32_t*>(&sm.Mq[i1][c + 8]);
-          }
-#pragma unroll
-          for (int ks = 0; ks < KD / 16; ks += 2) {
-            mma_f16(acc_q, af[ks], bf[ks][0], bf[ks][1]);
-            mma_f16(acc_q2, af[ks + 1], bf[ks + 1][0], bf[ks + 1][1]);
-          }
-        }
 #pragma unroll
         for (int x = 0; x < 4; ++x) { acc_k[x] += acc_k2[x]; acc_q[x] += acc_q2[x]; }
         // outputs: rows i0 (acc[0],acc[1]) and i1 (acc[2],acc[3]), tile columns 2 t4, 2 t4 + 1
@@ -339,6 +330,7 @@ __global__ void __launch_bounds__(256, 1) kda_intra_kernel(const KdaIntraParams 
             if (which != 1) sm.Akk[i][j] = sm.beta[i] * acc_k[x];
             if (which != 0) sm.Aqk[i][j] = __float2half_rn(p.scale * acc_q[x]);
           }
+        }
         }
       }
       KDA_LAP(12);
@@ -368,11 +360,12 @@ __global__ void __launch_bounds__(256, 1) kda_intra_kernel(const KdaIntraParams 
   //          up to three 16-column blocks each.  T is zero above its diagonal, so the inner sums run over
   //          fixed ranges and unroll.
   {
-    const int r = tid >> 4, cc = tid & 15;
+    const bool act = tid < 256;                                    // 16 rows x 16 columns; the barriers stay uniform
+    const int r = (tid >> 4) & 15, cc = tid & 15;
     for (int I = 1; I < 4; ++I) {
       float w[3] = {0.f, 0.f, 0.f};
       const float* arow = &sm.Akk[I * 16 + r][0];
-      for (int mb = 0; mb < I; ++mb) {
+      for (int mb = 0; act && mb < I; ++mb) {
 #pragma unroll
         for (int mm = 0; mm < 16; ++mm) {
           const int m = mb * 16 + mm;
@@ -384,33 +377,33 @@ __global__ void __launch_bounds__(256, 1) kda_intra_kernel(const KdaIntraParams 
       }
       __syncthreads();
 #pragma unroll
-      for (int cb = 0; cb < 3; ++cb) sm.Wt[r][cb * 16 + cc] = w[cb];
+      for (int cb = 0; cb < 3; ++cb) if (act) sm.Wt[r][cb * 16 + cc] = w[cb];
       __syncthreads();
       float s[3] = {0.f, 0.f, 0.f};
       const float* trow = &sm.Tm[I * 16 + r][I * 16];
 #pragma unroll
-      for (int m = 0; m < 16; ++m) {
+      for (int m = 0; act && m < 16; ++m) {
         const float tv = trow[m];                                  // zero for m > r
 #pragma unroll
         for (int cb = 0; cb < 3; ++cb) s[cb] = fmaf(tv, sm.Wt[m][cb * 16 + cc], s[cb]);
       }
 #pragma unroll
       for (int cb = 0; cb < 3; ++cb)
-        if (cb < I) sm.Tm[I * 16 + r][cb * 16 + cc] = -s[cb];
+        if (act && cb < I) sm.Tm[I * 16 + r][cb * 16 + cc] = -s[cb];
       __syncthreads();
     }
   }
 
   KDA_MARK(7);
-  // ---- P5: W = T X  (warp = row block I x channel half) and U0^T = Y^T T^T (warp = 16 V rows), fp16 MMAs.
+  // ---- P5: W = T X  (warp = row block I x channel quarter) and U0^T = Y^T T^T (warp = 16 V rows x token half), fp16 MMAs.
   //          G and kraw/qraw are dead: they become the staging images.
   __half* w_img = reinterpret_cast<__half*>(&sm.G[0][0]);          // [64][136]
   __half* u_img = reinterpret_cast<__half*>(&sm.kraw[0][0]);       // [128][72]  (kraw + qraw = 32 KB)
   {
-    const int I = warp >> 1, ch = (warp & 1) * 64;
-    float acc[8][4];
+    const int I = warp >> 2, ch = (warp & 3) * 32;
+    float acc[4][4];
 #pragma unroll
-    for (int nt = 0; nt < 8; ++nt) { acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f; }
+    for (int nt = 0; nt < 4; ++nt) { acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f; }
     const int i0 = I * 16 + g8, i1 = i0 + 8;
     for (int ks = 0; ks <= I; ++ks) {
       uint32_t a[4];
@@ -420,24 +413,24 @@ __global__ void __launch_bounds__(256, 1) kda_intra_kernel(const KdaIntraParams 
       a[2] = pack_h2(sm.Tm[i0][j + 8], sm.Tm[i0][j + 9]);
       a[3] = pack_h2(sm.Tm[i1][j + 8], sm.Tm[i1][j + 9]);
 #pragma unroll
-      for (int nt = 0; nt < 8; ++nt) {
+      for (int nt = 0; nt < 4; ++nt) {
         const int c = ch + nt * 8 + g8;
         mma_f16(acc[nt], a, *reinterpret_cast<const uint32_t*>(&sm.XT[c][j]), *reinterpret_cast<const uint32_t*>(&sm.XT[c][j + 8]));
       }
     }
     __syncthreads();                                               // every reader of G is done
 #pragma unroll
-    for (int nt = 0; nt < 8; ++nt) {
+    for (int nt = 0; nt < 4; ++nt) {
       const int c = ch + nt * 8 + 2 * t4;
       *reinterpret_cast<uint32_t*>(&w_img[i0 * LDW + c]) = pack_h2(acc[nt][0], acc[nt][1]);
       *reinterpret_cast<uint32_t*>(&w_img[i1 * LDW + c]) = pack_h2(acc[nt][2], acc[nt][3]);
     }
   }
   {
-    const int v0 = warp * 16 + g8, v1 = v0 + 8;
-    float acc[8][4];
+    const int v0 = (warp >> 1) * 16 + g8, v1 = v0 + 8, nt0 = (warp & 1) * 4;
+    float acc[4][4];
 #pragma unroll
-    for (int nt = 0; nt < 8; ++nt) { acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f; }
+    for (int nt = 0; nt < 4; ++nt) { acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f; }
     for (int ks = 0; ks < 4; ++ks) {
       uint32_t a[4];
       const int j = ks * 16 + 2 * t4;
@@ -446,15 +439,15 @@ __global__ void __launch_bounds__(256, 1) kda_intra_kernel(const KdaIntraParams 
       a[2] = *reinterpret_cast<const uint32_t*>(&sm.YT[v0][j + 8]);
       a[3] = *reinterpret_cast<const uint32_t*>(&sm.YT[v1][j + 8]);
 #pragma unroll
-      for (int nt = 0; nt < 8; ++nt) {
-        if (ks * 16 > nt * 8 + 7) continue;                        // T[i][j] = 0 for j > i
-        const int i = nt * 8 + g8;
+      for (int nt = 0; nt < 4; ++nt) {
+        if (ks * 16 > (nt0 + nt) * 8 + 7) continue;                // T[i][j] = 0 for j > i
+        const int i = (nt0 + nt) * 8 + g8;
         mma_f16(acc[nt], a, pack_h2(sm.Tm[i][j], sm.Tm[i][j + 1]), pack_h2(sm.Tm[i][j + 8], sm.Tm[i][j + 9]));
       }
     }
 #pragma unroll
-    for (int nt = 0; nt < 8; ++nt) {
-      const int i = nt * 8 + 2 * t4;
+    for (int nt = 0; nt < 4; ++nt) {
+      const int i = (nt0 + nt) * 8 + 2 * t4;
       *reinterpret_cast<uint32_t*>(&u_img[v0 * LDT + i]) = pack_h2(acc[nt][0], acc[nt][1]);
       *reinterpret_cast<uint32_t*>(&u_img[v1 * LDT + i]) = pack_h2(acc[nt][2], acc[nt][3]);
     }
@@ -463,11 +456,11 @@ __global__ void __launch_bounds__(256, 1) kda_intra_kernel(const KdaIntraParams 
 
   KDA_MARK(8);
   // ---- P6: staged images -> workspace, 16 bytes per thread per store
-  for (int idx = tid; idx < KC * LDW * 2 / 16; idx += 256)
+  for (int idx = tid; idx < KC * LDW * 2 / 16; idx += KDA_INTRA_THREADS)
     reinterpret_cast<uint4*>(rec + OFF_W)[idx] = reinterpret_cast<const uint4*>(w_img)[idx];
-  for (int idx = tid; idx < KD * LDT * 2 / 16; idx += 256)
+  for (int idx = tid; idx < KD * LDT * 2 / 16; idx += KDA_INTRA_THREADS)
     reinterpret_cast<uint4*>(rec + OFF_UT)[idx] = reinterpret_cast<const uint4*>(u_img)[idx];
-  for (int idx = tid; idx < KC * LDT * 2 / 16; idx += 256)
+  for (int idx = tid; idx < KC * LDT * 2 / 16; idx += KDA_INTRA_THREADS)
     reinterpret_cast<uint4*>(rec + OFF_AQK)[idx] = reinterpret_cast<const uint4*>(&sm.Aqk[0][0])[idx];
   KDA_MARK(9);
 }
@@ -712,7 +705,7 @@ extern "C" int daisy_b200_kda_chunk_fwd(const void* q, const void* k, const void
   ip.T = T; ip.H = H; ip.NC = NC;
   ip.scale = scale > 0.f ? scale : 1.0f / sqrtf((float)K);
   ip.l2norm = (flags & DAISY_KDA_L2NORM_QK) ? 1 : 0;
-  kda_intra_kernel<<<dim3(NC, H, B), 256, sizeof(KdaIntraSmem), st>>>(ip);
+  kda_intra_kernel<<<dim3(NC, H, B), KDA_INTRA_THREADS, sizeof(KdaIntraSmem), st>>>(ip);
   DAISY_CHECK_LAUNCH();
 
   KdaStateParams sp;
