@@ -16,18 +16,28 @@
 // All mbarrier waits are bounded; a wait that runs out raises an abort flag that every role polls,
 // the CTA drains to its teardown, frees TMEM and reports DAISY_ETIMEOUT through the status word.
 #include "common.cuh"
+#include <mutex>
+#include <cstdlib>
 
 namespace daisy {
 
 constexpr int BM = 128;
 constexpr int BN = 128;
-constexpr int NSTAGE = 3;              // K/V ring stages (32 KB each)
-constexpr int NQBUF = 2;               // Q double buffer: the next item's Q lands while this item computes
+#ifndef PREFILL_NSTAGE
+#define PREFILL_NSTAGE 3
+#endif
+#ifndef PREFILL_NQBUF
+#define PREFILL_NQBUF 2
+#endif
+constexpr int NSTAGE = PREFILL_NSTAGE; // K/V ring stages (32 KB each)
+constexpr int NQBUF = PREFILL_NQBUF;   // Q double buffer: the next item's Q lands while this item computes
 constexpr int TILE_BYTES = BM * DAISY_HEAD_DIM * 2;      // 32768
 constexpr int HALF_BYTES = TILE_BYTES / 2;               // one [128 x 64] swizzled box
-constexpr int PREFILL_THREADS = 320;
+constexpr int PREFILL_THREADS = 320;          // one softmax warpgroup per stream
+constexpr int PREFILL_THREADS_SPLIT = 576;    // two softmax warpgroups per stream (64 key columns each)
 constexpr int SMEM_TILES = (2 * NQBUF + NSTAGE) * TILE_BYTES;
-constexpr int PREFILL_SMEM = 1024 + SMEM_TILES + 256;
+constexpr int PREFILL_SMEM = 1024 + SMEM_TILES + 256 + 2 * 128 * 4;   // alignment slack, tiles, barriers, row-sum exchange
+static_assert(PREFILL_SMEM <= 232448, "over the 227 KB a CTA may use");
 constexpr float NEG_BIG = -1.0e30f;
 #ifndef POLY_HALF
 #define POLY_HALF 0                      // 1: every second pair of exponentials by polynomial; 0: one pair in four
@@ -105,8 +115,14 @@ __device__ __forceinline__ ItemGeom item_geom(int item, int nq, int H, int T, in
 // running counters per role, so the K/V ring, the Q buffers and the TMEM accumulators carry over from
 // one item to the next: the producer prefetches the next item's Q and K while the softmax warps are
 // still writing the previous item's output.
-template <bool QRAW, bool BOUNDED>
-__global__ void __launch_bounds__(PREFILL_THREADS, 1)
+//
+// NSPLIT = 2 (bounded logits only): each stream's S tile is shared by two warpgroups, 64 key columns each, so a
+// tile's exponentials take half as long on the critical path  Q K^T -> softmax -> P V  of its stream.  With
+// |logit * log2 e| <= 60 no reference maximum is needed at all (2^x stays far inside fp32 and bf16 range), so the
+// two halves of a row never talk to each other until the epilogue adds their partial row sums.  Each half writes
+// its P over the first 32 columns of its OWN 64 S columns (P_s = two 32-column pieces at S_s + 0 and S_s + 64).
+template <bool QRAW, bool BOUNDED, int NSPLIT>
+__global__ void __launch_bounds__(32 * (8 * NSPLIT + 2), 1)
 swa_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                    const __grid_constant__ CUtensorMap tm_v, const PrefillParams p) {
   extern __shared__ uint8_t smem_raw[];
@@ -116,6 +132,8 @@ swa_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
   PrefillBarriers* bars = reinterpret_cast<PrefillBarriers*>(smem + SMEM_TILES);
   volatile int* abort_flag = &bars->abort_flag;
 
+  static_assert(NSPLIT == 1 || (NSPLIT == 2 && BOUNDED && !QRAW), "the split softmax needs bounded logits and a prepared Q");
+  constexpr int TMA_WARP = 8 * NSPLIT, MMA_WARP = 8 * NSPLIT + 1;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int T = p.T, window = p.window;
   const int nq = (T + 2 * BM - 1) / (2 * BM);
@@ -125,14 +143,14 @@ swa_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     for (int s = 0; s < 2; ++s) {
       for (int qb = 0; qb < NQBUF; ++qb) { mbar_init(&bars->q_full[s][qb], 1); mbar_init(&bars->q_empty[s][qb], 1); mbar_init(&bars->q_ready[s][qb], 128); }
       mbar_init(&bars->s_full[s], 1);
-      mbar_init(&bars->p_full[s], 128);
+      mbar_init(&bars->p_full[s], 128 * NSPLIT);
       mbar_init(&bars->o_full[s], 1);
     }
     for (int i = 0; i < NSTAGE; ++i) { mbar_init(&bars->kv_full[i], 1); mbar_init(&bars->kv_empty[i], 1); }
     bars->abort_flag = 0;
     mbar_init_fence();
   }
-  if (warp == 9) {
+  if (warp == MMA_WARP) {
     tmem_alloc(&bars->tmem_base, 512);
     tmem_relinquish();
   }
@@ -141,7 +159,7 @@ swa_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
   tc_fence_after();
   const uint32_t tmem_base = bars->tmem_base;
 
-  if (warp == 8) {
+  if (warp == TMA_WARP) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
       prefetch_tmap(&tm_q); prefetch_tmap(&tm_k); prefetch_tmap(&tm_v);
@@ -179,11 +197,11 @@ swa_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
           }
           // next item's Q: after this item's first K/V tiles are on their way (its buffer was released when the
           // previous item issued its last Q K^T, which the ring has long passed by now)
-          if (j == g.jlo && item + (int)gridDim.x < n_items) load_q(item + gridDim.x);
+          if (j == (NQBUF > 1 ? g.jlo : g.jhi) && item + (int)gridDim.x < n_items) load_q(item + gridDim.x);
         }
       }
     }
-  } else if (warp == 9) {
+  } else if (warp == MMA_WARP) {
     // ------------------------------------------------------------------ MMA issuer (one thread)
     // Issue order per K/V tile j:  PV_0(j-1) QK_0(j) PV_1(j-1) QK_1(j).  While softmax 0 works on S_0(j) the
     // tensor core runs stream 1's pair and vice versa.  (Splitting the issue over one thread per stream was
@@ -230,8 +248,8 @@ swa_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
               const bool first = (j - 1 == g.jlo_s[s]);             // first PV of the item overwrites O_s
               umma_ts_lh_p(leader, o_tmem, s_tmem, v_lo, v_hi, idesc_pv, first ? 0u : 1u);
 #pragma unroll
-              for (int k = 1; k < BN / 16; ++k)
-                umma_ts_lh_p(leader, o_tmem, s_tmem + k * 8, v_lo + k * (2048 >> 4), v_hi, idesc_pv, 1u);
+              for (int k = 1; k < BN / 16; ++k)   // P columns: contiguous, or (split softmax) 32 at S_s and 32 at S_s + 64
+                umma_ts_lh_p(leader, o_tmem, s_tmem + (NSPLIT == 2 ? (k & 3) * 8 + (k >> 2) * 64 : k * 8), v_lo + k * (2048 >> 4), v_hi, idesc_pv, 1u);
               const bool other_uses = (s == 0) && g.valid[1] && (j - 1 >= g.jlo_s[1]) && (j - 1 <= g.jhi_s[1]);
               if (!other_uses) tc_commit_p(leader, &bars->kv_empty[stage]);
               if (j - 1 == g.jhi_s[s]) tc_commit_p(leader, &bars->o_full[s]);
@@ -270,6 +288,149 @@ swa_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       PT_LAP(5);
       PT_FLUSH(16, lane == 0);
     }
+  } else if constexpr (NSPLIT == 2) {
+    // ------------------------------------------------------------------ split softmax + epilogue (bounded logits)
+    const int grp = warp >> 2, quarter = warp & 3;
+    const int s = grp & 1, half = grp >> 1;
+    const int row = quarter * 32 + lane;
+    const uint32_t lane_off = (uint32_t)(quarter * 32) << 16;
+    const uint32_t s_tmem = tmem_base + lane_off + s * 128 + half * 64;          // this thread's 64 S columns; P over the first 32
+    const uint32_t o_tmem = tmem_base + lane_off + 256 + s * 128 + half * 64;    // and its 64 output columns in the epilogue
+    float* lsum = reinterpret_cast<float*>(smem + SMEM_TILES + 256) + s * 128 + row;   // one exchange slot per row
+    const uint64_t c2p = pack2f(p.scale_log2, p.scale_log2);
+    uint32_t n_s = 0, n_o = 0;
+    bool ok = true;
+    PT_DECL;
+    PT_START();
+    for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
+      const ItemGeom g = item_geom(item, nq, p.H, T, window);
+      if (!g.valid[s]) continue;
+      const int q0 = g.q0[s];
+      const int q_row = q0 + row;
+      uint64_t sum_a = pack2f(0.f, 0.f), sum_b = sum_a;
+      for (int j = g.jlo_s[s]; j <= g.jhi_s[s]; ++j) {
+        ok = __all_sync(0xffffffffu, mbar_wait(&bars->s_full[s], n_s & 1, abort_flag, p.status, 6));
+        if (!ok) break;
+        ++n_s;
+        PT_LAP(0);
+        tc_fence_after();
+        const int k0 = j * BN + half * 64;                            // key index of this thread's first column
+        const bool full_tile = (j * BN + BN - 1 <= q0) && (window <= 0 || j * BN > q0 + BM - 1 - window);
+        uint32_t r[64];
+        tmem_ld32(s_tmem, r);
+        tmem_ld32(s_tmem + 32, r + 32);
+        tc_wait_ld();
+        PT_LAP(1);
+        if (!full_tile) {
+          const int hi = q_row - k0;                                   // column i is visible iff lo < i <= hi
+          const int lo = window > 0 ? q_row - window - k0 : -1;
+#pragma unroll
+          for (int i = 0; i < 64; ++i)
+            if (!(i > lo && i <= hi)) r[i] = 0xff800000u;              // -inf -> weight 0
+        }
+        PT_LAP(2);
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          uint32_t pk[16];
+#pragma unroll
+          for (int i = 0; i < 32; i += 4) {
+            const uint64_t xa = fmul2(pack2f(__uint_as_float(r[32 * c + i]), __uint_as_float(r[32 * c + i + 1])), c2p);
+            const uint64_t xb = fmul2(pack2f(__uint_as_float(r[32 * c + i + 2]), __uint_as_float(r[32 * c + i + 3])), c2p);
+            float x0, x1, p2, p3;
+            unpack2f(xa, x0, x1);
+            const float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
+            uint64_t pb;
+            if (POLY_HALF || (i & 4) == 4) {                           // a share of the pairs goes to the FMA pipes
+              pb = exp2_poly2(xb);
+              unpack2f(pb, p2, p3);
+            } else {
+              float x2, x3;
+              unpack2f(xb, x2, x3);
+              p2 = fast_exp2(x2); p3 = fast_exp2(x3);
+              pb = pack2f(p2, p3);
+            }
+            sum_a = fadd2(sum_a, pack2f(p0, p1));
+            sum_b = fadd2(sum_b, pb);
+            pk[i >> 1] = pack_bf16(p0, p1);
+            pk[(i >> 1) + 1] = pack_bf16(p2, p3);
+          }
+          tmem_st16(s_tmem + 16 * c, pk);
+        }
+        PT_LAP(3);
+        tc_wait_st();
+        tc_fence_before();
+        mbar_arrive(&bars->p_full[s]);
+        PT_LAP(4);
+      }
+      float l;
+      {
+        float a0, a1, b0, b1;
+        unpack2f(sum_a, a0, a1);
+        unpack2f(sum_b, b0, b1);
+        l = (a0 + a1) + (b0 + b1);
+      }
+      // the upper half publishes its partial sum, the lower half replaces it by the total (one slot per row)
+      if (half == 1) *lsum = l;
+      if (s == 0) asm volatile("bar.sync 1, 256;" ::: "memory");       // the 256 threads of this stream
+      else        asm volatile("bar.sync 2, 256;" ::: "memory");
+      if (half == 0) { l += *lsum; *lsum = l; }
+      if (s == 0) asm volatile("bar.sync 1, 256;" ::: "memory");
+      else        asm volatile("bar.sync 2, 256;" ::: "memory");
+      if (half == 1) l = *lsum;
+      if (ok) {
+        ok = __all_sync(0xffffffffu, mbar_wait(&bars->o_full[s], n_o & 1, abort_flag, p.status, 7));
+        ++n_o;
+      }
+      PT_LAP(5);
+      if (ok) {
+        tc_fence_after();
+        const float inv = 1.0f / l;
+        uint32_t r[64];
+        tmem_ld32(o_tmem, r);
+        tmem_ld32(o_tmem + 32, r + 32);
+        tc_wait_ld();
+        // this thread's 64 normalised outputs as eight 16-byte chunks
+        uint4 ch[8];
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+          ch[c].x = pack_bf16(__uint_as_float(r[8 * c]) * inv, __uint_as_float(r[8 * c + 1]) * inv);
+          ch[c].y = pack_bf16(__uint_as_float(r[8 * c + 2]) * inv, __uint_as_float(r[8 * c + 3]) * inv);
+          ch[c].z = pack_bf16(__uint_as_float(r[8 * c + 4]) * inv, __uint_as_float(r[8 * c + 5]) * inv);
+          ch[c].w = pack_bf16(__uint_as_float(r[8 * c + 6]) * inv, __uint_as_float(r[8 * c + 7]) * inv);
+        }
+        // 8 x 8 transpose of chunks inside each group of eight lanes (three butterfly stages): afterwards lane l of
+        // a group holds chunk l of the group's eight rows, so one store instruction writes four whole 128-byte
+        // row segments instead of 32 scattered 16-byte pieces (rows are H*D*2 bytes apart in memory).
+#pragma unroll
+        for (int m = 4; m >= 1; m >>= 1) {
+          const bool up = (lane & m) != 0;
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            if (i & m) continue;
+            const uint4 send = up ? ch[i] : ch[i | m];
+            uint4 recv;
+            recv.x = __shfl_xor_sync(0xffffffffu, send.x, m);
+            recv.y = __shfl_xor_sync(0xffffffffu, send.y, m);
+            recv.z = __shfl_xor_sync(0xffffffffu, send.z, m);
+            recv.w = __shfl_xor_sync(0xffffffffu, send.w, m);
+            if (up) ch[i] = recv; else ch[i | m] = recv;
+          }
+        }
+        {
+          const int l8 = lane & 7, row_g = q_row - l8;                   // first row of this lane's group
+          __nv_bfloat16* dst = p.out + g.b * p.o_sb + (int64_t)row_g * p.o_st + g.h * p.o_sh + half * 64 + l8 * 8;
+#pragma unroll
+          for (int jr = 0; jr < 8; ++jr)
+            if (row_g + jr < T) *reinterpret_cast<uint4*>(dst + (int64_t)jr * p.o_st) = ch[jr];
+        }
+        // the next item's first PV overwrites O_s only after every thread's P of that item has been signalled,
+        // i.e. after these loads: program order is the guard
+        tc_fence_before();
+      }
+      PT_LAP(6);
+    }
+    PT_FLUSH(0, threadIdx.x == 0);
+    PT_FLUSH(8, threadIdx.x == 128);
   } else {
     // ------------------------------------------------------------------ softmax + epilogue
     const int s = warp >> 2, quarter = warp & 3;
@@ -511,7 +672,7 @@ swa_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
   // ------------------------------------------------------------------ teardown
   tc_fence_before();
   __syncthreads();
-  if (warp == 9) {
+  if (warp == MMA_WARP) {
     tc_fence_after();
     tmem_dealloc(tmem_base, 512);
   }
@@ -616,10 +777,11 @@ extern "C" void daisy_b200_prefill_clk_dump(long long* out, void* stream) { pref
 static int ensure_smem_attr() {
   static bool done = false;
   if (done) return DAISY_OK;
-  if (cudaFuncSetAttribute(swa_prefill_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, PREFILL_SMEM) != cudaSuccess) return DAISY_ECUDA;
-  if (cudaFuncSetAttribute(swa_prefill_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, PREFILL_SMEM) != cudaSuccess) return DAISY_ECUDA;
-  if (cudaFuncSetAttribute(swa_prefill_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, PREFILL_SMEM) != cudaSuccess) return DAISY_ECUDA;
-  if (cudaFuncSetAttribute(swa_prefill_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, PREFILL_SMEM) != cudaSuccess) return DAISY_ECUDA;
+  if (cudaFuncSetAttribute(swa_prefill_kernel<false, false, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, PREFILL_SMEM) != cudaSuccess) return DAISY_ECUDA;
+  if (cudaFuncSetAttribute(swa_prefill_kernel<false, true, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, PREFILL_SMEM) != cudaSuccess) return DAISY_ECUDA;
+  if (cudaFuncSetAttribute(swa_prefill_kernel<false, true, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, PREFILL_SMEM) != cudaSuccess) return DAISY_ECUDA;
+  if (cudaFuncSetAttribute(swa_prefill_kernel<true, false, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, PREFILL_SMEM) != cudaSuccess) return DAISY_ECUDA;
+  if (cudaFuncSetAttribute(swa_prefill_kernel<true, true, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, PREFILL_SMEM) != cudaSuccess) return DAISY_ECUDA;
   if (cudaFuncSetAttribute(umma_selftest_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 1024 + 2 * TILE_BYTES + 64) != cudaSuccess) return DAISY_ECUDA;
   done = true;
   return DAISY_OK;
@@ -667,10 +829,13 @@ static int launch_attend(const void* q, const void* k, const void* v,
   // with RMS-normalised q and k every logit is bounded by scale * D: 2^(logit - reference) cannot overflow
   const bool bounded = bounded_qk && scale * 1.4426950408889634f * (float)D <= 60.f;
   cudaStream_t st = (cudaStream_t)stream;
-  if (raw && bounded)       swa_prefill_kernel<true, true><<<grid, PREFILL_THREADS, PREFILL_SMEM, st>>>(tq, tk, tv, p);
-  else if (raw)             swa_prefill_kernel<true, false><<<grid, PREFILL_THREADS, PREFILL_SMEM, st>>>(tq, tk, tv, p);
-  else if (bounded)         swa_prefill_kernel<false, true><<<grid, PREFILL_THREADS, PREFILL_SMEM, st>>>(tq, tk, tv, p);
-  else                      swa_prefill_kernel<false, false><<<grid, PREFILL_THREADS, PREFILL_SMEM, st>>>(tq, tk, tv, p);
+  static int split = -1;                   // DAISY_PREFILL_SPLIT=0 keeps one softmax warpgroup per stream
+  if (split < 0) { const char* e = getenv("DAISY_PREFILL_SPLIT"); split = e ? atoi(e) : 1; }
+  if (raw && bounded)       swa_prefill_kernel<true, true, 1><<<grid, PREFILL_THREADS, PREFILL_SMEM, st>>>(tq, tk, tv, p);
+  else if (raw)             swa_prefill_kernel<true, false, 1><<<grid, PREFILL_THREADS, PREFILL_SMEM, st>>>(tq, tk, tv, p);
+  else if (bounded && split) swa_prefill_kernel<false, true, 2><<<grid, PREFILL_THREADS_SPLIT, PREFILL_SMEM, st>>>(tq, tk, tv, p);
+  else if (bounded)         swa_prefill_kernel<false, true, 1><<<grid, PREFILL_THREADS, PREFILL_SMEM, st>>>(tq, tk, tv, p);
+  else                      swa_prefill_kernel<false, false, 1><<<grid, PREFILL_THREADS, PREFILL_SMEM, st>>>(tq, tk, tv, p);
   DAISY_CHECK_LAUNCH();
   return DAISY_OK;
 }
@@ -684,6 +849,49 @@ extern "C" int daisy_b200_swa_attend(const void* q, const void* k, const void* v
                                      int* status_word, void* stream) {
   return launch_attend(q, k, v, q_sb, q_st, q_sh, k_sb, k_st, k_sh, v_sb, v_st, v_sh, out, o_sb, o_st, o_sh,
                        B, T, H, D, window, scale, nullptr, false, status_word, stream);
+}
+
+// Side stream for the sliced prefill: one per device, made on first use outside any stream capture.
+constexpr int PREFILL_MAX_SLICES = 8;
+struct PrefillSide {
+  std::mutex mu;
+  cudaStream_t stream = nullptr;
+  cudaEvent_t fork = nullptr, ready[PREFILL_MAX_SLICES] = {};
+  bool ok = false;
+};
+
+static PrefillSide* prefill_side() {
+  static PrefillSide sides[16];
+  static std::mutex init_mu;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 16) { (void)cudaGetLastError(); return nullptr; }
+  PrefillSide* s = &sides[dev];
+  std::lock_guard<std::mutex> g(init_mu);
+  if (s->ok) return s;
+  if (cudaStreamCreateWithFlags(&s->stream, cudaStreamNonBlocking) != cudaSuccess) { (void)cudaGetLastError(); return nullptr; }
+  bool good = cudaEventCreateWithFlags(&s->fork, cudaEventDisableTiming) == cudaSuccess;
+  for (int i = 0; good && i < PREFILL_MAX_SLICES; ++i) good = cudaEventCreateWithFlags(&s->ready[i], cudaEventDisableTiming) == cudaSuccess;
+  if (!good) { (void)cudaGetLastError(); return nullptr; }
+  s->ok = true;
+  return s;
+}
+
+// Number of batch slices: each slice must still fill the machine several times over, or the persistent
+// attention kernel's tail costs more than the hidden streaming pass saves.
+static int prefill_slices(int B, int64_t items_per_batch) {
+  static int forced = -1;
+  if (forced < 0) {
+    const char* e = getenv("DAISY_PREFILL_SLICES");
+    forced = e ? atoi(e) : 0;
+  }
+  int n = forced > 0 ? forced : 4;
+  if (n > PREFILL_MAX_SLICES) n = PREFILL_MAX_SLICES;
+  if (n > B) n = B;
+  static int sms = 0;
+  if (sms <= 0) sms = daisy_b200_sm_count();
+  if (sms <= 0) return 1;
+  while (n > 1 && ((int64_t)((B + n - 1) / n) * items_per_batch) < 4 * (int64_t)sms) --n;
+  return n;
 }
 
 static size_t align1k(size_t x) { return (x + 1023) & ~size_t(1023); }
@@ -720,19 +928,68 @@ extern "C" int daisy_b200_swa_prefill_fwd(const void* q, const void* k, const vo
   const bool bounded_qk = (flags & DAISY_NORM_Q) && (flags & DAISY_NORM_K);
   void* qp = ws;
   const unsigned pf = (flags & DAISY_QKV_DEFAULT) | ((flags & DAISY_KV_BHTD) ? 0u : DAISY_OUT_BTHD);
-  int rc = daisy_b200_qkv_prep(q_in_kernel ? nullptr : q, k, v, q_sb, q_st, q_sh, k_sb, k_st, k_sh, v_sb, v_st, v_sh, cos, sin,
-                               q_in_kernel ? nullptr : qp, kp, vp, B, T, H, D, eps, pf, stream);
-  if (rc != DAISY_OK) return rc;
   const int64_t HD = (int64_t)H * D, TD = (int64_t)T * D;
   int64_t sb_ = (int64_t)T * HD, st_ = HD, sh_ = D;
   if (flags & DAISY_KV_BHTD) { st_ = D; sh_ = TD; }
-  if (q_in_kernel) {
-    QTransform qt{cos, sin, eps, (flags & DAISY_NORM_Q) ? 1 : 0, (flags & DAISY_ROPE) ? 1 : 0};
-    return launch_attend(q, kp, vp, q_sb, q_st, q_sh, sb_, st_, sh_, sb_, st_, sh_, out, o_sb, o_st, o_sh,
-                         B, T, H, D, window, scale, &qt, bounded_qk, status_word, stream);
+  QTransform qt{cos, sin, eps, (flags & DAISY_NORM_Q) ? 1 : 0, (flags & DAISY_ROPE) ? 1 : 0};
+
+  // One batch slice [b0, b0 + nb): the streaming pass, then the attention over what it wrote.
+  auto off = [](const void* base, int64_t elems) { return (const void*)((const char*)base + elems * 2); };
+  auto prep = [&](int b0, int nb, void* s) {
+    return daisy_b200_qkv_prep(q_in_kernel ? nullptr : off(q, b0 * q_sb), off(k, b0 * k_sb), off(v, b0 * v_sb),
+                               q_sb, q_st, q_sh, k_sb, k_st, k_sh, v_sb, v_st, v_sh, cos, sin,
+                               q_in_kernel ? nullptr : (void*)off(qp, b0 * sb_), (void*)off(kp, b0 * sb_), (void*)off(vp, b0 * sb_),
+                               nb, T, H, D, eps, pf, s);
+  };
+  auto attend = [&](int b0, int nb, void* s) {
+    if (q_in_kernel)
+      return launch_attend(off(q, b0 * q_sb), off(kp, b0 * sb_), off(vp, b0 * sb_), q_sb, q_st, q_sh, sb_, st_, sh_, sb_, st_, sh_,
+                           (void*)off(out, b0 * o_sb), o_sb, o_st, o_sh, nb, T, H, D, window, scale, &qt, bounded_qk, status_word, s);
+    return launch_attend(off(qp, b0 * sb_), off(kp, b0 * sb_), off(vp, b0 * sb_), sb_, st_, sh_, sb_, st_, sh_, sb_, st_, sh_,
+                         (void*)off(out, b0 * o_sb), o_sb, o_st, o_sh, nb, T, H, D, window, scale, nullptr, bounded_qk, status_word, s);
+  };
+
+  // The streaming pass is HBM-bound and the attention kernel is tensor-core bound, and the attention CTAs leave
+  // registers and thread slots free on every SM.  With enough work the batch is therefore cut into slices: the
+  // pass over slice i+1 runs on a side stream underneath the attention over slice i, and only the first slice's
+  // pass is exposed.  The side stream forks from and joins back into the caller's stream through events, so the
+  // caller sees one in-order operation (and a stream capture records the fork and the join).
+  const int64_t items_per_batch = (int64_t)((T + 2 * BM - 1) / (2 * BM)) * H;
+  int nslice = prefill_slices(B, items_per_batch);
+  PrefillSide* side = nslice > 1 ? prefill_side() : nullptr;
+  if (!side) nslice = 1;
+  if (nslice == 1) {
+    int rc = prep(0, B, stream);
+    if (rc != DAISY_OK) return rc;
+    return attend(0, B, stream);
   }
-  return launch_attend(qp, kp, vp, sb_, st_, sh_, sb_, st_, sh_, sb_, st_, sh_, out, o_sb, o_st, o_sh,
-                       B, T, H, D, window, scale, nullptr, bounded_qk, status_word, stream);
+  std::lock_guard<std::mutex> guard(side->mu);
+  cudaStream_t main_st = (cudaStream_t)stream;
+  const int per = (B + nslice - 1) / nslice;
+  int rc = DAISY_OK;
+  bool forked = false;
+  for (int i = 0, b0 = 0; b0 < B && rc == DAISY_OK; ++i, b0 += per) {
+    const int nb = B - b0 < per ? B - b0 : per;
+    if (i == 0) {
+      rc = prep(0, nb, stream);
+      if (rc != DAISY_OK) break;
+      if (cudaEventRecord(side->fork, main_st) != cudaSuccess || cudaStreamWaitEvent(side->stream, side->fork, 0) != cudaSuccess) { rc = DAISY_ECUDA; break; }
+      forked = true;
+    } else if (cudaStreamWaitEvent(main_st, side->ready[(i - 1) % PREFILL_MAX_SLICES], 0) != cudaSuccess) { rc = DAISY_ECUDA; break; }
+    const int nb_next = B - (b0 + per) < per ? B - (b0 + per) : per;
+    if (nb_next > 0) {
+      rc = prep(b0 + per, nb_next, side->stream);
+      if (rc != DAISY_OK) break;
+      if (cudaEventRecord(side->ready[i % PREFILL_MAX_SLICES], side->stream) != cudaSuccess) { rc = DAISY_ECUDA; break; }
+    }
+    rc = attend(b0, nb, stream);
+  }
+  if (rc != DAISY_OK && forked) {
+    // join whatever the side stream was given, so that the caller's stream still orders after it
+    if (cudaEventRecord(side->ready[0], side->stream) == cudaSuccess) (void)cudaStreamWaitEvent(main_st, side->ready[0], 0);
+    (void)cudaGetLastError();
+  }
+  return rc;
 }
 
 extern "C" int daisy_b200_selftest_umma(const void* a, const void* b, float* c, int K, int mode,
