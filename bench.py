@@ -175,14 +175,16 @@ def run_prefill(cfg, steps, warmup, dist, rank, world, peaks, name, lean=False):
     # dominant kernel alone (attention on prepared tensors), CUDA events around each launch
     qp, kp, vp = ops.qkv_prep(q, k, v, cos, sin, swa.FP32_EPS)
     ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
+    out_k = torch.empty_like(out)
     for _ in range(warmup):
-        ops.swa_attend(qp, kp, vp, W, out=out)
+        ops.swa_attend(qp, kp, vp, W, out=out_k, bounded_qk=True)      # the kernel the step launches
     torch.cuda.synchronize()
     for a, b in ev:
-        a.record(); ops.swa_attend(qp, kp, vp, W, out=out); b.record()
+        a.record(); ops.swa_attend(qp, kp, vp, W, out=out_k, bounded_qk=True); b.record()
     torch.cuda.synchronize()
     k_ms = sum(a.elapsed_time(b) for a, b in ev) / steps
-    del qp, kp, vp
+    kernel_same = bool(torch.equal(out_k, out))
+    del qp, kp, vp, out_k
 
     # end to end through the public host-buffer call: pinned host q,k,v in, pinned host result out, every step;
     # batch rows stream through copy-in / kernels / copy-out on three CUDA streams
@@ -215,7 +217,7 @@ def run_prefill(cfg, steps, warmup, dist, rank, world, peaks, name, lean=False):
                      "frac": ach / peaks["bf16_tflops"], "traffic": (NCU_TRAFFIC["prefill_per_batch_row"] * B if (T, W) == (8192, 2048) else None),
                      "traffic_unit": "bytes per launch (ncu dram read+write on B=2, scaled by batch)",
                      "kernel": "swa_prefill_kernel",
-                     "kernel_ms": k_ms, "peak_source": peaks["which"] + " (burst cuBLAS bf16)"},
+                     "kernel_ms": k_ms, "kernel_output_equals_step": kernel_same, "peak_source": peaks["which"] + " (burst cuBLAS bf16)"},
         "e2e": {"value": world * flops / (e2e_ms / e2e_steps * 1e-3) / 1e12, "unit": "TFLOP/s",
                 "h2d_bytes_per_step": in_bytes, "d2h_bytes_per_step": out_bytes,
                 "matches_device_result": e2e_same, "api": "daisy_b200.host_api.HostPrefill"},

@@ -12,7 +12,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "libdaisy_b200.so")
 
 OK, EINVAL, EUNSUPPORTED, EALIGN, EWORKSPACE, ECUDA, ETIMEOUT, ENODEV = 0, -1, -2, -3, -4, -5, -6, -7
-NORM_Q, NORM_K, NORM_V, ROPE, QKV_DEFAULT, WRITE_RING, OUT_BTHD, KV_BHTD, Q_IN_KERNEL = 1, 2, 4, 8, 15, 16, 32, 64, 128
+NORM_Q, NORM_K, NORM_V, ROPE, QKV_DEFAULT, WRITE_RING, OUT_BTHD, KV_BHTD, Q_IN_KERNEL, BOUNDED_QK = 1, 2, 4, 8, 15, 16, 32, 64, 128, 256
 KDA_L2NORM_QK, KDA_OUT_FP32 = 1, 2
 
 _vp, _i, _i64, _f, _u, _sz = C.c_void_p, C.c_int, C.c_int64, C.c_float, C.c_uint, C.c_size_t
@@ -26,7 +26,7 @@ SIGNATURES = {
     "daisy_b200_swa_prefill_workspace_bytes": (_sz, [_i] * 4),
     "daisy_b200_swa_prefill_fwd": (_i, [_vp] * 3 + [_i64] * 9 + [_vp] * 2 + [_vp] + [_i64] * 3 + [_vp] * 2 +
                                    [_i] * 5 + [_f, _f, _u, _vp, _sz, _vp, _vp]),
-    "daisy_b200_swa_attend": (_i, [_vp] * 3 + [_i64] * 9 + [_vp] + [_i64] * 3 + [_i] * 5 + [_f, _vp, _vp]),
+    "daisy_b200_swa_attend": (_i, [_vp] * 3 + [_i64] * 9 + [_vp] + [_i64] * 3 + [_i] * 5 + [_f, _u, _vp, _vp]),
     "daisy_b200_swa_decode_splits": (_i, [_i] * 4),
     "daisy_b200_swa_decode_workspace_bytes": (_sz, [_i] * 4),
     "daisy_b200_swa_decode_step": (_i, [_vp] * 3 + [_i64] * 6 + [_vp] * 2 + [_i64] * 3 + [_i64, _i, _i] +

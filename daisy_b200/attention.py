@@ -121,7 +121,7 @@ class B200CausalSelfAttention(nn.Module):
             qp, kp, vp = ops.qkv_prep(q, k, v, cos, sin, self.norm_eps)
             g = torch.sigmoid(self.g_ve).to(vp.dtype)
             vp = g * vp + (1.0 - g) * ve.view(B, T, self.num_heads, self.head_dim).to(vp.dtype)
-            y = ops.swa_attend(qp, kp, vp, window, self.attn_scale)
+            y = ops.swa_attend(qp, kp, vp, window, self.attn_scale, bounded_qk=True)   # q, k are RMS-normalised
             qp, kp, vp = qp.transpose(1, 2), kp.transpose(1, 2), vp.transpose(1, 2)
         else:
             y, kp, vp = ops.swa_prefill(q, k, v, cos, sin, window, self.attn_scale, self.norm_eps)

@@ -77,9 +77,10 @@ def qkv_prep(q, k, v, cos, sin, eps: float, flags: int = QKV_DEFAULT, bhtd: bool
 
 
 def swa_attend(q, k, v, window: Optional[int], scale: float = ATTN_SCALE,
-               out: Optional[torch.Tensor] = None) -> torch.Tensor:
+               out: Optional[torch.Tensor] = None, bounded_qk: bool = False) -> torch.Tensor:
     """Windowed causal attention on prepared tensors of logical shape ``[B,T,H,D]`` (any batch / token /
-    head strides, D contiguous); returns ``[B,T,H,D]``."""
+    head strides, D contiguous); returns ``[B,T,H,D]``.  ``bounded_qk=True`` promises RMS-normalised q and k
+    (every logit bounded), which selects the kernel without a running maximum."""
     for n, t in (("q", q), ("k", k), ("v", v)):
         _req(t, n)
     B, T, H, D = q.shape
@@ -91,7 +92,7 @@ def swa_attend(q, k, v, window: Optional[int], scale: float = ATTN_SCALE,
         q.stride(0), q.stride(1), q.stride(2), k.stride(0), k.stride(1), k.stride(2),
         v.stride(0), v.stride(1), v.stride(2), out.data_ptr(),
         out.stride(0), out.stride(1), out.stride(2), B, T, H, D, int(window or 0), scale,
-        status_word(q.device).data_ptr(), _stream(q))
+        _lib.BOUNDED_QK if bounded_qk else 0, status_word(q.device).data_ptr(), _stream(q))
     _lib.check(rc, "daisy_b200_swa_attend")
     return out
 

@@ -47,6 +47,9 @@ extern "C" {
 #define DAISY_OUT_BTHD   32u    /* qkv_prep: outputs keep the [B,T,H,D] memory order (default [B,H,T,D]) */
 #define DAISY_KV_BHTD    64u    /* swa_prefill_fwd: k_out/v_out memory order [B,H,T,D] (default [B,T,H,D]) */
 #define DAISY_Q_IN_KERNEL 128u  /* swa_prefill_fwd: normalise / rotate Q inside the attention kernel (on load) */
+#define DAISY_BOUNDED_QK  256u  /* swa_attend: the caller guarantees |q_i . k_j| * scale * log2(e) <= 60 for every pair
+                                   (true for RMS-normalised q and k with scale * D <= 41); selects the kernel that
+                                   needs no running maximum.  swa_prefill_fwd sets it itself when it normalises q and k. */
 /* KDA flags */
 #define DAISY_KDA_L2NORM_QK 1u  /* L2-normalise q and k over K inside the kernel (eps 1e-6)         */
 #define DAISY_KDA_OUT_FP32  2u  /* `o` is float32 instead of bf16                                   */
@@ -102,14 +105,14 @@ int daisy_b200_swa_prefill_fwd(const void* q, const void* k, const void* v,
 
 /* The attention core alone on already-prepared q,k,v, logical [B,T,H,D] with strides
  * (s_b,s_t,s_h), D contiguous -- any memory order (what F.scaled_dot_product_attention(q_,k_,v_,
- * attn_mask=M,scale=...) computes at models/daisy/attention.py:145). */
+ * attn_mask=M,scale=...) computes at models/daisy/attention.py:145).  flags: 0 or DAISY_BOUNDED_QK. */
 int daisy_b200_swa_attend(const void* q, const void* k, const void* v,
                           int64_t q_sb, int64_t q_st, int64_t q_sh,
                           int64_t k_sb, int64_t k_st, int64_t k_sh,
                           int64_t v_sb, int64_t v_st, int64_t v_sh,
                           void* out, int64_t o_sb, int64_t o_st, int64_t o_sh,
                           int B, int T, int H, int D, int window, float scale,
-                          int* status_word, void* stream);
+                          unsigned flags, int* status_word, void* stream);
 
 /* ---------------------------------------------------------------------------------------------
  * Sliding-window decode step over a ring-buffer KV cache, split-KV.

@@ -90,6 +90,24 @@ def test_attend_large_logits_rescale_path():
     assert_close_bf16(y, y_ref, "rescale", max_tol=4e-2, mean_tol=4e-3)
 
 
+@pytest.mark.parametrize("T,window", [(7, None), (300, 64), (513, 129), (1300, 512), (2100, 1024)])
+def test_attend_bounded_qk_kernel_matches(T, window):
+    """DAISY_BOUNDED_QK on prepared (RMS-normalised, rotated) q and k: the kernel with two softmax warpgroups per
+    stream and no running maximum gives the oracle's result, and agrees with the general kernel."""
+    from daisy_b200 import ops
+    B, H = 2, 3
+    qkv = bf16_randn(B, T, 3 * H, D, seed=91)
+    q, k, v = qkv.chunk(3, dim=-2)
+    cos, sin = swa.rope_tables(D, T)
+    qp, kp, vp = ops.qkv_prep(q, k, v, cos.cuda(), sin.cuda(), swa.FP32_EPS)
+    y_ref = swa.attend_windowed(qp.float().cpu(), kp.float().cpu(), vp.float().cpu(), window)
+    y_b = ops.swa_attend(qp, kp, vp, window, bounded_qk=True)
+    y_g = ops.swa_attend(qp, kp, vp, window)
+    ops.check_device_status(q.device)
+    assert_close_bf16(y_b, y_ref, "bounded")
+    assert_close_bf16(y_b, y_g.float().cpu(), "bounded vs general", max_tol=1e-2, mean_tol=1e-3)
+
+
 @pytest.mark.parametrize("T,window", [(5, 3), (300, 64), (513, 129), (1300, 512)])
 def test_q_prepared_in_kernel_matches(T, window):
     """DAISY_Q_IN_KERNEL: Q is normalised and rotated inside the attention kernel (in the swizzled tile, one
