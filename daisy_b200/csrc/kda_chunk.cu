@@ -87,9 +87,10 @@ struct KdaIntraSmem {
   __nv_bfloat16 kraw[KC][LDR];     // later (with qraw) the U0^T staging image
   __nv_bfloat16 qraw[KC][LDR];
   __nv_bfloat16 vraw[KC][KD];
-  float Akk[KC][LDA];
-  float Tm[KC][LDA];
-  float Wt[16][3 * 16 + 1];        // scratch of the block forward substitution
+  float Akk[KC][LDA];              // beta * gated k k^T: the 16 x 16 diagonal blocks (fp32, for the exact block inverses)
+  __half Akh[KC][LDT];             //                     the off-diagonal blocks as tensor-core operands
+  __half Th[KC][LDT];              // T = (I + A_kk)^-1, row-major
+  __half ThT[KC][LDT];             // T^T
   __half Aqk[KC][LDT];
   __half Mk[KC][LDW];              // one level's Gram operands: k * e^{-|G - r|}
   __half Mq[KC][LDW];              //                             q * e^{-|G - r|} on upper rows, else 0
@@ -132,7 +133,6 @@ __global__ void __launch_bounds__(KDA_INTRA_THREADS, 1) kda_intra_kernel(const K
     }
     if (tid < KC) sm.beta[tid] = tid < rows ? p.beta[tok0 + (size_t)tid * p.H] : 0.f;
     for (int idx = tid; idx < KC * LDT / 2; idx += KDA_INTRA_THREADS) reinterpret_cast<uint32_t*>(&sm.Aqk[0][0])[idx] = 0u;
-    for (int idx = tid; idx < KC * LDA; idx += KDA_INTRA_THREADS) { (&sm.Akk[0][0])[idx] = 0.f; (&sm.Tm[0][0])[idx] = 0.f; }
 #pragma unroll
     for (int u = 0; u < 2; ++u) {
       const int idx = tid + u * KDA_INTRA_THREADS, r = idx >> 4, c8 = (idx & 15) * 8;
@@ -327,7 +327,10 @@ __global__ void __launch_bounds__(KDA_INTRA_THREADS, 1) kda_intra_kernel(const K
             ok = ((r >> (ls + 1)) == (n >> ls)) && ((r & s) != 0);
           }
           if (ok) {
-            if (which != 1) sm.Akk[i][j] = sm.beta[i] * acc_k[x];
+            if (which != 1) {
+              const float a = sm.beta[i] * acc_k[x];
+              if (s >= 16) sm.Akh[i][j] = __float2half_rn(a); else sm.Akk[i][j] = a;
+            }
             if (which != 0) sm.Aqk[i][j] = __float2half_rn(p.scale * acc_q[x]);
           }
         }
@@ -340,7 +343,7 @@ __global__ void __launch_bounds__(KDA_INTRA_THREADS, 1) kda_intra_kernel(const K
   }
 
   KDA_MARK(5);
-  // ---- P4: T = (I + A_kk)^-1, fp32.  (a) the four 16x16 diagonal blocks by forward substitution
+  // ---- P4: T = (I + A_kk)^-1.  (a) the four 16x16 diagonal blocks by forward substitution in fp32
   if (warp < 4 && lane < 16) {
     const int base = warp * 16;
     float t[16];
@@ -352,46 +355,54 @@ __global__ void __launch_bounds__(KDA_INTRA_THREADS, 1) kda_intra_kernel(const K
       t[i] = s;
     }
 #pragma unroll
-    for (int i = 0; i < 16; ++i) sm.Tm[base + i][base + lane] = t[i];
+    for (int i = 0; i < 16; ++i) {                                 // t[i] = T[base + i][base + lane]
+      const __half th = __float2half_rn(t[i]);
+      sm.Th[base + i][base + lane] = th;
+      sm.ThT[base + lane][base + i] = th;
+    }
   }
   __syncthreads();
   KDA_MARK(6);
-  //      (b) block rows 1..3:  T_{I,<I} = -T_II * (A_{I,<I} T_{<I,<I}); thread = (row r, column lane cc),
-  //          up to three 16-column blocks each.  T is zero above its diagonal, so the inner sums run over
-  //          fixed ranges and unroll.
-  {
-    const bool act = tid < 256;                                    // 16 rows x 16 columns; the barriers stay uniform
-    const int r = (tid >> 4) & 15, cc = tid & 15;
-    for (int I = 1; I < 4; ++I) {
-      float w[3] = {0.f, 0.f, 0.f};
-      const float* arow = &sm.Akk[I * 16 + r][0];
-      for (int mb = 0; act && mb < I; ++mb) {
+  //      (b) block rows I = 1..3 on tensor cores, in transposed form so that the two products chain through
+  //          registers:  R = T^T,  R_{<I,I} = -(R_{<I,<I} A_{I,<I}^T) R_II.  Warp mt < I owns 16 rows of R_{<I,I};
+  //          the first product's accumulator pair is the second product's A fragment.  fp16 operands here cost
+  //          nothing measurable: T is consumed as fp16 by every later product anyway.
+#pragma unroll 1
+  for (int I = 1; I < 4; ++I) {
+    if (warp < I) {
+      const int mt = warp;
+      float acc1[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+      for (int kb = mt; kb < I; ++kb) {                            // R is block upper triangular
+        uint32_t a[4];
+        const int kc = kb * 16 + 2 * t4;
+        a[0] = *reinterpret_cast<const uint32_t*>(&sm.ThT[mt * 16 + g8][kc]);
+        a[1] = *reinterpret_cast<const uint32_t*>(&sm.ThT[mt * 16 + g8 + 8][kc]);
+        a[2] = *reinterpret_cast<const uint32_t*>(&sm.ThT[mt * 16 + g8][kc + 8]);
+        a[3] = *reinterpret_cast<const uint32_t*>(&sm.ThT[mt * 16 + g8 + 8][kc + 8]);
 #pragma unroll
-        for (int mm = 0; mm < 16; ++mm) {
-          const int m = mb * 16 + mm;
-          const float a = arow[m];
-#pragma unroll
-          for (int cb = 0; cb < 3; ++cb)
-            if (cb <= mb) w[cb] = fmaf(a, sm.Tm[m][cb * 16 + cc], w[cb]);
+        for (int nn = 0; nn < 2; ++nn) {
+          const __half* arow = &sm.Akh[I * 16 + nn * 8 + g8][kc];
+          mma_f16(acc1[nn], a, *reinterpret_cast<const uint32_t*>(arow), *reinterpret_cast<const uint32_t*>(arow + 8));
         }
       }
-      __syncthreads();
+      uint32_t a2[4];
+      a2[0] = pack_h2(acc1[0][0], acc1[0][1]); a2[1] = pack_h2(acc1[0][2], acc1[0][3]);
+      a2[2] = pack_h2(acc1[1][0], acc1[1][1]); a2[3] = pack_h2(acc1[1][2], acc1[1][3]);
 #pragma unroll
-      for (int cb = 0; cb < 3; ++cb) if (act) sm.Wt[r][cb * 16 + cc] = w[cb];
-      __syncthreads();
-      float s[3] = {0.f, 0.f, 0.f};
-      const float* trow = &sm.Tm[I * 16 + r][I * 16];
-#pragma unroll
-      for (int m = 0; act && m < 16; ++m) {
-        const float tv = trow[m];                                  // zero for m > r
-#pragma unroll
-        for (int cb = 0; cb < 3; ++cb) s[cb] = fmaf(tv, sm.Wt[m][cb * 16 + cc], s[cb]);
+      for (int nn = 0; nn < 2; ++nn) {
+        float acc2[4] = {0.f, 0.f, 0.f, 0.f};
+        const __half* trow = &sm.Th[I * 16 + nn * 8 + g8][I * 16 + 2 * t4];
+        mma_f16(acc2, a2, *reinterpret_cast<const uint32_t*>(trow), *reinterpret_cast<const uint32_t*>(trow + 8));
+        // acc2[0..1] = R[mt*16 + g8][nn*8 + 2 t4 (+1)], acc2[2..3] the same for row g8 + 8;  T[i][j] = -R[j][i]
+        const int ti = I * 16 + nn * 8 + 2 * t4, tj = mt * 16 + g8;
+        const __half h0 = __float2half_rn(-acc2[0]), h1 = __float2half_rn(-acc2[1]);
+        const __half h2 = __float2half_rn(-acc2[2]), h3 = __float2half_rn(-acc2[3]);
+        sm.Th[ti][tj] = h0; sm.Th[ti + 1][tj] = h1; sm.Th[ti][tj + 8] = h2; sm.Th[ti + 1][tj + 8] = h3;
+        *reinterpret_cast<__half2*>(&sm.ThT[tj][ti]) = __halves2half2(h0, h1);
+        *reinterpret_cast<__half2*>(&sm.ThT[tj + 8][ti]) = __halves2half2(h2, h3);
       }
-#pragma unroll
-      for (int cb = 0; cb < 3; ++cb)
-        if (act && cb < I) sm.Tm[I * 16 + r][cb * 16 + cc] = -s[cb];
-      __syncthreads();
     }
+    __syncthreads();
   }
 
   KDA_MARK(7);
@@ -408,10 +419,10 @@ __global__ void __launch_bounds__(KDA_INTRA_THREADS, 1) kda_intra_kernel(const K
     for (int ks = 0; ks <= I; ++ks) {
       uint32_t a[4];
       const int j = ks * 16 + 2 * t4;
-      a[0] = pack_h2(sm.Tm[i0][j], sm.Tm[i0][j + 1]);
-      a[1] = pack_h2(sm.Tm[i1][j], sm.Tm[i1][j + 1]);
-      a[2] = pack_h2(sm.Tm[i0][j + 8], sm.Tm[i0][j + 9]);
-      a[3] = pack_h2(sm.Tm[i1][j + 8], sm.Tm[i1][j + 9]);
+      a[0] = *reinterpret_cast<const uint32_t*>(&sm.Th[i0][j]);
+      a[1] = *reinterpret_cast<const uint32_t*>(&sm.Th[i1][j]);
+      a[2] = *reinterpret_cast<const uint32_t*>(&sm.Th[i0][j + 8]);
+      a[3] = *reinterpret_cast<const uint32_t*>(&sm.Th[i1][j + 8]);
 #pragma unroll
       for (int nt = 0; nt < 4; ++nt) {
         const int c = ch + nt * 8 + g8;
@@ -442,7 +453,7 @@ __global__ void __launch_bounds__(KDA_INTRA_THREADS, 1) kda_intra_kernel(const K
       for (int nt = 0; nt < 4; ++nt) {
         if (ks * 16 > (nt0 + nt) * 8 + 7) continue;                // T[i][j] = 0 for j > i
         const int i = (nt0 + nt) * 8 + g8;
-        mma_f16(acc[nt], a, pack_h2(sm.Tm[i][j], sm.Tm[i][j + 1]), pack_h2(sm.Tm[i][j + 8], sm.Tm[i][j + 9]));
+        mma_f16(acc[nt], a, *reinterpret_cast<const uint32_t*>(&sm.Th[i][j]), *reinterpret_cast<const uint32_t*>(&sm.Th[i][j + 8]));
       }
     }
 #pragma unroll

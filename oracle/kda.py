@@ -56,6 +56,27 @@ def kda_recurrent(q, k, v, g, beta, scale: Optional[float] = None,
     return o, S
 
 
+def kda_gate(g: torch.Tensor, A_log: torch.Tensor, head_k_dim: int, g_bias: Optional[torch.Tensor] = None,
+             beta: float = 1.0, threshold: float = 20.0) -> torch.Tensor:
+    """Log-decay gate of the KDA layer, ``[..., H*D] -> [..., H, D]`` in ``g.dtype``:
+
+        y = -exp(A_log[h]) * softplus(g + g_bias, beta, threshold)        (fp32 math, then cast)
+
+    Restates ``_gate_impl`` (models/daisy/fla_custom_ops.py:71-103) as called from
+    ``KimiLinearSelfAttention._kda_eager`` (models/daisy/attention_kimi.py:132:
+    ``fused_kda_gate(g, A_log, head_k_dim, dt_bias, None, 1.0, 20.0)``).  softplus(x) = log1p(exp(beta x)) / beta
+    and exactly x where beta x > threshold (torch.nn.functional.softplus).  ``A_log`` is ``[H]``, ``g_bias``
+    ``[H*D]`` or None."""
+    H = g.shape[-1] // head_k_dim
+    x = g.float().reshape(*g.shape[:-1], H, head_k_dim)
+    if g_bias is not None:
+        x = x + g_bias.float().reshape(H, head_k_dim)
+    bx = x * beta
+    sp = torch.where(bx > threshold, x, torch.log1p(torch.exp(torch.clamp(bx, max=threshold))) / beta)
+    y = -torch.exp(A_log.float().reshape(H, 1)) * sp
+    return y.to(g.dtype)
+
+
 def kda_bytes_per_token_head(K: int = 128, V: int = 128) -> int:
     """Algorithmic HBM bytes per (token, head): q,k bf16, v bf16, g fp32, beta fp32, o bf16."""
     return 2 * K * 2 + V * 2 + K * 4 + 4 + V * 2

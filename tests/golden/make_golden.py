@@ -142,11 +142,32 @@ def kda_case():
                         o=o.numpy(), s=s.numpy(), o_h0=o2.numpy(), s_h0=s2.numpy(), fla_version=fla.__version__)
 
 
+def kda_gate_case():
+    """``fused_kda_gate`` as the KDA layer calls it (attention_kimi.py:132), through the reference's own
+    pure-PyTorch implementation ``_gate_impl`` (fla_custom_ops.py:71-103): fp32 and bf16 inputs, with the
+    softplus threshold (20) exercised on both sides."""
+    from models.daisy.fla_custom_ops import _gate_impl
+    g = torch.Generator().manual_seed(11)
+    H, Dk = 3, 128
+    x = torch.randn(2, 37, H * Dk, generator=g) * 6.0
+    x[0, 0, :8] = torch.tensor([19.5, 20.0, 20.5, 25.0, -30.0, 0.0, 35.0, -0.5])
+    A_log = torch.log(torch.empty(H).uniform_(1.0, 16.0, generator=g))
+    bias = torch.randn(H * Dk, generator=g)
+    y32, _ = _gate_impl(x, A_log, Dk, bias, None, 1.0, 20.0)
+    ybf, _ = _gate_impl(x.bfloat16(), A_log, Dk, bias, None, 1.0, 20.0)
+    ynb, _ = _gate_impl(x, A_log, Dk, None, None, 1.0, 20.0)
+    np.savez_compressed(os.path.join(HERE, "kda_gate_small.npz"),
+                        x=x.numpy(), A_log=A_log.numpy(), bias=bias.numpy(), y_fp32=y32.numpy(),
+                        y_bf16_as_fp32=ybf.float().numpy(), y_nobias=ynb.numpy())
+    print("kda_gate_small", tuple(y32.shape))
+
+
 if __name__ == "__main__":
     csa_prefill_case()
     csa_step_case()
     swa_inner_case()
     kda_case()
+    kda_gate_case()
     for f in sorted(os.listdir(HERE)):
         if f.endswith(".npz"):
             print(f, os.path.getsize(os.path.join(HERE, f)))
