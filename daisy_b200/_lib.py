@@ -14,6 +14,7 @@ LIB_PATH = os.path.join(_HERE, "libdaisy_b200.so")
 OK, EINVAL, EUNSUPPORTED, EALIGN, EWORKSPACE, ECUDA, ETIMEOUT, ENODEV = 0, -1, -2, -3, -4, -5, -6, -7
 NORM_Q, NORM_K, NORM_V, ROPE, QKV_DEFAULT, WRITE_RING, OUT_BTHD, KV_BHTD, Q_IN_KERNEL, BOUNDED_QK = 1, 2, 4, 8, 15, 16, 32, 64, 128, 256
 KDA_L2NORM_QK, KDA_OUT_FP32 = 1, 2
+KDA_GATE_ROUND_BF16 = 1
 
 _vp, _i, _i64, _f, _u, _sz = C.c_void_p, C.c_int, C.c_int64, C.c_float, C.c_uint, C.c_size_t
 
@@ -39,6 +40,8 @@ SIGNATURES = {
     "daisy_b200_ring_copy_rows": (_i, [_vp] + [_i64] * 3 + [_vp] + [_i64] * 3 + [_i] * 4 + [_i64] + [_i] * 3 + [_vp]),
     "daisy_b200_kda_workspace_bytes": (_sz, [_i] * 5),
     "daisy_b200_kda_chunk_fwd": (_i, [_vp] * 8 + [_i] * 6 + [_f, _u, _vp, _sz, _vp, _vp]),
+    "daisy_b200_kda_recurrent_fwd": (_i, [_vp] * 8 + [_i] * 5 + [_f, _u, _vp]),
+    "daisy_b200_kda_gate": (_i, [_vp, _i, _vp, _vp, _vp, _i64, _i, _i, _f, _f, _u, _vp]),
     "daisy_b200_selftest_umma": (_i, [_vp] * 3 + [_i, _i, _vp, _vp]),
 }
 

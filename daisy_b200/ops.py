@@ -229,6 +229,74 @@ def kda_chunk_fwd(q, k, v, g, beta, scale: Optional[float] = None, initial_state
     return o, hT
 
 
+def kda_recurrent_fwd(q, k, v, g, beta, scale: Optional[float] = None, initial_state=None,
+                      output_final_state: bool = False, l2norm_qk: bool = True, out_fp32: bool = False,
+                      state_in_place: bool = False):
+    """KDA token-by-token recurrence (short inputs, decode steps); same arguments and layouts as
+    :func:`kda_chunk_fwd`.  ``state_in_place=True`` updates ``initial_state`` itself and returns it."""
+    for n, t in (("q", q), ("k", k), ("v", v)):
+        _req(t, n)
+        if not t.is_contiguous():
+            raise ValueError(f"{n} must be contiguous")
+    g, beta = _f32c(g, "g"), _f32c(beta, "beta")
+    B, T, H, K = q.shape
+    V = v.shape[-1]
+    o = torch.empty(B, T, H, V, dtype=torch.float32 if out_fp32 else torch.bfloat16, device=q.device)
+    if initial_state is not None:
+        if state_in_place and not (initial_state.dtype == torch.float32 and initial_state.is_contiguous()):
+            raise ValueError("an in-place state must be a contiguous float32 tensor")
+        initial_state = _f32c(initial_state, "initial_state")
+    if state_in_place:
+        if initial_state is None:
+            raise ValueError("state_in_place needs an initial_state")
+        hT = initial_state
+    else:
+        hT = torch.empty(B, H, K, V, dtype=torch.float32, device=q.device) if output_final_state else None
+    flags = (KDA_L2NORM_QK if l2norm_qk else 0) | (KDA_OUT_FP32 if out_fp32 else 0)
+    rc = _lib.lib().daisy_b200_kda_recurrent_fwd(
+        q.data_ptr(), k.data_ptr(), v.data_ptr(), g.data_ptr(), beta.data_ptr(),
+        initial_state.data_ptr() if initial_state is not None else None, o.data_ptr(),
+        hT.data_ptr() if hT is not None else None, B, T, H, K, V,
+        float(scale) if scale is not None else 0.0, flags, _stream(q))
+    _lib.check(rc, "daisy_b200_kda_recurrent_fwd")
+    return o, hT
+
+
+def kda_gate(g: torch.Tensor, a_log: torch.Tensor, head_k_dim: int, g_bias: Optional[torch.Tensor] = None,
+             beta: float = 1.0, threshold: float = 20.0, round_bf16: Optional[bool] = None) -> torch.Tensor:
+    """``-exp(A_log[h]) * softplus(g + bias)`` for ``g [..., H*D]`` (bf16 or fp32) -> fp32 ``[..., H, D]``.
+    ``round_bf16`` (default: when ``g`` is bf16) rounds the values to bf16 before storing them as fp32, the
+    reference's cast of the gate back to the activation dtype."""
+    if not g.is_cuda:
+        raise ValueError("g must be a CUDA tensor")
+    if g.dtype not in (torch.bfloat16, torch.float32):
+        g = g.float()
+    g = g.contiguous()
+    HD = g.shape[-1]
+    H = HD // int(head_k_dim)
+    if H * int(head_k_dim) != HD:
+        raise ValueError("last dim must be divisible by head_k_dim")
+    a = a_log.to(device=g.device, dtype=torch.float32).reshape(-1).contiguous()
+    if a.numel() != H:
+        raise ValueError(f"A_log must hold {H} values")
+    bias = None
+    if g_bias is not None:
+        bias = g_bias.to(device=g.device, dtype=torch.float32)
+        bias = (bias.reshape(H, 1).expand(H, head_k_dim) if bias.numel() == H else bias).reshape(-1).contiguous()
+        if bias.numel() != HD:
+            raise ValueError("g_bias must hold H or H*D values")
+    if round_bf16 is None:
+        round_bf16 = g.dtype == torch.bfloat16
+    out = torch.empty(*g.shape[:-1], H, int(head_k_dim), dtype=torch.float32, device=g.device)
+    rows = g.numel() // HD
+    rc = _lib.lib().daisy_b200_kda_gate(g.data_ptr(), 1 if g.dtype == torch.bfloat16 else 0, a.data_ptr(),
+                                        bias.data_ptr() if bias is not None else None, out.data_ptr(), rows, H,
+                                        int(head_k_dim), float(beta), float(threshold),
+                                        _lib.KDA_GATE_ROUND_BF16 if round_bf16 else 0, _stream(g))
+    _lib.check(rc, "daisy_b200_kda_gate")
+    return out
+
+
 def selftest_umma(a: torch.Tensor, b: torch.Tensor, mode: int) -> torch.Tensor:
     """C[128,128] fp32 = A[128,K] x B (B is [128,K] for mode 0, [K,128] for modes 1 and 2)."""
     _req(a, "a"); _req(b, "b")

@@ -53,6 +53,8 @@ extern "C" {
 /* KDA flags */
 #define DAISY_KDA_L2NORM_QK 1u  /* L2-normalise q and k over K inside the kernel (eps 1e-6)         */
 #define DAISY_KDA_OUT_FP32  2u  /* `o` is float32 instead of bf16                                   */
+#define DAISY_KDA_GATE_ROUND_BF16 1u  /* kda_gate: round the result to bf16 first (what the reference's cast of the
+                                         gate to a bf16 activation dtype does), then store it as float32     */
 
 int         daisy_b200_version(void);
 const char* daisy_b200_strerror(int code);
@@ -194,6 +196,24 @@ int daisy_b200_kda_chunk_fwd(const void* q, const void* k, const void* v, const 
                              int B, int T, int H, int K, int V, int chunk, float scale,
                              unsigned flags, void* workspace, size_t workspace_bytes,
                              int* status_word, void* stream);
+
+/* The same recurrence token by token, for short inputs (decode steps; the reference calls chunk_kda with
+ * T = 1 and the cached state, models/daisy/attention_kimi.py:144-149,175-180).  The state of one (batch, head)
+ * stays in registers across the T tokens: read from h0 once (null = zero state), written to hT once (null =
+ * discarded; hT may alias h0 for an in-place cache update).  No workspace.  Same layouts and flags as
+ * daisy_b200_kda_chunk_fwd. */
+int daisy_b200_kda_recurrent_fwd(const void* q, const void* k, const void* v, const float* g,
+                                 const float* beta, const float* h0, void* o, float* hT,
+                                 int B, int T, int H, int K, int V, float scale, unsigned flags,
+                                 void* stream);
+
+/* Log-decay gate of the KDA layer.  Replaces fused_kda_gate(g, A_log, head_k_dim, dt_bias, None, beta,
+ * threshold) at models/daisy/attention_kimi.py:132 (forward of _gate_impl, models/daisy/fla_custom_ops.py:71-103):
+ *   out[r, h, d] = -exp(a_log[h]) * softplus(g[r, h*D + d] + bias[h*D + d]; beta, threshold)      (fp32 math)
+ * g [rows, H*D] bf16 (g_is_bf16 != 0) or float32; a_log [H] float32; bias [H*D] float32 or null; out [rows, H*D]
+ * float32, the layout daisy_b200_kda_chunk_fwd takes.  D a multiple of 4.  flags: 0 or DAISY_KDA_GATE_ROUND_BF16. */
+int daisy_b200_kda_gate(const void* g, int g_is_bf16, const float* a_log, const float* bias, float* out,
+                        int64_t rows, int H, int D, float beta, float threshold, unsigned flags, void* stream);
 
 /* ---------------------------------------------------------------------------------------------
  * Self-test of the tensor-core building blocks (no reference counterpart): C[128,128] float32 =

@@ -93,3 +93,71 @@ def test_kda_chunked_state_carry():
                     output_final_state=True, out_fp32=True)
     assert _rel(torch.cat([o_a, o_b], 1), o_full.cpu()) <= 1e-5
     assert _rel(s_b, s_full.cpu()) <= 1e-5
+
+
+def test_kda_decode_steps_carry_state():
+    """Prefill through the chunked kernels, then single-token calls (the token-by-token kernel) that carry
+    the state: the reference's decode pattern (chunk_kda with T = 1 and the cached state)."""
+    from daisy_b200 import ops
+    from daisy_b200.kda import chunk_kda, RECURRENT_MAX_T
+    B, T0, n_steps, H = 2, 130, 6, 3
+    q, k, v, g, beta = _inputs(B, T0 + n_steps + 3, H, seed=21)
+    o_ref, s_ref = okda.kda_recurrent(q.float(), k.float(), v.float(), g, beta)
+    dev = [x.cuda() for x in (q, k, v, g, beta)]
+    cut = lambda a, b: [x[:, a:b].contiguous() for x in dev]
+    o0, state = chunk_kda(*cut(0, T0), output_final_state=True, use_qk_l2norm_in_kernel=True, out_fp32=True)
+    outs = [o0]
+    for t in range(T0, T0 + n_steps):
+        o1, state = chunk_kda(*cut(t, t + 1), initial_state=state, output_final_state=True,
+                              use_qk_l2norm_in_kernel=True, out_fp32=True)
+        outs.append(o1)
+    # a short multi-token block, state updated in place
+    assert 3 <= RECURRENT_MAX_T
+    o3, state2 = ops.kda_recurrent_fwd(*cut(T0 + n_steps, T0 + n_steps + 3), initial_state=state,
+                                       l2norm_qk=True, out_fp32=True, state_in_place=True)
+    assert state2.data_ptr() == state.data_ptr()
+    outs.append(o3)
+    ops.check_device_status("cuda")
+    o = torch.cat(outs, dim=1)
+    assert _rel(o, o_ref) <= REL_TOL
+    assert _rel(state, s_ref) <= REL_TOL
+
+
+@pytest.mark.parametrize("T", [1, 2, 4])
+def test_kda_recurrent_kernel_matches_oracle_and_chunk_kernel(T):
+    from daisy_b200 import ops
+    B, H = 3, 5
+    q, k, v, g, beta = _inputs(B, T, H, seed=40 + T)
+    h0 = torch.randn(B, H, 128, 128, generator=torch.Generator().manual_seed(T)) * 0.3
+    o_ref, s_ref = okda.kda_recurrent(q.float(), k.float(), v.float(), g, beta, initial_state=h0)
+    dev = [x.cuda() for x in (q, k, v, g, beta)]
+    o_r, s_r = ops.kda_recurrent_fwd(*dev, initial_state=h0.cuda(), output_final_state=True, out_fp32=True)
+    o_c, s_c = ops.kda_chunk_fwd(*dev, initial_state=h0.cuda(), output_final_state=True, out_fp32=True)
+    ops.check_device_status("cuda")
+    assert _rel(o_r, o_ref) <= 1e-5 and _rel(s_r, s_ref) <= 1e-5          # fp32 arithmetic end to end
+    assert _rel(o_c, o_ref) <= REL_TOL and _rel(s_c, s_ref) <= REL_TOL
+    o_b, _ = ops.kda_recurrent_fwd(*dev, initial_state=h0.cuda())
+    assert o_b.dtype == torch.bfloat16 and _rel(o_b, o_ref.bfloat16().float()) <= 4e-3
+
+
+def test_kda_gate_matches_reference_fixture(golden_dir):
+    """The gate kernel against values produced by the reference's own ``_gate_impl``
+    (models/daisy/fla_custom_ops.py:71-103): fp32 input, bf16 input (result rounded to bf16 like the
+    reference's cast), no bias; softplus threshold crossed on both sides."""
+    from daisy_b200 import ops
+    from daisy_b200.kda import fused_kda_gate
+    d = np.load(os.path.join(golden_dir, "kda_gate_small.npz"))
+    x, A, bias = (torch.from_numpy(d[n]).cuda() for n in ("x", "A_log", "bias"))
+    y = ops.kda_gate(x, A, 128, bias)
+    ref = torch.from_numpy(d["y_fp32"])
+    assert y.shape == ref.shape
+    assert ((y.cpu() - ref).abs() <= 2e-6 * ref.abs() + 1e-6).all()
+    y_nb = ops.kda_gate(x, A, 128, None)
+    ref_nb = torch.from_numpy(d["y_nobias"])
+    assert ((y_nb.cpu() - ref_nb).abs() <= 2e-6 * ref_nb.abs() + 1e-6).all()
+    yb, bs = fused_kda_gate(x.bfloat16(), A, 128, bias)
+    refb = torch.from_numpy(d["y_bf16_as_fp32"])
+    assert yb.dtype == torch.bfloat16 and bs.shape == (*x.shape[:-1], 3) and not bs.any()
+    # identical up to one bf16 ulp where the fp32 value sits on a rounding boundary
+    assert ((yb.float().cpu() - refb).abs() <= refb.abs() * 2.0 ** -7).all()
+    assert (yb.float().cpu() == refb).float().mean().item() > 0.999

@@ -120,3 +120,16 @@ def test_work_counts():
     assert swa.prefill_flops(1, 65536, 16, 128, 8192) == pytest.approx(4.1232e12, rel=1e-4)
     assert swa.decode_bytes(64, 16, 128, 4095) == pytest.approx(2.1485e9, rel=1e-4)
     assert kda.kda_bytes_per_token_head() == 1540
+
+
+def test_kda_gate_against_reference_fixture(golden_dir):
+    """oracle.kda.kda_gate vs values produced by the reference's own ``_gate_impl``
+    (models/daisy/fla_custom_ops.py:71-103)."""
+    import numpy as np
+    d = np.load(os.path.join(golden_dir, "kda_gate_small.npz"))
+    x, A, bias = (torch.from_numpy(d[n]) for n in ("x", "A_log", "bias"))
+    for got, ref in ((kda.kda_gate(x, A, 128, bias), d["y_fp32"]), (kda.kda_gate(x, A, 128, None), d["y_nobias"])):
+        ref = torch.from_numpy(ref)
+        assert got.shape == ref.shape and ((got - ref).abs() <= 1e-6 * ref.abs() + 1e-7).all()
+    got = kda.kda_gate(x.bfloat16(), A, 128, bias)
+    assert got.dtype == torch.bfloat16 and torch.equal(got.float(), torch.from_numpy(d["y_bf16_as_fp32"]))
