@@ -71,17 +71,14 @@ struct KdaIntraParams {
 #ifdef KDA_PHASE_TIMING
 __device__ long long kda_phase_clk[16];
 #define KDA_MARK(n) do { __syncthreads(); if (threadIdx.x == 0 && blockIdx.x == 1 && blockIdx.y == 0 && blockIdx.z == 0) kda_phase_clk[n] = clock64(); } while (0)
-#define KDA_LAP(n) do { if (threadIdx.x == 0 && blockIdx.x == 1 && blockIdx.y == 0 && blockIdx.z == 0) { long long t_ = clock64(); kda_phase_clk[n] += t_ - kda_lap_t; kda_lap_t = t_; } } while (0)
-#define KDA_LAP_DECL long long kda_lap_t = clock64(); if (threadIdx.x == 0 && blockIdx.x == 1 && blockIdx.y == 0 && blockIdx.z == 0) { kda_phase_clk[10] = kda_phase_clk[11] = kda_phase_clk[12] = kda_phase_clk[13] = 0; }
 #else
 #define KDA_MARK(n)
-#define KDA_LAP(n)
-#define KDA_LAP_DECL
 #endif
 
 constexpr int LDA = 65;    // padded row (floats) of the fp32 [64 x 64] matrices
 constexpr int LDG = KD + 4;     // padded row (floats) of G: fragment gathers (8 rows x 4 column pairs) hit 32 banks
 constexpr int LDR = KD + 8;     // padded row (bf16) of the raw k / q tiles, same reason
+static_assert(KC * LDG * 4 <= 2 * KC * LDW * 2, "the decay image must fit under Mk + Mq");
 struct KdaIntraSmem {
   float G[KC][LDG];                // cumulative log-decay; later the W staging image
   __nv_bfloat16 kraw[KC][LDR];     // later (with qraw) the U0^T staging image
@@ -92,7 +89,7 @@ struct KdaIntraSmem {
   __half Th[KC][LDT];              // T = (I + A_kk)^-1, row-major
   __half ThT[KC][LDT];             // T^T
   __half Aqk[KC][LDT];
-  __half Mk[KC][LDW];              // one level's Gram operands: k * e^{-|G - r|}
+  __half Mk[KC][LDW];              // one level's Gram operands: k * e^{-|G - r|}   (Mk + Mq first hold e^g, fp32 [64][LDG])
   __half Mq[KC][LDW];              //                             q * e^{-|G - r|} on upper rows, else 0
   __half XT[KD][LDT];              // (beta k e^G)^T
   __half YT[KD][LDT];              // (beta v)^T
@@ -144,6 +141,11 @@ __global__ void __launch_bounds__(KDA_INTRA_THREADS, 1) kda_intra_kernel(const K
     for (int u = 0; u < 4; ++u) {
       const int idx = tid + u * KDA_INTRA_THREADS, r = idx >> 5, c4 = (idx & 31) * 4;
       *reinterpret_cast<uint4*>(&sm.G[r][c4]) = rg_[u];
+      // per-token decays d = e^g <= 1 for the running products of P3; the image borrows the Mk / Mq buffers
+      // until the Gram levels need them
+      float (*dd)[LDG] = reinterpret_cast<float (*)[LDG]>(&sm.Mk[0][0]);
+      *reinterpret_cast<float4*>(&dd[r][c4]) = make_float4(__expf(__uint_as_float(rg_[u].x)), __expf(__uint_as_float(rg_[u].y)),
+                                                           __expf(__uint_as_float(rg_[u].z)), __expf(__uint_as_float(rg_[u].w)));
     }
   }
   __syncthreads();
@@ -181,13 +183,13 @@ __global__ void __launch_bounds__(KDA_INTRA_THREADS, 1) kda_intra_kernel(const K
   for (int idx = tid; idx < KC * 16; idx += KDA_INTRA_THREADS) {                 // q~[i][8 channels]
     const int i = idx >> 4, c8 = (idx & 15) * 8;
     const float rs = sm.rq[i] * p.scale;
+    float qf[8];
+    unpack8(*reinterpret_cast<const uint4*>(&sm.qraw[i][c8]), qf);
+    const float4 g0 = *reinterpret_cast<const float4*>(&sm.G[i][c8]), g1 = *reinterpret_cast<const float4*>(&sm.G[i][c8 + 4]);
+    const float gg[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
     uint32_t o[4];
 #pragma unroll
-    for (int e = 0; e < 8; e += 2) {
-      const float a0 = __bfloat162float(sm.qraw[i][c8 + e]) * rs * __expf(sm.G[i][c8 + e]);
-      const float a1 = __bfloat162float(sm.qraw[i][c8 + e + 1]) * rs * __expf(sm.G[i][c8 + e + 1]);
-      o[e >> 1] = pack_h2(a0, a1);
-    }
+    for (int e = 0; e < 8; e += 2) o[e >> 1] = pack_h2(qf[e] * rs * __expf(gg[e]), qf[e + 1] * rs * __expf(gg[e + 1]));
     *reinterpret_cast<uint4*>(rec + OFF_Q + ((size_t)i * LDW + c8) * 2) = make_uint4(o[0], o[1], o[2], o[3]);
   }
   for (int idx = tid; idx < KD * 8; idx += KDA_INTRA_THREADS) {                  // (channel c, 8 tokens)
@@ -215,20 +217,107 @@ __global__ void __launch_bounds__(KDA_INTRA_THREADS, 1) kda_intra_kernel(const K
   }
 
   KDA_MARK(3);
-  // ---- P3: both gated Gram matrices on tensor cores, one binary level at a time.
-  // Level s in {32,16,8,4,2,1}: tokens fall into groups of 2s; rows in the upper half of a group (i & s) pair
-  // with columns in the lower half of the same group, and every pair i > j belongs to exactly one level (the
-  // highest bit in which i and j differ).  With r = G at the last row of the lower half,
-  //     e^{G_i - G_j} = e^{G_i - r} * e^{r - G_j},   both exponents <= 0,
-  // so each row gets ONE factor per level, e^{-|G_i - r|}: upper rows carry it as the left operand, lower rows as
-  // the right operand.  Mk = k * factor (all rows), Mq = q * factor (upper rows, else 0) are staged as fp16 and
-  // the level's blocks are plain m16n8k16 products; no exponent is ever positive, whatever the gate values.
+  // ---- P3: both gated Gram matrices.  e^{G_i - G_j} must never be formed from a positive exponent, whatever
+  // the gate values, so pairs are split by distance:
+  //  (a) pairs inside a 16-token block, on the FMA pipes with RUNNING PRODUCTS of the per-token decays
+  //      d_t = e^{g_t} <= 1:  k_j * prod_{t=j+1..i} d_t  is carried from row i-1 to row i with one multiply per
+  //      channel -- no exponential per pair at all;
+  //  (b) pairs in different blocks, on tensor cores by two binary levels s = 32, 16: tokens fall into groups of
+  //      2s, rows of a group's upper half pair with columns of its lower half.  With r = G at the last row of the
+  //      lower half, e^{G_i - G_j} = e^{G_i - r} * e^{r - G_j}, both exponents <= 0: each row carries ONE factor
+  //      e^{-|G_i - r|} per level, staged as fp16 operands Mk = k * factor (all rows), Mq = q * factor (upper
+  //      rows, else 0), and the level's blocks are plain m16n8k16 products.
   {
-    // build mapping: lanes 0-7 of a warp take 8 consecutive rows at the same channels, so every 8-lane phase of a
-    // 16-byte shared-memory access spreads over all banks (row strides are 4 banks apart).  Two warps share
+    // (a) a warp takes four columns j of one block over a range of rows, lane = four channels: row i of d, k, q is
+    //     read once per warp (512 + 256 + 256 contiguous bytes) and serves four columns from registers; the 2 x 4
+    //     partial dots of a row are reduced over the 32 lanes by a halving butterfly (9 shuffles for 8 values).
+    //     A column group's rows (15, 11, 7 or 3 of them) are cut into segments so that each of a block's four
+    //     warps walks nine rows -- the pass is bound by the dependent chain of one row after another, not by
+    //     issue slots.  A segment that does not begin at its columns' first row starts its running product from
+    //     e^{G_{start-1} - G_j} (exponent <= 0).  block = warp & 3: one block per scheduler.
+    {
+      const float (*dd)[LDG] = reinterpret_cast<const float (*)[LDG]>(&sm.Mk[0][0]);
+      const int blk = warp & 3, c0 = lane * 4;
+      int jq = 0;                                                  // column group of the segment being walked
+      float kp[4][4];                                              // k_j * running decay product, 4 columns x 4 channels
+      const bool hi16 = (lane & 16) != 0, hi8 = (lane & 8) != 0, hi4 = (lane & 4) != 0;
+      const int vsel = lane >> 2;                                  // after the butterfly: the value this lane holds
+      auto row = [&](const int i, const bool all_started) {
+        const int ii = blk * 16 + i, cc = jq * 4 + (vsel >> 1);
+        const float4 d4 = *reinterpret_cast<const float4*>(&dd[ii][c0]);
+        const uint2 kr = *reinterpret_cast<const uint2*>(&sm.kraw[ii][c0]);
+        const uint2 qr = *reinterpret_cast<const uint2*>(&sm.qraw[ii][c0]);
+        const float out_scale = (vsel & 1) ? p.scale * sm.rq[ii] : sm.beta[ii] * sm.rk[ii];
+        const float ki[4] = {__uint_as_float(kr.x << 16), __uint_as_float(kr.x & 0xffff0000u),
+                             __uint_as_float(kr.y << 16), __uint_as_float(kr.y & 0xffff0000u)};
+        const float qi[4] = {__uint_as_float(qr.x << 16), __uint_as_float(qr.x & 0xffff0000u),
+                             __uint_as_float(qr.y << 16), __uint_as_float(qr.y & 0xffff0000u)};
+        float val[8];                                              // [2 c] = k_i . kp_c, [2 c + 1] = q_i . kp_c
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          const bool on = all_started || i > jq * 4 + c;           // column c has started (warp-uniform)
+          kp[c][0] *= on ? d4.x : 1.f; kp[c][1] *= on ? d4.y : 1.f; kp[c][2] *= on ? d4.z : 1.f; kp[c][3] *= on ? d4.w : 1.f;
+          val[2 * c] = fmaf(ki[0], kp[c][0], ki[1] * kp[c][1]) + fmaf(ki[2], kp[c][2], ki[3] * kp[c][3]);
+          val[2 * c + 1] = fmaf(qi[0], kp[c][0], qi[1] * kp[c][1]) + fmaf(qi[2], kp[c][2], qi[3] * kp[c][3]);
+        }
+        float v4[4], v2[2], tot;
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+          const float recv = __shfl_xor_sync(0xffffffffu, hi16 ? val[t] : val[t + 4], 16);
+          v4[t] = (hi16 ? val[t + 4] : val[t]) + recv;
+        }
+#pragma unroll
+        for (int t = 0; t < 2; ++t) {
+          const float recv = __shfl_xor_sync(0xffffffffu, hi8 ? v4[t] : v4[t + 2], 8);
+          v2[t] = (hi8 ? v4[t + 2] : v4[t]) + recv;
+        }
+        tot = (hi4 ? v2[1] : v2[0]) + __shfl_xor_sync(0xffffffffu, hi4 ? v2[0] : v2[1], 4);
+        tot += __shfl_xor_sync(0xffffffffu, tot, 2);
+        tot += __shfl_xor_sync(0xffffffffu, tot, 1);
+        // the lane now holds value number lane >> 2 of this row, summed over all channels
+        if ((lane & 3) == 0 && i > cc) {
+          if (vsel & 1) sm.Aqk[ii][blk * 16 + cc] = __float2half_rn(out_scale * tot);
+          else          sm.Akk[ii][blk * 16 + cc] = out_scale * tot;
+        }
+      };
+      auto segment = [&](const int q, const int r0, const int r1) {
+        jq = q;
+        const bool fresh = (r0 == q * 4 + 1);
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          const int jj = blk * 16 + q * 4 + c;
+          const float rkj = sm.rk[jj];
+          const uint2 kr = *reinterpret_cast<const uint2*>(&sm.kraw[jj][c0]);
+          float f[4] = {1.f, 1.f, 1.f, 1.f};
+          if (!fresh) {
+            const float4 ga = *reinterpret_cast<const float4*>(&sm.G[blk * 16 + r0 - 1][c0]);
+            const float4 gj = *reinterpret_cast<const float4*>(&sm.G[jj][c0]);
+            f[0] = __expf(ga.x - gj.x); f[1] = __expf(ga.y - gj.y); f[2] = __expf(ga.z - gj.z); f[3] = __expf(ga.w - gj.w);
+          }
+          kp[c][0] = __uint_as_float(kr.x << 16) * rkj * f[0]; kp[c][1] = __uint_as_float(kr.x & 0xffff0000u) * rkj * f[1];
+          kp[c][2] = __uint_as_float(kr.y << 16) * rkj * f[2]; kp[c][3] = __uint_as_float(kr.y & 0xffff0000u) * rkj * f[3];
+        }
+        if (fresh) {                                               // the first three rows see only some of the columns
+          for (int i = r0; i < r0 + 3 && i < r1; ++i) row(i, false);
+#pragma unroll 2
+          for (int i = r0 + 3; i < r1; ++i) row(i, true);
+        } else {
+#pragma unroll 2
+          for (int i = r0; i < r1; ++i) row(i, true);
+        }
+      };
+      switch (warp >> 2) {                                         // nine rows per warp
+        case 0:  segment(0, 1, 10); break;
+        case 1:  segment(0, 10, 16); segment(3, 13, 16); break;
+        case 2:  segment(1, 5, 14); break;
+        default: segment(1, 14, 16); segment(2, 9, 16); break;
+      }
+    }
+    // (b) build mapping: lanes 0-7 of a warp take 8 consecutive rows at the same channels, so every 8-lane phase of
+    // a 16-byte shared-memory access spreads over all banks (row strides are 4 banks apart).  Two warps share
     // eight rows; a thread owns channels bq + 64 k .. + 8 (k = 0, 1).
     const int brow = (warp >> 1) * 8 + (lane & 7), bq = ((lane >> 3) + 4 * (warp & 1)) * 8;
-    // this thread's 16 normalised k and q values and cumulative gates stay in registers across the six levels
+    // this thread's 16 normalised k and q values and cumulative gates stay in registers across the levels
     float kn[16], qn[16], gi[16];
     {
       const float rkb = sm.rk[brow], rqb = sm.rq[brow];
@@ -245,10 +334,11 @@ __global__ void __launch_bounds__(KDA_INTRA_THREADS, 1) kda_intra_kernel(const K
         for (int e = 0; e < 8; ++e) { kn[8 * kq + e] = kf[e] * rkb; qn[8 * kq + e] = qf[e] * rqb; gi[8 * kq + e] = gg[e]; }
       }
     }
-    KDA_LAP_DECL;
+    __syncthreads();                                                 // (a) is done with the decay image under Mk / Mq
+    KDA_MARK(4);
 #pragma unroll 1
-    for (int ls = 5; ls >= 0; --ls) {
-      const int s = 1 << ls;                                         // shifts and masks below: s is a power of two
+    for (int ls = 5; ls >= 4; --ls) {
+      const int s = 1 << ls;
       // -- build the level's operands
       {
         const bool upper = (brow & s) != 0;
@@ -270,75 +360,50 @@ __global__ void __launch_bounds__(KDA_INTRA_THREADS, 1) kda_intra_kernel(const K
           *reinterpret_cast<uint4*>(&sm.Mq[brow][c]) = make_uint4(mq[0], mq[1], mq[2], mq[3]);
         }
       }
-      KDA_LAP(10);
       __syncthreads();
-      KDA_LAP(11);
-      // -- the level's blocks.  A tile = 16 rows x 8 columns; for s <= 8 one 16-row tile spans 8/s groups and
-      //    its 8 columns are the lower halves of those groups (column n -> group n / s, offset n % s).
+      // -- the level's blocks, one 16 x 8 tile per warp.  Level 32: rows 32-63 x columns 0-31, eight tiles per
+      //    matrix, all 16 warps (warp -> tile w & 7, matrix w >> 3).  Level 16: rows 16-31 x columns 0-15 and rows
+      //    48-63 x columns 32-47, four tiles per matrix, warps 0-7 (tile w & 3, matrix w >> 2).
       {
-        // 16 warps: level 32 has 8 tiles per matrix (warp -> tile w & 7, matrix w >> 3); the other levels have 4
-        // (warp -> tile w & 3, matrix (w >> 2) & 1) and keep warps 8-15 free for the next build
         int mrow, ncol0;
         const int which = (s == 32) ? (warp >> 3) : ((warp >> 2) & 1);      // 0 = A_kk, 1 = A_qk
         const bool active = (s == 32) || warp < 8;
         if (s == 32) { const int c = warp & 7; mrow = 32 + 16 * (c >> 2); ncol0 = 8 * (c & 3); }
-        else if (s == 16) { const int c = warp & 3; mrow = 16 + 32 * (c >> 1); ncol0 = 32 * (c >> 1) + 8 * (c & 1); }
-        else { mrow = 16 * (warp & 3); ncol0 = mrow; }
+        else { const int c = warp & 3; mrow = 16 + 32 * (c >> 1); ncol0 = 32 * (c >> 1) + 8 * (c & 1); }
         if (active) {
-        // column (token) held by this lane's B fragment, and validity of this lane's four outputs
-        const int nb = g8;                                           // B fragment: n = lane >> 2
-        const int jb = (s >= 8) ? ncol0 + nb : mrow + ((nb >> ls) << (ls + 1)) + (nb & (s - 1));
-        float acc_k[4] = {0.f, 0.f, 0.f, 0.f}, acc_q[4] = {0.f, 0.f, 0.f, 0.f};
-        float acc_k2[4] = {0.f, 0.f, 0.f, 0.f}, acc_q2[4] = {0.f, 0.f, 0.f, 0.f};   // odd k-steps: two independent chains
-        const int i0 = mrow + g8, i1 = i0 + 8;
-        // all fragments first (independent shared-memory loads), then the products
-        uint32_t bf[KD / 16][2], af[KD / 16][4];
-        const __half* arow0 = (which == 1) ? &sm.Mq[i0][0] : &sm.Mk[i0][0];
-        const __half* arow1 = (which == 1) ? &sm.Mq[i1][0] : &sm.Mk[i1][0];
+          const int jb = ncol0 + g8;                                 // column (token) held by this lane's B fragment
+          float acc[4] = {0.f, 0.f, 0.f, 0.f}, acc2[4] = {0.f, 0.f, 0.f, 0.f};   // two independent chains
+          const int i0 = mrow + g8, i1 = i0 + 8;
+          // all fragments first (independent shared-memory loads), then the products
+          uint32_t bf[KD / 16][2], af[KD / 16][4];
+          const __half* arow0 = (which == 1) ? &sm.Mq[i0][0] : &sm.Mk[i0][0];
+          const __half* arow1 = (which == 1) ? &sm.Mq[i1][0] : &sm.Mk[i1][0];
 #pragma unroll
-        for (int ks = 0; ks < KD / 16; ++ks) {
-          const int c = ks * 16 + 2 * t4;
-          bf[ks][0] = *reinterpret_cast<const uint32_t*>(&sm.Mk[jb][c]);
-          bf[ks][1] = *reinterpret_cast<const uint32_t*>(&sm.Mk[jb][c + 8]);
-          af[ks][0] = *reinterpret_cast<const uint32_t*>(&arow0[c]);
-          af[ks][1] = *reinterpret_cast<const uint32_t*>(&arow1[c]);
-          af[ks][2] = *reinterpret_cast<const uint32_t*>(&arow0[c + 8]);
-          af[ks][3] = *reinterpret_cast<const uint32_t*>(&arow1[c + 8]);
-        }
-        float* accA = (which == 1) ? acc_q : acc_k;
-        float* accB = (which == 1) ? acc_q2 : acc_k2;
-#pragma unroll
-        for (int ks = 0; ks < KD / 16; ks += 2) {
-          mma_f16(accA, af[ks], bf[ks][0], bf[ks][1]);
-          mma_f16(accB, af[ks + 1], bf[ks + 1][0], bf[ks + 1][1]);
-        }
-#pragma unroll
-        for (int x = 0; x < 4; ++x) { acc_k[x] += acc_k2[x]; acc_q[x] += acc_q2[x]; }
-        // outputs: rows i0 (acc[0],acc[1]) and i1 (acc[2],acc[3]), tile columns 2 t4, 2 t4 + 1
-#pragma unroll
-        for (int x = 0; x < 4; ++x) {
-          const int i = (x < 2) ? i0 : i1;
-          const int n = 2 * t4 + (x & 1);
-          int j; bool ok;
-          if (s >= 16) { j = ncol0 + n; ok = true; }
-          else {
-            const int r = i - mrow;
-            j = mrow + ((n >> ls) << (ls + 1)) + (n & (s - 1));
-            ok = ((r >> (ls + 1)) == (n >> ls)) && ((r & s) != 0);
+          for (int ks = 0; ks < KD / 16; ++ks) {
+            const int c = ks * 16 + 2 * t4;
+            bf[ks][0] = *reinterpret_cast<const uint32_t*>(&sm.Mk[jb][c]);
+            bf[ks][1] = *reinterpret_cast<const uint32_t*>(&sm.Mk[jb][c + 8]);
+            af[ks][0] = *reinterpret_cast<const uint32_t*>(&arow0[c]);
+            af[ks][1] = *reinterpret_cast<const uint32_t*>(&arow1[c]);
+            af[ks][2] = *reinterpret_cast<const uint32_t*>(&arow0[c + 8]);
+            af[ks][3] = *reinterpret_cast<const uint32_t*>(&arow1[c + 8]);
           }
-          if (ok) {
-            if (which != 1) {
-              const float a = sm.beta[i] * acc_k[x];
-              if (s >= 16) sm.Akh[i][j] = __float2half_rn(a); else sm.Akk[i][j] = a;
-            }
-            if (which != 0) sm.Aqk[i][j] = __float2half_rn(p.scale * acc_q[x]);
+#pragma unroll
+          for (int ks = 0; ks < KD / 16; ks += 2) {
+            mma_f16(acc, af[ks], bf[ks][0], bf[ks][1]);
+            mma_f16(acc2, af[ks + 1], bf[ks + 1][0], bf[ks + 1][1]);
           }
-        }
+          // outputs: rows i0 (acc[0], acc[1]) and i1 (acc[2], acc[3]), columns ncol0 + 2 t4 (+1)
+#pragma unroll
+          for (int x = 0; x < 4; ++x) {
+            const int i = (x < 2) ? i0 : i1, jc = ncol0 + 2 * t4 + (x & 1);
+            const float a = acc[x] + acc2[x];
+            if (which == 0) sm.Akh[i][jc] = __float2half_rn(sm.beta[i] * a);
+            else            sm.Aqk[i][jc] = __float2half_rn(p.scale * a);
+          }
         }
       }
-      KDA_LAP(12);
       __syncthreads();
-      KDA_LAP(13);
     }
   }
 
