@@ -64,6 +64,7 @@ struct KdaIntraParams {
   const float *g, *beta;
   uint8_t* ws;
   int T, H, NC;            // NC = chunks per sequence
+  int ahead;               // CTAs per wave: how far ahead (in launch order) a CTA prefetches
   float scale;
   int l2norm;
 };
@@ -129,6 +130,25 @@ __global__ void __launch_bounds__(KDA_INTRA_THREADS, 1) kda_intra_kernel(const K
       if (r < rows) rg_[u] = ld_stream16(p.g + (tok0 + (size_t)r * p.H) * KD + c4);
     }
     if (tid < KC) sm.beta[tid] = tid < rows ? p.beta[tok0 + (size_t)tid * p.H] : 0.f;
+    // Pull the inputs of the CTA that will run one wave from now into L2 (ten 128-byte lines per token row), so
+    // that its load phase, which nothing overlaps, pays L2 latency instead of HBM latency.
+    {
+      const long long lin = (long long)blockIdx.x + (long long)gridDim.x * (blockIdx.y + (long long)gridDim.y * blockIdx.z) + p.ahead;
+      const int nchunk = (int)(lin % p.NC), nh = (int)((lin / p.NC) % p.H);
+      const long long nb = lin / ((long long)p.NC * p.H);
+      for (int idx = tid; idx < KC * 10; idx += KDA_INTRA_THREADS) {
+        const int r = idx / 10, w = idx - r * 10;
+        const int t = nchunk * KC + r;
+        if (nb < (long long)gridDim.z && t < p.T) {
+          const size_t ntok = ((size_t)nb * p.T + t) * p.H + nh;
+          const void* a = w < 2 ? (const void*)(reinterpret_cast<const char*>(p.q + ntok * KD) + w * 128)
+                        : w < 4 ? (const void*)(reinterpret_cast<const char*>(p.k + ntok * KD) + (w - 2) * 128)
+                        : w < 6 ? (const void*)(reinterpret_cast<const char*>(p.v + ntok * KD) + (w - 4) * 128)
+                                : (const void*)(reinterpret_cast<const char*>(p.g + ntok * KD) + (w - 6) * 128);
+          asm volatile("prefetch.global.L2 [%0];" ::"l"(a));
+        }
+      }
+    }
     for (int idx = tid; idx < KC * LDT / 2; idx += KDA_INTRA_THREADS) reinterpret_cast<uint32_t*>(&sm.Aqk[0][0])[idx] = 0u;
 #pragma unroll
     for (int u = 0; u < 2; ++u) {
@@ -781,6 +801,11 @@ extern "C" int daisy_b200_kda_chunk_fwd(const void* q, const void* k, const void
   ip.T = T; ip.H = H; ip.NC = NC;
   ip.scale = scale > 0.f ? scale : 1.0f / sqrtf((float)K);
   ip.l2norm = (flags & DAISY_KDA_L2NORM_QK) ? 1 : 0;
+  {
+    static int sms = 0;
+    if (sms <= 0) sms = daisy_b200_sm_count();
+    ip.ahead = sms > 0 ? sms : 148;
+  }
   kda_intra_kernel<<<dim3(NC, H, B), KDA_INTRA_THREADS, sizeof(KdaIntraSmem), st>>>(ip);
   DAISY_CHECK_LAUNCH();
 
