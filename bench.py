@@ -39,7 +39,7 @@ DECODE_SMALL = dict(B=4, H=16, D=128, cap=32768, window=4096, steps=4)
 KDA_SMALL = dict(B=1, T=8192, H=16, K=128, V=128, chunk=64)
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch from the ncu captures summarised under profiles/
 # (reduced workloads of the same kernels); traffic grows in proportion to the batch (independent sequences)
-NCU_TRAFFIC = {"prefill_per_batch_row": 246.4e6 / 2, "decode_per_batch_row": 137.3e6 / 4}
+NCU_TRAFFIC = {"prefill_per_batch_row": 246.8e6 / 2, "decode_per_batch_row": 137.3e6 / 4}
 ROPE_BASE = 10000.0     # the benchmark configs name base 10000 (the module default is 1024, half-truncated)
 
 
