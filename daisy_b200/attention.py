@@ -28,8 +28,27 @@ from .kv_cache import B200KVCache
 
 @dataclass(frozen=True)
 class WindowMask:
-    """Stands in for the dense additive mask of ``build_attn_mask``: causal, ``window`` most recent keys."""
+    """Stands in for the dense additive mask of ``build_attn_mask`` (models/daisy/daisy_core.py:53-69): causal,
+    ``window`` most recent keys and, with ``doc_start``, only keys of the query's own document.
+    ``doc_start`` is an integer tensor ``[T]`` or ``[B,T]`` holding each token's first document position
+    (:func:`doc_starts` builds it from the token ids the way the reference numbers documents)."""
     window: Optional[int]
+    doc_start: Optional[Tensor] = None
+
+    @classmethod
+    def from_tokens(cls, input_seq: Tensor, window: Optional[int], eos_token_id: int) -> "WindowMask":
+        """Same arguments as ``build_attn_mask(input_seq, window_size, eos_token_id)``."""
+        return cls(window, doc_starts(input_seq, eos_token_id))
+
+
+def doc_starts(input_seq: Tensor, eos_token_id: int) -> Tensor:
+    """First position of each token's document, int32, shape of ``input_seq`` without a leading batch of 1.
+    The reference counts ``docs = (input_seq == eos).cumsum(0)``: an EOS token opens the next document, so the
+    start is the position of the last EOS at or before the token (0 if there is none)."""
+    seq = input_seq.squeeze(0) if input_seq.dim() == 2 and input_seq.size(0) == 1 else input_seq
+    pos = torch.arange(seq.shape[-1], device=seq.device).expand_as(seq)
+    marks = torch.where(seq == eos_token_id, pos, torch.zeros_like(pos))
+    return torch.cummax(marks, dim=-1).values.to(torch.int32)
 
 
 class Rotary(nn.Module):
@@ -102,17 +121,19 @@ class B200CausalSelfAttention(nn.Module):
         return qkv.chunk(3, dim=-2)                       # strided views, no copies
 
     @staticmethod
-    def _window_of(attn_mask) -> Optional[int]:
+    def _window_of(attn_mask):
+        """-> (window or None, doc_start tensor or None)"""
         if attn_mask is None:
-            return None
+            return None, None
         if isinstance(attn_mask, WindowMask):
-            return attn_mask.window
+            return attn_mask.window, attn_mask.doc_start
         if isinstance(attn_mask, int):
-            return attn_mask
-        raise TypeError("attn_mask must be None, an int window or WindowMask(window); dense mask tensors are "
-                        "not consumed by the B200 kernels")
+            return attn_mask, None
+        raise TypeError("attn_mask must be None, an int window or WindowMask(window[, doc_start]); dense mask "
+                        "tensors are not consumed by the B200 kernels")
 
-    def _attend(self, x: Tensor, ve: Optional[Tensor], window: Optional[int]):
+    def _attend(self, x: Tensor, ve: Optional[Tensor], mask):
+        window, doc_start = mask
         B, T = x.size(0), x.size(1)
         q, k, v = self._project(x)
         cos, sin = self.rotary.tables(T)
@@ -121,10 +142,11 @@ class B200CausalSelfAttention(nn.Module):
             qp, kp, vp = ops.qkv_prep(q, k, v, cos, sin, self.norm_eps)
             g = torch.sigmoid(self.g_ve).to(vp.dtype)
             vp = g * vp + (1.0 - g) * ve.view(B, T, self.num_heads, self.head_dim).to(vp.dtype)
-            y = ops.swa_attend(qp, kp, vp, window, self.attn_scale, bounded_qk=True)   # q, k are RMS-normalised
+            y = ops.swa_attend(qp, kp, vp, window, self.attn_scale, bounded_qk=True,   # q, k are RMS-normalised
+                               doc_start=doc_start)
             qp, kp, vp = qp.transpose(1, 2), kp.transpose(1, 2), vp.transpose(1, 2)
         else:
-            y, kp, vp = ops.swa_prefill(q, k, v, cos, sin, window, self.attn_scale, self.norm_eps)
+            y, kp, vp = ops.swa_prefill(q, k, v, cos, sin, window, self.attn_scale, self.norm_eps, doc_start=doc_start)
             qp = None
         y = F.linear(y.view(B, T, self.m_dim), self.qkvo_w[3])
         return y, kp, vp, qp

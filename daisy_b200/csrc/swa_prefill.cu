@@ -48,6 +48,10 @@ struct PrefillParams {
   int T, H, B, window;
   float scale_log2;
   int* status;
+  // document mask: doc_start[b * doc_sb + t] = first key position of the document token t belongs to (null: one
+  // document).  Non-decreasing in t.
+  const int* doc_start;
+  int64_t doc_sb;
   // raw-Q mode: the kernel RMS-normalises and rotates the Q tile in shared memory before the first product
   const float* cos;
   const float* sin;
@@ -92,7 +96,8 @@ struct ItemGeom {
   bool valid[2];
   int jlo, jhi;
 };
-__device__ __forceinline__ ItemGeom item_geom(int item, int nq, int H, int T, int window) {
+__device__ __forceinline__ ItemGeom item_geom(int item, int nq, int H, int T, int window,
+                                              const int* doc_start = nullptr, int64_t doc_sb = 0) {
   ItemGeom g;
   const int qp = item % nq, bh = item / nq;
   g.h = bh % H; g.b = bh / H;
@@ -100,7 +105,9 @@ __device__ __forceinline__ ItemGeom item_geom(int item, int nq, int H, int T, in
   for (int s = 0; s < 2; ++s) {
     g.q0[s] = (qp * 2 + s) * BM;
     g.valid[s] = g.q0[s] < T;
-    const int klo = window > 0 ? max(0, g.q0[s] - window + 1) : 0;
+    int klo = window > 0 ? max(0, g.q0[s] - window + 1) : 0;
+    // keys before the document of the stream's FIRST row are invisible to every row of the stream
+    if (doc_start && g.valid[s]) klo = max(klo, doc_start[g.b * doc_sb + g.q0[s]]);
     g.jlo_s[s] = g.valid[s] ? klo / BN : 1;
     g.jhi_s[s] = g.valid[s] ? min(g.q0[s] + BM - 1, T - 1) / BN : 0;
   }
@@ -168,7 +175,7 @@ swa_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       // Q tiles run one item ahead of the K/V stream (double buffer), so the softmax warps can prepare the
       // next item's Q while the current item is still computing.
       auto load_q = [&](int it_item) {
-        const ItemGeom gq = item_geom(it_item, nq, p.H, T, window);
+        const ItemGeom gq = item_geom(it_item, nq, p.H, T, window, p.doc_start, p.doc_sb);
         for (int s = 0; s < 2 && ok; ++s) {
           if (!gq.valid[s]) continue;
           const int qb = qn[s] % NQBUF;
@@ -182,7 +189,7 @@ swa_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       };
       if ((int)blockIdx.x < n_items) load_q(blockIdx.x);
       for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
-        const ItemGeom g = item_geom(item, nq, p.H, T, window);
+        const ItemGeom g = item_geom(item, nq, p.H, T, window, p.doc_start, p.doc_sb);
         for (int j = g.jlo; j <= g.jhi && ok; ++j) {
           for (int kv = 0; kv < 2; ++kv, ++n) {
             const int stage = n % NSTAGE;
@@ -224,7 +231,7 @@ swa_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       PT_DECL;
       PT_START();
       for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
-        const ItemGeom g = item_geom(item, nq, p.H, T, window);
+        const ItemGeom g = item_geom(item, nq, p.H, T, window, p.doc_start, p.doc_sb);
         for (int j = g.jlo; j <= g.jhi + 1 && ok; ++j) {
 #pragma unroll
           for (int s = 0; s < 2; ++s) {
@@ -302,11 +309,14 @@ swa_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     PT_DECL;
     PT_START();
     for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
-      const ItemGeom g = item_geom(item, nq, p.H, T, window);
+      const ItemGeom g = item_geom(item, nq, p.H, T, window, p.doc_start, p.doc_sb);
       if (!g.valid[s]) continue;
       const int q0 = g.q0[s];
       const int q_row = q0 + row;
       uint64_t sum_a = pack2f(0.f, 0.f), sum_b = sum_a;
+      // first visible key of this row's document, and the latest such start among the stream's rows
+      const int ds_row = p.doc_start ? p.doc_start[g.b * p.doc_sb + min(q_row, T - 1)] : 0;
+      const int ds_max = p.doc_start ? p.doc_start[g.b * p.doc_sb + min(q0 + BM - 1, T - 1)] : 0;
       for (int j = g.jlo_s[s]; j <= g.jhi_s[s]; ++j) {
         ok = __all_sync(0xffffffffu, mbar_wait(&bars->s_full[s], n_s & 1, abort_flag, p.status, 6));
         if (!ok) break;
@@ -314,7 +324,7 @@ swa_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         PT_LAP(0);
         tc_fence_after();
         const int k0 = j * BN + half * 64;                            // key index of this thread's first column
-        const bool full_tile = (j * BN + BN - 1 <= q0) && (window <= 0 || j * BN > q0 + BM - 1 - window);
+        const bool full_tile = (j * BN + BN - 1 <= q0) && (window <= 0 || j * BN > q0 + BM - 1 - window) && ds_max <= j * BN;
         uint32_t r[64];
         tmem_ld32(s_tmem, r);
         tmem_ld32(s_tmem + 32, r + 32);
@@ -322,7 +332,7 @@ swa_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         PT_LAP(1);
         if (!full_tile) {
           const int hi = q_row - k0;                                   // column i is visible iff lo < i <= hi
-          const int lo = window > 0 ? q_row - window - k0 : -1;
+          const int lo = max(window > 0 ? q_row - window - k0 : -1, ds_row - 1 - k0);
 #pragma unroll
           for (int i = 0; i < 64; ++i)
             if (!(i > lo && i <= hi)) r[i] = 0xff800000u;              // -inf -> weight 0
@@ -494,7 +504,7 @@ swa_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     PT_DECL;
     PT_START();
     for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
-      const ItemGeom g = item_geom(item, nq, p.H, T, window);
+      const ItemGeom g = item_geom(item, nq, p.H, T, window, p.doc_start, p.doc_sb);
       if (!g.valid[s]) continue;
       const int q0 = g.q0[s];
       const int q_row = q0 + row;
@@ -509,11 +519,13 @@ swa_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       bool next_valid = false;
       int q_row_next = 0;
       if (QRAW && item_next < n_items) {
-        const ItemGeom gn = item_geom(item_next, nq, p.H, T, window);
+        const ItemGeom gn = item_geom(item_next, nq, p.H, T, window, p.doc_start, p.doc_sb);
         next_valid = gn.valid[s];
         q_row_next = gn.q0[s] + row;
       }
       float m_ref = NEG_BIG, l = 0.f, pend = 0.f;   // pend: how far the reference is known to lag (applied before the next P)
+      const int ds_row = p.doc_start ? p.doc_start[g.b * p.doc_sb + min(q_row, T - 1)] : 0;
+      const int ds_max = p.doc_start ? p.doc_start[g.b * p.doc_sb + min(q0 + BM - 1, T - 1)] : 0;
       for (int j = g.jlo_s[s]; j <= g.jhi_s[s]; ++j) {
         const bool first = (j == g.jlo_s[s]);
         ok = __all_sync(0xffffffffu, mbar_wait(&bars->s_full[s], n_s & 1, abort_flag, p.status, 6));
@@ -522,7 +534,7 @@ swa_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         PT_LAP(0);
         tc_fence_after();
         const int k0 = j * BN;
-        const bool full_tile = (k0 + BN - 1 <= q0) && (window <= 0 || k0 > q0 + BM - 1 - window);
+        const bool full_tile = (k0 + BN - 1 <= q0) && (window <= 0 || k0 > q0 + BM - 1 - window) && ds_max <= k0;
         // whole S row into registers
         tmem_ld32(s_tmem, r);
         tmem_ld32(s_tmem + 32, r + 32);
@@ -533,7 +545,7 @@ swa_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         if (!full_tile) {
           // column i of this tile is visible iff lo < i <= hi
           const int hi = q_row - k0;
-          const int lo = window > 0 ? q_row - window - k0 : -1;
+          const int lo = max(window > 0 ? q_row - window - k0 : -1, ds_row - 1 - k0);
 #pragma unroll
           for (int i = 0; i < 128; ++i)
             if (!(i > lo && i <= hi)) r[i] = 0xff800000u;              // -inf
@@ -794,7 +806,7 @@ static int launch_attend(const void* q, const void* k, const void* v,
                          int64_t v_sb, int64_t v_st, int64_t v_sh,
                          void* out, int64_t o_sb, int64_t o_st, int64_t o_sh,
                          int B, int T, int H, int D, int window, float scale, const QTransform* qt, bool bounded_qk,
-                         int* status_word, void* stream) {
+                         const int* doc_start, int64_t doc_sb, int* status_word, void* stream) {
   if (!q || !k || !v || !out || B <= 0 || T <= 0 || H <= 0 || !(scale > 0.f)) return DAISY_EINVAL;
   if (D != DAISY_HEAD_DIM) return DAISY_EUNSUPPORTED;
   if (!daisy_aligned16(q) || !daisy_aligned16(k) || !daisy_aligned16(v) || !daisy_aligned16(out) || ((o_sb | o_st | o_sh) & 7) ||
@@ -802,6 +814,7 @@ static int launch_attend(const void* q, const void* k, const void* v,
     return DAISY_EALIGN;
   if (q_st <= 0 || k_st <= 0 || v_st <= 0 || q_sh < 0 || k_sh < 0 || v_sh < 0 || q_sb < 0 || k_sb < 0 || v_sb < 0) return DAISY_EINVAL;
   if (qt && qt->rope && (!qt->cos || !qt->sin)) return DAISY_EINVAL;
+  if (doc_start && (doc_sb < 0 || (reinterpret_cast<uintptr_t>(doc_start) & 3))) return DAISY_EINVAL;
   if (qt && qt->rope && (!daisy_aligned16(qt->cos) || !daisy_aligned16(qt->sin))) return DAISY_EALIGN;
   if (ensure_smem_attr() != DAISY_OK) { (void)cudaGetLastError(); return DAISY_ECUDA; }
   CUtensorMap tq, tk, tv;
@@ -816,6 +829,7 @@ static int launch_attend(const void* q, const void* k, const void* v,
   p.T = T; p.H = H; p.B = B; p.window = window;
   p.scale_log2 = scale * 1.4426950408889634f;
   p.status = status_word;
+  p.doc_start = doc_start; p.doc_sb = doc_sb;
   p.cos = qt ? qt->cos : nullptr; p.sin = qt ? qt->sin : nullptr;
   p.eps = qt ? qt->eps : 0.f; p.q_norm = qt ? qt->norm : 0; p.q_rope = qt ? qt->rope : 0;
   const int64_t items = (int64_t)((T + 2 * BM - 1) / (2 * BM)) * H * B;
@@ -845,10 +859,12 @@ extern "C" int daisy_b200_swa_attend(const void* q, const void* k, const void* v
                                      int64_t v_sb, int64_t v_st, int64_t v_sh,
                                      void* out, int64_t o_sb, int64_t o_st, int64_t o_sh,
                                      int B, int T, int H, int D, int window, float scale,
+                                     const int32_t* doc_start, int64_t doc_sb,
                                      unsigned flags, int* status_word, void* stream) {
   if (flags & ~DAISY_BOUNDED_QK) return DAISY_EINVAL;
   return launch_attend(q, k, v, q_sb, q_st, q_sh, k_sb, k_st, k_sh, v_sb, v_st, v_sh, out, o_sb, o_st, o_sh,
-                       B, T, H, D, window, scale, nullptr, (flags & DAISY_BOUNDED_QK) != 0, status_word, stream);
+                       B, T, H, D, window, scale, nullptr, (flags & DAISY_BOUNDED_QK) != 0, doc_start, doc_sb,
+                       status_word, stream);
 }
 
 static size_t align1k(size_t x) { return (x + 1023) & ~size_t(1023); }
@@ -866,6 +882,7 @@ extern "C" int daisy_b200_swa_prefill_fwd(const void* q, const void* k, const vo
                                           void* out, int64_t o_sb, int64_t o_st, int64_t o_sh,
                                           void* k_out, void* v_out,
                                           int B, int T, int H, int D, int window, float scale, float eps,
+                                          const int32_t* doc_start, int64_t doc_sb,
                                           unsigned flags, void* workspace, size_t workspace_bytes,
                                           int* status_word, void* stream) {
   if (!q || !k || !v || !out || !workspace || B <= 0 || T <= 0 || H <= 0) return DAISY_EINVAL;
@@ -901,9 +918,11 @@ extern "C" int daisy_b200_swa_prefill_fwd(const void* q, const void* k, const vo
   auto attend = [&](int b0, int nb, void* s) {
     if (q_in_kernel)
       return launch_attend(off(q, b0 * q_sb), off(kp, b0 * sb_), off(vp, b0 * sb_), q_sb, q_st, q_sh, sb_, st_, sh_, sb_, st_, sh_,
-                           (void*)off(out, b0 * o_sb), o_sb, o_st, o_sh, nb, T, H, D, window, scale, &qt, bounded_qk, status_word, s);
+                           (void*)off(out, b0 * o_sb), o_sb, o_st, o_sh, nb, T, H, D, window, scale, &qt, bounded_qk,
+                           doc_start ? doc_start + b0 * doc_sb : nullptr, doc_sb, status_word, s);
     return launch_attend(off(qp, b0 * sb_), off(kp, b0 * sb_), off(vp, b0 * sb_), sb_, st_, sh_, sb_, st_, sh_, sb_, st_, sh_,
-                         (void*)off(out, b0 * o_sb), o_sb, o_st, o_sh, nb, T, H, D, window, scale, nullptr, bounded_qk, status_word, s);
+                         (void*)off(out, b0 * o_sb), o_sb, o_st, o_sh, nb, T, H, D, window, scale, nullptr, bounded_qk,
+                         doc_start ? doc_start + b0 * doc_sb : nullptr, doc_sb, status_word, s);
   };
 
   // (Cutting the batch into slices so that the streaming pass over slice i+1 runs on a side stream underneath the

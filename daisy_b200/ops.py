@@ -76,22 +76,39 @@ def qkv_prep(q, k, v, cos, sin, eps: float, flags: int = QKV_DEFAULT, bhtd: bool
     return tuple(outs)
 
 
+def _doc_arg(doc_start: Optional[torch.Tensor], B: int, T: int, device):
+    """``doc_start`` ([T] shared by the batch, or [B,T]) -> (int32 contiguous tensor or None, pointer, batch stride)."""
+    if doc_start is None:
+        return None, None, 0
+    if not doc_start.is_cuda:
+        raise ValueError("doc_start must be a CUDA tensor")
+    d = doc_start.to(device=device, dtype=torch.int32).contiguous()
+    if d.dim() == 1 and d.shape[0] == T:
+        return d, d.data_ptr(), 0
+    if d.dim() == 2 and d.shape == (B, T):
+        return d, d.data_ptr(), T
+    raise ValueError(f"doc_start must have shape [{T}] or [{B},{T}], got {tuple(d.shape)}")
+
+
 def swa_attend(q, k, v, window: Optional[int], scale: float = ATTN_SCALE,
-               out: Optional[torch.Tensor] = None, bounded_qk: bool = False) -> torch.Tensor:
+               out: Optional[torch.Tensor] = None, bounded_qk: bool = False,
+               doc_start: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Windowed causal attention on prepared tensors of logical shape ``[B,T,H,D]`` (any batch / token /
     head strides, D contiguous); returns ``[B,T,H,D]``.  ``bounded_qk=True`` promises RMS-normalised q and k
-    (every logit bounded), which selects the kernel without a running maximum."""
+    (every logit bounded), which selects the kernel without a running maximum.  ``doc_start`` (int, ``[T]`` or
+    ``[B,T]``): first position of each token's document; keys before it are masked."""
     for n, t in (("q", q), ("k", k), ("v", v)):
         _req(t, n)
     B, T, H, D = q.shape
     assert k.shape == q.shape and v.shape == q.shape
     if out is None:
         out = torch.empty(B, T, H, D, dtype=torch.bfloat16, device=q.device)
+    _doc, doc_ptr, doc_sb = _doc_arg(doc_start, B, T, q.device)
     rc = _lib.lib().daisy_b200_swa_attend(
         q.data_ptr(), k.data_ptr(), v.data_ptr(),
         q.stride(0), q.stride(1), q.stride(2), k.stride(0), k.stride(1), k.stride(2),
         v.stride(0), v.stride(1), v.stride(2), out.data_ptr(),
-        out.stride(0), out.stride(1), out.stride(2), B, T, H, D, int(window or 0), scale,
+        out.stride(0), out.stride(1), out.stride(2), B, T, H, D, int(window or 0), scale, doc_ptr, doc_sb,
         _lib.BOUNDED_QK if bounded_qk else 0, status_word(q.device).data_ptr(), _stream(q))
     _lib.check(rc, "daisy_b200_swa_attend")
     return out
@@ -99,8 +116,8 @@ def swa_attend(q, k, v, window: Optional[int], scale: float = ATTN_SCALE,
 
 def swa_prefill(q, k, v, cos, sin, window: Optional[int], scale: float = ATTN_SCALE, eps: float = 1.1920929e-07,
                 flags: int = QKV_DEFAULT, workspace: Optional[torch.Tensor] = None,
-                out: Optional[torch.Tensor] = None, k_out=None, v_out=None
-                ) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+                out: Optional[torch.Tensor] = None, k_out=None, v_out=None,
+                doc_start: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
     """Raw projections ``[B,T,H,D]`` -> ``(y [B,T,H,D], k' [B,H,T,D], v' [B,H,T,D])``.  Like the reference's
     ``prefill`` the returned k', v' are ``[B,H,T,D]``-shaped views of ``[B,T,H,D]`` memory; pass
     ``k_out``/``v_out`` as ``[B,T,H,D]`` contiguous buffers to reuse storage."""
@@ -120,12 +137,13 @@ def swa_prefill(q, k, v, cos, sin, window: Optional[int], scale: float = ATTN_SC
     if v_out is None:
         v_out = torch.empty(B, T, H, D, dtype=torch.bfloat16, device=q.device)
     assert k_out.shape == (B, T, H, D) and k_out.is_contiguous() and v_out.shape == (B, T, H, D) and v_out.is_contiguous()
+    _doc, doc_ptr, doc_sb = _doc_arg(doc_start, B, T, q.device)
     rc = L.daisy_b200_swa_prefill_fwd(
         q.data_ptr(), k.data_ptr(), v.data_ptr(),
         q.stride(0), q.stride(1), q.stride(2), k.stride(0), k.stride(1), k.stride(2),
         v.stride(0), v.stride(1), v.stride(2), cos.data_ptr(), sin.data_ptr(),
         out.data_ptr(), out.stride(0), out.stride(1), out.stride(2), k_out.data_ptr(), v_out.data_ptr(),
-        B, T, H, D, int(window or 0), scale, eps, flags, workspace.data_ptr(), workspace.numel(),
+        B, T, H, D, int(window or 0), scale, eps, doc_ptr, doc_sb, flags, workspace.data_ptr(), workspace.numel(),
         status_word(q.device).data_ptr(), _stream(q))
     _lib.check(rc, "daisy_b200_swa_prefill_fwd")
     return out, k_out.transpose(1, 2), v_out.transpose(1, 2)

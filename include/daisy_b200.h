@@ -83,9 +83,13 @@ int daisy_b200_qkv_prep(const void* q, const void* k, const void* v,
  * Sliding-window causal softmax attention, prefill form.
  * Replaces CausalSelfAttention._sdpa_common between the two projections
  * (models/daisy/attention.py:141-148) with the mask of build_attn_mask
- * (models/daisy/daisy_core.py:53-69, single document): key k is visible to query q iff
- * 0 <= q - k < window; window <= 0 means plain causal.  Also produces what prefill()
+ * (models/daisy/daisy_core.py:53-69): key k is visible to query q iff 0 <= q - k < window and
+ * both lie in the same document; window <= 0 means plain causal.  Also produces what prefill()
  * returns for the cache (models/daisy/attention.py:173-179).
+ *   doc_start  NULL (one document) or int32: doc_start[b * doc_sb + t] = first position of the document
+ *              of token t, non-decreasing in t; doc_sb = 0 shares one row over the batch.  For the
+ *              reference's numbering (docs = (input_seq == eos).cumsum(0), an EOS token opens the next
+ *              document) that is the position of the last EOS at or before t, else 0.
  *   q,k,v      raw projections, logical [B,T,H,D] with strides as above
  *   out        [B,T,H,D] with strides (o_sb,o_st,o_sh)
  *   k_out,v_out  normalised/rotated k and v; memory order [B,T,H,D] (what the reference returns: a
@@ -102,6 +106,7 @@ int daisy_b200_swa_prefill_fwd(const void* q, const void* k, const void* v,
                                void* out, int64_t o_sb, int64_t o_st, int64_t o_sh,
                                void* k_out, void* v_out,
                                int B, int T, int H, int D, int window, float scale, float eps,
+                               const int32_t* doc_start, int64_t doc_sb,
                                unsigned flags, void* workspace, size_t workspace_bytes,
                                int* status_word, void* stream);
 
@@ -114,6 +119,7 @@ int daisy_b200_swa_attend(const void* q, const void* k, const void* v,
                           int64_t v_sb, int64_t v_st, int64_t v_sh,
                           void* out, int64_t o_sb, int64_t o_st, int64_t o_sh,
                           int B, int T, int H, int D, int window, float scale,
+                          const int32_t* doc_start, int64_t doc_sb,
                           unsigned flags, int* status_word, void* stream);
 
 /* ---------------------------------------------------------------------------------------------

@@ -79,26 +79,43 @@ def qkv_transform(q, k, v, cos_td, sin_td, eps: float, norm_q=True, norm_k=True,
 
 # --------------------------------------------------------------------------- prefill
 
-def window_mask(q_lo: int, q_hi: int, k_lo: int, k_hi: int, window: Optional[int]) -> torch.Tensor:
+def doc_starts(input_seq: torch.Tensor, eos_token_id: int) -> torch.Tensor:
+    """For every position t of ``input_seq [T]`` (or ``[B,T]``) the first position of its document, int32.
+    ``build_attn_mask`` numbers documents ``docs = (input_seq == eos).cumsum(0)``
+    (models/daisy/daisy_core.py:60), so an EOS token opens the next document and belongs to it:
+    document of t = [last EOS position <= t (or 0), next EOS position)."""
+    is_eos = input_seq == eos_token_id
+    pos = torch.arange(input_seq.shape[-1]).expand_as(input_seq)
+    marks = torch.where(is_eos, pos, torch.zeros_like(pos))
+    return torch.cummax(marks, dim=-1).values.to(torch.int32)
+
+
+def window_mask(q_lo: int, q_hi: int, k_lo: int, k_hi: int, window: Optional[int],
+                doc_start: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Additive mask block for query rows [q_lo,q_hi) x key cols [k_lo,k_hi): 0 where
-    ``0 <= q - k < window`` else -inf (models/daisy/daisy_core.py:56-67, single
-    document).  ``window=None`` means plain causal."""
+    ``0 <= q - k < window`` and q, k lie in the same document, else -inf
+    (models/daisy/daisy_core.py:53-69).  ``window=None`` means plain causal; ``doc_start [T]`` (see
+    :func:`doc_starts`) None means one document.  With causality, "same document" is ``k >= doc_start[q]``."""
     qi = torch.arange(q_lo, q_hi)[:, None]
     ki = torch.arange(k_lo, k_hi)[None, :]
     d = qi - ki
     bad = d < 0
     if window is not None:
         bad = bad | (d >= window)
+    if doc_start is not None:
+        bad = bad | (ki < doc_start[q_lo:q_hi].to(torch.int64)[:, None])
     m = torch.zeros(q_hi - q_lo, k_hi - k_lo, dtype=torch.float32)
     m[bad] = float("-inf")
     return m
 
 
-def attend_windowed(q, k, v, window: Optional[int], scale: float = ATTN_SCALE, block: int = 512):
-    """``softmax(scale * q k^T + M) v`` with the window mask, on already
+def attend_windowed(q, k, v, window: Optional[int], scale: float = ATTN_SCALE, block: int = 512,
+                    doc_start: Optional[torch.Tensor] = None):
+    """``softmax(scale * q k^T + M) v`` with the window (and document) mask, on already
     normalised / rotated ``[B, T, H, D]`` tensors (models/daisy/attention.py:141-148).
     Evaluated in blocks of ``block`` query rows against only the keys the mask can
-    admit, which is the same arithmetic as the dense ``[T, T]`` mask."""
+    admit, which is the same arithmetic as the dense ``[T, T]`` mask.  ``doc_start`` is ``[T]`` (shared by the
+    batch, as the reference's single ``input_seq``) or ``[B,T]``."""
     B, T, H, D = q.shape
     qh, kh, vh = (x.permute(0, 2, 1, 3) for x in (q, k, v))       # [B,H,T,D]
     out = torch.empty(B, H, T, D, dtype=q.dtype)
@@ -106,7 +123,11 @@ def attend_windowed(q, k, v, window: Optional[int], scale: float = ATTN_SCALE, b
         q1 = min(T, q0 + block)
         k0 = 0 if window is None else max(0, q0 - window + 1)
         s = torch.matmul(qh[:, :, q0:q1], kh[:, :, k0:q1].transpose(-1, -2)) * scale
-        s = s + window_mask(q0, q1, k0, q1, window).to(s.dtype)
+        if doc_start is not None and doc_start.dim() == 2:
+            m = torch.stack([window_mask(q0, q1, k0, q1, window, doc_start[b]) for b in range(B)])[:, None]
+        else:
+            m = window_mask(q0, q1, k0, q1, window, doc_start)
+        s = s + m.to(s.dtype)
         p = torch.softmax(s, dim=-1)
         out[:, :, q0:q1] = torch.matmul(p, vh[:, :, k0:q1])
     return out.permute(0, 2, 1, 3).contiguous()                   # [B,T,H,D]
@@ -114,12 +135,12 @@ def attend_windowed(q, k, v, window: Optional[int], scale: float = ATTN_SCALE, b
 
 def swa_prefill(q, k, v, cos_td, sin_td, window: Optional[int], scale: float = ATTN_SCALE,
                 eps: float = FP32_EPS, norm_q=True, norm_k=True, norm_v=True, rope=True,
-                block: int = 512):
+                block: int = 512, doc_start: Optional[torch.Tensor] = None):
     """Projection-to-projection part of ``CausalSelfAttention.prefill``
     (models/daisy/attention.py:121-125,141-148,173-179): takes raw projected
     q,k,v ``[B,T,H,D]``, returns ``(y [B,T,H,D], k' [B,H,T,D], v' [B,H,T,D])`` in fp32."""
     qn, kn, vn = qkv_transform(q, k, v, cos_td, sin_td, eps, norm_q, norm_k, norm_v, rope)
-    y = attend_windowed(qn, kn, vn, window, scale, block)
+    y = attend_windowed(qn, kn, vn, window, scale, block, doc_start)
     return y, kn.permute(0, 2, 1, 3).contiguous(), vn.permute(0, 2, 1, 3).contiguous()
 
 
@@ -214,12 +235,12 @@ def project_qkv(x, qkvo_w, num_heads: int, head_dim: int):
 
 
 def csa_prefill(x, qkvo_w, num_heads, head_dim, window, cos_td, sin_td, eps=FP32_EPS,
-                scale=ATTN_SCALE):
+                scale=ATTN_SCALE, doc_start=None):
     """Whole ``CausalSelfAttention.prefill`` with ``ve=None``
     (models/daisy/attention.py:141-150,173-179): returns ``(y [B,T,dim], k', v' [B,H,T,D])``."""
     B, T, dim = x.shape
     q, k, v = project_qkv(x, qkvo_w, num_heads, head_dim)
-    y, kn, vn = swa_prefill(q, k, v, cos_td[:T], sin_td[:T], window, scale, eps)
+    y, kn, vn = swa_prefill(q, k, v, cos_td[:T], sin_td[:T], window, scale, eps, doc_start=doc_start)
     y = torch.matmul(y.reshape(B, T, dim), qkvo_w[3].float().t())
     return y, kn, vn
 

@@ -142,6 +142,27 @@ def kda_case():
                         o=o.numpy(), s=s.numpy(), o_h0=o2.numpy(), s_h0=s2.numpy(), fla_version=fla.__version__)
 
 
+def doc_mask_case():
+    """``build_attn_mask`` with EOS tokens in the sequence (document masking, daisy_core.py:53-69) and the
+    module's ``forward`` under that mask."""
+    torch.manual_seed(5)
+    dim, heads, hd, T, window, eos = 256, 2, 128, 200, 64, 7
+    attn = make_attn(dim, heads, hd, seed=5)
+    g = torch.Generator().manual_seed(6)
+    seq = torch.randint(8, 100, (1, T), generator=g)
+    for p in (0, 1, 40, 41, 90, 150, 199):
+        seq[0, p] = eos
+    x = torch.randn(1, T, dim, generator=g)
+    mask = build_attn_mask(seq, window, eos)
+    with torch.no_grad():
+        y = attn(x, None, attn_mask=mask)
+    np.savez_compressed(os.path.join(HERE, "doc_mask_small.npz"),
+                        seq=seq.numpy(), eos=np.int64(eos), window=np.int64(window), x=x.numpy(),
+                        qkvo_w=attn.qkvo_w.detach().numpy(), mask=mask[0, 0].numpy(), y=y.numpy(),
+                        cos=attn.rotary.cos[:T].numpy(), sin=attn.rotary.sin[:T].numpy())
+    print("doc_mask_small", tuple(y.shape))
+
+
 def kda_gate_case():
     """``fused_kda_gate`` as the KDA layer calls it (attention_kimi.py:132), through the reference's own
     pure-PyTorch implementation ``_gate_impl`` (fla_custom_ops.py:71-103): fp32 and bf16 inputs, with the
@@ -168,6 +189,7 @@ if __name__ == "__main__":
     swa_inner_case()
     kda_case()
     kda_gate_case()
+    doc_mask_case()
     for f in sorted(os.listdir(HERE)):
         if f.endswith(".npz"):
             print(f, os.path.getsize(os.path.join(HERE, f)))

@@ -52,16 +52,16 @@ def test_argument_validation_without_gpu(lib):
     assert lib.daisy_b200_qkv_prep(a, a, a, 0, 0, 0, 0, 0, 0, 0, 0, 0, a, a, a, a, a, 1, 1, 1, 64, 1e-6, 15, None) == _lib.EUNSUPPORTED
     # null pointers / bad sizes
     assert lib.daisy_b200_qkv_prep(None, None, None, 0, 0, 0, 0, 0, 0, 0, 0, 0, a, a, None, None, None, 1, 1, 1, 128, 1e-6, 15, None) == _lib.EINVAL
-    assert lib.daisy_b200_swa_attend(None, a, a, 0, 0, 0, 0, 0, 0, 0, 0, 0, a, 0, 0, 0, 1, 1, 1, 128, 0, 0.12, 0, None, None) == _lib.EINVAL
-    assert lib.daisy_b200_swa_attend(a, a, a, 128, 128, 128, 128, 128, 128, 128, 128, 128, a, 128, 128, 128, 1, 1, 1, 128, 0, -1.0, 0, None, None) == _lib.EINVAL
+    assert lib.daisy_b200_swa_attend(None, a, a, 0, 0, 0, 0, 0, 0, 0, 0, 0, a, 0, 0, 0, 1, 1, 1, 128, 0, 0.12, None, 0, 0, None, None) == _lib.EINVAL
+    assert lib.daisy_b200_swa_attend(a, a, a, 128, 128, 128, 128, 128, 128, 128, 128, 128, a, 128, 128, 128, 1, 1, 1, 128, 0, -1.0, None, 0, 0, None, None) == _lib.EINVAL
     # misaligned pointer / stride
-    assert lib.daisy_b200_swa_attend(a + 2, a, a, 128, 128, 128, 128, 128, 128, 128, 128, 128, a, 128, 128, 128, 1, 1, 1, 128, 0, 0.12, 0, None, None) == _lib.EALIGN
-    assert lib.daisy_b200_swa_attend(a, a, a, 128, 132, 128, 128, 128, 128, 128, 128, 128, a, 128, 128, 128, 1, 1, 1, 128, 0, 0.12, 0, None, None) == _lib.EALIGN
+    assert lib.daisy_b200_swa_attend(a + 2, a, a, 128, 128, 128, 128, 128, 128, 128, 128, 128, a, 128, 128, 128, 1, 1, 1, 128, 0, 0.12, None, 0, 0, None, None) == _lib.EALIGN
+    assert lib.daisy_b200_swa_attend(a, a, a, 128, 132, 128, 128, 128, 128, 128, 128, 128, a, 128, 128, 128, 1, 1, 1, 128, 0, 0.12, None, 0, 0, None, None) == _lib.EALIGN
     # workspace too small
     need = lib.daisy_b200_swa_prefill_workspace_bytes(1, 128, 2, 128)
     assert need == 3 * 128 * 2 * 128 * 2
     assert lib.daisy_b200_swa_prefill_fwd(a, a, a, 256, 256, 128, 256, 256, 128, 256, 256, 128, a, a, a, 256, 256, 128, None, None,
-                                          1, 128, 2, 128, 64, 0.12, 1e-6, 15, a, need - 1, None, None) == _lib.EWORKSPACE
+                                          1, 128, 2, 128, 64, 0.12, 1e-6, None, 0, 15, a, need - 1, None, None) == _lib.EWORKSPACE
     # decode: workspace, D, negative t
     w = lib.daisy_b200_swa_decode_workspace_bytes(2, 3, 128, 4)
     assert w == 2 * 3 * 4 * 130 * 4

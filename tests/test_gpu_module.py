@@ -237,3 +237,22 @@ def test_host_buffer_prefill_equals_device_call():
         torch.cuda.synchronize()
         assert torch.equal(hout, y_dev.cpu())
         assert torch.equal(hk_out.transpose(1, 2), k_dev.cpu())
+
+
+def test_forward_with_eos_document_mask_matches_reference_fixture(golden_dir):
+    """``forward`` under ``build_attn_mask`` with EOS tokens in the sequence (document masking),
+    against the reference module's own output."""
+    import numpy as np
+    from daisy_b200 import B200CausalSelfAttention, WindowMask
+    d = np.load(os.path.join(golden_dir, "doc_mask_small.npz"))
+    x = torch.from_numpy(d["x"])
+    attn = B200CausalSelfAttention(dim=256, num_heads=2, head_dim=128, max_seq_len=256).cuda()
+    with torch.no_grad():
+        attn.qkvo_w.copy_(torch.from_numpy(d["qkvo_w"]).to(attn.qkvo_w.dtype))
+    seq = torch.from_numpy(d["seq"]).cuda()
+    mask = WindowMask.from_tokens(seq, int(d["window"]), int(d["eos"]))
+    y = attn(x.cuda().bfloat16(), None, attn_mask=mask)
+    ref = torch.from_numpy(d["y"])
+    err = (y.float().cpu() - ref).abs()
+    scale = max(1.0, ref.abs().max().item())
+    assert err.max().item() <= 4e-2 * scale and err.mean().item() <= 4e-3 * scale

@@ -128,3 +128,43 @@ def test_q_prepared_in_kernel_matches(T, window):
     y2, _, _ = ops.swa_prefill(q, k, v, cos.cuda(), sin.cuda(), window, flags=_lib.Q_IN_KERNEL)
     y2r = swa.attend_windowed(q.float().cpu(), k.float().cpu(), v.float().cpu(), window)
     assert_close_bf16(y2, y2r, "no transform")
+
+
+def _random_doc_starts(B, T, n_docs, seed, per_batch):
+    g = torch.Generator().manual_seed(seed)
+    rows = []
+    for _ in range(B if per_batch else 1):
+        cuts = torch.randperm(max(T - 1, 1), generator=g)[:n_docs].sort().values + (1 if T > 1 else 0)
+        ds = torch.zeros(T, dtype=torch.int32)
+        for c in cuts.tolist():
+            if c < T:
+                ds[c:] = c
+        rows.append(ds)
+    return torch.stack(rows) if per_batch else rows[0]
+
+
+@pytest.mark.parametrize("T,window,n_docs,per_batch", [(9, 4, 2, False), (300, 64, 5, True), (520, None, 3, False),
+                                                        (1300, 512, 4, True), (2100, 1024, 7, True),
+                                                        (700, 300, 40, False)])
+def test_document_mask_matches_oracle(T, window, n_docs, per_batch):
+    """Keys before the start of the query's document are invisible (the EOS document mask of
+    build_attn_mask); documents start at arbitrary positions, also inside a tile and per batch row."""
+    from daisy_b200 import ops
+    B, H = 2, 3
+    qkv = bf16_randn(B, T, 3 * H, D, seed=T)
+    q, k, v = qkv.chunk(3, dim=-2)
+    cos, sin = swa.rope_tables(D, T)
+    ds = _random_doc_starts(B, T, n_docs, seed=T + 1, per_batch=per_batch)
+    y_ref, _, _ = swa.swa_prefill(q.float().cpu(), k.float().cpu(), v.float().cpu(), cos, sin, window, doc_start=ds)
+    y, _, _ = ops.swa_prefill(q, k, v, cos.cuda(), sin.cuda(), window, doc_start=ds.cuda())
+    ops.check_device_status(q.device)
+    assert_close_bf16(y, y_ref, "doc mask, fused step")
+    # the attention core alone, both kernels
+    qp, kp, vp = ops.qkv_prep(q, k, v, cos.cuda(), sin.cuda(), swa.FP32_EPS)
+    for bounded in (True, False):
+        ya = ops.swa_attend(qp, kp, vp, window, bounded_qk=bounded, doc_start=ds.cuda())
+        assert_close_bf16(ya, y_ref, f"doc mask, attend bounded={bounded}")
+    # and the mask really bites: without it the result differs
+    y_nodoc, _, _ = ops.swa_prefill(q, k, v, cos.cuda(), sin.cuda(), window)
+    assert (y_nodoc.float() - y.float()).abs().max().item() > 1e-2
+    ops.check_device_status(q.device)

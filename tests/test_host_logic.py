@@ -39,7 +39,11 @@ def test_module_construction_and_mask_parsing(monkeypatch):
     assert m.attn_scale == 0.12 and m.num_heads == 2 and m.head_dim == 128
     cos, sin = swa.rope_tables(128, 64)
     assert torch.equal(m.rotary.cos, cos) and torch.equal(m.rotary.sin, sin)
-    assert m._window_of(None) is None and m._window_of(WindowMask(5)) == 5 and m._window_of(7) == 7
+    assert m._window_of(None) == (None, None) and m._window_of(WindowMask(5)) == (5, None) and m._window_of(7) == (7, None)
+    from daisy_b200.attention import doc_starts
+    seq = torch.tensor([[3, 9, 4, 4, 9, 9, 2]])
+    assert doc_starts(seq, 9).tolist() == [0, 1, 1, 1, 4, 5, 5]              # an EOS opens the next document
+    assert WindowMask.from_tokens(seq, 4, 9).doc_start.tolist() == [0, 1, 1, 1, 4, 5, 5]
     with pytest.raises(TypeError):
         m._window_of(torch.zeros(1, 1, 4, 4))
     with pytest.raises(Exception):

@@ -133,3 +133,17 @@ def test_kda_gate_against_reference_fixture(golden_dir):
         assert got.shape == ref.shape and ((got - ref).abs() <= 1e-6 * ref.abs() + 1e-7).all()
     got = kda.kda_gate(x.bfloat16(), A, 128, bias)
     assert got.dtype == torch.bfloat16 and torch.equal(got.float(), torch.from_numpy(d["y_bf16_as_fp32"]))
+
+
+def test_document_mask_against_reference_fixture(golden_dir):
+    """oracle window_mask / doc_starts / csa_prefill vs ``build_attn_mask`` with EOS tokens
+    (models/daisy/daisy_core.py:53-69) and the module's forward under that mask."""
+    d = np.load(os.path.join(golden_dir, "doc_mask_small.npz"))
+    seq = torch.from_numpy(d["seq"])[0]
+    T, W = seq.numel(), int(d["window"])
+    ds = swa.doc_starts(seq, int(d["eos"]))
+    assert torch.equal(swa.window_mask(0, T, 0, T, W, ds), torch.from_numpy(d["mask"]))
+    assert torch.equal(swa.window_mask(10, 90, 3, 77, W, ds), torch.from_numpy(d["mask"])[10:90, 3:77])
+    y, _, _ = swa.csa_prefill(torch.from_numpy(d["x"]), torch.from_numpy(d["qkvo_w"]), 2, 128, W,
+                              torch.from_numpy(d["cos"]), torch.from_numpy(d["sin"]), doc_start=ds)
+    assert (y - torch.from_numpy(d["y"])).abs().max().item() < 1e-5
