@@ -26,6 +26,20 @@ extern "C" int daisy_b200_sm_count(void) {
 
 namespace daisy_host {
 
+int device_slot() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) { (void)cudaGetLastError(); return -1; }
+  return (dev >= 0 && dev < MAX_DEVICES) ? dev : -1;
+}
+
+int sm_count_cached() {
+  static int sms[MAX_DEVICES] = {};
+  const int d = device_slot();
+  if (d < 0) return 0;
+  if (sms[d] <= 0) sms[d] = daisy_b200_sm_count();
+  return sms[d];
+}
+
 EncodeTiledFn get_encode_tiled() {
   static EncodeTiledFn fn = nullptr;
   if (fn) return fn;

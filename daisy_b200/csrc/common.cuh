@@ -336,6 +336,13 @@ __device__ __forceinline__ bool elect_one() {
 // ---------------------------------------------------------------------- host: tensor maps
 namespace daisy_host {
 
+// Per-device host state (kernel attributes are per device; a process may drive several).
+constexpr int MAX_DEVICES = 64;
+// Index of the current device into such tables, or -1.
+int device_slot();
+// SM count of the current device, cached per device; 0 if there is none.
+int sm_count_cached();
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);

@@ -764,10 +764,12 @@ extern "C" size_t daisy_b200_kda_workspace_bytes(int B, int T, int H, int K, int
 template <int NW>
 static int launch_state(const KdaStateParams& sp, int BH, cudaStream_t st) {
   using L = KdaStateSmem<NW>;
-  static bool attr = false;
-  if (!attr) {
+  static bool attr[daisy_host::MAX_DEVICES] = {};             // the attribute is per device
+  const int dev = daisy_host::device_slot();
+  if (dev < 0) return DAISY_ENODEV;
+  if (!attr[dev]) {
     if (cudaFuncSetAttribute(kda_state_kernel<NW>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::BYTES) != cudaSuccess) return DAISY_ECUDA;
-    attr = true;
+    attr[dev] = true;
   }
   kda_state_kernel<NW><<<dim3(KD / L::VS, BH), 32 * (NW + 1), L::BYTES, st>>>(sp);
   return cudaGetLastError() == cudaSuccess ? DAISY_OK : DAISY_ECUDA;
@@ -787,13 +789,15 @@ extern "C" int daisy_b200_kda_chunk_fwd(const void* q, const void* k, const void
     return DAISY_EALIGN;
   cudaStream_t st = (cudaStream_t)stream;
   const int NC = (T + KC - 1) / KC;
-  static bool attr = false;
-  if (!attr) {
+  static bool attr[daisy_host::MAX_DEVICES] = {};             // the attribute is per device
+  const int dev = daisy_host::device_slot();
+  if (dev < 0) return DAISY_ENODEV;
+  if (!attr[dev]) {
     if (cudaFuncSetAttribute(kda_intra_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(KdaIntraSmem)) != cudaSuccess) {
       (void)cudaGetLastError();
       return DAISY_ECUDA;
     }
-    attr = true;
+    attr[dev] = true;
   }
   KdaIntraParams ip;
   ip.q = (const __nv_bfloat16*)q; ip.k = (const __nv_bfloat16*)k; ip.v = (const __nv_bfloat16*)v;
@@ -802,8 +806,7 @@ extern "C" int daisy_b200_kda_chunk_fwd(const void* q, const void* k, const void
   ip.scale = scale > 0.f ? scale : 1.0f / sqrtf((float)K);
   ip.l2norm = (flags & DAISY_KDA_L2NORM_QK) ? 1 : 0;
   {
-    static int sms = 0;
-    if (sms <= 0) sms = daisy_b200_sm_count();
+    const int sms = daisy_host::sm_count_cached();
     ip.ahead = sms > 0 ? sms : 148;
   }
   kda_intra_kernel<<<dim3(NC, H, B), KDA_INTRA_THREADS, sizeof(KdaIntraSmem), st>>>(ip);

@@ -1,18 +1,20 @@
 // Sliding-window causal softmax attention, prefill form, on tcgen05 tensor cores.
 //
 // One CTA owns 256 consecutive query rows of one (batch, head): two 128-row streams that share
-// every K/V tile.  Roles (320 threads):
+// every K/V tile.  Roles, general form (NSPLIT = 1, 320 threads):
 //   warps 0-3   softmax of stream 0 (thread = query row = TMEM lane)
 //   warps 4-7   softmax of stream 1
-//   warp  8     TMA producer: Q tiles once, then K_j, V_j tiles into a ring of 32 KB buffers
-//   warp  9     MMA issuer (one thread): S_s = Q_s K_j^T (smem x smem), O_s += P_s V_j (TMEM x smem)
+//   warp  8     TMA producer: Q tiles one item ahead, then K_j, V_j tiles into a ring of 32 KB buffers
+//   warp  9     MMA issuer (one elected lane): S_s = Q_s K_j^T (smem x smem), O_s += P_s V_j (TMEM x smem)
+// Bounded-logit form (NSPLIT = 2, 576 threads): warps 0-15 are two softmax warpgroups per stream, 64 key
+// columns each; warp 16 producer, warp 17 issuer (see the comment above the kernel).
 // TMEM (512 columns): S_0 [0,128) S_1 [128,256) O_0 [256,384) O_1 [384,512), fp32.  P_s (bf16,
-// two keys per column) overwrites the first 64 columns of S_s once S_s has been read.
-// Softmax is online in the exp2 domain with a lazily refreshed reference maximum: the accumulator
-// is rescaled only when the running maximum has grown by more than 8 (a factor 256), so most
-// iterations touch O only through the tensor core.  KV tiles wholly outside the window are never
-// loaded; the two partially visible tile classes (causal diagonal, trailing window edge) go through
-// the same element-wise predicate 0 <= q - k < window.
+// two keys per column) overwrites columns of S_s once they have been read.
+// General form: softmax is online in the exp2 domain with a lazily refreshed reference maximum: the
+// accumulator is rescaled only when the running maximum has grown by more than 8 (a factor 256), so most
+// iterations touch O only through the tensor core.  KV tiles wholly outside the window, or wholly before
+// the document of the block's first query, are never loaded; the partially visible tiles (causal diagonal,
+// trailing window edge, a document boundary) go through one element-wise predicate.
 // All mbarrier waits are bounded; a wait that runs out raises an abort flag that every role polls,
 // the CTA drains to its teardown, frees TMEM and reports DAISY_ETIMEOUT through the status word.
 #include "common.cuh"
@@ -116,6 +118,56 @@ __device__ __forceinline__ ItemGeom item_geom(int item, int nq, int H, int T, in
   return g;
 }
 
+// Raw-Q mode: RMS norm over the row and half-rotation RoPE at position `qrow`, in place in the 128-byte-
+// swizzled Q tile (thread = row; chunk c of row r sits at r*128 + ((c ^ r) & 7)*16 of box c >> 3).  Called by
+// the 128 threads that own the rows of stream s, between two softmax tiles; signals q_ready.
+__device__ __forceinline__ bool prepare_q_tile(PrefillBarriers* bars, uint8_t* q_tiles, int s, int row, uint32_t& n_qs,
+                                               int qrow, const PrefillParams& p, volatile int* abort_flag) {
+  const uint32_t qb = n_qs % NQBUF;
+  if (!__all_sync(0xffffffffu, mbar_wait(&bars->q_full[s][qb], (n_qs / NQBUF) & 1, abort_flag, p.status, 12))) return false;
+  ++n_qs;
+  uint8_t* qt = q_tiles + (qb * 2 + s) * TILE_BYTES + row * 128;
+  const int sw = row & 7;
+  // two passes over the row in shared memory (sum of squares, then rotate) keep the live registers few
+  float ss = 0.f;
+#pragma unroll 4
+  for (int c = 0; c < 16; ++c) {
+    float f[8];
+    unpack8(*reinterpret_cast<const uint4*>(qt + (c >> 3) * HALF_BYTES + (((c & 7) ^ sw) << 4)), f);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) ss = fmaf(f[e], f[e], ss);
+  }
+  const float rs = p.q_norm ? rsqrtf(ss * (1.0f / DAISY_HEAD_DIM) + p.eps) : 1.f;
+  const int pos = min(qrow, p.T - 1);
+  const float* cr = p.cos + (int64_t)pos * 64;
+  const float* sr = p.sin + (int64_t)pos * 64;
+#pragma unroll 2
+  for (int c = 0; c < 8; ++c) {
+    float x1[8], x2[8];
+    unpack8(*reinterpret_cast<const uint4*>(qt + (((c & 7) ^ sw) << 4)), x1);
+    unpack8(*reinterpret_cast<const uint4*>(qt + HALF_BYTES + (((c & 7) ^ sw) << 4)), x2);
+    float cs[8] = {1.f, 1.f, 1.f, 1.f, 1.f, 1.f, 1.f, 1.f}, sn[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    if (p.q_rope) {
+      const float4 c0 = *reinterpret_cast<const float4*>(cr + 8 * c), c1 = *reinterpret_cast<const float4*>(cr + 8 * c + 4);
+      const float4 s0 = *reinterpret_cast<const float4*>(sr + 8 * c), s1 = *reinterpret_cast<const float4*>(sr + 8 * c + 4);
+      cs[0] = c0.x; cs[1] = c0.y; cs[2] = c0.z; cs[3] = c0.w; cs[4] = c1.x; cs[5] = c1.y; cs[6] = c1.z; cs[7] = c1.w;
+      sn[0] = s0.x; sn[1] = s0.y; sn[2] = s0.z; sn[3] = s0.w; sn[4] = s1.x; sn[5] = s1.y; sn[6] = s1.z; sn[7] = s1.w;
+    }
+    float y1[8], y2[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      const float a = x1[e] * rs, b2 = x2[e] * rs;
+      y1[e] = a * cs[e] + b2 * sn[e];
+      y2[e] = b2 * cs[e] - a * sn[e];
+    }
+    *reinterpret_cast<uint4*>(qt + (((c & 7) ^ sw) << 4)) = pack8(y1);
+    *reinterpret_cast<uint4*>(qt + HALF_BYTES + (((c & 7) ^ sw) << 4)) = pack8(y2);
+  }
+  fence_proxy_async();                                              // generic-proxy writes -> visible to the MMA's reads
+  mbar_arrive(&bars->q_ready[s][qb]);
+  return true;
+}
+
 // Persistent: CTA c walks items c, c + gridDim.x, ...; item = (batch*H + head) * nq + q-pair, so the CTAs
 // running at any moment share a handful of (batch, head) K/V streams in L2.  Barrier phases are kept as
 // running counters per role, so the K/V ring, the Q buffers and the TMEM accumulators carry over from
@@ -138,7 +190,7 @@ swa_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
   PrefillBarriers* bars = reinterpret_cast<PrefillBarriers*>(smem + SMEM_TILES);
   volatile int* abort_flag = &bars->abort_flag;
 
-  static_assert(NSPLIT == 1 || (NSPLIT == 2 && BOUNDED && !QRAW), "the split softmax needs bounded logits and a prepared Q");
+  static_assert(NSPLIT == 1 || (NSPLIT == 2 && BOUNDED), "the split softmax needs bounded logits");
   constexpr int TMA_WARP = 8 * NSPLIT, MMA_WARP = 8 * NSPLIT + 1;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int T = p.T, window = p.window;
@@ -304,8 +356,9 @@ swa_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     const uint32_t o_tmem = tmem_base + lane_off + 256 + s * 128 + half * 64;    // and its 64 output columns in the epilogue
     float* lsum = reinterpret_cast<float*>(smem + SMEM_TILES + 256) + s * 128 + row;   // one exchange slot per row
     const uint64_t c2p = pack2f(p.scale_log2, p.scale_log2);
-    uint32_t n_s = 0, n_o = 0;
+    uint32_t n_s = 0, n_o = 0, n_qs = 0;
     bool ok = true;
+    bool q_prepared = false;                                       // raw-Q mode: the lower half prepares the stream's Q rows
     PT_DECL;
     PT_START();
     for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
@@ -313,6 +366,21 @@ swa_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       if (!g.valid[s]) continue;
       const int q0 = g.q0[s];
       const int q_row = q0 + row;
+      bool next_valid = false;
+      int q_row_next = 0;
+      if (QRAW && half == 0) {
+        if (!q_prepared) {
+          ok = prepare_q_tile(bars, q_tiles, s, row, n_qs, q_row, p, abort_flag);
+          if (!ok) break;
+        }
+        q_prepared = false;
+        const int item_next = item + gridDim.x;
+        if (item_next < n_items) {
+          const ItemGeom gn = item_geom(item_next, nq, p.H, T, window, p.doc_start, p.doc_sb);
+          next_valid = gn.valid[s];
+          q_row_next = gn.q0[s] + row;
+        }
+      }
       uint64_t sum_a = pack2f(0.f, 0.f), sum_b = sum_a;
       // first visible key of this row's document, and the latest such start among the stream's rows
       const int ds_row = p.doc_start ? p.doc_start[g.b * p.doc_sb + min(q_row, T - 1)] : 0;
@@ -370,6 +438,11 @@ swa_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         tc_fence_before();
         mbar_arrive(&bars->p_full[s]);
         PT_LAP(4);
+        if (QRAW && half == 0 && next_valid && !q_prepared && j == g.jlo_s[s] + 1) {   // next item's Q, inside this item
+          ok = prepare_q_tile(bars, q_tiles, s, row, n_qs, q_row_next, p, abort_flag);
+          if (!ok) break;
+          q_prepared = true;
+        }
       }
       float l;
       {
@@ -452,55 +525,7 @@ swa_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     bool ok = true;
     uint32_t r[128];
     bool q_prepared = false;
-    // Raw-Q mode: RMS norm over the row and half-rotation RoPE at position `qrow`, in place in the 128-byte-
-    // swizzled Q tile (thread = row; chunk c of row r sits at r*128 + ((c ^ r) & 7)*16 of box c >> 3).  Uses
-    // the S register buffer as scratch, so it runs between two softmax tiles.
-    auto prepare_q = [&](int qrow) -> bool {
-      const uint32_t qb = n_qs % NQBUF;
-      if (!__all_sync(0xffffffffu, mbar_wait(&bars->q_full[s][qb], (n_qs / NQBUF) & 1, abort_flag, p.status, 12))) return false;
-      ++n_qs;
-      uint8_t* qt = q_tiles + (qb * 2 + s) * TILE_BYTES + row * 128;
-      const int sw = row & 7;
-      uint4* rq = reinterpret_cast<uint4*>(r);
-      float ss = 0.f;
-#pragma unroll
-      for (int c = 0; c < 16; ++c) {
-        rq[c] = *reinterpret_cast<const uint4*>(qt + (c >> 3) * HALF_BYTES + (((c & 7) ^ sw) << 4));
-        float f[8];
-        unpack8(rq[c], f);
-#pragma unroll
-        for (int e = 0; e < 8; ++e) ss = fmaf(f[e], f[e], ss);
-      }
-      const float rs = p.q_norm ? rsqrtf(ss * (1.0f / DAISY_HEAD_DIM) + p.eps) : 1.f;
-      const int pos = min(qrow, T - 1);
-      const float* cr = p.cos + (int64_t)pos * 64;
-      const float* sr = p.sin + (int64_t)pos * 64;
-#pragma unroll
-      for (int c = 0; c < 8; ++c) {
-        float x1[8], x2[8];
-        unpack8(rq[c], x1);
-        unpack8(rq[c + 8], x2);
-        float cs[8] = {1.f, 1.f, 1.f, 1.f, 1.f, 1.f, 1.f, 1.f}, sn[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-        if (p.q_rope) {
-          const float4 c0 = *reinterpret_cast<const float4*>(cr + 8 * c), c1 = *reinterpret_cast<const float4*>(cr + 8 * c + 4);
-          const float4 s0 = *reinterpret_cast<const float4*>(sr + 8 * c), s1 = *reinterpret_cast<const float4*>(sr + 8 * c + 4);
-          cs[0] = c0.x; cs[1] = c0.y; cs[2] = c0.z; cs[3] = c0.w; cs[4] = c1.x; cs[5] = c1.y; cs[6] = c1.z; cs[7] = c1.w;
-          sn[0] = s0.x; sn[1] = s0.y; sn[2] = s0.z; sn[3] = s0.w; sn[4] = s1.x; sn[5] = s1.y; sn[6] = s1.z; sn[7] = s1.w;
-        }
-        float y1[8], y2[8];
-#pragma unroll
-        for (int e = 0; e < 8; ++e) {
-          const float a = x1[e] * rs, b2 = x2[e] * rs;
-          y1[e] = a * cs[e] + b2 * sn[e];
-          y2[e] = b2 * cs[e] - a * sn[e];
-        }
-        *reinterpret_cast<uint4*>(qt + (((c & 7) ^ sw) << 4)) = pack8(y1);
-        *reinterpret_cast<uint4*>(qt + HALF_BYTES + (((c & 7) ^ sw) << 4)) = pack8(y2);
-      }
-      fence_proxy_async();                                              // generic-proxy writes -> visible to the MMA's reads
-      mbar_arrive(&bars->q_ready[s][qb]);
-      return true;
-    };
+    auto prepare_q = [&](int qrow) -> bool { return prepare_q_tile(bars, q_tiles, s, row, n_qs, qrow, p, abort_flag); };
     PT_DECL;
     PT_START();
     for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
@@ -786,15 +811,18 @@ extern "C" void daisy_b200_prefill_clk_dump(long long* out, void* stream) { pref
 #endif
 
 static int ensure_smem_attr() {
-  static bool done = false;
-  if (done) return DAISY_OK;
+  static bool done[daisy_host::MAX_DEVICES] = {};             // the attribute is per device
+  const int dev = daisy_host::device_slot();
+  if (dev < 0) return DAISY_ENODEV;
+  if (done[dev]) return DAISY_OK;
   if (cudaFuncSetAttribute(swa_prefill_kernel<false, false, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, PREFILL_SMEM) != cudaSuccess) return DAISY_ECUDA;
   if (cudaFuncSetAttribute(swa_prefill_kernel<false, true, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, PREFILL_SMEM) != cudaSuccess) return DAISY_ECUDA;
   if (cudaFuncSetAttribute(swa_prefill_kernel<false, true, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, PREFILL_SMEM) != cudaSuccess) return DAISY_ECUDA;
   if (cudaFuncSetAttribute(swa_prefill_kernel<true, false, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, PREFILL_SMEM) != cudaSuccess) return DAISY_ECUDA;
   if (cudaFuncSetAttribute(swa_prefill_kernel<true, true, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, PREFILL_SMEM) != cudaSuccess) return DAISY_ECUDA;
+  if (cudaFuncSetAttribute(swa_prefill_kernel<true, true, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, PREFILL_SMEM) != cudaSuccess) return DAISY_ECUDA;
   if (cudaFuncSetAttribute(umma_selftest_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 1024 + 2 * TILE_BYTES + 64) != cudaSuccess) return DAISY_ECUDA;
-  done = true;
+  done[dev] = true;
   return DAISY_OK;
 }
 
@@ -816,7 +844,7 @@ static int launch_attend(const void* q, const void* k, const void* v,
   if (qt && qt->rope && (!qt->cos || !qt->sin)) return DAISY_EINVAL;
   if (doc_start && (doc_sb < 0 || (reinterpret_cast<uintptr_t>(doc_start) & 3))) return DAISY_EINVAL;
   if (qt && qt->rope && (!daisy_aligned16(qt->cos) || !daisy_aligned16(qt->sin))) return DAISY_EALIGN;
-  if (ensure_smem_attr() != DAISY_OK) { (void)cudaGetLastError(); return DAISY_ECUDA; }
+  if (const int arc = ensure_smem_attr(); arc != DAISY_OK) { (void)cudaGetLastError(); return arc; }
   CUtensorMap tq, tk, tv;
   int rc;
   // a size-1 dimension may come with any stride; the encoder wants a non-zero multiple of 16 bytes
@@ -834,8 +862,7 @@ static int launch_attend(const void* q, const void* k, const void* v,
   p.eps = qt ? qt->eps : 0.f; p.q_norm = qt ? qt->norm : 0; p.q_rope = qt ? qt->rope : 0;
   const int64_t items = (int64_t)((T + 2 * BM - 1) / (2 * BM)) * H * B;
   if (items >= (int64_t)1 << 31) return DAISY_EUNSUPPORTED;
-  static int sms = 0;                      // one process drives one device
-  if (sms <= 0) sms = daisy_b200_sm_count();
+  const int sms = daisy_host::sm_count_cached();
   if (sms <= 0) return DAISY_ENODEV;
   dim3 grid((unsigned)(items < sms ? items : sms), 1, 1);
   const bool raw = qt && (qt->norm || qt->rope);
@@ -844,7 +871,8 @@ static int launch_attend(const void* q, const void* k, const void* v,
   cudaStream_t st = (cudaStream_t)stream;
   static int split = -1;                   // DAISY_PREFILL_SPLIT=0 keeps one softmax warpgroup per stream
   if (split < 0) { const char* e = getenv("DAISY_PREFILL_SPLIT"); split = e ? atoi(e) : 1; }
-  if (raw && bounded)       swa_prefill_kernel<true, true, 1><<<grid, PREFILL_THREADS, PREFILL_SMEM, st>>>(tq, tk, tv, p);
+  if (raw && bounded && split) swa_prefill_kernel<true, true, 2><<<grid, PREFILL_THREADS_SPLIT, PREFILL_SMEM, st>>>(tq, tk, tv, p);
+  else if (raw && bounded)  swa_prefill_kernel<true, true, 1><<<grid, PREFILL_THREADS, PREFILL_SMEM, st>>>(tq, tk, tv, p);
   else if (raw)             swa_prefill_kernel<true, false, 1><<<grid, PREFILL_THREADS, PREFILL_SMEM, st>>>(tq, tk, tv, p);
   else if (bounded && split) swa_prefill_kernel<false, true, 2><<<grid, PREFILL_THREADS_SPLIT, PREFILL_SMEM, st>>>(tq, tk, tv, p);
   else if (bounded)         swa_prefill_kernel<false, true, 1><<<grid, PREFILL_THREADS, PREFILL_SMEM, st>>>(tq, tk, tv, p);
@@ -896,8 +924,9 @@ extern "C" int daisy_b200_swa_prefill_fwd(const void* q, const void* k, const vo
   // K and V are prepared once (they are outputs anyway: the cache rows) and keep the [B,T,H,D] memory order
   // of the projections, a pure streaming pass.  Q is either prepared in the same pass (default) or, with
   // DAISY_Q_IN_KERNEL, consumed raw: the attention kernel then normalises and rotates each Q tile in shared
-  // memory one item ahead of its use.  Measured on C2 the in-kernel form is slower (1.46 ms vs 1.33 ms per
-  // step: the transform competes with the softmax warps for issue slots and L2 latency), so it is opt-in.
+  // memory one item ahead of its use.  Measured on C2 the in-kernel form is slower (1.22 ms vs 1.18 ms per
+  // step, 3.69 vs 3.45 ms at C4: the transform sits on the softmax warps, whose P the tensor pipe waits for),
+  // so it is opt-in.
   const bool q_in_kernel = (flags & DAISY_Q_IN_KERNEL) != 0;
   const bool bounded_qk = (flags & DAISY_NORM_Q) && (flags & DAISY_NORM_K);
   void* qp = ws;
@@ -936,7 +965,7 @@ extern "C" int daisy_b200_swa_prefill_fwd(const void* q, const void* k, const vo
 extern "C" int daisy_b200_selftest_umma(const void* a, const void* b, float* c, int K, int mode,
                                         int* status_word, void* stream) {
   if (!a || !b || !c || (K != 64 && K != 128) || mode < 0 || mode > 2) return DAISY_EINVAL;
-  if (ensure_smem_attr() != DAISY_OK) { (void)cudaGetLastError(); return DAISY_ECUDA; }
+  if (const int arc = ensure_smem_attr(); arc != DAISY_OK) { (void)cudaGetLastError(); return arc; }
   CUtensorMap ta, tb;
   int rc;
   if ((rc = daisy_host::make_tmap_bf16_3d(&ta, a, K, 128, 1, (uint64_t)K * 2, (uint64_t)K * 256, 64, 128)) != DAISY_OK) return rc;
