@@ -23,7 +23,7 @@ SIGNATURES = {
     "daisy_b200_version": (_i, []),
     "daisy_b200_strerror": (C.c_char_p, [_i]),
     "daisy_b200_sm_count": (_i, []),
-    "daisy_b200_qkv_prep": (_i, [_vp] * 3 + [_i64] * 9 + [_vp] * 2 + [_vp] * 3 + [_i] * 4 + [_f, _u, _vp]),
+    "daisy_b200_qkv_prep": (_i, [_vp] * 3 + [_i64] * 9 + [_vp] * 2 + [_vp] * 3 + [_vp] + [_i64] * 3 + [_vp] + [_i] * 4 + [_f, _u, _vp]),
     "daisy_b200_swa_prefill_workspace_bytes": (_sz, [_i] * 4),
     "daisy_b200_swa_prefill_fwd": (_i, [_vp] * 3 + [_i64] * 9 + [_vp] * 2 + [_vp] + [_i64] * 3 + [_vp] * 2 +
                                    [_i] * 5 + [_f, _f, _vp, _i64, _u, _vp, _sz, _vp, _vp]),

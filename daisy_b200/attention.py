@@ -139,9 +139,10 @@ class B200CausalSelfAttention(nn.Module):
         cos, sin = self.rotary.tables(T)
         if self.receives_ve:
             torch._assert(ve is not None, "ve must be provided when receives_ve=True")
-            qp, kp, vp = ops.qkv_prep(q, k, v, cos, sin, self.norm_eps)
-            g = torch.sigmoid(self.g_ve).to(vp.dtype)
-            vp = g * vp + (1.0 - g) * ve.view(B, T, self.num_heads, self.head_dim).to(vp.dtype)
+            # the gate v' = sigmoid(g_ve) * norm(v) + (1 - sigmoid(g_ve)) * ve rides on the norm/RoPE pass
+            ve_ = ve.view(B, T, self.num_heads, self.head_dim).to(torch.bfloat16)
+            qp, kp, vp = ops.qkv_prep(q, k, v, cos, sin, self.norm_eps, ve=ve_,
+                                      ve_gate_logit=self.g_ve.detach().float().reshape(1))
             y = ops.swa_attend(qp, kp, vp, window, self.attn_scale, bounded_qk=True,   # q, k are RMS-normalised
                                doc_start=doc_start)
             qp, kp, vp = qp.transpose(1, 2), kp.transpose(1, 2), vp.transpose(1, 2)

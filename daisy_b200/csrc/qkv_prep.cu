@@ -9,6 +9,10 @@ struct PrepTensor {
   __nv_bfloat16* out;
   int64_t sb, st, sh;
   int do_norm, do_rope;
+  // value-embedding gate (v only): out = g * x + (1 - g) * mix, g = sigmoid(*gate_logit), after the norm
+  const __nv_bfloat16* mix;
+  int64_t mix_sb, mix_st, mix_sh;
+  const float* gate_logit;
 };
 struct PrepParams {
   PrepTensor t[3];
@@ -30,7 +34,7 @@ __global__ void __launch_bounds__(256) qkv_prep_kernel(const PrepParams p) {
   // 32-bit row arithmetic (the host refuses B*T*H >= 2^31): one division pair per thread, then increments
   const uint32_t rows = (uint32_t)p.B * p.T * p.H;
   const uint32_t row0 = ((blockIdx.x * 256u + threadIdx.x) >> 4) * PREP_ROWS;
-  uint2 lo[PREP_ROWS], hi[PREP_ROWS];
+  uint2 lo[PREP_ROWS], hi[PREP_ROWS], mlo[PREP_ROWS], mhi[PREP_ROWS];
   int hh[PREP_ROWS], tt[PREP_ROWS], bb[PREP_ROWS];
   bool live[PREP_ROWS];
   const uint32_t fast = p.out_bthd ? (uint32_t)p.H : (uint32_t)p.T;   // extent of the fastest row index
@@ -51,7 +55,13 @@ __global__ void __launch_bounds__(256) qkv_prep_kernel(const PrepParams p) {
     const __nv_bfloat16* src = ten.in + bb[u] * ten.sb + tt[u] * ten.st + hh[u] * ten.sh + 4 * sub;
     asm volatile("ld.global.nc.L1::no_allocate.v2.u32 {%0,%1}, [%2];" : "=r"(lo[u].x), "=r"(lo[u].y) : "l"(src));
     asm volatile("ld.global.nc.L1::no_allocate.v2.u32 {%0,%1}, [%2];" : "=r"(hi[u].x), "=r"(hi[u].y) : "l"(src + 64));
+    if (ten.mix) {
+      const __nv_bfloat16* ms = ten.mix + bb[u] * ten.mix_sb + tt[u] * ten.mix_st + hh[u] * ten.mix_sh + 4 * sub;
+      asm volatile("ld.global.nc.L1::no_allocate.v2.u32 {%0,%1}, [%2];" : "=r"(mlo[u].x), "=r"(mlo[u].y) : "l"(ms));
+      asm volatile("ld.global.nc.L1::no_allocate.v2.u32 {%0,%1}, [%2];" : "=r"(mhi[u].x), "=r"(mhi[u].y) : "l"(ms + 64));
+    }
   }
+  const float gate = ten.mix ? 1.0f / (1.0f + __expf(-*ten.gate_logit)) : 1.0f;
 #pragma unroll
   for (int u = 0; u < PREP_ROWS; ++u) {
     float x1[4] = {bf16_lo(lo[u].x), bf16_hi(lo[u].x), bf16_lo(lo[u].y), bf16_hi(lo[u].y)};
@@ -74,6 +84,15 @@ __global__ void __launch_bounds__(256) qkv_prep_kernel(const PrepParams p) {
         const float a = x1[e], b2 = x2[e];
         x1[e] = a * c[e] + b2 * s[e];
         x2[e] = b2 * c[e] - a * s[e];
+      }
+    }
+    if (ten.mix) {
+      const float m1[4] = {bf16_lo(mlo[u].x), bf16_hi(mlo[u].x), bf16_lo(mlo[u].y), bf16_hi(mlo[u].y)};
+      const float m2[4] = {bf16_lo(mhi[u].x), bf16_hi(mhi[u].x), bf16_lo(mhi[u].y), bf16_hi(mhi[u].y)};
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        x1[e] = gate * x1[e] + (1.0f - gate) * m1[e];
+        x2[e] = gate * x2[e] + (1.0f - gate) * m2[e];
       }
     }
     if (live[u]) {
@@ -126,6 +145,7 @@ extern "C" int daisy_b200_qkv_prep(const void* q, const void* k, const void* v,
                                    int64_t v_sb, int64_t v_st, int64_t v_sh,
                                    const float* cos, const float* sin,
                                    void* q_out, void* k_out, void* v_out,
+                                   const void* ve, int64_t ve_sb, int64_t ve_st, int64_t ve_sh, const float* ve_gate_logit,
                                    int B, int T, int H, int D, float eps, unsigned flags, void* stream) {
   if (B <= 0 || T <= 0 || H <= 0) return DAISY_EINVAL;
   if (D != DAISY_HEAD_DIM) return DAISY_EUNSUPPORTED;
@@ -134,14 +154,17 @@ extern "C" int daisy_b200_qkv_prep(const void* q, const void* k, const void* v,
     return DAISY_EINVAL;
   if (!q && !k && !v) return DAISY_EINVAL;
   if ((flags & DAISY_ROPE) && (!cos || !sin)) return DAISY_EINVAL;
+  if (ve && (!v || !ve_gate_logit)) return DAISY_EINVAL;
   int rc;
+  if ((rc = check_in(ve, ve_sb, ve_st, ve_sh))) return rc;
   if ((rc = check_in(q, q_sb, q_st, q_sh)) || (rc = check_in(k, k_sb, k_st, k_sh)) || (rc = check_in(v, v_sb, v_st, v_sh))) return rc;
   if (!daisy_aligned16(q_out) || !daisy_aligned16(k_out) || !daisy_aligned16(v_out)) return DAISY_EALIGN;
   if ((flags & DAISY_ROPE) && (!daisy_aligned16(cos) || !daisy_aligned16(sin))) return DAISY_EALIGN;
   PrepParams p;
-  p.t[0] = {(const __nv_bfloat16*)q, (__nv_bfloat16*)q_out, q_sb, q_st, q_sh, (flags & DAISY_NORM_Q) ? 1 : 0, (flags & DAISY_ROPE) ? 1 : 0};
-  p.t[1] = {(const __nv_bfloat16*)k, (__nv_bfloat16*)k_out, k_sb, k_st, k_sh, (flags & DAISY_NORM_K) ? 1 : 0, (flags & DAISY_ROPE) ? 1 : 0};
-  p.t[2] = {(const __nv_bfloat16*)v, (__nv_bfloat16*)v_out, v_sb, v_st, v_sh, (flags & DAISY_NORM_V) ? 1 : 0, 0};
+  p.t[0] = {(const __nv_bfloat16*)q, (__nv_bfloat16*)q_out, q_sb, q_st, q_sh, (flags & DAISY_NORM_Q) ? 1 : 0, (flags & DAISY_ROPE) ? 1 : 0, nullptr, 0, 0, 0, nullptr};
+  p.t[1] = {(const __nv_bfloat16*)k, (__nv_bfloat16*)k_out, k_sb, k_st, k_sh, (flags & DAISY_NORM_K) ? 1 : 0, (flags & DAISY_ROPE) ? 1 : 0, nullptr, 0, 0, 0, nullptr};
+  p.t[2] = {(const __nv_bfloat16*)v, (__nv_bfloat16*)v_out, v_sb, v_st, v_sh, (flags & DAISY_NORM_V) ? 1 : 0, 0,
+            (const __nv_bfloat16*)ve, ve_sb, ve_st, ve_sh, ve_gate_logit};
   p.cos = cos; p.sin = sin; p.B = B; p.T = T; p.H = H; p.eps = eps;
   p.out_bthd = (flags & DAISY_OUT_BTHD) ? 1 : 0;
   const int64_t rows = (int64_t)B * T * H;

@@ -942,7 +942,7 @@ extern "C" int daisy_b200_swa_prefill_fwd(const void* q, const void* k, const vo
     return daisy_b200_qkv_prep(q_in_kernel ? nullptr : off(q, b0 * q_sb), off(k, b0 * k_sb), off(v, b0 * v_sb),
                                q_sb, q_st, q_sh, k_sb, k_st, k_sh, v_sb, v_st, v_sh, cos, sin,
                                q_in_kernel ? nullptr : (void*)off(qp, b0 * sb_), (void*)off(kp, b0 * sb_), (void*)off(vp, b0 * sb_),
-                               nb, T, H, D, eps, pf, s);
+                               nullptr, 0, 0, 0, nullptr, nb, T, H, D, eps, pf, s);
   };
   auto attend = [&](int b0, int nb, void* s) {
     if (q_in_kernel)

@@ -54,12 +54,24 @@ def _f32c(t: torch.Tensor, name: str) -> torch.Tensor:
     return t
 
 
-def qkv_prep(q, k, v, cos, sin, eps: float, flags: int = QKV_DEFAULT, bhtd: bool = False):
+def qkv_prep(q, k, v, cos, sin, eps: float, flags: int = QKV_DEFAULT, bhtd: bool = False,
+             ve: Optional[torch.Tensor] = None, ve_gate_logit: Optional[torch.Tensor] = None):
     """RMS-norm / RoPE raw ``[B,T,H,D]`` projections.  Returns three ``[B,T,H,D]`` contiguous tensors, or
-    ``[B,H,T,D]`` contiguous ones with ``bhtd=True``."""
+    ``[B,H,T,D]`` contiguous ones with ``bhtd=True``.  With ``ve`` (bf16, viewable as ``[B,T,H,D]``) and
+    ``ve_gate_logit`` (float32 scalar tensor on the device) the value-embedding gate is applied to the
+    normalised v: ``v' = g * norm(v) + (1 - g) * ve``, ``g = sigmoid(logit)``."""
     for n, t in (("q", q), ("k", k), ("v", v)):
         _req(t, n)
     B, T, H, D = q.shape
+    ve_args = (None, 0, 0, 0, None)
+    if ve is not None:
+        if ve_gate_logit is None:
+            raise ValueError("ve needs ve_gate_logit")
+        ve = ve.view(B, T, H, D)
+        _req(ve, "ve")
+        if not (ve_gate_logit.is_cuda and ve_gate_logit.dtype == torch.float32 and ve_gate_logit.numel() == 1):
+            raise ValueError("ve_gate_logit must be a float32 scalar CUDA tensor")
+        ve_args = (ve.data_ptr(), ve.stride(0), ve.stride(1), ve.stride(2), ve_gate_logit.data_ptr())
     if flags & ROPE:
         cos, sin = _f32c(cos, "cos"), _f32c(sin, "sin")
         assert cos.shape[0] >= T and cos.shape[1] == D // 2
@@ -70,7 +82,7 @@ def qkv_prep(q, k, v, cos, sin, eps: float, flags: int = QKV_DEFAULT, bhtd: bool
         q.stride(0), q.stride(1), q.stride(2), k.stride(0), k.stride(1), k.stride(2),
         v.stride(0), v.stride(1), v.stride(2), cos.data_ptr() if cos is not None else None,
         sin.data_ptr() if sin is not None else None,
-        outs[0].data_ptr(), outs[1].data_ptr(), outs[2].data_ptr(), B, T, H, D, eps,
+        outs[0].data_ptr(), outs[1].data_ptr(), outs[2].data_ptr(), *ve_args, B, T, H, D, eps,
         flags | (0 if bhtd else OUT_BTHD), _stream(q))
     _lib.check(rc, "daisy_b200_qkv_prep")
     return tuple(outs)

@@ -70,6 +70,10 @@ int         daisy_b200_sm_count(void);
  *   cos,sin    float32 [T, D/2], row t = position of token t
  *   *_out      [B,H,T,D] contiguous, or [B,T,H,D] contiguous with DAISY_OUT_BTHD (a pure streaming
  *              pass); any of the three pairs (in,out) may be NULL together
+ *   ve         NULL, or the layer's value embedding, logical [B,T,H,D] bf16 with strides: the value-embedding
+ *              gate of _qkv_common (models/daisy/attention.py:129-136) is applied to the normalised v,
+ *              v' = g * norm(v) + (1 - g) * ve,  g = sigmoid(*ve_gate_logit)  (a float32 scalar in device memory,
+ *              the module's g_ve parameter)
  */
 int daisy_b200_qkv_prep(const void* q, const void* k, const void* v,
                         int64_t q_sb, int64_t q_st, int64_t q_sh,
@@ -77,6 +81,7 @@ int daisy_b200_qkv_prep(const void* q, const void* k, const void* v,
                         int64_t v_sb, int64_t v_st, int64_t v_sh,
                         const float* cos, const float* sin,
                         void* q_out, void* k_out, void* v_out,
+                        const void* ve, int64_t ve_sb, int64_t ve_st, int64_t ve_sh, const float* ve_gate_logit,
                         int B, int T, int H, int D, float eps, unsigned flags, void* stream);
 
 /* ---------------------------------------------------------------------------------------------

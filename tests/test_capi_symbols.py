@@ -49,9 +49,9 @@ def test_argument_validation_without_gpu(lib):
     a = C.addressof(buf)
     a = (a + 255) & ~255                                    # 256-byte aligned scratch address, never dereferenced
     # head_dim != 128
-    assert lib.daisy_b200_qkv_prep(a, a, a, 0, 0, 0, 0, 0, 0, 0, 0, 0, a, a, a, a, a, 1, 1, 1, 64, 1e-6, 15, None) == _lib.EUNSUPPORTED
+    assert lib.daisy_b200_qkv_prep(a, a, a, 0, 0, 0, 0, 0, 0, 0, 0, 0, a, a, a, a, a, None, 0, 0, 0, None, 1, 1, 1, 64, 1e-6, 15, None) == _lib.EUNSUPPORTED
     # null pointers / bad sizes
-    assert lib.daisy_b200_qkv_prep(None, None, None, 0, 0, 0, 0, 0, 0, 0, 0, 0, a, a, None, None, None, 1, 1, 1, 128, 1e-6, 15, None) == _lib.EINVAL
+    assert lib.daisy_b200_qkv_prep(None, None, None, 0, 0, 0, 0, 0, 0, 0, 0, 0, a, a, None, None, None, None, 0, 0, 0, None, 1, 1, 1, 128, 1e-6, 15, None) == _lib.EINVAL
     assert lib.daisy_b200_swa_attend(None, a, a, 0, 0, 0, 0, 0, 0, 0, 0, 0, a, 0, 0, 0, 1, 1, 1, 128, 0, 0.12, None, 0, 0, None, None) == _lib.EINVAL
     assert lib.daisy_b200_swa_attend(a, a, a, 128, 128, 128, 128, 128, 128, 128, 128, 128, a, 128, 128, 128, 1, 1, 1, 128, 0, -1.0, None, 0, 0, None, None) == _lib.EINVAL
     # misaligned pointer / stride

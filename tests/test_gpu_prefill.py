@@ -168,3 +168,25 @@ def test_document_mask_matches_oracle(T, window, n_docs, per_batch):
     y_nodoc, _, _ = ops.swa_prefill(q, k, v, cos.cuda(), sin.cuda(), window)
     assert (y_nodoc.float() - y.float()).abs().max().item() > 1e-2
     ops.check_device_status(q.device)
+
+
+@pytest.mark.parametrize("logit", [-1.5163, 0.0, 10.0])
+def test_prep_value_embedding_gate(logit):
+    """qkv_prep with ``ve``: v' = g * norm(v) + (1 - g) * ve with g = sigmoid(g_ve)
+    (models/daisy/attention.py:129-136), q' and k' untouched by it; ``ve`` arrives as a strided view."""
+    from daisy_b200 import ops
+    B, T, H = 2, 77, 3
+    qkv = bf16_randn(B, T, 3 * H, D, seed=8)
+    q, k, v = qkv.chunk(3, dim=-2)
+    ve_wide = bf16_randn(B, T, 2 * H * D, seed=9)
+    ve = ve_wide[:, :, H * D:].unflatten(-1, (H, D))               # [B,T,H,D] with a padded token stride
+    cos, sin = swa.rope_tables(D, T)
+    g = torch.tensor([logit], device="cuda")
+    qp, kp, vp = ops.qkv_prep(q, k, v, cos.cuda(), sin.cuda(), swa.FP32_EPS, ve=ve, ve_gate_logit=g)
+    q0, k0, v0 = ops.qkv_prep(q, k, v, cos.cuda(), sin.cuda(), swa.FP32_EPS)
+    assert torch.equal(qp, q0) and torch.equal(kp, k0)
+    gate = torch.sigmoid(torch.tensor(logit))
+    ref = gate * swa.rms_norm(v.float().cpu(), swa.FP32_EPS) + (1 - gate) * ve.float().cpu()
+    assert_close_bf16(vp, ref, "ve gate")
+    with pytest.raises(ValueError):
+        ops.qkv_prep(q, k, v, cos.cuda(), sin.cuda(), swa.FP32_EPS, ve=ve)
