@@ -1,5 +1,5 @@
 // q/k/v preparation (RMS norm + RoPE + [B,T,H,D] -> [B,H,T,D]) and ring-buffer row copies.
-// Both are pure HBM streaming kernels: one half-warp per 256-byte row, 16 bytes per lane.
+// Both are pure HBM streaming kernels: eight lanes per 256-byte row, 2 x 16 bytes per lane.
 #include "rowops.cuh"
 
 namespace daisy {
@@ -23,18 +23,23 @@ struct PrepParams {
   int out_bthd;
 };
 
-constexpr int PREP_ROWS = 4;     // rows per half-warp: independent loads in flight per lane
+#ifndef PREP_ROWS_N
+#define PREP_ROWS_N 2
+#endif
+constexpr int PREP_ROWS = PREP_ROWS_N;   // rows per lane group: independent loads in flight per lane
+constexpr int PREP_LPR = 8;              // lanes per 256-byte row: 16 bytes of each half of the row per lane
 
-// Lane `sub` of a half-warp owns elements [4 sub, 4 sub + 4) and [64 + 4 sub, 64 + 4 sub + 4) of a row: the
-// two halves RoPE pairs together, so the rotation needs no shuffle and one float4 of cos and of sin.
+// Lane `sub` of a group of eight owns elements [8 sub, 8 sub + 8) and [64 + 8 sub, 64 + 8 sub + 8) of a row: the
+// two halves RoPE pairs together, so the rotation needs no shuffle and two float4 of cos and of sin.
+template <bool MIX>
 __global__ void __launch_bounds__(256) qkv_prep_kernel(const PrepParams p) {
   const PrepTensor& ten = p.t[blockIdx.y];
   if (ten.in == nullptr) return;
-  const int lane = threadIdx.x & 31, sub = lane & 15;
+  const int lane = threadIdx.x & 31, sub = lane & (PREP_LPR - 1);
   // 32-bit row arithmetic (the host refuses B*T*H >= 2^31): one division pair per thread, then increments
   const uint32_t rows = (uint32_t)p.B * p.T * p.H;
-  const uint32_t row0 = ((blockIdx.x * 256u + threadIdx.x) >> 4) * PREP_ROWS;
-  uint2 lo[PREP_ROWS], hi[PREP_ROWS], mlo[PREP_ROWS], mhi[PREP_ROWS];
+  const uint32_t row0 = ((blockIdx.x * 256u + threadIdx.x) / PREP_LPR) * PREP_ROWS;
+  uint4 lo[PREP_ROWS], hi[PREP_ROWS], mlo[MIX ? PREP_ROWS : 1], mhi[MIX ? PREP_ROWS : 1];
   int hh[PREP_ROWS], tt[PREP_ROWS], bb[PREP_ROWS];
   bool live[PREP_ROWS];
   const uint32_t fast = p.out_bthd ? (uint32_t)p.H : (uint32_t)p.T;   // extent of the fastest row index
@@ -52,45 +57,52 @@ __global__ void __launch_bounds__(256) qkv_prep_kernel(const PrepParams p) {
     if (row0 + u + 1 < rows) {                     // advance; past the end the last row is repeated
       if (++i_fast == fast) { i_fast = 0; if (++i_mid == mid) { i_mid = 0; ++i_b; } }
     }
-    const __nv_bfloat16* src = ten.in + bb[u] * ten.sb + tt[u] * ten.st + hh[u] * ten.sh + 4 * sub;
-    asm volatile("ld.global.nc.L1::no_allocate.v2.u32 {%0,%1}, [%2];" : "=r"(lo[u].x), "=r"(lo[u].y) : "l"(src));
-    asm volatile("ld.global.nc.L1::no_allocate.v2.u32 {%0,%1}, [%2];" : "=r"(hi[u].x), "=r"(hi[u].y) : "l"(src + 64));
-    if (ten.mix) {
-      const __nv_bfloat16* ms = ten.mix + bb[u] * ten.mix_sb + tt[u] * ten.mix_st + hh[u] * ten.mix_sh + 4 * sub;
-      asm volatile("ld.global.nc.L1::no_allocate.v2.u32 {%0,%1}, [%2];" : "=r"(mlo[u].x), "=r"(mlo[u].y) : "l"(ms));
-      asm volatile("ld.global.nc.L1::no_allocate.v2.u32 {%0,%1}, [%2];" : "=r"(mhi[u].x), "=r"(mhi[u].y) : "l"(ms + 64));
+    const __nv_bfloat16* src = ten.in + bb[u] * ten.sb + tt[u] * ten.st + hh[u] * ten.sh + 8 * sub;
+    lo[u] = ld_stream16(src);
+    hi[u] = ld_stream16(src + 64);
+    if (MIX && ten.mix) {
+      const __nv_bfloat16* ms = ten.mix + bb[u] * ten.mix_sb + tt[u] * ten.mix_st + hh[u] * ten.mix_sh + 8 * sub;
+      mlo[MIX ? u : 0] = ld_stream16(ms);
+      mhi[MIX ? u : 0] = ld_stream16(ms + 64);
     }
   }
-  const float gate = ten.mix ? 1.0f / (1.0f + __expf(-*ten.gate_logit)) : 1.0f;
+  const float gate = (MIX && ten.mix) ? 1.0f / (1.0f + __expf(-*ten.gate_logit)) : 1.0f;
 #pragma unroll
   for (int u = 0; u < PREP_ROWS; ++u) {
-    float x1[4] = {bf16_lo(lo[u].x), bf16_hi(lo[u].x), bf16_lo(lo[u].y), bf16_hi(lo[u].y)};
-    float x2[4] = {bf16_lo(hi[u].x), bf16_hi(hi[u].x), bf16_lo(hi[u].y), bf16_hi(hi[u].y)};
+    float x1[8], x2[8];
+    unpack8(lo[u], x1);
+    unpack8(hi[u], x2);
     if (ten.do_norm) {
       float ss = 0.f;
 #pragma unroll
-      for (int e = 0; e < 4; ++e) ss += x1[e] * x1[e] + x2[e] * x2[e];
-      ss = halfwarp_sum(ss);
+      for (int e = 0; e < 8; ++e) ss += x1[e] * x1[e] + x2[e] * x2[e];
+      ss += __shfl_xor_sync(0xffffffffu, ss, 4);
+      ss += __shfl_xor_sync(0xffffffffu, ss, 2);
+      ss += __shfl_xor_sync(0xffffffffu, ss, 1);
       const float r = rsqrtf(ss * (1.0f / DAISY_HEAD_DIM) + p.eps);
 #pragma unroll
-      for (int e = 0; e < 4; ++e) { x1[e] *= r; x2[e] *= r; }
+      for (int e = 0; e < 8; ++e) { x1[e] *= r; x2[e] *= r; }
     }
     if (ten.do_rope) {
-      const float4 c4 = *reinterpret_cast<const float4*>(p.cos + (int64_t)tt[u] * 64 + 4 * sub);
-      const float4 s4 = *reinterpret_cast<const float4*>(p.sin + (int64_t)tt[u] * 64 + 4 * sub);
-      const float c[4] = {c4.x, c4.y, c4.z, c4.w}, s[4] = {s4.x, s4.y, s4.z, s4.w};
+      const float* cr = p.cos + (int64_t)tt[u] * 64 + 8 * sub;
+      const float* sr = p.sin + (int64_t)tt[u] * 64 + 8 * sub;
+      const float4 c0 = *reinterpret_cast<const float4*>(cr), c1 = *reinterpret_cast<const float4*>(cr + 4);
+      const float4 s0 = *reinterpret_cast<const float4*>(sr), s1 = *reinterpret_cast<const float4*>(sr + 4);
+      const float c[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+      const float s[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
+      for (int e = 0; e < 8; ++e) {
         const float a = x1[e], b2 = x2[e];
         x1[e] = a * c[e] + b2 * s[e];
         x2[e] = b2 * c[e] - a * s[e];
       }
     }
-    if (ten.mix) {
-      const float m1[4] = {bf16_lo(mlo[u].x), bf16_hi(mlo[u].x), bf16_lo(mlo[u].y), bf16_hi(mlo[u].y)};
-      const float m2[4] = {bf16_lo(mhi[u].x), bf16_hi(mhi[u].x), bf16_lo(mhi[u].y), bf16_hi(mhi[u].y)};
+    if (MIX && ten.mix) {
+      float m1[8], m2[8];
+      unpack8(mlo[MIX ? u : 0], m1);
+      unpack8(mhi[MIX ? u : 0], m2);
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
+      for (int e = 0; e < 8; ++e) {
         x1[e] = gate * x1[e] + (1.0f - gate) * m1[e];
         x2[e] = gate * x2[e] + (1.0f - gate) * m2[e];
       }
@@ -98,9 +110,9 @@ __global__ void __launch_bounds__(256) qkv_prep_kernel(const PrepParams p) {
     if (live[u]) {
       const int64_t orow = p.out_bthd ? ((int64_t)bb[u] * p.T + tt[u]) * p.H + hh[u]
                                       : ((int64_t)bb[u] * p.H + hh[u]) * p.T + tt[u];
-      __nv_bfloat16* dst = ten.out + orow * DAISY_HEAD_DIM + 4 * sub;
-      *reinterpret_cast<uint2*>(dst) = make_uint2(pack_bf16(x1[0], x1[1]), pack_bf16(x1[2], x1[3]));
-      *reinterpret_cast<uint2*>(dst + 64) = make_uint2(pack_bf16(x2[0], x2[1]), pack_bf16(x2[2], x2[3]));
+      __nv_bfloat16* dst = ten.out + orow * DAISY_HEAD_DIM + 8 * sub;
+      *reinterpret_cast<uint4*>(dst) = pack8(x1);
+      *reinterpret_cast<uint4*>(dst + 64) = pack8(x2);
     }
   }
 }
@@ -168,8 +180,10 @@ extern "C" int daisy_b200_qkv_prep(const void* q, const void* k, const void* v,
   p.cos = cos; p.sin = sin; p.B = B; p.T = T; p.H = H; p.eps = eps;
   p.out_bthd = (flags & DAISY_OUT_BTHD) ? 1 : 0;
   const int64_t rows = (int64_t)B * T * H;
-  dim3 grid((unsigned)((rows + 16 * PREP_ROWS - 1) / (16 * PREP_ROWS)), 3, 1);
-  qkv_prep_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(p);
+  const int64_t rows_per_block = (256 / PREP_LPR) * PREP_ROWS;
+  dim3 grid((unsigned)((rows + rows_per_block - 1) / rows_per_block), 3, 1);
+  if (ve) qkv_prep_kernel<true><<<grid, 256, 0, (cudaStream_t)stream>>>(p);
+  else    qkv_prep_kernel<false><<<grid, 256, 0, (cudaStream_t)stream>>>(p);
   DAISY_CHECK_LAUNCH();
   return DAISY_OK;
 }
