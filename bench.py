@@ -21,6 +21,7 @@ import json
 import os
 import statistics
 import subprocess
+import threading
 import sys
 import time
 
@@ -55,15 +56,50 @@ def measured_peaks():
 
 
 class ClockSampler:
-    """nvidia-smi clock/throttle samples taken while the timed region runs."""
+    """SM clock and throttle reasons sampled WHILE the timed region runs: NVML from a thread every ~2 ms (the
+    timed regions here last tens of milliseconds, too short for `nvidia-smi -lms`), else `nvidia-smi -lms 100`.
+    Read-only queries; nothing is set."""
     Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
          "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
          "clocks_event_reasons.sw_power_cap")
 
     def __init__(self, index: int):
-        self.index, self.proc = index, None
+        self.index, self.proc, self.thread = index, None, None
+        self.samples, self.reason_bits, self.power = [], 0, []
+        self._stop = threading.Event()
+        self.nvml = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            # NVML numbers devices like nvidia-smi; CUDA_VISIBLE_DEVICES remaps torch's index
+            vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+            phys = index
+            if vis:
+                ids = [x.strip() for x in vis.split(",") if x.strip()]
+                if index < len(ids) and ids[index].isdigit():
+                    phys = int(ids[index])
+            self.handle = pynvml.nvmlDeviceGetHandleByIndex(phys)
+            self.max_mhz = float(pynvml.nvmlDeviceGetMaxClockInfo(self.handle, pynvml.NVML_CLOCK_SM))
+            self.nvml = pynvml
+        except Exception:
+            self.nvml = None
+
+    def _poll(self):
+        n = self.nvml
+        while not self._stop.is_set():
+            try:
+                self.samples.append(float(n.nvmlDeviceGetClockInfo(self.handle, n.NVML_CLOCK_SM)))
+                self.reason_bits |= int(n.nvmlDeviceGetCurrentClocksEventReasons(self.handle))
+                self.power.append(n.nvmlDeviceGetPowerUsage(self.handle) / 1000.0)
+            except Exception:
+                break
+            time.sleep(0.002)
 
     def start(self):
+        if self.nvml is not None:
+            self.thread = threading.Thread(target=self._poll, daemon=True)
+            self.thread.start()
+            return
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
                                           "-i", str(self.index), "-lms", "100"],
@@ -72,6 +108,17 @@ class ClockSampler:
             self.proc = None
 
     def stop(self):
+        if self.thread is not None:
+            self._stop.set()
+            self.thread.join(timeout=2)
+            n = self.nvml
+            names = (("hw_slowdown", "nvmlClocksEventReasonHwSlowdown"), ("hw_thermal_slowdown", "nvmlClocksEventReasonHwThermalSlowdown"),
+                     ("sw_thermal_slowdown", "nvmlClocksEventReasonSwThermalSlowdown"), ("sw_power_cap", "nvmlClocksEventReasonSwPowerCap"))
+            reasons = sorted(k for k, attr in names if self.reason_bits & int(getattr(n, attr, 0)))
+            return {"sm_mhz": statistics.median(self.samples) if self.samples else None,
+                    "sm_min_mhz": min(self.samples) if self.samples else None, "sm_max_mhz": self.max_mhz,
+                    "power_w_max": max(self.power) if self.power else None, "reasons": reasons,
+                    "samples": len(self.samples), "source": "nvml, 2 ms period, during the timed region"}
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         time.sleep(0.15)
@@ -96,7 +143,7 @@ class ClockSampler:
                     reasons.add(n)
         busy = [x for x in sm if x > 0]
         return {"sm_mhz": statistics.median(busy) if busy else None, "sm_max_mhz": max(mx) if mx else None,
-                "reasons": sorted(reasons), "samples": len(sm)}
+                "reasons": sorted(reasons), "samples": len(sm), "source": "nvidia-smi -lms 100"}
 
 
 def shard_bounds(n: int, world: int, rank: int):
