@@ -13,6 +13,7 @@ LIB_PATH = os.path.join(_HERE, "libdaisy_b200.so")
 
 OK, EINVAL, EUNSUPPORTED, EALIGN, EWORKSPACE, ECUDA, ETIMEOUT, ENODEV = 0, -1, -2, -3, -4, -5, -6, -7
 NORM_Q, NORM_K, NORM_V, ROPE, QKV_DEFAULT, WRITE_RING, OUT_BTHD, KV_BHTD, Q_IN_KERNEL, BOUNDED_QK = 1, 2, 4, 8, 15, 16, 32, 64, 128, 256
+WINDOW_BLOCKS = 512
 KDA_L2NORM_QK, KDA_OUT_FP32 = 1, 2
 KDA_GATE_ROUND_BF16 = 1
 

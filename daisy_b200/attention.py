@@ -41,6 +41,34 @@ class WindowMask:
         return cls(window, doc_starts(input_seq, eos_token_id))
 
 
+WINDOW_BLOCK_SIZE = 128      # models/daisy/daisy_core.py: WINDOW_BLOCK_SIZE, also the kernels' key tile
+
+
+@dataclass(frozen=True)
+class BlockWindowMask:
+    """Stands in for one flex-attention ``BlockMask`` of ``DaisyCore.create_blockmasks``
+    (models/daisy/daisy_core.py:182-229), the training-form mask: causal and same-document per token, and
+    only the ``window_blocks`` nearest key blocks of 128 tokens (key block >= query block - window_blocks + 1).
+    That is what the reference's block lists select: its "full" blocks are clamped to the ``window_blocks - 1``
+    nearest, its "partial" blocks (the diagonal and blocks a document boundary crosses) to
+    ``max(window_blocks - #full, 1)`` nearest, and together these are always the nearest ``window_blocks``
+    blocks that hold any visible key."""
+    window_blocks: int
+    doc_start: Optional[Tensor] = None
+
+
+def create_blockmasks(input_seq: Tensor, sliding_window_num_blocks: int, L: int, eos_token_id: int):
+    """One mask per layer in the reference's long/short cycle (daisy_core.py:224-228): ``long`` uses
+    ``sliding_window_num_blocks``, ``short`` half of it; layers cycle long, short, short, short and the last
+    layer is long."""
+    torch._assert(input_seq.shape[-1] % WINDOW_BLOCK_SIZE == 0, "input_seq length must be divisible by the block size")
+    ds = doc_starts(input_seq, eos_token_id)
+    wb = int(sliding_window_num_blocks)
+    long_bm, short_bm = BlockWindowMask(wb, ds), BlockWindowMask(wb // 2, ds)
+    cycle = [long_bm] + [short_bm] * 3
+    return (cycle * ((L + 3) // 4))[:L - 1] + [long_bm]
+
+
 def doc_starts(input_seq: Tensor, eos_token_id: int) -> Tensor:
     """First position of each token's document, int32, shape of ``input_seq`` without a leading batch of 1.
     The reference counts ``docs = (input_seq == eos).cumsum(0)``: an EOS token opens the next document, so the
@@ -122,18 +150,22 @@ class B200CausalSelfAttention(nn.Module):
 
     @staticmethod
     def _window_of(attn_mask):
-        """-> (window or None, doc_start tensor or None)"""
+        """-> (window or None, doc_start tensor or None[, True when the window counts 128-token blocks])"""
         if attn_mask is None:
             return None, None
         if isinstance(attn_mask, WindowMask):
             return attn_mask.window, attn_mask.doc_start
+        if isinstance(attn_mask, BlockWindowMask):
+            torch._assert(attn_mask.window_blocks >= 1, "a block window keeps at least the diagonal block")
+            return attn_mask.window_blocks, attn_mask.doc_start, True
         if isinstance(attn_mask, int):
             return attn_mask, None
         raise TypeError("attn_mask must be None, an int window or WindowMask(window[, doc_start]); dense mask "
                         "tensors are not consumed by the B200 kernels")
 
     def _attend(self, x: Tensor, ve: Optional[Tensor], mask):
-        window, doc_start = mask
+        window, doc_start = mask[0], mask[1]
+        in_blocks = len(mask) > 2 and mask[2]
         B, T = x.size(0), x.size(1)
         q, k, v = self._project(x)
         cos, sin = self.rotary.tables(T)
@@ -144,17 +176,24 @@ class B200CausalSelfAttention(nn.Module):
             qp, kp, vp = ops.qkv_prep(q, k, v, cos, sin, self.norm_eps, ve=ve_,
                                       ve_gate_logit=self.g_ve.detach().float().reshape(1))
             y = ops.swa_attend(qp, kp, vp, window, self.attn_scale, bounded_qk=True,   # q, k are RMS-normalised
-                               doc_start=doc_start)
+                               doc_start=doc_start, window_in_blocks=in_blocks)
             qp, kp, vp = qp.transpose(1, 2), kp.transpose(1, 2), vp.transpose(1, 2)
         else:
-            y, kp, vp = ops.swa_prefill(q, k, v, cos, sin, window, self.attn_scale, self.norm_eps, doc_start=doc_start)
+            y, kp, vp = ops.swa_prefill(q, k, v, cos, sin, window, self.attn_scale, self.norm_eps, doc_start=doc_start,
+                                        window_in_blocks=in_blocks)
             qp = None
         y = F.linear(y.view(B, T, self.m_dim), self.qkvo_w[3])
         return y, kp, vp, qp
 
     # ------------------------------------------------------------------ AttentionProtocol
     def forward(self, x: Tensor, ve: Optional[Tensor], block_mask=None, attn_mask=None):
-        torch._assert(block_mask is None, "flex block masks (training form) are not implemented by the B200 kernels")
+        # block_mask: a BlockWindowMask (what create_blockmasks returns here) selects the training-form mask of
+        # forward_flex (models/daisy/attention.py:156-162); otherwise attn_mask as in forward_sdpa
+        if block_mask is not None:
+            torch._assert(isinstance(block_mask, BlockWindowMask), "block_mask must be a daisy_b200 BlockWindowMask")
+            torch._assert(x.size(1) % WINDOW_BLOCK_SIZE == 0, "the block-granular mask needs T divisible by 128")
+            y, _, _, _ = self._attend(x, ve, self._window_of(block_mask))
+            return y
         y, _, _, _ = self._attend(x, ve, self._window_of(attn_mask))
         return y
 

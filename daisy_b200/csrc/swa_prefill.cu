@@ -48,6 +48,7 @@ struct PrefillParams {
   __nv_bfloat16* out;
   int64_t o_sb, o_st, o_sh;
   int T, H, B, window;
+  int window_blocks;       // > 0: block-granular window (key tile >= query tile - window_blocks + 1), window = 0
   float scale_log2;
   int* status;
   // document mask: doc_start[b * doc_sb + t] = first key position of the document token t belongs to (null: one
@@ -99,7 +100,7 @@ struct ItemGeom {
   int jlo, jhi;
 };
 __device__ __forceinline__ ItemGeom item_geom(int item, int nq, int H, int T, int window,
-                                              const int* doc_start = nullptr, int64_t doc_sb = 0) {
+                                              const int* doc_start = nullptr, int64_t doc_sb = 0, int window_blocks = 0) {
   ItemGeom g;
   const int qp = item % nq, bh = item / nq;
   g.h = bh % H; g.b = bh / H;
@@ -108,6 +109,8 @@ __device__ __forceinline__ ItemGeom item_geom(int item, int nq, int H, int T, in
     g.q0[s] = (qp * 2 + s) * BM;
     g.valid[s] = g.q0[s] < T;
     int klo = window > 0 ? max(0, g.q0[s] - window + 1) : 0;
+    // block-granular window of the training form: whole key tiles, the nearest window_blocks of them
+    if (window_blocks > 0) klo = max(0, g.q0[s] / BM - window_blocks + 1) * BN;
     // keys before the document of the stream's FIRST row are invisible to every row of the stream
     if (doc_start && g.valid[s]) klo = max(klo, doc_start[g.b * doc_sb + g.q0[s]]);
     g.jlo_s[s] = g.valid[s] ? klo / BN : 1;
@@ -227,7 +230,7 @@ swa_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       // Q tiles run one item ahead of the K/V stream (double buffer), so the softmax warps can prepare the
       // next item's Q while the current item is still computing.
       auto load_q = [&](int it_item) {
-        const ItemGeom gq = item_geom(it_item, nq, p.H, T, window, p.doc_start, p.doc_sb);
+        const ItemGeom gq = item_geom(it_item, nq, p.H, T, window, p.doc_start, p.doc_sb, p.window_blocks);
         for (int s = 0; s < 2 && ok; ++s) {
           if (!gq.valid[s]) continue;
           const int qb = qn[s] % NQBUF;
@@ -241,7 +244,7 @@ swa_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       };
       if ((int)blockIdx.x < n_items) load_q(blockIdx.x);
       for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
-        const ItemGeom g = item_geom(item, nq, p.H, T, window, p.doc_start, p.doc_sb);
+        const ItemGeom g = item_geom(item, nq, p.H, T, window, p.doc_start, p.doc_sb, p.window_blocks);
         for (int j = g.jlo; j <= g.jhi && ok; ++j) {
           for (int kv = 0; kv < 2; ++kv, ++n) {
             const int stage = n % NSTAGE;
@@ -283,7 +286,7 @@ swa_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       PT_DECL;
       PT_START();
       for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
-        const ItemGeom g = item_geom(item, nq, p.H, T, window, p.doc_start, p.doc_sb);
+        const ItemGeom g = item_geom(item, nq, p.H, T, window, p.doc_start, p.doc_sb, p.window_blocks);
         for (int j = g.jlo; j <= g.jhi + 1 && ok; ++j) {
 #pragma unroll
           for (int s = 0; s < 2; ++s) {
@@ -362,7 +365,7 @@ swa_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     PT_DECL;
     PT_START();
     for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
-      const ItemGeom g = item_geom(item, nq, p.H, T, window, p.doc_start, p.doc_sb);
+      const ItemGeom g = item_geom(item, nq, p.H, T, window, p.doc_start, p.doc_sb, p.window_blocks);
       if (!g.valid[s]) continue;
       const int q0 = g.q0[s];
       const int q_row = q0 + row;
@@ -376,7 +379,7 @@ swa_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         q_prepared = false;
         const int item_next = item + gridDim.x;
         if (item_next < n_items) {
-          const ItemGeom gn = item_geom(item_next, nq, p.H, T, window, p.doc_start, p.doc_sb);
+          const ItemGeom gn = item_geom(item_next, nq, p.H, T, window, p.doc_start, p.doc_sb, p.window_blocks);
           next_valid = gn.valid[s];
           q_row_next = gn.q0[s] + row;
         }
@@ -529,7 +532,7 @@ swa_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     PT_DECL;
     PT_START();
     for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
-      const ItemGeom g = item_geom(item, nq, p.H, T, window, p.doc_start, p.doc_sb);
+      const ItemGeom g = item_geom(item, nq, p.H, T, window, p.doc_start, p.doc_sb, p.window_blocks);
       if (!g.valid[s]) continue;
       const int q0 = g.q0[s];
       const int q_row = q0 + row;
@@ -544,7 +547,7 @@ swa_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       bool next_valid = false;
       int q_row_next = 0;
       if (QRAW && item_next < n_items) {
-        const ItemGeom gn = item_geom(item_next, nq, p.H, T, window, p.doc_start, p.doc_sb);
+        const ItemGeom gn = item_geom(item_next, nq, p.H, T, window, p.doc_start, p.doc_sb, p.window_blocks);
         next_valid = gn.valid[s];
         q_row_next = gn.q0[s] + row;
       }
@@ -834,7 +837,7 @@ static int launch_attend(const void* q, const void* k, const void* v,
                          int64_t v_sb, int64_t v_st, int64_t v_sh,
                          void* out, int64_t o_sb, int64_t o_st, int64_t o_sh,
                          int B, int T, int H, int D, int window, float scale, const QTransform* qt, bool bounded_qk,
-                         const int* doc_start, int64_t doc_sb, int* status_word, void* stream) {
+                         const int* doc_start, int64_t doc_sb, bool window_in_blocks, int* status_word, void* stream) {
   if (!q || !k || !v || !out || B <= 0 || T <= 0 || H <= 0 || !(scale > 0.f)) return DAISY_EINVAL;
   if (D != DAISY_HEAD_DIM) return DAISY_EUNSUPPORTED;
   if (!daisy_aligned16(q) || !daisy_aligned16(k) || !daisy_aligned16(v) || !daisy_aligned16(out) || ((o_sb | o_st | o_sh) & 7) ||
@@ -854,7 +857,9 @@ static int launch_attend(const void* q, const void* k, const void* v,
   if ((rc = daisy_host::make_tmap_bf16_dthb(&tv, v, D, T, H, B, v_st * 2, sb(v_sh, H), sb(v_sb, B), 64, BN)) != DAISY_OK) return rc;
   PrefillParams p;
   p.out = (__nv_bfloat16*)out; p.o_sb = o_sb; p.o_st = o_st; p.o_sh = o_sh;
-  p.T = T; p.H = H; p.B = B; p.window = window;
+  p.T = T; p.H = H; p.B = B;
+  p.window = window_in_blocks ? 0 : window;
+  p.window_blocks = (window_in_blocks && window > 0) ? window : 0;
   p.scale_log2 = scale * 1.4426950408889634f;
   p.status = status_word;
   p.doc_start = doc_start; p.doc_sb = doc_sb;
@@ -889,10 +894,10 @@ extern "C" int daisy_b200_swa_attend(const void* q, const void* k, const void* v
                                      int B, int T, int H, int D, int window, float scale,
                                      const int32_t* doc_start, int64_t doc_sb,
                                      unsigned flags, int* status_word, void* stream) {
-  if (flags & ~DAISY_BOUNDED_QK) return DAISY_EINVAL;
+  if (flags & ~(DAISY_BOUNDED_QK | DAISY_WINDOW_BLOCKS)) return DAISY_EINVAL;
   return launch_attend(q, k, v, q_sb, q_st, q_sh, k_sb, k_st, k_sh, v_sb, v_st, v_sh, out, o_sb, o_st, o_sh,
                        B, T, H, D, window, scale, nullptr, (flags & DAISY_BOUNDED_QK) != 0, doc_start, doc_sb,
-                       status_word, stream);
+                       (flags & DAISY_WINDOW_BLOCKS) != 0, status_word, stream);
 }
 
 static size_t align1k(size_t x) { return (x + 1023) & ~size_t(1023); }
@@ -948,10 +953,10 @@ extern "C" int daisy_b200_swa_prefill_fwd(const void* q, const void* k, const vo
     if (q_in_kernel)
       return launch_attend(off(q, b0 * q_sb), off(kp, b0 * sb_), off(vp, b0 * sb_), q_sb, q_st, q_sh, sb_, st_, sh_, sb_, st_, sh_,
                            (void*)off(out, b0 * o_sb), o_sb, o_st, o_sh, nb, T, H, D, window, scale, &qt, bounded_qk,
-                           doc_start ? doc_start + b0 * doc_sb : nullptr, doc_sb, status_word, s);
+                           doc_start ? doc_start + b0 * doc_sb : nullptr, doc_sb, (flags & DAISY_WINDOW_BLOCKS) != 0, status_word, s);
     return launch_attend(off(qp, b0 * sb_), off(kp, b0 * sb_), off(vp, b0 * sb_), sb_, st_, sh_, sb_, st_, sh_, sb_, st_, sh_,
                          (void*)off(out, b0 * o_sb), o_sb, o_st, o_sh, nb, T, H, D, window, scale, nullptr, bounded_qk,
-                         doc_start ? doc_start + b0 * doc_sb : nullptr, doc_sb, status_word, s);
+                         doc_start ? doc_start + b0 * doc_sb : nullptr, doc_sb, (flags & DAISY_WINDOW_BLOCKS) != 0, status_word, s);
   };
 
   // (Cutting the batch into slices so that the streaming pass over slice i+1 runs on a side stream underneath the

@@ -104,11 +104,12 @@ def _doc_arg(doc_start: Optional[torch.Tensor], B: int, T: int, device):
 
 def swa_attend(q, k, v, window: Optional[int], scale: float = ATTN_SCALE,
                out: Optional[torch.Tensor] = None, bounded_qk: bool = False,
-               doc_start: Optional[torch.Tensor] = None) -> torch.Tensor:
+               doc_start: Optional[torch.Tensor] = None, window_in_blocks: bool = False) -> torch.Tensor:
     """Windowed causal attention on prepared tensors of logical shape ``[B,T,H,D]`` (any batch / token /
     head strides, D contiguous); returns ``[B,T,H,D]``.  ``bounded_qk=True`` promises RMS-normalised q and k
     (every logit bounded), which selects the kernel without a running maximum.  ``doc_start`` (int, ``[T]`` or
-    ``[B,T]``): first position of each token's document; keys before it are masked."""
+    ``[B,T]``): first position of each token's document; keys before it are masked.  ``window_in_blocks``:
+    ``window`` counts blocks of 128 tokens (key block >= query block - window + 1), the training-form mask."""
     for n, t in (("q", q), ("k", k), ("v", v)):
         _req(t, n)
     B, T, H, D = q.shape
@@ -121,7 +122,8 @@ def swa_attend(q, k, v, window: Optional[int], scale: float = ATTN_SCALE,
         q.stride(0), q.stride(1), q.stride(2), k.stride(0), k.stride(1), k.stride(2),
         v.stride(0), v.stride(1), v.stride(2), out.data_ptr(),
         out.stride(0), out.stride(1), out.stride(2), B, T, H, D, int(window or 0), scale, doc_ptr, doc_sb,
-        _lib.BOUNDED_QK if bounded_qk else 0, status_word(q.device).data_ptr(), _stream(q))
+        (_lib.BOUNDED_QK if bounded_qk else 0) | (_lib.WINDOW_BLOCKS if window_in_blocks else 0),
+        status_word(q.device).data_ptr(), _stream(q))
     _lib.check(rc, "daisy_b200_swa_attend")
     return out
 
@@ -129,7 +131,8 @@ def swa_attend(q, k, v, window: Optional[int], scale: float = ATTN_SCALE,
 def swa_prefill(q, k, v, cos, sin, window: Optional[int], scale: float = ATTN_SCALE, eps: float = 1.1920929e-07,
                 flags: int = QKV_DEFAULT, workspace: Optional[torch.Tensor] = None,
                 out: Optional[torch.Tensor] = None, k_out=None, v_out=None,
-                doc_start: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+                doc_start: Optional[torch.Tensor] = None, window_in_blocks: bool = False
+                ) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
     """Raw projections ``[B,T,H,D]`` -> ``(y [B,T,H,D], k' [B,H,T,D], v' [B,H,T,D])``.  Like the reference's
     ``prefill`` the returned k', v' are ``[B,H,T,D]``-shaped views of ``[B,T,H,D]`` memory; pass
     ``k_out``/``v_out`` as ``[B,T,H,D]`` contiguous buffers to reuse storage."""
@@ -155,7 +158,8 @@ def swa_prefill(q, k, v, cos, sin, window: Optional[int], scale: float = ATTN_SC
         q.stride(0), q.stride(1), q.stride(2), k.stride(0), k.stride(1), k.stride(2),
         v.stride(0), v.stride(1), v.stride(2), cos.data_ptr(), sin.data_ptr(),
         out.data_ptr(), out.stride(0), out.stride(1), out.stride(2), k_out.data_ptr(), v_out.data_ptr(),
-        B, T, H, D, int(window or 0), scale, eps, doc_ptr, doc_sb, flags, workspace.data_ptr(), workspace.numel(),
+        B, T, H, D, int(window or 0), scale, eps, doc_ptr, doc_sb,
+        flags | (_lib.WINDOW_BLOCKS if window_in_blocks else 0), workspace.data_ptr(), workspace.numel(),
         status_word(q.device).data_ptr(), _stream(q))
     _lib.check(rc, "daisy_b200_swa_prefill_fwd")
     return out, k_out.transpose(1, 2), v_out.transpose(1, 2)

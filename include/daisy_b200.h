@@ -51,6 +51,9 @@ extern "C" {
                                    (true for RMS-normalised q and k with scale * D <= 41); selects the kernel that
                                    needs no running maximum.  swa_prefill_fwd sets it itself when it normalises q and k. */
 /* KDA flags */
+#define DAISY_WINDOW_BLOCKS 512u /* swa_attend / swa_prefill_fwd: `window` counts blocks of 128 tokens: key block >= query block -
+                                   window + 1 (with causality and documents token-exact inside), the mask the flex-attention
+                                   BlockMasks of DaisyCore.create_blockmasks select (models/daisy/daisy_core.py:182-229)     */
 #define DAISY_KDA_L2NORM_QK 1u  /* L2-normalise q and k over K inside the kernel (eps 1e-6)         */
 #define DAISY_KDA_OUT_FP32  2u  /* `o` is float32 instead of bf16                                   */
 #define DAISY_KDA_GATE_ROUND_BF16 1u  /* kda_gate: round the result to bf16 first (what the reference's cast of the

@@ -90,8 +90,30 @@ def doc_starts(input_seq: torch.Tensor, eos_token_id: int) -> torch.Tensor:
     return torch.cummax(marks, dim=-1).values.to(torch.int32)
 
 
+BLOCK = 128      # WINDOW_BLOCK_SIZE of the reference (models/daisy/daisy_core.py)
+
+
+def flex_block_lists(docs: torch.Tensor, window_blocks: int):
+    """The key-block lists ``build_bm(window_blocks)`` hands to ``BlockMask.from_kv_blocks``
+    (models/daisy/daisy_core.py:196-221), restated: per query block, the selected *partial* blocks (some but not
+    all (q,k) pairs pass ``document_causal``) and *full* blocks (all pass), as Python sets.  ``docs [T]`` are the
+    document numbers ``(input_seq == eos).cumsum(0)``.  Both kinds are listed nearest first; full blocks are cut
+    to the ``window_blocks - 1`` nearest, partial ones to ``max(window_blocks - #full, 1)`` nearest."""
+    nb = docs.numel() // BLOCK
+    lo, hi = docs.view(nb, BLOCK)[:, 0], docs.view(nb, BLOCK)[:, -1]
+    partial, full = [], []
+    for qb in range(nb):
+        any_ = [kb for kb in range(qb, -1, -1) if lo[qb] <= hi[kb] and hi[qb] >= lo[kb]]           # nearest first
+        all_ = [kb for kb in range(qb - 1, -1, -1) if lo[qb] == hi[kb] and hi[qb] == lo[kb]]
+        part = [kb for kb in any_ if kb not in all_]
+        n_full = len(all_)
+        full.append(set(all_[:max(min(n_full, window_blocks - 1), 0)]))
+        partial.append(set(part[:min(len(part), max(window_blocks - n_full, 1))]))
+    return partial, full
+
+
 def window_mask(q_lo: int, q_hi: int, k_lo: int, k_hi: int, window: Optional[int],
-                doc_start: Optional[torch.Tensor] = None) -> torch.Tensor:
+                doc_start: Optional[torch.Tensor] = None, window_blocks: Optional[int] = None) -> torch.Tensor:
     """Additive mask block for query rows [q_lo,q_hi) x key cols [k_lo,k_hi): 0 where
     ``0 <= q - k < window`` and q, k lie in the same document, else -inf
     (models/daisy/daisy_core.py:53-69).  ``window=None`` means plain causal; ``doc_start [T]`` (see
@@ -104,13 +126,17 @@ def window_mask(q_lo: int, q_hi: int, k_lo: int, k_hi: int, window: Optional[int
         bad = bad | (d >= window)
     if doc_start is not None:
         bad = bad | (ki < doc_start[q_lo:q_hi].to(torch.int64)[:, None])
+    if window_blocks is not None:
+        # training form (flex BlockMasks of create_blockmasks, daisy_core.py:182-229): the lists of
+        # :func:`flex_block_lists` always amount to the window_blocks nearest key blocks
+        bad = bad | (ki // BLOCK < qi // BLOCK - window_blocks + 1)
     m = torch.zeros(q_hi - q_lo, k_hi - k_lo, dtype=torch.float32)
     m[bad] = float("-inf")
     return m
 
 
 def attend_windowed(q, k, v, window: Optional[int], scale: float = ATTN_SCALE, block: int = 512,
-                    doc_start: Optional[torch.Tensor] = None):
+                    doc_start: Optional[torch.Tensor] = None, window_blocks: Optional[int] = None):
     """``softmax(scale * q k^T + M) v`` with the window (and document) mask, on already
     normalised / rotated ``[B, T, H, D]`` tensors (models/daisy/attention.py:141-148).
     Evaluated in blocks of ``block`` query rows against only the keys the mask can
@@ -124,9 +150,9 @@ def attend_windowed(q, k, v, window: Optional[int], scale: float = ATTN_SCALE, b
         k0 = 0 if window is None else max(0, q0 - window + 1)
         s = torch.matmul(qh[:, :, q0:q1], kh[:, :, k0:q1].transpose(-1, -2)) * scale
         if doc_start is not None and doc_start.dim() == 2:
-            m = torch.stack([window_mask(q0, q1, k0, q1, window, doc_start[b]) for b in range(B)])[:, None]
+            m = torch.stack([window_mask(q0, q1, k0, q1, window, doc_start[b], window_blocks) for b in range(B)])[:, None]
         else:
-            m = window_mask(q0, q1, k0, q1, window, doc_start)
+            m = window_mask(q0, q1, k0, q1, window, doc_start, window_blocks)
         s = s + m.to(s.dtype)
         p = torch.softmax(s, dim=-1)
         out[:, :, q0:q1] = torch.matmul(p, vh[:, :, k0:q1])
@@ -135,12 +161,12 @@ def attend_windowed(q, k, v, window: Optional[int], scale: float = ATTN_SCALE, b
 
 def swa_prefill(q, k, v, cos_td, sin_td, window: Optional[int], scale: float = ATTN_SCALE,
                 eps: float = FP32_EPS, norm_q=True, norm_k=True, norm_v=True, rope=True,
-                block: int = 512, doc_start: Optional[torch.Tensor] = None):
+                block: int = 512, doc_start: Optional[torch.Tensor] = None, window_blocks: Optional[int] = None):
     """Projection-to-projection part of ``CausalSelfAttention.prefill``
     (models/daisy/attention.py:121-125,141-148,173-179): takes raw projected
     q,k,v ``[B,T,H,D]``, returns ``(y [B,T,H,D], k' [B,H,T,D], v' [B,H,T,D])`` in fp32."""
     qn, kn, vn = qkv_transform(q, k, v, cos_td, sin_td, eps, norm_q, norm_k, norm_v, rope)
-    y = attend_windowed(qn, kn, vn, window, scale, block, doc_start)
+    y = attend_windowed(qn, kn, vn, window, scale, block, doc_start, window_blocks)
     return y, kn.permute(0, 2, 1, 3).contiguous(), vn.permute(0, 2, 1, 3).contiguous()
 
 

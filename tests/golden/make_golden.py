@@ -163,6 +163,42 @@ def doc_mask_case():
     print("doc_mask_small", tuple(y.shape))
 
 
+def flex_blockmask_case():
+    """Block lists of ``DaisyCore.create_blockmasks`` (daisy_core.py:182-229) for sequences with documents
+    of many lengths: kv_num_blocks / kv_indices / full_kv_num_blocks / full_kv_indices of the long and the short
+    mask, for several window sizes.  (The CPU path of ``flex_attention`` applies ``mask_mod`` densely and ignores
+    the lists, so the lists themselves are the fixture; the compiled GPU kernel visits exactly the listed
+    blocks and applies ``mask_mod`` inside the partial ones.)"""
+    import types
+    from models.daisy.daisy_core import DaisyCore
+    eos, T = 7, 2048
+    g = torch.Generator().manual_seed(17)
+    out = {}
+    for case in range(3):
+        seq = torch.randint(8, 100, (T,), generator=g)
+        n_eos = (3, 12, 40)[case]
+        seq[torch.randperm(T, generator=g)[:n_eos]] = eos
+        if case == 1:
+            seq[640:1400] = 9                                      # one long document
+        out[f"seq{case}"] = seq.numpy()
+        for wb in (2, 3, 6, 8):
+            bms = DaisyCore.create_blockmasks(types.SimpleNamespace(eos_token_id=eos), seq,
+                                              torch.tensor(wb, dtype=torch.int32), 2)
+            for name, bm in (("long", bms[-1]), ("short", bms[0] if wb // 2 >= 1 else None)):
+                if bm is None:
+                    continue
+                bm = bms[-1] if name == "long" else DaisyCore.create_blockmasks(
+                    types.SimpleNamespace(eos_token_id=eos), seq, torch.tensor(wb, dtype=torch.int32), 5)[1]
+                key = f"c{case}_wb{wb}_{name}"
+                out[key + "_pn"] = bm.kv_num_blocks[0, 0].numpy()
+                out[key + "_pi"] = bm.kv_indices[0, 0].numpy()
+                out[key + "_fn"] = bm.full_kv_num_blocks[0, 0].numpy()
+                out[key + "_fi"] = bm.full_kv_indices[0, 0].numpy()
+    out["eos"] = np.int64(eos)
+    np.savez_compressed(os.path.join(HERE, "flex_blockmask_lists.npz"), **out)
+    print("flex_blockmask_lists", len(out))
+
+
 def kda_gate_case():
     """``fused_kda_gate`` as the KDA layer calls it (attention_kimi.py:132), through the reference's own
     pure-PyTorch implementation ``_gate_impl`` (fla_custom_ops.py:71-103): fp32 and bf16 inputs, with the
@@ -190,6 +226,7 @@ if __name__ == "__main__":
     kda_case()
     kda_gate_case()
     doc_mask_case()
+    flex_blockmask_case()
     for f in sorted(os.listdir(HERE)):
         if f.endswith(".npz"):
             print(f, os.path.getsize(os.path.join(HERE, f)))

@@ -256,3 +256,27 @@ def test_forward_with_eos_document_mask_matches_reference_fixture(golden_dir):
     err = (y.float().cpu() - ref).abs()
     scale = max(1.0, ref.abs().max().item())
     assert err.max().item() <= 4e-2 * scale and err.mean().item() <= 4e-3 * scale
+
+
+def test_forward_with_block_mask_training_form():
+    """``forward(x, ve, block_mask=...)`` with the masks of ``create_blockmasks`` (long / short cycle) against
+    the oracle's block-granular mask."""
+    from daisy_b200 import B200CausalSelfAttention, create_blockmasks
+    H, T, eos = 2, 768, 5
+    m = _module(H * 128, H, 128, eps=swa.FP32_EPS)
+    g = torch.Generator().manual_seed(12)
+    seq = torch.randint(6, 50, (T,), generator=g)
+    seq[[100, 300, 301, 640]] = eos
+    x = torch.randn(1, T, H * 128, generator=g).bfloat16()
+    masks = create_blockmasks(seq.cuda(), 4, 6, eos)
+    assert [bm.window_blocks for bm in masks] == [4, 2, 2, 2, 4, 4]
+    w = m.qkvo_w.detach().float().cpu()
+    ds = swa.doc_starts(seq, eos)
+    for bm in (masks[0], masks[1]):
+        with torch.inference_mode():
+            y = m(x.cuda(), None, block_mask=bm)
+        q, k, v = swa.project_qkv(x.float(), w, H, 128)
+        yo, _, _ = swa.swa_prefill(q, k, v, m.rotary.cos[:T].cpu(), m.rotary.sin[:T].cpu(), None, doc_start=ds,
+                                   window_blocks=bm.window_blocks)
+        yo = torch.matmul(yo.reshape(1, T, H * 128), w[3].t())
+        assert_close_bf16(y, yo, f"block mask wb={bm.window_blocks}", max_tol=4e-2, mean_tol=4e-3)

@@ -190,3 +190,27 @@ def test_prep_value_embedding_gate(logit):
     assert_close_bf16(vp, ref, "ve gate")
     with pytest.raises(ValueError):
         ops.qkv_prep(q, k, v, cos.cuda(), sin.cuda(), swa.FP32_EPS, ve=ve)
+
+
+@pytest.mark.parametrize("T,wb,n_docs", [(256, 1, 0), (1024, 2, 3), (1536, 4, 6), (2048, 3, 30), (1280, 20, 2)])
+def test_block_window_training_form_matches_oracle(T, wb, n_docs):
+    """DAISY_WINDOW_BLOCKS: the mask the flex BlockMasks of create_blockmasks select -- causal and same
+    document per token, the wb nearest key blocks of 128 tokens."""
+    from daisy_b200 import ops
+    B, H = 2, 2
+    qkv = bf16_randn(B, T, 3 * H, D, seed=T + wb)
+    q, k, v = qkv.chunk(3, dim=-2)
+    cos, sin = swa.rope_tables(D, T)
+    ds = _random_doc_starts(B, T, n_docs, seed=wb, per_batch=True) if n_docs else None
+    y_ref, _, _ = swa.swa_prefill(q.float().cpu(), k.float().cpu(), v.float().cpu(), cos, sin, None,
+                                  doc_start=ds, window_blocks=wb)
+    dsc = ds.cuda() if ds is not None else None
+    y, _, _ = ops.swa_prefill(q, k, v, cos.cuda(), sin.cuda(), wb, doc_start=dsc, window_in_blocks=True)
+    ops.check_device_status(q.device)
+    assert_close_bf16(y, y_ref, "block window, fused step")
+    qp, kp, vp = ops.qkv_prep(q, k, v, cos.cuda(), sin.cuda(), swa.FP32_EPS)
+    ya = ops.swa_attend(qp, kp, vp, wb, doc_start=dsc, window_in_blocks=True)       # the general kernel
+    assert_close_bf16(ya, y_ref, "block window, attend")
+    if T // 128 > wb and n_docs <= 6:                             # differs from the token-exact window of wb * 128
+        y_tok, _, _ = ops.swa_prefill(q, k, v, cos.cuda(), sin.cuda(), wb * 128, doc_start=dsc)
+        assert (y_tok.float() - y.float()).abs().max().item() > 1e-3

@@ -147,3 +147,34 @@ def test_document_mask_against_reference_fixture(golden_dir):
     y, _, _ = swa.csa_prefill(torch.from_numpy(d["x"]), torch.from_numpy(d["qkvo_w"]), 2, 128, W,
                               torch.from_numpy(d["cos"]), torch.from_numpy(d["sin"]), doc_start=ds)
     assert (y - torch.from_numpy(d["y"])).abs().max().item() < 1e-5
+
+
+def test_flex_block_lists_against_reference_fixture(golden_dir):
+    """The block lists of ``DaisyCore.create_blockmasks`` (models/daisy/daisy_core.py:182-229), produced by the
+    reference itself for documents of many lengths and several window sizes, against the oracle's restatement;
+    and the token-level rule the kernels implement (causal, same document, key block >= query block -
+    window_blocks + 1) selects exactly the union of those lists."""
+    d = np.load(os.path.join(golden_dir, "flex_blockmask_lists.npz"))
+    eos, checked = int(d["eos"]), 0
+    for case in range(3):
+        seq = torch.from_numpy(d[f"seq{case}"])
+        docs, T = (seq == eos).cumsum(0), seq.numel()
+        nb = T // swa.BLOCK
+        ds = swa.doc_starts(seq, eos)
+        for wb in (2, 3, 6, 8):
+            for name, w in (("long", wb), ("short", wb // 2)):
+                key = f"c{case}_wb{wb}_{name}"
+                if key + "_pn" not in d.files:
+                    continue
+                part, full = swa.flex_block_lists(docs, w)
+                for qb in range(nb):
+                    ref_p = set(d[key + "_pi"][qb][:d[key + "_pn"][qb]].tolist())
+                    ref_f = set(d[key + "_fi"][qb][:d[key + "_fn"][qb]].tolist())
+                    assert ref_p == part[qb] and ref_f == full[qb], (key, qb)
+                    m = swa.window_mask(qb * swa.BLOCK, (qb + 1) * swa.BLOCK, 0, T, None, ds, w)
+                    vis = torch.isfinite(m).any(0).view(nb, swa.BLOCK)
+                    assert set(vis.any(1).nonzero().flatten().tolist()) == (ref_p | ref_f), (key, qb)
+                    for kb in ref_f:                                # a "full" block is visible to every row
+                        assert bool(vis[kb].all()) and bool(torch.isfinite(m[:, kb * swa.BLOCK:(kb + 1) * swa.BLOCK]).all())
+                    checked += 1
+    assert checked == 384
