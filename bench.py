@@ -329,7 +329,9 @@ def run_decode(cfg, warmup, dist, rank, world, peaks, lean=False):
     if dist is not None:
         gathered = [torch.empty_like(out[0]) for _ in range(world)]
         dist.all_gather(gathered, out[0])
-    return {"name": "decode_c3", "ms_per_step": per, "tokens_per_s": world * B / (per * 1e-3), "hbm_gbs": world * gbs,
+    del kc, vc
+    gen = generator_step_latency(H, D, W) if rank == 0 else None
+    return {"name": "decode_c3", "generator_step": gen, "ms_per_step": per, "tokens_per_s": world * B / (per * 1e-3), "hbm_gbs": world * gbs,
             "splits": splits, "steps": nsteps, "launches_per_step": 2, "finite": bool(torch.isfinite(out.float()).all()),
             "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                          "frac": gbs / peaks["hbm_gbs"], "traffic": NCU_TRAFFIC["decode_per_batch_row"] * B,
@@ -340,6 +342,39 @@ def run_decode(cfg, warmup, dist, rank, world, peaks, lean=False):
                     "h2d_bytes_per_step": 3 * B * H * D * 2, "d2h_bytes_per_step": B * H * D * 2},
             "config": {"workload": f"decode_c3: batch {B} x {H} heads x {D}, ring capacity {cap}, window {W}, "
                                    f"{nsteps} steps from t={cap} (ring wraps every step)", "per_gpu_batch": B}}
+
+
+def generator_step_latency(H, D, W, layers=4, batch=1, steps=200):
+    """The reference's Generator shape (batch 1, `inference/generate.py:76`): one token through `layers` attention
+    layers (projections + fused ring decode), issued launch by launch from Python and as one CUDA-graph replay
+    with the position in device memory.  Microseconds per token, steady state (full window, wrapped ring)."""
+    from daisy_b200 import B200CausalSelfAttention, StepRunner
+    os.environ["DISABLE_O_ZERO_INIT"] = "1"
+    torch.manual_seed(0)
+    dim, cap = H * D, 2 * W
+    mods = [B200CausalSelfAttention(dim, H, D, max_seq_len=cap + 2 * steps + 64).cuda().eval() for _ in range(layers)]
+    res = {}
+    for name in ("eager", "graph"):
+        run = StepRunner(mods, window=W, cache_capacity=cap, batch=batch)
+        run.cache.k.normal_(); run.cache.v.normal_()
+        run.cache.t = cap + 1; run.cache.t_dev.fill_(cap + 1)
+        x = torch.randn(batch, 1, dim, device="cuda", dtype=torch.bfloat16)
+        if name == "graph":
+            run.capture_step(batch, dim)
+        step = (lambda: run._step_graph(x)) if name == "graph" else (lambda: run._step(x))
+        for _ in range(5):
+            step()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            step()
+        e1.record()
+        torch.cuda.synchronize()
+        res[name + "_us_per_token"] = e0.elapsed_time(e1) / steps * 1e3
+        del run
+    res.update({"layers": layers, "batch": batch, "window": W, "dim": dim})
+    return res
 
 
 # ----------------------------------------------------------------------------- our arm: KDA

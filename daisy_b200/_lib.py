@@ -34,6 +34,9 @@ SIGNATURES = {
     "daisy_b200_swa_decode_step": (_i, [_vp] * 3 + [_i64] * 6 + [_vp] * 2 + [_i64] * 3 + [_i64, _i, _i] +
                                    [_vp] * 2 + [_vp, _i64, _i64] + [_vp] * 2 + [_i] * 3 + [_f, _f, _u] +
                                    [_vp, _sz, _i, _vp, _vp]),
+    "daisy_b200_swa_decode_step_dev": (_i, [_vp] * 3 + [_i64] * 6 + [_vp] * 2 + [_i64] * 3 + [_vp, _i, _i] +
+                                       [_vp] * 2 + [_i] + [_vp, _i64, _i64] + [_vp] * 2 + [_i] * 3 + [_f, _f, _u] +
+                                       [_vp, _sz, _i, _vp, _vp]),
     "daisy_b200_swa_decode_static_capacity": (_sz, []),
     "daisy_b200_swa_decode_step_static": (_i, [_vp] * 3 + [_i64] * 6 + [_vp] * 2 + [_i64] * 3 + [_i64, _i, _i] +
                                           [_vp] * 2 + [_vp, _i64, _i64] + [_vp] * 2 + [_i] * 3 + [_f, _f, _u] +

@@ -232,6 +232,18 @@ class B200CausalSelfAttention(nn.Module):
         y = F.linear(y.view(B, 1, self.m_dim), self.qkvo_w[3])
         return y, k_new, v_new
 
+    def step_ring_dev(self, x, cache: B200KVCache, layer: int, window: Optional[int]):
+        """``step_ring`` with the position read from ``cache.t_dev`` on the device: nothing in the launch
+        sequence depends on the token index, so it can be captured once in a CUDA graph and replayed
+        (``StepRunner.capture_step``).  Position = tokens in the cache, as in ``Generator._step``."""
+        torch._assert(not self.receives_ve, "the graph step does not take value embeddings")
+        B = x.size(0)
+        q, k, v = self._project(x)
+        kr, vr = cache.ring(layer)
+        y = ops.swa_decode_step_dev(q, k, v, kr, vr, cache.t_dev, cache.W, window, self.rotary.cos, self.rotary.sin,
+                                    self.attn_scale, self.norm_eps, QKV_DEFAULT, write_ring=True)
+        return F.linear(y.view(B, 1, self.m_dim), self.qkvo_w[3])
+
     def _decode(self, q, k, v, kc, vc, t, cap, pos, ve, window, write_ring):
         cos, sin = self.rotary.tables(pos + 1)
         flags = QKV_DEFAULT

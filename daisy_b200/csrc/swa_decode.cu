@@ -31,20 +31,53 @@ struct DecodeParams {
   float* ws_acc;   // [B,H,splits,128]
   float* ws_ml;    // [B,H,splits,2]
   int splits, rows_per_split;
+  // position on the device (CUDA-graph replays): when t_dev is set, start_slot / r / new_slot / rows_per_split are
+  // derived from *t_dev in the kernels, and cos_row / sin_row are the BASES of tables with table_rows rows
+  const long long* t_dev;
+  int window, table_rows;
+  int* status;
 };
 
+// Row range and table rows of this step: the host's values, or derived from the device-side position.
+struct DecodeGeom { int r, start_slot, new_slot, rows_per_split; const float *cos_row, *sin_row; };
+template <bool DEV>
+__device__ __forceinline__ DecodeGeom decode_geom(const DecodeParams& p) {
+  DecodeGeom g{p.r, p.start_slot, p.new_slot, p.rows_per_split, p.cos_row, p.sin_row};
+  if (DEV) {
+    const long long t = *p.t_dev;
+    long long r = t < p.cap ? t : p.cap;
+    if (p.window > 0 && r > (long long)p.window - 1) r = p.window - 1;
+    g.r = (int)r;
+    g.start_slot = p.cap > 0 ? (int)((t - r) % p.cap) : 0;
+    g.new_slot = p.cap > 0 ? (int)(t % p.cap) : 0;
+    int rps = ((int)r + p.splits - 1) / p.splits;
+    rps = (rps + 31) / 32 * 32;
+    g.rows_per_split = rps ? rps : 32;
+    long long pos = t;
+    if (pos >= p.table_rows) {                                     // past the RoPE table: report, stay in bounds
+      pos = p.table_rows - 1;
+      if (p.status && threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) p.status[0] = DAISY_EINVAL;
+    }
+    g.cos_row = p.cos_row + pos * (DAISY_HEAD_DIM / 2);
+    g.sin_row = p.sin_row + pos * (DAISY_HEAD_DIM / 2);
+  }
+  return g;
+}
+
+template <bool DEV>
 __global__ void __launch_bounds__(128) swa_decode_partial_kernel(const DecodeParams p) {
   const int s = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, hw = lane >> 4, sub = lane & 15;
 
+  const DecodeGeom g = decode_geom<DEV>(p);
   float qf[8];
   unpack8(*reinterpret_cast<const uint4*>(p.q + b * p.q_sb + h * p.q_sh + 8 * sub), qf);
-  norm_rope_row8(qf, sub, p.flags & DAISY_NORM_Q, p.flags & DAISY_ROPE, p.eps, p.cos_row, p.sin_row);
+  norm_rope_row8(qf, sub, p.flags & DAISY_NORM_Q, p.flags & DAISY_ROPE, p.eps, g.cos_row, g.sin_row);
 #pragma unroll
   for (int e = 0; e < 8; ++e) qf[e] *= p.qscale;
 
-  const int i0 = s * p.rows_per_split;
-  const int i1 = min(p.r, i0 + p.rows_per_split);
+  const int i0 = s * g.rows_per_split;
+  const int i1 = min(g.r, i0 + g.rows_per_split);
   const __nv_bfloat16* kbase = p.kc + b * p.c_sb + h * p.c_sh + 8 * sub;
   const __nv_bfloat16* vbase = p.vc + b * p.c_sb + h * p.c_sh + 8 * sub;
 
@@ -59,7 +92,7 @@ __global__ void __launch_bounds__(128) swa_decode_partial_kernel(const DecodePar
     for (int j = 0; j < 4; ++j) {
       const int row = base + 2 * j + hw;
       valid[j] = row < i1;
-      int slot = p.start_slot + (valid[j] ? row : i0);
+      int slot = g.start_slot + (valid[j] ? row : i0);
       if (slot >= p.cap) slot -= p.cap;
       kk[j] = ld_stream16(kbase + (int64_t)slot * p.c_sr);
       vv[j] = ld_stream16(vbase + (int64_t)slot * p.c_sr);
@@ -138,8 +171,10 @@ __device__ __forceinline__ float block128_sum(float x, float* red) {
   return (red[0] + red[1]) + (red[2] + red[3]);
 }
 
+template <bool DEV>
 __global__ void __launch_bounds__(128) swa_decode_combine_kernel(const DecodeParams p) {
   const int h = blockIdx.x, b = blockIdx.y, d = threadIdx.x;
+  const DecodeGeom g = decode_geom<DEV>(p);
   __shared__ float red[4];
   __shared__ float xq[DAISY_HEAD_DIM], xk[DAISY_HEAD_DIM];
   float q = __bfloat162float(p.q[b * p.q_sb + h * p.q_sh + d]);
@@ -152,7 +187,7 @@ __global__ void __launch_bounds__(128) swa_decode_combine_kernel(const DecodePar
   if (p.flags & DAISY_ROPE) {
     xq[d] = q; xk[d] = k;
     __syncthreads();
-    const float c = p.cos_row[d & 63], sn = p.sin_row[d & 63];
+    const float c = g.cos_row[d & 63], sn = g.sin_row[d & 63];
     const float sgn = d < 64 ? 1.f : -1.f;
     q = q * c + sgn * xq[d ^ 64] * sn;
     k = k * c + sgn * xk[d ^ 64] * sn;
@@ -177,8 +212,8 @@ __global__ void __launch_bounds__(128) swa_decode_combine_kernel(const DecodePar
   if (p.k_new_out) p.k_new_out[row] = kb;
   if (p.v_new_out) p.v_new_out[row] = vb;
   if (p.flags & DAISY_WRITE_RING) {
-    p.kc[b * p.c_sb + h * p.c_sh + (int64_t)p.new_slot * p.c_sr + d] = kb;
-    p.vc[b * p.c_sb + h * p.c_sh + (int64_t)p.new_slot * p.c_sr + d] = vb;
+    p.kc[b * p.c_sb + h * p.c_sh + (int64_t)g.new_slot * p.c_sr + d] = kb;
+    p.vc[b * p.c_sb + h * p.c_sh + (int64_t)g.new_slot * p.c_sr + d] = vb;
   }
 }
 
@@ -204,24 +239,22 @@ extern "C" size_t daisy_b200_swa_decode_workspace_bytes(int B, int H, int D, int
   return (size_t)B * H * splits * (D + 2) * sizeof(float);
 }
 
-extern "C" int daisy_b200_swa_decode_step(const void* q_new, const void* k_new, const void* v_new,
-                                          int64_t q_sb, int64_t q_sh, int64_t k_sb, int64_t k_sh,
-                                          int64_t v_sb, int64_t v_sh,
-                                          void* kcache, void* vcache, int64_t c_sb, int64_t c_sh, int64_t c_sr,
-                                          int64_t t, int cap, int window,
-                                          const float* cos_row, const float* sin_row,
-                                          void* out, int64_t o_sb, int64_t o_sh,
-                                          void* k_new_out, void* v_new_out,
-                                          int B, int H, int D, float scale, float eps, unsigned flags,
-                                          void* workspace, size_t workspace_bytes, int splits,
-                                          int* status_word, void* stream) {
-  (void)status_word;
+static int decode_launch(const void* q_new, const void* k_new, const void* v_new,
+                         int64_t q_sb, int64_t q_sh, int64_t k_sb, int64_t k_sh, int64_t v_sb, int64_t v_sh,
+                         void* kcache, void* vcache, int64_t c_sb, int64_t c_sh, int64_t c_sr,
+                         int64_t t, const int64_t* t_dev, int table_rows, int cap, int window,
+                         const float* cos_row, const float* sin_row,
+                         void* out, int64_t o_sb, int64_t o_sh, void* k_new_out, void* v_new_out,
+                         int B, int H, int D, float scale, float eps, unsigned flags,
+                         void* workspace, size_t workspace_bytes, int splits, int* status_word, void* stream) {
   if (!q_new || !k_new || !v_new || !out || B <= 0 || H <= 0 || t < 0 || cap < 0 || splits <= 0) return DAISY_EINVAL;
   if (D != DAISY_HEAD_DIM) return DAISY_EUNSUPPORTED;
   if (B > 65535 || H > 65535) return DAISY_EUNSUPPORTED;
   if ((flags & DAISY_ROPE) && (!cos_row || !sin_row)) return DAISY_EINVAL;
   if ((flags & DAISY_WRITE_RING) && cap == 0) return DAISY_EINVAL;
-  int64_t r = t < cap ? t : cap;
+  if (t_dev && (table_rows <= 0 || (reinterpret_cast<uintptr_t>(t_dev) & 7))) return DAISY_EINVAL;
+  // with the position on the device the host sizes the launch for the longest context it can meet
+  int64_t r = t_dev ? cap : (t < cap ? t : cap);
   if (window > 0 && r > (int64_t)window - 1) r = window - 1;
   if ((r > 0 || (flags & DAISY_WRITE_RING)) && (!kcache || !vcache)) return DAISY_EINVAL;
   if (!workspace) return DAISY_EINVAL;
@@ -238,8 +271,8 @@ extern "C" int daisy_b200_swa_decode_step(const void* q_new, const void* k_new, 
   p.kc = (__nv_bfloat16*)kcache; p.vc = (__nv_bfloat16*)vcache;
   p.c_sb = c_sb; p.c_sh = c_sh; p.c_sr = c_sr;
   p.r = (int)r; p.cap = cap;
-  p.start_slot = cap > 0 ? (int)((t - r) % cap) : 0;
-  p.new_slot = cap > 0 ? (int)(t % cap) : 0;
+  p.start_slot = (cap > 0 && !t_dev) ? (int)((t - r) % cap) : 0;
+  p.new_slot = (cap > 0 && !t_dev) ? (int)(t % cap) : 0;
   p.cos_row = cos_row; p.sin_row = sin_row;
   p.out = (__nv_bfloat16*)out; p.o_sb = o_sb; p.o_sh = o_sh;
   p.k_new_out = (__nv_bfloat16*)k_new_out; p.v_new_out = (__nv_bfloat16*)v_new_out;
@@ -253,13 +286,49 @@ extern "C" int daisy_b200_swa_decode_step(const void* q_new, const void* k_new, 
   rps = (rps + 31) / 32 * 32;                                 // whole 32-row CTA iterations
   if (rps == 0) rps = 32;
   p.rows_per_split = rps;
+  p.t_dev = (const long long*)t_dev; p.window = window; p.table_rows = table_rows; p.status = status_word;
 
   cudaStream_t st = (cudaStream_t)stream;
-  swa_decode_partial_kernel<<<dim3(splits, H, B), 128, 0, st>>>(p);
+  if (t_dev) swa_decode_partial_kernel<true><<<dim3(splits, H, B), 128, 0, st>>>(p);
+  else       swa_decode_partial_kernel<false><<<dim3(splits, H, B), 128, 0, st>>>(p);
   DAISY_CHECK_LAUNCH();
-  swa_decode_combine_kernel<<<dim3(H, B), 128, 0, st>>>(p);
+  if (t_dev) swa_decode_combine_kernel<true><<<dim3(H, B), 128, 0, st>>>(p);
+  else       swa_decode_combine_kernel<false><<<dim3(H, B), 128, 0, st>>>(p);
   DAISY_CHECK_LAUNCH();
   return DAISY_OK;
+}
+
+extern "C" int daisy_b200_swa_decode_step(const void* q_new, const void* k_new, const void* v_new,
+                                          int64_t q_sb, int64_t q_sh, int64_t k_sb, int64_t k_sh,
+                                          int64_t v_sb, int64_t v_sh,
+                                          void* kcache, void* vcache, int64_t c_sb, int64_t c_sh, int64_t c_sr,
+                                          int64_t t, int cap, int window,
+                                          const float* cos_row, const float* sin_row,
+                                          void* out, int64_t o_sb, int64_t o_sh,
+                                          void* k_new_out, void* v_new_out,
+                                          int B, int H, int D, float scale, float eps, unsigned flags,
+                                          void* workspace, size_t workspace_bytes, int splits,
+                                          int* status_word, void* stream) {
+  return decode_launch(q_new, k_new, v_new, q_sb, q_sh, k_sb, k_sh, v_sb, v_sh, kcache, vcache, c_sb, c_sh, c_sr,
+                       t, nullptr, 0, cap, window, cos_row, sin_row, out, o_sb, o_sh, k_new_out, v_new_out,
+                       B, H, D, scale, eps, flags, workspace, workspace_bytes, splits, status_word, stream);
+}
+
+extern "C" int daisy_b200_swa_decode_step_dev(const void* q_new, const void* k_new, const void* v_new,
+                                              int64_t q_sb, int64_t q_sh, int64_t k_sb, int64_t k_sh,
+                                              int64_t v_sb, int64_t v_sh,
+                                              void* kcache, void* vcache, int64_t c_sb, int64_t c_sh, int64_t c_sr,
+                                              const int64_t* t_dev, int cap, int window,
+                                              const float* cos_table, const float* sin_table, int table_rows,
+                                              void* out, int64_t o_sb, int64_t o_sh,
+                                              void* k_new_out, void* v_new_out,
+                                              int B, int H, int D, float scale, float eps, unsigned flags,
+                                              void* workspace, size_t workspace_bytes, int splits,
+                                              int* status_word, void* stream) {
+  if (!t_dev) return DAISY_EINVAL;
+  return decode_launch(q_new, k_new, v_new, q_sb, q_sh, k_sb, k_sh, v_sb, v_sh, kcache, vcache, c_sb, c_sh, c_sr,
+                       0, t_dev, table_rows, cap, window, cos_table, sin_table, out, o_sb, o_sh, k_new_out, v_new_out,
+                       B, H, D, scale, eps, flags, workspace, workspace_bytes, splits, status_word, stream);
 }
 
 // ---------------------------------------------------------------------------------------------

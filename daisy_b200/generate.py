@@ -43,6 +43,42 @@ class StepRunner:
         self.cache.bulk_write_packed(torch.stack([torch.stack(ks), torch.stack(vs)]), T)
         return x
 
+    # ------------------------------------------------------------------ CUDA-graph step
+    @torch.inference_mode()
+    def capture_step(self, batch: int, dim: int) -> None:
+        """Record one token step of all layers into a CUDA graph.  The position lives in ``cache.t_dev`` and is
+        advanced inside the graph, the input and output are fixed buffers: ``_step_graph`` then costs one copy
+        and one graph launch per token instead of four launches per layer issued from Python."""
+        dev = self.cache.device
+        self._gx = torch.zeros(batch, 1, dim, device=dev, dtype=torch.bfloat16)
+        t_saved = self.cache.t_dev.clone()
+        side = torch.cuda.Stream(device=dev)
+        side.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(side):                              # warm-up outside the capture (lazy initialisation)
+            self._graph_body()
+        torch.cuda.current_stream(dev).wait_stream(side)
+        self.cache.t_dev.copy_(t_saved)                            # the warm-up advanced the device counter
+        self._graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self._graph):
+            self._gy = self._graph_body()
+        self.cache.t_dev.copy_(t_saved)
+
+    def _graph_body(self) -> torch.Tensor:
+        x = self._gx
+        for i, a in enumerate(self.layers):
+            x = a.step_ring_dev(x, self.cache, i, self.window)
+        self.cache.t_dev += 1
+        return x
+
+    @torch.inference_mode()
+    def _step_graph(self, x: torch.Tensor) -> torch.Tensor:
+        """``_step`` through the captured graph.  The warm-up and the capture wrote one ring slot each (the slot
+        of the position they ran at), which the first replay overwrites with the same token's real row."""
+        self._gx.copy_(x)
+        self._graph.replay()
+        self.cache.t += 1                                          # host mirror; the device counter moved in the graph
+        return self._gy
+
     @torch.inference_mode()
     def _step(self, x: torch.Tensor) -> torch.Tensor:
         """One token ``x [B,1,dim]``: every layer reads the ring in place and stores its new row; one advance."""

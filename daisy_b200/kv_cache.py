@@ -36,6 +36,9 @@ class B200KVCache:
         self.k = torch.zeros(shape, device=self.device, dtype=self.dtype)
         self.v = torch.zeros(shape, device=self.device, dtype=self.dtype)
         self.t = 0
+        # the same counter in device memory, for decode launches that must not depend on host values
+        # (CUDA-graph replays); kept in step with `t` by stream-ordered updates, never read back
+        self.t_dev = torch.zeros(1, device=self.device, dtype=torch.int64)
         self._staged = [False] * self.L
 
     # ------------------------------------------------------------------ reference API
@@ -70,6 +73,7 @@ class B200KVCache:
 
     def advance(self):
         self.t += 1
+        self.t_dev += 1
         self._staged = [False] * self.L
 
     def bulk_write_packed(self, kv, pos):
@@ -82,6 +86,7 @@ class B200KVCache:
                 ops.ring_copy_rows(self.k[layer], k[layer][:, :, pos - r:pos], pos - r, to_ring=True)
                 ops.ring_copy_rows(self.v[layer], v[layer][:, :, pos - r:pos], pos - r, to_ring=True)
         self.t = pos
+        self.t_dev.fill_(pos)
         self._staged = [False] * self.L
 
     # ------------------------------------------------------------------ in-place access for the decode kernel

@@ -219,6 +219,41 @@ def swa_decode_step(q_new, k_new, v_new, kcache, vcache, t: int, cap: int, windo
     return out, k_o, v_o
 
 
+def swa_decode_step_dev(q_new, k_new, v_new, kcache, vcache, t_dev: torch.Tensor, cap: int, window: Optional[int],
+                        cos_table, sin_table, scale: float = ATTN_SCALE, eps: float = 1.1920929e-07,
+                        flags: int = QKV_DEFAULT, write_ring: bool = True, splits: Optional[int] = None,
+                        workspace: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None):
+    """:func:`swa_decode_step` with the position in device memory (``t_dev``: int64 tensor of one element), so the
+    launch can sit inside a CUDA graph and be replayed for every token.  ``cos_table, sin_table`` are whole
+    ``[rows, D/2]`` tables; the kernels pick row ``t_dev[0]``.  Returns ``y [B,1,H,D]``."""
+    for n, x in (("q_new", q_new), ("k_new", k_new), ("v_new", v_new), ("kcache", kcache), ("vcache", vcache)):
+        _req(x, n)
+    if not (t_dev.is_cuda and t_dev.dtype == torch.int64 and t_dev.numel() == 1):
+        raise ValueError("t_dev must be an int64 CUDA tensor with one element")
+    B, one, H, D = q_new.shape
+    assert one == 1 and kcache.shape == vcache.shape and kcache.stride() == vcache.stride()
+    cos_table, sin_table = _f32c(cos_table, "cos_table"), _f32c(sin_table, "sin_table")
+    L = _lib.lib()
+    r = cap if not window else min(cap, window - 1)
+    if splits is None:
+        splits = decode_splits(B, H, r)
+    need = L.daisy_b200_swa_decode_workspace_bytes(B, H, D, splits)
+    if workspace is None:
+        workspace = torch.empty(need, dtype=torch.uint8, device=q_new.device)
+    if out is None:
+        out = torch.empty(B, 1, H, D, dtype=torch.bfloat16, device=q_new.device)
+    rc = L.daisy_b200_swa_decode_step_dev(
+        q_new.data_ptr(), k_new.data_ptr(), v_new.data_ptr(),
+        q_new.stride(0), q_new.stride(2), k_new.stride(0), k_new.stride(2), v_new.stride(0), v_new.stride(2),
+        kcache.data_ptr(), vcache.data_ptr(), kcache.stride(0), kcache.stride(1), kcache.stride(2),
+        t_dev.data_ptr(), int(cap), int(window or 0), cos_table.data_ptr(), sin_table.data_ptr(), cos_table.shape[0],
+        out.data_ptr(), out.stride(0), out.stride(2), None, None,
+        B, H, D, scale, eps, flags | (WRITE_RING if write_ring else 0), workspace.data_ptr(), workspace.numel(), splits,
+        status_word(q_new.device).data_ptr(), _stream(q_new))
+    _lib.check(rc, "daisy_b200_swa_decode_step_dev")
+    return out
+
+
 def ring_copy_rows(ring_bhcd, lin_bhnd, first_pos: int, to_ring: bool) -> None:
     """Copy rows between a ring ``[B,H,cap,D]`` and a chronological ``[B,H,n,D]`` tensor (any strides
     with D contiguous): row i of ``lin`` <-> ring row ``(first_pos + i) % cap``."""

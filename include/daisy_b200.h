@@ -164,6 +164,24 @@ int daisy_b200_swa_decode_step(const void* q_new, const void* k_new, const void*
                                void* workspace, size_t workspace_bytes, int splits,
                                int* status_word, void* stream);
 
+/* The same step with the position in DEVICE memory, for CUDA-graph replays of Generator._step
+ * (inference/generate.py:231-248): *t_dev (int64) is read by the kernels, so one captured launch sequence serves
+ * every token; the caller advances *t_dev on the stream after the last layer.  cos_table / sin_table are the
+ * table bases ([table_rows, D/2] float32); the row is *t_dev (a position past the table writes DAISY_EINVAL to
+ * the status word and uses the last row).  `splits` must be chosen for the longest context,
+ * min(cap, window - 1) rows. */
+int daisy_b200_swa_decode_step_dev(const void* q_new, const void* k_new, const void* v_new,
+                                   int64_t q_sb, int64_t q_sh, int64_t k_sb, int64_t k_sh,
+                                   int64_t v_sb, int64_t v_sh,
+                                   void* kcache, void* vcache, int64_t c_sb, int64_t c_sh, int64_t c_sr,
+                                   const int64_t* t_dev, int cap, int window,
+                                   const float* cos_table, const float* sin_table, int table_rows,
+                                   void* out, int64_t o_sb, int64_t o_sh,
+                                   void* k_new_out, void* v_new_out,
+                                   int B, int H, int D, float scale, float eps, unsigned flags,
+                                   void* workspace, size_t workspace_bytes, int splits,
+                                   int* status_word, void* stream);
+
 /* The same decode step for callers that cannot allocate device memory (no counterpart in the reference;
  * it exists for embedders: code inside a stream capture, plugins under a pool allocator that forbids
  * cudaMalloc after start-up, FFI hosts that only hold the tensors they were given).  The split partials go

@@ -280,3 +280,32 @@ def test_forward_with_block_mask_training_form():
                                    window_blocks=bm.window_blocks)
         yo = torch.matmul(yo.reshape(1, T, H * 128), w[3].t())
         assert_close_bf16(y, yo, f"block mask wb={bm.window_blocks}", max_tol=4e-2, mean_tol=4e-3)
+
+
+def test_step_through_cuda_graph_equals_eager_steps():
+    """``StepRunner.capture_step`` / ``_step_graph``: one captured launch sequence with the position in device
+    memory, replayed per token, gives bit-identical outputs and ring contents to the eager ``_step`` -- through
+    the ramp-up (fewer context rows than the window), the steady state and the ring wrap."""
+    from daisy_b200 import B200CausalSelfAttention, StepRunner
+    os.environ["DISABLE_O_ZERO_INIT"] = "1"
+    torch.manual_seed(4)
+    B, H, D, W, cap, P, N = 2, 2, 128, 24, 32, 10, 45
+    layers = [B200CausalSelfAttention(H * D, H, D, max_seq_len=256).cuda().eval() for _ in range(2)]
+    for m in layers:
+        with torch.no_grad():
+            m.qkvo_w.mul_(4.0)
+    x = torch.randn(B, P + N, H * D, device="cuda", dtype=torch.bfloat16)
+    eager = StepRunner(layers, window=W, cache_capacity=cap, batch=B)
+    graph = StepRunner(layers, window=W, cache_capacity=cap, batch=B)
+    eager._prefill(x[:, :P])
+    graph._prefill(x[:, :P])
+    graph.capture_step(B, H * D)
+    for i in range(N):
+        xi = x[:, P + i:P + i + 1]
+        y_e = eager._step(xi)
+        y_g = graph._step_graph(xi).clone()
+        assert torch.equal(y_e, y_g), f"step {i} (t={P + i})"
+    from daisy_b200 import ops
+    ops.check_device_status("cuda")
+    assert graph.cache.t == eager.cache.t == P + N and int(graph.cache.t_dev.item()) == P + N
+    assert torch.equal(graph.cache.k, eager.cache.k) and torch.equal(graph.cache.v, eager.cache.v)
