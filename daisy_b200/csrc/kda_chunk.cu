@@ -38,6 +38,14 @@ constexpr int SHARED_BYTES = OFF_D + KD * 4;           // 62976: identical for e
 constexpr int OFF_UT = SHARED_BYTES;                   // U0^T     [128][72] fp16
 constexpr int REC_BYTES = OFF_UT + KD * LDT * 2;       // 81408
 
+// Four 8x8 fp16 matrices from shared memory: lanes 8m..8m+7 give the row addresses of matrix m (16 bytes per
+// row); register m of lane l then holds elements (row l/4, columns 2(l%4), 2(l%4)+1) of matrix m -- the B
+// fragment layout of mma.m16n8k16 when the rows are the n index and the columns the k index.
+__device__ __forceinline__ void ldmatrix_x4(uint32_t* r, const void* row_ptr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_u32(row_ptr)));
+}
+
 __device__ __forceinline__ void mma_f16(float* c, const uint32_t* a, uint32_t b0, uint32_t b1) {
   asm volatile(
       "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
@@ -391,22 +399,21 @@ __global__ void __launch_bounds__(KDA_INTRA_THREADS, 1) kda_intra_kernel(const K
         if (s == 32) { const int c = warp & 7; mrow = 32 + 16 * (c >> 2); ncol0 = 8 * (c & 3); }
         else { const int c = warp & 3; mrow = 16 + 32 * (c >> 1); ncol0 = 32 * (c >> 1) + 8 * (c & 1); }
         if (active) {
-          const int jb = ncol0 + g8;                                 // column (token) held by this lane's B fragment
           float acc[4] = {0.f, 0.f, 0.f, 0.f}, acc2[4] = {0.f, 0.f, 0.f, 0.f};   // two independent chains
           const int i0 = mrow + g8, i1 = i0 + 8;
           // all fragments first (independent shared-memory loads), then the products
           uint32_t bf[KD / 16][2], af[KD / 16][4];
-          const __half* arow0 = (which == 1) ? &sm.Mq[i0][0] : &sm.Mk[i0][0];
-          const __half* arow1 = (which == 1) ? &sm.Mq[i1][0] : &sm.Mk[i1][0];
+          const __half* abase = (which == 1) ? &sm.Mq[0][0] : &sm.Mk[0][0];
+          // ldmatrix.x4: the four 8x8 pieces of a 16x16 A fragment; two k-steps of an 8-column B fragment
+          const __half* aptr = abase + (mrow + (lane & 7) + ((lane >> 3) & 1) * 8) * LDW + (lane >> 4) * 8;
+          const __half* bptr = &sm.Mk[ncol0 + (lane & 7)][(lane >> 3) * 8];
 #pragma unroll
-          for (int ks = 0; ks < KD / 16; ++ks) {
-            const int c = ks * 16 + 2 * t4;
-            bf[ks][0] = *reinterpret_cast<const uint32_t*>(&sm.Mk[jb][c]);
-            bf[ks][1] = *reinterpret_cast<const uint32_t*>(&sm.Mk[jb][c + 8]);
-            af[ks][0] = *reinterpret_cast<const uint32_t*>(&arow0[c]);
-            af[ks][1] = *reinterpret_cast<const uint32_t*>(&arow1[c]);
-            af[ks][2] = *reinterpret_cast<const uint32_t*>(&arow0[c + 8]);
-            af[ks][3] = *reinterpret_cast<const uint32_t*>(&arow1[c + 8]);
+          for (int ks = 0; ks < KD / 16; ++ks) ldmatrix_x4(af[ks], aptr + ks * 16);
+#pragma unroll
+          for (int ks = 0; ks < KD / 16; ks += 2) {
+            uint32_t b4[4];
+            ldmatrix_x4(b4, bptr + ks * 16);
+            bf[ks][0] = b4[0]; bf[ks][1] = b4[1]; bf[ks + 1][0] = b4[2]; bf[ks + 1][1] = b4[3];
           }
 #pragma unroll
           for (int ks = 0; ks < KD / 16; ks += 2) {
@@ -663,12 +670,17 @@ __global__ void __launch_bounds__(32 * (NW + 1), 1) kda_state_kernel(const KdaSt
       uint32_t a[4];
       a[0] = pack_h2(st[2 * ks][0], st[2 * ks][1]); a[1] = pack_h2(st[2 * ks][2], st[2 * ks][3]);
       a[2] = pack_h2(st[2 * ks + 1][0], st[2 * ks + 1][1]); a[3] = pack_h2(st[2 * ks + 1][2], st[2 * ks + 1][3]);
-      const int kk = ks * 16 + 2 * t4;
+      // B fragments of two token tiles per ldmatrix.x4: matrix m = (tile nt + (m >> 1), k half m & 1)
+      const int lrow = (lane >> 4) * 8 + (lane & 7), lcol = ks * 16 + ((lane >> 3) & 1) * 8;
 #pragma unroll
-      for (int nt = 0; nt < 8; ++nt) {
-        const int tok = nt * 8 + g8;
-        mma_f16(au[nt], a, *reinterpret_cast<const uint32_t*>(&Wm[tok * LDW + kk]), *reinterpret_cast<const uint32_t*>(&Wm[tok * LDW + kk + 8]));
-        mma_f16(ao[nt], a, *reinterpret_cast<const uint32_t*>(&Qm[tok * LDW + kk]), *reinterpret_cast<const uint32_t*>(&Qm[tok * LDW + kk + 8]));
+      for (int nt = 0; nt < 8; nt += 2) {
+        uint32_t bw[4], bq[4];
+        ldmatrix_x4(bw, &Wm[(nt * 8 + lrow) * LDW + lcol]);
+        ldmatrix_x4(bq, &Qm[(nt * 8 + lrow) * LDW + lcol]);
+        mma_f16(au[nt], a, bw[0], bw[1]);
+        mma_f16(ao[nt], a, bq[0], bq[1]);
+        mma_f16(au[nt + 1], a, bw[2], bw[3]);
+        mma_f16(ao[nt + 1], a, bq[2], bq[3]);
       }
     }
     // U^T = U0^T - accU, as fp16 A fragments over the token axis
@@ -686,12 +698,13 @@ __global__ void __launch_bounds__(32 * (NW + 1), 1) kda_state_kernel(const KdaSt
     // (2b) accO += U^T A_qk^T
 #pragma unroll
     for (int ks = 0; ks < 4; ++ks) {
-      const int jj = ks * 16 + 2 * t4;
+      const int lrow = (lane >> 4) * 8 + (lane & 7), lcol = ks * 16 + ((lane >> 3) & 1) * 8;
 #pragma unroll
-      for (int nt = 0; nt < 8; ++nt) {
-        if (ks * 16 > nt * 8 + 7) continue;                        // A_qk[i][j] = 0 for j > i
-        const int i = nt * 8 + g8;
-        mma_f16(ao[nt], ua[ks], *reinterpret_cast<const uint32_t*>(&Aq[i * LDT + jj]), *reinterpret_cast<const uint32_t*>(&Aq[i * LDT + jj + 8]));
+      for (int nt = 2 * ks; nt < 8; nt += 2) {                     // A_qk[i][j] = 0 for j > i: tiles below 2 ks are empty
+        uint32_t ba[4];
+        ldmatrix_x4(ba, &Aq[(nt * 8 + lrow) * LDT + lcol]);
+        mma_f16(ao[nt], ua[ks], ba[0], ba[1]);
+        mma_f16(ao[nt + 1], ua[ks], ba[2], ba[3]);
       }
     }
     // (3) S^T = S^T diag(e^{G_C}) + U^T k~
@@ -702,11 +715,13 @@ __global__ void __launch_bounds__(32 * (NW + 1), 1) kda_state_kernel(const KdaSt
     }
 #pragma unroll
     for (int ks = 0; ks < 4; ++ks) {
-      const int jj = ks * 16 + 2 * t4;
+      const int lrow = (lane >> 4) * 8 + (lane & 7), lcol = ks * 16 + ((lane >> 3) & 1) * 8;
 #pragma unroll
-      for (int nt = 0; nt < 16; ++nt) {
-        const int ch = nt * 8 + g8;
-        mma_f16(st[nt], ua[ks], *reinterpret_cast<const uint32_t*>(&Kt[ch * LDT + jj]), *reinterpret_cast<const uint32_t*>(&Kt[ch * LDT + jj + 8]));
+      for (int nt = 0; nt < 16; nt += 2) {
+        uint32_t bk[4];
+        ldmatrix_x4(bk, &Kt[(nt * 8 + lrow) * LDT + lcol]);
+        mma_f16(st[nt], ua[ks], bk[0], bk[1]);
+        mma_f16(st[nt + 1], ua[ks], bk[2], bk[3]);
       }
     }
     __syncwarp();

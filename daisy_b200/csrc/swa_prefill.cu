@@ -112,7 +112,8 @@ __device__ __forceinline__ ItemGeom item_geom(int item, int nq, int H, int T, in
     // block-granular window of the training form: whole key tiles, the nearest window_blocks of them
     if (window_blocks > 0) klo = max(0, g.q0[s] / BM - window_blocks + 1) * BN;
     // keys before the document of the stream's FIRST row are invisible to every row of the stream
-    if (doc_start && g.valid[s]) klo = max(klo, doc_start[g.b * doc_sb + g.q0[s]]);
+    // (clamped to the row itself: a malformed table must not leave a stream without tiles)
+    if (doc_start && g.valid[s]) klo = max(klo, min(doc_start[g.b * doc_sb + g.q0[s]], g.q0[s]));
     g.jlo_s[s] = g.valid[s] ? klo / BN : 1;
     g.jhi_s[s] = g.valid[s] ? min(g.q0[s] + BM - 1, T - 1) / BN : 0;
   }
@@ -386,7 +387,7 @@ swa_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       }
       uint64_t sum_a = pack2f(0.f, 0.f), sum_b = sum_a;
       // first visible key of this row's document, and the latest such start among the stream's rows
-      const int ds_row = p.doc_start ? p.doc_start[g.b * p.doc_sb + min(q_row, T - 1)] : 0;
+      const int ds_row = p.doc_start ? min(p.doc_start[g.b * p.doc_sb + min(q_row, T - 1)], q_row) : 0;   // a row always sees itself
       const int ds_max = p.doc_start ? p.doc_start[g.b * p.doc_sb + min(q0 + BM - 1, T - 1)] : 0;
       for (int j = g.jlo_s[s]; j <= g.jhi_s[s]; ++j) {
         ok = __all_sync(0xffffffffu, mbar_wait(&bars->s_full[s], n_s & 1, abort_flag, p.status, 6));
@@ -552,7 +553,7 @@ swa_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         q_row_next = gn.q0[s] + row;
       }
       float m_ref = NEG_BIG, l = 0.f, pend = 0.f;   // pend: how far the reference is known to lag (applied before the next P)
-      const int ds_row = p.doc_start ? p.doc_start[g.b * p.doc_sb + min(q_row, T - 1)] : 0;
+      const int ds_row = p.doc_start ? min(p.doc_start[g.b * p.doc_sb + min(q_row, T - 1)], q_row) : 0;   // a row always sees itself
       const int ds_max = p.doc_start ? p.doc_start[g.b * p.doc_sb + min(q0 + BM - 1, T - 1)] : 0;
       for (int j = g.jlo_s[s]; j <= g.jhi_s[s]; ++j) {
         const bool first = (j == g.jlo_s[s]);
