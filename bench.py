@@ -40,7 +40,7 @@ DECODE_SMALL = dict(B=4, H=16, D=128, cap=32768, window=4096, steps=4)
 KDA_SMALL = dict(B=1, T=8192, H=16, K=128, V=128, chunk=64)
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch from the ncu captures summarised under profiles/
 # (reduced workloads of the same kernels); traffic grows in proportion to the batch (independent sequences)
-NCU_TRAFFIC = {"prefill_per_batch_row": 246.8e6 / 2, "decode_per_batch_row": 137.3e6 / 4}
+NCU_TRAFFIC = {"prefill_per_batch_row": 1077.9e6 / 8, "decode_per_batch_row": 137.3e6 / 4}
 ROPE_BASE = 10000.0     # the benchmark configs name base 10000 (the module default is 1024, half-truncated)
 
 
@@ -262,7 +262,7 @@ def run_prefill(cfg, steps, warmup, dist, rank, world, peaks, name, lean=False):
         "clocks": clocks, "finite": finite, "launches_per_step": 2,
         "roofline": {"bound": "tensor", "achieved": ach, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
                      "frac": ach / peaks["bf16_tflops"], "traffic": (NCU_TRAFFIC["prefill_per_batch_row"] * B if (T, W) == (8192, 2048) else None),
-                     "traffic_unit": "bytes per launch (ncu dram read+write on B=2, scaled by batch)",
+                     "traffic_unit": "bytes per launch (ncu dram read+write of one full-size C2 launch, per batch row x batch)",
                      "kernel": "swa_prefill_kernel",
                      "kernel_ms": k_ms, "kernel_output_equals_step": kernel_same, "peak_source": peaks["which"] + " (burst cuBLAS bf16)"},
         "e2e": {"value": world * flops / (e2e_ms / e2e_steps * 1e-3) / 1e12, "unit": "TFLOP/s",
