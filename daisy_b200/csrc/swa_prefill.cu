@@ -40,6 +40,9 @@ constexpr int SMEM_TILES = (2 * NQBUF + NSTAGE) * TILE_BYTES;
 constexpr int PREFILL_SMEM = 1024 + SMEM_TILES + 256 + 2 * 128 * 4;   // alignment slack, tiles, barriers, row-sum exchange
 static_assert(PREFILL_SMEM <= 232448, "over the 227 KB a CTA may use");
 constexpr float NEG_BIG = -1.0e30f;
+#ifndef POLY_MASK
+#define POLY_MASK 4                        // pairs with (i & POLY_MASK) == POLY_MASK go to the polynomial: 4 = one in four
+#endif
 #ifndef POLY_HALF
 #define POLY_HALF 0                      // 1: every second pair of exponentials by polynomial; 0: one pair in four
 #endif
@@ -421,7 +424,7 @@ swa_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
             unpack2f(xa, x0, x1);
             const float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
             uint64_t pb;
-            if (POLY_HALF || (i & 4) == 4) {                           // a share of the pairs goes to the FMA pipes
+            if (POLY_HALF || (POLY_MASK && (i & POLY_MASK) == POLY_MASK)) {                           // a share of the pairs goes to the FMA pipes
               pb = exp2_poly2(xb);
               unpack2f(pb, p2, p3);
             } else {
@@ -630,7 +633,7 @@ swa_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
             unpack2f(xa, x0, x1);
             const float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
             uint64_t pb;
-            if (POLY_HALF || (i & 4) == 4) {                       // a share of the pairs goes to the FMA pipes
+            if (POLY_HALF || (POLY_MASK && (i & POLY_MASK) == POLY_MASK)) {                       // a share of the pairs goes to the FMA pipes
               pb = exp2_poly2(xb);
               unpack2f(pb, p2, p3);
             } else {
