@@ -1,7 +1,7 @@
 """Host orchestration of prefill and per-token steps over the ring cache.
 
 Mirror of the reference ``Generator._prefill`` / ``Generator._step`` (inference/generate.py:220-248) for a
-stack of attention layers: prefill fills the ring through ``bulk_write_packed``; each step hands every
+stack of attention layers: prefill fills the ring layer by layer (the rows ``bulk_write_packed`` would write); each step hands every
 layer the ring itself (no per-layer chronological ``view`` copy, no separate ``write``) and advances once.
 Sampling, embeddings and the MLPs are outside this path; the runner works on hidden states.
 """
@@ -33,14 +33,12 @@ class StepRunner:
     @torch.inference_mode()
     def _prefill(self, x: torch.Tensor) -> torch.Tensor:
         """``x [B,T,dim]`` through every layer's ``prefill`` (each layer sees the previous layer's output),
-        then the cache is filled from the stacked k,v exactly as ``Generator._prefill`` does."""
+        the cache receives the rows ``Generator._prefill`` stores through ``bulk_write_packed``."""
         T = x.size(1)
-        ks: List[torch.Tensor] = []
-        vs: List[torch.Tensor] = []
-        for a in self.layers:
+        for i, a in enumerate(self.layers):
             x, k, v = a.prefill(x, None, attn_mask=WindowMask(self.window))
-            ks.append(k); vs.append(v)
-        self.cache.bulk_write_packed(torch.stack([torch.stack(ks), torch.stack(vs)]), T)
+            self.cache.bulk_write_layer(i, k, v, T)               # same rows and slots as bulk_write_packed
+        self.cache.set_position(T)
         return x
 
     # ------------------------------------------------------------------ CUDA-graph step

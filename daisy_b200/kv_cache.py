@@ -89,6 +89,20 @@ class B200KVCache:
         self.t_dev.fill_(pos)
         self._staged = [False] * self.L
 
+    def bulk_write_layer(self, layer, k, v, pos):
+        """One layer of ``bulk_write_packed`` straight from that layer's prefill output ``k, v [B,H,T,D]`` (any
+        strides): the runner fills the ring layer by layer and never builds the stacked ``[2,L,B,H,T,D]`` tensor
+        (models/daisy/daisy_core.py:358-369).  Call :meth:`set_position` once after the last layer."""
+        r = min(pos, max(self.W - 1, 0))
+        if r > 0:
+            ops.ring_copy_rows(self.k[layer], k.to(self.dtype)[:, :, pos - r:pos], pos - r, to_ring=True)
+            ops.ring_copy_rows(self.v[layer], v.to(self.dtype)[:, :, pos - r:pos], pos - r, to_ring=True)
+
+    def set_position(self, pos):
+        self.t = pos
+        self.t_dev.fill_(pos)
+        self._staged = [False] * self.L
+
     # ------------------------------------------------------------------ in-place access for the decode kernel
     def ring(self, layer):
         """``(k_ring, v_ring)`` as ``[B, H, W, D]`` views of the storage (no copy)."""
