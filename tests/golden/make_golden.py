@@ -22,6 +22,8 @@ REF = os.environ.get("DAISY_REFERENCE_ROOT", "/root/reference")
 HERE = os.path.dirname(os.path.abspath(__file__))
 os.environ["DISABLE_O_ZERO_INIT"] = "1"
 sys.path.insert(0, REF)
+import tempfile                                                       # noqa: E402
+os.chdir(tempfile.mkdtemp(prefix="daisy_golden_"))                    # the reference's logger creates ./logs
 
 from models.daisy.attention import CausalSelfAttention, _apply_rope   # noqa: E402
 from models.daisy.daisy_core import build_attn_mask                   # noqa: E402
