@@ -79,7 +79,8 @@ struct KdaIntraParams {
 
 #ifdef KDA_PHASE_TIMING
 __device__ long long kda_phase_clk[16];
-#define KDA_MARK(n) do { __syncthreads(); if (threadIdx.x == 0 && blockIdx.x == 1 && blockIdx.y == 0 && blockIdx.z == 0) kda_phase_clk[n] = clock64(); } while (0)
+// a CTA of the last wave: the first CTAs on an SM also pay for a cold instruction cache
+#define KDA_MARK(n) do { __syncthreads(); if (threadIdx.x == 0 && blockIdx.x == gridDim.x - 2 && blockIdx.y == gridDim.y - 1 && blockIdx.z == gridDim.z - 1) kda_phase_clk[n] = clock64(); } while (0)
 #else
 #define KDA_MARK(n)
 #endif
