@@ -735,7 +735,10 @@ umma_selftest_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_cons
   struct Bars { uint64_t full, done; uint32_t tmem_base; int abort_flag; };
   Bars* bars = reinterpret_cast<Bars*>(smem + 2 * TILE_BYTES);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int K = p.K, mode = p.mode;
+  // mode 3 is mode 0 with a transaction count that nothing completes: the bounded wait must give up, raise the
+  // abort flag, report DAISY_ETIMEOUT and leave through the normal teardown
+  const bool starve = (p.mode == 3);
+  const int K = p.K, mode = starve ? 0 : p.mode;
   const int nhalf = K / 64;
 
   if (threadIdx.x == 0) {
@@ -755,7 +758,7 @@ umma_selftest_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_cons
   const uint32_t b_half = (mode == 0) ? HALF_BYTES : (uint32_t)K * 128u;
   if (threadIdx.x == 0) {
     uint32_t bytes = (mode == 2 ? 0 : 128 * K * 2) + 128 * K * 2;
-    mbar_expect_tx(&bars->full, bytes);
+    mbar_expect_tx(&bars->full, bytes + (starve ? 16u : 0u));
     if (mode != 2)
       for (int hlf = 0; hlf < nhalf; ++hlf) tma_load_3d(a_tile + hlf * HALF_BYTES, &tm_a, &bars->full, 64 * hlf, 0, 0);
     if (mode == 0)
@@ -973,12 +976,12 @@ extern "C" int daisy_b200_swa_prefill_fwd(const void* q, const void* k, const vo
 
 extern "C" int daisy_b200_selftest_umma(const void* a, const void* b, float* c, int K, int mode,
                                         int* status_word, void* stream) {
-  if (!a || !b || !c || (K != 64 && K != 128) || mode < 0 || mode > 2) return DAISY_EINVAL;
+  if (!a || !b || !c || (K != 64 && K != 128) || mode < 0 || mode > 3) return DAISY_EINVAL;
   if (const int arc = ensure_smem_attr(); arc != DAISY_OK) { (void)cudaGetLastError(); return arc; }
   CUtensorMap ta, tb;
   int rc;
   if ((rc = daisy_host::make_tmap_bf16_3d(&ta, a, K, 128, 1, (uint64_t)K * 2, (uint64_t)K * 256, 64, 128)) != DAISY_OK) return rc;
-  if (mode == 0) rc = daisy_host::make_tmap_bf16_3d(&tb, b, K, 128, 1, (uint64_t)K * 2, (uint64_t)K * 256, 64, 128);
+  if (mode == 0 || mode == 3) rc = daisy_host::make_tmap_bf16_3d(&tb, b, K, 128, 1, (uint64_t)K * 2, (uint64_t)K * 256, 64, 128);
   else           rc = daisy_host::make_tmap_bf16_3d(&tb, b, 128, K, 1, 256, (uint64_t)K * 256, 64, K);
   if (rc != DAISY_OK) return rc;
   SelftestParams p{(const __nv_bfloat16*)a, c, K, mode, status_word};

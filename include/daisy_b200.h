@@ -253,6 +253,8 @@ int daisy_b200_kda_gate(const void* g, int g_is_bf16, const float* a_log, const 
  *   mode 0: B given as [128,K] row-major (K-major operand, the Q K^T form)
  *   mode 1: B given as [K,128] row-major (MN-major operand, the P V form), A from shared memory
  *   mode 2: as mode 1 but A is first written to TMEM as packed bf16 (the P-in-TMEM form)
+ *   mode 3: mode 0 with a barrier that nothing completes -- exercises the bounded wait: the kernel gives up after
+ *           its time limit, writes DAISY_ETIMEOUT to the status word, frees its TMEM and returns; C is not written
  * K must be a multiple of 64 and <= 128.  Used by the GPU tests only.
  */
 int daisy_b200_selftest_umma(const void* a, const void* b, float* c, int K, int mode,
