@@ -277,7 +277,7 @@ def run_prefill(cfg, steps, warmup, dist, rank, world, peaks, name, lean=False):
 
 # ----------------------------------------------------------------------------- our arm: decode
 
-def run_decode(cfg, warmup, dist, rank, world, peaks, lean=False):
+def run_decode(cfg, warmup, dist, rank, world, peaks, lean=False, extras=True):
     from daisy_b200 import ops, _lib
     from oracle import swa
     B, H, D, cap, W, nsteps = cfg["B"], cfg["H"], cfg["D"], cfg["cap"], cfg["window"], cfg["steps"]
@@ -330,7 +330,7 @@ def run_decode(cfg, warmup, dist, rank, world, peaks, lean=False):
         gathered = [torch.empty_like(out[0]) for _ in range(world)]
         dist.all_gather(gathered, out[0])
     del kc, vc
-    gen = generator_step_latency(H, D, W) if rank == 0 else None
+    gen = generator_step_latency(H, D, W) if (rank == 0 and extras) else None
     return {"name": "decode_c3", "generator_step": gen, "ms_per_step": per, "tokens_per_s": world * B / (per * 1e-3), "hbm_gbs": world * gbs,
             "splits": splits, "steps": nsteps, "launches_per_step": 2, "finite": bool(torch.isfinite(out.float()).all()),
             "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
@@ -485,6 +485,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="all", choices=["all", "prefill_c2", "prefill_c4", "decode_c3", "kda_c5", "prefill_small", "decode_small", "kda_small"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-extras", action="store_true",
+                    help="skip the measurements beside the three workloads (generator-step latency): launch-list captures")
     args = ap.parse_args()
     world, rank, local = dist_env()
     if args.impl == "reference":
@@ -514,7 +516,7 @@ def main():
         res = run_prefill(PREFILL_C4, max(2, args.steps // 4), warm, dist, rank, world, peaks, "prefill_c4")
     if want in ("all", "decode_c3"):
         torch.cuda.empty_cache()
-        d = run_decode(DECODE_C3, warm, dist, rank, world, peaks)
+        d = run_decode(DECODE_C3, warm, dist, rank, world, peaks, extras=not args.no_extras)
         if res is None:
             res = d
         else:
