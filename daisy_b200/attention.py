@@ -130,6 +130,11 @@ class B200CausalSelfAttention(nn.Module):
         self.last_q = None
         self.last_k = None
         self.receives_ve = receives_ve
+        # True (default): forward / prefill run the projections on this library's tcgen05 GEMM, the norm and RoPE in
+        # the QKV epilogue (measured faster than cuBLAS followed by the norm/RoPE pass); False or
+        # DAISY_NATIVE_GEMM=0: F.linear (cuBLAS) + qkv_prep.  Layers with a value embedding and single-token
+        # steps always take the F.linear form.
+        self.native_gemm = os.environ.get("DAISY_NATIVE_GEMM", "1") == "1"
         if receives_ve:
             init = {0: 0.3228, 1: 0.0, 2: -1.5163, 21: -2.4423, 22: -2.9444, 23: 10.0}.get(layer_idx, 0.0) \
                 if layer_idx is not None else 0.0
@@ -167,8 +172,16 @@ class B200CausalSelfAttention(nn.Module):
         window, doc_start = mask[0], mask[1]
         in_blocks = len(mask) > 2 and mask[2]
         B, T = x.size(0), x.size(1)
-        q, k, v = self._project(x)
         cos, sin = self.rotary.tables(T)
+        if self.native_gemm and not self.receives_ve and self.m_dim % 64 == 0:
+            # every kernel hand-written: QKV GEMM with norm + RoPE in its epilogue, attention, output GEMM
+            w = self.qkvo_w
+            qp, kp, vp = ops.qkv_gemm(x.to(w.dtype), w[:3].flatten(end_dim=1), cos, sin, self.num_heads, self.norm_eps)
+            y = ops.swa_attend(qp, kp, vp, window, self.attn_scale, bounded_qk=True, doc_start=doc_start,
+                               window_in_blocks=in_blocks)
+            y = ops.gemm_nt(y.view(B, T, self.m_dim), w[3])
+            return y, kp.transpose(1, 2), vp.transpose(1, 2), qp.transpose(1, 2)
+        q, k, v = self._project(x)
         if self.receives_ve:
             torch._assert(ve is not None, "ve must be provided when receives_ve=True")
             # the gate v' = sigmoid(g_ve) * norm(v) + (1 - sigmoid(g_ve)) * ve rides on the norm/RoPE pass

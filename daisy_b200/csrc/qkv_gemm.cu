@@ -1,0 +1,287 @@
+// C[M,N] = X[M,K] W[N,K]^T on tcgen05 tensor cores, bf16 in, fp32 accumulation in TMEM, with the projection's
+// element-wise tail as the epilogue.
+//
+// Two uses (the GEMMs either side of the attention core, models/daisy/attention.py:118-125 and :149):
+//   EPI_QKV    W = qkvo_w[:3] flattened ([3*H*128, dim]): a 128-column output tile is one head of q, k or v of 128
+//              tokens, so the weightless RMS norm over D and the half-rotation RoPE are per-thread work on the
+//              accumulator row (thread = token = TMEM lane); q', k', v' leave as [B,T,H,D] bf16 and the separate
+//              norm/RoPE pass over q, k, v (1.6 GB at B=8, T=8192, 16 heads) disappears.
+//   EPI_PLAIN  bf16 store of C (the output projection).
+//
+// Persistent CTAs walk 128 x BN output tiles (n fastest, so concurrently running CTAs share X tiles and the
+// whole W in L2).  Roles (192 threads): warps 0-3 epilogue, warp 4 TMA producer, warp 5 MMA issuer.  Both
+// operands are K-major with 128-byte swizzle (64-element boxes), exactly the Q K^T operand form of the
+// attention kernel; BN = 256 halves the shared-memory bytes read per flop against BN = 128 (the SS form of a
+// 128 x 128 x 16 MMA reads 8 KB per 64 cycles, all the shared-memory pipe has).  Two accumulators in TMEM
+// (2 x BN columns) let the epilogue of tile i run under the main loop of tile i + 1.
+// All mbarrier waits are bounded (abort flag, DAISY_ETIMEOUT through the status word), as everywhere else.
+#include "common.cuh"
+
+namespace daisy {
+
+constexpr int GM = 128, GK = 64;
+constexpr int G_THREADS = 192;
+constexpr int G_A_BYTES = GM * GK * 2;                 // 16 KB
+constexpr int G_STAGE_ROW = 256 + 16;                  // one staged output row (128 bf16) + pad: conflict-free 16-byte accesses
+constexpr int G_STAGING = 4 * 16 * G_STAGE_ROW;        // per warp 16 rows at a time
+
+template <int BN> struct GemmCfg {
+  static constexpr int B_BYTES = BN * GK * 2;
+  static constexpr int STAGE = G_A_BYTES + B_BYTES;
+  static constexpr int NST = BN == 256 ? 4 : 6;
+  static constexpr int SMEM = 1024 + NST * STAGE + G_STAGING + 256;
+};
+
+struct GemmParams {
+  int M, N, K;
+  int epi;                       // 0 plain, 1 qkv
+  // plain
+  __nv_bfloat16* c; int64_t ldc;
+  // qkv
+  __nv_bfloat16* out[3];         // q', k', v'  [M, H, 128]
+  const float *cos, *sin;        // [T, 64]
+  int T, H;
+  float eps;
+  unsigned flags;
+  int* status;
+};
+
+struct GemmBars {
+  uint64_t full[6], empty[6];
+  uint64_t acc_full[2], acc_empty[2];
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+template <int BN>
+__global__ void __launch_bounds__(G_THREADS, 1)
+qkv_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_w, const GemmParams p) {
+  using Cfg = GemmCfg<BN>;
+  extern __shared__ uint8_t gemm_smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(gemm_smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* stages = smem;
+  uint8_t* staging = smem + Cfg::NST * Cfg::STAGE;
+  GemmBars* bars = reinterpret_cast<GemmBars*>(staging + G_STAGING);
+  volatile int* abort_flag = &bars->abort_flag;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int m_tiles = (p.M + GM - 1) / GM, n_tiles = p.N / BN, kb_n = p.K / GK;
+  const int tiles = m_tiles * n_tiles;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < Cfg::NST; ++i) { mbar_init(&bars->full[i], 1); mbar_init(&bars->empty[i], 1); }
+    for (int i = 0; i < 2; ++i) { mbar_init(&bars->acc_full[i], 1); mbar_init(&bars->acc_empty[i], 128); }
+    bars->abort_flag = 0;
+    mbar_init_fence();
+  }
+  if (warp == 5) { tmem_alloc(&bars->tmem_base, 2 * BN); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = bars->tmem_base;
+
+  if (warp == 4) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      prefetch_tmap(&tm_x); prefetch_tmap(&tm_w);
+      uint32_t n = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
+        const int m0 = (tile / n_tiles) * GM, n0 = (tile % n_tiles) * BN;
+        for (int kb = 0; kb < kb_n; ++kb, ++n) {
+          const int st = n % Cfg::NST;
+          if (!mbar_wait(&bars->empty[st], ((n / Cfg::NST) & 1) ^ 1, abort_flag, p.status, 1)) { ok = false; break; }
+          uint8_t* dst = stages + st * Cfg::STAGE;
+          mbar_expect_tx(&bars->full[st], Cfg::STAGE);
+          tma_load_3d(dst, &tm_x, &bars->full[st], kb * GK, m0, 0);
+          tma_load_3d(dst + G_A_BYTES, &tm_w, &bars->full[st], kb * GK, n0, 0);
+        }
+      }
+    }
+  } else if (warp == 5) {
+    // ------------------------------------------------------------------ MMA issuer
+    const uint32_t leader = elect_one() ? 1u : 0u;
+    constexpr uint32_t idesc = umma_idesc_bf16(GM, BN, 0, 0);
+    const uint64_t ad = umma_desc_sw128(smem_u32(stages), 16, 1024);
+    const uint64_t bd = umma_desc_sw128(smem_u32(stages + G_A_BYTES), 16, 1024);
+    const uint32_t a_lo0 = (uint32_t)ad, b_lo0 = (uint32_t)bd, hi = (uint32_t)(ad >> 32);
+    uint32_t n = 0, it = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x, ++it) {
+      const uint32_t buf = it & 1;
+      if (!mbar_wait(&bars->acc_empty[buf], ((it >> 1) & 1) ^ 1, abort_flag, p.status, 2)) { ok = false; break; }
+      tc_fence_after();
+      const uint32_t d_tmem = tmem_base + buf * BN;
+      for (int kb = 0; kb < kb_n; ++kb, ++n) {
+        const int st = n % Cfg::NST;
+        if (!mbar_wait(&bars->full[st], (n / Cfg::NST) & 1, abort_flag, p.status, 3)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t a_lo = a_lo0 + st * (Cfg::STAGE >> 4), b_lo = b_lo0 + st * (Cfg::STAGE >> 4);
+#pragma unroll
+        for (int k = 0; k < GK / 16; ++k)
+          umma_ss_lh_p(leader, d_tmem, a_lo + k * 2, hi, b_lo + k * 2, hi, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+        tc_commit_p(leader, &bars->empty[st]);
+      }
+      if (ok) tc_commit_p(leader, &bars->acc_full[buf]);
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue: thread = output row
+    const int row = warp * 32 + lane;
+    const uint32_t lane_off = (uint32_t)(warp * 32) << 16;
+    uint8_t* stg = staging + warp * 16 * G_STAGE_ROW;
+    uint32_t it = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x, ++it) {
+      const uint32_t buf = it & 1;
+      const int m0 = (tile / n_tiles) * GM, n0 = (tile % n_tiles) * BN;
+      const int m = m0 + row;
+      ok = __all_sync(0xffffffffu, mbar_wait(&bars->acc_full[buf], (it >> 1) & 1, abort_flag, p.status, 4));
+      if (!ok) break;
+      tc_fence_after();
+#pragma unroll 1
+      for (int half = 0; half < BN / 128; ++half) {
+        uint32_t r[128];
+        const uint32_t t0 = tmem_base + lane_off + buf * BN + half * 128;
+        tmem_ld32(t0, r); tmem_ld32(t0 + 32, r + 32); tmem_ld32(t0 + 64, r + 64); tmem_ld32(t0 + 96, r + 96);
+        tc_wait_ld();
+        if (half == BN / 128 - 1) {                                // accumulator read out: the MMA warp may refill it
+          tc_fence_before();
+          mbar_arrive(&bars->acc_empty[buf]);
+        }
+        __nv_bfloat16* dst_row;                                    // this thread's output row (128 bf16)
+        if (p.epi == 1) {
+          const int nh = (n0 + half * 128) >> 7;                   // head slot among 3 H
+          const int which = nh / p.H, h = nh - which * p.H;
+          const bool do_norm = (p.flags & (which == 0 ? DAISY_NORM_Q : which == 1 ? DAISY_NORM_K : DAISY_NORM_V)) != 0;
+          if (do_norm) {
+            float ss = 0.f;
+#pragma unroll
+            for (int i = 0; i < 128; ++i) { const float x = __uint_as_float(r[i]); ss = fmaf(x, x, ss); }
+            const float rs = rsqrtf(ss * (1.0f / 128.0f) + p.eps);
+#pragma unroll
+            for (int i = 0; i < 128; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * rs);
+          }
+          if (which < 2 && (p.flags & DAISY_ROPE)) {
+            const int pos = min(m, p.M - 1) % p.T;
+            const float4* cr = reinterpret_cast<const float4*>(p.cos + (size_t)pos * 64);
+            const float4* sr = reinterpret_cast<const float4*>(p.sin + (size_t)pos * 64);
+#pragma unroll
+            for (int i4 = 0; i4 < 16; ++i4) {
+              const float4 c = cr[i4], s = sr[i4];
+              const float cc[4] = {c.x, c.y, c.z, c.w}, sn[4] = {s.x, s.y, s.z, s.w};
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                const int i = 4 * i4 + e;
+                const float a = __uint_as_float(r[i]), b2 = __uint_as_float(r[i + 64]);
+                r[i] = __float_as_uint(a * cc[e] + b2 * sn[e]);
+                r[i + 64] = __float_as_uint(b2 * cc[e] - a * sn[e]);
+              }
+            }
+          }
+          dst_row = p.out[which] + ((size_t)m * p.H + h) * 128;
+        } else {
+          dst_row = p.c + (size_t)m * p.ldc + n0 + half * 128;
+        }
+        // bf16 pack, then through the warp's staging rows so that each store instruction writes two whole rows
+        uint4 ch[16];
+#pragma unroll
+        for (int c = 0; c < 16; ++c)
+          ch[c] = make_uint4(pack_bf16(__uint_as_float(r[8 * c]), __uint_as_float(r[8 * c + 1])),
+                             pack_bf16(__uint_as_float(r[8 * c + 2]), __uint_as_float(r[8 * c + 3])),
+                             pack_bf16(__uint_as_float(r[8 * c + 4]), __uint_as_float(r[8 * c + 5])),
+                             pack_bf16(__uint_as_float(r[8 * c + 6]), __uint_as_float(r[8 * c + 7])));
+#pragma unroll
+        for (int pass = 0; pass < 2; ++pass) {
+          if ((lane >> 4) == pass) {
+#pragma unroll
+            for (int c = 0; c < 16; ++c) *reinterpret_cast<uint4*>(stg + (lane & 15) * G_STAGE_ROW + c * 16) = ch[c];
+          }
+          __syncwarp();
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int rr = 2 * i + (lane >> 4);                    // staged row, = warp row 16 pass + rr
+            const uint4 val = *reinterpret_cast<const uint4*>(stg + rr * G_STAGE_ROW + (lane & 15) * 16);
+            const int src_lane = 16 * pass + rr;
+            // the row's global address lives in the lane that owns the row
+            const unsigned long long base = __shfl_sync(0xffffffffu, (unsigned long long)reinterpret_cast<uintptr_t>(dst_row), src_lane);
+            const int mm = __shfl_sync(0xffffffffu, m, src_lane);
+            if (mm < p.M) *reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(base) + (lane & 15) * 16) = val;
+          }
+          __syncwarp();
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 5) { tc_fence_after(); tmem_dealloc(tmem_base, 2 * BN); }
+}
+
+}  // namespace daisy
+
+using namespace daisy;
+
+template <int BN>
+static int launch_gemm(const CUtensorMap& tx, const CUtensorMap& tw, const GemmParams& p, cudaStream_t st) {
+  using Cfg = GemmCfg<BN>;
+  static_assert(Cfg::SMEM <= 232448, "over the 227 KB a CTA may use");
+  static bool attr[daisy_host::MAX_DEVICES] = {};
+  const int dev = daisy_host::device_slot();
+  if (dev < 0) return DAISY_ENODEV;
+  if (!attr[dev]) {
+    if (cudaFuncSetAttribute(qkv_gemm_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM) != cudaSuccess) {
+      (void)cudaGetLastError();
+      return DAISY_ECUDA;
+    }
+    attr[dev] = true;
+  }
+  const int sms = daisy_host::sm_count_cached();
+  if (sms <= 0) return DAISY_ENODEV;
+  const int64_t tiles = (int64_t)((p.M + GM - 1) / GM) * (p.N / BN);
+  const unsigned grid = (unsigned)(tiles < sms ? tiles : sms);
+  qkv_gemm_kernel<BN><<<grid, G_THREADS, Cfg::SMEM, st>>>(tx, tw, p);
+  DAISY_CHECK_LAUNCH();
+  return DAISY_OK;
+}
+
+static int gemm_common(const void* x, int64_t ldx, const void* w, int64_t ldw, GemmParams& p, void* stream) {
+  if (!x || !w || p.M <= 0 || p.N <= 0 || p.K <= 0) return DAISY_EINVAL;
+  if (p.K % GK != 0 || p.N % 128 != 0) return DAISY_EUNSUPPORTED;
+  if (!daisy_aligned16(x) || !daisy_aligned16(w) || (ldx & 7) || (ldw & 7) || ldx < p.K || ldw < p.K) return DAISY_EALIGN;
+  const int BN = (p.N % 256 == 0) ? 256 : 128;
+  CUtensorMap tx, tw;
+  int rc;
+  if ((rc = daisy_host::make_tmap_bf16_3d(&tx, x, p.K, p.M, 1, (uint64_t)ldx * 2, (uint64_t)ldx * 2 * p.M, GK, GM)) != DAISY_OK) return rc;
+  if ((rc = daisy_host::make_tmap_bf16_3d(&tw, w, p.K, p.N, 1, (uint64_t)ldw * 2, (uint64_t)ldw * 2 * p.N, GK, BN)) != DAISY_OK) return rc;
+  return BN == 256 ? launch_gemm<256>(tx, tw, p, (cudaStream_t)stream) : launch_gemm<128>(tx, tw, p, (cudaStream_t)stream);
+}
+
+extern "C" int daisy_b200_gemm_nt(const void* x, int64_t ldx, const void* w, int64_t ldw, void* c, int64_t ldc,
+                                  int M, int N, int K, int* status_word, void* stream) {
+  if (!c) return DAISY_EINVAL;
+  if (!daisy_aligned16(c) || (ldc & 7) || ldc < N) return DAISY_EALIGN;
+  GemmParams p{};
+  p.M = M; p.N = N; p.K = K; p.epi = 0;
+  p.c = (__nv_bfloat16*)c; p.ldc = ldc; p.status = status_word;
+  return gemm_common(x, ldx, w, ldw, p, stream);
+}
+
+extern "C" int daisy_b200_qkv_gemm(const void* x, int64_t ldx, const void* w_qkv, int64_t ldw,
+                                   const float* cos, const float* sin,
+                                   void* q_out, void* k_out, void* v_out,
+                                   int B, int T, int H, int D, int dim, float eps, unsigned flags,
+                                   int* status_word, void* stream) {
+  if (!q_out || !k_out || !v_out || B <= 0 || T <= 0 || H <= 0) return DAISY_EINVAL;
+  if (D != DAISY_HEAD_DIM) return DAISY_EUNSUPPORTED;
+  if ((int64_t)B * T >= (int64_t)1 << 31) return DAISY_EUNSUPPORTED;
+  if (flags & ~DAISY_QKV_DEFAULT) return DAISY_EINVAL;
+  if ((flags & DAISY_ROPE) && (!cos || !sin)) return DAISY_EINVAL;
+  if ((flags & DAISY_ROPE) && (!daisy_aligned16(cos) || !daisy_aligned16(sin))) return DAISY_EALIGN;
+  if (!daisy_aligned16(q_out) || !daisy_aligned16(k_out) || !daisy_aligned16(v_out)) return DAISY_EALIGN;
+  GemmParams p{};
+  p.M = B * T; p.N = 3 * H * D; p.K = dim; p.epi = 1;
+  p.out[0] = (__nv_bfloat16*)q_out; p.out[1] = (__nv_bfloat16*)k_out; p.out[2] = (__nv_bfloat16*)v_out;
+  p.cos = cos; p.sin = sin; p.T = T; p.H = H; p.eps = eps; p.flags = flags; p.status = status_word;
+  return gemm_common(x, ldx, w_qkv, ldw, p, stream);
+}

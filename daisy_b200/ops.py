@@ -88,6 +88,45 @@ def qkv_prep(q, k, v, cos, sin, eps: float, flags: int = QKV_DEFAULT, bhtd: bool
     return tuple(outs)
 
 
+def qkv_gemm(x, w_qkv, cos, sin, num_heads: int, eps: float, flags: int = QKV_DEFAULT):
+    """``x [B,T,dim]`` times the merged ``w_qkv [3*H*128, dim]`` (``qkvo_w[:3].flatten(end_dim=1)``) with the RMS
+    norm and RoPE applied in the GEMM epilogue: returns prepared ``q', k', v'`` as ``[B,T,H,128]`` contiguous."""
+    _req(x, "x"); _req(w_qkv, "w_qkv")
+    B, T, dim = x.shape
+    H, D = int(num_heads), 128
+    if w_qkv.shape != (3 * H * D, dim):
+        raise ValueError(f"w_qkv must be [{3 * H * D}, {dim}], got {tuple(w_qkv.shape)}")
+    x2 = x.reshape(B * T, dim)
+    if x2.stride(1) != 1:
+        x2 = x2.contiguous()
+    if flags & ROPE:
+        cos, sin = _f32c(cos, "cos"), _f32c(sin, "sin")
+        assert cos.shape[0] >= T and cos.shape[1] == D // 2
+    outs = [torch.empty(B, T, H, D, dtype=torch.bfloat16, device=x.device) for _ in range(3)]
+    rc = _lib.lib().daisy_b200_qkv_gemm(
+        x2.data_ptr(), x2.stride(0), w_qkv.data_ptr(), w_qkv.stride(0),
+        cos.data_ptr() if cos is not None else None, sin.data_ptr() if sin is not None else None,
+        outs[0].data_ptr(), outs[1].data_ptr(), outs[2].data_ptr(), B, T, H, D, dim, eps, flags,
+        status_word(x.device).data_ptr(), _stream(x))
+    _lib.check(rc, "daisy_b200_qkv_gemm")
+    return tuple(outs)
+
+
+def gemm_nt(x, w):
+    """``x [..., K] @ w[N, K]^T`` in bf16 with fp32 accumulation (``F.linear(x, w)``) on the tcgen05 GEMM kernel."""
+    _req(x, "x"); _req(w, "w")
+    K = x.shape[-1]
+    x2 = x.reshape(-1, K)
+    if x2.stride(1) != 1:
+        x2 = x2.contiguous()
+    M, N = x2.shape[0], w.shape[0]
+    c = torch.empty(M, N, dtype=torch.bfloat16, device=x.device)
+    rc = _lib.lib().daisy_b200_gemm_nt(x2.data_ptr(), x2.stride(0), w.data_ptr(), w.stride(0), c.data_ptr(), c.stride(0),
+                                       M, N, K, status_word(x.device).data_ptr(), _stream(x))
+    _lib.check(rc, "daisy_b200_gemm_nt")
+    return c.view(*x.shape[:-1], N)
+
+
 def _doc_arg(doc_start: Optional[torch.Tensor], B: int, T: int, device):
     """``doc_start`` ([T] shared by the batch, or [B,T]) -> (int32 contiguous tensor or None, pointer, batch stride)."""
     if doc_start is None:

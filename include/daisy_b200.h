@@ -88,6 +88,27 @@ int daisy_b200_qkv_prep(const void* q, const void* k, const void* v,
                         int B, int T, int H, int D, float eps, unsigned flags, void* stream);
 
 /* ---------------------------------------------------------------------------------------------
+ * The merged QKV projection with its element-wise tail fused: replaces F.linear(x, qkvo_w[:3].flatten(0,1)),
+ * the head split and the norm / RoPE of CausalSelfAttention._calc_qkv in one kernel
+ * (models/daisy/attention.py:116-127), i.e. the GEMM plus daisy_b200_qkv_prep.
+ *   x          [B*T, dim] bf16, row stride ldx (elements)
+ *   w_qkv      [3*H*D, dim] bf16, row stride ldw: rows h*D.. of the first H*D rows are head h of q, then k, then v
+ *              (the layout of qkvo_w[:3].flatten(end_dim=1))
+ *   q_out,k_out,v_out   [B,T,H,D] bf16 contiguous, normalised (flags) and rotated (q, k)
+ * dim must be a multiple of 64, D = 128.  flags: DAISY_NORM_Q | DAISY_NORM_K | DAISY_NORM_V | DAISY_ROPE.
+ */
+int daisy_b200_qkv_gemm(const void* x, int64_t ldx, const void* w_qkv, int64_t ldw,
+                        const float* cos, const float* sin,
+                        void* q_out, void* k_out, void* v_out,
+                        int B, int T, int H, int D, int dim, float eps, unsigned flags,
+                        int* status_word, void* stream);
+
+/* C[M,N] = X[M,K] W[N,K]^T, bf16 in and out, fp32 accumulation: F.linear(y, qkvo_w[3]), the output projection
+ * (models/daisy/attention.py:149).  K a multiple of 64, N a multiple of 128; ld* are row strides in elements. */
+int daisy_b200_gemm_nt(const void* x, int64_t ldx, const void* w, int64_t ldw, void* c, int64_t ldc,
+                       int M, int N, int K, int* status_word, void* stream);
+
+/* ---------------------------------------------------------------------------------------------
  * Sliding-window causal softmax attention, prefill form.
  * Replaces CausalSelfAttention._sdpa_common between the two projections
  * (models/daisy/attention.py:141-148) with the mask of build_attn_mask

@@ -1,0 +1,73 @@
+"""The tcgen05 projection GEMM: plain bf16 output (the output projection) and the QKV form whose epilogue applies
+the RMS norm and RoPE (the merged projection plus the element-wise tail of ``_calc_qkv``), against fp32 matmuls
+and the oracle's transform on the same bf16 inputs."""
+import pytest
+import torch
+
+from gpu_util import bf16_randn, assert_close_bf16
+from oracle import swa
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (300, 256, 128), (77, 384, 192), (1000, 2048, 768), (4096, 768, 2048)])
+def test_gemm_nt_matches_fp32_matmul(M, N, K):
+    from daisy_b200 import ops
+    x = bf16_randn(M, K, seed=M) * 0.5
+    w = bf16_randn(N, K, seed=N + 1) * (K ** -0.5)
+    c = ops.gemm_nt(x, w)
+    ops.check_device_status(x.device)
+    ref = x.float().cpu() @ w.float().cpu().t()
+    assert_close_bf16(c, ref, f"gemm {M}x{N}x{K}")
+
+
+def test_gemm_nt_strided_rows_and_batch_shape():
+    from daisy_b200 import ops
+    xw = bf16_randn(3, 50, 2 * 256, seed=4)
+    x = xw[..., :256]                                              # row stride 512
+    w = bf16_randn(512, 256, seed=5) * 0.06
+    c = ops.gemm_nt(x, w)
+    assert c.shape == (3, 50, 512)
+    assert_close_bf16(c, x.float().cpu() @ w.float().cpu().t(), "strided")
+
+
+@pytest.mark.parametrize("B,T,H,dim", [(1, 128, 2, 256), (2, 300, 2, 256), (1, 1024, 6, 768), (3, 77, 3, 384)])
+def test_qkv_gemm_epilogue_matches_oracle(B, T, H, dim):
+    """H = 3 makes 3*H*128 = 1152 columns, not a multiple of 256: the 128-column tile variant."""
+    from daisy_b200 import ops
+    D = 128
+    x = bf16_randn(B, T, dim, seed=T)
+    w = bf16_randn(3 * H * D, dim, seed=dim) * (dim ** -0.5)
+    cos, sin = swa.rope_tables(D, T)
+    qp, kp, vp = ops.qkv_gemm(x, w, cos.cuda(), sin.cuda(), H, swa.FP32_EPS)
+    ops.check_device_status(x.device)
+    qkv = (x.float().cpu() @ w.float().cpu().t()).view(B, T, 3 * H, D)
+    q, k, v = qkv.chunk(3, dim=-2)
+    qn, kn, vn = swa.qkv_transform(q, k, v, cos, sin, swa.FP32_EPS)
+    assert_close_bf16(qp, qn, "q'")
+    assert_close_bf16(kp, kn, "k'")
+    assert_close_bf16(vp, vn, "v'")
+
+
+def test_module_forward_native_gemm_matches_library_gemm_path(golden_dir):
+    """``native_gemm=True`` (the default) runs the whole forward on hand-written kernels (fused QKV GEMM, attention, output
+    GEMM); same result as the cuBLAS-projection path within bf16 rounding, and the reference fixture's bar."""
+    import os
+    import numpy as np
+    from daisy_b200 import B200CausalSelfAttention, WindowMask
+    z = np.load(os.path.join(golden_dir, "csa_prefill_small.npz"))
+    H, D, W = int(z["heads"]), int(z["head_dim"]), int(z["window"])
+    os.environ["DISABLE_O_ZERO_INIT"] = "1"
+    m = B200CausalSelfAttention(H * D, H, D).cuda().eval()
+    m.norm_eps = swa.FP32_EPS
+    with torch.no_grad():
+        m.qkvo_w.copy_(torch.from_numpy(z["qkvo_w"]).to(m.qkvo_w.dtype))
+    x = torch.from_numpy(z["x"]).bfloat16().cuda()
+    with torch.inference_mode():
+        m.native_gemm = False
+        y_lib = m(x, None, attn_mask=WindowMask(W))
+        m.native_gemm = True
+        y_nat = m(x, None, attn_mask=WindowMask(W))
+    ref = torch.from_numpy(z["y"])
+    assert_close_bf16(y_nat, ref, "native forward vs reference fixture", max_tol=4e-2, mean_tol=4e-3)
+    assert_close_bf16(y_nat, y_lib.float().cpu(), "native vs cuBLAS projections", max_tol=3e-2, mean_tol=3e-3)
