@@ -377,6 +377,49 @@ def generator_step_latency(H, D, W, layers=4, batch=1, steps=200):
     return res
 
 
+def run_projection(B, T, H, D, steps, warmup, lean=False):
+    """The GEMMs either side of the attention at the headline shape (the module's forward = fused QKV GEMM +
+    attention + output GEMM): the hand-written tcgen05 GEMM whose epilogue applies the norm and RoPE, against
+    cuBLAS followed by the separate norm/RoPE pass.  Not part of the headline step (BASELINE's config starts
+    from q, k, v after the projection); reported beside it."""
+    import torch.nn.functional as F
+    from daisy_b200 import ops
+    from oracle import swa
+    dev = torch.device("cuda", torch.cuda.current_device())
+    dim = H * D
+    g = torch.Generator(device=dev).manual_seed(7)
+    x = torch.randn(B, T, dim, device=dev, generator=g).bfloat16()
+    w = (torch.randn(4, dim, dim, device=dev, generator=g) * dim ** -0.5).bfloat16()
+    wq = w[:3].flatten(end_dim=1)
+    cos, sin = rope_full(D, T, dev)
+
+    def ours():
+        return ops.qkv_gemm(x, wq, cos, sin, H, swa.FP32_EPS)
+
+    ms = timed_steps(ours, steps, warmup, None) / steps
+    flops = 2.0 * B * T * dim * 3 * dim
+    res = {"name": "qkv_gemm", "ms_per_step": ms, "tflops": flops / (ms * 1e-3) / 1e12,
+           "value": flops / (ms * 1e-3) / 1e12, "unit": "TFLOP/s", "steps": steps,
+           "config": {"workload": f"qkv_gemm: x [{B},{T},{dim}] x W_qkv [{3 * dim},{dim}]^T, norm + RoPE in the epilogue"}}
+    if lean:
+        res.update({"clocks": None, "roofline": None, "e2e": None, "launches_per_step": 1})
+        return res
+
+    def lib():
+        q, k, v = F.linear(x, wq).view(B, T, 3 * H, D).chunk(3, dim=-2)
+        return ops.qkv_prep(q, k, v, cos, sin, swa.FP32_EPS)
+
+    y = torch.randn(B, T, dim, device=dev, generator=g).bfloat16()
+    res["cublas_plus_prep_ms"] = timed_steps(lib, steps, warmup, None) / steps
+    res["cublas_gemm_alone_ms"] = timed_steps(lambda: F.linear(x, wq), steps, warmup, None) / steps
+    o_ms = timed_steps(lambda: ops.gemm_nt(y, w[3]), steps, warmup, None) / steps
+    res["out_proj"] = {"ms": o_ms, "tflops": 2.0 * B * T * dim * dim / (o_ms * 1e-3) / 1e12,
+                       "cublas_ms": timed_steps(lambda: F.linear(y, w[3]), steps, warmup, None) / steps}
+    a, b = ours(), lib()
+    res["max_abs_diff_vs_library_path"] = max(float((a[i].float() - b[i].float()).abs().max()) for i in range(3))
+    return res
+
+
 # ----------------------------------------------------------------------------- our arm: KDA
 
 def run_kda(cfg, steps, warmup, dist, rank, world, peaks, lean=False):
@@ -483,7 +526,7 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="all", choices=["all", "prefill_c2", "prefill_c4", "decode_c3", "kda_c5", "prefill_small", "decode_small", "kda_small"])
+    ap.add_argument("--workload", default="all", choices=["all", "prefill_c2", "prefill_c4", "decode_c3", "kda_c5", "prefill_small", "decode_small", "kda_small", "gemm_small"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extras", action="store_true",
                     help="skip the measurements beside the three workloads (generator-step latency): launch-list captures")
@@ -508,12 +551,18 @@ def main():
         res = run_prefill(PREFILL_C2, args.steps, warm, dist, rank, world, peaks, "prefill_c2")
     if want == "prefill_small":
         res = run_prefill(PREFILL_SMALL, args.steps, args.warmup, dist, rank, world, peaks, "prefill_small", lean=True)
+    if want == "gemm_small":
+        res = run_projection(1, 8192, 16, 128, args.steps, args.warmup, lean=True)
     if want == "decode_small":
         res = run_decode(DECODE_SMALL, args.warmup, dist, rank, world, peaks, lean=True)
     if want == "kda_small":
         res = run_kda(KDA_SMALL, args.steps, args.warmup, dist, rank, world, peaks, lean=True)
     if want == "prefill_c4":
         res = run_prefill(PREFILL_C4, max(2, args.steps // 4), warm, dist, rank, world, peaks, "prefill_c4")
+    if want == "all" and rank == 0 and not args.no_extras:
+        torch.cuda.empty_cache()
+        extra["projection"] = run_projection(PREFILL_C2["B"], PREFILL_C2["T"], PREFILL_C2["H"], PREFILL_C2["D"],
+                                             max(5, args.steps // 2), warm)
     if want in ("all", "decode_c3"):
         torch.cuda.empty_cache()
         d = run_decode(DECODE_C3, warm, dist, rank, world, peaks, extras=not args.no_extras)
