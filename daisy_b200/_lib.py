@@ -14,6 +14,7 @@ LIB_PATH = os.path.join(_HERE, "libdaisy_b200.so")
 OK, EINVAL, EUNSUPPORTED, EALIGN, EWORKSPACE, ECUDA, ETIMEOUT, ENODEV = 0, -1, -2, -3, -4, -5, -6, -7
 NORM_Q, NORM_K, NORM_V, ROPE, QKV_DEFAULT, WRITE_RING, OUT_BTHD, KV_BHTD, Q_IN_KERNEL, BOUNDED_QK = 1, 2, 4, 8, 15, 16, 32, 64, 128, 256
 WINDOW_BLOCKS = 512
+CACHE_FP16 = 1024
 KDA_L2NORM_QK, KDA_OUT_FP32 = 1, 2
 KDA_GATE_ROUND_BF16 = 1
 
@@ -25,7 +26,7 @@ SIGNATURES = {
     "daisy_b200_strerror": (C.c_char_p, [_i]),
     "daisy_b200_sm_count": (_i, []),
     "daisy_b200_qkv_prep": (_i, [_vp] * 3 + [_i64] * 9 + [_vp] * 2 + [_vp] * 3 + [_vp] + [_i64] * 3 + [_vp] + [_i] * 4 + [_f, _u, _vp]),
-    "daisy_b200_qkv_gemm": (_i, [_vp, _i64, _vp, _i64, _vp, _vp, _vp, _vp, _vp] + [_i] * 5 + [_f, _u, _vp, _vp]),
+    "daisy_b200_qkv_gemm": (_i, [_vp, _i64, _vp, _i64, _vp, _vp, _vp, _vp, _vp] + [_vp, _i64, _vp] + [_i] * 5 + [_f, _u, _vp, _vp]),
     "daisy_b200_gemm_nt": (_i, [_vp, _i64, _vp, _i64, _vp, _i64, _i, _i, _i, _vp, _vp]),
     "daisy_b200_swa_prefill_workspace_bytes": (_sz, [_i] * 4),
     "daisy_b200_swa_prefill_fwd": (_i, [_vp] * 3 + [_i64] * 9 + [_vp] * 2 + [_vp] + [_i64] * 3 + [_vp] * 2 +

@@ -132,8 +132,7 @@ class B200CausalSelfAttention(nn.Module):
         self.receives_ve = receives_ve
         # True (default): forward / prefill run the projections on this library's tcgen05 GEMM, the norm and RoPE in
         # the QKV epilogue (measured faster than cuBLAS followed by the norm/RoPE pass); False or
-        # DAISY_NATIVE_GEMM=0: F.linear (cuBLAS) + qkv_prep.  Layers with a value embedding and single-token
-        # steps always take the F.linear form.
+        # DAISY_NATIVE_GEMM=0: F.linear (cuBLAS) + qkv_prep.  Single-token steps always take the F.linear form.
         self.native_gemm = os.environ.get("DAISY_NATIVE_GEMM", "1") == "1"
         if receives_ve:
             init = {0: 0.3228, 1: 0.0, 2: -1.5163, 21: -2.4423, 22: -2.9444, 23: 10.0}.get(layer_idx, 0.0) \
@@ -173,10 +172,16 @@ class B200CausalSelfAttention(nn.Module):
         in_blocks = len(mask) > 2 and mask[2]
         B, T = x.size(0), x.size(1)
         cos, sin = self.rotary.tables(T)
-        if self.native_gemm and not self.receives_ve and self.m_dim % 64 == 0:
-            # every kernel hand-written: QKV GEMM with norm + RoPE in its epilogue, attention, output GEMM
+        if self.native_gemm and self.m_dim % 64 == 0:
+            # every kernel hand-written: QKV GEMM with norm + RoPE (+ the value-embedding gate) in its epilogue,
+            # attention, output GEMM
             w = self.qkvo_w
-            qp, kp, vp = ops.qkv_gemm(x.to(w.dtype), w[:3].flatten(end_dim=1), cos, sin, self.num_heads, self.norm_eps)
+            ve_kw = {}
+            if self.receives_ve:
+                torch._assert(ve is not None, "ve must be provided when receives_ve=True")
+                ve_kw = dict(ve=ve.to(torch.bfloat16), ve_gate_logit=self.g_ve.detach().float().reshape(1))
+            qp, kp, vp = ops.qkv_gemm(x.to(w.dtype), w[:3].flatten(end_dim=1), cos, sin, self.num_heads, self.norm_eps,
+                                      **ve_kw)
             y = ops.swa_attend(qp, kp, vp, window, self.attn_scale, bounded_qk=True, doc_start=doc_start,
                                window_in_blocks=in_blocks)
             y = ops.gemm_nt(y.view(B, T, self.m_dim), w[3])

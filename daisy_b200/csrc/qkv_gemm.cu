@@ -40,6 +40,9 @@ struct GemmParams {
   // qkv
   __nv_bfloat16* out[3];         // q', k', v'  [M, H, 128]
   const float *cos, *sin;        // [T, 64]
+  const __nv_bfloat16* ve;       // value embedding [M, H, 128] (row stride ve_ld elements) or null
+  int64_t ve_ld;
+  const float* ve_gate_logit;    // v' = g * norm(v) + (1 - g) * ve, g = sigmoid(*ve_gate_logit)
   int T, H;
   float eps;
   unsigned flags;
@@ -178,6 +181,17 @@ qkv_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant_
               }
             }
           }
+          if (which == 2 && p.ve) {                                // value-embedding gate on the normalised v
+            const float gte = 1.0f / (1.0f + __expf(-*p.ve_gate_logit));
+            const uint4* vr = reinterpret_cast<const uint4*>(p.ve + (size_t)min(m, p.M - 1) * p.ve_ld + h * 128);
+#pragma unroll
+            for (int c = 0; c < 16; ++c) {
+              float f[8];
+              unpack8(vr[c], f);
+#pragma unroll
+              for (int e = 0; e < 8; ++e) r[8 * c + e] = __float_as_uint(gte * __uint_as_float(r[8 * c + e]) + (1.0f - gte) * f[e]);
+            }
+          }
           dst_row = p.out[which] + ((size_t)m * p.H + h) * 128;
         } else {
           dst_row = p.c + (size_t)m * p.ldc + n0 + half * 128;
@@ -270,6 +284,7 @@ extern "C" int daisy_b200_gemm_nt(const void* x, int64_t ldx, const void* w, int
 extern "C" int daisy_b200_qkv_gemm(const void* x, int64_t ldx, const void* w_qkv, int64_t ldw,
                                    const float* cos, const float* sin,
                                    void* q_out, void* k_out, void* v_out,
+                                   const void* ve, int64_t ve_ld, const float* ve_gate_logit,
                                    int B, int T, int H, int D, int dim, float eps, unsigned flags,
                                    int* status_word, void* stream) {
   if (!q_out || !k_out || !v_out || B <= 0 || T <= 0 || H <= 0) return DAISY_EINVAL;
@@ -279,7 +294,9 @@ extern "C" int daisy_b200_qkv_gemm(const void* x, int64_t ldx, const void* w_qkv
   if ((flags & DAISY_ROPE) && (!cos || !sin)) return DAISY_EINVAL;
   if ((flags & DAISY_ROPE) && (!daisy_aligned16(cos) || !daisy_aligned16(sin))) return DAISY_EALIGN;
   if (!daisy_aligned16(q_out) || !daisy_aligned16(k_out) || !daisy_aligned16(v_out)) return DAISY_EALIGN;
+  if (ve && (!ve_gate_logit || !daisy_aligned16(ve) || (ve_ld & 7) || ve_ld < (int64_t)H * D)) return ve_gate_logit ? DAISY_EALIGN : DAISY_EINVAL;
   GemmParams p{};
+  p.ve = (const __nv_bfloat16*)ve; p.ve_ld = ve_ld; p.ve_gate_logit = ve_gate_logit;
   p.M = B * T; p.N = 3 * H * D; p.K = dim; p.epi = 1;
   p.out[0] = (__nv_bfloat16*)q_out; p.out[1] = (__nv_bfloat16*)k_out; p.out[2] = (__nv_bfloat16*)v_out;
   p.cos = cos; p.sin = sin; p.T = T; p.H = H; p.eps = eps; p.flags = flags; p.status = status_word;

@@ -10,10 +10,24 @@
 // writes the output and stores the new k,v row into the ring -- after every read of pass 1 has
 // completed, so a window larger than the ring capacity still sees the row it is about to overwrite.
 #include "rowops.cuh"
+#include <cuda_fp16.h>
 
 namespace daisy {
 
 #define DEC_NEG (-1.0e30f)
+
+// eight 16-bit cache values -> fp32: bf16 (the model dtype) or fp16 (the reference Generator's default cache
+// dtype, inference/generate.py:62)
+template <bool F16>
+__device__ __forceinline__ void unpack8_cache(const uint4& u, float* f) {
+  if (F16) {
+    const __half2* h = reinterpret_cast<const __half2*>(&u);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { const float2 t = __half22float2(h[i]); f[2 * i] = t.x; f[2 * i + 1] = t.y; }
+  } else {
+    unpack8(u, f);
+  }
+}
 
 struct DecodeParams {
   const __nv_bfloat16 *q, *k, *v;
@@ -64,7 +78,7 @@ __device__ __forceinline__ DecodeGeom decode_geom(const DecodeParams& p) {
   return g;
 }
 
-template <bool DEV>
+template <bool DEV, bool F16>
 __global__ void __launch_bounds__(128) swa_decode_partial_kernel(const DecodeParams p) {
   const int s = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, hw = lane >> 4, sub = lane & 15;
@@ -101,7 +115,7 @@ __global__ void __launch_bounds__(128) swa_decode_partial_kernel(const DecodePar
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       float kf[8];
-      unpack8(kk[j], kf);
+      unpack8_cache<F16>(kk[j], kf);
       float d = 0.f;
 #pragma unroll
       for (int e = 0; e < 8; ++e) d = fmaf(qf[e], kf[e], d);
@@ -119,7 +133,7 @@ __global__ void __launch_bounds__(128) swa_decode_partial_kernel(const DecodePar
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       float vf[8];
-      unpack8(vv[j], vf);
+      unpack8_cache<F16>(vv[j], vf);
 #pragma unroll
       for (int e = 0; e < 8; ++e) acc[e] = fmaf(pj[j], vf[e], acc[e]);
     }
@@ -171,7 +185,7 @@ __device__ __forceinline__ float block128_sum(float x, float* red) {
   return (red[0] + red[1]) + (red[2] + red[3]);
 }
 
-template <bool DEV>
+template <bool DEV, bool F16>
 __global__ void __launch_bounds__(128) swa_decode_combine_kernel(const DecodeParams p) {
   const int h = blockIdx.x, b = blockIdx.y, d = threadIdx.x;
   const DecodeGeom g = decode_geom<DEV>(p);
@@ -194,7 +208,9 @@ __global__ void __launch_bounds__(128) swa_decode_combine_kernel(const DecodePar
   }
   // the new row is used at the precision it will have in the cache
   const __nv_bfloat16 kb = __float2bfloat16_rn(k), vb = __float2bfloat16_rn(v);
-  k = __bfloat162float(kb); v = __bfloat162float(vb);
+  const __half kh = __float2half_rn(k), vh = __float2half_rn(v);
+  k = F16 ? __half2float(kh) : __bfloat162float(kb);
+  v = F16 ? __half2float(vh) : __bfloat162float(vb);
   const float s_self = block128_sum(q * p.qscale * k, red);
 
   const int64_t base = ((int64_t)b * p.H + h) * p.splits;
@@ -212,8 +228,9 @@ __global__ void __launch_bounds__(128) swa_decode_combine_kernel(const DecodePar
   if (p.k_new_out) p.k_new_out[row] = kb;
   if (p.v_new_out) p.v_new_out[row] = vb;
   if (p.flags & DAISY_WRITE_RING) {
-    p.kc[b * p.c_sb + h * p.c_sh + (int64_t)g.new_slot * p.c_sr + d] = kb;
-    p.vc[b * p.c_sb + h * p.c_sh + (int64_t)g.new_slot * p.c_sr + d] = vb;
+    const int64_t at = b * p.c_sb + h * p.c_sh + (int64_t)g.new_slot * p.c_sr + d;
+    if (F16) { reinterpret_cast<__half*>(p.kc)[at] = kh; reinterpret_cast<__half*>(p.vc)[at] = vh; }
+    else     { p.kc[at] = kb; p.vc[at] = vb; }
   }
 }
 
@@ -289,11 +306,13 @@ static int decode_launch(const void* q_new, const void* k_new, const void* v_new
   p.t_dev = (const long long*)t_dev; p.window = window; p.table_rows = table_rows; p.status = status_word;
 
   cudaStream_t st = (cudaStream_t)stream;
-  if (t_dev) swa_decode_partial_kernel<true><<<dim3(splits, H, B), 128, 0, st>>>(p);
-  else       swa_decode_partial_kernel<false><<<dim3(splits, H, B), 128, 0, st>>>(p);
+  const bool f16 = (flags & DAISY_CACHE_FP16) != 0;
+  const dim3 g1(splits, H, B), g2(H, B);
+  if (t_dev) { if (f16) swa_decode_partial_kernel<true, true><<<g1, 128, 0, st>>>(p); else swa_decode_partial_kernel<true, false><<<g1, 128, 0, st>>>(p); }
+  else       { if (f16) swa_decode_partial_kernel<false, true><<<g1, 128, 0, st>>>(p); else swa_decode_partial_kernel<false, false><<<g1, 128, 0, st>>>(p); }
   DAISY_CHECK_LAUNCH();
-  if (t_dev) swa_decode_combine_kernel<true><<<dim3(H, B), 128, 0, st>>>(p);
-  else       swa_decode_combine_kernel<false><<<dim3(H, B), 128, 0, st>>>(p);
+  if (t_dev) { if (f16) swa_decode_combine_kernel<true, true><<<g2, 128, 0, st>>>(p); else swa_decode_combine_kernel<true, false><<<g2, 128, 0, st>>>(p); }
+  else       { if (f16) swa_decode_combine_kernel<false, true><<<g2, 128, 0, st>>>(p); else swa_decode_combine_kernel<false, false><<<g2, 128, 0, st>>>(p); }
   DAISY_CHECK_LAUNCH();
   return DAISY_OK;
 }

@@ -88,9 +88,12 @@ def qkv_prep(q, k, v, cos, sin, eps: float, flags: int = QKV_DEFAULT, bhtd: bool
     return tuple(outs)
 
 
-def qkv_gemm(x, w_qkv, cos, sin, num_heads: int, eps: float, flags: int = QKV_DEFAULT):
+def qkv_gemm(x, w_qkv, cos, sin, num_heads: int, eps: float, flags: int = QKV_DEFAULT,
+             ve: Optional[torch.Tensor] = None, ve_gate_logit: Optional[torch.Tensor] = None):
     """``x [B,T,dim]`` times the merged ``w_qkv [3*H*128, dim]`` (``qkvo_w[:3].flatten(end_dim=1)``) with the RMS
-    norm and RoPE applied in the GEMM epilogue: returns prepared ``q', k', v'`` as ``[B,T,H,128]`` contiguous."""
+    norm and RoPE applied in the GEMM epilogue: returns prepared ``q', k', v'`` as ``[B,T,H,128]`` contiguous.
+    ``ve [B,T,H*128]`` (bf16) with ``ve_gate_logit`` (float32 scalar on the device) mixes the value embedding into
+    the normalised v: ``v' = g * norm(v) + (1 - g) * ve``."""
     _req(x, "x"); _req(w_qkv, "w_qkv")
     B, T, dim = x.shape
     H, D = int(num_heads), 128
@@ -102,11 +105,18 @@ def qkv_gemm(x, w_qkv, cos, sin, num_heads: int, eps: float, flags: int = QKV_DE
     if flags & ROPE:
         cos, sin = _f32c(cos, "cos"), _f32c(sin, "sin")
         assert cos.shape[0] >= T and cos.shape[1] == D // 2
+    ve_args = (None, 0, None)
+    if ve is not None:
+        if ve_gate_logit is None or not (ve_gate_logit.is_cuda and ve_gate_logit.dtype == torch.float32 and ve_gate_logit.numel() == 1):
+            raise ValueError("ve needs ve_gate_logit, a float32 scalar CUDA tensor")
+        ve2 = ve.reshape(B * T, H * D)
+        _req(ve2, "ve")
+        ve_args = (ve2.data_ptr(), ve2.stride(0), ve_gate_logit.data_ptr())
     outs = [torch.empty(B, T, H, D, dtype=torch.bfloat16, device=x.device) for _ in range(3)]
     rc = _lib.lib().daisy_b200_qkv_gemm(
         x2.data_ptr(), x2.stride(0), w_qkv.data_ptr(), w_qkv.stride(0),
         cos.data_ptr() if cos is not None else None, sin.data_ptr() if sin is not None else None,
-        outs[0].data_ptr(), outs[1].data_ptr(), outs[2].data_ptr(), B, T, H, D, dim, eps, flags,
+        outs[0].data_ptr(), outs[1].data_ptr(), outs[2].data_ptr(), *ve_args, B, T, H, D, dim, eps, flags,
         status_word(x.device).data_ptr(), _stream(x))
     _lib.check(rc, "daisy_b200_qkv_gemm")
     return tuple(outs)
@@ -234,8 +244,10 @@ def swa_decode_step(q_new, k_new, v_new, kcache, vcache, t: int, cap: int, windo
         out = torch.empty(B, 1, H, D, dtype=torch.bfloat16, device=q_new.device)
     k_o = torch.empty(B, 1, H, D, dtype=torch.bfloat16, device=q_new.device) if return_new_kv else None
     v_o = torch.empty(B, 1, H, D, dtype=torch.bfloat16, device=q_new.device) if return_new_kv else None
+    cache_f16 = kcache is not None and kcache.dtype == torch.float16
     if kcache is not None:
-        _req(kcache, "kcache"); _req(vcache, "vcache")
+        _req(kcache, "kcache", kcache.dtype if cache_f16 else torch.bfloat16)
+        _req(vcache, "vcache", kcache.dtype if cache_f16 else torch.bfloat16)
         assert kcache.shape == vcache.shape and kcache.stride() == vcache.stride()
         kc_ptr, vc_ptr = kcache.data_ptr(), vcache.data_ptr()
         c_sb, c_sh, c_sr = kcache.stride(0), kcache.stride(1), kcache.stride(2)
@@ -244,7 +256,7 @@ def swa_decode_step(q_new, k_new, v_new, kcache, vcache, t: int, cap: int, windo
         c_sb = c_sh = c_sr = 0
     if flags & ROPE:
         cos_row, sin_row = _f32c(cos_row, "cos_row"), _f32c(sin_row, "sin_row")
-    f = flags | (WRITE_RING if write_ring else 0)
+    f = flags | (WRITE_RING if write_ring else 0) | (_lib.CACHE_FP16 if cache_f16 else 0)
     rc = L.daisy_b200_swa_decode_step(
         q_new.data_ptr(), k_new.data_ptr(), v_new.data_ptr(),
         q_new.stride(0), q_new.stride(2), k_new.stride(0), k_new.stride(2), v_new.stride(0), v_new.stride(2),
@@ -265,8 +277,11 @@ def swa_decode_step_dev(q_new, k_new, v_new, kcache, vcache, t_dev: torch.Tensor
     """:func:`swa_decode_step` with the position in device memory (``t_dev``: int64 tensor of one element), so the
     launch can sit inside a CUDA graph and be replayed for every token.  ``cos_table, sin_table`` are whole
     ``[rows, D/2]`` tables; the kernels pick row ``t_dev[0]``.  Returns ``y [B,1,H,D]``."""
-    for n, x in (("q_new", q_new), ("k_new", k_new), ("v_new", v_new), ("kcache", kcache), ("vcache", vcache)):
+    for n, x in (("q_new", q_new), ("k_new", k_new), ("v_new", v_new)):
         _req(x, n)
+    cache_f16 = kcache.dtype == torch.float16
+    _req(kcache, "kcache", kcache.dtype if cache_f16 else torch.bfloat16)
+    _req(vcache, "vcache", kcache.dtype if cache_f16 else torch.bfloat16)
     if not (t_dev.is_cuda and t_dev.dtype == torch.int64 and t_dev.numel() == 1):
         raise ValueError("t_dev must be an int64 CUDA tensor with one element")
     B, one, H, D = q_new.shape
@@ -287,7 +302,8 @@ def swa_decode_step_dev(q_new, k_new, v_new, kcache, vcache, t_dev: torch.Tensor
         kcache.data_ptr(), vcache.data_ptr(), kcache.stride(0), kcache.stride(1), kcache.stride(2),
         t_dev.data_ptr(), int(cap), int(window or 0), cos_table.data_ptr(), sin_table.data_ptr(), cos_table.shape[0],
         out.data_ptr(), out.stride(0), out.stride(2), None, None,
-        B, H, D, scale, eps, flags | (WRITE_RING if write_ring else 0), workspace.data_ptr(), workspace.numel(), splits,
+        B, H, D, scale, eps, flags | (WRITE_RING if write_ring else 0) | (_lib.CACHE_FP16 if cache_f16 else 0),
+        workspace.data_ptr(), workspace.numel(), splits,
         status_word(q_new.device).data_ptr(), _stream(q_new))
     _lib.check(rc, "daisy_b200_swa_decode_step_dev")
     return out

@@ -51,6 +51,8 @@ extern "C" {
                                    (true for RMS-normalised q and k with scale * D <= 41); selects the kernel that
                                    needs no running maximum.  swa_prefill_fwd sets it itself when it normalises q and k. */
 /* KDA flags */
+#define DAISY_CACHE_FP16 1024u  /* decode entries: the ring holds float16 rows (the reference Generator's default cache dtype,
+                                   inference/generate.py:62) instead of bf16; q, k, v and the output stay bf16 */
 #define DAISY_WINDOW_BLOCKS 512u /* swa_attend / swa_prefill_fwd: `window` counts blocks of 128 tokens: key block >= query block -
                                    window + 1 (with causality and documents token-exact inside), the mask the flex-attention
                                    BlockMasks of DaisyCore.create_blockmasks select (models/daisy/daisy_core.py:182-229)     */
@@ -95,11 +97,15 @@ int daisy_b200_qkv_prep(const void* q, const void* k, const void* v,
  *   w_qkv      [3*H*D, dim] bf16, row stride ldw: rows h*D.. of the first H*D rows are head h of q, then k, then v
  *              (the layout of qkvo_w[:3].flatten(end_dim=1))
  *   q_out,k_out,v_out   [B,T,H,D] bf16 contiguous, normalised (flags) and rotated (q, k)
+ *   ve, ve_ld, ve_gate_logit   NULL, or the value embedding [B*T, H*D] bf16 (row stride ve_ld) and the gate
+ *              parameter (float32 scalar in device memory): v' = g * norm(v) + (1 - g) * ve, g = sigmoid(gate)
+ *              (models/daisy/attention.py:129-136)
  * dim must be a multiple of 64, D = 128.  flags: DAISY_NORM_Q | DAISY_NORM_K | DAISY_NORM_V | DAISY_ROPE.
  */
 int daisy_b200_qkv_gemm(const void* x, int64_t ldx, const void* w_qkv, int64_t ldw,
                         const float* cos, const float* sin,
                         void* q_out, void* k_out, void* v_out,
+                        const void* ve, int64_t ve_ld, const float* ve_gate_logit,
                         int B, int T, int H, int D, int dim, float eps, unsigned flags,
                         int* status_word, void* stream);
 

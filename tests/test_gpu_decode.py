@@ -85,3 +85,23 @@ def test_decode_long_window_many_splits():
         assert_close_bf16(y, y_ref, f"splits={splits}")
     y2, _, _ = ops.swa_decode_step(q, k, v, ring_k, ring_v, t, cap, window, cos[t].cuda(), sin[t].cuda(), splits=32)
     assert torch.equal(y, y2), "decode is not run-to-run deterministic"
+
+
+@pytest.mark.parametrize("t,window,cap", [(0, 16, 48), (30, 16, 48), (100, None, 48), (1000, 100, 48)])
+def test_decode_float16_ring(t, window, cap):
+    """The ring may hold float16 rows (the reference Generator's default cache dtype, inference/generate.py:62)
+    while q, k, v are bf16: rows are read as fp16, the new row is stored as fp16 and attended at that precision."""
+    from daisy_b200 import ops
+    ring_k = bf16_randn(B, H, cap, D, seed=t).to(torch.float16)
+    ring_v = bf16_randn(B, H, cap, D, seed=t + 7).to(torch.float16)
+    q, k, v = (bf16_randn(B, 1, H, D, seed=200 + i + t) for i in range(3))
+    cos, sin = swa.rope_tables(D, t + 1)
+    kc, vc = _oracle_ctx(ring_k, ring_v, t, cap)
+    y_ref, k_ref, v_ref = swa.decode_step(q.float().cpu(), k.float().cpu(), v.float().cpu(), kc, vc, t, window, cos, sin)
+    y, k_new, v_new = ops.swa_decode_step(q, k, v, ring_k, ring_v, t, cap, window, cos[t].cuda(), sin[t].cuda(), write_ring=True)
+    ops.check_device_status(q.device)
+    assert_close_bf16(y, y_ref, f"y fp16 ring t={t}")
+    slot = t % cap
+    assert ring_k.dtype == torch.float16
+    assert (ring_k[:, :, slot].float().cpu() - k_ref[:, 0]).abs().max().item() <= 4e-3 * max(1.0, k_ref.abs().max().item())
+    assert (ring_v[:, :, slot].float().cpu() - v_ref[:, 0]).abs().max().item() <= 4e-3 * max(1.0, v_ref.abs().max().item())

@@ -71,3 +71,22 @@ def test_module_forward_native_gemm_matches_library_gemm_path(golden_dir):
     ref = torch.from_numpy(z["y"])
     assert_close_bf16(y_nat, ref, "native forward vs reference fixture", max_tol=4e-2, mean_tol=4e-3)
     assert_close_bf16(y_nat, y_lib.float().cpu(), "native vs cuBLAS projections", max_tol=3e-2, mean_tol=3e-3)
+
+
+def test_qkv_gemm_value_embedding_gate():
+    """The value-embedding gate in the GEMM epilogue: v' = g * norm(v) + (1 - g) * ve, q' and k' unaffected."""
+    from daisy_b200 import ops
+    B, T, H, D, dim = 2, 200, 2, 128, 256
+    x = bf16_randn(B, T, dim, seed=3)
+    w = bf16_randn(3 * H * D, dim, seed=4) * (dim ** -0.5)
+    ve = bf16_randn(B, T, H * D, seed=5)
+    cos, sin = swa.rope_tables(D, T)
+    logit = torch.tensor([-1.5163], device="cuda")
+    qp, kp, vp = ops.qkv_gemm(x, w, cos.cuda(), sin.cuda(), H, swa.FP32_EPS, ve=ve, ve_gate_logit=logit)
+    q0, k0, v0 = ops.qkv_gemm(x, w, cos.cuda(), sin.cuda(), H, swa.FP32_EPS)
+    ops.check_device_status(x.device)
+    assert torch.equal(qp, q0) and torch.equal(kp, k0)
+    v = (x.float().cpu() @ w.float().cpu().t()).view(B, T, 3 * H, D)[:, :, 2 * H:]
+    g = torch.sigmoid(torch.tensor(-1.5163))
+    ref = g * swa.rms_norm(v, swa.FP32_EPS) + (1 - g) * ve.float().cpu().view(B, T, H, D)
+    assert_close_bf16(vp, ref, "ve gate in the epilogue")

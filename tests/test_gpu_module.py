@@ -309,3 +309,29 @@ def test_step_through_cuda_graph_equals_eager_steps():
     ops.check_device_status("cuda")
     assert graph.cache.t == eager.cache.t == P + N and int(graph.cache.t_dev.item()) == P + N
     assert torch.equal(graph.cache.k, eager.cache.k) and torch.equal(graph.cache.v, eager.cache.v)
+
+
+def test_step_runner_with_float16_cache():
+    """The runner with ``dtype=torch.float16`` for the cache, as ``Generator`` defaults to: prefill fills the fp16
+    ring, eager and CUDA-graph steps read and extend it; results stay within the bf16 bar of the oracle."""
+    from daisy_b200 import B200CausalSelfAttention, StepRunner
+    os.environ["DISABLE_O_ZERO_INIT"] = "1"
+    torch.manual_seed(6)
+    H, D, W, P, N = 2, 128, 24, 40, 10
+    layers = [B200CausalSelfAttention(H * D, H, D, max_seq_len=128).cuda().eval() for _ in range(2)]
+    for m in layers:
+        m.norm_eps = swa.FP32_EPS
+        with torch.no_grad():
+            m.qkvo_w.mul_(4.0)
+    x = torch.randn(1, P + N, H * D, device="cuda", dtype=torch.bfloat16)
+    run = StepRunner(layers, window=W, cache_capacity=32, dtype=torch.float16)
+    assert run.cache.k.dtype == torch.float16
+    run._prefill(x[:, :P])
+    ys = [run._step(x[:, P + i:P + i + 1]) for i in range(N // 2)]
+    run.capture_step(1, H * D)
+    ys += [run._step_graph(x[:, P + i:P + i + 1]).clone() for i in range(N // 2, N)]
+    cos, sin = swa.rope_tables(D, P + N)
+    h = x.float().cpu()
+    for m in layers:
+        h, _, _ = swa.csa_prefill(h.bfloat16().float(), m.qkvo_w.detach().float().cpu(), H, D, W, cos, sin)
+    assert_close_bf16(torch.cat(ys, 1), h[:, P:], "stepped part, fp16 cache", max_tol=6e-2, mean_tol=6e-3)
