@@ -1,7 +1,7 @@
 """Generate the golden fixtures in this directory from the REFERENCE's own code.
 
-Run once in a container that has the reference tree (default ``/root/reference``,
-override with ``DAISY_REFERENCE_ROOT``) and, for the KDA fixture, the third-party
+Run once in a container that has the reference tree (its root is taken from ``DAISY_REFERENCE_ROOT``,
+default ``../reference`` beside the repository's parent directory) and, for the KDA fixture, the third-party
 ``flash-linear-attention`` package:
 
     python tests/golden/make_golden.py
@@ -18,7 +18,8 @@ import sys
 import numpy as np
 import torch
 
-REF = os.environ.get("DAISY_REFERENCE_ROOT", "/root/reference")
+REF = os.environ.get("DAISY_REFERENCE_ROOT",
+                     os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))), "reference"))
 HERE = os.path.dirname(os.path.abspath(__file__))
 os.environ["DISABLE_O_ZERO_INIT"] = "1"
 sys.path.insert(0, REF)
