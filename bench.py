@@ -380,8 +380,8 @@ def generator_step_latency(H, D, W, layers=4, batch=1, steps=200):
 def run_projection(B, T, H, D, steps, warmup, lean=False):
     """The GEMMs either side of the attention at the headline shape (the module's forward = fused QKV GEMM +
     attention + output GEMM): the hand-written tcgen05 GEMM whose epilogue applies the norm and RoPE, against
-    cuBLAS followed by the separate norm/RoPE pass.  Not part of the headline step (BASELINE's config starts
-    from q, k, v after the projection); reported beside it."""
+    cuBLAS followed by the separate norm/RoPE pass.  Not part of the headline step (the benchmark configuration
+    starts from q, k, v after the projection); reported beside it."""
     import torch.nn.functional as F
     from daisy_b200 import ops
     from oracle import swa

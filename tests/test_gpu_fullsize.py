@@ -24,7 +24,7 @@ def _rope(T, base=10000.0):
 
 
 def test_prefill_c2_full_size():
-    """B=8, T=8192, 16 heads, window 2048 (BASELINE configs[1])."""
+    """B=8, T=8192, 16 heads, window 2048 (the headline prefill configuration)."""
     from daisy_b200 import ops
     B, T, H, W = 8, 8192, 16, 2048
     q, k, v = (_randn_bf16((B, T, H, D), 10 + i) for i in range(3))
@@ -47,7 +47,7 @@ def test_prefill_c2_full_size():
 
 
 def test_prefill_c4_full_size():
-    """B=1, T=65536, 16 heads, window 8192 (BASELINE configs[3]): sampled query blocks of sampled heads."""
+    """B=1, T=65536, 16 heads, window 8192 (the long-context prefill configuration): sampled query blocks of sampled heads."""
     from daisy_b200 import ops
     B, T, H, W = 1, 65536, 16, 8192
     q, k, v = (_randn_bf16((B, T, H, D), 20 + i) for i in range(3))
@@ -70,7 +70,7 @@ def test_prefill_c4_full_size():
 
 
 def test_decode_c3_full_size():
-    """Batch 64, 16 heads, ring capacity 32768, window 4096, steps that wrap the ring (BASELINE configs[2])."""
+    """Batch 64, 16 heads, ring capacity 32768, window 4096, steps that wrap the ring (the decode configuration)."""
     from daisy_b200 import ops
     B, H, cap, W = 64, 16, 32768, 4096
     kc = torch.empty(B, H, cap, D, dtype=torch.bfloat16, device="cuda")
@@ -100,7 +100,7 @@ def test_decode_c3_full_size():
 
 
 def test_kda_c5_full_size():
-    """B=4, T=16384, 16 heads, K=V=128 (BASELINE configs[4]): prefixes of sampled (b, h) against the fp32
+    """B=4, T=16384, 16 heads, K=V=128 (the KDA configuration): prefixes of sampled (b, h) against the fp32
     recurrence, and one call over T against two calls over T/2 chained through the state."""
     from daisy_b200 import ops
     B, T, H = 4, 16384, 16
