@@ -417,6 +417,18 @@ def run_projection(B, T, H, D, steps, warmup, lean=False):
                        "cublas_ms": timed_steps(lambda: F.linear(y, w[3]), steps, warmup, None) / steps}
     a, b = ours(), lib()
     res["max_abs_diff_vs_library_path"] = max(float((a[i].float() - b[i].float()).abs().max()) for i in range(3))
+    del a, b, y
+    # the whole module forward (projection -> attention -> projection) both ways
+    from daisy_b200 import B200CausalSelfAttention, WindowMask
+    os.environ["DISABLE_O_ZERO_INIT"] = "1"
+    mod = B200CausalSelfAttention(dim, H, D, max_seq_len=T).cuda().eval()
+    mask = WindowMask(PREFILL_C2["window"])
+    with torch.inference_mode():
+        fwd = {}
+        for name, flag in (("native_ms", True), ("library_gemm_ms", False)):
+            mod.native_gemm = flag
+            fwd[name] = timed_steps(lambda: mod(x, None, attn_mask=mask), steps, warmup, None) / steps
+    res["module_forward"] = fwd
     return res
 
 
