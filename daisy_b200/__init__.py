@@ -4,7 +4,9 @@ from .attention import (B200CausalSelfAttention, WindowMask, BlockWindowMask, Ro
                         create_blockmasks, doc_starts)
 from .kv_cache import B200KVCache, ring_segment                       # noqa: F401
 from .generate import StepRunner                                      # noqa: F401
+from .kda import B200KimiLinearSelfAttention, B200ShortConvolution, B200FusedRMSNormGated   # noqa: F401
 from . import ops                                                      # noqa: F401
 
 __all__ = ["B200CausalSelfAttention", "B200KVCache", "WindowMask", "BlockWindowMask", "create_blockmasks", "doc_starts",
-           "Rotary", "ring_segment", "StepRunner", "ops"]
+           "Rotary", "ring_segment", "StepRunner", "B200KimiLinearSelfAttention", "B200ShortConvolution",
+           "B200FusedRMSNormGated", "ops"]

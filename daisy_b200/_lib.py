@@ -17,6 +17,8 @@ WINDOW_BLOCKS = 512
 CACHE_FP16 = 1024
 KDA_L2NORM_QK, KDA_OUT_FP32 = 1, 2
 KDA_GATE_ROUND_BF16 = 1
+KDA_CONV_SILU = 1
+KDA_NORM_SIGMOID, KDA_NORM_SWISH, KDA_NORM_SWISH_SIGMOID = 0, 1, 2
 
 _vp, _i, _i64, _f, _u, _sz = C.c_void_p, C.c_int, C.c_int64, C.c_float, C.c_uint, C.c_size_t
 
@@ -49,6 +51,8 @@ SIGNATURES = {
     "daisy_b200_kda_chunk_fwd": (_i, [_vp] * 8 + [_i] * 6 + [_f, _u, _vp, _sz, _vp, _vp]),
     "daisy_b200_kda_recurrent_fwd": (_i, [_vp] * 8 + [_i] * 5 + [_f, _u, _vp]),
     "daisy_b200_kda_gate": (_i, [_vp, _i, _vp, _vp, _vp, _i64, _i, _i, _f, _f, _u, _vp]),
+    "daisy_b200_kda_short_conv": (_i, [_vp, _i64, _i64, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i, _i, _i, _i, _u, _vp]),
+    "daisy_b200_kda_out_norm": (_i, [_vp, _i, _vp, _vp, _vp, _i64, _i, _f, _i, _vp]),
     "daisy_b200_selftest_umma": (_i, [_vp] * 3 + [_i, _i, _vp, _vp]),
 }
 

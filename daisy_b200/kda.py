@@ -52,3 +52,140 @@ def fused_kda_gate(g, A_log, head_k_dim: int, g_bias=None, b=None, beta: float =
     else:
         b_sigmoid = torch.sigmoid(b.to(device=g.device, dtype=g.dtype))
     return y, b_sigmoid
+
+
+# ----------------------------------------------------------------------------------------------- the layer
+class B200ShortConvolution(torch.nn.Conv1d):
+    """The ``ShortConvolution`` the reference's KDA layer builds (models/daisy/attention_kimi.py:88-91; third-party
+    ``fla.modules``): a depthwise causal ``Conv1d`` (weight ``[C, 1, W]``, so checkpoints load unchanged) with SiLU,
+    called as ``y, cache = conv(x=..., cache=..., output_final_state=...)`` (:160-162).  ``cache [B, C, W]`` holds the
+    last W inputs; on decode steps it is updated in place, as the reference's is."""
+
+    def __init__(self, hidden_size: int, kernel_size: int, bias: bool = False, activation: Optional[str] = "silu",
+                 device=None, dtype=None):
+        super().__init__(hidden_size, hidden_size, kernel_size, groups=hidden_size, bias=bias,
+                         padding=kernel_size - 1, device=device, dtype=dtype)
+        if activation not in (None, "silu", "swish"):
+            raise ValueError(f"activation {activation!r} not supported")
+        self.hidden_size, self.activation = hidden_size, activation
+
+    def forward(self, x, cache=None, output_final_state: bool = False, cu_seqlens=None, **_):
+        if cu_seqlens is not None:
+            raise NotImplementedError("variable-length packing (cu_seqlens) is not implemented by the B200 KDA kernels")
+        if cache is not None and cache.dtype != torch.bfloat16:
+            cache = cache.to(torch.bfloat16)
+        step = cache is not None and x.shape[1] <= 32
+        return ops.kda_short_conv(x if x.dtype == torch.bfloat16 else x.to(torch.bfloat16), self.weight, self.bias,
+                                  state=cache, output_final_state=output_final_state or step,
+                                  silu=self.activation is not None, inplace_state=step)
+
+
+class B200FusedRMSNormGated(torch.nn.Module):
+    """``CompilableFusedRMSNormGated`` (models/daisy/attention_kimi.py:41-62): ``rms_norm_gated(x, gate, weight)`` with
+    that function's default swish gate and eps 1e-6, times ``sigmoid(gate)`` -- one kernel here."""
+
+    def __init__(self, hidden_size: int, activation: str = "sigmoid", dtype=torch.bfloat16):
+        if activation != "sigmoid":
+            raise ValueError("Only sigmoid activation is supported")
+        super().__init__()
+        self.hidden_size, self.activation = hidden_size, activation
+        self.weight = torch.nn.Parameter(torch.ones(hidden_size, dtype=dtype))
+        self.bias = None
+
+    def forward(self, x, gate):
+        return ops.kda_out_norm(x, gate, self.weight, eps=1e-6)
+
+
+def _linear(x, weight, bias=None):
+    """``F.linear`` on this library's GEMM where its tiles apply (at least 64 rows, N % 128 == 0, K % 64 == 0);
+    the narrow ones (the per-head beta projection, single decode rows) go to torch's."""
+    N, K = weight.shape
+    if x.numel() // K >= 64 and N % 128 == 0 and K % 64 == 0 and weight.dtype == torch.bfloat16 and x.dtype == torch.bfloat16:
+        y = ops.gemm_nt(x, weight)
+        return y if bias is None else y.add_(bias)
+    return torch.nn.functional.linear(x, weight, bias)
+
+
+class B200KimiLinearSelfAttention(torch.nn.Module):
+    """The reference's ``KimiLinearSelfAttention`` (models/daisy/attention_kimi.py:65-211) with the same constructor,
+    parameter names and ``forward`` / ``prefill`` / ``step`` / ``reset_history`` protocol, running on the B200 kernels:
+    projections -> short convolutions (:160-162) -> decay gate (:132) -> KDA (:133-134; chunked for prompts, the
+    recurrent step for decode) -> gated norm (:135-137) -> output projection.  The reference's ``forward`` cannot
+    run as written (it passes five arguments to a four-parameter ``_forward_core`` whose body then reads an
+    undefined ``sa_lambdas``); this class implements what those lines evidently intend, with ``sa_lambdas``
+    threaded through.  The batch-size-1 assertion (:151) is lifted; ``attn_mask`` (varlen unpadding) is not
+    supported."""
+
+    def __init__(self, dim: int, num_heads: int, max_seq_len: int, head_dim: int, expand_v: float = 1.0,
+                 mode: str = "chunk", use_short_conv: bool = True, allow_neg_eigval: bool = False, conv_size: int = 4,
+                 conv_bias: bool = False, layer_idx: int = 0, receives_ve: bool = False):
+        if allow_neg_eigval or mode != "chunk":
+            raise ValueError("allow_neg_eigval=False and mode='chunk' only, as in the reference")
+        super().__init__()
+        nn, bf = torch.nn, torch.bfloat16
+        self.hidden_size, self.num_heads, self.head_dim = dim, num_heads, head_dim
+        self.head_k_dim, self.head_v_dim = head_dim, int(head_dim * expand_v)
+        self.key_dim, self.value_dim = num_heads * self.head_k_dim, num_heads * self.head_v_dim
+        self.use_short_conv, self.conv_size, self.layer_idx = use_short_conv, conv_size, layer_idx
+        self.q_proj = nn.Linear(dim, self.key_dim, bias=False, dtype=bf)
+        self.k_proj = nn.Linear(dim, self.key_dim, bias=False, dtype=bf)
+        self.v_proj = nn.Linear(dim, self.value_dim, bias=False, dtype=bf)
+        if use_short_conv:
+            self.q_conv1d = B200ShortConvolution(self.key_dim, conv_size, bias=conv_bias, dtype=bf)
+            self.k_conv1d = B200ShortConvolution(self.key_dim, conv_size, bias=conv_bias, dtype=bf)
+            self.v_conv1d = B200ShortConvolution(self.value_dim, conv_size, bias=conv_bias, dtype=bf)
+        self.f_proj = nn.Sequential(nn.Linear(dim, self.head_v_dim, bias=False, dtype=bf),
+                                    nn.Linear(self.head_v_dim, self.key_dim, bias=False, dtype=bf))
+        self.b_proj = nn.Linear(dim, num_heads, bias=False, dtype=bf)
+        self.A_log = nn.Parameter(torch.log(torch.empty(num_heads, dtype=torch.float32).uniform_(1, 16)).view(1, 1, -1, 1))
+        self.dt_bias = nn.Parameter(torch.zeros(self.key_dim, dtype=torch.float32))
+        self.g_proj = nn.Sequential(nn.Linear(dim, self.head_v_dim, bias=False, dtype=bf),
+                                    nn.Linear(self.head_v_dim, self.value_dim, bias=True, dtype=bf))
+        self.o_norm = B200FusedRMSNormGated(self.head_v_dim, activation="sigmoid", dtype=bf)
+        self.o_proj = nn.Linear(self.value_dim, dim, bias=False, dtype=bf)
+        self.reset_history()
+
+    def reset_history(self):
+        self._recurrent_state, self._conv_state, self._seen = None, None, 0
+
+    def _forward_core(self, x, ve, sa_lambdas, attn_mask, use_cache: bool):
+        if attn_mask is not None:
+            raise NotImplementedError("attn_mask (variable-length unpadding) is not implemented by the B200 KDA layer")
+        B, T, _ = x.shape
+        H = self.num_heads
+        q, k, v = _linear(x, self.q_proj.weight), _linear(x, self.k_proj.weight), _linear(x, self.v_proj.weight)
+        if self.use_short_conv:
+            cs = self._conv_state if (use_cache and self._conv_state is not None) else (None, None, None)
+            q, cs_q = self.q_conv1d(x=q, cache=cs[0], output_final_state=use_cache)
+            k, cs_k = self.k_conv1d(x=k, cache=cs[1], output_final_state=use_cache)
+            v, cs_v = self.v_conv1d(x=v, cache=cs[2], output_final_state=use_cache)
+            conv_state = (cs_q, cs_k, cs_v)
+        else:
+            q, k, v = (torch.nn.functional.silu(t) for t in (q, k, v))
+            conv_state = None
+        q, k = q.view(B, T, H, self.head_k_dim), k.view(B, T, H, self.head_k_dim)
+        v = v.view(B, T, H, self.head_v_dim)
+        if sa_lambdas is not None and ve is not None:                      # attention_kimi.py:118-126
+            v = sa_lambdas[0].to(v.dtype) * v + sa_lambdas[1].to(v.dtype) * ve.to(dtype=v.dtype, device=v.device).view_as(v)
+        g = _linear(_linear(x, self.f_proj[0].weight), self.f_proj[1].weight)
+        g = ops.kda_gate(g, self.A_log, self.head_k_dim, self.dt_bias, 1.0, 20.0)
+        beta = torch.nn.functional.linear(x, self.b_proj.weight).sigmoid().float()
+        rec = self._recurrent_state if use_cache else None
+        o, rec = chunk_kda(q=q, k=k, v=v, g=g, beta=beta, initial_state=rec, output_final_state=use_cache,
+                           use_qk_l2norm_in_kernel=True)
+        gp = _linear(_linear(x, self.g_proj[0].weight), self.g_proj[1].weight, self.g_proj[1].bias)
+        o = self.o_norm(o, gp.view(B, T, H, self.head_v_dim))
+        if use_cache:
+            self._recurrent_state, self._conv_state = rec, conv_state
+            self._seen += T
+        return _linear(o.view(B, T, self.value_dim), self.o_proj.weight)
+
+    def forward(self, x, ve=None, sa_lambdas=None, attn_mask=None, sliding_window_num_blocks=None, block_mask=None):
+        assert block_mask is None, "block_mask not supported for KimiLinearSelfAttention"
+        return self._forward_core(x, ve, sa_lambdas, attn_mask, use_cache=False)
+
+    def prefill(self, x, ve=None, sa_lambdas=None, attn_mask=None, debug: bool = False):
+        return self._forward_core(x, ve, sa_lambdas, attn_mask, use_cache=True), None, None
+
+    def step(self, x, k_ctx=None, v_ctx=None, pos: int = 0, ve=None, sa_lambdas=None, window=None):
+        return self._forward_core(x, ve, sa_lambdas, None, use_cache=True), None, None

@@ -421,6 +421,63 @@ def kda_gate(g: torch.Tensor, a_log: torch.Tensor, head_k_dim: int, g_bias: Opti
     return out
 
 
+def kda_short_conv(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None,
+                   state: Optional[torch.Tensor] = None, output_final_state: bool = False, silu: bool = True,
+                   inplace_state: bool = False):
+    """Causal depthwise convolution (+ SiLU) of ``x [B,T,C]`` bf16 with ``weight [C,W]`` (or the Conv1d layout
+    ``[C,1,W]``), W <= 4.  ``state [B,C,W]`` holds the W inputs before ``x`` (oldest first).  Returns
+    ``(y, final_state or None)``; with ``inplace_state`` (T <= 32 only) the final state overwrites ``state``."""
+    _req(x, "x")
+    if x.dim() != 3:
+        raise ValueError("x must be [B, T, C]")
+    if x.stride(2) != 1:
+        x = x.contiguous()
+    B, T, C = x.shape
+    w = weight.reshape(C, -1)
+    w = (w if w.dtype == torch.bfloat16 else w.to(torch.bfloat16)).contiguous()
+    W = w.shape[1]
+    if bias is not None:
+        bias = bias.to(device=x.device, dtype=torch.bfloat16).contiguous()
+    s_out = None
+    if state is not None:
+        if state.shape != (B, C, W) or state.dtype != torch.bfloat16 or not state.is_contiguous():
+            raise ValueError(f"state must be a contiguous bf16 [{B}, {C}, {W}] tensor")
+    if output_final_state:
+        s_out = state if (inplace_state and state is not None) else torch.empty(B, C, W, dtype=torch.bfloat16, device=x.device)
+    y = torch.empty(B, T, C, dtype=torch.bfloat16, device=x.device)
+    rc = _lib.lib().daisy_b200_kda_short_conv(x.data_ptr(), x.stride(0), x.stride(1), w.data_ptr(),
+                                              bias.data_ptr() if bias is not None else None,
+                                              state.data_ptr() if state is not None else None,
+                                              s_out.data_ptr() if s_out is not None else None,
+                                              y.data_ptr(), y.stride(0), y.stride(1), B, T, C, W,
+                                              _lib.KDA_CONV_SILU if silu else 0, _stream(x))
+    _lib.check(rc, "daisy_b200_kda_short_conv")
+    return y, s_out
+
+
+def kda_out_norm(o: torch.Tensor, gate: torch.Tensor, weight: Optional[torch.Tensor] = None, eps: float = 1e-6,
+                 mode: int = _lib.KDA_NORM_SWISH_SIGMOID) -> torch.Tensor:
+    """Gated RMS norm over the last dimension (128) of ``o`` (bf16 or fp32) with the gate pre-activation ``gate``
+    (bf16, same shape); bf16 result of ``o``'s shape.  ``mode``: ``_lib.KDA_NORM_*``."""
+    if not o.is_cuda:
+        raise ValueError("o must be a CUDA tensor")
+    if o.dtype not in (torch.bfloat16, torch.float32):
+        o = o.to(torch.bfloat16)
+    o = o.contiguous()
+    gate = gate.to(device=o.device, dtype=torch.bfloat16).contiguous()
+    if gate.shape != o.shape:
+        raise ValueError("gate must have the shape of o")
+    D = o.shape[-1]
+    if weight is not None:
+        weight = weight.to(device=o.device, dtype=torch.bfloat16).contiguous()
+    y = torch.empty(o.shape, dtype=torch.bfloat16, device=o.device)
+    rc = _lib.lib().daisy_b200_kda_out_norm(o.data_ptr(), 1 if o.dtype == torch.float32 else 0, gate.data_ptr(),
+                                            weight.data_ptr() if weight is not None else None, y.data_ptr(),
+                                            o.numel() // D, D, float(eps), int(mode), _stream(o))
+    _lib.check(rc, "daisy_b200_kda_out_norm")
+    return y
+
+
 def selftest_umma(a: torch.Tensor, b: torch.Tensor, mode: int) -> torch.Tensor:
     """C[128,128] fp32 = A[128,K] x B (B is [128,K] for mode 0, [K,128] for modes 1 and 2)."""
     _req(a, "a"); _req(b, "b")

@@ -61,6 +61,13 @@ extern "C" {
 #define DAISY_KDA_GATE_ROUND_BF16 1u  /* kda_gate: round the result to bf16 first (what the reference's cast of the
                                          gate to a bf16 activation dtype does), then store it as float32     */
 
+#define DAISY_KDA_CONV_SILU 1u  /* kda_short_conv: apply SiLU to the convolution result             */
+#define DAISY_KDA_NORM_SIGMOID 0        /* kda_out_norm gate modes: y = norm(o) * w * sigmoid(g)                          */
+#define DAISY_KDA_NORM_SWISH 1          /*   y = norm(o) * w * g * sigmoid(g)                                            */
+#define DAISY_KDA_NORM_SWISH_SIGMOID 2  /*   y = bf16(norm(o) * w * g * sigmoid(g)) * bf16(sigmoid(g)): what the reference's
+                                             CompilableFusedRMSNormGated evaluates (models/daisy/attention_kimi.py:52-60:
+                                             rms_norm_gated with its default swish gate, then a second sigmoid factor) */
+
 int         daisy_b200_version(void);
 const char* daisy_b200_strerror(int code);
 /* Number of SMs of the current device (0 if there is none). */
@@ -273,6 +280,27 @@ int daisy_b200_kda_recurrent_fwd(const void* q, const void* k, const void* v, co
  * float32, the layout daisy_b200_kda_chunk_fwd takes.  D a multiple of 4.  flags: 0 or DAISY_KDA_GATE_ROUND_BF16. */
 int daisy_b200_kda_gate(const void* g, int g_is_bf16, const float* a_log, const float* bias, float* out,
                         int64_t rows, int H, int D, float beta, float threshold, unsigned flags, void* stream);
+
+/* Short causal depthwise convolution of the KDA layer's q / k / v projections.  Replaces the ShortConvolution
+ * calls at models/daisy/attention_kimi.py:160-162 (modules built at :88-91; third-party fla.modules, a depthwise
+ * nn.Conv1d with padding W-1 and SiLU):
+ *   y[b, t, c] = act(bias[c] + sum_{j<W} w[c, j] * in[b, t - (W-1) + j, c]),   in[t<0] = the carried state or 0
+ * x, y [B, T, C] bf16 with batch / row strides in elements (multiples of 8); w [C, W] bf16 (the Conv1d weight
+ * [C, 1, W]); bias [C] bf16 or null; state_in / state_out [B, C, W] bf16 or null: the last W inputs, oldest first
+ * (the `cache` / final state of the reference call; state_out[., ., j] = in[T - W + j]).  state_out may alias
+ * state_in only when T <= 32 (decode steps: the in-place cache update of the reference).  W <= 4, C % 8 == 0.
+ * flags: 0 or DAISY_KDA_CONV_SILU.  fp32 accumulation, one rounding to bf16. */
+int daisy_b200_kda_short_conv(const void* x, int64_t x_sb, int64_t x_st, const void* w, const void* bias,
+                              const void* state_in, void* state_out, void* y, int64_t y_sb, int64_t y_st,
+                              int B, int T, int C, int W, unsigned flags, void* stream);
+
+/* Gated RMS norm of the KDA output over the head dimension.  Replaces self.o_norm(o, gp) at
+ * models/daisy/attention_kimi.py:137 (CompilableFusedRMSNormGated, :41-62; third-party fla rms_norm_gated):
+ *   n = o * rsqrt(mean(o^2) + eps) * weight,  y = n combined with the gate as `mode` says (DAISY_KDA_NORM_*).
+ * o [rows, D] bf16 (o_is_fp32 == 0) or float32; gate [rows, D] bf16; weight [D] bf16 or null (ones); y [rows, D]
+ * bf16.  D = 128.  The reference passes no eps: rms_norm_gated's default 1e-6. */
+int daisy_b200_kda_out_norm(const void* o, int o_is_fp32, const void* gate, const void* weight, void* y,
+                            int64_t rows, int D, float eps, int mode, void* stream);
 
 /* ---------------------------------------------------------------------------------------------
  * Self-test of the tensor-core building blocks (no reference counterpart): C[128,128] float32 =

@@ -77,6 +77,89 @@ def kda_gate(g: torch.Tensor, A_log: torch.Tensor, head_k_dim: int, g_bias: Opti
     return y.to(g.dtype)
 
 
+def short_conv(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None,
+               state: Optional[torch.Tensor] = None, activation: Optional[str] = "silu"
+               ) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Short causal depthwise convolution of the KDA layer's q / k / v projections, fp32.
+
+    Restates the ``ShortConvolution`` calls of ``KimiLinearSelfAttention._forward_core``
+    (models/daisy/attention_kimi.py:160-162; modules built at :88-91 with ``activation="silu"``).  The class is
+    third-party (``fla.modules``): a depthwise ``nn.Conv1d(C, C, W, groups=C, padding=W-1)`` truncated to the
+    first T outputs, so with cross-correlation taps ``w[c, 0..W-1]``
+
+        y[b, t, c] = act(bias[c] + sum_j w[c, j] * in[b, t - (W-1) + j, c])
+
+    where ``in`` is ``x`` preceded by the carried ``state [B, C, W]`` (the W inputs before x, oldest first; zeros
+    when None).  Returns ``(y [B,T,C], final_state [B,C,W])``, final_state[..., j] = in[T - W + j]: the decode
+    step's cache update (shift left by one, newest input last) is the T = 1 case."""
+    B, T, C = x.shape
+    w = weight.float().reshape(C, -1)
+    W = w.shape[1]
+    hist = state.float().transpose(1, 2) if state is not None else torch.zeros(B, W, C)
+    full = torch.cat([hist, x.float()], dim=1)                     # [B, W+T, C]; row W+t is input t
+    y = torch.zeros(B, T, C)
+    for j in range(W):
+        y = y + w[:, j] * full[:, 1 + j:1 + j + T]                 # input t-(W-1)+j = row t+1+j
+    if bias is not None:
+        y = y + bias.float()
+    if activation in ("silu", "swish"):
+        y = y * torch.sigmoid(y)
+    return y, full[:, T:T + W].transpose(1, 2).contiguous()
+
+
+def gated_rms_norm(o: torch.Tensor, gate: torch.Tensor, weight: Optional[torch.Tensor] = None,
+                   eps: float = 1e-6, mode: str = "swish_sigmoid") -> torch.Tensor:
+    """Gated RMS norm of the KDA output over the head dimension, fp32 result.
+
+    Restates ``CompilableFusedRMSNormGated.forward`` (models/daisy/attention_kimi.py:52-60) as called at :137.  It
+    calls the third-party ``fla.modules.fused_norm_gate.rms_norm_gated(x, gate, weight, bias)`` with that function's
+    defaults (swish gate, eps 1e-6): ``n = x * rsqrt(mean(x^2) + eps) * weight * gate * sigmoid(gate)`` in fp32,
+    rounded to x's dtype -- and then multiplies by ``sigmoid(gate)`` once more in that dtype.  ``mode``:
+    "swish_sigmoid" (the reference: both factors, with the bf16 roundings in between), "swish", "sigmoid" (the
+    single-factor forms of the third-party operator)."""
+    x, g = o.float(), gate.float()
+    n = x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + eps)
+    if weight is not None:
+        n = n * weight.float()
+    sg = torch.sigmoid(g)
+    if mode == "sigmoid":
+        return n * sg
+    if mode == "swish":
+        return n * g * sg
+    return (n * g * sg).bfloat16().float() * sg.bfloat16().float()
+
+
+def kimi_layer_forward(x: torch.Tensor, params: dict, num_heads: int, head_dim: int,
+                       state: Optional[dict] = None, round_stages: bool = True):
+    """The KDA layer end to end, ``x [B,T,dim] -> (y [B,T,dim], state)``: what
+    ``KimiLinearSelfAttention._forward_core`` / ``_kda_eager`` (models/daisy/attention_kimi.py:128-193) compute,
+    composed from the restatements above -- q/k/v projections, short convolutions with SiLU (:160-162), decay gate
+    ``fused_kda_gate(f_proj(x), A_log, head_k_dim, dt_bias, None, 1.0, 20.0)`` (:132), ``beta = sigmoid(b_proj(x))``
+    (:178), KDA with L2-normalised q, k (:133-134), gated norm with ``g_proj(x)`` (:135-137), output projection
+    (:189).  ``params`` maps the module's parameter names to tensors.  ``state`` carries ``{"rec", "conv"}`` between
+    calls (prefill -> steps).  With ``round_stages`` every stage output is rounded to bf16 where the bf16 module
+    stores one, so that a bf16 device run can be compared tightly."""
+    r = (lambda t: t.bfloat16().float()) if round_stages else (lambda t: t)
+    P = {k: v.float() for k, v in params.items()}
+    B, T, _ = x.shape
+    x = x.float()
+    lin = lambda t, w, b=None: r(torch.nn.functional.linear(t, w, b))
+    st = state or {}
+    conv_in = st.get("conv", (None, None, None))
+    qkv, conv_out = [], []
+    for name, cs in zip("qkv", conv_in):
+        y, s_new = short_conv(lin(x, P[f"{name}_proj.weight"]), P[f"{name}_conv1d.weight"],
+                              P.get(f"{name}_conv1d.bias"), state=cs)
+        qkv.append(r(y).view(B, T, num_heads, head_dim)); conv_out.append(s_new)
+    g = kda_gate(lin(lin(x, P["f_proj.0.weight"]), P["f_proj.1.weight"]), P["A_log"].reshape(-1), head_dim, P["dt_bias"])
+    beta = r(torch.sigmoid(lin(x, P["b_proj.weight"])))
+    o, rec = kda_recurrent(qkv[0], qkv[1], qkv[2], r(g), beta, None, st.get("rec"), True)
+    gp = lin(lin(x, P["g_proj.0.weight"]), P["g_proj.1.weight"], P["g_proj.1.bias"]).view(B, T, num_heads, head_dim)
+    o = gated_rms_norm(r(o), gp, P["o_norm.weight"], mode="swish_sigmoid")
+    y = lin(r(o).reshape(B, T, num_heads * head_dim), P["o_proj.weight"])
+    return y, {"rec": rec, "conv": tuple(conv_out)}
+
+
 def kda_bytes_per_token_head(K: int = 128, V: int = 128) -> int:
     """Algorithmic HBM bytes per (token, head): q,k bf16, v bf16, g fp32, beta fp32, o bf16."""
     return 2 * K * 2 + V * 2 + K * 4 + 4 + V * 2

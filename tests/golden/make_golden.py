@@ -222,12 +222,52 @@ def kda_gate_case():
     print("kda_gate_small", tuple(y32.shape))
 
 
+def kda_layer_case():
+    """The two row-wise passes of the KDA layer whose kernels are third-party Triton code that has no CPU path:
+    the short convolution through ``torch.nn.Conv1d``'s own forward on an ``fla.modules.ShortConvolution``
+    instance (the class *is* that Conv1d: its parameters, groups and padding define the operator), in one piece
+    and as prefill + single-token steps through the carried state; and the gated norm through
+    ``torch.nn.functional.rms_norm`` / ``silu`` / ``sigmoid`` in the order of
+    ``CompilableFusedRMSNormGated.forward`` (attention_kimi.py:52-60)."""
+    from fla.modules import ShortConvolution
+    g = torch.Generator().manual_seed(12)
+    out = {}
+    for W, use_bias in ((4, False), (3, True), (2, False)):
+        C, B, T = 64, 2, 21
+        conv = ShortConvolution(C, W, bias=use_bias, activation="silu")
+        with torch.no_grad():
+            conv.weight.copy_(torch.randn(C, 1, W, generator=g) * 0.5)
+            if use_bias:
+                conv.bias.copy_(torch.randn(C, generator=g) * 0.3)
+            x = torch.randn(B, T, C, generator=g)
+            y = torch.nn.functional.silu(torch.nn.Conv1d.forward(conv, x.transpose(1, 2))[..., :T]).transpose(1, 2)
+        tag = f"conv_w{W}"
+        out[tag + "_x"] = x.numpy(); out[tag + "_weight"] = conv.weight.detach().numpy()
+        out[tag + "_bias"] = conv.bias.detach().numpy() if use_bias else np.zeros(0, np.float32)
+        out[tag + "_y"] = y.contiguous().numpy()
+    D = 128
+    x = torch.randn(3, 9, 2, D, generator=g) * 2.0
+    gate = torch.randn(3, 9, 2, D, generator=g) * 3.0
+    wgt = 1.0 + 0.2 * torch.randn(D, generator=g)
+    F = torch.nn.functional
+    normed = F.rms_norm(x, (D,), wgt, 1e-6) * F.silu(gate)
+    xb, gb, wb = x.bfloat16(), gate.bfloat16(), wgt.bfloat16()
+    normed_b = (F.rms_norm(xb.float(), (D,), wb.float(), 1e-6) * F.silu(gb.float())).bfloat16()
+    y_b = normed_b * torch.sigmoid(gb)                               # bf16 x bf16, as the module's last line
+    out.update(norm_x=x.numpy(), norm_gate=gate.numpy(), norm_weight=wgt.numpy(), norm_swish=normed.numpy(),
+               norm_sigmoid=(F.rms_norm(x, (D,), wgt, 1e-6) * torch.sigmoid(gate)).numpy(),
+               norm_ref_bf16_as_fp32=y_b.float().numpy())
+    np.savez_compressed(os.path.join(HERE, "kda_layer_small.npz"), **out)
+    print("kda_layer_small", sorted(out))
+
+
 if __name__ == "__main__":
     csa_prefill_case()
     csa_step_case()
     swa_inner_case()
     kda_case()
     kda_gate_case()
+    kda_layer_case()
     doc_mask_case()
     flex_blockmask_case()
     for f in sorted(os.listdir(HERE)):

@@ -178,3 +178,33 @@ def test_flex_block_lists_against_reference_fixture(golden_dir):
                         assert bool(vis[kb].all()) and bool(torch.isfinite(m[:, kb * swa.BLOCK:(kb + 1) * swa.BLOCK]).all())
                     checked += 1
     assert checked == 384
+
+
+def test_kda_layer_passes_against_fixture(golden_dir):
+    """oracle.kda.short_conv vs torch's Conv1d forward on fla's ShortConvolution instances (taps 4, 3 with bias, 2),
+    in one piece and as prefill + single-token steps through the carried state; oracle.kda.gated_rms_norm vs the
+    torch.nn.functional evaluation in the order of CompilableFusedRMSNormGated.forward
+    (models/daisy/attention_kimi.py:52-60)."""
+    d = np.load(os.path.join(golden_dir, "kda_layer_small.npz"))
+    for W in (4, 3, 2):
+        x, w, b, ref = (torch.from_numpy(d[f"conv_w{W}_{n}"]) for n in ("x", "weight", "bias", "y"))
+        b = b if b.numel() else None
+        y, s = kda.short_conv(x, w, b)
+        assert (y - ref).abs().max().item() <= 2e-6
+        assert torch.equal(s, x[:, -W:].transpose(1, 2))
+        # prefill of 13 tokens, then 8 single-token steps on the state
+        y0, s = kda.short_conv(x[:, :13], w, b)
+        ys = [y0]
+        for t in range(13, x.shape[1]):
+            yt, s = kda.short_conv(x[:, t:t + 1], w, b, state=s)
+            ys.append(yt)
+        assert (torch.cat(ys, 1) - ref).abs().max().item() <= 2e-6
+        # a prompt shorter than the taps keeps the zero padding in the state
+        _, s1 = kda.short_conv(x[:, :1], w, b)
+        assert not s1[..., :-1].any() and torch.equal(s1[..., -1], x[:, 0])
+    x, g, w = (torch.from_numpy(d[n]) for n in ("norm_x", "norm_gate", "norm_weight"))
+    assert (kda.gated_rms_norm(x, g, w, mode="swish") - torch.from_numpy(d["norm_swish"])).abs().max() <= 1e-5
+    assert (kda.gated_rms_norm(x, g, w, mode="sigmoid") - torch.from_numpy(d["norm_sigmoid"])).abs().max() <= 1e-5
+    got = kda.gated_rms_norm(x.bfloat16(), g.bfloat16(), w.bfloat16()).bfloat16().float()
+    ref = torch.from_numpy(d["norm_ref_bf16_as_fp32"])
+    assert (got == ref).float().mean().item() > 0.995 and ((got - ref).abs() <= ref.abs() * 2.0 ** -6 + 1e-30).all()
