@@ -486,6 +486,35 @@ def run_kda(cfg, steps, warmup, dist, rank, world, peaks, lean=False):
                                    "g=logsigmoid(N(0,1)), beta=sigmoid(N(0,1)), bf16 I/O, fp32 state", "per_gpu_batch": B}}
 
 
+def run_kda_layer(cfg, steps, warmup, peaks):
+    """The row-wise passes of the KDA layer at the KDA configuration's shape (C = H*K channels), each against the
+    copy bandwidth, and the whole layer's forward (dim = H*K) with its share spent in the KDA kernels."""
+    from daisy_b200 import ops, B200KimiLinearSelfAttention
+    B, T, H, K = cfg["B"], cfg["T"], cfg["H"], cfg["K"]
+    C = H * K
+    dev = torch.device("cuda", torch.cuda.current_device())
+    g_ = torch.Generator(device=dev).manual_seed(5)
+    x = torch.randn(B, T, C, device=dev, generator=g_).bfloat16()
+    w = (torch.randn(C, 4, device=dev, generator=g_) * 0.5).bfloat16()
+    o = torch.randn(B, T, H, K, device=dev, generator=g_).bfloat16()
+    gate = torch.randn(B, T, H, K, device=dev, generator=g_).bfloat16()
+    nw = torch.ones(K, device=dev).bfloat16()
+    out = {}
+    ms = timed_steps(lambda: ops.kda_short_conv(x, w), steps, warmup, None) / steps
+    gbs = 2 * x.numel() * 2 / (ms * 1e-3) / 1e9
+    out["short_conv"] = {"ms": ms, "hbm_gbs": gbs, "frac_of_copy": gbs / peaks["hbm_gbs"], "bytes": "read x + write y"}
+    ms = timed_steps(lambda: ops.kda_out_norm(o, gate, nw), steps, warmup, None) / steps
+    gbs = 3 * o.numel() * 2 / (ms * 1e-3) / 1e9
+    out["out_norm"] = {"ms": ms, "hbm_gbs": gbs, "frac_of_copy": gbs / peaks["hbm_gbs"], "bytes": "read o, gate + write y"}
+    del o, gate, w
+    layer = B200KimiLinearSelfAttention(C, H, T, K).to(dev).eval()
+    with torch.inference_mode():
+        ms = timed_steps(lambda: layer(x, None, None), max(3, steps // 2), 2, None) / max(3, steps // 2)
+    out["layer_forward_ms"] = ms
+    out["config"] = {"workload": f"kda layer: B={B} T={T} dim={C} H={H} K=V={K}, conv taps 4"}
+    return out
+
+
 # ----------------------------------------------------------------------------- CPU baseline / reference arm
 
 def cpu_prefill_sample(cfg, threads=None):
@@ -589,6 +618,9 @@ def main():
             res = kd
         else:
             extra["kda"] = kd
+        if want == "all" and rank == 0 and not args.no_extras:
+            torch.cuda.empty_cache()
+            extra["kda_layer"] = run_kda_layer(KDA_C5, args.steps, warm, peaks)
     if rank == 0:
         is_prefill = res["name"].startswith("prefill")
         line = {

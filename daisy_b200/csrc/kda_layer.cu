@@ -9,8 +9,12 @@
 namespace daisy {
 
 constexpr int SC_MAX_W = 4;      // taps
-constexpr int SC_TT = 32;        // time steps per thread: the W-1 halo rows are re-read once per 32 rows
-constexpr int SC_THREADS = 128;  // thread = 8 adjacent channels (one 16-byte access per row)
+constexpr int SC_CH = 4;         // channels per thread: one 8-byte access per row keeps the thread under 64 registers,
+                                 // so eight warps per scheduler overlap the SiLU arithmetic with the loads
+constexpr int SC_TT = 8;         // outputs per thread: it loads SC_TT + 3 rows, all independent, before any arithmetic
+constexpr int SC_CG = 128;       // channel groups per CTA: 1 KB of a row
+constexpr int SC_SLICES = 2;     // time slices per CTA: the halo rows of a slice are its neighbour's rows (L1 / L2 hits)
+constexpr int SC_THREADS = SC_CG * SC_SLICES;
 
 struct ShortConvParams {
   const __nv_bfloat16* x;        // [B, T, C], row stride x_st, batch stride x_sb (elements)
@@ -23,91 +27,98 @@ struct ShortConvParams {
   int T, C, W, silu;
 };
 
-__device__ __forceinline__ uint32_t pack2(float a, float b) {
-  const __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
-  return *reinterpret_cast<const uint32_t*>(&h);
+__device__ __forceinline__ void unpack4(const uint2 u, float* f) {
+  f[0] = bf16_lo(u.x); f[1] = bf16_hi(u.x); f[2] = bf16_lo(u.y); f[3] = bf16_hi(u.y);
 }
+__device__ __forceinline__ float fast_sigmoid(float a) { return __fdividef(1.f, 1.f + __expf(-a)); }
 
-// Input at time t (may be negative: the carried state, else zero) for the 8 channels from c0.
+// Input at time t (may be negative: the carried state, else zero) for the SC_CH channels from c0.
 __device__ __forceinline__ void conv_input_row(const ShortConvParams& p, int b, int t, int c0, float* f) {
   if (t >= 0) {
-    unpack8(*reinterpret_cast<const uint4*>(p.x + (long long)b * p.x_sb + (long long)t * p.x_st + c0), f);
+    unpack4(*reinterpret_cast<const uint2*>(p.x + (long long)b * p.x_sb + (long long)t * p.x_st + c0), f);
   } else if (p.s_in && p.W + t >= 0) {
     const __nv_bfloat16* s = p.s_in + ((long long)b * p.C + c0) * p.W + (p.W + t);
 #pragma unroll
-    for (int e = 0; e < 8; ++e) f[e] = __bfloat162float(s[e * p.W]);
+    for (int e = 0; e < SC_CH; ++e) f[e] = __bfloat162float(s[e * p.W]);
   } else {
 #pragma unroll
-    for (int e = 0; e < 8; ++e) f[e] = 0.f;
+    for (int e = 0; e < SC_CH; ++e) f[e] = 0.f;
   }
 }
 
 __global__ void __launch_bounds__(SC_THREADS) kda_short_conv_kernel(const ShortConvParams p) {
-  const int c0 = (blockIdx.z * SC_THREADS + threadIdx.x) * 8;
-  if (c0 >= p.C) return;
-  const int b = blockIdx.y;
-  const int t0 = blockIdx.x * SC_TT;
+  // channel blocks vary fastest, then time blocks: CTAs launched together walk the tensor front to back
+  const int c0 = (blockIdx.x * SC_CG + (threadIdx.x % SC_CG)) * SC_CH;
+  const int b = blockIdx.z;
+  const int t0 = (blockIdx.y * SC_SLICES + threadIdx.x / SC_CG) * SC_TT;
+  if (c0 >= p.C || t0 >= p.T) return;
   const int t1 = min(t0 + SC_TT, p.T);
 
+  // every row this thread needs, in flight at once: rows t0-3 .. t0+SC_TT-1
+  uint2 raw[SC_TT + 3];
+  const __nv_bfloat16* xr = p.x + (long long)b * p.x_sb + c0;
+#pragma unroll
+  for (int i = 0; i < SC_TT + 3; ++i) {
+    const int t = t0 - 3 + i;
+    raw[i] = (t >= 0 && t < t1) ? __ldg(reinterpret_cast<const uint2*>(xr + (long long)t * p.x_st)) : make_uint2(0, 0);
+  }
+  if (t0 < 3) {                                                    // rows before the call: the carried state or zeros
+#pragma unroll
+    for (int i = 0; i < 3; ++i)
+      if (t0 - 3 + i < 0) {
+        float f[SC_CH];
+        conv_input_row(p, b, t0 - 3 + i, c0, f);
+        raw[i] = make_uint2(pack_bf16(f[0], f[1]), pack_bf16(f[2], f[3]));
+      }
+  }
+
   // taps right-aligned in four slots: slot 3 multiplies the current row, slot 3-i the row i steps back
-  float wt[8][SC_MAX_W];
+  float wt[SC_CH][SC_MAX_W];
   if (p.W == 4) {
 #pragma unroll
-    for (int h = 0; h < 4; ++h) {                                  // 8 channels x 4 taps = 64 contiguous bytes
+    for (int h = 0; h < 2; ++h) {                                  // 4 channels x 4 taps = 32 contiguous bytes
       float f[8];
-      unpack8(*reinterpret_cast<const uint4*>(p.w + (long long)c0 * 4 + h * 8), f);
+      unpack8(__ldg(reinterpret_cast<const uint4*>(p.w + (long long)c0 * 4 + h * 8)), f);
 #pragma unroll
       for (int i = 0; i < 8; ++i) wt[h * 2 + i / 4][i % 4] = f[i];
     }
   } else {
 #pragma unroll
-    for (int e = 0; e < 8; ++e)
+    for (int e = 0; e < SC_CH; ++e)
 #pragma unroll
       for (int j = 0; j < SC_MAX_W; ++j) {
         const int tap = j - (SC_MAX_W - p.W);
         wt[e][j] = tap >= 0 ? __bfloat162float(p.w[(long long)(c0 + e) * p.W + tap]) : 0.f;
       }
   }
-  float bs[8];
+  float bs[SC_CH];
 #pragma unroll
-  for (int e = 0; e < 8; ++e) bs[e] = 0.f;
-  if (p.bias) unpack8(*reinterpret_cast<const uint4*>(p.bias + c0), bs);
+  for (int e = 0; e < SC_CH; ++e) bs[e] = p.bias ? __bfloat162float(p.bias[c0 + e]) : 0.f;
 
-  float h1[8], h2[8], h3[8];                                       // rows t-1, t-2, t-3
-  conv_input_row(p, b, t0 - 1, c0, h1);
-  conv_input_row(p, b, t0 - 2, c0, h2);
-  conv_input_row(p, b, t0 - 3, c0, h3);
-
-  const __nv_bfloat16* xr = p.x + (long long)b * p.x_sb + c0;
   __nv_bfloat16* yr = p.y + (long long)b * p.y_sb + c0;
-  for (int t = t0; t < t1; t += 4) {
-    uint4 raw[4];
+  float h1[SC_CH], h2[SC_CH], h3[SC_CH];                           // rows t-1, t-2, t-3
+  unpack4(raw[0], h3); unpack4(raw[1], h2); unpack4(raw[2], h1);
 #pragma unroll
-    for (int i = 0; i < 4; ++i)                                    // four independent 16-byte loads in flight
-      raw[i] = (t + i < t1) ? *reinterpret_cast<const uint4*>(xr + (long long)(t + i) * p.x_st) : make_uint4(0, 0, 0, 0);
+  for (int i = 0; i < SC_TT; ++i) {
+    float cur[SC_CH], o[SC_CH];
+    unpack4(raw[i + 3], cur);
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      if (t + i >= t1) break;
-      float cur[8], o[8];
-      unpack8(raw[i], cur);
-#pragma unroll
-      for (int e = 0; e < 8; ++e) {
-        float a = bs[e];
-        a = fmaf(wt[e][0], h3[e], a);
-        a = fmaf(wt[e][1], h2[e], a);
-        a = fmaf(wt[e][2], h1[e], a);
-        a = fmaf(wt[e][3], cur[e], a);
-        o[e] = p.silu ? a / (1.f + __expf(-a)) : a;
-        h3[e] = h2[e]; h2[e] = h1[e]; h1[e] = cur[e];
-      }
-      *reinterpret_cast<uint4*>(yr + (long long)(t + i) * p.y_st) =
-          make_uint4(pack2(o[0], o[1]), pack2(o[2], o[3]), pack2(o[4], o[5]), pack2(o[6], o[7]));
+    for (int e = 0; e < SC_CH; ++e) {
+      float a = bs[e];
+      a = fmaf(wt[e][0], h3[e], a);
+      a = fmaf(wt[e][1], h2[e], a);
+      a = fmaf(wt[e][2], h1[e], a);
+      a = fmaf(wt[e][3], cur[e], a);
+      o[e] = p.silu ? a * fast_sigmoid(a) : a;
+      h3[e] = h2[e]; h2[e] = h1[e]; h1[e] = cur[e];
     }
+    if (t0 + i < t1)
+      *reinterpret_cast<uint2*>(yr + (long long)(t0 + i) * p.y_st) = make_uint2(pack_bf16(o[0], o[1]), pack_bf16(o[2], o[3]));
   }
 
-  // the CTA that owns the last row leaves the state: the last W inputs, oldest first
+  // the thread that owns the last row leaves the state: the last W inputs, oldest first
   if (p.s_out && t1 == p.T) {
-    float st[SC_MAX_W][8];
+    float st[SC_MAX_W][SC_CH];
 #pragma unroll
     for (int j = 0; j < SC_MAX_W; ++j)
       if (j < p.W) conv_input_row(p, b, p.T - p.W + j, c0, st[j]);
@@ -116,7 +127,7 @@ __global__ void __launch_bounds__(SC_THREADS) kda_short_conv_kernel(const ShortC
     for (int j = 0; j < SC_MAX_W; ++j)
       if (j < p.W) {
 #pragma unroll
-        for (int e = 0; e < 8; ++e) s[e * p.W + j] = __float2bfloat16_rn(st[j][e]);
+        for (int e = 0; e < SC_CH; ++e) s[e * p.W + j] = __float2bfloat16_rn(st[j][e]);
       }
   }
 }
@@ -136,44 +147,76 @@ struct OutNormParams {
 
 __device__ __forceinline__ float round_bf16(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
 
+constexpr int ON_ROWS = 1;       // rows per lane group
+constexpr int ON_LPR = 8;        // lanes per row: elements [8 sub, 8 sub + 8) and [64 + 8 sub, 64 + 8 sub + 8)
+
+// One pass per thread, no loop: the block scheduler keeps the memory system fed.
 __global__ void __launch_bounds__(256) kda_out_norm_kernel(const OutNormParams p) {
-  const int sub = threadIdx.x & 15;                                // lane within the row
-  float wv[8];
+  const int sub = threadIdx.x & (ON_LPR - 1);
+  const long long row0 = (((long long)blockIdx.x * 256 + threadIdx.x) / ON_LPR) * ON_ROWS;
+  uint4 xa[ON_ROWS][2], xb[ON_ROWS][2], ga[ON_ROWS], gb[ON_ROWS];
+  long long row[ON_ROWS];
+  bool live[ON_ROWS];
 #pragma unroll
-  for (int e = 0; e < 8; ++e) wv[e] = 1.f;
-  if (p.w) unpack8(*reinterpret_cast<const uint4*>(p.w + sub * 8), wv);
-  const long long stride = (long long)gridDim.x * 16;
-  for (long long base = (long long)blockIdx.x * 16; base < p.rows; base += stride) {   // uniform per block: the
-    const long long row_raw = base + (threadIdx.x >> 4);                                // shuffles below need whole warps
-    const bool valid = row_raw < p.rows;
-    const long long row = valid ? row_raw : p.rows - 1;
-    float x[8], g[8];
+  for (int u = 0; u < ON_ROWS; ++u) {
+    live[u] = row0 + u < p.rows;
+    row[u] = live[u] ? row0 + u : p.rows - 1;                      // past the end the last row is repeated
     if (p.o_fp32) {
-      const float4* src = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.o) + row * ON_D + sub * 8);
-      const float4 a = src[0], c = src[1];
-      x[0] = a.x; x[1] = a.y; x[2] = a.z; x[3] = a.w; x[4] = c.x; x[5] = c.y; x[6] = c.z; x[7] = c.w;
+      const float* src = reinterpret_cast<const float*>(p.o) + row[u] * ON_D + 8 * sub;
+      xa[u][0] = ld_stream16(src);      xa[u][1] = ld_stream16(src + 4);
+      xb[u][0] = ld_stream16(src + 64); xb[u][1] = ld_stream16(src + 68);
     } else {
-      unpack8(*reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(p.o) + row * ON_D + sub * 8), x);
+      const __nv_bfloat16* src = reinterpret_cast<const __nv_bfloat16*>(p.o) + row[u] * ON_D + 8 * sub;
+      xa[u][0] = ld_stream16(src); xb[u][0] = ld_stream16(src + 64);
     }
-    unpack8(*reinterpret_cast<const uint4*>(p.g + row * ON_D + sub * 8), g);
+    ga[u] = ld_stream16(p.g + row[u] * ON_D + 8 * sub);
+    gb[u] = ld_stream16(p.g + row[u] * ON_D + 64 + 8 * sub);
+  }
+  float w1[8], w2[8];
+#pragma unroll
+  for (int e = 0; e < 8; ++e) { w1[e] = 1.f; w2[e] = 1.f; }
+  if (p.w) {
+    unpack8(__ldg(reinterpret_cast<const uint4*>(p.w + 8 * sub)), w1);
+    unpack8(__ldg(reinterpret_cast<const uint4*>(p.w + 64 + 8 * sub)), w2);
+  }
+#pragma unroll
+  for (int u = 0; u < ON_ROWS; ++u) {
+    float x1[8], x2[8], g1[8], g2[8];
+    if (p.o_fp32) {
+      x1[0] = __uint_as_float(xa[u][0].x); x1[1] = __uint_as_float(xa[u][0].y); x1[2] = __uint_as_float(xa[u][0].z);
+      x1[3] = __uint_as_float(xa[u][0].w); x1[4] = __uint_as_float(xa[u][1].x); x1[5] = __uint_as_float(xa[u][1].y);
+      x1[6] = __uint_as_float(xa[u][1].z); x1[7] = __uint_as_float(xa[u][1].w);
+      x2[0] = __uint_as_float(xb[u][0].x); x2[1] = __uint_as_float(xb[u][0].y); x2[2] = __uint_as_float(xb[u][0].z);
+      x2[3] = __uint_as_float(xb[u][0].w); x2[4] = __uint_as_float(xb[u][1].x); x2[5] = __uint_as_float(xb[u][1].y);
+      x2[6] = __uint_as_float(xb[u][1].z); x2[7] = __uint_as_float(xb[u][1].w);
+    } else {
+      unpack8(xa[u][0], x1); unpack8(xb[u][0], x2);
+    }
+    unpack8(ga[u], g1); unpack8(gb[u], g2);
     float ss = 0.f;
 #pragma unroll
-    for (int e = 0; e < 8; ++e) ss = fmaf(x[e], x[e], ss);
-#pragma unroll
-    for (int m = 8; m >= 1; m >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, m);
-    const float rstd = 1.0f / sqrtf(ss * (1.0f / ON_D) + p.eps);
-    float o[8];
+    for (int e = 0; e < 8; ++e) ss += x1[e] * x1[e] + x2[e] * x2[e];
+    ss += __shfl_xor_sync(0xffffffffu, ss, 4);                     // every lane of the warp is here: no early exit above
+    ss += __shfl_xor_sync(0xffffffffu, ss, 2);
+    ss += __shfl_xor_sync(0xffffffffu, ss, 1);
+    const float rstd = rsqrtf(ss * (1.0f / ON_D) + p.eps);
+    float o1[8], o2[8];
 #pragma unroll
     for (int e = 0; e < 8; ++e) {
-      const float n = x[e] * rstd * wv[e];
-      const float sg = 1.f / (1.f + __expf(-g[e]));
-      if (p.mode == 0)      o[e] = n * sg;                         // sigmoid gate
-      else if (p.mode == 1) o[e] = n * g[e] * sg;                  // swish gate
-      else                  o[e] = round_bf16(n * g[e] * sg) * round_bf16(sg);   // swish-gated norm (rounded), then x sigmoid
+      const float n1 = x1[e] * rstd * w1[e], n2 = x2[e] * rstd * w2[e];
+      const float s1 = fast_sigmoid(g1[e]), s2 = fast_sigmoid(g2[e]);
+      if (p.mode == 0)      { o1[e] = n1 * s1; o2[e] = n2 * s2; }                              // sigmoid gate
+      else if (p.mode == 1) { o1[e] = n1 * g1[e] * s1; o2[e] = n2 * g2[e] * s2; }              // swish gate
+      else {                                                       // swish-gated norm (rounded), then x sigmoid
+        o1[e] = round_bf16(n1 * g1[e] * s1) * round_bf16(s1);
+        o2[e] = round_bf16(n2 * g2[e] * s2) * round_bf16(s2);
+      }
     }
-    if (valid)
-      *reinterpret_cast<uint4*>(p.y + row * ON_D + sub * 8) =
-          make_uint4(pack2(o[0], o[1]), pack2(o[2], o[3]), pack2(o[4], o[5]), pack2(o[6], o[7]));
+    if (live[u]) {
+      __nv_bfloat16* dst = p.y + row[u] * ON_D + 8 * sub;
+      *reinterpret_cast<uint4*>(dst) = pack8(o1);
+      *reinterpret_cast<uint4*>(dst + 64) = pack8(o2);
+    }
   }
 }
 
@@ -185,20 +228,20 @@ extern "C" int daisy_b200_kda_short_conv(const void* x, int64_t x_sb, int64_t x_
                                          const void* state_in, void* state_out, void* y, int64_t y_sb, int64_t y_st,
                                          int B, int T, int C, int W, unsigned flags, void* stream) {
   if (!x || !w || !y || B <= 0 || T <= 0 || C <= 0) return DAISY_EINVAL;
-  if (W < 1 || W > SC_MAX_W || C % 8 != 0 || B > 65535) return DAISY_EUNSUPPORTED;
+  if (W < 1 || W > SC_MAX_W || C % 8 != 0 || B > 65535 || (T + SC_TT * SC_SLICES - 1) / (SC_TT * SC_SLICES) > 65535) return DAISY_EUNSUPPORTED;
   if (flags & ~DAISY_KDA_CONV_SILU) return DAISY_EINVAL;
   if (!daisy_aligned16(x) || !daisy_aligned16(y) || !daisy_aligned16(w) || (bias && !daisy_aligned16(bias)) ||
       x_sb % 8 || x_st % 8 || y_sb % 8 || y_st % 8)
     return DAISY_EALIGN;
-  // a state updated in place is read by the first time block and written by the last: one block only
+  // a state updated in place is read by the threads of the first rows and written by those of the last: one thread only
   if (state_in && state_in == state_out && T > SC_TT) return DAISY_EINVAL;
   ShortConvParams p;
   p.x = (const __nv_bfloat16*)x; p.w = (const __nv_bfloat16*)w; p.bias = (const __nv_bfloat16*)bias;
   p.s_in = (const __nv_bfloat16*)state_in; p.s_out = (__nv_bfloat16*)state_out; p.y = (__nv_bfloat16*)y;
   p.x_sb = x_sb; p.x_st = x_st; p.y_sb = y_sb; p.y_st = y_st;
   p.T = T; p.C = C; p.W = W; p.silu = (flags & DAISY_KDA_CONV_SILU) ? 1 : 0;
-  const int groups = C / 8;
-  const dim3 grid((T + SC_TT - 1) / SC_TT, B, (groups + SC_THREADS - 1) / SC_THREADS);
+  const int groups = C / SC_CH, tb = SC_TT * SC_SLICES;
+  const dim3 grid((groups + SC_CG - 1) / SC_CG, (T + tb - 1) / tb, B);
   kda_short_conv_kernel<<<grid, SC_THREADS, 0, (cudaStream_t)stream>>>(p);
   DAISY_CHECK_LAUNCH();
   return DAISY_OK;
@@ -213,8 +256,10 @@ extern "C" int daisy_b200_kda_out_norm(const void* o, int o_is_fp32, const void*
   OutNormParams p;
   p.o = o; p.g = (const __nv_bfloat16*)gate; p.w = (const __nv_bfloat16*)weight; p.y = (__nv_bfloat16*)y;
   p.rows = rows; p.eps = eps; p.o_fp32 = o_is_fp32 ? 1 : 0; p.mode = mode;
-  const long long want = (rows + 15) / 16;
-  const unsigned grid = (unsigned)(want < 148LL * 16 ? want : 148LL * 16);
+  const long long rows_per_cta = 256 / ON_LPR * ON_ROWS;
+  const long long want = (rows + rows_per_cta - 1) / rows_per_cta;
+  if (want > 0x7fffffffLL) return DAISY_EUNSUPPORTED;
+  const unsigned grid = (unsigned)want;
   kda_out_norm_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(p);
   DAISY_CHECK_LAUNCH();
   return DAISY_OK;
