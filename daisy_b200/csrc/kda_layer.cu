@@ -9,12 +9,13 @@
 namespace daisy {
 
 constexpr int SC_MAX_W = 4;      // taps
-constexpr int SC_CH = 4;         // channels per thread: one 8-byte access per row keeps the thread under 64 registers,
-                                 // so eight warps per scheduler overlap the SiLU arithmetic with the loads
-constexpr int SC_TT = 8;         // outputs per thread: it loads SC_TT + 3 rows, all independent, before any arithmetic
-constexpr int SC_CG = 128;       // channel groups per CTA: 1 KB of a row
-constexpr int SC_SLICES = 2;     // time slices per CTA: the halo rows of a slice are its neighbour's rows (L1 / L2 hits)
-constexpr int SC_THREADS = SC_CG * SC_SLICES;
+constexpr int SC_ROWS = 32;      // output rows per CTA; the tile in shared memory holds 3 more in front (9 % re-read, L2 hits)
+constexpr int SC_COLS = 512;     // channels per CTA: 1 KB of a row, 64 16-byte chunks
+constexpr int SC_CH = 4;         // channels per thread in the arithmetic phase (8-byte shared-memory reads)
+constexpr int SC_SLICES = 2;     // the 32 rows as two slices of 16 consecutive rows per thread
+constexpr int SC_THREADS = SC_COLS / SC_CH * SC_SLICES;   // 256
+constexpr int SC_TILE_ROWS = SC_ROWS + 3;
+constexpr int SC_LOADS = (SC_TILE_ROWS * (SC_COLS / 8) + SC_THREADS - 1) / SC_THREADS;   // 16-byte loads per thread: 9
 
 struct ShortConvParams {
   const __nv_bfloat16* x;        // [B, T, C], row stride x_st, batch stride x_sb (elements)
@@ -32,76 +33,96 @@ __device__ __forceinline__ void unpack4(const uint2 u, float* f) {
 }
 __device__ __forceinline__ float fast_sigmoid(float a) { return __fdividef(1.f, 1.f + __expf(-a)); }
 
-// Input at time t (may be negative: the carried state, else zero) for the SC_CH channels from c0.
-__device__ __forceinline__ void conv_input_row(const ShortConvParams& p, int b, int t, int c0, float* f) {
-  if (t >= 0) {
-    unpack4(*reinterpret_cast<const uint2*>(p.x + (long long)b * p.x_sb + (long long)t * p.x_st + c0), f);
-  } else if (p.s_in && p.W + t >= 0) {
-    const __nv_bfloat16* s = p.s_in + ((long long)b * p.C + c0) * p.W + (p.W + t);
+// The 8 channels from c at time t < 0: the carried state, else zeros.
+__device__ __forceinline__ uint4 conv_state_row(const ShortConvParams& p, int b, int t, int c) {
+  float f[8];
 #pragma unroll
-    for (int e = 0; e < SC_CH; ++e) f[e] = __bfloat162float(s[e * p.W]);
-  } else {
+  for (int e = 0; e < 8; ++e) f[e] = 0.f;
+  if (p.s_in && p.W + t >= 0) {
+    const __nv_bfloat16* s = p.s_in + ((long long)b * p.C + c) * p.W + (p.W + t);
 #pragma unroll
-    for (int e = 0; e < SC_CH; ++e) f[e] = 0.f;
+    for (int e = 0; e < 8; ++e) f[e] = __bfloat162float(s[e * p.W]);
   }
+  return pack8(f);
 }
 
+// Phase 1: the CTA's tile of x (35 rows x 1 KB) goes to shared memory with coalesced 16-byte loads, all of a thread's
+// loads in flight before the first is used.  Phase 2: thread = 4 channels x 16 consecutive rows, sliding the taps'
+// window through registers, one 8-byte shared-memory read and one 8-byte store per row.
 __global__ void __launch_bounds__(SC_THREADS) kda_short_conv_kernel(const ShortConvParams p) {
-  // channel blocks vary fastest, then time blocks: CTAs launched together walk the tensor front to back
-  const int c0 = (blockIdx.x * SC_CG + (threadIdx.x % SC_CG)) * SC_CH;
-  const int b = blockIdx.z;
-  const int t0 = (blockIdx.y * SC_SLICES + threadIdx.x / SC_CG) * SC_TT;
-  if (c0 >= p.C || t0 >= p.T) return;
-  const int t1 = min(t0 + SC_TT, p.T);
+  __shared__ uint4 tile[SC_TILE_ROWS][SC_COLS / 8];
+  const int cblk = blockIdx.x * SC_COLS;                           // channel blocks vary fastest, then time blocks:
+  const int b = blockIdx.z;                                        // CTAs launched together walk the tensor front to back
+  const int tblk = blockIdx.y * SC_ROWS;
+  const int t_end = min(tblk + SC_ROWS, p.T);
 
-  // every row this thread needs, in flight at once: rows t0-3 .. t0+SC_TT-1
-  uint2 raw[SC_TT + 3];
-  const __nv_bfloat16* xr = p.x + (long long)b * p.x_sb + c0;
+  uint4 v[SC_LOADS];
+  const __nv_bfloat16* xb = p.x + (long long)b * p.x_sb;
 #pragma unroll
-  for (int i = 0; i < SC_TT + 3; ++i) {
-    const int t = t0 - 3 + i;
-    raw[i] = (t >= 0 && t < t1) ? __ldg(reinterpret_cast<const uint2*>(xr + (long long)t * p.x_st)) : make_uint2(0, 0);
-  }
-  if (t0 < 3) {                                                    // rows before the call: the carried state or zeros
-#pragma unroll
-    for (int i = 0; i < 3; ++i)
-      if (t0 - 3 + i < 0) {
-        float f[SC_CH];
-        conv_input_row(p, b, t0 - 3 + i, c0, f);
-        raw[i] = make_uint2(pack_bf16(f[0], f[1]), pack_bf16(f[2], f[3]));
-      }
-  }
-
-  // taps right-aligned in four slots: slot 3 multiplies the current row, slot 3-i the row i steps back
-  float wt[SC_CH][SC_MAX_W];
-  if (p.W == 4) {
-#pragma unroll
-    for (int h = 0; h < 2; ++h) {                                  // 4 channels x 4 taps = 32 contiguous bytes
-      float f[8];
-      unpack8(__ldg(reinterpret_cast<const uint4*>(p.w + (long long)c0 * 4 + h * 8)), f);
-#pragma unroll
-      for (int i = 0; i < 8; ++i) wt[h * 2 + i / 4][i % 4] = f[i];
+  for (int i = 0; i < SC_LOADS; ++i) {
+    const int idx = i * SC_THREADS + threadIdx.x;
+    const int r = idx / (SC_COLS / 8), c = cblk + (idx % (SC_COLS / 8)) * 8, t = tblk - 3 + r;
+    v[i] = make_uint4(0, 0, 0, 0);
+    if (r < SC_TILE_ROWS && c < p.C) {
+      if (t >= 0) { if (t < t_end) v[i] = ld_stream16(xb + (long long)t * p.x_st + c); }
+      else v[i] = conv_state_row(p, b, t, c);
     }
-  } else {
-#pragma unroll
-    for (int e = 0; e < SC_CH; ++e)
-#pragma unroll
-      for (int j = 0; j < SC_MAX_W; ++j) {
-        const int tap = j - (SC_MAX_W - p.W);
-        wt[e][j] = tap >= 0 ? __bfloat162float(p.w[(long long)(c0 + e) * p.W + tap]) : 0.f;
-      }
   }
-  float bs[SC_CH];
 #pragma unroll
-  for (int e = 0; e < SC_CH; ++e) bs[e] = p.bias ? __bfloat162float(p.bias[c0 + e]) : 0.f;
+  for (int i = 0; i < SC_LOADS; ++i) {
+    const int idx = i * SC_THREADS + threadIdx.x;
+    if (idx < SC_TILE_ROWS * (SC_COLS / 8)) tile[idx / (SC_COLS / 8)][idx % (SC_COLS / 8)] = v[i];
+  }
 
-  __nv_bfloat16* yr = p.y + (long long)b * p.y_sb + c0;
-  float h1[SC_CH], h2[SC_CH], h3[SC_CH];                           // rows t-1, t-2, t-3
-  unpack4(raw[0], h3); unpack4(raw[1], h2); unpack4(raw[2], h1);
+  const int cg = threadIdx.x % (SC_COLS / SC_CH), slice = threadIdx.x / (SC_COLS / SC_CH);
+  const int c0 = cblk + cg * SC_CH;
+  const bool have = c0 < p.C;
+  // taps right-aligned in four slots: slot 3 multiplies the current row, slot 3-i the row i steps back
+  float wt[SC_CH][SC_MAX_W], bs[SC_CH];
 #pragma unroll
-  for (int i = 0; i < SC_TT; ++i) {
+  for (int e = 0; e < SC_CH; ++e) {
+    bs[e] = 0.f;
+#pragma unroll
+    for (int j = 0; j < SC_MAX_W; ++j) wt[e][j] = 0.f;
+  }
+  if (have) {
+    if (p.W == 4) {
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {                                // 4 channels x 4 taps = 32 contiguous bytes
+        float f[8];
+        unpack8(__ldg(reinterpret_cast<const uint4*>(p.w + (long long)c0 * 4 + h * 8)), f);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) wt[h * 2 + i / 4][i % 4] = f[i];
+      }
+    } else {
+#pragma unroll
+      for (int e = 0; e < SC_CH; ++e)
+#pragma unroll
+        for (int j = 0; j < SC_MAX_W; ++j) {
+          const int tap = j - (SC_MAX_W - p.W);
+          if (tap >= 0) wt[e][j] = __bfloat162float(p.w[(long long)(c0 + e) * p.W + tap]);
+        }
+    }
+    if (p.bias) {
+#pragma unroll
+      for (int e = 0; e < SC_CH; ++e) bs[e] = __bfloat162float(p.bias[c0 + e]);
+    }
+  }
+  __syncthreads();
+  if (!have) return;
+
+  const uint2* col = reinterpret_cast<const uint2*>(&tile[0][0]) + cg;      // row stride: SC_COLS / 4 uint2
+  constexpr int RS = SC_COLS / SC_CH;
+  constexpr int PER = SC_ROWS / SC_SLICES;
+  const int r0 = slice * PER;                                      // tile row of input t-3 for this slice's first output
+  float h1[SC_CH], h2[SC_CH], h3[SC_CH];                           // rows t-1, t-2, t-3
+  unpack4(col[(r0 + 0) * RS], h3); unpack4(col[(r0 + 1) * RS], h2); unpack4(col[(r0 + 2) * RS], h1);
+  __nv_bfloat16* yr = p.y + (long long)b * p.y_sb + c0;
+#pragma unroll
+  for (int i = 0; i < PER; ++i) {
+    const int t = tblk + r0 + i;
     float cur[SC_CH], o[SC_CH];
-    unpack4(raw[i + 3], cur);
+    unpack4(col[(r0 + 3 + i) * RS], cur);
 #pragma unroll
     for (int e = 0; e < SC_CH; ++e) {
       float a = bs[e];
@@ -112,23 +133,19 @@ __global__ void __launch_bounds__(SC_THREADS) kda_short_conv_kernel(const ShortC
       o[e] = p.silu ? a * fast_sigmoid(a) : a;
       h3[e] = h2[e]; h2[e] = h1[e]; h1[e] = cur[e];
     }
-    if (t0 + i < t1)
-      *reinterpret_cast<uint2*>(yr + (long long)(t0 + i) * p.y_st) = make_uint2(pack_bf16(o[0], o[1]), pack_bf16(o[2], o[3]));
+    if (t < t_end)
+      *reinterpret_cast<uint2*>(yr + (long long)t * p.y_st) = make_uint2(pack_bf16(o[0], o[1]), pack_bf16(o[2], o[3]));
   }
 
-  // the thread that owns the last row leaves the state: the last W inputs, oldest first
-  if (p.s_out && t1 == p.T) {
-    float st[SC_MAX_W][SC_CH];
-#pragma unroll
-    for (int j = 0; j < SC_MAX_W; ++j)
-      if (j < p.W) conv_input_row(p, b, p.T - p.W + j, c0, st[j]);
+  // the CTA that owns the last row leaves the state: the last W inputs, oldest first (tile row of input t: t - tblk + 3)
+  if (p.s_out && t_end == p.T && slice == 0) {
     __nv_bfloat16* s = p.s_out + ((long long)b * p.C + c0) * p.W;
+    for (int j = 0; j < p.W; ++j) {
+      float f[SC_CH];
+      unpack4(col[(p.T - p.W + j - tblk + 3) * RS], f);
 #pragma unroll
-    for (int j = 0; j < SC_MAX_W; ++j)
-      if (j < p.W) {
-#pragma unroll
-        for (int e = 0; e < SC_CH; ++e) s[e * p.W + j] = __float2bfloat16_rn(st[j][e]);
-      }
+      for (int e = 0; e < SC_CH; ++e) s[e * p.W + j] = __float2bfloat16_rn(f[e]);
+    }
   }
 }
 
@@ -228,20 +245,19 @@ extern "C" int daisy_b200_kda_short_conv(const void* x, int64_t x_sb, int64_t x_
                                          const void* state_in, void* state_out, void* y, int64_t y_sb, int64_t y_st,
                                          int B, int T, int C, int W, unsigned flags, void* stream) {
   if (!x || !w || !y || B <= 0 || T <= 0 || C <= 0) return DAISY_EINVAL;
-  if (W < 1 || W > SC_MAX_W || C % 8 != 0 || B > 65535 || (T + SC_TT * SC_SLICES - 1) / (SC_TT * SC_SLICES) > 65535) return DAISY_EUNSUPPORTED;
+  if (W < 1 || W > SC_MAX_W || C % 8 != 0 || B > 65535 || (T + SC_ROWS - 1) / SC_ROWS > 65535) return DAISY_EUNSUPPORTED;
   if (flags & ~DAISY_KDA_CONV_SILU) return DAISY_EINVAL;
   if (!daisy_aligned16(x) || !daisy_aligned16(y) || !daisy_aligned16(w) || (bias && !daisy_aligned16(bias)) ||
       x_sb % 8 || x_st % 8 || y_sb % 8 || y_st % 8)
     return DAISY_EALIGN;
-  // a state updated in place is read by the threads of the first rows and written by those of the last: one thread only
-  if (state_in && state_in == state_out && T > SC_TT) return DAISY_EINVAL;
+  // a state updated in place is read by the threads of the first rows and written by the CTA of the last: one CTA only
+  if (state_in && state_in == state_out && T > SC_ROWS) return DAISY_EINVAL;
   ShortConvParams p;
   p.x = (const __nv_bfloat16*)x; p.w = (const __nv_bfloat16*)w; p.bias = (const __nv_bfloat16*)bias;
   p.s_in = (const __nv_bfloat16*)state_in; p.s_out = (__nv_bfloat16*)state_out; p.y = (__nv_bfloat16*)y;
   p.x_sb = x_sb; p.x_st = x_st; p.y_sb = y_sb; p.y_st = y_st;
   p.T = T; p.C = C; p.W = W; p.silu = (flags & DAISY_KDA_CONV_SILU) ? 1 : 0;
-  const int groups = C / SC_CH, tb = SC_TT * SC_SLICES;
-  const dim3 grid((groups + SC_CG - 1) / SC_CG, (T + tb - 1) / tb, B);
+  const dim3 grid((C + SC_COLS - 1) / SC_COLS, (T + SC_ROWS - 1) / SC_ROWS, B);
   kda_short_conv_kernel<<<grid, SC_THREADS, 0, (cudaStream_t)stream>>>(p);
   DAISY_CHECK_LAUNCH();
   return DAISY_OK;

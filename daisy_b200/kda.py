@@ -74,7 +74,7 @@ class B200ShortConvolution(torch.nn.Conv1d):
             raise NotImplementedError("variable-length packing (cu_seqlens) is not implemented by the B200 KDA kernels")
         if cache is not None and cache.dtype != torch.bfloat16:
             cache = cache.to(torch.bfloat16)
-        step = cache is not None and x.shape[1] <= 8
+        step = cache is not None and x.shape[1] <= 32
         return ops.kda_short_conv(x if x.dtype == torch.bfloat16 else x.to(torch.bfloat16), self.weight, self.bias,
                                   state=cache, output_final_state=output_final_state or step,
                                   silu=self.activation is not None, inplace_state=step)

@@ -426,7 +426,7 @@ def kda_short_conv(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.T
                    inplace_state: bool = False):
     """Causal depthwise convolution (+ SiLU) of ``x [B,T,C]`` bf16 with ``weight [C,W]`` (or the Conv1d layout
     ``[C,1,W]``), W <= 4.  ``state [B,C,W]`` holds the W inputs before ``x`` (oldest first).  Returns
-    ``(y, final_state or None)``; with ``inplace_state`` (T <= 8 only) the final state overwrites ``state``."""
+    ``(y, final_state or None)``; with ``inplace_state`` (T <= 32 only) the final state overwrites ``state``."""
     _req(x, "x")
     if x.dim() != 3:
         raise ValueError("x must be [B, T, C]")

@@ -288,7 +288,7 @@ int daisy_b200_kda_gate(const void* g, int g_is_bf16, const float* a_log, const 
  * x, y [B, T, C] bf16 with batch / row strides in elements (multiples of 8); w [C, W] bf16 (the Conv1d weight
  * [C, 1, W]); bias [C] bf16 or null; state_in / state_out [B, C, W] bf16 or null: the last W inputs, oldest first
  * (the `cache` / final state of the reference call; state_out[., ., j] = in[T - W + j]).  state_out may alias
- * state_in only when T <= 8 (decode steps: the in-place cache update of the reference).  W <= 4, C % 8 == 0.
+ * state_in only when T <= 32 (decode steps: the in-place cache update of the reference).  W <= 4, C % 8 == 0.
  * flags: 0 or DAISY_KDA_CONV_SILU.  fp32 accumulation, one rounding to bf16. */
 int daisy_b200_kda_short_conv(const void* x, int64_t x_sb, int64_t x_st, const void* w, const void* bias,
                               const void* state_in, void* state_out, void* y, int64_t y_sb, int64_t y_st,
