@@ -162,79 +162,80 @@ struct OutNormParams {
   int o_fp32, mode;
 };
 
-__device__ __forceinline__ float round_bf16(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
-
-constexpr int ON_ROWS = 1;       // rows per lane group
 constexpr int ON_LPR = 8;        // lanes per row: elements [8 sub, 8 sub + 8) and [64 + 8 sub, 64 + 8 sub + 8)
 
-// One pass per thread, no loop: the block scheduler keeps the memory system fed.
+__device__ __forceinline__ uint32_t mul_bf16x2(uint32_t a, uint32_t b) {       // one rounding per lane, like a bf16 tensor product
+  uint32_t r;
+  asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+  return r;
+}
+
+// Gate combination for eight elements -> four packed bf16 pairs.  The exp / reciprocal / conversion unit is what this
+// kernel saturates first, so the two-factor mode rounds in pairs (one conversion per two values) and multiplies the
+// rounded factors as packed bf16, which is exactly bf16(bf16(n g s) * bf16(s)).
+template <int MODE>
+__device__ __forceinline__ uint4 gate8(const float* n, const float* g) {
+  uint32_t out[4];
+#pragma unroll
+  for (int e = 0; e < 8; e += 2) {
+    const float s0 = fast_sigmoid(g[e]), s1 = fast_sigmoid(g[e + 1]);
+    if (MODE == 0)      out[e / 2] = pack_bf16(n[e] * s0, n[e + 1] * s1);
+    else if (MODE == 1) out[e / 2] = pack_bf16(n[e] * g[e] * s0, n[e + 1] * g[e + 1] * s1);
+    else                out[e / 2] = mul_bf16x2(pack_bf16(n[e] * g[e] * s0, n[e + 1] * g[e + 1] * s1), pack_bf16(s0, s1));
+  }
+  return make_uint4(out[0], out[1], out[2], out[3]);
+}
+
+// One pass per thread (one row per group of eight lanes), no loop: the block scheduler keeps the memory system fed.
+template <int MODE, bool O32>
 __global__ void __launch_bounds__(256) kda_out_norm_kernel(const OutNormParams p) {
   const int sub = threadIdx.x & (ON_LPR - 1);
-  const long long row0 = (((long long)blockIdx.x * 256 + threadIdx.x) / ON_LPR) * ON_ROWS;
-  uint4 xa[ON_ROWS][2], xb[ON_ROWS][2], ga[ON_ROWS], gb[ON_ROWS];
-  long long row[ON_ROWS];
-  bool live[ON_ROWS];
-#pragma unroll
-  for (int u = 0; u < ON_ROWS; ++u) {
-    live[u] = row0 + u < p.rows;
-    row[u] = live[u] ? row0 + u : p.rows - 1;                      // past the end the last row is repeated
-    if (p.o_fp32) {
-      const float* src = reinterpret_cast<const float*>(p.o) + row[u] * ON_D + 8 * sub;
-      xa[u][0] = ld_stream16(src);      xa[u][1] = ld_stream16(src + 4);
-      xb[u][0] = ld_stream16(src + 64); xb[u][1] = ld_stream16(src + 68);
-    } else {
-      const __nv_bfloat16* src = reinterpret_cast<const __nv_bfloat16*>(p.o) + row[u] * ON_D + 8 * sub;
-      xa[u][0] = ld_stream16(src); xb[u][0] = ld_stream16(src + 64);
-    }
-    ga[u] = ld_stream16(p.g + row[u] * ON_D + 8 * sub);
-    gb[u] = ld_stream16(p.g + row[u] * ON_D + 64 + 8 * sub);
+  const long long row_raw = ((long long)blockIdx.x * 256 + threadIdx.x) / ON_LPR;
+  const bool live = row_raw < p.rows;
+  const long long row = live ? row_raw : p.rows - 1;               // past the end the last row is repeated: the
+  float x1[8], x2[8], g1[8], g2[8];                                // shuffles below need whole warps
+  if (O32) {
+    const float4* src = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.o) + row * ON_D + 8 * sub);
+    const float4 a = src[0], b = src[1], c = src[16], d = src[17];
+    x1[0] = a.x; x1[1] = a.y; x1[2] = a.z; x1[3] = a.w; x1[4] = b.x; x1[5] = b.y; x1[6] = b.z; x1[7] = b.w;
+    x2[0] = c.x; x2[1] = c.y; x2[2] = c.z; x2[3] = c.w; x2[4] = d.x; x2[5] = d.y; x2[6] = d.z; x2[7] = d.w;
+  } else {
+    const __nv_bfloat16* src = reinterpret_cast<const __nv_bfloat16*>(p.o) + row * ON_D + 8 * sub;
+    const uint4 a = ld_stream16(src), c = ld_stream16(src + 64);
+    unpack8(a, x1); unpack8(c, x2);
   }
-  float w1[8], w2[8];
+  {
+    const uint4 a = ld_stream16(p.g + row * ON_D + 8 * sub), c = ld_stream16(p.g + row * ON_D + 64 + 8 * sub);
+    unpack8(a, g1); unpack8(c, g2);
+  }
+  float ss = 0.f;
 #pragma unroll
-  for (int e = 0; e < 8; ++e) { w1[e] = 1.f; w2[e] = 1.f; }
+  for (int e = 0; e < 8; ++e) ss += x1[e] * x1[e] + x2[e] * x2[e];
+  ss += __shfl_xor_sync(0xffffffffu, ss, 4);
+  ss += __shfl_xor_sync(0xffffffffu, ss, 2);
+  ss += __shfl_xor_sync(0xffffffffu, ss, 1);
+  const float rstd = rsqrtf(ss * (1.0f / ON_D) + p.eps);
   if (p.w) {
+    float w1[8], w2[8];
     unpack8(__ldg(reinterpret_cast<const uint4*>(p.w + 8 * sub)), w1);
     unpack8(__ldg(reinterpret_cast<const uint4*>(p.w + 64 + 8 * sub)), w2);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) { x1[e] *= rstd * w1[e]; x2[e] *= rstd * w2[e]; }
+  } else {
+#pragma unroll
+    for (int e = 0; e < 8; ++e) { x1[e] *= rstd; x2[e] *= rstd; }
   }
-#pragma unroll
-  for (int u = 0; u < ON_ROWS; ++u) {
-    float x1[8], x2[8], g1[8], g2[8];
-    if (p.o_fp32) {
-      x1[0] = __uint_as_float(xa[u][0].x); x1[1] = __uint_as_float(xa[u][0].y); x1[2] = __uint_as_float(xa[u][0].z);
-      x1[3] = __uint_as_float(xa[u][0].w); x1[4] = __uint_as_float(xa[u][1].x); x1[5] = __uint_as_float(xa[u][1].y);
-      x1[6] = __uint_as_float(xa[u][1].z); x1[7] = __uint_as_float(xa[u][1].w);
-      x2[0] = __uint_as_float(xb[u][0].x); x2[1] = __uint_as_float(xb[u][0].y); x2[2] = __uint_as_float(xb[u][0].z);
-      x2[3] = __uint_as_float(xb[u][0].w); x2[4] = __uint_as_float(xb[u][1].x); x2[5] = __uint_as_float(xb[u][1].y);
-      x2[6] = __uint_as_float(xb[u][1].z); x2[7] = __uint_as_float(xb[u][1].w);
-    } else {
-      unpack8(xa[u][0], x1); unpack8(xb[u][0], x2);
-    }
-    unpack8(ga[u], g1); unpack8(gb[u], g2);
-    float ss = 0.f;
-#pragma unroll
-    for (int e = 0; e < 8; ++e) ss += x1[e] * x1[e] + x2[e] * x2[e];
-    ss += __shfl_xor_sync(0xffffffffu, ss, 4);                     // every lane of the warp is here: no early exit above
-    ss += __shfl_xor_sync(0xffffffffu, ss, 2);
-    ss += __shfl_xor_sync(0xffffffffu, ss, 1);
-    const float rstd = rsqrtf(ss * (1.0f / ON_D) + p.eps);
-    float o1[8], o2[8];
-#pragma unroll
-    for (int e = 0; e < 8; ++e) {
-      const float n1 = x1[e] * rstd * w1[e], n2 = x2[e] * rstd * w2[e];
-      const float s1 = fast_sigmoid(g1[e]), s2 = fast_sigmoid(g2[e]);
-      if (p.mode == 0)      { o1[e] = n1 * s1; o2[e] = n2 * s2; }                              // sigmoid gate
-      else if (p.mode == 1) { o1[e] = n1 * g1[e] * s1; o2[e] = n2 * g2[e] * s2; }              // swish gate
-      else {                                                       // swish-gated norm (rounded), then x sigmoid
-        o1[e] = round_bf16(n1 * g1[e] * s1) * round_bf16(s1);
-        o2[e] = round_bf16(n2 * g2[e] * s2) * round_bf16(s2);
-      }
-    }
-    if (live[u]) {
-      __nv_bfloat16* dst = p.y + row[u] * ON_D + 8 * sub;
-      *reinterpret_cast<uint4*>(dst) = pack8(o1);
-      *reinterpret_cast<uint4*>(dst + 64) = pack8(o2);
-    }
+  if (live) {
+    __nv_bfloat16* dst = p.y + row * ON_D + 8 * sub;
+    *reinterpret_cast<uint4*>(dst) = gate8<MODE>(x1, g1);
+    *reinterpret_cast<uint4*>(dst + 64) = gate8<MODE>(x2, g2);
   }
+}
+
+template <int MODE>
+static void launch_out_norm(const OutNormParams& p, unsigned grid, cudaStream_t st) {
+  if (p.o_fp32) kda_out_norm_kernel<MODE, true><<<grid, 256, 0, st>>>(p);
+  else          kda_out_norm_kernel<MODE, false><<<grid, 256, 0, st>>>(p);
 }
 
 }  // namespace daisy
@@ -272,11 +273,13 @@ extern "C" int daisy_b200_kda_out_norm(const void* o, int o_is_fp32, const void*
   OutNormParams p;
   p.o = o; p.g = (const __nv_bfloat16*)gate; p.w = (const __nv_bfloat16*)weight; p.y = (__nv_bfloat16*)y;
   p.rows = rows; p.eps = eps; p.o_fp32 = o_is_fp32 ? 1 : 0; p.mode = mode;
-  const long long rows_per_cta = 256 / ON_LPR * ON_ROWS;
+  const long long rows_per_cta = 256 / ON_LPR;
   const long long want = (rows + rows_per_cta - 1) / rows_per_cta;
   if (want > 0x7fffffffLL) return DAISY_EUNSUPPORTED;
   const unsigned grid = (unsigned)want;
-  kda_out_norm_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(p);
+  if (mode == 0)      launch_out_norm<0>(p, grid, (cudaStream_t)stream);
+  else if (mode == 1) launch_out_norm<1>(p, grid, (cudaStream_t)stream);
+  else                launch_out_norm<2>(p, grid, (cudaStream_t)stream);
   DAISY_CHECK_LAUNCH();
   return DAISY_OK;
 }
