@@ -604,7 +604,7 @@ def main():
     if want == "kda_small":
         res = run_kda(KDA_SMALL, args.steps, args.warmup, dist, rank, world, peaks, lean=True)
     if want == "kda_layer_small":
-        res = run_kda_layer(dict(KDA_SMALL, B=2), args.steps, args.warmup, peaks, lean=True)
+        res = run_kda_layer(dict(KDA_SMALL, B=4), args.steps, args.warmup, peaks, lean=True)
     if want == "prefill_c4":
         res = run_prefill(PREFILL_C4, max(2, args.steps // 4), warm, dist, rank, world, peaks, "prefill_c4")
     if want == "all" and rank == 0 and not args.no_extras:
