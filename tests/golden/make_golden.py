@@ -257,6 +257,11 @@ def kda_layer_case():
     out.update(norm_x=x.numpy(), norm_gate=gate.numpy(), norm_weight=wgt.numpy(), norm_swish=normed.numpy(),
                norm_sigmoid=(F.rms_norm(x, (D,), wgt, 1e-6) * torch.sigmoid(gate)).numpy(),
                norm_ref_bf16_as_fp32=y_b.float().numpy())
+    # the layer's parameter names and shapes, from the reference class itself (state-dict compatibility)
+    from models.daisy.attention_kimi import KimiLinearSelfAttention
+    ref_layer = KimiLinearSelfAttention(256, 2, 64, 128)
+    names = sorted(f"{n}:{'x'.join(map(str, p.shape))}:{str(p.dtype).replace('torch.', '')}" for n, p in ref_layer.named_parameters())
+    out["layer_parameters"] = np.array(names)
     np.savez_compressed(os.path.join(HERE, "kda_layer_small.npz"), **out)
     print("kda_layer_small", sorted(out))
 

@@ -110,3 +110,15 @@ def test_shard_bounds_cover_everything():
             assert all(a[1] == b[0] for a, b in zip(spans, spans[1:]))
             sizes = [b - a for a, b in spans]
             assert max(sizes) - min(sizes) <= 1
+
+
+def test_kda_layer_module_has_the_reference_parameters(golden_dir):
+    """B200KimiLinearSelfAttention registers the parameters of the reference's KimiLinearSelfAttention
+    (models/daisy/attention_kimi.py:65-112), name for name, shape for shape, dtype for dtype: the list in the
+    fixture was written from the reference class."""
+    import numpy as np
+    from daisy_b200 import B200KimiLinearSelfAttention
+    want = sorted(np.load(os.path.join(golden_dir, "kda_layer_small.npz"))["layer_parameters"].tolist())
+    m = B200KimiLinearSelfAttention(256, 2, 64, 128)
+    got = sorted(f"{n}:{'x'.join(map(str, p.shape))}:{str(p.dtype).replace('torch.', '')}" for n, p in m.named_parameters())
+    assert got == want
