@@ -506,6 +506,11 @@ def run_kda_layer(cfg, steps, warmup, peaks, lean=False):
     ms = timed_steps(lambda: ops.kda_out_norm(o, gate, nw), steps, warmup, None) / steps
     gbs = 3 * o.numel() * 2 / (ms * 1e-3) / 1e9
     out["out_norm"] = {"ms": ms, "hbm_gbs": gbs, "frac_of_copy": gbs / peaks["hbm_gbs"], "bytes": "read o, gate + write y"}
+    a_log = torch.log(torch.empty(H, device=dev).uniform_(1, 16))
+    dt_bias = torch.zeros(C, device=dev)
+    ms = timed_steps(lambda: ops.kda_gate(x, a_log, K, dt_bias), steps, warmup, None) / steps
+    gbs = x.numel() * 6 / (ms * 1e-3) / 1e9
+    out["gate"] = {"ms": ms, "hbm_gbs": gbs, "frac_of_copy": gbs / peaks["hbm_gbs"], "bytes": "read g (bf16) + write fp32"}
     if lean:
         return {"name": "kda_layer", "ms_per_step": out["short_conv"]["ms"] + out["out_norm"]["ms"],
                 "value": out["short_conv"]["hbm_gbs"], "unit": "GB/s (short_conv)", "steps": steps, "launches_per_step": 2,
@@ -644,6 +649,8 @@ def main():
             line["cpu_baseline"] = cpu_prefill_sample(PREFILL_C2)[0]
         else:
             line["cpu_baseline"] = None
+        if "passes" in res:
+            line["passes"] = res["passes"]
         for k_, v_ in extra.items():
             line[k_] = {kk: vv for kk, vv in v_.items() if kk not in ("name",)}
         print(json.dumps(line), flush=True)
