@@ -52,7 +52,7 @@ SIGNATURES = {
     "daisy_b200_kda_recurrent_fwd": (_i, [_vp] * 8 + [_i] * 5 + [_f, _u, _vp]),
     "daisy_b200_kda_gate": (_i, [_vp, _i, _vp, _vp, _vp, _i64, _i, _i, _f, _f, _u, _vp]),
     "daisy_b200_kda_short_conv": (_i, [_vp, _i64, _i64, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i, _i, _i, _i, _u, _vp]),
-    "daisy_b200_kda_out_norm": (_i, [_vp, _i, _vp, _vp, _vp, _i64, _i, _f, _i, _vp]),
+    "daisy_b200_kda_out_norm": (_i, [_vp, _i, _vp, _vp, _i, _vp, _vp, _i64, _i, _f, _i, _vp]),
     "daisy_b200_selftest_umma": (_i, [_vp] * 3 + [_i, _i, _vp, _vp]),
 }
 

@@ -162,6 +162,8 @@ struct OutNormParams {
   const void* o;                 // [rows, 128] bf16 or fp32
   const __nv_bfloat16* g;        // [rows, 128] gate pre-activation
   const __nv_bfloat16* w;        // [128] or null (ones)
+  const __nv_bfloat16* gbias;    // [H, 128] or null: added to the gate (row r belongs to head r % H), rounded to bf16
+  int H;
   __nv_bfloat16* y;              // [rows, 128]
   long long rows;
   float eps;
@@ -213,6 +215,17 @@ __global__ void __launch_bounds__(256) kda_out_norm_kernel(const OutNormParams p
   {
     const uint4 a = ld_stream16(p.g + row * ON_D + 8 * sub), c = ld_stream16(p.g + row * ON_D + 64 + 8 * sub);
     unpack8(a, g1); unpack8(c, g2);
+  }
+  if (p.gbias) {                                                   // the bias of the gate's projection, as its Linear adds it
+    const __nv_bfloat16* bsrc = p.gbias + (row % p.H) * ON_D + 8 * sub;
+    float b1[8], b2[8];
+    unpack8(__ldg(reinterpret_cast<const uint4*>(bsrc)), b1);
+    unpack8(__ldg(reinterpret_cast<const uint4*>(bsrc + 64)), b2);
+#pragma unroll
+    for (int e = 0; e < 8; e += 2) {
+      const uint32_t r1 = pack_bf16(g1[e] + b1[e], g1[e + 1] + b1[e + 1]), r2 = pack_bf16(g2[e] + b2[e], g2[e + 1] + b2[e + 1]);
+      g1[e] = bf16_lo(r1); g1[e + 1] = bf16_hi(r1); g2[e] = bf16_lo(r2); g2[e + 1] = bf16_hi(r2);
+    }
   }
   float ss = 0.f;
 #pragma unroll
@@ -271,14 +284,18 @@ extern "C" int daisy_b200_kda_short_conv(const void* x, int64_t x_sb, int64_t x_
   return DAISY_OK;
 }
 
-extern "C" int daisy_b200_kda_out_norm(const void* o, int o_is_fp32, const void* gate, const void* weight, void* y,
-                                       int64_t rows, int D, float eps, int mode, void* stream) {
+extern "C" int daisy_b200_kda_out_norm(const void* o, int o_is_fp32, const void* gate, const void* gate_bias, int H,
+                                       const void* weight, void* y, int64_t rows, int D, float eps, int mode,
+                                       void* stream) {
   if (!o || !gate || !y || rows <= 0 || mode < 0 || mode > 2 || !(eps >= 0.f)) return DAISY_EINVAL;
+  if (gate_bias && (H <= 0 || rows % H != 0)) return DAISY_EINVAL;
   if (D != ON_D) return DAISY_EUNSUPPORTED;
-  if (!daisy_aligned16(o) || !daisy_aligned16(gate) || !daisy_aligned16(y) || (weight && !daisy_aligned16(weight)))
+  if (!daisy_aligned16(o) || !daisy_aligned16(gate) || !daisy_aligned16(y) || (weight && !daisy_aligned16(weight)) ||
+      (gate_bias && !daisy_aligned16(gate_bias)))
     return DAISY_EALIGN;
   OutNormParams p;
   p.o = o; p.g = (const __nv_bfloat16*)gate; p.w = (const __nv_bfloat16*)weight; p.y = (__nv_bfloat16*)y;
+  p.gbias = (const __nv_bfloat16*)gate_bias; p.H = gate_bias ? H : 1;
   p.rows = rows; p.eps = eps; p.o_fp32 = o_is_fp32 ? 1 : 0; p.mode = mode;
   const long long rows_per_cta = 256 / ON_LPR;
   const long long want = (rows + rows_per_cta - 1) / rows_per_cta;

@@ -92,8 +92,8 @@ class B200FusedRMSNormGated(torch.nn.Module):
         self.weight = torch.nn.Parameter(torch.ones(hidden_size, dtype=dtype))
         self.bias = None
 
-    def forward(self, x, gate):
-        return ops.kda_out_norm(x, gate, self.weight, eps=1e-6)
+    def forward(self, x, gate, gate_bias=None):
+        return ops.kda_out_norm(x, gate, self.weight, eps=1e-6, gate_bias=gate_bias)
 
 
 def _linear(x, weight, bias=None):
@@ -173,8 +173,8 @@ class B200KimiLinearSelfAttention(torch.nn.Module):
         rec = self._recurrent_state if use_cache else None
         o, rec = chunk_kda(q=q, k=k, v=v, g=g, beta=beta, initial_state=rec, output_final_state=use_cache,
                            use_qk_l2norm_in_kernel=True)
-        gp = _linear(_linear(x, self.g_proj[0].weight), self.g_proj[1].weight, self.g_proj[1].bias)
-        o = self.o_norm(o, gp.view(B, T, H, self.head_v_dim))
+        gp = _linear(_linear(x, self.g_proj[0].weight), self.g_proj[1].weight)        # its bias is added in the norm kernel
+        o = self.o_norm(o, gp.view(B, T, H, self.head_v_dim), self.g_proj[1].bias)
         if use_cache:
             self._recurrent_state, self._conv_state = rec, conv_state
             self._seen += T

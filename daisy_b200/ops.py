@@ -456,9 +456,10 @@ def kda_short_conv(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.T
 
 
 def kda_out_norm(o: torch.Tensor, gate: torch.Tensor, weight: Optional[torch.Tensor] = None, eps: float = 1e-6,
-                 mode: int = _lib.KDA_NORM_SWISH_SIGMOID) -> torch.Tensor:
-    """Gated RMS norm over the last dimension (128) of ``o`` (bf16 or fp32) with the gate pre-activation ``gate``
-    (bf16, same shape); bf16 result of ``o``'s shape.  ``mode``: ``_lib.KDA_NORM_*``."""
+                 mode: int = _lib.KDA_NORM_SWISH_SIGMOID, gate_bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Gated RMS norm over the last dimension (128) of ``o [..., H, 128]`` (bf16 or fp32) with the gate
+    pre-activation ``gate`` (bf16, same shape); bf16 result of ``o``'s shape.  ``mode``: ``_lib.KDA_NORM_*``.
+    ``gate_bias [H*128]``: added to the gate inside the kernel (the bias of the projection that produced it)."""
     if not o.is_cuda:
         raise ValueError("o must be a CUDA tensor")
     if o.dtype not in (torch.bfloat16, torch.float32):
@@ -470,8 +471,15 @@ def kda_out_norm(o: torch.Tensor, gate: torch.Tensor, weight: Optional[torch.Ten
     D = o.shape[-1]
     if weight is not None:
         weight = weight.to(device=o.device, dtype=torch.bfloat16).contiguous()
+    H = 1
+    if gate_bias is not None:
+        if o.dim() < 2 or gate_bias.numel() != o.shape[-2] * D:
+            raise ValueError("gate_bias must hold H*D values for o [..., H, D]")
+        H = o.shape[-2]
+        gate_bias = gate_bias.to(device=o.device, dtype=torch.bfloat16).contiguous()
     y = torch.empty(o.shape, dtype=torch.bfloat16, device=o.device)
     rc = _lib.lib().daisy_b200_kda_out_norm(o.data_ptr(), 1 if o.dtype == torch.float32 else 0, gate.data_ptr(),
+                                            gate_bias.data_ptr() if gate_bias is not None else None, H,
                                             weight.data_ptr() if weight is not None else None, y.data_ptr(),
                                             o.numel() // D, D, float(eps), int(mode), _stream(o))
     _lib.check(rc, "daisy_b200_kda_out_norm")

@@ -298,9 +298,11 @@ int daisy_b200_kda_short_conv(const void* x, int64_t x_sb, int64_t x_st, const v
  * models/daisy/attention_kimi.py:137 (CompilableFusedRMSNormGated, :41-62; third-party fla rms_norm_gated):
  *   n = o * rsqrt(mean(o^2) + eps) * weight,  y = n combined with the gate as `mode` says (DAISY_KDA_NORM_*).
  * o [rows, D] bf16 (o_is_fp32 == 0) or float32; gate [rows, D] bf16; weight [D] bf16 or null (ones); y [rows, D]
- * bf16.  D = 128.  The reference passes no eps: rms_norm_gated's default 1e-6. */
-int daisy_b200_kda_out_norm(const void* o, int o_is_fp32, const void* gate, const void* weight, void* y,
-                            int64_t rows, int D, float eps, int mode, void* stream);
+ * bf16.  D = 128.  The reference passes no eps: rms_norm_gated's default 1e-6.  gate_bias [H, D] bf16 or null: the
+ * bias of the gate's projection (g_proj[1].bias, :106), added to `gate` here -- row r belongs to head r % H, the sum is
+ * rounded to bf16 as the Linear's output would be -- so the projection itself can run bias-free. */
+int daisy_b200_kda_out_norm(const void* o, int o_is_fp32, const void* gate, const void* gate_bias, int H,
+                            const void* weight, void* y, int64_t rows, int D, float eps, int mode, void* stream);
 
 /* ---------------------------------------------------------------------------------------------
  * Self-test of the tensor-core building blocks (no reference counterpart): C[128,128] float32 =

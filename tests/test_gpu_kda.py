@@ -161,3 +161,39 @@ def test_kda_gate_matches_reference_fixture(golden_dir):
     # identical up to one bf16 ulp where the fp32 value sits on a rounding boundary
     assert ((yb.float().cpu() - refb).abs() <= refb.abs() * 2.0 ** -7).all()
     assert (yb.float().cpu() == refb).float().mean().item() > 0.999
+
+
+def test_chunk_kda_against_fla_triton():
+    """The function the reference itself calls (fla.ops.kda.chunk_kda, models/daisy/attention_kimi.py:133-134, with
+    use_qk_l2norm_in_kernel=True), run on this GPU where the third-party package works: same inputs, with an
+    initial state and the final state returned, T not a multiple of the chunk.  Skips if fla / Triton cannot run."""
+    try:
+        from fla.ops.kda import chunk_kda as fla_chunk_kda
+    except Exception as e:
+        pytest.skip(f"fla not importable: {e}")
+    from daisy_b200.kda import chunk_kda
+    B, T, H, K = 2, 333, 4, 128
+    g_ = torch.Generator(device="cuda").manual_seed(77)
+    q, k, v = (torch.randn(B, T, H, K, device="cuda", generator=g_).bfloat16() for _ in range(3))
+    g = torch.nn.functional.logsigmoid(torch.randn(B, T, H, K, device="cuda", generator=g_))
+    beta = torch.sigmoid(torch.randn(B, T, H, device="cuda", generator=g_))
+    h0 = torch.randn(B, H, K, K, device="cuda", generator=g_) * 0.1
+    try:
+        with torch.no_grad():
+            o_ref, s_ref = fla_chunk_kda(q=q, k=k, v=v, g=g, beta=beta, initial_state=h0.clone(), output_final_state=True,
+                                         use_qk_l2norm_in_kernel=True)
+        torch.cuda.synchronize()
+    except Exception as e:
+        pytest.skip(f"fla's Triton kernels did not run here: {type(e).__name__}: {e}")
+    o, s = chunk_kda(q=q, k=k, v=v, g=g, beta=beta, initial_state=h0, output_final_state=True,
+                     use_qk_l2norm_in_kernel=True)
+    rel_o = ((o.float() - o_ref.float()).norm() / o_ref.float().norm()).item()
+    rel_s = ((s.float() - s_ref.float()).norm() / s_ref.float().norm()).item()
+    # both sides round their output to bf16 (1.7e-3 of rounding noise each) and differ in internal precision
+    assert rel_o <= 5e-3, rel_o
+    assert rel_s <= 5e-3, rel_s
+    # and both sit equally close to the fp32 recurrence
+    o_or, s_or = okda.kda_recurrent(q.float().cpu(), k.float().cpu(), v.float().cpu(), g.cpu(), beta.cpu(), None, h0.cpu(), True)
+    ours = ((o.float().cpu() - o_or).norm() / o_or.norm()).item()
+    theirs = ((o_ref.float().cpu() - o_or).norm() / o_or.norm()).item()
+    assert ours <= max(3e-3, 1.5 * theirs), (ours, theirs)

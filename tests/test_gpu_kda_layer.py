@@ -102,6 +102,12 @@ def test_out_norm_matches_oracle(rows):
         ref = okda.gated_rms_norm(o.float().cpu(), gate.float().cpu(), w.float().cpu(), mode=name)
         assert y.shape == o.shape
         assert_close_bf16(y, ref, f"{name} rows={rows}")
+    if len(rows) >= 2:                                               # gate bias per (head, channel), added in the kernel
+        H = rows[-1]
+        gb = (torch.randn(H * 128, device="cuda", generator=g_) * 0.5).bfloat16()
+        yb = ops.kda_out_norm(o, gate, w, gate_bias=gb)
+        gsum = (gate.float() + gb.float().view(H, 128)).bfloat16()
+        assert torch.equal(yb, ops.kda_out_norm(o, gsum, w))
     y32 = ops.kda_out_norm(o.float(), gate, None)
     assert_close_bf16(y32, okda.gated_rms_norm(o.float().cpu(), gate.float().cpu(), None), "fp32 input, no weight")
 
