@@ -159,9 +159,10 @@ def dist_env():
 
 
 def rope_full(D, T, device):
-    from oracle import swa
-    cos, sin = swa.rope_tables(D, T, base=ROPE_BASE, truncate=False)
-    return cos.to(device), sin.to(device)
+    """Full (untruncated) cos/sin tables [T, D/2] fp32, frequencies (1/base)**linspace(0, 1, D/2)."""
+    freq = (1.0 / ROPE_BASE) ** torch.linspace(0, 1, steps=D // 2, dtype=torch.float32)
+    theta = torch.arange(T, dtype=torch.float32)[:, None] * freq[None, :]
+    return theta.cos().to(device), theta.sin().to(device)
 
 
 def timed_steps(step, steps, warmup, dist):
@@ -193,7 +194,7 @@ def timed_steps(step, steps, warmup, dist):
 
 def run_prefill(cfg, steps, warmup, dist, rank, world, peaks, name, lean=False):
     from daisy_b200 import ops, _lib
-    from oracle import swa
+    from daisy_b200 import accounting as acct
     B, T, H, D, W = cfg["B"], cfg["T"], cfg["H"], cfg["D"], cfg["window"]
     dev = torch.device("cuda", torch.cuda.current_device())
     g = torch.Generator(device=dev).manual_seed(1234 + rank)
@@ -204,10 +205,10 @@ def run_prefill(cfg, steps, warmup, dist, rank, world, peaks, name, lean=False):
     out = torch.empty(B, T, H, D, dtype=torch.bfloat16, device=dev)
     k_out = torch.empty(B, T, H, D, dtype=torch.bfloat16, device=dev)
     v_out = torch.empty_like(k_out)
-    flops = swa.prefill_flops(B, T, H, D, W)
+    flops = acct.prefill_flops(B, T, H, D, W)
 
     def step():
-        ops.swa_prefill(q, k, v, cos, sin, W, eps=swa.FP32_EPS, workspace=ws, out=out, k_out=k_out, v_out=v_out)
+        ops.swa_prefill(q, k, v, cos, sin, W, eps=acct.FP32_EPS, workspace=ws, out=out, k_out=k_out, v_out=v_out)
 
     sampler = ClockSampler(dev.index or 0)
     sampler.start()
@@ -220,7 +221,7 @@ def run_prefill(cfg, steps, warmup, dist, rank, world, peaks, name, lean=False):
                 "clocks": clocks, "launches_per_step": 2, "roofline": None, "e2e": None,
                 "config": {"workload": f"{name}: B={B} T={T} H={H} D={D} window={W} (profiler capture case)"}}
     # dominant kernel alone (attention on prepared tensors), CUDA events around each launch
-    qp, kp, vp = ops.qkv_prep(q, k, v, cos, sin, swa.FP32_EPS)
+    qp, kp, vp = ops.qkv_prep(q, k, v, cos, sin, acct.FP32_EPS)
     ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
     out_k = torch.empty_like(out)
     for _ in range(warmup):
@@ -241,7 +242,7 @@ def run_prefill(cfg, steps, warmup, dist, rank, world, peaks, name, lean=False):
     host_call = HostPrefill(T, H, D, device=dev, rows_per_chunk=1)
 
     def e2e_step():
-        host_call(hq, hk, hv, cos, sin, W, hout, eps=swa.FP32_EPS)
+        host_call(hq, hk, hv, cos, sin, W, hout, eps=acct.FP32_EPS)
 
     e2e_steps = max(2, min(steps, 5))
     e2e_ms = timed_steps(e2e_step, e2e_steps, 1, dist)
@@ -279,7 +280,7 @@ def run_prefill(cfg, steps, warmup, dist, rank, world, peaks, name, lean=False):
 
 def run_decode(cfg, warmup, dist, rank, world, peaks, lean=False, extras=True):
     from daisy_b200 import ops, _lib
-    from oracle import swa
+    from daisy_b200 import accounting as acct
     B, H, D, cap, W, nsteps = cfg["B"], cfg["H"], cfg["D"], cfg["cap"], cfg["window"], cfg["steps"]
     dev = torch.device("cuda", torch.cuda.current_device())
     g = torch.Generator(device=dev).manual_seed(4321 + rank)
@@ -299,14 +300,14 @@ def run_decode(cfg, warmup, dist, rank, world, peaks, lean=False, extras=True):
 
     def step():
         t, i = state["t"], state["i"]
-        ops.swa_decode_step(qs[i], ks[i], vs[i], kc, vc, t, cap, W, cos[t], sin[t], eps=swa.FP32_EPS,
+        ops.swa_decode_step(qs[i], ks[i], vs[i], kc, vc, t, cap, W, cos[t], sin[t], eps=acct.FP32_EPS,
                             write_ring=True, splits=splits, workspace=ws, out=out[i], return_new_kv=False)
         state["t"], state["i"] = t + 1, i + 1
 
     ms = timed_steps(step, nsteps, warmup, dist)
     ops.check_device_status(dev)
     per = ms / nsteps
-    byts = swa.decode_bytes(B, H, D, W - 1)
+    byts = acct.decode_bytes(B, H, D, W - 1)
     gbs = byts / (per * 1e-3) / 1e9
     if lean:
         return {"name": "decode", "ms_per_step": per, "tokens_per_s": world * B / (per * 1e-3), "hbm_gbs": gbs,
@@ -384,7 +385,7 @@ def run_projection(B, T, H, D, steps, warmup, lean=False):
     starts from q, k, v after the projection); reported beside it."""
     import torch.nn.functional as F
     from daisy_b200 import ops
-    from oracle import swa
+    from daisy_b200 import accounting as acct
     dev = torch.device("cuda", torch.cuda.current_device())
     dim = H * D
     g = torch.Generator(device=dev).manual_seed(7)
@@ -394,7 +395,7 @@ def run_projection(B, T, H, D, steps, warmup, lean=False):
     cos, sin = rope_full(D, T, dev)
 
     def ours():
-        return ops.qkv_gemm(x, wq, cos, sin, H, swa.FP32_EPS)
+        return ops.qkv_gemm(x, wq, cos, sin, H, acct.FP32_EPS)
 
     ms = timed_steps(ours, steps, warmup, None) / steps
     flops = 2.0 * B * T * dim * 3 * dim
@@ -407,7 +408,7 @@ def run_projection(B, T, H, D, steps, warmup, lean=False):
 
     def lib():
         q, k, v = F.linear(x, wq).view(B, T, 3 * H, D).chunk(3, dim=-2)
-        return ops.qkv_prep(q, k, v, cos, sin, swa.FP32_EPS)
+        return ops.qkv_prep(q, k, v, cos, sin, acct.FP32_EPS)
 
     y = torch.randn(B, T, dim, device=dev, generator=g).bfloat16()
     res["cublas_plus_prep_ms"] = timed_steps(lib, steps, warmup, None) / steps
@@ -436,7 +437,7 @@ def run_projection(B, T, H, D, steps, warmup, lean=False):
 
 def run_kda(cfg, steps, warmup, dist, rank, world, peaks, lean=False):
     from daisy_b200 import ops
-    from oracle import kda as okda
+    from daisy_b200 import accounting as acct
     B, T, H, K = cfg["B"], cfg["T"], cfg["H"], cfg["K"]
     dev = torch.device("cuda", torch.cuda.current_device())
     g_ = torch.Generator(device=dev).manual_seed(99 + rank)
@@ -452,7 +453,7 @@ def run_kda(cfg, steps, warmup, dist, rank, world, peaks, lean=False):
     ops.check_device_status(dev)
     per = ms / steps
     th = B * T * H
-    byts = th * okda.kda_bytes_per_token_head(K, K)
+    byts = th * acct.kda_bytes_per_token_head(K, K)
     gbs = byts / (per * 1e-3) / 1e9
     if lean:
         return {"name": "kda", "ms_per_step": per, "value": world * th / (per * 1e-3), "unit": "token-heads/s", "steps": steps,
@@ -474,7 +475,7 @@ def run_kda(cfg, steps, warmup, dist, rank, world, peaks, lean=False):
         dist.all_gather(gathered, res["o"])
         del gathered
     return {"name": "kda_c5", "ms_per_step": per, "value": world * th / (per * 1e-3), "unit": "token-heads/s",
-            "hbm_gbs": world * gbs, "tflops": world * th * okda.kda_flops_per_token_head(K, K) / (per * 1e-3) / 1e12,
+            "hbm_gbs": world * gbs, "tflops": world * th * acct.kda_flops_per_token_head(K, K) / (per * 1e-3) / 1e12,
             "steps": steps, "launches_per_step": 2, "finite": bool(torch.isfinite(res["o"].float()).all()),
             "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                          "frac": gbs / peaks["hbm_gbs"], "traffic": None,
@@ -522,6 +523,72 @@ def run_kda_layer(cfg, steps, warmup, peaks, lean=False):
         ms = timed_steps(lambda: layer(x, None, None), max(3, steps // 2), 2, None) / max(3, steps // 2)
     out["layer_forward_ms"] = ms
     out["config"] = {"workload": f"kda layer: B={B} T={T} dim={C} H={H} K=V={K}, conv taps 4"}
+    return out
+
+
+def run_library_context(steps, warmup):
+    """Context numbers, not a bench arm (``--library-context``): the GPU library calls the reference makes for the
+    same work, written out here with torch / third-party calls because the reference's modules cannot travel to the
+    GPU box.  (1) Its inference attention path (models/daisy/attention.py:116-127,141-154): RMS norm and rotation
+    in eager torch, then ``scaled_dot_product_attention`` with the dense additive window mask, scale 0.12, at the
+    headline prefill shape.  (2) The fla Triton kernels its KDA layer calls (``chunk_kda``, ``ShortConvolution``,
+    ``rms_norm_gated``) at the KDA shape.  Each entry is None with a reason if the call cannot run here."""
+    import torch.nn.functional as F
+    from daisy_b200 import accounting
+    accounting_prefill_flops = lambda: accounting.prefill_flops(*(PREFILL_C2[k] for k in ("B", "T", "H", "D", "window")))
+    out = {}
+    dev = torch.device("cuda", torch.cuda.current_device())
+    g_ = torch.Generator(device=dev).manual_seed(3)
+    B, T, H, D, W = (PREFILL_C2[k] for k in ("B", "T", "H", "D", "window"))
+    try:
+        q, k, v = (torch.randn(B, T, H, D, device=dev, generator=g_).bfloat16() for _ in range(3))
+        ang = torch.arange(T, device=dev)[:, None] * (ROPE_BASE ** (-torch.arange(0, D, 2, device=dev) / D))[None, :]
+        cos, sin = ang.cos()[None, :, None, :], ang.sin()[None, :, None, :]
+        i = torch.arange(T, device=dev)
+        allowed = (i[:, None] >= i[None, :]) & (i[:, None] - i[None, :] < W)
+        mask = torch.zeros(T, T, device=dev, dtype=torch.bfloat16).masked_fill_(~allowed, float("-inf"))[None, None]
+
+        def rope(x):
+            x1, x2 = x[..., :D // 2].float(), x[..., D // 2:].float()
+            return torch.cat([x1 * cos + x2 * sin, x2 * cos - x1 * sin], -1).to(x.dtype)
+
+        def step():
+            qn, kn, vn = (F.rms_norm(t, (D,)) for t in (q, k, v))
+            qn, kn = rope(qn), rope(kn)
+            return F.scaled_dot_product_attention(qn.transpose(1, 2), kn.transpose(1, 2), vn.transpose(1, 2),
+                                                  is_causal=False, attn_mask=mask, scale=0.12)
+
+        ms = timed_steps(step, max(2, steps // 4), 2, None) / max(2, steps // 4)
+        ms_attn = timed_steps(lambda: F.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2),
+                                                                     is_causal=False, attn_mask=mask, scale=0.12),
+                              max(2, steps // 4), 1, None) / max(2, steps // 4)
+        out["torch_sdpa_dense_mask"] = {"step_ms": ms, "sdpa_only_ms": ms_attn,
+                                        "tflops_window_algorithmic": accounting_prefill_flops() / (ms * 1e-3) / 1e12}
+        del q, k, v, mask, cos, sin
+    except Exception as e:                                           # noqa: BLE001 - a context number only
+        out["torch_sdpa_dense_mask"] = None
+        out["torch_sdpa_reason"] = f"{type(e).__name__}: {e}"[:200]
+    torch.cuda.empty_cache()
+    try:
+        from fla.ops.kda import chunk_kda as fla_chunk_kda
+        from fla.modules import ShortConvolution
+        from fla.modules.fused_norm_gate import rms_norm_gated
+        B, T, H, K = (KDA_C5[k] for k in ("B", "T", "H", "K"))
+        q, k, v = (torch.randn(B, T, H, K, device=dev, generator=g_).bfloat16() for _ in range(3))
+        g = F.logsigmoid(torch.randn(B, T, H, K, device=dev, generator=g_))
+        beta = torch.sigmoid(torch.randn(B, T, H, device=dev, generator=g_))
+        with torch.no_grad():
+            ms = timed_steps(lambda: fla_chunk_kda(q=q, k=k, v=v, g=g, beta=beta, use_qk_l2norm_in_kernel=True),
+                             steps, warmup, None) / steps
+            out["fla_chunk_kda_ms"] = ms
+            conv = ShortConvolution(H * K, 4, activation="silu", dtype=torch.bfloat16).to(dev)
+            x = q.view(B, T, H * K)
+            out["fla_short_conv_ms"] = timed_steps(lambda: conv(x=x), steps, warmup, None) / steps
+            w = torch.ones(K, device=dev, dtype=torch.bfloat16)
+            out["fla_rms_norm_gated_x_sigmoid_ms"] = timed_steps(lambda: rms_norm_gated(q, k, w, None) * torch.sigmoid(k),
+                                                                 steps, warmup, None) / steps
+    except Exception as e:                                           # noqa: BLE001
+        out["fla_reason"] = f"{type(e).__name__}: {e}"[:200]
     return out
 
 
@@ -577,6 +644,8 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--library-context", action="store_true",
+                    help="also time the GPU library calls the reference makes for the same work (context, minutes)")
     ap.add_argument("--workload", default="all", choices=["all", "prefill_c2", "prefill_c4", "decode_c3", "kda_c5", "prefill_small", "decode_small", "kda_small", "gemm_small", "kda_layer_small"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extras", action="store_true",
@@ -633,6 +702,9 @@ def main():
         if want == "all" and rank == 0 and not args.no_extras:
             torch.cuda.empty_cache()
             extra["kda_layer"] = run_kda_layer(KDA_C5, args.steps, warm, peaks)
+        if args.library_context and rank == 0:
+            torch.cuda.empty_cache()
+            extra["library_context"] = run_library_context(args.steps, warm)
     if rank == 0:
         is_prefill = res["name"].startswith("prefill")
         line = {

@@ -122,3 +122,15 @@ def test_kda_layer_module_has_the_reference_parameters(golden_dir):
     m = B200KimiLinearSelfAttention(256, 2, 64, 128)
     got = sorted(f"{n}:{'x'.join(map(str, p.shape))}:{str(p.dtype).replace('torch.', '')}" for n, p in m.named_parameters())
     assert got == want
+
+
+def test_accounting_matches_the_oracle_formulas():
+    """The package's FLOP / byte counts (what bench.py's roofline figures use) equal the oracle's."""
+    from daisy_b200 import accounting as a
+    from oracle import kda
+    for B, T, H, D, W in ((8, 8192, 16, 128, 2048), (1, 65536, 16, 128, 8192), (2, 100, 3, 128, None), (1, 5, 1, 128, 9)):
+        assert a.prefill_flops(B, T, H, D, W) == swa.prefill_flops(B, T, H, D, W)
+    assert a.decode_bytes(64, 16, 128, 4095) == swa.decode_bytes(64, 16, 128, 4095)
+    assert a.kda_bytes_per_token_head() == kda.kda_bytes_per_token_head() == 1540
+    assert a.kda_flops_per_token_head() == kda.kda_flops_per_token_head()
+    assert a.FP32_EPS == swa.FP32_EPS
