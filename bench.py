@@ -522,6 +522,13 @@ def run_kda_layer(cfg, steps, warmup, peaks, lean=False):
     with torch.inference_mode():
         ms = timed_steps(lambda: layer(x, None, None), max(3, steps // 2), 2, None) / max(3, steps // 2)
     out["layer_forward_ms"] = ms
+    with torch.inference_mode():                                     # decode: prompt of 256 tokens, then single-token steps
+        layer.reset_history()
+        layer.prefill(x[:1, :256], None, None)
+        x1 = x[:1, 256:257].contiguous()
+        out["layer_step_us_batch1"] = timed_steps(lambda: layer.step(x1, None, None, 0, None, None, None), 50, 5, None) / 50 * 1e3
+        layer.capture_step(batch=1)
+        out["layer_step_graph_us_batch1"] = timed_steps(lambda: layer.step_graph(x1), 50, 5, None) / 50 * 1e3
     out["config"] = {"workload": f"kda layer: B={B} T={T} dim={C} H={H} K=V={K}, conv taps 4"}
     return out
 

@@ -171,14 +171,57 @@ class B200KimiLinearSelfAttention(torch.nn.Module):
         g = ops.kda_gate(g, self.A_log, self.head_k_dim, self.dt_bias, 1.0, 20.0)
         beta = torch.nn.functional.linear(x, self.b_proj.weight).sigmoid().float()
         rec = self._recurrent_state if use_cache else None
-        o, rec = chunk_kda(q=q, k=k, v=v, g=g, beta=beta, initial_state=rec, output_final_state=use_cache,
-                           use_qk_l2norm_in_kernel=True)
+        if rec is not None and T <= RECURRENT_MAX_T and rec.dtype == torch.float32 and rec.is_contiguous():
+            # decode step: the cached state is updated where it lies (no allocation: the step can be graph-captured)
+            o, rec = ops.kda_recurrent_fwd(q.contiguous(), k.contiguous(), v.contiguous(), g, beta, None, rec, True,
+                                           l2norm_qk=True, state_in_place=True)
+        else:
+            o, rec = chunk_kda(q=q, k=k, v=v, g=g, beta=beta, initial_state=rec, output_final_state=use_cache,
+                               use_qk_l2norm_in_kernel=True)
         gp = _linear(_linear(x, self.g_proj[0].weight), self.g_proj[1].weight)        # its bias is added in the norm kernel
         o = self.o_norm(o, gp.view(B, T, H, self.head_v_dim), self.g_proj[1].bias)
         if use_cache:
             self._recurrent_state, self._conv_state = rec, conv_state
             self._seen += T
         return _linear(o.view(B, T, self.value_dim), self.o_proj.weight)
+
+    # ------------------------------------------------------------------ CUDA-graph decode step
+    @torch.inference_mode()
+    def capture_step(self, batch: int = 1) -> None:
+        """Record one single-token ``step`` (no value embedding) into a CUDA graph.  Needs the states a ``prefill``
+        leaves; they are updated in place by the replayed kernels, input and output are fixed buffers.
+        ``step_graph(x)`` then costs one copy and one graph launch instead of ~17 launches issued from Python."""
+        if self._recurrent_state is None or (self.use_short_conv and self._conv_state is None):
+            raise RuntimeError("capture_step needs the cached states of a prefill")
+        dev = self._recurrent_state.device
+        self._gx = torch.zeros(batch, 1, self.hidden_size, device=dev, dtype=torch.bfloat16)
+        saved = [self._recurrent_state.clone()] + [c.clone() for c in (self._conv_state or ())]
+        seen = self._seen
+
+        def restore():
+            self._recurrent_state.copy_(saved[0])
+            for c, s_ in zip(self._conv_state or (), saved[1:]):
+                c.copy_(s_)
+            self._seen = seen
+
+        side = torch.cuda.Stream(device=dev)
+        side.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(side):                              # warm-up outside the capture (lazy initialisation)
+            self._forward_core(self._gx, None, None, None, use_cache=True)
+        torch.cuda.current_stream(dev).wait_stream(side)
+        restore()
+        self._graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self._graph):
+            self._gy = self._forward_core(self._gx, None, None, None, use_cache=True)
+        restore()
+
+    @torch.inference_mode()
+    def step_graph(self, x):
+        """``step`` through the captured graph: ``x [batch, 1, dim]`` -> ``y`` (a fixed buffer, overwritten by the next call)."""
+        self._gx.copy_(x)
+        self._graph.replay()
+        self._seen += 1
+        return self._gy
 
     def forward(self, x, ve=None, sa_lambdas=None, attn_mask=None, sliding_window_num_blocks=None, block_mask=None):
         assert block_mask is None, "block_mask not supported for KimiLinearSelfAttention"

@@ -227,3 +227,22 @@ def test_layer_prefill_then_steps():
     assert rel <= 2e-2, rel
     m.reset_history()
     assert m._recurrent_state is None and m._conv_state is None and m._seen == 0
+
+
+def test_layer_step_graph_matches_eager():
+    """The captured single-token step replays to the bits of the step launched kernel by kernel, states included."""
+    m = _layer(seed=9)
+    B, T0, n = 2, 70, 6
+    x = torch.randn(B, T0 + n, 256, device="cuda").bfloat16()
+    with torch.inference_mode():
+        m.prefill(x[:, :T0], None, None)
+        eager = [m.step(x[:, t:t + 1], None, None, t, None, None, None)[0].clone() for t in range(T0, T0 + n)]
+        rec_e, conv_e = m._recurrent_state.clone(), [c.clone() for c in m._conv_state]
+        m.reset_history()
+        m.prefill(x[:, :T0], None, None)
+        m.capture_step(batch=B)
+        graph = [m.step_graph(x[:, t:t + 1]).clone() for t in range(T0, T0 + n)]
+    for a, b in zip(eager, graph):
+        assert torch.equal(a, b)
+    assert torch.equal(m._recurrent_state, rec_e) and all(torch.equal(a, b) for a, b in zip(m._conv_state, conv_e))
+    assert m._seen == T0 + n
