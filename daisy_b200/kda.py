@@ -12,6 +12,10 @@ chunked pair.
 
 ``fused_kda_gate`` mirrors the gate call one line above it (attention_kimi.py:132; forward of
 ``_gate_impl``, models/daisy/fla_custom_ops.py:71-103).
+
+``B200ShortConvolution``, ``B200FusedRMSNormGated`` and ``B200KimiLinearSelfAttention`` mirror the rest of the
+layer (attention_kimi.py:41-62, 65-211): same constructors, parameter names and call protocol, on the kernels of
+``csrc/kda_layer.cu``; the layer adds ``capture_step`` / ``step_graph`` (one CUDA-graph replay per decoded token).
 """
 from __future__ import annotations
 
