@@ -7,9 +7,16 @@ Headline (the JSON line's metric/value): windowed causal prefill TFLOP/s on
 B=8, T=8192, 16 heads x 128, window 2048, bf16 -- one "step" = q/k/v preparation (RMS norm + RoPE)
 plus the windowed attention over one synthetic batch.  The same line carries the decode workload
 (batch 64, 16 x 128, ring capacity 32768, window 4096: tokens/s and HBM GB/s) and, when built, the KDA
-workload as sub-objects, each with its own roofline.  Multi-GPU (torchrun, one rank per GPU) is weak
-scaling: every rank runs the same per-GPU workload on its own shard of independent sequences, no
-collective on the data path; an NCCL all-gather reassembles the outputs after the timed region.
+workload and the long-context prefill (B=1, T=65536, window 8192) as sub-objects, each with its own roofline.
+
+Multi-GPU (torchrun, one rank per GPU), no collective on the data path anywhere:
+  * the headline prefill (a configuration quoted "on 1 B200") runs as replicas: every rank its own batch of 8
+    independent sequences ("scaling": "weak");
+  * the decode workload shards its batch of 64 over the ranks (64/32/16/8 rows per GPU), the long-context
+    prefill its 16 heads (16/8/4/2 per GPU), the KDA workload its 64 (batch, head) pairs (64/32/16/8 per GPU).
+    These are strong-scaling runs of ONE global problem: rank 0 also runs the whole problem alone, so each
+    sub-object carries T(1), T(N) and strong_efficiency = T(1) / (N * T(N)); an NCCL all-gather after the
+    timed region reassembles the shard outputs, which must equal that single-GPU result bit for bit.
 
 `--impl reference` times the CPU oracle (the fp32 restatement of the reference's PyTorch path) on a
 bounded sample of the same workload with all host threads.
@@ -38,9 +45,16 @@ KDA_C5 = dict(B=4, T=16384, H=16, K=128, V=128, chunk=64)
 PREFILL_SMALL = dict(B=2, T=8192, H=16, D=128, window=2048)
 DECODE_SMALL = dict(B=4, H=16, D=128, cap=32768, window=4096, steps=4)
 KDA_SMALL = dict(B=1, T=8192, H=16, K=128, V=128, chunk=64)
-# dram__bytes_read.sum + dram__bytes_write.sum of one launch from the ncu captures summarised under profiles/
-# (reduced workloads of the same kernels); traffic grows in proportion to the batch (independent sequences)
-NCU_TRAFFIC = {"prefill_per_batch_row": 1077.9e6 / 8, "decode_per_batch_row": 137.3e6 / 4}
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch, transcribed from the ncu captures summarised under
+# profiles/ (reduced workloads of the same kernels; traffic grows in proportion to the number of independent
+# sequences).  NOT measured by this run: each entry names the summary and the source revision it was captured at,
+# and goes stale when that kernel changes.
+NCU_TRAFFIC = {
+    "prefill_per_batch_row": {"bytes": 1077.9e6 / 8, "profile": "profiles/swa_prefill_kernel__prefill_small.md",
+                              "captured_at": "813cf57"},
+    "decode_per_batch_row": {"bytes": 137.3e6 / 4, "profile": "profiles/swa_decode_partial_kernel__decode_small.md",
+                             "captured_at": "c27d954"},
+}
 ROPE_BASE = 10000.0     # the benchmark configs name base 10000 (the module default is 1024, half-truncated)
 
 
@@ -51,8 +65,9 @@ def measured_peaks():
     if os.path.exists(p):
         with open(p) as f:
             d = json.load(f)
-        return dict(hbm_gbs=float(d["hbm_gbs"]), bf16_tflops=float(d["bf16_tflops"]), which="measured")
-    return dict(hbm_gbs=6650.0, bf16_tflops=1590.0, which="fallback")
+        return dict(hbm_gbs=float(d["hbm_gbs"]), bf16_tflops=float(d["bf16_tflops"]),
+                    bf16_tflops_sustained=float(d.get("bf16_tflops_sustained", d["bf16_tflops"])), which="measured")
+    return dict(hbm_gbs=6650.0, bf16_tflops=1590.0, bf16_tflops_sustained=1400.0, which="fallback")
 
 
 class ClockSampler:
@@ -165,19 +180,62 @@ def rope_full(D, T, device):
     return theta.cos().to(device), theta.sin().to(device)
 
 
-def timed_steps(step, steps, warmup, dist):
+L2_BYTES = 126 << 20
+_flush_buf = {}
+
+
+def l2_flush_buffer(dev):
+    """256 MiB scratch whose rewrite between timed steps evicts the 126 MB L2 (used when a step's own inputs are not
+    larger than L2, e.g. the per-GPU shards of the strong-scaling runs)."""
+    key = dev.index
+    if key not in _flush_buf:
+        _flush_buf[key] = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    return _flush_buf[key]
+
+
+def timed_steps(step, steps, warmup, dist, flush=None):
     """W warm-up steps, then K steps between barrier+synchronize on both sides; device time by CUDA
-    events on the launching stream; MAX over ranks."""
+    events on the launching stream; MAX over ranks.  With `flush` (a buffer larger than L2) every step is
+    bracketed by its own pair of events and the buffer is rewritten between steps, outside the events."""
     for _ in range(warmup):
         step()
     torch.cuda.synchronize()
     if dist is not None:
         dist.barrier()
     torch.cuda.synchronize()
+    if flush is None:
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            step()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1)
+    else:
+        ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
+        for a, b in ev:
+            flush.zero_()
+            a.record(); step(); b.record()
+        torch.cuda.synchronize()
+        ms = sum(a.elapsed_time(b) for a, b in ev)
+    if dist is not None:
+        dist.barrier()
+        t = torch.tensor([ms], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    return ms
+
+
+def timed_region(fn, dist):
+    """One call of `fn` (which enqueues a whole loop of steps) between barrier + synchronize on both sides;
+    device time by CUDA events on the launching stream; MAX over ranks."""
+    torch.cuda.synchronize()
+    if dist is not None:
+        dist.barrier()
+    torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
-    for _ in range(steps):
-        step()
+    fn()
     e1.record()
     torch.cuda.synchronize()
     if dist is not None:
@@ -190,38 +248,107 @@ def timed_steps(step, steps, warmup, dist):
     return ms
 
 
+def unit_shard(B: int, H: int, world: int, rank: int):
+    """Shard the B x H independent (batch, head) pairs of one problem over the ranks: whole batch rows while the
+    per-rank share is a multiple of H, else a head range of one batch row.  Returns (b_lo, b_hi, h_lo, h_hi)."""
+    n = B * H
+    if n % world == 0:
+        per = n // world
+        if per % H == 0:
+            return rank * per // H, (rank + 1) * per // H, 0, H
+        if H % per == 0:
+            u = rank * per
+            return u // H, u // H + 1, u % H, u % H + per
+    if B < world:
+        raise SystemExit(f"cannot shard {B} x {H} (batch, head) pairs evenly over {world} ranks")
+    lo, hi = shard_bounds(B, world, rank)
+    return lo, hi, 0, H
+
+
+def strong_summary(t1_ms, tn_ms, world):
+    """Strong scaling of one global problem: T(1) is rank 0 running the whole problem alone in this same run."""
+    return {"t1_ms": t1_ms, "tn_ms": tn_ms, "strong_efficiency": (t1_ms / (world * tn_ms)) if tn_ms else None}
+
+
 # ----------------------------------------------------------------------------- our arm: prefill
 
-def run_prefill(cfg, steps, warmup, dist, rank, world, peaks, name, lean=False):
+def prefill_inputs(cfg, seed, dev):
+    B, T, H, D = cfg["B"], cfg["T"], cfg["H"], cfg["D"]
+    g = torch.Generator(device=dev).manual_seed(seed)
+    return tuple(torch.randn(B, T, H, D, device=dev, generator=g).bfloat16() for _ in range(3))
+
+
+def sustained_prefill(step, flops, peaks, dev, seconds=2.0):
+    """The same step looped for >= `seconds` so that the power-capped clock settles: TFLOP/s against the measured
+    SUSTAINED cuBLAS rate, NVML clock samples (read only), and time x median SM MHz (a clock-normalised figure
+    that can be compared between runs).  Rank-local, no barrier."""
+    n = 50
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    sampler = ClockSampler(dev.index or 0)
+    torch.cuda.synchronize()
+    sampler.start()
+    t_begin, total_ms, total_steps, last = time.perf_counter(), 0.0, 0, None
+    while time.perf_counter() - t_begin < seconds:
+        e0.record()
+        for _ in range(n):
+            step()
+        e1.record()
+        torch.cuda.synchronize()
+        last = e0.elapsed_time(e1) / n
+        total_ms += last * n
+        total_steps += n
+    clocks = sampler.stop()
+    tf = flops / (last * 1e-3) / 1e12                        # the last block: the settled clock
+    mhz = clocks.get("sm_mhz")
+    return {"seconds": total_ms / 1e3, "steps": total_steps, "ms_per_step_settled": last, "tflops_settled": tf,
+            "ms_per_step_mean": total_ms / total_steps, "peak_sustained": peaks["bf16_tflops_sustained"],
+            "frac_of_sustained_peak": tf / peaks["bf16_tflops_sustained"], "clocks": clocks,
+            "ms_x_mhz": (last * mhz) if mhz else None,
+            "note": "TFLOP/s of the last 50-step block of a loop that ran this long; peak = cuBLAS bf16 looped for seconds"}
+
+
+def run_prefill(cfg, steps, warmup, dist, rank, world, peaks, name, lean=False, shard_heads=False, sustained=False):
+    """`shard_heads=False`: every rank runs the whole configuration on its own sequences (replicas, weak scaling).
+    `shard_heads=True`: ONE global problem, the heads split over the ranks (strided views of the global q, k, v);
+    rank 0 also runs all heads alone for T(1)."""
     from daisy_b200 import ops, _lib
     from daisy_b200 import accounting as acct
     B, T, H, D, W = cfg["B"], cfg["T"], cfg["H"], cfg["D"], cfg["window"]
     dev = torch.device("cuda", torch.cuda.current_device())
-    g = torch.Generator(device=dev).manual_seed(1234 + rank)
-    q, k, v = (torch.randn(B, T, H, D, device=dev, generator=g).bfloat16() for _ in range(3))
+    q, k, v = prefill_inputs(cfg, 1234 + (0 if shard_heads else rank), dev)
+    h_lo, h_hi = shard_bounds(H, world, rank) if shard_heads else (0, H)
+    if shard_heads and H % world != 0:
+        raise SystemExit(f"{name}: {H} heads do not split evenly over {world} ranks")
+    Hs = h_hi - h_lo
+    qs, ks, vs = q[:, :, h_lo:h_hi], k[:, :, h_lo:h_hi], v[:, :, h_lo:h_hi]
     cos, sin = rope_full(D, T, dev)
     L = _lib.lib()
     ws = torch.empty(L.daisy_b200_swa_prefill_workspace_bytes(B, T, H, D), dtype=torch.uint8, device=dev)
-    out = torch.empty(B, T, H, D, dtype=torch.bfloat16, device=dev)
-    k_out = torch.empty(B, T, H, D, dtype=torch.bfloat16, device=dev)
+    out = torch.empty(B, T, Hs, D, dtype=torch.bfloat16, device=dev)
+    k_out = torch.empty(B, T, Hs, D, dtype=torch.bfloat16, device=dev)
     v_out = torch.empty_like(k_out)
-    flops = acct.prefill_flops(B, T, H, D, W)
+    flops_global = acct.prefill_flops(B, T, H, D, W)
+    flops_rank = acct.prefill_flops(B, T, Hs, D, W)
+    total_flops = flops_global if shard_heads else world * flops_global
 
     def step():
-        ops.swa_prefill(q, k, v, cos, sin, W, eps=acct.FP32_EPS, workspace=ws, out=out, k_out=k_out, v_out=v_out)
+        ops.swa_prefill(qs, ks, vs, cos, sin, W, eps=acct.FP32_EPS, workspace=ws, out=out, k_out=k_out, v_out=v_out)
 
+    in_bytes_dev = 3 * qs.numel() * 2
+    flush = l2_flush_buffer(dev) if (in_bytes_dev < 2 * L2_BYTES and not lean) else None
     sampler = ClockSampler(dev.index or 0)
     sampler.start()
-    ms = timed_steps(step, steps, warmup, dist)
+    ms = timed_steps(step, steps, warmup, dist, flush)
     clocks = sampler.stop()
     ops.check_device_status(dev)
+    per = ms / steps
 
     if lean:                                                 # profiler capture: the timed loop only
-        return {"name": name, "ms_per_step": ms / steps, "tflops": world * flops / (ms / steps * 1e-3) / 1e12,
+        return {"name": name, "ms_per_step": per, "tflops": total_flops / (per * 1e-3) / 1e12,
                 "clocks": clocks, "launches_per_step": 2, "roofline": None, "e2e": None,
                 "config": {"workload": f"{name}: B={B} T={T} H={H} D={D} window={W} (profiler capture case)"}}
     # dominant kernel alone (attention on prepared tensors), CUDA events around each launch
-    qp, kp, vp = ops.qkv_prep(q, k, v, cos, sin, acct.FP32_EPS)
+    qp, kp, vp = ops.qkv_prep(qs, ks, vs, cos, sin, acct.FP32_EPS)
     ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
     out_k = torch.empty_like(out)
     for _ in range(warmup):
@@ -237,9 +364,9 @@ def run_prefill(cfg, steps, warmup, dist, rank, world, peaks, name, lean=False):
     # end to end through the public host-buffer call: pinned host q,k,v in, pinned host result out, every step;
     # batch rows stream through copy-in / kernels / copy-out on three CUDA streams
     from daisy_b200.host_api import HostPrefill
-    hq, hk, hv = (x.cpu().pin_memory() for x in (q, k, v))
+    hq, hk, hv = (x.cpu().pin_memory() for x in (qs, ks, vs))
     hout = torch.empty(out.shape, dtype=out.dtype).pin_memory()
-    host_call = HostPrefill(T, H, D, device=dev, rows_per_chunk=1)
+    host_call = HostPrefill(T, Hs, D, device=dev, rows_per_chunk=1)
 
     def e2e_step():
         host_call(hq, hk, hv, cos, sin, W, hout, eps=acct.FP32_EPS)
@@ -248,101 +375,197 @@ def run_prefill(cfg, steps, warmup, dist, rank, world, peaks, name, lean=False):
     e2e_ms = timed_steps(e2e_step, e2e_steps, 1, dist)
     torch.cuda.synchronize()
     e2e_same = bool(torch.equal(hout, out.cpu()))             # same inputs -> the host path must reproduce `out`
-    in_bytes = 3 * q.numel() * 2
+    in_bytes = 3 * qs.numel() * 2
     out_bytes = out.numel() * 2
+    del host_call, hq, hk, hv, hout
 
+    strong = None
     if dist is not None:                                      # reassemble outputs (verification only)
         gathered = [torch.empty_like(out) for _ in range(world)]
         dist.all_gather(gathered, out)
-        assert all(torch.isfinite(x[:, :64].float()).all() for x in gathered)
+        if shard_heads and rank == 0:
+            full = torch.cat(gathered, dim=2)
+        else:
+            assert all(torch.isfinite(x[:, :64].float()).all() for x in gathered)
         del gathered
+    if shard_heads:
+        t1 = per
+        same = None
+        if world > 1 and rank == 0:                           # the whole problem on one GPU: T(1) and the reference bits
+            out1 = torch.empty(B, T, H, D, dtype=torch.bfloat16, device=dev)
+            k1, v1 = torch.empty_like(out1), torch.empty_like(out1)
+
+            def step1():
+                ops.swa_prefill(q, k, v, cos, sin, W, eps=acct.FP32_EPS, workspace=ws, out=out1, k_out=k1, v_out=v1)
+
+            t1 = timed_steps(step1, steps, warmup, None, flush) / steps
+            same = bool(torch.equal(full, out1))
+            del out1, k1, v1, full
+        strong = strong_summary(t1, per, world)
+        strong["gathered_equals_single_gpu_result"] = same
+    sus = sustained_prefill(step, flops_rank, peaks, dev) if sustained else None
     finite = bool(torch.isfinite(out.float()).all())
-    ach = flops / (k_ms * 1e-3) / 1e12
-    return {
-        "name": name, "ms_per_step": ms / steps, "tflops": world * flops / (ms / steps * 1e-3) / 1e12,
-        "clocks": clocks, "finite": finite, "launches_per_step": 2,
+    ach = flops_rank / (k_ms * 1e-3) / 1e12
+    traffic = None
+    if (T, W) == (8192, 2048) and Hs == 16:
+        traffic = NCU_TRAFFIC["prefill_per_batch_row"]["bytes"] * B
+    res = {
+        "name": name, "ms_per_step": per, "tflops": total_flops / (per * 1e-3) / 1e12,
+        "clocks": clocks, "finite": finite, "launches_per_step": 2, "steps": steps,
         "roofline": {"bound": "tensor", "achieved": ach, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
-                     "frac": ach / peaks["bf16_tflops"], "traffic": (NCU_TRAFFIC["prefill_per_batch_row"] * B if (T, W) == (8192, 2048) else None),
-                     "traffic_unit": "bytes per launch (ncu dram read+write of one full-size C2 launch, per batch row x batch)",
-                     "kernel": "swa_prefill_kernel",
-                     "kernel_ms": k_ms, "kernel_output_equals_step": kernel_same, "peak_source": peaks["which"] + " (burst cuBLAS bf16)"},
-        "e2e": {"value": world * flops / (e2e_ms / e2e_steps * 1e-3) / 1e12, "unit": "TFLOP/s",
+                     "frac": ach / peaks["bf16_tflops"], "traffic": traffic,
+                     "traffic_unit": "bytes per launch (ncu dram read+write of one full-size launch; transcribed, see traffic_source)",
+                     "traffic_source": NCU_TRAFFIC["prefill_per_batch_row"] if traffic else None,
+                     "kernel": "swa_prefill_kernel", "per_rank_heads": Hs,
+                     "kernel_ms": k_ms, "kernel_output_equals_step": kernel_same, "peak_source": peaks["which"] + " (burst cuBLAS bf16)",
+                     "step_frac_of_burst_peak": flops_rank / (per * 1e-3) / 1e12 / peaks["bf16_tflops"]},
+        "e2e": {"value": total_flops / (e2e_ms / e2e_steps * 1e-3) / 1e12, "unit": "TFLOP/s",
                 "h2d_bytes_per_step": in_bytes, "d2h_bytes_per_step": out_bytes,
                 "matches_device_result": e2e_same, "api": "daisy_b200.host_api.HostPrefill"},
-        "config": {"workload": f"{name}: B={B} T={T} H={H} D={D} window={W} causal, RMS-norm q,k,v + RoPE base "
-                               f"{int(ROPE_BASE)} fused in the step", "per_gpu_batch": B, "global_batch": B * world,
-                   "parallelism": f"dp{world} (independent sequences per GPU, no collective)",
-                   "l2": "inputs (768 MiB q,k,v) exceed L2"},
+        "config": {"workload": f"{name}: B={B} T={T} H={H} D={D} window={W} causal; one step = two launches: RMS-norm q,k,v + RoPE "
+                               f"base {int(ROPE_BASE)} (qkv_prep_kernel), then windowed attention (swa_prefill_kernel)",
+                   "per_gpu_batch": B, "per_gpu_heads": Hs, "global_batch": B if shard_heads else B * world,
+                   "parallelism": (f"heads sharded {H} -> {Hs} per GPU over {world} GPU(s), one global problem, no collective"
+                                   if shard_heads else
+                                   f"dp{world} replicas: this configuration is quoted on 1 GPU, every rank runs it whole on its own "
+                                   "sequences, no collective"),
+                   "l2": (f"inputs ({in_bytes_dev >> 20} MiB q,k,v per GPU) exceed L2" if flush is None else
+                          f"inputs are {in_bytes_dev >> 20} MiB per GPU: L2 flushed between steps (256 MiB rewrite outside the events)")},
     }
+    if strong is not None:
+        res["scaling"] = "strong"
+        res["strong"] = strong
+    if sus is not None:
+        res["sustained"] = sus
+    return res
 
 
 # ----------------------------------------------------------------------------- our arm: decode
 
+class DecodeCase:
+    """The decode workload for a set of GLOBAL batch rows (a rank's shard, or all rows): ring and per-step inputs are
+    seeded per global row, so a shard holds exactly the rows of the global problem it names."""
+
+    def __init__(self, cfg, rows, nq, dev):
+        from daisy_b200 import ops, _lib
+        from daisy_b200 import accounting as acct
+        self.ops, self.acct = ops, acct
+        self.B = B = len(rows)
+        self.H, self.D, self.cap, self.W = H, D, cap, W = cfg["H"], cfg["D"], cfg["cap"], cfg["window"]
+        self.kc = torch.empty(B, H, cap, D, dtype=torch.bfloat16, device=dev)
+        self.vc = torch.empty_like(self.kc)
+        self.qs, self.ks, self.vs = (torch.empty(nq, B, 1, H, D, dtype=torch.bfloat16, device=dev) for _ in range(3))
+        for i, b in enumerate(rows):
+            g = torch.Generator(device=dev).manual_seed(4321 + 7919 * int(b))
+            self.kc[i] = torch.randn(H, cap, D, device=dev, generator=g).bfloat16()
+            self.vc[i] = torch.randn(H, cap, D, device=dev, generator=g).bfloat16()
+            for x in (self.qs, self.ks, self.vs):
+                x[:, i] = torch.randn(nq, 1, H, D, device=dev, generator=g).bfloat16()
+        self.cos, self.sin = rope_full(D, cap + nq + 128, dev)
+        self.splits = ops.decode_splits(B, H, W - 1)
+        self.ws = torch.empty(_lib.lib().daisy_b200_swa_decode_workspace_bytes(B, H, D, self.splits), dtype=torch.uint8, device=dev)
+        self.out = torch.empty(nq, B, 1, H, D, dtype=torch.bfloat16, device=dev)
+        self.bytes_per_step = acct.decode_bytes(B, H, D, W - 1)
+
+    def step(self, i):
+        """Input row i at position cap + i: the ring is full, so every step wraps and overwrites the oldest slot."""
+        t = self.cap + i
+        self.ops.swa_decode_step(self.qs[i], self.ks[i], self.vs[i], self.kc, self.vc, t, self.cap, self.W, self.cos[t], self.sin[t],
+                                 eps=self.acct.FP32_EPS, write_ring=True, splits=self.splits, workspace=self.ws, out=self.out[i],
+                                 return_new_kv=False)
+
+    def time(self, warmup, nsteps, dist):
+        """(ms per step launched from Python, ms per step as ONE CUDA graph of the same nsteps launches pairs).  The graph
+        replays the same positions, so it rewrites the same ring slots with the same rows and must reproduce the
+        outputs of the plain loop bit for bit."""
+        for i in range(warmup):
+            self.step(i)
+        plain = timed_region(lambda: [self.step(warmup + i) for i in range(nsteps)], dist) / nsteps
+        ref = self.out[warmup:warmup + nsteps].clone()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            for i in range(nsteps):
+                self.step(warmup + i)
+        graph.replay()                                              # warm-up replay
+        self.out[warmup:warmup + nsteps].zero_()
+        graphed = timed_region(graph.replay, dist) / nsteps
+        same = bool(torch.equal(self.out[warmup:warmup + nsteps], ref))
+        del graph
+        return plain, graphed, same
+
+
 def run_decode(cfg, warmup, dist, rank, world, peaks, lean=False, extras=True):
-    from daisy_b200 import ops, _lib
-    from daisy_b200 import accounting as acct
+    """The batch is sharded over the ranks (one global problem, strong scaling); rank 0 also runs the whole batch
+    alone for T(1) when there is more than one rank."""
+    from daisy_b200 import ops
     B, H, D, cap, W, nsteps = cfg["B"], cfg["H"], cfg["D"], cfg["cap"], cfg["window"], cfg["steps"]
     dev = torch.device("cuda", torch.cuda.current_device())
-    g = torch.Generator(device=dev).manual_seed(4321 + rank)
-    kc = torch.empty(B, H, cap, D, dtype=torch.bfloat16, device=dev)
-    vc = torch.empty_like(kc)
-    for b in range(B):
-        kc[b] = torch.randn(H, cap, D, device=dev, generator=g).bfloat16()
-        vc[b] = torch.randn(H, cap, D, device=dev, generator=g).bfloat16()
+    if B % world != 0:
+        raise SystemExit(f"decode: batch {B} does not split evenly over {world} ranks")
+    lo, hi = shard_bounds(B, world, rank)
     nq = nsteps + warmup
-    qs, ks, vs = (torch.randn(nq, B, 1, H, D, device=dev, generator=g).bfloat16() for _ in range(3))
-    cos, sin = rope_full(D, cap + nq + 128, dev)
-    L = _lib.lib()
-    splits = ops.decode_splits(B, H, W - 1)
-    ws = torch.empty(L.daisy_b200_swa_decode_workspace_bytes(B, H, D, splits), dtype=torch.uint8, device=dev)
-    out = torch.empty(nq, B, 1, H, D, dtype=torch.bfloat16, device=dev)
-    state = {"t": cap, "i": 0}                       # ring already full: every step wraps
-
-    def step():
-        t, i = state["t"], state["i"]
-        ops.swa_decode_step(qs[i], ks[i], vs[i], kc, vc, t, cap, W, cos[t], sin[t], eps=acct.FP32_EPS,
-                            write_ring=True, splits=splits, workspace=ws, out=out[i], return_new_kv=False)
-        state["t"], state["i"] = t + 1, i + 1
-
-    ms = timed_steps(step, nsteps, warmup, dist)
+    ops.status_word(dev)                                     # allocated before any graph capture
+    case = DecodeCase(cfg, range(lo, hi), nq, dev)
+    Bs = case.B
+    plain, graphed, graph_same = case.time(warmup, nsteps, dist)
     ops.check_device_status(dev)
-    per = ms / nsteps
-    byts = acct.decode_bytes(B, H, D, W - 1)
-    gbs = byts / (per * 1e-3) / 1e9
+    per = min(plain, graphed)
+    gbs = case.bytes_per_step / (per * 1e-3) / 1e9
     if lean:
-        return {"name": "decode", "ms_per_step": per, "tokens_per_s": world * B / (per * 1e-3), "hbm_gbs": gbs,
+        return {"name": "decode", "ms_per_step": plain, "tokens_per_s": B / (plain * 1e-3), "hbm_gbs": case.bytes_per_step / (plain * 1e-3) / 1e9,
                 "steps": nsteps, "launches_per_step": 2, "roofline": None, "e2e": None,
                 "config": {"workload": f"decode: batch {B} x {H} x {D}, capacity {cap}, window {W} (profiler capture case)"}}
     # e2e: the step's host inputs (new q,k,v rows) in, the output row back, cache resident
-    hq, hk, hv = (x[:8].cpu().pin_memory() for x in (qs, ks, vs))
-    hout = torch.empty(out[0].shape, dtype=out.dtype).pin_memory()
-    state["i"] = 0
+    hq, hk, hv = (x[:8].cpu().pin_memory() for x in (case.qs, case.ks, case.vs))
+    hout = torch.empty(case.out[0].shape, dtype=case.out.dtype).pin_memory()
+    state = {"i": 0}
 
     def e2e_step():
         i = state["i"] % 8
-        qs[i].copy_(hq[i], non_blocking=True); ks[i].copy_(hk[i], non_blocking=True); vs[i].copy_(hv[i], non_blocking=True)
-        state["i"] = i
-        step()
-        hout.copy_(out[i], non_blocking=True)
+        case.qs[i].copy_(hq[i], non_blocking=True); case.ks[i].copy_(hk[i], non_blocking=True); case.vs[i].copy_(hv[i], non_blocking=True)
+        case.step(i)
+        hout.copy_(case.out[i], non_blocking=True)
         torch.cuda.current_stream().synchronize()           # the token must reach the host before the next one
+        state["i"] = i + 1
 
     e2e_ms = timed_steps(e2e_step, 64, 2, dist)
+    first = case.out[warmup].clone()                         # first timed step's output [Bs,1,H,D]
+    finite = bool(torch.isfinite(case.out[warmup:].float()).all())
+    splits = case.splits
+    del case
+    torch.cuda.empty_cache()
+    strong = strong_summary(per, per, 1)
+    strong.update({"t1_plain_ms": plain, "t1_graph_ms": graphed})
     if dist is not None:
-        gathered = [torch.empty_like(out[0]) for _ in range(world)]
-        dist.all_gather(gathered, out[0])
-    del kc, vc
+        gathered = [torch.empty_like(first) for _ in range(world)]
+        dist.all_gather(gathered, first)
+        same = None
+        if rank == 0:
+            full = DecodeCase(cfg, range(B), nq, dev)
+            p1, g1, _ = full.time(warmup, nsteps, None)
+            same = bool(torch.equal(torch.cat(gathered, 0), full.out[warmup]))
+            strong = strong_summary(min(p1, g1), per, world)
+            strong.update({"t1_plain_ms": p1, "t1_graph_ms": g1})
+            del full
+            torch.cuda.empty_cache()
+        strong["gathered_equals_single_gpu_result"] = same
     gen = generator_step_latency(H, D, W) if (rank == 0 and extras) else None
-    return {"name": "decode_c3", "generator_step": gen, "ms_per_step": per, "tokens_per_s": world * B / (per * 1e-3), "hbm_gbs": world * gbs,
-            "splits": splits, "steps": nsteps, "launches_per_step": 2, "finite": bool(torch.isfinite(out.float()).all()),
+    traffic = NCU_TRAFFIC["decode_per_batch_row"]
+    return {"name": "decode_c3", "generator_step": gen, "ms_per_step": per, "ms_per_step_plain_launches": plain,
+            "ms_per_step_cuda_graph": graphed, "graph_output_equals_plain": graph_same,
+            "tokens_per_s": B / (per * 1e-3), "hbm_gbs": world * gbs, "scaling": "strong", "strong": strong,
+            "splits": splits, "steps": nsteps, "launches_per_step": 2, "finite": finite,
             "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                         "frac": gbs / peaks["hbm_gbs"], "traffic": NCU_TRAFFIC["decode_per_batch_row"] * B,
-                         "traffic_unit": "bytes per launch (ncu dram read+write on batch 4, scaled by batch)",
-                         "kernel": "swa_decode_partial_kernel",
+                         "frac": gbs / peaks["hbm_gbs"], "traffic": traffic["bytes"] * Bs,
+                         "traffic_unit": "bytes per launch (ncu dram read+write on batch 4, scaled by the per-GPU batch; transcribed, see traffic_source)",
+                         "traffic_source": traffic, "kernel": "swa_decode_partial_kernel", "per_rank_batch": Bs,
                          "peak_source": peaks["which"] + " (copy bandwidth)", "frac_of_8TBs": gbs / 8000.0},
-            "e2e": {"value": world * B / (e2e_ms / 64 * 1e-3), "unit": "tokens/s",
-                    "h2d_bytes_per_step": 3 * B * H * D * 2, "d2h_bytes_per_step": B * H * D * 2},
-            "config": {"workload": f"decode_c3: batch {B} x {H} heads x {D}, ring capacity {cap}, window {W}, "
-                                   f"{nsteps} steps from t={cap} (ring wraps every step)", "per_gpu_batch": B}}
+            "e2e": {"value": B / (e2e_ms / 64 * 1e-3), "unit": "tokens/s",
+                    "h2d_bytes_per_step": 3 * Bs * H * D * 2, "d2h_bytes_per_step": Bs * H * D * 2},
+            "config": {"workload": f"decode_c3: global batch {B} x {H} heads x {D}, ring capacity {cap}, window {W}, "
+                                   f"{nsteps} steps from t={cap} (ring wraps every step)", "per_gpu_batch": Bs, "global_batch": B,
+                       "parallelism": f"batch sharded {B} -> {Bs} rows per GPU over {world} GPU(s), no collective",
+                       "timing": "the faster of: the loop launched step by step from Python, the same loop as one CUDA-graph replay"}}
 
 
 def generator_step_latency(H, D, W, layers=4, batch=1, steps=200):
@@ -419,44 +642,67 @@ def run_projection(B, T, H, D, steps, warmup, lean=False):
     a, b = ours(), lib()
     res["max_abs_diff_vs_library_path"] = max(float((a[i].float() - b[i].float()).abs().max()) for i in range(3))
     del a, b, y
-    # the whole module forward (projection -> attention -> projection) both ways
+    # the whole module forward (projection -> attention -> projection): the module's own path (hand-written kernels
+    # only) against the same forward composed from torch's GEMMs and the separate norm / RoPE pass
     from daisy_b200 import B200CausalSelfAttention, WindowMask
     os.environ["DISABLE_O_ZERO_INIT"] = "1"
     mod = B200CausalSelfAttention(dim, H, D, max_seq_len=T).cuda().eval()
     mask = WindowMask(PREFILL_C2["window"])
+
+    def library_forward():
+        q_, k_, v_ = F.linear(x, mod.qkvo_w[:3].flatten(end_dim=1)).view(B, T, 3 * H, D).chunk(3, dim=-2)
+        y_, _, _ = ops.swa_prefill(q_, k_, v_, mod.rotary.cos, mod.rotary.sin, mask.window, mod.attn_scale, mod.norm_eps)
+        return F.linear(y_.view(B, T, dim), mod.qkvo_w[3])
+
     with torch.inference_mode():
-        fwd = {}
-        for name, flag in (("native_ms", True), ("library_gemm_ms", False)):
-            mod.native_gemm = flag
-            fwd[name] = timed_steps(lambda: mod(x, None, attn_mask=mask), steps, warmup, None) / steps
+        fwd = {"native_ms": timed_steps(lambda: mod(x, None, attn_mask=mask), steps, warmup, None) / steps,
+               "library_gemm_ms": timed_steps(library_forward, steps, warmup, None) / steps}
     res["module_forward"] = fwd
     return res
 
 
 # ----------------------------------------------------------------------------- our arm: KDA
 
+def kda_inputs(cfg, b_lo, b_hi, h_lo, h_hi, dev):
+    """The (batch rows, head range) shard of the global KDA problem, contiguous; every global batch row has its own seed."""
+    T, H, K = cfg["T"], cfg["H"], cfg["K"]
+    qs, ks, vs, gs, bs = [], [], [], [], []
+    for b in range(b_lo, b_hi):
+        g_ = torch.Generator(device=dev).manual_seed(99 + 7919 * b)
+        q, k, v = (torch.randn(1, T, H, K, device=dev, generator=g_).bfloat16() for _ in range(3))
+        g = torch.nn.functional.logsigmoid(torch.randn(1, T, H, K, device=dev, generator=g_))
+        beta = torch.sigmoid(torch.randn(1, T, H, device=dev, generator=g_))
+        for lst, x in ((qs, q), (ks, k), (vs, v), (gs, g), (bs, beta)):
+            lst.append(x[:, :, h_lo:h_hi])
+    return tuple(torch.cat(l, 0).contiguous() for l in (qs, ks, vs, gs, bs))
+
+
 def run_kda(cfg, steps, warmup, dist, rank, world, peaks, lean=False):
+    """The B x H (batch, head) pairs are sharded over the ranks (one global problem, strong scaling); rank 0 also runs
+    all of them alone for T(1) when there is more than one rank."""
     from daisy_b200 import ops
     from daisy_b200 import accounting as acct
     B, T, H, K = cfg["B"], cfg["T"], cfg["H"], cfg["K"]
     dev = torch.device("cuda", torch.cuda.current_device())
-    g_ = torch.Generator(device=dev).manual_seed(99 + rank)
-    q, k, v = (torch.randn(B, T, H, K, device=dev, generator=g_).bfloat16() for _ in range(3))
-    g = torch.nn.functional.logsigmoid(torch.randn(B, T, H, K, device=dev, generator=g_))
-    beta = torch.sigmoid(torch.randn(B, T, H, device=dev, generator=g_))
+    b_lo, b_hi, h_lo, h_hi = unit_shard(B, H, world, rank)
+    q, k, v, g, beta = kda_inputs(cfg, b_lo, b_hi, h_lo, h_hi, dev)
+    Bs, Hs = b_hi - b_lo, h_hi - h_lo
     res = {}
 
     def step():
         res["o"], _ = ops.kda_chunk_fwd(q, k, v, g, beta, None, None, False, l2norm_qk=True)
 
-    ms = timed_steps(step, steps, warmup, dist)
+    in_bytes = sum(x.numel() * x.element_size() for x in (q, k, v, g, beta))
+    flush = l2_flush_buffer(dev) if (in_bytes < 2 * L2_BYTES and not lean) else None
+    ms = timed_steps(step, steps, warmup, dist, flush)
     ops.check_device_status(dev)
     per = ms / steps
-    th = B * T * H
-    byts = th * acct.kda_bytes_per_token_head(K, K)
+    th = B * T * H                                           # global token-heads
+    th_rank = Bs * T * Hs
+    byts = th_rank * acct.kda_bytes_per_token_head(K, K)
     gbs = byts / (per * 1e-3) / 1e9
     if lean:
-        return {"name": "kda", "ms_per_step": per, "value": world * th / (per * 1e-3), "unit": "token-heads/s", "steps": steps,
+        return {"name": "kda", "ms_per_step": per, "value": th / (per * 1e-3), "unit": "token-heads/s", "steps": steps,
                 "launches_per_step": 2, "roofline": None, "e2e": None,
                 "config": {"workload": f"kda: B={B} T={T} H={H} K=V={K} (profiler capture case)"}}
     # e2e: host tensors in, output back
@@ -470,21 +716,47 @@ def run_kda(cfg, steps, warmup, dist, rank, world, peaks, lean=False):
         ho.copy_(res["o"], non_blocking=True)
 
     e2e_ms = timed_steps(e2e_step, 3, 1, dist) / 3
+    del hq, hk, hv, hg, hb, ho
+    strong = strong_summary(per, per, 1)
     if dist is not None:
-        gathered = [torch.empty_like(res["o"]) for _ in range(world)]
-        dist.all_gather(gathered, res["o"])
+        o = res["o"]
+        gathered = [torch.empty_like(o) for _ in range(world)]
+        dist.all_gather(gathered, o)
+        same = None
+        if rank == 0:
+            full_in = kda_inputs(cfg, 0, B, 0, H, dev)
+            full = {}
+
+            def step1():
+                full["o"], _ = ops.kda_chunk_fwd(*full_in, None, None, False, l2norm_qk=True)
+
+            t1 = timed_steps(step1, steps, warmup, None) / steps
+            same = True
+            for r, part in enumerate(gathered):
+                bl, bh_, hl, hh = unit_shard(B, H, world, r)
+                same = same and bool(torch.equal(part, full["o"][bl:bh_, :, hl:hh]))
+            strong = strong_summary(t1, per, world)
+            del full_in, full
+        strong["gathered_equals_single_gpu_result"] = same
         del gathered
-    return {"name": "kda_c5", "ms_per_step": per, "value": world * th / (per * 1e-3), "unit": "token-heads/s",
-            "hbm_gbs": world * gbs, "tflops": world * th * acct.kda_flops_per_token_head(K, K) / (per * 1e-3) / 1e12,
+    kt = NCU_TRAFFIC.get("kda_per_token_head")
+    return {"name": "kda_c5", "ms_per_step": per, "value": th / (per * 1e-3), "unit": "token-heads/s",
+            "hbm_gbs": world * gbs, "tflops": th * acct.kda_flops_per_token_head(K, K) / (per * 1e-3) / 1e12,
+            "scaling": "strong", "strong": strong,
             "steps": steps, "launches_per_step": 2, "finite": bool(torch.isfinite(res["o"].float()).all()),
             "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                         "frac": gbs / peaks["hbm_gbs"], "traffic": None,
+                         "frac": gbs / peaks["hbm_gbs"], "traffic": (kt["bytes"] * th_rank) if kt else None,
+                         "traffic_unit": "bytes per call, both kernels (ncu dram read+write on a reduced case, scaled by token-heads; transcribed, see traffic_source)",
+                         "traffic_source": kt, "per_rank_batch_heads": Bs * Hs,
                          "kernel": "kda_intra_kernel + kda_state_kernel (one call)",
                          "peak_source": peaks["which"] + " (copy bandwidth)"},
-            "e2e": {"value": world * th / (e2e_ms * 1e-3), "unit": "token-heads/s",
-                    "h2d_bytes_per_step": th * (3 * K * 2 + K * 4 + 4), "d2h_bytes_per_step": th * K * 2},
-            "config": {"workload": f"kda_c5: B={B} T={T} H={H} K=V={K} chunk=64, L2-normalised q,k, "
-                                   "g=logsigmoid(N(0,1)), beta=sigmoid(N(0,1)), bf16 I/O, fp32 state", "per_gpu_batch": B}}
+            "e2e": {"value": th / (e2e_ms * 1e-3), "unit": "token-heads/s",
+                    "h2d_bytes_per_step": th_rank * (3 * K * 2 + K * 4 + 4), "d2h_bytes_per_step": th_rank * K * 2},
+            "config": {"workload": f"kda_c5: global B={B} T={T} H={H} K=V={K} chunk=64, L2-normalised q,k, "
+                                   "g=logsigmoid(N(0,1)), beta=sigmoid(N(0,1)), bf16 I/O, fp32 state",
+                       "per_gpu_batch_heads": Bs * Hs, "per_gpu_shape": f"B={Bs} H={Hs}",
+                       "parallelism": f"(batch, head) pairs sharded {B * H} -> {Bs * Hs} per GPU over {world} GPU(s), no collective",
+                       "l2": ("inputs exceed L2" if flush is None else "L2 flushed between steps (256 MiB rewrite outside the events)")}}
 
 
 def run_kda_layer(cfg, steps, warmup, peaks, lean=False):
@@ -619,16 +891,26 @@ def cpu_prefill_sample(cfg, threads=None):
             "sample": f"1 of {cfg['B']} batch rows, T={Tcap}, all {H} heads, fp32 oracle, {dt:.1f} s"}, dt, fl
 
 
+def host_threads() -> int:
+    """Every core this process may run on.  torchrun exports OMP_NUM_THREADS=1 to its workers, which would make the
+    CPU arm a single-thread run: the CPU legs set the thread count themselves."""
+    try:
+        return max(1, len(os.sched_getaffinity(0)))
+    except AttributeError:
+        return max(1, os.cpu_count() or 1)
+
+
 def run_reference(args, world, rank):
     if rank != 0:
         return
     cfg = PREFILL_C2
+    threads = host_threads()
     vals, fl = [], None
     for _ in range(args.warmup if args.warmup < 2 else 1):
-        cpu_prefill_sample(cfg)
+        cpu_prefill_sample(cfg, threads)
     n = max(1, min(args.steps, 3))
     for _ in range(n):
-        cb, dt, fl = cpu_prefill_sample(cfg)
+        cb, dt, fl = cpu_prefill_sample(cfg, threads)
         vals.append(dt)
     dt = sum(vals) / len(vals)
     val = fl / dt / 1e12
@@ -656,7 +938,8 @@ def main():
     ap.add_argument("--workload", default="all", choices=["all", "prefill_c2", "prefill_c4", "decode_c3", "kda_c5", "prefill_small", "decode_small", "kda_small", "gemm_small", "kda_layer_small"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extras", action="store_true",
-                    help="skip the measurements beside the three workloads (generator-step latency): launch-list captures")
+                    help="skip the measurements beside the workloads (projection GEMMs, generator-step latency, KDA layer "
+                         "passes, the sustained loop): launch-list captures")
     args = ap.parse_args()
     world, rank, local = dist_env()
     if args.impl == "reference":
@@ -675,7 +958,8 @@ def main():
     res, extra = None, {}
     want = args.workload
     if want in ("all", "prefill_c2"):
-        res = run_prefill(PREFILL_C2, args.steps, warm, dist, rank, world, peaks, "prefill_c2")
+        res = run_prefill(PREFILL_C2, args.steps, warm, dist, rank, world, peaks, "prefill_c2",
+                          sustained=(want == "all" and not args.no_extras))
     if want == "prefill_small":
         res = run_prefill(PREFILL_SMALL, args.steps, args.warmup, dist, rank, world, peaks, "prefill_small", lean=True)
     if want == "gemm_small":
@@ -686,8 +970,13 @@ def main():
         res = run_kda(KDA_SMALL, args.steps, args.warmup, dist, rank, world, peaks, lean=True)
     if want == "kda_layer_small":
         res = run_kda_layer(dict(KDA_SMALL, B=4), args.steps, args.warmup, peaks, lean=True)
-    if want == "prefill_c4":
-        res = run_prefill(PREFILL_C4, max(2, args.steps // 4), warm, dist, rank, world, peaks, "prefill_c4")
+    if want in ("all", "prefill_c4"):
+        torch.cuda.empty_cache()
+        c4 = run_prefill(PREFILL_C4, max(3, args.steps // 4), warm, dist, rank, world, peaks, "prefill_c4", shard_heads=True)
+        if res is None:
+            res = c4
+        else:
+            extra["prefill_c4"] = c4
     if want == "all" and rank == 0 and not args.no_extras:
         torch.cuda.empty_cache()
         extra["projection"] = run_projection(PREFILL_C2["B"], PREFILL_C2["T"], PREFILL_C2["H"], PREFILL_C2["D"],
@@ -714,22 +1003,24 @@ def main():
             extra["library_context"] = run_library_context(args.steps, warm)
     if rank == 0:
         is_prefill = res["name"].startswith("prefill")
+        nsteps = res.get("steps", args.steps)
         line = {
             "metric": "windowed prefill TFLOP/s" if is_prefill else res["name"],
             "value": res["tflops"] if is_prefill else res.get("tokens_per_s", res.get("value")),
             "unit": "TFLOP/s" if is_prefill else res.get("unit", "tokens/s"),
-            "n_gpus": world, "steps": args.steps if is_prefill else res.get("steps", args.steps), "warmup": warm,
-            "ms_per_step": res["ms_per_step"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "n_gpus": world, "steps": nsteps, "warmup": warm,
+            "ms_per_step": res["ms_per_step"], "higher_is_better": True, "scaling": res.get("scaling", "weak"), "vs_baseline": None,
             "dtype": "bf16", "data": "synthetic", "config": res["config"], "clocks": res.get("clocks"),
             "roofline": res["roofline"], "e2e": res["e2e"],
-            "gpu_launches": res["launches_per_step"] * (args.steps if is_prefill else res.get("steps", args.steps)),
+            "gpu_launches": res["launches_per_step"] * nsteps,
         }
+        for k_ in ("strong", "sustained", "passes"):
+            if k_ in res:
+                line[k_] = res[k_]
         if world == 1 and not args.no_cpu_baseline and not want.endswith("_small"):
-            line["cpu_baseline"] = cpu_prefill_sample(PREFILL_C2)[0]
+            line["cpu_baseline"] = cpu_prefill_sample(PREFILL_C2, host_threads())[0]
         else:
             line["cpu_baseline"] = None
-        if "passes" in res:
-            line["passes"] = res["passes"]
         for k_, v_ in extra.items():
             line[k_] = {kk: vv for kk, vv in v_.items() if kk not in ("name",)}
         print(json.dumps(line), flush=True)

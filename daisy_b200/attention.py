@@ -1,15 +1,21 @@
 """Drop-in for the reference ``CausalSelfAttention`` (models/daisy/attention.py:73-202).
 
 Same constructor, parameters (``qkvo_w [4, dim, dim]`` bf16, ``g_ve``), attributes and the three
-``AttentionProtocol`` entry points (models/daisy/attention_protocol.py:5-42).  The two
-projections stay cuBLAS GEMMs; everything between them -- q/k/v RMS norm, RoPE, the windowed
-softmax attention, the ring-cache read and write -- runs in the hand-written sm_100a kernels of
-``libdaisy_b200.so``.  There is no other code path: on a machine without the library or without a
-GPU the calls raise.
+``AttentionProtocol`` entry points (models/daisy/attention_protocol.py:5-42).  ``forward`` and ``prefill``
+run on hand-written sm_100a kernels of ``libdaisy_b200.so`` only: the merged QKV projection with the RMS
+norm, RoPE and value-embedding gate in its epilogue, the windowed softmax attention, the output projection.
+The single-token ``step`` forms run the ring-cache decode kernels; their two skinny projections are
+``F.linear``.  There is no other code path and no switch that selects one: on a machine without the library
+or without a GPU the calls raise.
 
-Masking.  The kernels implement the reference's inference mask (models/daisy/daisy_core.py:53-69,
-one document): key visible iff ``0 <= q - k < window``.  ``attn_mask`` therefore is a
-``WindowMask(window)`` (or ``None`` for plain causal) instead of a dense ``[1,1,T,T]`` tensor.
+Masking.  The kernels evaluate the reference's inference mask (models/daisy/daisy_core.py:53-69)
+analytically: key visible iff ``0 <= q - k < window`` and both tokens lie in one document.  ``attn_mask`` is
+a ``WindowMask(window[, doc_start])``, an int, ``None`` (plain causal) -- or the reference's own dense additive
+``[1,1,T,T]`` tensor, which is read once on the device to recover each row's first visible key
+(:func:`band_of_dense_mask`) and rejected if it is not such a band.
+
+Training.  The backward pass is not implemented: a call that would need gradients raises instead of
+returning a tensor autograd treats as a constant.
 """
 from __future__ import annotations
 
@@ -64,7 +70,9 @@ def create_blockmasks(input_seq: Tensor, sliding_window_num_blocks: int, L: int,
     torch._assert(input_seq.shape[-1] % WINDOW_BLOCK_SIZE == 0, "input_seq length must be divisible by the block size")
     ds = doc_starts(input_seq, eos_token_id)
     wb = int(sliding_window_num_blocks)
-    long_bm, short_bm = BlockWindowMask(wb, ds), BlockWindowMask(wb // 2, ds)
+    # the reference clamps a layer's partial-block count to at least 1 (daisy_core.py:216), so the short layers
+    # of a one-block window keep the diagonal block
+    long_bm, short_bm = BlockWindowMask(wb, ds), BlockWindowMask(max(wb // 2, 1), ds)
     cycle = [long_bm] + [short_bm] * 3
     return (cycle * ((L + 3) // 4))[:L - 1] + [long_bm]
 
@@ -77,6 +85,37 @@ def doc_starts(input_seq: Tensor, eos_token_id: int) -> Tensor:
     pos = torch.arange(seq.shape[-1], device=seq.device).expand_as(seq)
     marks = torch.where(seq == eos_token_id, pos, torch.zeros_like(pos))
     return torch.cummax(marks, dim=-1).values.to(torch.int32)
+
+
+def band_of_dense_mask(mask: Tensor) -> Tensor:
+    """First visible key of every query row of a dense attention mask, int32 ``[T]`` or ``[B,T]``.
+
+    ``mask`` is what the reference passes to ``F.scaled_dot_product_attention``: additive float (0 = visible,
+    -inf = masked; models/daisy/daisy_core.py:53-69) or boolean (True = visible), shape ``[T,T]``,
+    ``[1,1,T,T]`` or ``[B,1,T,T]``.  The kernels can express exactly the masks of that builder -- row q sees the
+    contiguous keys ``first[q] .. q`` with ``first`` non-decreasing (causal, sliding window, documents) -- so the
+    tensor is checked to be such a band on the device (one pass over T x T and one host synchronisation; pass a
+    ``WindowMask`` to avoid both) and ``ValueError`` is raised otherwise."""
+    if mask.dim() == 4:
+        torch._assert(mask.size(1) == 1, "a dense mask must broadcast over heads: [B,1,T,T]")
+        mask = mask[:, 0]
+    if mask.dim() == 2:
+        mask = mask[None]
+    torch._assert(mask.dim() == 3 and mask.size(-1) == mask.size(-2), "a dense mask must be [T,T], [1,1,T,T] or [B,1,T,T]")
+    if not mask.is_cuda:
+        raise ValueError("the dense mask must be a CUDA tensor (daisy_b200 has no CPU path)")
+    T = mask.size(-1)
+    vis = mask if mask.dtype == torch.bool else (mask == 0)
+    cnt = vis.sum(-1)
+    first = vis.to(torch.uint8).argmax(-1)
+    last = (T - 1) - vis.flip(-1).to(torch.uint8).argmax(-1)
+    q = torch.arange(T, device=mask.device)
+    ok = (cnt > 0) & (last == q) & (cnt == q - first + 1)
+    ok = ok.all() & (first[:, 1:] >= first[:, :-1]).all()
+    if not bool(ok):
+        raise ValueError("the dense attn_mask is not a causal band (window / document mask): the B200 kernels cannot express it")
+    first = first.to(torch.int32)
+    return first[0] if first.size(0) == 1 else first
 
 
 class Rotary(nn.Module):
@@ -130,10 +169,6 @@ class B200CausalSelfAttention(nn.Module):
         self.last_q = None
         self.last_k = None
         self.receives_ve = receives_ve
-        # True (default): forward / prefill run the projections on this library's tcgen05 GEMM, the norm and RoPE in
-        # the QKV epilogue (measured faster than cuBLAS followed by the norm/RoPE pass); False or
-        # DAISY_NATIVE_GEMM=0: F.linear (cuBLAS) + qkv_prep.  Single-token steps always take the F.linear form.
-        self.native_gemm = os.environ.get("DAISY_NATIVE_GEMM", "1") == "1"
         if receives_ve:
             init = {0: 0.3228, 1: 0.0, 2: -1.5163, 21: -2.4423, 22: -2.9444, 23: 10.0}.get(layer_idx, 0.0) \
                 if layer_idx is not None else 0.0
@@ -147,6 +182,7 @@ class B200CausalSelfAttention(nn.Module):
 
     # ------------------------------------------------------------------ helpers
     def _project(self, x: Tensor):
+        self._no_autograd(x)
         B, T = x.size(0), x.size(1)
         x = x.to(self.qkvo_w.dtype)
         qkv = F.linear(x, self.qkvo_w[:3].flatten(end_dim=1)).view(B, T, 3 * self.num_heads, self.head_dim)
@@ -164,44 +200,37 @@ class B200CausalSelfAttention(nn.Module):
             return attn_mask.window_blocks, attn_mask.doc_start, True
         if isinstance(attn_mask, int):
             return attn_mask, None
-        raise TypeError("attn_mask must be None, an int window or WindowMask(window[, doc_start]); dense mask "
-                        "tensors are not consumed by the B200 kernels")
+        if isinstance(attn_mask, Tensor):
+            # the reference's dense mask: causal + "first visible key per row" says everything it can hold
+            return None, band_of_dense_mask(attn_mask)
+        raise TypeError("attn_mask must be None, an int window, WindowMask(window[, doc_start]) or the dense mask tensor of "
+                        "build_attn_mask")
+
+    def _no_autograd(self, x: Tensor):
+        if torch.is_grad_enabled() and (x.requires_grad or self.qkvo_w.requires_grad
+                                        or (self.g_ve is not None and self.g_ve.requires_grad)):
+            raise NotImplementedError("daisy_b200 implements the forward pass only: call under torch.no_grad() / "
+                                      "inference_mode(), or detach the input and freeze the parameters")
 
     def _attend(self, x: Tensor, ve: Optional[Tensor], mask):
+        """Every kernel hand-written: QKV GEMM with norm + RoPE (+ the value-embedding gate) in its epilogue,
+        attention, output GEMM.  Returns ``(y, k', v', q')`` with k', v', q' shaped ``[B,H,T,D]``."""
+        self._no_autograd(x)
         window, doc_start = mask[0], mask[1]
         in_blocks = len(mask) > 2 and mask[2]
         B, T = x.size(0), x.size(1)
         cos, sin = self.rotary.tables(T)
-        if self.native_gemm and self.m_dim % 64 == 0:
-            # every kernel hand-written: QKV GEMM with norm + RoPE (+ the value-embedding gate) in its epilogue,
-            # attention, output GEMM
-            w = self.qkvo_w
-            ve_kw = {}
-            if self.receives_ve:
-                torch._assert(ve is not None, "ve must be provided when receives_ve=True")
-                ve_kw = dict(ve=ve.to(torch.bfloat16), ve_gate_logit=self.g_ve.detach().float().reshape(1))
-            qp, kp, vp = ops.qkv_gemm(x.to(w.dtype), w[:3].flatten(end_dim=1), cos, sin, self.num_heads, self.norm_eps,
-                                      **ve_kw)
-            y = ops.swa_attend(qp, kp, vp, window, self.attn_scale, bounded_qk=True, doc_start=doc_start,
-                               window_in_blocks=in_blocks)
-            y = ops.gemm_nt(y.view(B, T, self.m_dim), w[3])
-            return y, kp.transpose(1, 2), vp.transpose(1, 2), qp.transpose(1, 2)
-        q, k, v = self._project(x)
+        w = self.qkvo_w.detach()
+        ve_kw = {}
         if self.receives_ve:
             torch._assert(ve is not None, "ve must be provided when receives_ve=True")
-            # the gate v' = sigmoid(g_ve) * norm(v) + (1 - sigmoid(g_ve)) * ve rides on the norm/RoPE pass
-            ve_ = ve.view(B, T, self.num_heads, self.head_dim).to(torch.bfloat16)
-            qp, kp, vp = ops.qkv_prep(q, k, v, cos, sin, self.norm_eps, ve=ve_,
-                                      ve_gate_logit=self.g_ve.detach().float().reshape(1))
-            y = ops.swa_attend(qp, kp, vp, window, self.attn_scale, bounded_qk=True,   # q, k are RMS-normalised
-                               doc_start=doc_start, window_in_blocks=in_blocks)
-            qp, kp, vp = qp.transpose(1, 2), kp.transpose(1, 2), vp.transpose(1, 2)
-        else:
-            y, kp, vp = ops.swa_prefill(q, k, v, cos, sin, window, self.attn_scale, self.norm_eps, doc_start=doc_start,
-                                        window_in_blocks=in_blocks)
-            qp = None
-        y = F.linear(y.view(B, T, self.m_dim), self.qkvo_w[3])
-        return y, kp, vp, qp
+            ve_kw = dict(ve=ve.to(torch.bfloat16), ve_gate_logit=self.g_ve.detach().float().reshape(1))
+        qp, kp, vp = ops.qkv_gemm(x.detach().to(w.dtype), w[:3].flatten(end_dim=1), cos, sin, self.num_heads, self.norm_eps,
+                                  **ve_kw)
+        y = ops.swa_attend(qp, kp, vp, window, self.attn_scale, bounded_qk=True, doc_start=doc_start,   # q, k are RMS-normalised
+                           window_in_blocks=in_blocks)
+        y = ops.gemm_nt(y.view(B, T, self.m_dim), w[3])
+        return y, kp.transpose(1, 2), vp.transpose(1, 2), qp.transpose(1, 2)
 
     # ------------------------------------------------------------------ AttentionProtocol
     def forward(self, x: Tensor, ve: Optional[Tensor], block_mask=None, attn_mask=None):
@@ -219,7 +248,7 @@ class B200CausalSelfAttention(nn.Module):
         """Returns ``(y [B,T,dim], k [B,H,T,D], v [B,H,T,D])`` (models/daisy/attention.py:173-179)."""
         y, k, v, q = self._attend(x, ve, self._window_of(attn_mask))
         if debug:
-            self.last_q = None if q is None else q.transpose(1, 2)
+            self.last_q = q.transpose(1, 2)
             self.last_k = k.transpose(1, 2)
         return y, k, v
 
@@ -250,7 +279,7 @@ class B200CausalSelfAttention(nn.Module):
         y = F.linear(y.view(B, 1, self.m_dim), self.qkvo_w[3])
         return y, k_new, v_new
 
-    def step_ring_dev(self, x, cache: B200KVCache, layer: int, window: Optional[int]):
+    def step_ring_dev(self, x, cache: B200KVCache, layer: int, window: Optional[int], write_ring: bool = True):
         """``step_ring`` with the position read from ``cache.t_dev`` on the device: nothing in the launch
         sequence depends on the token index, so it can be captured once in a CUDA graph and replayed
         (``StepRunner.capture_step``).  Position = tokens in the cache, as in ``Generator._step``."""
@@ -259,7 +288,7 @@ class B200CausalSelfAttention(nn.Module):
         q, k, v = self._project(x)
         kr, vr = cache.ring(layer)
         y = ops.swa_decode_step_dev(q, k, v, kr, vr, cache.t_dev, cache.W, window, self.rotary.cos, self.rotary.sin,
-                                    self.attn_scale, self.norm_eps, QKV_DEFAULT, write_ring=True)
+                                    self.attn_scale, self.norm_eps, QKV_DEFAULT, write_ring=write_ring)
         return F.linear(y.view(B, 1, self.m_dim), self.qkvo_w[3])
 
     def _decode(self, q, k, v, kc, vc, t, cap, pos, ve, window, write_ring):

@@ -77,14 +77,6 @@ struct KdaIntraParams {
   int l2norm;
 };
 
-#ifdef KDA_PHASE_TIMING
-__device__ long long kda_phase_clk[16];
-// a CTA of the last wave: the first CTAs on an SM also pay for a cold instruction cache
-#define KDA_MARK(n) do { __syncthreads(); if (threadIdx.x == 0 && blockIdx.x == gridDim.x - 2 && blockIdx.y == gridDim.y - 1 && blockIdx.z == gridDim.z - 1) kda_phase_clk[n] = clock64(); } while (0)
-#else
-#define KDA_MARK(n)
-#endif
-
 constexpr int LDA = 65;    // padded row (floats) of the fp32 [64 x 64] matrices
 constexpr int LDG = KD + 4;     // padded row (floats) of G: fragment gathers (8 rows x 4 column pairs) hit 32 banks
 constexpr int LDR = KD + 8;     // padded row (bf16) of the raw k / q tiles, same reason
@@ -117,7 +109,6 @@ __global__ void __launch_bounds__(KDA_INTRA_THREADS, 1) kda_intra_kernel(const K
   const int rows = min(KC, p.T - t0);
   uint8_t* rec = p.ws + ((size_t)(b * p.H + h) * p.NC + chunk) * REC_BYTES;
 
-  KDA_MARK(0);
   // ---- P0: load the chunk (rows beyond T are zero: g = 0, beta = 0, q = k = v = 0).  All of a thread's
   //           16-byte loads are issued before the first store so that ~20 are in flight per thread.
   {
@@ -179,7 +170,6 @@ __global__ void __launch_bounds__(KDA_INTRA_THREADS, 1) kda_intra_kernel(const K
   }
   __syncthreads();
 
-  KDA_MARK(1);
   // ---- P1: cumulative gates (threads 0-127, one channel each) and L2 norms (threads 128-383)
   if (tid < KD) {
     float acc = 0.f;
@@ -207,7 +197,6 @@ __global__ void __launch_bounds__(KDA_INTRA_THREADS, 1) kda_intra_kernel(const K
   }
   __syncthreads();
 
-  KDA_MARK(2);
   // ---- P2: element-wise images: q~ and k~^T and e^{G_C} straight to the workspace, X^T and Y^T to smem
   for (int idx = tid; idx < KC * 16; idx += KDA_INTRA_THREADS) {                 // q~[i][8 channels]
     const int i = idx >> 4, c8 = (idx & 15) * 8;
@@ -245,7 +234,6 @@ __global__ void __launch_bounds__(KDA_INTRA_THREADS, 1) kda_intra_kernel(const K
     if (j8 == 0) reinterpret_cast<float*>(rec + OFF_D)[c] = __expf(gc);
   }
 
-  KDA_MARK(3);
   // ---- P3: both gated Gram matrices.  e^{G_i - G_j} must never be formed from a positive exponent, whatever
   // the gate values, so pairs are split by distance:
   //  (a) pairs inside a 16-token block, on the FMA pipes with RUNNING PRODUCTS of the per-token decays
@@ -364,7 +352,6 @@ __global__ void __launch_bounds__(KDA_INTRA_THREADS, 1) kda_intra_kernel(const K
       }
     }
     __syncthreads();                                                 // (a) is done with the decay image under Mk / Mq
-    KDA_MARK(4);
 #pragma unroll 1
     for (int ls = 5; ls >= 4; --ls) {
       const int s = 1 << ls;
@@ -435,7 +422,6 @@ __global__ void __launch_bounds__(KDA_INTRA_THREADS, 1) kda_intra_kernel(const K
     }
   }
 
-  KDA_MARK(5);
   // ---- P4: T = (I + A_kk)^-1.  (a) the four 16x16 diagonal blocks by forward substitution in fp32
   if (warp < 4 && lane < 16) {
     const int base = warp * 16;
@@ -455,7 +441,6 @@ __global__ void __launch_bounds__(KDA_INTRA_THREADS, 1) kda_intra_kernel(const K
     }
   }
   __syncthreads();
-  KDA_MARK(6);
   //      (b) block rows I = 1..3 on tensor cores, in transposed form so that the two products chain through
   //          registers:  R = T^T,  R_{<I,I} = -(R_{<I,<I} A_{I,<I}^T) R_II.  Warp mt < I owns 16 rows of R_{<I,I};
   //          the first product's accumulator pair is the second product's A fragment.  fp16 operands here cost
@@ -498,7 +483,6 @@ __global__ void __launch_bounds__(KDA_INTRA_THREADS, 1) kda_intra_kernel(const K
     __syncthreads();
   }
 
-  KDA_MARK(7);
   // ---- P5: W = T X  (warp = row block I x channel quarter) and U0^T = Y^T T^T (warp = 16 V rows x token half), fp16 MMAs.
   //          G and kraw/qraw are dead: they become the staging images.
   __half* w_img = reinterpret_cast<__half*>(&sm.G[0][0]);          // [64][136]
@@ -558,7 +542,6 @@ __global__ void __launch_bounds__(KDA_INTRA_THREADS, 1) kda_intra_kernel(const K
   }
   __syncthreads();
 
-  KDA_MARK(8);
   // ---- P6: staged images -> workspace, 16 bytes per thread per store
   for (int idx = tid; idx < KC * LDW * 2 / 16; idx += KDA_INTRA_THREADS)
     reinterpret_cast<uint4*>(rec + OFF_W)[idx] = reinterpret_cast<const uint4*>(w_img)[idx];
@@ -566,12 +549,7 @@ __global__ void __launch_bounds__(KDA_INTRA_THREADS, 1) kda_intra_kernel(const K
     reinterpret_cast<uint4*>(rec + OFF_UT)[idx] = reinterpret_cast<const uint4*>(u_img)[idx];
   for (int idx = tid; idx < KC * LDT * 2 / 16; idx += KDA_INTRA_THREADS)
     reinterpret_cast<uint4*>(rec + OFF_AQK)[idx] = reinterpret_cast<const uint4*>(&sm.Aqk[0][0])[idx];
-  KDA_MARK(9);
 }
-
-#ifdef KDA_PHASE_TIMING
-extern "C" __global__ void kda_phase_dump(long long* out) { if (threadIdx.x < 16) out[threadIdx.x] = kda_phase_clk[threadIdx.x]; }
-#endif
 
 // =============================================================================================
 // inter-chunk state kernel
@@ -766,10 +744,6 @@ __global__ void __launch_bounds__(32 * (NW + 1), 1) kda_state_kernel(const KdaSt
 }  // namespace daisy
 
 using namespace daisy;
-
-#ifdef KDA_PHASE_TIMING
-extern "C" void daisy_b200_kda_phase_dump(long long* out, void* stream) { kda_phase_dump<<<1, 32, 0, (cudaStream_t)stream>>>(out); }
-#endif
 
 extern "C" size_t daisy_b200_kda_workspace_bytes(int B, int T, int H, int K, int V) {
   if (B <= 0 || T <= 0 || H <= 0 || K != KD || V != KD) return 0;

@@ -18,7 +18,6 @@
 // All mbarrier waits are bounded; a wait that runs out raises an abort flag that every role polls,
 // the CTA drains to its teardown, frees TMEM and reports DAISY_ETIMEOUT through the status word.
 #include "common.cuh"
-#include <cstdlib>
 
 namespace daisy {
 
@@ -81,19 +80,6 @@ struct PrefillBarriers {
 __device__ __forceinline__ bool key_visible(int q, int k, int window) {
   return (k <= q) && (window <= 0 || k > q - window);
 }
-
-#ifdef PREFILL_TIMING
-__device__ long long prefill_clk[32];
-#define PT_DECL long long pt_t0 = 0, pt_acc[8] = {0, 0, 0, 0, 0, 0, 0, 0}; const bool pt_on = (blockIdx.x == 3)
-#define PT_START() do { if (pt_on) pt_t0 = clock64(); } while (0)
-#define PT_LAP(i) do { if (pt_on) { long long t_ = clock64(); pt_acc[i] += t_ - pt_t0; pt_t0 = t_; } } while (0)
-#define PT_FLUSH(base, cond) do { if (pt_on && (cond)) { for (int i_ = 0; i_ < 8; ++i_) prefill_clk[(base) + i_] = pt_acc[i_]; } } while (0)
-#else
-#define PT_DECL
-#define PT_START()
-#define PT_LAP(i)
-#define PT_FLUSH(base, cond)
-#endif
 
 // Geometry of one work item: 256 query rows (two streams) of one (batch, head).
 struct ItemGeom {
@@ -287,8 +273,6 @@ swa_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       uint32_t n_pv[2] = {0, 0};         // P tiles consumed so far per stream (phase of p_full)
       uint32_t n_q[2] = {0, 0};          // Q tiles consumed so far per stream (phase of q_full)
       bool ok = true;
-      PT_DECL;
-      PT_START();
       for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
         const ItemGeom g = item_geom(item, nq, p.H, T, window, p.doc_start, p.doc_sb, p.window_blocks);
         for (int j = g.jlo; j <= g.jhi + 1 && ok; ++j) {
@@ -301,13 +285,10 @@ swa_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
             if (j - 1 >= g.jlo_s[s] && j - 1 <= g.jhi_s[s]) {
               const int n = n_base + 2 * (j - 1 - g.jlo) + 1;
               const int stage = n % NSTAGE;
-              PT_LAP(0);
               if (!mbar_wait(&bars->p_full[s], n_pv[s] & 1, abort_flag, p.status, 2)) { ok = false; break; }
               ++n_pv[s];
-              PT_LAP(1);
               const bool v_seen = (s == 1) && g.valid[0] && (j - 1 >= g.jlo_s[0]) && (j - 1 <= g.jhi_s[0]);   // stream 0 waited on V_{j-1}
               if (!v_seen && !mbar_wait(&bars->kv_full[stage], (n / NSTAGE) & 1, abort_flag, p.status, 3)) { ok = false; break; }
-              PT_LAP(2);
               tc_fence_after();
               const uint32_t v_lo = v_lo0 + stage * (TILE_BYTES >> 4);
               const bool first = (j - 1 == g.jlo_s[s]);             // first PV of the item overwrites O_s
@@ -323,7 +304,6 @@ swa_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
             if (j >= g.jlo_s[s] && j <= g.jhi_s[s]) {
               const int n = n_base + 2 * (j - g.jlo);
               const int stage = n % NSTAGE;
-              PT_LAP(3);
               if (j == g.jlo_s[s]) {
                 const uint32_t qb = n_q[s] % NQBUF;
                 if (!mbar_wait(QRAW ? &bars->q_ready[s][qb] : &bars->q_full[s][qb], (n_q[s] / NQBUF) & 1, abort_flag, p.status, 4)) { ok = false; break; }
@@ -331,7 +311,6 @@ swa_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
               }
               const bool k_seen = (s == 1) && g.valid[0] && (j >= g.jlo_s[0]) && (j <= g.jhi_s[0]);           // stream 0 waited on K_j
               if (!k_seen && !mbar_wait(&bars->kv_full[stage], (n / NSTAGE) & 1, abort_flag, p.status, 5)) { ok = false; break; }
-              PT_LAP(4);
               tc_fence_after();
               const uint32_t q_buf = (n_q[s] - 1) % NQBUF;              // the buffer this item's Q_s sits in
               const uint32_t q_lo = q_lo0 + (q_buf * 2 + s) * (TILE_BYTES >> 4);
@@ -350,8 +329,6 @@ swa_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         }
         n_base += 2 * (g.jhi - g.jlo + 1);
       }
-      PT_LAP(5);
-      PT_FLUSH(16, lane == 0);
     }
   } else if constexpr (NSPLIT == 2) {
     // ------------------------------------------------------------------ split softmax + epilogue (bounded logits)
@@ -366,8 +343,6 @@ swa_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     uint32_t n_s = 0, n_o = 0, n_qs = 0;
     bool ok = true;
     bool q_prepared = false;                                       // raw-Q mode: the lower half prepares the stream's Q rows
-    PT_DECL;
-    PT_START();
     for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
       const ItemGeom g = item_geom(item, nq, p.H, T, window, p.doc_start, p.doc_sb, p.window_blocks);
       if (!g.valid[s]) continue;
@@ -376,10 +351,9 @@ swa_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       bool next_valid = false;
       int q_row_next = 0;
       if (QRAW && half == 0) {
-        if (!q_prepared) {
-          ok = prepare_q_tile(bars, q_tiles, s, row, n_qs, q_row, p, abort_flag);
-          if (!ok) break;
-        }
+        // a wait that ran out must not leave the item loop here: the stream's other half still comes to the two
+        // named barriers below, which need all 256 threads -- skip the tile loop and the epilogue instead
+        if (!q_prepared) ok = prepare_q_tile(bars, q_tiles, s, row, n_qs, q_row, p, abort_flag);
         q_prepared = false;
         const int item_next = item + gridDim.x;
         if (item_next < n_items) {
@@ -392,11 +366,10 @@ swa_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       // first visible key of this row's document, and the latest such start among the stream's rows
       const int ds_row = p.doc_start ? min(p.doc_start[g.b * p.doc_sb + min(q_row, T - 1)], q_row) : 0;   // a row always sees itself
       const int ds_max = p.doc_start ? p.doc_start[g.b * p.doc_sb + min(q0 + BM - 1, T - 1)] : 0;
-      for (int j = g.jlo_s[s]; j <= g.jhi_s[s]; ++j) {
+      for (int j = g.jlo_s[s]; ok && j <= g.jhi_s[s]; ++j) {
         ok = __all_sync(0xffffffffu, mbar_wait(&bars->s_full[s], n_s & 1, abort_flag, p.status, 6));
         if (!ok) break;
         ++n_s;
-        PT_LAP(0);
         tc_fence_after();
         const int k0 = j * BN + half * 64;                            // key index of this thread's first column
         const bool full_tile = (j * BN + BN - 1 <= q0) && (window <= 0 || j * BN > q0 + BM - 1 - window) && ds_max <= j * BN;
@@ -404,7 +377,6 @@ swa_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         tmem_ld32(s_tmem, r);
         tmem_ld32(s_tmem + 32, r + 32);
         tc_wait_ld();
-        PT_LAP(1);
         if (!full_tile) {
           const int hi = q_row - k0;                                   // column i is visible iff lo < i <= hi
           const int lo = max(window > 0 ? q_row - window - k0 : -1, ds_row - 1 - k0);
@@ -412,7 +384,6 @@ swa_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
           for (int i = 0; i < 64; ++i)
             if (!(i > lo && i <= hi)) r[i] = 0xff800000u;              // -inf -> weight 0
         }
-        PT_LAP(2);
 #pragma unroll
         for (int c = 0; c < 2; ++c) {
           uint32_t pk[16];
@@ -440,11 +411,9 @@ swa_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
           }
           tmem_st16(s_tmem + 16 * c, pk);
         }
-        PT_LAP(3);
         tc_wait_st();
         tc_fence_before();
         mbar_arrive(&bars->p_full[s]);
-        PT_LAP(4);
         if (QRAW && half == 0 && next_valid && !q_prepared && j == g.jlo_s[s] + 1) {   // next item's Q, inside this item
           ok = prepare_q_tile(bars, q_tiles, s, row, n_qs, q_row_next, p, abort_flag);
           if (!ok) break;
@@ -470,7 +439,6 @@ swa_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         ok = __all_sync(0xffffffffu, mbar_wait(&bars->o_full[s], n_o & 1, abort_flag, p.status, 7));
         ++n_o;
       }
-      PT_LAP(5);
       if (ok) {
         tc_fence_after();
         const float inv = 1.0f / l;
@@ -516,10 +484,7 @@ swa_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         // i.e. after these loads: program order is the guard
         tc_fence_before();
       }
-      PT_LAP(6);
     }
-    PT_FLUSH(0, threadIdx.x == 0);
-    PT_FLUSH(8, threadIdx.x == 128);
   } else {
     // ------------------------------------------------------------------ softmax + epilogue
     const int s = warp >> 2, quarter = warp & 3;
@@ -533,8 +498,6 @@ swa_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     uint32_t r[128];
     bool q_prepared = false;
     auto prepare_q = [&](int qrow) -> bool { return prepare_q_tile(bars, q_tiles, s, row, n_qs, qrow, p, abort_flag); };
-    PT_DECL;
-    PT_START();
     for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
       const ItemGeom g = item_geom(item, nq, p.H, T, window, p.doc_start, p.doc_sb, p.window_blocks);
       if (!g.valid[s]) continue;
@@ -563,7 +526,6 @@ swa_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         ok = __all_sync(0xffffffffu, mbar_wait(&bars->s_full[s], n_s & 1, abort_flag, p.status, 6));
         if (!ok) break;
         ++n_s;
-        PT_LAP(0);
         tc_fence_after();
         const int k0 = j * BN;
         const bool full_tile = (k0 + BN - 1 <= q0) && (window <= 0 || k0 > q0 + BM - 1 - window) && ds_max <= k0;
@@ -573,7 +535,6 @@ swa_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         tmem_ld32(s_tmem + 64, r + 64);
         tmem_ld32(s_tmem + 96, r + 96);
         tc_wait_ld();
-        PT_LAP(1);
         if (!full_tile) {
           // column i of this tile is visible iff lo < i <= hi
           const int hi = q_row - k0;
@@ -617,7 +578,6 @@ swa_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
           }
         }
         pend = 0.f;
-        PT_LAP(2);
         // P = exp2(S * c2 - m_ref) as bf16 into TMEM over S; row sum in fp32
         const uint64_t c2p = pack2f(c2, c2), nm = pack2f(-m_ref, -m_ref);
         uint64_t sum_a = pack2f(0.f, 0.f), sum_b = sum_a;
@@ -666,11 +626,9 @@ swa_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
           pend = pmaxf > 256.f ? __log2f(pmaxf) : 0.f;
         }
         l += rowsum;
-        PT_LAP(3);
         tc_wait_st();
         tc_fence_before();
         mbar_arrive(&bars->p_full[s]);
-        PT_LAP(4);
         if (QRAW && next_valid && !q_prepared && j == g.jlo_s[s] + 1) {
           ok = prepare_q(q_row_next);
           if (!ok) break;
@@ -681,7 +639,6 @@ swa_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         ok = __all_sync(0xffffffffu, mbar_wait(&bars->o_full[s], n_o & 1, abort_flag, p.status, 7));
         ++n_o;
       }
-      PT_LAP(5);
       if (ok) {
         tc_fence_after();
         const float inv = 1.0f / l;
@@ -706,10 +663,7 @@ swa_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         // i.e. after these loads: program order of this warp is the guard
         tc_fence_before();
       }
-      PT_LAP(6);
     }
-    PT_FLUSH(0, threadIdx.x == 0);
-    PT_FLUSH(8, threadIdx.x == 128);
   }
 
   // ------------------------------------------------------------------ teardown
@@ -815,21 +769,14 @@ umma_selftest_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_cons
 
 using namespace daisy;
 
-#ifdef PREFILL_TIMING
-__global__ void prefill_clk_dump(long long* out) { if (threadIdx.x < 32) out[threadIdx.x] = prefill_clk[threadIdx.x]; }
-extern "C" void daisy_b200_prefill_clk_dump(long long* out, void* stream) { prefill_clk_dump<<<1, 32, 0, (cudaStream_t)stream>>>(out); }
-#endif
-
 static int ensure_smem_attr() {
   static bool done[daisy_host::MAX_DEVICES] = {};             // the attribute is per device
   const int dev = daisy_host::device_slot();
   if (dev < 0) return DAISY_ENODEV;
   if (done[dev]) return DAISY_OK;
   if (cudaFuncSetAttribute(swa_prefill_kernel<false, false, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, PREFILL_SMEM) != cudaSuccess) return DAISY_ECUDA;
-  if (cudaFuncSetAttribute(swa_prefill_kernel<false, true, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, PREFILL_SMEM) != cudaSuccess) return DAISY_ECUDA;
   if (cudaFuncSetAttribute(swa_prefill_kernel<false, true, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, PREFILL_SMEM) != cudaSuccess) return DAISY_ECUDA;
   if (cudaFuncSetAttribute(swa_prefill_kernel<true, false, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, PREFILL_SMEM) != cudaSuccess) return DAISY_ECUDA;
-  if (cudaFuncSetAttribute(swa_prefill_kernel<true, true, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, PREFILL_SMEM) != cudaSuccess) return DAISY_ECUDA;
   if (cudaFuncSetAttribute(swa_prefill_kernel<true, true, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, PREFILL_SMEM) != cudaSuccess) return DAISY_ECUDA;
   if (cudaFuncSetAttribute(umma_selftest_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 1024 + 2 * TILE_BYTES + 64) != cudaSuccess) return DAISY_ECUDA;
   done[dev] = true;
@@ -851,6 +798,8 @@ static int launch_attend(const void* q, const void* k, const void* v,
       ((q_sb | q_st | q_sh | k_sb | k_st | k_sh | v_sb | v_st | v_sh) & 7))
     return DAISY_EALIGN;
   if (q_st <= 0 || k_st <= 0 || v_st <= 0 || q_sh < 0 || k_sh < 0 || v_sh < 0 || q_sb < 0 || k_sb < 0 || v_sb < 0) return DAISY_EINVAL;
+  // a zero stride on a dimension longer than 1 is a broadcast (expanded) view, which the tile loads cannot express
+  if ((H > 1 && (q_sh == 0 || k_sh == 0 || v_sh == 0)) || (B > 1 && (q_sb == 0 || k_sb == 0 || v_sb == 0))) return DAISY_EINVAL;
   if (qt && qt->rope && (!qt->cos || !qt->sin)) return DAISY_EINVAL;
   if (doc_start && (doc_sb < 0 || (reinterpret_cast<uintptr_t>(doc_start) & 3))) return DAISY_EINVAL;
   if (qt && qt->rope && (!daisy_aligned16(qt->cos) || !daisy_aligned16(qt->sin))) return DAISY_EALIGN;
@@ -858,7 +807,7 @@ static int launch_attend(const void* q, const void* k, const void* v,
   CUtensorMap tq, tk, tv;
   int rc;
   // a size-1 dimension may come with any stride; the encoder wants a non-zero multiple of 16 bytes
-  auto sb = [](int64_t s, int n) { return (uint64_t)((n == 1 || s == 0) ? 16 : s * 2); };
+  auto sb = [](int64_t s, int n) { return (uint64_t)(n == 1 ? 16 : s * 2); };
   if ((rc = daisy_host::make_tmap_bf16_dthb(&tq, q, D, T, H, B, q_st * 2, sb(q_sh, H), sb(q_sb, B), 64, BM)) != DAISY_OK) return rc;
   if ((rc = daisy_host::make_tmap_bf16_dthb(&tk, k, D, T, H, B, k_st * 2, sb(k_sh, H), sb(k_sb, B), 64, BN)) != DAISY_OK) return rc;
   if ((rc = daisy_host::make_tmap_bf16_dthb(&tv, v, D, T, H, B, v_st * 2, sb(v_sh, H), sb(v_sb, B), 64, BN)) != DAISY_OK) return rc;
@@ -881,14 +830,11 @@ static int launch_attend(const void* q, const void* k, const void* v,
   // with RMS-normalised q and k every logit is bounded by scale * D: 2^(logit - reference) cannot overflow
   const bool bounded = bounded_qk && scale * 1.4426950408889634f * (float)D <= 60.f;
   cudaStream_t st = (cudaStream_t)stream;
-  static int split = -1;                   // DAISY_PREFILL_SPLIT=0 keeps one softmax warpgroup per stream
-  if (split < 0) { const char* e = getenv("DAISY_PREFILL_SPLIT"); split = e ? atoi(e) : 1; }
-  if (raw && bounded && split) swa_prefill_kernel<true, true, 2><<<grid, PREFILL_THREADS_SPLIT, PREFILL_SMEM, st>>>(tq, tk, tv, p);
-  else if (raw && bounded)  swa_prefill_kernel<true, true, 1><<<grid, PREFILL_THREADS, PREFILL_SMEM, st>>>(tq, tk, tv, p);
-  else if (raw)             swa_prefill_kernel<true, false, 1><<<grid, PREFILL_THREADS, PREFILL_SMEM, st>>>(tq, tk, tv, p);
-  else if (bounded && split) swa_prefill_kernel<false, true, 2><<<grid, PREFILL_THREADS_SPLIT, PREFILL_SMEM, st>>>(tq, tk, tv, p);
-  else if (bounded)         swa_prefill_kernel<false, true, 1><<<grid, PREFILL_THREADS, PREFILL_SMEM, st>>>(tq, tk, tv, p);
-  else                      swa_prefill_kernel<false, false, 1><<<grid, PREFILL_THREADS, PREFILL_SMEM, st>>>(tq, tk, tv, p);
+  // bounded logits take the form with two softmax warpgroups per stream, everything else the general form
+  if (raw && bounded)  swa_prefill_kernel<true, true, 2><<<grid, PREFILL_THREADS_SPLIT, PREFILL_SMEM, st>>>(tq, tk, tv, p);
+  else if (raw)        swa_prefill_kernel<true, false, 1><<<grid, PREFILL_THREADS, PREFILL_SMEM, st>>>(tq, tk, tv, p);
+  else if (bounded)    swa_prefill_kernel<false, true, 2><<<grid, PREFILL_THREADS_SPLIT, PREFILL_SMEM, st>>>(tq, tk, tv, p);
+  else                 swa_prefill_kernel<false, false, 1><<<grid, PREFILL_THREADS, PREFILL_SMEM, st>>>(tq, tk, tv, p);
   DAISY_CHECK_LAUNCH();
   return DAISY_OK;
 }

@@ -52,8 +52,8 @@ class StepRunner:
         t_saved = self.cache.t_dev.clone()
         side = torch.cuda.Stream(device=dev)
         side.wait_stream(torch.cuda.current_stream(dev))
-        with torch.cuda.stream(side):                              # warm-up outside the capture (lazy initialisation)
-            self._graph_body()
+        with torch.cuda.stream(side):                              # warm-up outside the capture (lazy initialisation);
+            self._graph_body(write_ring=False)                     # it must not store its dummy row into the ring
         torch.cuda.current_stream(dev).wait_stream(side)
         self.cache.t_dev.copy_(t_saved)                            # the warm-up advanced the device counter
         self._graph = torch.cuda.CUDAGraph()
@@ -61,17 +61,18 @@ class StepRunner:
             self._gy = self._graph_body()
         self.cache.t_dev.copy_(t_saved)
 
-    def _graph_body(self) -> torch.Tensor:
+    def _graph_body(self, write_ring: bool = True) -> torch.Tensor:
         x = self._gx
         for i, a in enumerate(self.layers):
-            x = a.step_ring_dev(x, self.cache, i, self.window)
+            x = a.step_ring_dev(x, self.cache, i, self.window, write_ring=write_ring)
         self.cache.t_dev += 1
         return x
 
     @torch.inference_mode()
     def _step_graph(self, x: torch.Tensor) -> torch.Tensor:
-        """``_step`` through the captured graph.  The warm-up and the capture wrote one ring slot each (the slot
-        of the position they ran at), which the first replay overwrites with the same token's real row."""
+        """``_step`` through the captured graph.  Neither the warm-up run (made without the ring store) nor the
+        capture itself (which executes nothing) has touched the ring, so a capture is safe at any position, also
+        with a window larger than the ring, where the slot of the next token is the oldest row still attended."""
         self._gx.copy_(x)
         self._graph.replay()
         self.cache.t += 1                                          # host mirror; the device counter moved in the graph

@@ -155,6 +155,10 @@ class B200KimiLinearSelfAttention(torch.nn.Module):
     def _forward_core(self, x, ve, sa_lambdas, attn_mask, use_cache: bool):
         if attn_mask is not None:
             raise NotImplementedError("attn_mask (variable-length unpadding) is not implemented by the B200 KDA layer")
+        if torch.is_grad_enabled() and (x.requires_grad or any(p.requires_grad for p in self.parameters())):
+            # the kernels return tensors without a grad_fn: autograd would treat the layer as a constant
+            raise NotImplementedError("daisy_b200 implements the forward pass only: call under torch.no_grad() / "
+                                      "inference_mode(), or detach the input and freeze the parameters")
         B, T, _ = x.shape
         H = self.num_heads
         q, k, v = _linear(x, self.q_proj.weight), _linear(x, self.k_proj.weight), _linear(x, self.v_proj.weight)

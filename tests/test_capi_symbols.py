@@ -57,6 +57,9 @@ def test_argument_validation_without_gpu(lib):
     # misaligned pointer / stride
     assert lib.daisy_b200_swa_attend(a + 2, a, a, 128, 128, 128, 128, 128, 128, 128, 128, 128, a, 128, 128, 128, 1, 1, 1, 128, 0, 0.12, None, 0, 0, None, None) == _lib.EALIGN
     assert lib.daisy_b200_swa_attend(a, a, a, 128, 132, 128, 128, 128, 128, 128, 128, 128, a, 128, 128, 128, 1, 1, 1, 128, 0, 0.12, None, 0, 0, None, None) == _lib.EALIGN
+    # a broadcast (zero-stride) head or batch dimension longer than 1 is refused, not read at overlapping offsets
+    assert lib.daisy_b200_swa_attend(a, a, a, 128, 128, 0, 128, 128, 128, 128, 128, 128, a, 256, 256, 128, 1, 1, 2, 128, 0, 0.12, None, 0, 0, None, None) == _lib.EINVAL
+    assert lib.daisy_b200_swa_attend(a, a, a, 128, 128, 128, 0, 128, 128, 128, 128, 128, a, 128, 128, 128, 2, 1, 1, 128, 0, 0.12, None, 0, 0, None, None) == _lib.EINVAL
     # workspace too small
     need = lib.daisy_b200_swa_prefill_workspace_bytes(1, 128, 2, 128)
     assert need == 3 * 128 * 2 * 128 * 2

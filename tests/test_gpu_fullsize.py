@@ -100,8 +100,11 @@ def test_decode_c3_full_size():
 
 
 def test_kda_c5_full_size():
-    """B=4, T=16384, 16 heads, K=V=128 (the KDA configuration): prefixes of sampled (b, h) against the fp32
-    recurrence, and one call over T against two calls over T/2 chained through the state."""
+    """B=4, T=16384, 16 heads, K=V=128 (the KDA configuration): sampled (b, h) against the fp32 recurrence --
+    prefixes, and for one pair the WHOLE length (every output row, the last 256 rows on their own, the final
+    state), so drift of the fp32 state over 256 chunks is compared with the recurrence and not only with the
+    kernel itself; one call over T against two calls over T/2 chained through the state; and the per-GPU shapes of
+    the multi-GPU partition (8 (batch, head) pairs = half the heads of one batch row) give the same bits."""
     from daisy_b200 import ops
     B, T, H = 4, 16384, 16
     g_ = torch.Generator(device="cuda").manual_seed(50)
@@ -117,6 +120,18 @@ def test_kda_c5_full_size():
         o_ref, _ = okda.kda_recurrent(sl(q), sl(k), sl(v), sl(g), beta[b:b + 1, :n, h:h + 1].cpu())
         rel = ((o[b:b + 1, :n, h:h + 1].cpu() - o_ref).norm() / o_ref.norm()).item()
         assert rel <= 1e-3, rel
+    # full length for one (b, h): 16384 steps of the CPU recurrence (seconds)
+    b, h = 2, 7
+    sl = lambda x: x[b:b + 1, :, h:h + 1].float().cpu()
+    o_ref, s_ref = okda.kda_recurrent(sl(q), sl(k), sl(v), sl(g), beta[b:b + 1, :, h:h + 1].cpu())
+    o_bh = o[b:b + 1, :, h:h + 1].cpu()
+    assert ((o_bh - o_ref).norm() / o_ref.norm()).item() <= 1e-3
+    assert ((o_bh[:, -256:] - o_ref[:, -256:]).norm() / o_ref[:, -256:].norm()).item() <= 1e-3
+    assert ((s[b:b + 1, h:h + 1].cpu() - s_ref).norm() / s_ref.norm()).item() <= 1e-3
+    # the shard one GPU of eight computes: heads 0..7 of batch row 2, as its own contiguous tensors
+    shard = lambda x: x[b:b + 1, :, :8].contiguous()
+    o_sh, s_sh = ops.kda_chunk_fwd(shard(q), shard(k), shard(v), shard(g), shard(beta), None, None, True, out_fp32=True)
+    assert torch.equal(o_sh, o[b:b + 1, :, :8]) and torch.equal(s_sh, s[b:b + 1, :8])
     half = T // 2
     cut = lambda x, a, b_: x[:, a:b_].contiguous()
     o1, s1 = ops.kda_chunk_fwd(cut(q, 0, half), cut(k, 0, half), cut(v, 0, half), cut(g, 0, half), cut(beta, 0, half),

@@ -49,12 +49,14 @@ def test_qkv_gemm_epilogue_matches_oracle(B, T, H, dim):
     assert_close_bf16(vp, vn, "v'")
 
 
-def test_module_forward_native_gemm_matches_library_gemm_path(golden_dir):
-    """``native_gemm=True`` (the default) runs the whole forward on hand-written kernels (fused QKV GEMM, attention, output
-    GEMM); same result as the cuBLAS-projection path within bf16 rounding, and the reference fixture's bar."""
+def test_module_forward_matches_library_gemm_composition(golden_dir):
+    """The module's forward runs on hand-written kernels only (fused QKV GEMM, attention, output GEMM); the same
+    forward composed here from torch's GEMMs and the separate norm / RoPE pass agrees within bf16 rounding, and both
+    meet the reference fixture's bar."""
     import os
     import numpy as np
-    from daisy_b200 import B200CausalSelfAttention, WindowMask
+    import torch.nn.functional as F
+    from daisy_b200 import B200CausalSelfAttention, WindowMask, ops
     z = np.load(os.path.join(golden_dir, "csa_prefill_small.npz"))
     H, D, W = int(z["heads"]), int(z["head_dim"]), int(z["window"])
     os.environ["DISABLE_O_ZERO_INIT"] = "1"
@@ -63,14 +65,15 @@ def test_module_forward_native_gemm_matches_library_gemm_path(golden_dir):
     with torch.no_grad():
         m.qkvo_w.copy_(torch.from_numpy(z["qkvo_w"]).to(m.qkvo_w.dtype))
     x = torch.from_numpy(z["x"]).bfloat16().cuda()
+    B, T = x.shape[:2]
     with torch.inference_mode():
-        m.native_gemm = False
-        y_lib = m(x, None, attn_mask=WindowMask(W))
-        m.native_gemm = True
         y_nat = m(x, None, attn_mask=WindowMask(W))
+        q, k, v = F.linear(x, m.qkvo_w[:3].flatten(end_dim=1)).view(B, T, 3 * H, D).chunk(3, dim=-2)
+        y_lib, _, _ = ops.swa_prefill(q, k, v, m.rotary.cos, m.rotary.sin, W, m.attn_scale, m.norm_eps)
+        y_lib = F.linear(y_lib.view(B, T, H * D), m.qkvo_w[3])
     ref = torch.from_numpy(z["y"])
     assert_close_bf16(y_nat, ref, "native forward vs reference fixture", max_tol=4e-2, mean_tol=4e-3)
-    assert_close_bf16(y_nat, y_lib.float().cpu(), "native vs cuBLAS projections", max_tol=3e-2, mean_tol=3e-3)
+    assert_close_bf16(y_nat, y_lib.float().cpu(), "native vs library projections", max_tol=3e-2, mean_tol=3e-3)
 
 
 def test_qkv_gemm_value_embedding_gate():

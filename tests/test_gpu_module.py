@@ -251,11 +251,33 @@ def test_forward_with_eos_document_mask_matches_reference_fixture(golden_dir):
         attn.qkvo_w.copy_(torch.from_numpy(d["qkvo_w"]).to(attn.qkvo_w.dtype))
     seq = torch.from_numpy(d["seq"]).cuda()
     mask = WindowMask.from_tokens(seq, int(d["window"]), int(d["eos"]))
-    y = attn(x.cuda().bfloat16(), None, attn_mask=mask)
+    with torch.inference_mode():
+        y = attn(x.cuda().bfloat16(), None, attn_mask=mask)
     ref = torch.from_numpy(d["y"])
     err = (y.float().cpu() - ref).abs()
     scale = max(1.0, ref.abs().max().item())
     assert err.max().item() <= 4e-2 * scale and err.mean().item() <= 4e-3 * scale
+    # the reference's own dense additive mask tensor (what DaisyCore.prefill passes, daisy_core.py:338-346), as
+    # [1,1,T,T], as [T,T] and as a boolean mask: same bits as the analytic form
+    dense = torch.from_numpy(d["mask"]).cuda()
+    with torch.inference_mode():
+        for mk in (dense[None, None], dense, dense == 0):
+            y_d, k_d, v_d = attn.prefill(x.cuda().bfloat16(), None, attn_mask=mk)
+            assert torch.equal(y_d, y)
+    from daisy_b200.attention import band_of_dense_mask
+    T = dense.shape[0]
+    first = band_of_dense_mask(dense[None, None])
+    want = torch.maximum(mask.doc_start.cuda().view(-1), (torch.arange(T, device="cuda") - int(d["window"]) + 1).clamp_min(0).int())
+    assert torch.equal(first, want.to(torch.int32))
+    # masks the kernels cannot express are refused, not approximated
+    holed = dense.clone(); holed[150, 120] = float("-inf")
+    future = dense.clone(); future[10, 11] = 0.0
+    for bad in (holed, future, torch.full_like(dense, float("-inf"))):
+        with pytest.raises(ValueError, match="causal band"):
+            band_of_dense_mask(bad)
+    # a call that would need gradients raises (the backward pass is not implemented)
+    with pytest.raises(NotImplementedError, match="forward pass only"):
+        attn(x.cuda().bfloat16(), None, attn_mask=mask)
 
 
 def test_forward_with_block_mask_training_form():
@@ -308,6 +330,35 @@ def test_step_through_cuda_graph_equals_eager_steps():
     from daisy_b200 import ops
     ops.check_device_status("cuda")
     assert graph.cache.t == eager.cache.t == P + N and int(graph.cache.t_dev.item()) == P + N
+    assert torch.equal(graph.cache.k, eager.cache.k) and torch.equal(graph.cache.v, eager.cache.v)
+
+
+def test_graph_capture_after_the_ring_wrapped_with_window_larger_than_capacity():
+    """Capturing the graph step must leave the ring alone: with a window larger than the ring capacity the slot of
+    the next token holds the oldest row the next step still attends to.  Eager steps first (so that slot holds a real
+    row), then the capture, then graph steps against eager ones."""
+    from daisy_b200 import B200CausalSelfAttention, StepRunner
+    os.environ["DISABLE_O_ZERO_INIT"] = "1"
+    torch.manual_seed(8)
+    B, H, D, W, cap, P, E, N = 1, 2, 128, 40, 16, 10, 12, 20
+    layers = [B200CausalSelfAttention(H * D, H, D, max_seq_len=256).cuda().eval() for _ in range(2)]
+    for m in layers:
+        with torch.no_grad():
+            m.qkvo_w.mul_(4.0)
+    x = torch.randn(B, P + E + N, H * D, device="cuda", dtype=torch.bfloat16)
+    eager = StepRunner(layers, window=W, cache_capacity=cap, batch=B)
+    graph = StepRunner(layers, window=W, cache_capacity=cap, batch=B)
+    for run in (eager, graph):
+        run._prefill(x[:, :P])
+        for i in range(E):
+            run._step(x[:, P + i:P + i + 1])
+    assert graph.cache.t == P + E > cap
+    before = (graph.cache.k.clone(), graph.cache.v.clone())
+    graph.capture_step(B, H * D)
+    assert torch.equal(graph.cache.k, before[0]) and torch.equal(graph.cache.v, before[1])
+    for i in range(N):
+        xi = x[:, P + E + i:P + E + i + 1]
+        assert torch.equal(eager._step(xi), graph._step_graph(xi).clone()), f"step {i}"
     assert torch.equal(graph.cache.k, eager.cache.k) and torch.equal(graph.cache.v, eager.cache.v)
 
 

@@ -45,7 +45,14 @@ def test_module_construction_and_mask_parsing(monkeypatch):
     assert doc_starts(seq, 9).tolist() == [0, 1, 1, 1, 4, 5, 5]              # an EOS opens the next document
     assert WindowMask.from_tokens(seq, 4, 9).doc_start.tolist() == [0, 1, 1, 1, 4, 5, 5]
     with pytest.raises(TypeError):
+        m._window_of("causal")
+    with pytest.raises(ValueError, match="CUDA tensor"):       # the dense mask is read on the device
         m._window_of(torch.zeros(1, 1, 4, 4))
+    # calls that would need gradients raise instead of returning a constant (the backward pass is not built)
+    with pytest.raises(NotImplementedError, match="forward pass only"):
+        m(torch.zeros(1, 4, 256, dtype=torch.bfloat16), None)
+    from daisy_b200.attention import create_blockmasks
+    assert [bm.window_blocks for bm in create_blockmasks(torch.zeros(128, dtype=torch.long), 1, 3, 9)] == [1, 1, 1]
     with pytest.raises(Exception):
         B200CausalSelfAttention(128, 2, 64)                    # head_dim must be 128
     g = B200CausalSelfAttention(256, 2, 128, receives_ve=True, layer_idx=2, max_seq_len=8)
