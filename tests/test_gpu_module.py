@@ -270,7 +270,8 @@ def test_forward_with_eos_document_mask_matches_reference_fixture(golden_dir):
     want = torch.maximum(mask.doc_start.cuda().view(-1), (torch.arange(T, device="cuda") - int(d["window"]) + 1).clamp_min(0).int())
     assert torch.equal(first, want.to(torch.int32))
     # masks the kernels cannot express are refused, not approximated
-    holed = dense.clone(); holed[150, 120] = float("-inf")
+    assert float(dense[140, 120]) == 0.0
+    holed = dense.clone(); holed[140, 120] = float("-inf")
     future = dense.clone(); future[10, 11] = 0.0
     for bad in (holed, future, torch.full_like(dense, float("-inf"))):
         with pytest.raises(ValueError, match="causal band"):
