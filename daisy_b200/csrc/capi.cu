@@ -82,4 +82,19 @@ int make_tmap_bf16_dthb(CUtensorMap* m, const void* base, uint64_t D, uint64_t T
   return r == CUDA_SUCCESS ? DAISY_OK : DAISY_ECUDA;
 }
 
+int make_tmap_rows_bthd(CUtensorMap* m, const void* base, int elem_bytes, uint64_t D, uint64_t T, uint64_t H, uint64_t B,
+                        uint32_t rows) {
+  EncodeTiledFn enc = get_encode_tiled();
+  if (!enc) return DAISY_ECUDA;
+  const uint64_t e = (uint64_t)elem_bytes;
+  cuuint64_t dims[4] = {D, T, H, B};
+  cuuint64_t strides[3] = {H * D * e, D * e, T * H * D * e};
+  cuuint32_t box[4] = {(cuuint32_t)D, rows, 1, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = enc(m, elem_bytes == 4 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4,
+                   const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? DAISY_OK : DAISY_ECUDA;
+}
+
 }  // namespace daisy_host

@@ -160,6 +160,11 @@ __host__ __device__ constexpr uint32_t umma_idesc_bf16(int M, int N, int a_mn_ma
   return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)a_mn_major << 15) | ((uint32_t)b_mn_major << 16) |
          ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
 }
+// The same descriptor for fp16 inputs (A and B format 0 = f16), fp32 accumulation.
+__host__ __device__ constexpr uint32_t umma_idesc_f16(int M, int N, int a_mn_major, int b_mn_major) {
+  return (1u << 4) | ((uint32_t)a_mn_major << 15) | ((uint32_t)b_mn_major << 16) |
+         ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
+}
 // D[tmem] (+)= A[smem] * B[smem]
 __device__ __forceinline__ void umma_ss(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
   asm volatile(
@@ -323,6 +328,22 @@ __device__ __forceinline__ uint64_t exp2_poly2(uint64_t x2) {
   return pack2f(__uint_as_float(r0), __uint_as_float(r1));
 }
 
+// Named barrier over `n` threads (a multiple of 32) that also ORs a predicate over them: every participant learns
+// whether any of them has given up, so a group leaves its loop together and nobody is left waiting at the next
+// named barrier.
+__device__ __forceinline__ bool named_bar_or(int id, int n, bool pred) {
+  uint32_t r;
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\tsetp.ne.b32 q, %3, 0;\n\t"
+      "bar.red.or.pred p, %1, %2, q;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(r) : "r"(id), "r"(n), "r"((uint32_t)pred) : "memory");
+  return r != 0;
+}
+__device__ __forceinline__ void named_bar(int id, int n) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(n) : "memory");
+}
+
 __device__ __forceinline__ bool elect_one() {
   uint32_t pred;
   asm volatile(
@@ -360,5 +381,10 @@ int make_tmap_bf16_3d(CUtensorMap* m, const void* base, uint64_t n0, uint64_t n1
 // (b0, b1, 1, 1), 128-byte swizzle, zero fill out of bounds.  Covers [B,T,H,D] and [B,H,T,D] alike.
 int make_tmap_bf16_dthb(CUtensorMap* m, const void* base, uint64_t D, uint64_t T, uint64_t H, uint64_t B,
                         uint64_t st_bytes, uint64_t sh_bytes, uint64_t sb_bytes, uint32_t b0, uint32_t b1);
+
+// The same addressing for a contiguous [B,T,H,D] tensor of bf16 (elem_bytes 2) or float32 (4) elements, box
+// (D, rows, 1, 1), NO swizzle: whole token rows land one after another in shared memory, for element-wise readers.
+int make_tmap_rows_bthd(CUtensorMap* m, const void* base, int elem_bytes, uint64_t D, uint64_t T, uint64_t H, uint64_t B,
+                        uint32_t rows);
 
 }  // namespace daisy_host

@@ -7,11 +7,12 @@
 //     T = (I + A_kk)^-1          W = T (beta k e^G)          U0 = T (beta v)
 //     U = U0 - W S_0             O = (scale q e^G) S_0 + A_qk U          S_C = e^{G_C} S_0 + (k e^{G_C-G})^T U
 // Two kernels:
-//  * kda_intra_kernel  -- one CTA per (batch, head, chunk), all chunks in parallel: cumulative gates,
-//    the two gated Gram matrices (off-diagonal 16x16 blocks on tensor cores with both decay factors <= 1,
-//    diagonal blocks with the exact e^{G_i-G_j} per pair), the unit-lower-triangular inverse in fp32,
-//    W and U0 on tensor cores.  It writes, per chunk, fp16 "shared-memory images" (rows padded so that
-//    fragment loads are bank-conflict free) of W, scale q e^G, (k e^{G_C-G})^T, A_qk, U0^T and e^{G_C}.
+//  * kda_intra_kernel  -- everything that does not depend on the state, all chunks in parallel, on tcgen05 tensor
+//    cores: a persistent CTA per SM walks (batch, head, chunk) work items; 16 "element" warps turn the TMA-staged
+//    inputs into fp16 operand images and issue the Gram products on them, 4 "solver" warps pull the Gram entries
+//    out of TMEM, invert I + A_kk and issue / drain the W and U0 products -- two pipelines that overlap across
+//    consecutive chunks.  Per chunk it writes a record of fp16 operand images (rows padded so that fragment loads
+//    are bank-conflict free): W^T, (scale q e^G)^T, (k e^{G_C-G})^T, U0^T as [128][72], A_qk as [64][72], e^{G_C}.
 //  * kda_state_kernel  -- one CTA per (batch, head, V-slice), sequential over chunks: a producer warp
 //    bulk-copies the images of chunk c+1.. into a shared-memory ring while the compute warps hold their
 //    slice of S^T (16 V-rows x 128 K-columns per warp) in fp32 accumulator registers and chain the
@@ -26,23 +27,30 @@ namespace daisy {
 
 constexpr int KC = 64;                 // chunk length
 constexpr int KD = 128;                // K = V
-constexpr int LDW = 136;               // padded row (halves) of a [64 x 128] image
 constexpr int LDT = 72;                // padded row (halves) of a [. x 64] image
+constexpr int IMG_T = KD * LDT * 2;    // one [128][72] fp16 image: 18432 bytes
 // per-chunk record in the workspace (bytes)
-constexpr int OFF_W = 0;                               // W        [64][136] fp16
-constexpr int OFF_Q = OFF_W + KC * LDW * 2;            // q~       [64][136] fp16   (scale q e^G)
-constexpr int OFF_KT = OFF_Q + KC * LDW * 2;           // k~^T     [128][72] fp16   (k e^{G_C-G})^T
-constexpr int OFF_AQK = OFF_KT + KD * LDT * 2;         // A_qk     [64][72]  fp16
+constexpr int OFF_WT = 0;                              // W^T      [128][72] fp16
+constexpr int OFF_QT = OFF_WT + IMG_T;                 // q~^T     [128][72] fp16   (scale q e^G)^T
+constexpr int OFF_KT = OFF_QT + IMG_T;                 // k~^T     [128][72] fp16   (k e^{G_C-G})^T
+constexpr int OFF_AQK = OFF_KT + IMG_T;                // A_qk     [64][72]  fp16
 constexpr int OFF_D = OFF_AQK + KC * LDT * 2;          // e^{G_C}  [128]     fp32
-constexpr int SHARED_BYTES = OFF_D + KD * 4;           // 62976: identical for every V-slice
+constexpr int SHARED_BYTES = OFF_D + KD * 4;           // 65024: identical for every V-slice
 constexpr int OFF_UT = SHARED_BYTES;                   // U0^T     [128][72] fp16
-constexpr int REC_BYTES = OFF_UT + KD * LDT * 2;       // 81408
+constexpr int REC_BYTES = OFF_UT + IMG_T;              // 83456
+static_assert(SHARED_BYTES % 16 == 0 && REC_BYTES % 16 == 0, "bulk copies move 16-byte units");
 
 // Four 8x8 fp16 matrices from shared memory: lanes 8m..8m+7 give the row addresses of matrix m (16 bytes per
 // row); register m of lane l then holds elements (row l/4, columns 2(l%4), 2(l%4)+1) of matrix m -- the B
 // fragment layout of mma.m16n8k16 when the rows are the n index and the columns the k index.
 __device__ __forceinline__ void ldmatrix_x4(uint32_t* r, const void* row_ptr) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_u32(row_ptr)));
+}
+// The transposing form: register m of lane l holds elements (rows 2(l%4), 2(l%4)+1, column l/4) of matrix m --
+// the same B fragment when the stored rows are the k index and the columns the n index.
+__device__ __forceinline__ void ldmatrix_x4_t(uint32_t* r, const void* row_ptr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_u32(row_ptr)));
 }
 
@@ -63,492 +71,535 @@ __device__ __forceinline__ void bulk_g2s(void* smem_dst, const void* gsrc, uint3
   asm volatile("cp.async.bulk.shared::cta.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                ::"r"(smem_u32(smem_dst)), "l"(gsrc), "r"(bytes), "r"(smem_u32(bar)) : "memory");
 }
+__device__ __forceinline__ void st_global16(void* p, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+  asm volatile("st.global.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
 
 // =============================================================================================
 // intra-chunk kernel
 // =============================================================================================
+//
+// Gated Gram matrices without a single positive exponent.  e^{G_i - G_j} (i > j) is needed per channel inside the
+// contraction over channels, so it must factor into a row term times a column term, and neither term may overflow
+// whatever the gates are.  Pairs are split by the highest bit in which i and j differ ("level" s = 1, 2, .., 32):
+// tokens fall into aligned groups of 2s, i lies in the upper half of its group, j in the lower half.  With r the
+// last row of the lower half,  e^{G_i - G_j} = e^{G_i - G_r} * e^{G_r - G_j}:  the row factor is the product of the
+// per-token decays d_t = e^{g_t} <= 1 from the start of the upper half up to i, the column factor their product from
+// j + 1 to the end of the lower half.  Every factor is a running product of numbers <= 1 -- ONE exponential per
+// input element, no cumulative sum, and underflow is the correct limit.  A level is then one plain product
+//      [ k * f ; q * f ]  (128 x 128 channels)   x   (k * f)^T  (128 channels x 64)      f = the level's factor per token
+// whose entries at (i upper, j lower, same group) are that level's Gram entries (everything else is ignored): six
+// 128 x 64 x 128 tcgen05 products per chunk with fp16 operand images staged in shared memory and fp32
+// accumulators in TMEM.  The prefix / suffix products are carried from one level to the next with one multiply per
+// element; after the last level they are e^{G} and e^{G_C - G}, the decay factors of the state-pass operands.
 struct KdaIntraParams {
-  const __nv_bfloat16 *q, *k, *v;
-  const float *g, *beta;
+  const float* beta;
   uint8_t* ws;
   int T, H, NC;            // NC = chunks per sequence
-  int ahead;               // CTAs per wave: how far ahead (in launch order) a CTA prefetches
+  int total;               // work items: B * H * NC
   float scale;
   int l2norm;
+  int* status;
 };
 
-constexpr int LDA = 65;    // padded row (floats) of the fp32 [64 x 64] matrices
-constexpr int LDG = KD + 4;     // padded row (floats) of G: fragment gathers (8 rows x 4 column pairs) hit 32 banks
-constexpr int LDR = KD + 8;     // padded row (bf16) of the raw k / q tiles, same reason
-static_assert(KC * LDG * 4 <= 2 * KC * LDW * 2, "the decay image must fit under Mk + Mq");
-struct KdaIntraSmem {
-  float G[KC][LDG];                // cumulative log-decay; later the W staging image
-  __nv_bfloat16 kraw[KC][LDR];     // later (with qraw) the U0^T staging image
-  __nv_bfloat16 qraw[KC][LDR];
-  __nv_bfloat16 vraw[KC][KD];
-  float Akk[KC][LDA];              // beta * gated k k^T: the 16 x 16 diagonal blocks (fp32, for the exact block inverses)
-  __half Akh[KC][LDT];             //                     the off-diagonal blocks as tensor-core operands
-  __half Th[KC][LDT];              // T = (I + A_kk)^-1, row-major
-  __half ThT[KC][LDT];             // T^T
-  __half Aqk[KC][LDT];
-  __half Mk[KC][LDW];              // one level's Gram operands: k * e^{-|G - r|}   (Mk + Mq first hold e^g, fp32 [64][LDG])
-  __half Mq[KC][LDW];              //                             q * e^{-|G - r|} on upper rows, else 0
-  __half XT[KD][LDT];              // (beta k e^G)^T
-  __half YT[KD][LDT];              // (beta v)^T
-  float rq[KC], rk[KC], beta[KC];
+constexpr int KI_ELEM_WARPS = 16, KI_SOLVER_WARPS = 4;
+constexpr int KI_ELEM_THREADS = 32 * KI_ELEM_WARPS;                         // 512
+constexpr int KI_SOLVER_THREADS = 32 * KI_SOLVER_WARPS;                     // 128
+// 20 warps = 5 per scheduler: 96 registers per thread (a 21st warp would cut that to 80)
+constexpr int KI_THREADS = KI_ELEM_THREADS + KI_SOLVER_THREADS;             // 640
+constexpr int KI_IMG_BYTES = KD * KC * 2;                                   // one [128 channels][64 tokens] fp16 image: 16384
+constexpr int KI_IN_BYTES = KC * KD * 4 + 2 * KC * KD * 2;                  // g + q + k tiles: 65536
+constexpr int LDAKH = 72;
+
+struct __align__(1024) KdaIntraSmem {
+  uint8_t img[2][2 * KI_IMG_BYTES];      // level operand images, two sets of (k image, q image); 128-byte swizzle
+  uint8_t ximg[KI_IMG_BYTES];            // (k e^G)^T image: A operand of W^T
+  uint8_t vtile[KI_IMG_BYTES];           // v tile as TMA leaves it (two [64 tokens][64 columns] boxes): A operand of U0^T
+  uint8_t t16[KC * 128], thi[KC * 128], tlo[KC * 128];   // T diag(beta): fp16, and bf16 high / low parts
+  float g[KC][KD];                       // TMA destinations, plain rows
+  __nv_bfloat16 q[KC][KD];
+  __nv_bfloat16 k[KC][KD];
+  float akk[4][16][17];                  // beta * A_kk, the four diagonal 16 x 16 blocks in fp32
+  __half akh[KC][LDAKH];                 //              the whole lower triangle as fp16 operands
+  __half th[KC][LDT];                    // T = (I + A_kk)^-1, row-major
+  __half tht[KC][LDT];                   // T^T
+  float tot[4][KD];                      // product of the decays of each 16-token segment
+  float rq[2][KC], rk[2][KC], beta[2][KC], qkd[2][KC];   // per-token scalars, double-buffered by chunk parity
+  float sbeta[KC], sqkd[KC];             // the solver's own copies
+  uint64_t in_full, v_full, x_full, x_empty, w_full;
+  uint64_t img_full[2], img_empty[2], d_full[6], d_empty[6];
+  uint32_t tmem_base;
+  int abort_flag;
 };
+static_assert(sizeof(KdaIntraSmem) + 1024 <= 232448, "over the 227 KB a CTA may use");
 
-constexpr int KDA_INTRA_THREADS = 512;   // 16 warps: one 200 KB CTA per SM, so latency is hidden by warps, not by CTAs
+// byte offset of (row, 16-byte chunk) inside a 128-byte-swizzled image whose rows are 128 bytes
+__device__ __forceinline__ uint32_t sw128(int row, int chunk) {
+  return (uint32_t)((row >> 3) * 1024 + (row & 7) * 128 + (((chunk ^ row) & 7) << 4));
+}
 
-__global__ void __launch_bounds__(KDA_INTRA_THREADS, 1) kda_intra_kernel(const KdaIntraParams p) {
-  extern __shared__ __align__(128) uint8_t kda_smem_raw[];
-  KdaIntraSmem& sm = *reinterpret_cast<KdaIntraSmem*>(kda_smem_raw);
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g8 = lane >> 2, t4 = lane & 3;
-  const int chunk = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
-  const int t0 = chunk * KC;
-  const int rows = min(KC, p.T - t0);
-  uint8_t* rec = p.ws + ((size_t)(b * p.H + h) * p.NC + chunk) * REC_BYTES;
+__device__ __forceinline__ void ki_coords(int w, int NC, int H, int& b, int& h, int& chunk) {
+  chunk = w % NC;
+  const int bh = w / NC;
+  h = bh % H;
+  b = bh / H;
+}
 
-  // ---- P0: load the chunk (rows beyond T are zero: g = 0, beta = 0, q = k = v = 0).  All of a thread's
-  //           16-byte loads are issued before the first store so that ~20 are in flight per thread.
-  {
-    const size_t tok0 = ((size_t)b * p.T + t0) * p.H + h;          // token row index into [B,T,H,*]
-    uint4 rq_[2], rk_[2], rv_[2], rg_[4];
+// One level's operand images (this thread's 16 tokens of channel c) into the image set of the level's turn, then --
+// warp 0 only -- the level's Gram product once every element thread has delivered its share.
+__device__ __forceinline__ void ki_emit_level(KdaIntraSmem& sm, const float (&f)[16], const float (&kn)[16], const float (&qn)[16],
+                                              const bool write_q, const int c, const int seg, const int warp, const uint32_t leader,
+                                              const uint32_t ci, uint32_t& n_img, bool& ok, const uint32_t tmem_base,
+                                              const uint32_t g_lo0, const uint32_t g_hi, volatile int* abort_flag, int* status) {
+  constexpr uint32_t idesc_g = umma_idesc_f16(128, KC, 1, 1);                   // A and B both token-contiguous (MN-major)
+  const uint32_t set = n_img & 1, use = n_img >> 1;
+  if (use >= 1) ok = mbar_wait(&sm.img_empty[set], (use - 1) & 1, abort_flag, status, 2) && ok;
+  uint8_t* kimg = sm.img[set];
 #pragma unroll
-    for (int u = 0; u < 2; ++u) {                                  // 16-byte chunks of the bf16 tiles
-      const int idx = tid + u * KDA_INTRA_THREADS, r = idx >> 4, c8 = (idx & 15) * 8;
-      rq_[u] = rk_[u] = rv_[u] = make_uint4(0, 0, 0, 0);
-      if (r < rows) {
-        const size_t off = (tok0 + (size_t)r * p.H) * KD + c8;
-        rq_[u] = ld_stream16(p.q + off); rk_[u] = ld_stream16(p.k + off); rv_[u] = ld_stream16(p.v + off);
-      }
-    }
-#pragma unroll
-    for (int u = 0; u < 4; ++u) {                                  // 16-byte chunks of the fp32 gate tile
-      const int idx = tid + u * KDA_INTRA_THREADS, r = idx >> 5, c4 = (idx & 31) * 4;
-      rg_[u] = make_uint4(0, 0, 0, 0);
-      if (r < rows) rg_[u] = ld_stream16(p.g + (tok0 + (size_t)r * p.H) * KD + c4);
-    }
-    if (tid < KC) sm.beta[tid] = tid < rows ? p.beta[tok0 + (size_t)tid * p.H] : 0.f;
-    // Pull the inputs of the CTA that will run one wave from now into L2 (ten 128-byte lines per token row), so
-    // that its load phase, which nothing overlaps, pays L2 latency instead of HBM latency.
-    {
-      const long long lin = (long long)blockIdx.x + (long long)gridDim.x * (blockIdx.y + (long long)gridDim.y * blockIdx.z) + p.ahead;
-      const int nchunk = (int)(lin % p.NC), nh = (int)((lin / p.NC) % p.H);
-      const long long nb = lin / ((long long)p.NC * p.H);
-      for (int idx = tid; idx < KC * 10; idx += KDA_INTRA_THREADS) {
-        const int r = idx / 10, w = idx - r * 10;
-        const int t = nchunk * KC + r;
-        if (nb < (long long)gridDim.z && t < p.T) {
-          const size_t ntok = ((size_t)nb * p.T + t) * p.H + nh;
-          const void* a = w < 2 ? (const void*)(reinterpret_cast<const char*>(p.q + ntok * KD) + w * 128)
-                        : w < 4 ? (const void*)(reinterpret_cast<const char*>(p.k + ntok * KD) + (w - 2) * 128)
-                        : w < 6 ? (const void*)(reinterpret_cast<const char*>(p.v + ntok * KD) + (w - 4) * 128)
-                                : (const void*)(reinterpret_cast<const char*>(p.g + ntok * KD) + (w - 6) * 128);
-          asm volatile("prefetch.global.L2 [%0];" ::"l"(a));
-        }
-      }
-    }
-    for (int idx = tid; idx < KC * LDT / 2; idx += KDA_INTRA_THREADS) reinterpret_cast<uint32_t*>(&sm.Aqk[0][0])[idx] = 0u;
-#pragma unroll
-    for (int u = 0; u < 2; ++u) {
-      const int idx = tid + u * KDA_INTRA_THREADS, r = idx >> 4, c8 = (idx & 15) * 8;
-      *reinterpret_cast<uint4*>(&sm.qraw[r][c8]) = rq_[u];
-      *reinterpret_cast<uint4*>(&sm.kraw[r][c8]) = rk_[u];
-      *reinterpret_cast<uint4*>(&sm.vraw[r][c8]) = rv_[u];
-    }
-#pragma unroll
-    for (int u = 0; u < 4; ++u) {
-      const int idx = tid + u * KDA_INTRA_THREADS, r = idx >> 5, c4 = (idx & 31) * 4;
-      *reinterpret_cast<uint4*>(&sm.G[r][c4]) = rg_[u];
-      // per-token decays d = e^g <= 1 for the running products of P3; the image borrows the Mk / Mq buffers
-      // until the Gram levels need them
-      float (*dd)[LDG] = reinterpret_cast<float (*)[LDG]>(&sm.Mk[0][0]);
-      *reinterpret_cast<float4*>(&dd[r][c4]) = make_float4(__expf(__uint_as_float(rg_[u].x)), __expf(__uint_as_float(rg_[u].y)),
-                                                           __expf(__uint_as_float(rg_[u].z)), __expf(__uint_as_float(rg_[u].w)));
-    }
+  for (int e = 0; e < 2; ++e) {
+    const uint32_t off = sw128(c, 2 * seg + e);
+    *reinterpret_cast<uint4*>(kimg + off) =
+        make_uint4(pack_h2(kn[8 * e] * f[8 * e], kn[8 * e + 1] * f[8 * e + 1]), pack_h2(kn[8 * e + 2] * f[8 * e + 2], kn[8 * e + 3] * f[8 * e + 3]),
+                   pack_h2(kn[8 * e + 4] * f[8 * e + 4], kn[8 * e + 5] * f[8 * e + 5]), pack_h2(kn[8 * e + 6] * f[8 * e + 6], kn[8 * e + 7] * f[8 * e + 7]));
+    if (write_q)
+      *reinterpret_cast<uint4*>(kimg + KI_IMG_BYTES + off) =
+          make_uint4(pack_h2(qn[8 * e] * f[8 * e], qn[8 * e + 1] * f[8 * e + 1]), pack_h2(qn[8 * e + 2] * f[8 * e + 2], qn[8 * e + 3] * f[8 * e + 3]),
+                     pack_h2(qn[8 * e + 4] * f[8 * e + 4], qn[8 * e + 5] * f[8 * e + 5]), pack_h2(qn[8 * e + 6] * f[8 * e + 6], qn[8 * e + 7] * f[8 * e + 7]));
   }
+  fence_proxy_async();
+  mbar_arrive(&sm.img_full[set]);
+  if (warp == 0) {
+    const int li = (int)(n_img % 6u);
+    ok = mbar_wait(&sm.img_full[set], use & 1, abort_flag, status, 4) && ok;
+    if (ci >= 1) ok = mbar_wait(&sm.d_empty[li], (ci - 1) & 1, abort_flag, status, 5) && ok;
+    ok = __all_sync(0xffffffffu, ok);
+    if (ok) {
+      tc_fence_after();
+      const uint32_t lo = g_lo0 + set * ((2 * KI_IMG_BYTES) >> 4);
+#pragma unroll
+      for (int ks = 0; ks < KD / 16; ++ks)                                      // 16 channels = 16 rows of 128 bytes per step
+        umma_ss_lh_p(leader, tmem_base + 64 * li, lo + ks * (2048 >> 4), g_hi, lo + ks * (2048 >> 4), g_hi, idesc_g, ks > 0 ? 1u : 0u);
+    }
+    tc_commit_p(leader, &sm.img_empty[set]);                                    // arrives at once when nothing was issued
+    tc_commit_p(leader, &sm.d_full[li]);
+  }
+  ++n_img;
+}
+
+// Level S < 16: the factor of token i is pre[i] if bit S of i is set, else suf[i]; afterwards both products are carried
+// from aligned blocks of S to blocks of 2 S (upper block: prefix times the lower block's total; lower block: suffix
+// times the upper block's total).
+template <int S, typename Emit>
+__device__ __forceinline__ void ki_level_inreg(float (&pre)[16], float (&suf)[16], Emit& emit) {
+  float f[16];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) f[i] = (i & S) ? pre[i] : suf[i];
+  emit(f, true);
+#pragma unroll
+  for (int a = 0; a < 16; a += 2 * S) {
+    const float tot_l = pre[a + S - 1], tot_u = pre[a + 2 * S - 1];
+#pragma unroll
+    for (int i = 0; i < S; ++i) { pre[a + S + i] *= tot_l; suf[a + i] *= tot_u; }
+  }
+}
+
+__global__ void __launch_bounds__(KI_THREADS, 1)
+kda_intra_kernel(const __grid_constant__ CUtensorMap tm_g, const __grid_constant__ CUtensorMap tm_q,
+                 const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
+                 const KdaIntraParams p) {
+  extern __shared__ uint8_t kda_smem_raw[];
+  KdaIntraSmem& sm = *reinterpret_cast<KdaIntraSmem*>((reinterpret_cast<uintptr_t>(kda_smem_raw) + 1023) & ~uintptr_t(1023));
+  volatile int* abort_flag = &sm.abort_flag;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+
+  if (tid == 0) {
+    mbar_init(&sm.in_full, 1); mbar_init(&sm.v_full, 1);
+    mbar_init(&sm.x_full, KI_ELEM_THREADS); mbar_init(&sm.x_empty, 1); mbar_init(&sm.w_full, 1);
+    for (int i = 0; i < 2; ++i) { mbar_init(&sm.img_full[i], KI_ELEM_THREADS); mbar_init(&sm.img_empty[i], 1); }
+    for (int i = 0; i < 6; ++i) { mbar_init(&sm.d_full[i], 1); mbar_init(&sm.d_empty[i], KI_SOLVER_THREADS); }
+    sm.abort_flag = 0;
+    mbar_init_fence();
+  }
+  // the T images keep zeros above the diagonal for the whole launch: only the lower triangle is ever rewritten
+  for (int i = tid; i < 3 * KC * 128 / 16; i += KI_THREADS) reinterpret_cast<uint4*>(sm.t16)[i] = make_uint4(0, 0, 0, 0);
+  if (warp == 0) { tmem_alloc(&sm.tmem_base, 512); tmem_relinquish(); }
+  fence_proxy_async();
+  tc_fence_before();
   __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = sm.tmem_base;
 
-  // ---- P1: cumulative gates (threads 0-127, one channel each) and L2 norms (threads 128-383)
-  if (tid < KD) {
-    float acc = 0.f;
-#pragma unroll 8
-    for (int i = 0; i < KC; ++i) { acc += sm.G[i][tid]; sm.G[i][tid] = acc; }
-  } else if (tid < KD + 4 * KC) {
-    const int r = (tid - KD) >> 2, quarter = tid & 3;                // four threads per row, 32 channels each
-    float sq = 0.f, sk = 0.f, dqk = 0.f;
-#pragma unroll 8
-    for (int c = 0; c < 32; ++c) {
-      const float xq = __bfloat162float(sm.qraw[r][quarter * 32 + c]), xk = __bfloat162float(sm.kraw[r][quarter * 32 + c]);
-      sq = fmaf(xq, xq, sq); sk = fmaf(xk, xk, sk); dqk = fmaf(xq, xk, dqk);
+  if (warp < KI_ELEM_WARPS) {
+    // ================================================================== element warps
+    const int c = tid & (KD - 1), seg = tid >> 7;          // this thread's channel and 16-token segment (warp-uniform)
+    if (tid == 0 && (int)blockIdx.x < p.total) {
+      int b, h, chunk;
+      ki_coords(blockIdx.x, p.NC, p.H, b, h, chunk);
+      prefetch_tmap(&tm_g); prefetch_tmap(&tm_q); prefetch_tmap(&tm_k);
+      mbar_expect_tx(&sm.in_full, KI_IN_BYTES);
+      tma_load_4d(&sm.g[0][0], &tm_g, &sm.in_full, 0, chunk * KC, h, b);
+      tma_load_4d(&sm.q[0][0], &tm_q, &sm.in_full, 0, chunk * KC, h, b);
+      tma_load_4d(&sm.k[0][0], &tm_k, &sm.in_full, 0, chunk * KC, h, b);
     }
-#pragma unroll
-    for (int o = 1; o <= 2; o <<= 1) {
-      sq += __shfl_xor_sync(0xffffffffu, sq, o);
-      sk += __shfl_xor_sync(0xffffffffu, sk, o);
-      dqk += __shfl_xor_sync(0xffffffffu, dqk, o);
-    }
-    if (quarter == 0) {
-      const float a = p.l2norm ? rsqrtf(sq + 1e-6f) : 1.f, c = p.l2norm ? rsqrtf(sk + 1e-6f) : 1.f;
-      sm.rq[r] = a; sm.rk[r] = c;
-      sm.Aqk[r][r] = __float2half_rn(p.scale * a * c * dqk);         // diagonal of A_qk: q_i . k_i, no decay
-    }
-  }
-  __syncthreads();
+    // warp 0 doubles as the issuer of the Gram products: after its own share of a level's images it waits for
+    // everybody else's (all element warps do the same work in step, so the wait is short) and issues the product
+    const uint32_t leader = (warp == 0 && elect_one()) ? 1u : 0u;
+    const uint64_t gd0 = umma_desc_sw128(smem_u32(sm.img[0]), KI_IMG_BYTES, 1024);
+    const uint32_t g_lo0 = (uint32_t)gd0, g_hi = (uint32_t)(gd0 >> 32);
+    uint32_t ci = 0, n_img = 0;
+    bool ok = true;
+    for (int w = blockIdx.x; w < p.total; w += gridDim.x, ++ci) {
+      int b, h, chunk;
+      ki_coords(w, p.NC, p.H, b, h, chunk);
+      const int par = ci & 1;
+      const int t0 = chunk * KC;
+      uint8_t* rec = p.ws + (size_t)w * REC_BYTES;
+      ok = mbar_wait(&sm.in_full, ci & 1, abort_flag, p.status, 1) && ok;
 
-  // ---- P2: element-wise images: q~ and k~^T and e^{G_C} straight to the workspace, X^T and Y^T to smem
-  for (int idx = tid; idx < KC * 16; idx += KDA_INTRA_THREADS) {                 // q~[i][8 channels]
-    const int i = idx >> 4, c8 = (idx & 15) * 8;
-    const float rs = sm.rq[i] * p.scale;
-    float qf[8];
-    unpack8(*reinterpret_cast<const uint4*>(&sm.qraw[i][c8]), qf);
-    const float4 g0 = *reinterpret_cast<const float4*>(&sm.G[i][c8]), g1 = *reinterpret_cast<const float4*>(&sm.G[i][c8 + 4]);
-    const float gg[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
-    uint32_t o[4];
+      // ---- per-token scalars: 8 threads per row, 16 channels each
+      {
+        const int r = tid >> 3, part = tid & 7;
+        float qf[16], kf[16];
+        unpack8(*reinterpret_cast<const uint4*>(&sm.q[r][16 * part]), qf);
+        unpack8(*reinterpret_cast<const uint4*>(&sm.q[r][16 * part + 8]), qf + 8);
+        unpack8(*reinterpret_cast<const uint4*>(&sm.k[r][16 * part]), kf);
+        unpack8(*reinterpret_cast<const uint4*>(&sm.k[r][16 * part + 8]), kf + 8);
+        float sq = 0.f, sk = 0.f, dqk = 0.f;
 #pragma unroll
-    for (int e = 0; e < 8; e += 2) o[e >> 1] = pack_h2(qf[e] * rs * __expf(gg[e]), qf[e + 1] * rs * __expf(gg[e + 1]));
-    *reinterpret_cast<uint4*>(rec + OFF_Q + ((size_t)i * LDW + c8) * 2) = make_uint4(o[0], o[1], o[2], o[3]);
-  }
-  for (int idx = tid; idx < KD * 8; idx += KDA_INTRA_THREADS) {                  // (channel c, 8 tokens)
-    const int c = idx & (KD - 1), j8 = (idx >> 7) * 8;
-    const float gc = sm.G[KC - 1][c];
-    uint32_t kt[4], xt[4], yt[4];
+        for (int e = 0; e < 16; ++e) { sq = fmaf(qf[e], qf[e], sq); sk = fmaf(kf[e], kf[e], sk); dqk = fmaf(qf[e], kf[e], dqk); }
 #pragma unroll
-    for (int e = 0; e < 8; e += 2) {
-      float kv[2], xv[2], yv[2];
-#pragma unroll
-      for (int u = 0; u < 2; ++u) {
-        const int j = j8 + e + u;
-        const float kn = __bfloat162float(sm.kraw[j][c]) * sm.rk[j];
-        const float gj = sm.G[j][c];
-        kv[u] = kn * __expf(gc - gj);
-        xv[u] = kn * sm.beta[j] * __expf(gj);
-        yv[u] = __bfloat162float(sm.vraw[j][c]) * sm.beta[j];
+        for (int o = 1; o <= 4; o <<= 1) {
+          sq += __shfl_xor_sync(0xffffffffu, sq, o);
+          sk += __shfl_xor_sync(0xffffffffu, sk, o);
+          dqk += __shfl_xor_sync(0xffffffffu, dqk, o);
+        }
+        if (part == 0) {
+          const float a = p.l2norm ? rsqrtf(sq + 1e-6f) : 1.f, cc = p.l2norm ? rsqrtf(sk + 1e-6f) : 1.f;
+          sm.rq[par][r] = a; sm.rk[par][r] = cc; sm.qkd[par][r] = a * cc * dqk;
+        }
+        if (tid < KC) sm.beta[par][tid] = (t0 + tid < p.T) ? p.beta[((size_t)b * p.T + t0 + tid) * p.H + h] : 0.f;
       }
-      kt[e >> 1] = pack_h2(kv[0], kv[1]); xt[e >> 1] = pack_h2(xv[0], xv[1]); yt[e >> 1] = pack_h2(yv[0], yv[1]);
-    }
-    *reinterpret_cast<uint4*>(rec + OFF_KT + ((size_t)c * LDT + j8) * 2) = make_uint4(kt[0], kt[1], kt[2], kt[3]);
-    *reinterpret_cast<uint4*>(&sm.XT[c][j8]) = make_uint4(xt[0], xt[1], xt[2], xt[3]);
-    *reinterpret_cast<uint4*>(&sm.YT[c][j8]) = make_uint4(yt[0], yt[1], yt[2], yt[3]);
-    if (j8 == 0) reinterpret_cast<float*>(rec + OFF_D)[c] = __expf(gc);
-  }
+      if (named_bar_or(1, KI_ELEM_THREADS, !ok)) break;
 
-  // ---- P3: both gated Gram matrices.  e^{G_i - G_j} must never be formed from a positive exponent, whatever
-  // the gate values, so pairs are split by distance:
-  //  (a) pairs inside a 16-token block, on the FMA pipes with RUNNING PRODUCTS of the per-token decays
-  //      d_t = e^{g_t} <= 1:  k_j * prod_{t=j+1..i} d_t  is carried from row i-1 to row i with one multiply per
-  //      channel -- no exponential per pair at all;
-  //  (b) pairs in different blocks, on tensor cores by two binary levels s = 32, 16: tokens fall into groups of
-  //      2s, rows of a group's upper half pair with columns of its lower half.  With r = G at the last row of the
-  //      lower half, e^{G_i - G_j} = e^{G_i - r} * e^{r - G_j}, both exponents <= 0: each row carries ONE factor
-  //      e^{-|G_i - r|} per level, staged as fp16 operands Mk = k * factor (all rows), Mq = q * factor (upper
-  //      rows, else 0), and the level's blocks are plain m16n8k16 products.
-  {
-    // (a) a warp takes four columns j of one block over a range of rows, lane = four channels: row i of d, k, q is
-    //     read once per warp (512 + 256 + 256 contiguous bytes) and serves four columns from registers; the 2 x 4
-    //     partial dots of a row are reduced over the 32 lanes by a halving butterfly (9 shuffles for 8 values).
-    //     A column group's rows (15, 11, 7 or 3 of them) are cut into segments so that each of a block's four
-    //     warps walks nine rows -- the pass is bound by the dependent chain of one row after another, not by
-    //     issue slots.  A segment that does not begin at its columns' first row starts its running product from
-    //     e^{G_{start-1} - G_j} (exponent <= 0).  block = warp & 3: one block per scheduler.
-    {
-      const float (*dd)[LDG] = reinterpret_cast<const float (*)[LDG]>(&sm.Mk[0][0]);
-      const int blk = warp & 3, c0 = lane * 4;
-      int jq = 0;                                                  // column group of the segment being walked
-      float kp[4][4];                                              // k_j * running decay product, 4 columns x 4 channels
-      const bool hi16 = (lane & 16) != 0, hi8 = (lane & 8) != 0, hi4 = (lane & 4) != 0;
-      const int vsel = lane >> 2;                                  // after the butterfly: the value this lane holds
-      auto row = [&](const int i, const bool all_started) {
-        const int ii = blk * 16 + i, cc = jq * 4 + (vsel >> 1);
-        const float4 d4 = *reinterpret_cast<const float4*>(&dd[ii][c0]);
-        const uint2 kr = *reinterpret_cast<const uint2*>(&sm.kraw[ii][c0]);
-        const uint2 qr = *reinterpret_cast<const uint2*>(&sm.qraw[ii][c0]);
-        const float out_scale = (vsel & 1) ? p.scale * sm.rq[ii] : sm.beta[ii] * sm.rk[ii];
-        const float ki[4] = {__uint_as_float(kr.x << 16), __uint_as_float(kr.x & 0xffff0000u),
-                             __uint_as_float(kr.y << 16), __uint_as_float(kr.y & 0xffff0000u)};
-        const float qi[4] = {__uint_as_float(qr.x << 16), __uint_as_float(qr.x & 0xffff0000u),
-                             __uint_as_float(qr.y << 16), __uint_as_float(qr.y & 0xffff0000u)};
-        float val[8];                                              // [2 c] = k_i . kp_c, [2 c + 1] = q_i . kp_c
+      // ---- this thread's column of the chunk: 16 tokens of channel c
+      float pre[16], suf[16], kn[16], qn[16];
+      {
+        const int r0 = 16 * seg;
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          const bool on = all_started || i > jq * 4 + c;           // column c has started (warp-uniform)
-          kp[c][0] *= on ? d4.x : 1.f; kp[c][1] *= on ? d4.y : 1.f; kp[c][2] *= on ? d4.z : 1.f; kp[c][3] *= on ? d4.w : 1.f;
-          val[2 * c] = fmaf(ki[0], kp[c][0], ki[1] * kp[c][1]) + fmaf(ki[2], kp[c][2], ki[3] * kp[c][3]);
-          val[2 * c + 1] = fmaf(qi[0], kp[c][0], qi[1] * kp[c][1]) + fmaf(qi[2], kp[c][2], qi[3] * kp[c][3]);
+        for (int i = 0; i < 16; ++i) {
+          pre[i] = fast_exp2(sm.g[r0 + i][c] * 1.4426950408889634f);           // d_t = e^{g_t}
+          suf[i] = 1.f;
+          kn[i] = __bfloat162float(sm.k[r0 + i][c]) * sm.rk[par][r0 + i];
+          qn[i] = __bfloat162float(sm.q[r0 + i][c]) * sm.rq[par][r0 + i];
         }
-        float v4[4], v2[2], tot;
-#pragma unroll
-        for (int t = 0; t < 4; ++t) {
-          const float recv = __shfl_xor_sync(0xffffffffu, hi16 ? val[t] : val[t + 4], 16);
-          v4[t] = (hi16 ? val[t + 4] : val[t]) + recv;
-        }
-#pragma unroll
-        for (int t = 0; t < 2; ++t) {
-          const float recv = __shfl_xor_sync(0xffffffffu, hi8 ? v4[t] : v4[t + 2], 8);
-          v2[t] = (hi8 ? v4[t + 2] : v4[t]) + recv;
-        }
-        tot = (hi4 ? v2[1] : v2[0]) + __shfl_xor_sync(0xffffffffu, hi4 ? v2[0] : v2[1], 4);
-        tot += __shfl_xor_sync(0xffffffffu, tot, 2);
-        tot += __shfl_xor_sync(0xffffffffu, tot, 1);
-        // the lane now holds value number lane >> 2 of this row, summed over all channels
-        if ((lane & 3) == 0 && i > cc) {
-          if (vsel & 1) sm.Aqk[ii][blk * 16 + cc] = __float2half_rn(out_scale * tot);
-          else          sm.Akk[ii][blk * 16 + cc] = out_scale * tot;
-        }
+      }
+      named_bar(1, KI_ELEM_THREADS);                                            // every read of the input tiles is done
+      if (tid == 0 && w + (int)gridDim.x < p.total) {                           // next item's inputs land under this item's work
+        int nb, nh, nchunk;
+        ki_coords(w + gridDim.x, p.NC, p.H, nb, nh, nchunk);
+        mbar_expect_tx(&sm.in_full, KI_IN_BYTES);
+        tma_load_4d(&sm.g[0][0], &tm_g, &sm.in_full, 0, nchunk * KC, nh, nb);
+        tma_load_4d(&sm.q[0][0], &tm_q, &sm.in_full, 0, nchunk * KC, nh, nb);
+        tma_load_4d(&sm.k[0][0], &tm_k, &sm.in_full, 0, nchunk * KC, nh, nb);
+      }
+
+      // ---- six levels.  At level s token t is "upper" iff bit s of t is set; its factor is pre (upper) or suf (lower):
+      //      the inclusive prefix / exclusive suffix product of d inside the aligned s-block of t.
+      auto emit = [&](const float (&f)[16], const bool write_q) {
+        ki_emit_level(sm, f, kn, qn, write_q, c, seg, warp, leader, ci, n_img, ok, tmem_base, g_lo0, g_hi, abort_flag, p.status);
       };
-      auto segment = [&](const int q, const int r0, const int r1) {
-        jq = q;
-        const bool fresh = (r0 == q * 4 + 1);
+      // s = 1, 2, 4, 8: inside the segment (rows of lower tokens in the q image are never read back)
+      ki_level_inreg<1>(pre, suf, emit);
+      ki_level_inreg<2>(pre, suf, emit);
+      ki_level_inreg<4>(pre, suf, emit);
+      ki_level_inreg<8>(pre, suf, emit);
+      sm.tot[seg][c] = pre[15];
+      if (named_bar_or(1, KI_ELEM_THREADS, !ok)) break;
+      {                                                                         // s = 16: segments pair up
+        const bool up = (seg & 1) != 0;
+        float f[16];
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          const int jj = blk * 16 + q * 4 + c;
-          const float rkj = sm.rk[jj];
-          const uint2 kr = *reinterpret_cast<const uint2*>(&sm.kraw[jj][c0]);
-          float f[4] = {1.f, 1.f, 1.f, 1.f};
-          if (!fresh) {
-            const float4 ga = *reinterpret_cast<const float4*>(&sm.G[blk * 16 + r0 - 1][c0]);
-            const float4 gj = *reinterpret_cast<const float4*>(&sm.G[jj][c0]);
-            f[0] = __expf(ga.x - gj.x); f[1] = __expf(ga.y - gj.y); f[2] = __expf(ga.z - gj.z); f[3] = __expf(ga.w - gj.w);
-          }
-          kp[c][0] = __uint_as_float(kr.x << 16) * rkj * f[0]; kp[c][1] = __uint_as_float(kr.x & 0xffff0000u) * rkj * f[1];
-          kp[c][2] = __uint_as_float(kr.y << 16) * rkj * f[2]; kp[c][3] = __uint_as_float(kr.y & 0xffff0000u) * rkj * f[3];
-        }
-        if (fresh) {                                               // the first three rows see only some of the columns
-          for (int i = r0; i < r0 + 3 && i < r1; ++i) row(i, false);
-#pragma unroll 2
-          for (int i = r0 + 3; i < r1; ++i) row(i, true);
+        for (int i = 0; i < 16; ++i) f[i] = up ? pre[i] : suf[i];
+        emit(f, up);
+        const float m = sm.tot[seg ^ 1][c];
+        if (seg & 1) {
+#pragma unroll
+          for (int i = 0; i < 16; ++i) pre[i] *= m;
         } else {
-#pragma unroll 2
-          for (int i = r0; i < r1; ++i) row(i, true);
+#pragma unroll
+          for (int i = 0; i < 16; ++i) suf[i] *= m;
         }
-      };
-      switch (warp >> 2) {                                         // nine rows per warp
-        case 0:  segment(0, 1, 10); break;
-        case 1:  segment(0, 10, 16); segment(3, 13, 16); break;
-        case 2:  segment(1, 5, 14); break;
-        default: segment(1, 14, 16); segment(2, 9, 16); break;
       }
-    }
-    // (b) build mapping: lanes 0-7 of a warp take 8 consecutive rows at the same channels, so every 8-lane phase of
-    // a 16-byte shared-memory access spreads over all banks (row strides are 4 banks apart).  Two warps share
-    // eight rows; a thread owns channels bq + 64 k .. + 8 (k = 0, 1).
-    const int brow = (warp >> 1) * 8 + (lane & 7), bq = ((lane >> 3) + 4 * (warp & 1)) * 8;
-    // this thread's 16 normalised k and q values and cumulative gates stay in registers across the levels
-    float kn[16], qn[16], gi[16];
-    {
-      const float rkb = sm.rk[brow], rqb = sm.rq[brow];
+      {                                                                         // s = 32: halves of the chunk
+        const bool up = (seg & 2) != 0;
+        float f[16];
 #pragma unroll
-      for (int kq = 0; kq < 2; ++kq) {
-        const int c = bq + 64 * kq;
-        float kf[8], qf[8];
-        unpack8(*reinterpret_cast<const uint4*>(&sm.kraw[brow][c]), kf);
-        unpack8(*reinterpret_cast<const uint4*>(&sm.qraw[brow][c]), qf);
-        const float4 g0 = *reinterpret_cast<const float4*>(&sm.G[brow][c]);
-        const float4 g1 = *reinterpret_cast<const float4*>(&sm.G[brow][c + 4]);
-        const float gg[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+        for (int i = 0; i < 16; ++i) f[i] = up ? pre[i] : suf[i];
+        emit(f, up);
+        const float m = (seg & 2) ? sm.tot[0][c] * sm.tot[1][c] : sm.tot[2][c] * sm.tot[3][c];
+        if (seg & 2) {
 #pragma unroll
-        for (int e = 0; e < 8; ++e) { kn[8 * kq + e] = kf[e] * rkb; qn[8 * kq + e] = qf[e] * rqb; gi[8 * kq + e] = gg[e]; }
+          for (int i = 0; i < 16; ++i) pre[i] *= m;
+        } else {
+#pragma unroll
+          for (int i = 0; i < 16; ++i) suf[i] *= m;
+        }
       }
+      // ---- pre = e^{G}, suf = e^{G_C - G}: the state-pass operands
+      if (ci >= 1) ok = mbar_wait(&sm.x_empty, (ci - 1) & 1, abort_flag, p.status, 3) && ok;
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        float x[8], qt[8], kt[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          x[i] = kn[8 * e + i] * pre[8 * e + i];
+          qt[i] = qn[8 * e + i] * pre[8 * e + i] * p.scale;
+          kt[i] = kn[8 * e + i] * suf[8 * e + i];
+        }
+        *reinterpret_cast<uint4*>(sm.ximg + sw128(c, 2 * seg + e)) =
+            make_uint4(pack_h2(x[0], x[1]), pack_h2(x[2], x[3]), pack_h2(x[4], x[5]), pack_h2(x[6], x[7]));
+        const size_t goff = ((size_t)c * LDT + 16 * seg + 8 * e) * 2;
+        st_global16(rec + OFF_QT + goff, pack_h2(qt[0], qt[1]), pack_h2(qt[2], qt[3]), pack_h2(qt[4], qt[5]), pack_h2(qt[6], qt[7]));
+        st_global16(rec + OFF_KT + goff, pack_h2(kt[0], kt[1]), pack_h2(kt[2], kt[3]), pack_h2(kt[4], kt[5]), pack_h2(kt[6], kt[7]));
+      }
+      if (seg == 3) reinterpret_cast<float*>(rec + OFF_D)[c] = pre[15];         // e^{G_C}
+      fence_proxy_async();
+      mbar_arrive(&sm.x_full);
     }
-    __syncthreads();                                                 // (a) is done with the decay image under Mk / Mq
-#pragma unroll 1
-    for (int ls = 5; ls >= 4; --ls) {
-      const int s = 1 << ls;
-      // -- build the level's operands
+  } else {
+    // ================================================================== solver warps
+    const int ws = warp - KI_ELEM_WARPS, st = tid - KI_ELEM_THREADS;            // 0..3, 0..127
+    const int g8 = lane >> 2, t4 = lane & 3;
+    const bool is_qk = ws >= 2;                                                 // TMEM lanes 0-63: k rows, 64-127: q rows
+    const int hb = ws & 1;                                                      // which 32-token half this warp's rows are in
+    const int row = 32 * hb + lane;
+    const uint32_t lane_base = tmem_base + ((uint32_t)(32 * ws) << 16);
+    if (st == 0 && (int)blockIdx.x < p.total) {
+      int b, h, chunk;
+      ki_coords(blockIdx.x, p.NC, p.H, b, h, chunk);
+      prefetch_tmap(&tm_v);
+      mbar_expect_tx(&sm.v_full, KI_IMG_BYTES);
+      tma_load_4d(sm.vtile, &tm_v, &sm.v_full, 0, chunk * KC, h, b);
+      tma_load_4d(sm.vtile + KI_IMG_BYTES / 2, &tm_v, &sm.v_full, 64, chunk * KC, h, b);
+    }
+    uint32_t ci = 0;
+    bool ok = true;
+    for (int w = blockIdx.x; w < p.total; w += gridDim.x, ++ci) {
+      const int par = ci & 1;
+      uint8_t* rec = p.ws + (size_t)w * REC_BYTES;
+      // ---- Gram entries out of TMEM.  acc[j] collects row `row`, columns 32 hb + j, level by level: the entry of
+      //      (row, column) lives in the level of the highest bit in which the two token indices differ.
+      float acc[32];
+#pragma unroll
+      for (int j = 0; j < 32; ++j) acc[j] = 0.f;
+      float my_beta = 0.f, my_qkd = 0.f;
+      for (int li = 0; li < 6; ++li) {
+        ok = __all_sync(0xffffffffu, mbar_wait(&sm.d_full[li], ci & 1, abort_flag, p.status, 6)) && ok;
+        if (li == 0) {                                                          // the item's scalars are final once its first image exists
+          if (st < KC) { sm.sbeta[st] = sm.beta[par][st]; sm.sqkd[st] = sm.qkd[par][st]; }
+          my_beta = sm.beta[par][row]; my_qkd = sm.qkd[par][row];
+        }
+        tc_fence_after();
+        uint32_t r[32];
+        if (li < 5) {
+          tmem_ld32(lane_base + 64 * li + 32 * hb, r);
+          tc_wait_ld();
+#pragma unroll
+          for (int j = 0; j < 32; ++j)
+            if ((((uint32_t)lane ^ (uint32_t)j) >> li) == 1u) acc[j] = __uint_as_float(r[j]);
+        } else if (hb == 1) {                                                   // s = 32: rows 32..63 against columns 0..31, all of them
+          tmem_ld32(lane_base + 64 * 5, r);
+          tc_wait_ld();
+          const float sc = is_qk ? p.scale : my_beta;
+          if (is_qk) {
+            uint8_t* dst = rec + OFF_AQK + (size_t)row * LDT * 2;
+#pragma unroll
+            for (int j = 0; j < 32; j += 8)
+              st_global16(dst + j * 2, pack_h2(sc * __uint_as_float(r[j]), sc * __uint_as_float(r[j + 1])),
+                          pack_h2(sc * __uint_as_float(r[j + 2]), sc * __uint_as_float(r[j + 3])),
+                          pack_h2(sc * __uint_as_float(r[j + 4]), sc * __uint_as_float(r[j + 5])),
+                          pack_h2(sc * __uint_as_float(r[j + 6]), sc * __uint_as_float(r[j + 7])));
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; j += 2)
+              *reinterpret_cast<uint32_t*>(&sm.akh[row][j]) = pack_h2(sc * __uint_as_float(r[j]), sc * __uint_as_float(r[j + 1]));
+          }
+        }
+        tc_fence_before();
+        mbar_arrive(&sm.d_empty[li]);
+      }
       {
-        const bool upper = (brow & s) != 0;
-        const int ref = (brow & ~(2 * s - 1)) + s - 1;
+        const float sc = is_qk ? p.scale : my_beta;
+        float v[32];
 #pragma unroll
-        for (int kq = 0; kq < 2; ++kq) {
-          const int c = bq + 64 * kq;
-          const float4 r0 = *reinterpret_cast<const float4*>(&sm.G[ref][c]);
-          const float4 r1 = *reinterpret_cast<const float4*>(&sm.G[ref][c + 4]);
-          const float gr[8] = {r0.x, r0.y, r0.z, r0.w, r1.x, r1.y, r1.z, r1.w};
-          uint32_t mk[4], mq[4];
+        for (int j = 0; j < 32; ++j) v[j] = (j < lane) ? sc * acc[j] : 0.f;
+        if (is_qk) {
 #pragma unroll
-          for (int e = 0; e < 8; e += 2) {
-            const float f0 = __expf(-fabsf(gi[8 * kq + e] - gr[e])), f1 = __expf(-fabsf(gi[8 * kq + e + 1] - gr[e + 1]));
-            mk[e >> 1] = pack_h2(kn[8 * kq + e] * f0, kn[8 * kq + e + 1] * f1);
-            mq[e >> 1] = upper ? pack_h2(qn[8 * kq + e] * f0, qn[8 * kq + e + 1] * f1) : 0u;
-          }
-          *reinterpret_cast<uint4*>(&sm.Mk[brow][c]) = make_uint4(mk[0], mk[1], mk[2], mk[3]);
-          *reinterpret_cast<uint4*>(&sm.Mq[brow][c]) = make_uint4(mq[0], mq[1], mq[2], mq[3]);
+          for (int j = 0; j < 32; ++j) if (j == lane) v[j] = p.scale * my_qkd;  // the diagonal: q_i . k_i, no decay
+          uint8_t* dst = rec + OFF_AQK + ((size_t)row * LDT + 32 * hb) * 2;
+#pragma unroll
+          for (int j = 0; j < 32; j += 8)
+            st_global16(dst + j * 2, pack_h2(v[j], v[j + 1]), pack_h2(v[j + 2], v[j + 3]), pack_h2(v[j + 4], v[j + 5]), pack_h2(v[j + 6], v[j + 7]));
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; j += 2) *reinterpret_cast<uint32_t*>(&sm.akh[row][32 * hb + j]) = pack_h2(v[j], v[j + 1]);
+          const int blk = row >> 4, jb = lane & 16;                              // the row's diagonal 16 x 16 block, in fp32
+#pragma unroll
+          for (int j = 0; j < 32; ++j)
+            if ((j & 16) == jb) sm.akk[blk][row & 15][j & 15] = v[j];
         }
       }
-      __syncthreads();
-      // -- the level's blocks, one 16 x 8 tile per warp.  Level 32: rows 32-63 x columns 0-31, eight tiles per
-      //    matrix, all 16 warps (warp -> tile w & 7, matrix w >> 3).  Level 16: rows 16-31 x columns 0-15 and rows
-      //    48-63 x columns 32-47, four tiles per matrix, warps 0-7 (tile w & 3, matrix w >> 2).
-      {
-        int mrow, ncol0;
-        const int which = (s == 32) ? (warp >> 3) : ((warp >> 2) & 1);      // 0 = A_kk, 1 = A_qk
-        const bool active = (s == 32) || warp < 8;
-        if (s == 32) { const int c = warp & 7; mrow = 32 + 16 * (c >> 2); ncol0 = 8 * (c & 3); }
-        else { const int c = warp & 3; mrow = 16 + 32 * (c >> 1); ncol0 = 32 * (c >> 1) + 8 * (c & 1); }
-        if (active) {
-          float acc[4] = {0.f, 0.f, 0.f, 0.f}, acc2[4] = {0.f, 0.f, 0.f, 0.f};   // two independent chains
-          const int i0 = mrow + g8, i1 = i0 + 8;
-          // all fragments first (independent shared-memory loads), then the products
-          uint32_t bf[KD / 16][2], af[KD / 16][4];
-          const __half* abase = (which == 1) ? &sm.Mq[0][0] : &sm.Mk[0][0];
-          // ldmatrix.x4: the four 8x8 pieces of a 16x16 A fragment; two k-steps of an 8-column B fragment
-          const __half* aptr = abase + (mrow + (lane & 7) + ((lane >> 3) & 1) * 8) * LDW + (lane >> 4) * 8;
-          const __half* bptr = &sm.Mk[ncol0 + (lane & 7)][(lane >> 3) * 8];
-#pragma unroll
-          for (int ks = 0; ks < KD / 16; ++ks) ldmatrix_x4(af[ks], aptr + ks * 16);
-#pragma unroll
-          for (int ks = 0; ks < KD / 16; ks += 2) {
-            uint32_t b4[4];
-            ldmatrix_x4(b4, bptr + ks * 16);
-            bf[ks][0] = b4[0]; bf[ks][1] = b4[1]; bf[ks + 1][0] = b4[2]; bf[ks + 1][1] = b4[3];
-          }
-#pragma unroll
-          for (int ks = 0; ks < KD / 16; ks += 2) {
-            mma_f16(acc, af[ks], bf[ks][0], bf[ks][1]);
-            mma_f16(acc2, af[ks + 1], bf[ks + 1][0], bf[ks + 1][1]);
-          }
-          // outputs: rows i0 (acc[0], acc[1]) and i1 (acc[2], acc[3]), columns ncol0 + 2 t4 (+1)
-#pragma unroll
-          for (int x = 0; x < 4; ++x) {
-            const int i = (x < 2) ? i0 : i1, jc = ncol0 + 2 * t4 + (x & 1);
-            const float a = acc[x] + acc2[x];
-            if (which == 0) sm.Akh[i][jc] = __float2half_rn(sm.beta[i] * a);
-            else            sm.Aqk[i][jc] = __float2half_rn(p.scale * a);
-          }
-        }
-      }
-      __syncthreads();
-    }
-  }
+      if (named_bar_or(2, KI_SOLVER_THREADS, !ok)) break;
 
-  // ---- P4: T = (I + A_kk)^-1.  (a) the four 16x16 diagonal blocks by forward substitution in fp32
-  if (warp < 4 && lane < 16) {
-    const int base = warp * 16;
-    float t[16];
+      // ---- T = (I + A_kk)^-1.  (a) the four 16x16 diagonal blocks by forward substitution in fp32
+      if (lane < 16) {
+        float t[16];
 #pragma unroll
-    for (int i = 0; i < 16; ++i) {
-      float s = (i == lane) ? 1.f : 0.f;
+        for (int i = 0; i < 16; ++i) {
+          float s = (i == lane) ? 1.f : 0.f;
 #pragma unroll
-      for (int j = 0; j < i; ++j) s = fmaf(-sm.Akk[base + i][base + j], t[j], s);
-      t[i] = s;
-    }
+          for (int j = 0; j < i; ++j) s = fmaf(-sm.akk[ws][i][j], t[j], s);
+          t[i] = s;
+        }
+        const int base = ws * 16;
 #pragma unroll
-    for (int i = 0; i < 16; ++i) {                                 // t[i] = T[base + i][base + lane]
-      const __half th = __float2half_rn(t[i]);
-      sm.Th[base + i][base + lane] = th;
-      sm.ThT[base + lane][base + i] = th;
-    }
-  }
-  __syncthreads();
-  //      (b) block rows I = 1..3 on tensor cores, in transposed form so that the two products chain through
-  //          registers:  R = T^T,  R_{<I,I} = -(R_{<I,<I} A_{I,<I}^T) R_II.  Warp mt < I owns 16 rows of R_{<I,I};
-  //          the first product's accumulator pair is the second product's A fragment.  fp16 operands here cost
-  //          nothing measurable: T is consumed as fp16 by every later product anyway.
+        for (int i = 0; i < 16; ++i) {                                 // t[i] = T[base + i][base + lane]
+          const __half thv = __float2half_rn(t[i]);
+          sm.th[base + i][base + lane] = thv;
+          sm.tht[base + lane][base + i] = thv;
+        }
+      }
+      named_bar(2, KI_SOLVER_THREADS);
+      //      (b) block rows I = 1..3 on tensor cores, in transposed form so that the two products chain through
+      //          registers:  R = T^T,  R_{<I,I} = -(R_{<I,<I} A_{I,<I}^T) R_II.  Warp mt < I owns 16 rows of R_{<I,I};
+      //          the first product's accumulator pair is the second product's A fragment.
 #pragma unroll 1
-  for (int I = 1; I < 4; ++I) {
-    if (warp < I) {
-      const int mt = warp;
-      float acc1[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
-      for (int kb = mt; kb < I; ++kb) {                            // R is block upper triangular
-        uint32_t a[4];
-        const int kc = kb * 16 + 2 * t4;
-        a[0] = *reinterpret_cast<const uint32_t*>(&sm.ThT[mt * 16 + g8][kc]);
-        a[1] = *reinterpret_cast<const uint32_t*>(&sm.ThT[mt * 16 + g8 + 8][kc]);
-        a[2] = *reinterpret_cast<const uint32_t*>(&sm.ThT[mt * 16 + g8][kc + 8]);
-        a[3] = *reinterpret_cast<const uint32_t*>(&sm.ThT[mt * 16 + g8 + 8][kc + 8]);
+      for (int I = 1; I < 4; ++I) {
+        if (ws < I) {
+          const int mt = ws;
+          float acc1[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+          for (int kb = mt; kb < I; ++kb) {                            // R is block upper triangular
+            uint32_t a[4];
+            const int kc = kb * 16 + 2 * t4;
+            a[0] = *reinterpret_cast<const uint32_t*>(&sm.tht[mt * 16 + g8][kc]);
+            a[1] = *reinterpret_cast<const uint32_t*>(&sm.tht[mt * 16 + g8 + 8][kc]);
+            a[2] = *reinterpret_cast<const uint32_t*>(&sm.tht[mt * 16 + g8][kc + 8]);
+            a[3] = *reinterpret_cast<const uint32_t*>(&sm.tht[mt * 16 + g8 + 8][kc + 8]);
 #pragma unroll
-        for (int nn = 0; nn < 2; ++nn) {
-          const __half* arow = &sm.Akh[I * 16 + nn * 8 + g8][kc];
-          mma_f16(acc1[nn], a, *reinterpret_cast<const uint32_t*>(arow), *reinterpret_cast<const uint32_t*>(arow + 8));
+            for (int nn = 0; nn < 2; ++nn) {
+              const __half* arow = &sm.akh[I * 16 + nn * 8 + g8][kc];
+              mma_f16(acc1[nn], a, *reinterpret_cast<const uint32_t*>(arow), *reinterpret_cast<const uint32_t*>(arow + 8));
+            }
+          }
+          uint32_t a2[4];
+          a2[0] = pack_h2(acc1[0][0], acc1[0][1]); a2[1] = pack_h2(acc1[0][2], acc1[0][3]);
+          a2[2] = pack_h2(acc1[1][0], acc1[1][1]); a2[3] = pack_h2(acc1[1][2], acc1[1][3]);
+#pragma unroll
+          for (int nn = 0; nn < 2; ++nn) {
+            float acc2[4] = {0.f, 0.f, 0.f, 0.f};
+            const __half* trow = &sm.th[I * 16 + nn * 8 + g8][I * 16 + 2 * t4];
+            mma_f16(acc2, a2, *reinterpret_cast<const uint32_t*>(trow), *reinterpret_cast<const uint32_t*>(trow + 8));
+            // acc2[0..1] = R[mt*16 + g8][nn*8 + 2 t4 (+1)], acc2[2..3] the same for row g8 + 8;  T[i][j] = -R[j][i]
+            const int ti = I * 16 + nn * 8 + 2 * t4, tj = mt * 16 + g8;
+            const __half h0 = __float2half_rn(-acc2[0]), h1 = __float2half_rn(-acc2[1]);
+            const __half h2 = __float2half_rn(-acc2[2]), h3 = __float2half_rn(-acc2[3]);
+            sm.th[ti][tj] = h0; sm.th[ti + 1][tj] = h1; sm.th[ti][tj + 8] = h2; sm.th[ti + 1][tj + 8] = h3;
+            *reinterpret_cast<__half2*>(&sm.tht[tj][ti]) = __halves2half2(h0, h1);
+            *reinterpret_cast<__half2*>(&sm.tht[tj + 8][ti]) = __halves2half2(h2, h3);
+          }
+        }
+        named_bar(2, KI_SOLVER_THREADS);
+      }
+      // ---- operand images of T diag(beta) (lower triangle; everything above stays zero): fp16 for W^T, and a
+      //      bf16 high + low pair for U0^T, whose other operand is the bf16 v tile as it came from memory
+      {
+        const int i = st >> 1, j0 = (st & 1) * 32;
+#pragma unroll
+        for (int ch = 0; ch < 4; ++ch) {
+          const int j = j0 + 8 * ch;
+          if (j > i) continue;
+          float tv[8];
+          const uint4 raw = *reinterpret_cast<const uint4*>(&sm.th[i][j]);
+          const float2 a0 = unpack_h2(raw.x), a1 = unpack_h2(raw.y), a2 = unpack_h2(raw.z), a3 = unpack_h2(raw.w);
+          tv[0] = a0.x; tv[1] = a0.y; tv[2] = a1.x; tv[3] = a1.y; tv[4] = a2.x; tv[5] = a2.y; tv[6] = a3.x; tv[7] = a3.y;
+          float hi_[8], lo_[8];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            tv[e] = (j + e <= i) ? tv[e] * sm.sbeta[j + e] : 0.f;
+            hi_[e] = __bfloat162float(__float2bfloat16_rn(tv[e]));
+            lo_[e] = tv[e] - hi_[e];
+          }
+          const uint32_t off = sw128(i, j >> 3);
+          *reinterpret_cast<uint4*>(sm.t16 + off) = make_uint4(pack_h2(tv[0], tv[1]), pack_h2(tv[2], tv[3]), pack_h2(tv[4], tv[5]), pack_h2(tv[6], tv[7]));
+          *reinterpret_cast<uint4*>(sm.thi + off) = pack8(hi_);
+          *reinterpret_cast<uint4*>(sm.tlo + off) = pack8(lo_);
         }
       }
-      uint32_t a2[4];
-      a2[0] = pack_h2(acc1[0][0], acc1[0][1]); a2[1] = pack_h2(acc1[0][2], acc1[0][3]);
-      a2[2] = pack_h2(acc1[1][0], acc1[1][1]); a2[3] = pack_h2(acc1[1][2], acc1[1][3]);
+      fence_proxy_async();
+      if (named_bar_or(2, KI_SOLVER_THREADS, !ok)) break;
+      // ---- W^T = (k e^G)^T (T diag beta)^T  and  U0^T = v^T (T diag beta)^T, one thread issues both
+      if (st == 0) {
+        bool go = mbar_wait(&sm.x_full, ci & 1, abort_flag, p.status, 7);
+        go = go && mbar_wait(&sm.v_full, ci & 1, abort_flag, p.status, 8);
+        if (go) {
+          tc_fence_after();
+          constexpr uint32_t idesc_w = umma_idesc_f16(128, KC, 0, 0);
+          constexpr uint32_t idesc_u = umma_idesc_bf16(128, KC, 1, 0);
+          const uint32_t xa = smem_u32(sm.ximg), va = smem_u32(sm.vtile);
 #pragma unroll
-      for (int nn = 0; nn < 2; ++nn) {
-        float acc2[4] = {0.f, 0.f, 0.f, 0.f};
-        const __half* trow = &sm.Th[I * 16 + nn * 8 + g8][I * 16 + 2 * t4];
-        mma_f16(acc2, a2, *reinterpret_cast<const uint32_t*>(trow), *reinterpret_cast<const uint32_t*>(trow + 8));
-        // acc2[0..1] = R[mt*16 + g8][nn*8 + 2 t4 (+1)], acc2[2..3] the same for row g8 + 8;  T[i][j] = -R[j][i]
-        const int ti = I * 16 + nn * 8 + 2 * t4, tj = mt * 16 + g8;
-        const __half h0 = __float2half_rn(-acc2[0]), h1 = __float2half_rn(-acc2[1]);
-        const __half h2 = __float2half_rn(-acc2[2]), h3 = __float2half_rn(-acc2[3]);
-        sm.Th[ti][tj] = h0; sm.Th[ti + 1][tj] = h1; sm.Th[ti][tj + 8] = h2; sm.Th[ti + 1][tj + 8] = h3;
-        *reinterpret_cast<__half2*>(&sm.ThT[tj][ti]) = __halves2half2(h0, h1);
-        *reinterpret_cast<__half2*>(&sm.ThT[tj + 8][ti]) = __halves2half2(h2, h3);
+          for (int ks = 0; ks < KC / 16; ++ks)
+            umma_ss(tmem_base + 384, umma_desc_sw128(xa + 32 * ks, 16, 1024), umma_desc_sw128(smem_u32(sm.t16) + 32 * ks, 16, 1024), idesc_w, ks > 0);
+#pragma unroll
+          for (int ks = 0; ks < KC / 16; ++ks) {
+            const uint64_t ad = umma_desc_sw128(va + 2048 * ks, KI_IMG_BYTES / 2, 1024);
+            umma_ss(tmem_base + 448, ad, umma_desc_sw128(smem_u32(sm.thi) + 32 * ks, 16, 1024), idesc_u, ks > 0);
+            umma_ss(tmem_base + 448, ad, umma_desc_sw128(smem_u32(sm.tlo) + 32 * ks, 16, 1024), idesc_u, 1u);
+          }
+        }
+        tc_commit(&sm.w_full);                                       // also arrives when nothing was issued, so no one is left waiting
+      }
+      ok = __all_sync(0xffffffffu, mbar_wait(&sm.w_full, ci & 1, abort_flag, p.status, 9)) && ok;
+      if (ok) {
+        tc_fence_after();
+        // lane = channel of W^T / value column of U0^T: one 128-byte row each
+#pragma unroll
+        for (int which = 0; which < 2; ++which) {
+          uint8_t* dst = rec + (which ? OFF_UT : OFF_WT) + (size_t)(32 * ws + lane) * LDT * 2;
+#pragma unroll
+          for (int half = 0; half < 2; ++half) {
+            uint32_t r[32];
+            tmem_ld32(lane_base + 384 + 64 * which + 32 * half, r);
+            tc_wait_ld();
+#pragma unroll
+            for (int j = 0; j < 32; j += 8)
+              st_global16(dst + (32 * half + j) * 2,
+                          pack_h2(__uint_as_float(r[j]), __uint_as_float(r[j + 1])), pack_h2(__uint_as_float(r[j + 2]), __uint_as_float(r[j + 3])),
+                          pack_h2(__uint_as_float(r[j + 4]), __uint_as_float(r[j + 5])), pack_h2(__uint_as_float(r[j + 6]), __uint_as_float(r[j + 7])));
+          }
+        }
+        tc_fence_before();
+      }
+      if (named_bar_or(2, KI_SOLVER_THREADS, !ok)) break;                      // every lane has read the two accumulators
+      if (st == 0) {
+        mbar_arrive(&sm.x_empty);                                               // the k e^G image and the v tile are free again
+        if (w + (int)gridDim.x < p.total) {
+          int nb, nh, nchunk;
+          ki_coords(w + gridDim.x, p.NC, p.H, nb, nh, nchunk);
+          mbar_expect_tx(&sm.v_full, KI_IMG_BYTES);
+          tma_load_4d(sm.vtile, &tm_v, &sm.v_full, 0, nchunk * KC, nh, nb);
+          tma_load_4d(sm.vtile + KI_IMG_BYTES / 2, &tm_v, &sm.v_full, 64, nchunk * KC, nh, nb);
+        }
       }
     }
-    __syncthreads();
   }
 
-  // ---- P5: W = T X  (warp = row block I x channel quarter) and U0^T = Y^T T^T (warp = 16 V rows x token half), fp16 MMAs.
-  //          G and kraw/qraw are dead: they become the staging images.
-  __half* w_img = reinterpret_cast<__half*>(&sm.G[0][0]);          // [64][136]
-  __half* u_img = reinterpret_cast<__half*>(&sm.kraw[0][0]);       // [128][72]  (kraw + qraw = 32 KB)
-  {
-    const int I = warp >> 2, ch = (warp & 3) * 32;
-    float acc[4][4];
-#pragma unroll
-    for (int nt = 0; nt < 4; ++nt) { acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f; }
-    const int i0 = I * 16 + g8, i1 = i0 + 8;
-    for (int ks = 0; ks <= I; ++ks) {
-      uint32_t a[4];
-      const int j = ks * 16 + 2 * t4;
-      a[0] = *reinterpret_cast<const uint32_t*>(&sm.Th[i0][j]);
-      a[1] = *reinterpret_cast<const uint32_t*>(&sm.Th[i1][j]);
-      a[2] = *reinterpret_cast<const uint32_t*>(&sm.Th[i0][j + 8]);
-      a[3] = *reinterpret_cast<const uint32_t*>(&sm.Th[i1][j + 8]);
-#pragma unroll
-      for (int nt = 0; nt < 4; ++nt) {
-        const int c = ch + nt * 8 + g8;
-        mma_f16(acc[nt], a, *reinterpret_cast<const uint32_t*>(&sm.XT[c][j]), *reinterpret_cast<const uint32_t*>(&sm.XT[c][j + 8]));
-      }
-    }
-    __syncthreads();                                               // every reader of G is done
-#pragma unroll
-    for (int nt = 0; nt < 4; ++nt) {
-      const int c = ch + nt * 8 + 2 * t4;
-      *reinterpret_cast<uint32_t*>(&w_img[i0 * LDW + c]) = pack_h2(acc[nt][0], acc[nt][1]);
-      *reinterpret_cast<uint32_t*>(&w_img[i1 * LDW + c]) = pack_h2(acc[nt][2], acc[nt][3]);
-    }
-  }
-  {
-    const int v0 = (warp >> 1) * 16 + g8, v1 = v0 + 8, nt0 = (warp & 1) * 4;
-    float acc[4][4];
-#pragma unroll
-    for (int nt = 0; nt < 4; ++nt) { acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f; }
-    for (int ks = 0; ks < 4; ++ks) {
-      uint32_t a[4];
-      const int j = ks * 16 + 2 * t4;
-      a[0] = *reinterpret_cast<const uint32_t*>(&sm.YT[v0][j]);
-      a[1] = *reinterpret_cast<const uint32_t*>(&sm.YT[v1][j]);
-      a[2] = *reinterpret_cast<const uint32_t*>(&sm.YT[v0][j + 8]);
-      a[3] = *reinterpret_cast<const uint32_t*>(&sm.YT[v1][j + 8]);
-#pragma unroll
-      for (int nt = 0; nt < 4; ++nt) {
-        if (ks * 16 > (nt0 + nt) * 8 + 7) continue;                // T[i][j] = 0 for j > i
-        const int i = (nt0 + nt) * 8 + g8;
-        mma_f16(acc[nt], a, *reinterpret_cast<const uint32_t*>(&sm.Th[i][j]), *reinterpret_cast<const uint32_t*>(&sm.Th[i][j + 8]));
-      }
-    }
-#pragma unroll
-    for (int nt = 0; nt < 4; ++nt) {
-      const int i = (nt0 + nt) * 8 + 2 * t4;
-      *reinterpret_cast<uint32_t*>(&u_img[v0 * LDT + i]) = pack_h2(acc[nt][0], acc[nt][1]);
-      *reinterpret_cast<uint32_t*>(&u_img[v1 * LDT + i]) = pack_h2(acc[nt][2], acc[nt][3]);
-    }
-  }
+  // ------------------------------------------------------------------ teardown
+  tc_fence_before();
   __syncthreads();
-
-  // ---- P6: staged images -> workspace, 16 bytes per thread per store
-  for (int idx = tid; idx < KC * LDW * 2 / 16; idx += KDA_INTRA_THREADS)
-    reinterpret_cast<uint4*>(rec + OFF_W)[idx] = reinterpret_cast<const uint4*>(w_img)[idx];
-  for (int idx = tid; idx < KD * LDT * 2 / 16; idx += KDA_INTRA_THREADS)
-    reinterpret_cast<uint4*>(rec + OFF_UT)[idx] = reinterpret_cast<const uint4*>(u_img)[idx];
-  for (int idx = tid; idx < KC * LDT * 2 / 16; idx += KDA_INTRA_THREADS)
-    reinterpret_cast<uint4*>(rec + OFF_AQK)[idx] = reinterpret_cast<const uint4*>(&sm.Aqk[0][0])[idx];
+  if (warp == 0) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
 }
 
 // =============================================================================================
@@ -633,8 +684,8 @@ __global__ void __launch_bounds__(32 * (NW + 1), 1) kda_state_kernel(const KdaSt
     const bool ok = __all_sync(0xffffffffu, mbar_wait(&full[s], (c / KDA_NST) & 1, abort_flag, p.status, 2));
     if (!ok) break;
     const uint8_t* sb = stages + s * L::STAGE;
-    const __half* Wm = reinterpret_cast<const __half*>(sb + OFF_W);
-    const __half* Qm = reinterpret_cast<const __half*>(sb + OFF_Q);
+    const __half* Wt = reinterpret_cast<const __half*>(sb + OFF_WT);
+    const __half* Qt = reinterpret_cast<const __half*>(sb + OFF_QT);
     const __half* Kt = reinterpret_cast<const __half*>(sb + OFF_KT);
     const __half* Aq = reinterpret_cast<const __half*>(sb + OFF_AQK);
     const float* dv = reinterpret_cast<const float*>(sb + OFF_D);
@@ -649,13 +700,14 @@ __global__ void __launch_bounds__(32 * (NW + 1), 1) kda_state_kernel(const KdaSt
       uint32_t a[4];
       a[0] = pack_h2(st[2 * ks][0], st[2 * ks][1]); a[1] = pack_h2(st[2 * ks][2], st[2 * ks][3]);
       a[2] = pack_h2(st[2 * ks + 1][0], st[2 * ks + 1][1]); a[3] = pack_h2(st[2 * ks + 1][2], st[2 * ks + 1][3]);
-      // B fragments of two token tiles per ldmatrix.x4: matrix m = (tile nt + (m >> 1), k half m & 1)
-      const int lrow = (lane >> 4) * 8 + (lane & 7), lcol = ks * 16 + ((lane >> 3) & 1) * 8;
+      // B fragments of two token tiles per transposing ldmatrix.x4 from the channel-major images: matrix m =
+      // (k half m & 1, token tile nt + (m >> 1)); its stored rows are channels, its columns tokens
+      const int lrow = ks * 16 + ((lane >> 3) & 1) * 8 + (lane & 7), lcol = (lane >> 4) * 8;
 #pragma unroll
       for (int nt = 0; nt < 8; nt += 2) {
         uint32_t bw[4], bq[4];
-        ldmatrix_x4(bw, &Wm[(nt * 8 + lrow) * LDW + lcol]);
-        ldmatrix_x4(bq, &Qm[(nt * 8 + lrow) * LDW + lcol]);
+        ldmatrix_x4_t(bw, &Wt[lrow * LDT + nt * 8 + lcol]);
+        ldmatrix_x4_t(bq, &Qt[lrow * LDT + nt * 8 + lcol]);
         mma_f16(au[nt], a, bw[0], bw[1]);
         mma_f16(ao[nt], a, bq[0], bq[1]);
         mma_f16(au[nt + 1], a, bw[2], bw[3]);
@@ -782,24 +834,31 @@ extern "C" int daisy_b200_kda_chunk_fwd(const void* q, const void* k, const void
   static bool attr[daisy_host::MAX_DEVICES] = {};             // the attribute is per device
   const int dev = daisy_host::device_slot();
   if (dev < 0) return DAISY_ENODEV;
+  constexpr int intra_smem = (int)sizeof(KdaIntraSmem) + 1024;   // the kernel aligns its image buffers to 1 KB itself
   if (!attr[dev]) {
-    if (cudaFuncSetAttribute(kda_intra_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(KdaIntraSmem)) != cudaSuccess) {
+    if (cudaFuncSetAttribute(kda_intra_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, intra_smem) != cudaSuccess) {
       (void)cudaGetLastError();
       return DAISY_ECUDA;
     }
     attr[dev] = true;
   }
+  if ((int64_t)B * H * NC >= ((int64_t)1 << 31)) return DAISY_EUNSUPPORTED;
+  CUtensorMap tg, tq, tk, tv;
+  int trc;
+  if ((trc = daisy_host::make_tmap_rows_bthd(&tg, g, 4, KD, T, H, B, KC)) != DAISY_OK) return trc;
+  if ((trc = daisy_host::make_tmap_rows_bthd(&tq, q, 2, KD, T, H, B, KC)) != DAISY_OK) return trc;
+  if ((trc = daisy_host::make_tmap_rows_bthd(&tk, k, 2, KD, T, H, B, KC)) != DAISY_OK) return trc;
+  // v keeps the 128-byte-swizzled form: its tile is a tensor-core operand as it lands
+  if ((trc = daisy_host::make_tmap_bf16_dthb(&tv, v, KD, T, H, B, (uint64_t)H * KD * 2, (uint64_t)KD * 2, (uint64_t)T * H * KD * 2, 64, KC)) != DAISY_OK) return trc;
   KdaIntraParams ip;
-  ip.q = (const __nv_bfloat16*)q; ip.k = (const __nv_bfloat16*)k; ip.v = (const __nv_bfloat16*)v;
-  ip.g = g; ip.beta = beta; ip.ws = (uint8_t*)workspace;
-  ip.T = T; ip.H = H; ip.NC = NC;
+  ip.beta = beta; ip.ws = (uint8_t*)workspace;
+  ip.T = T; ip.H = H; ip.NC = NC; ip.total = B * H * NC;
   ip.scale = scale > 0.f ? scale : 1.0f / sqrtf((float)K);
   ip.l2norm = (flags & DAISY_KDA_L2NORM_QK) ? 1 : 0;
-  {
-    const int sms = daisy_host::sm_count_cached();
-    ip.ahead = sms > 0 ? sms : 148;
-  }
-  kda_intra_kernel<<<dim3(NC, H, B), KDA_INTRA_THREADS, sizeof(KdaIntraSmem), st>>>(ip);
+  ip.status = status_word;
+  const int sms = daisy_host::sm_count_cached();
+  if (sms <= 0) return DAISY_ENODEV;
+  kda_intra_kernel<<<ip.total < sms ? ip.total : sms, KI_THREADS, intra_smem, st>>>(tg, tq, tk, tv, ip);
   DAISY_CHECK_LAUNCH();
 
   KdaStateParams sp;

@@ -76,7 +76,7 @@ def test_argument_validation_without_gpu(lib):
     assert lib.daisy_b200_swa_decode_step(*bad, a, w, 4, None, None) == _lib.EINVAL
     # KDA: K != 128, chunk != 64, workspace
     kw = lib.daisy_b200_kda_workspace_bytes(1, 100, 2, 128, 128)
-    assert kw == 1 * 2 * 2 * 81408
+    assert kw == 1 * 2 * 2 * 83456
     assert lib.daisy_b200_kda_workspace_bytes(1, 100, 2, 64, 128) == 0
     assert lib.daisy_b200_kda_chunk_fwd(a, a, a, a, a, None, a, None, 1, 100, 2, 64, 128, 64, 0.0, 1, a, kw, None, None) == _lib.EUNSUPPORTED
     assert lib.daisy_b200_kda_chunk_fwd(a, a, a, a, a, None, a, None, 1, 100, 2, 128, 128, 32, 0.0, 1, a, kw, None, None) == _lib.EUNSUPPORTED
