@@ -98,6 +98,36 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
   }
 }
 
+// The same bounded wait for barriers that many warps wait on for a long time: every failed test suspends the thread
+// inside the barrier unit for up to `hint_ns` (it still wakes as soon as the phase completes), so the waiters do not
+// flood the shared-memory pipe with polling while other warps need it for real loads and stores.
+__device__ __forceinline__ bool mbar_try_wait_hint(uint64_t* bar, uint32_t parity, uint32_t hint_ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity), "r"(hint_ns) : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait_long(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
+                                               int* status_word, int where) {
+  if (mbar_try_wait(bar, parity)) return true;
+  uint64_t t0 = globaltimer_ns();
+  uint32_t spins = 0;
+  while (true) {
+    if (mbar_try_wait_hint(bar, parity, 4000u)) return true;
+    if ((++spins & 15u) == 0) {
+      if (*abort_flag) return false;
+      if (globaltimer_ns() - t0 > 2000000000ull) {
+        *abort_flag = where;
+        if (status_word) { status_word[0] = DAISY_ETIMEOUT; }
+        return false;
+      }
+    }
+  }
+}
+
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
 // ------------------------------------------------------------------ TMA (no multicast anywhere)

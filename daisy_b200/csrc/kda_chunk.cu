@@ -10,8 +10,8 @@
 //  * kda_intra_kernel  -- everything that does not depend on the state, all chunks in parallel, on tcgen05 tensor
 //    cores: a persistent CTA per SM walks (batch, head, chunk) work items; 16 "element" warps turn the TMA-staged
 //    inputs into fp16 operand images and issue the Gram products on them, 4 "solver" warps pull the Gram entries
-//    out of TMEM, invert I + A_kk and issue / drain the W and U0 products -- two pipelines that overlap across
-//    consecutive chunks.  Per chunk it writes a record of fp16 operand images (rows padded so that fragment loads
+//    out of TMEM and solve (I + A_kk) W = beta k e^G, (I + A_kk) U0 = beta v block by block with register-chained
+//    mma.sync tiles -- two pipelines that overlap across consecutive chunks.  Per chunk it writes a record of fp16 operand images (rows padded so that fragment loads
 //    are bank-conflict free): W^T, (scale q e^G)^T, (k e^{G_C-G})^T, U0^T as [128][72], A_qk as [64][72], e^{G_C}.
 //  * kda_state_kernel  -- one CTA per (batch, head, V-slice), sequential over chunks: a producer warp
 //    bulk-copies the images of chunk c+1.. into a shared-memory ring while the compute warps hold their
@@ -55,7 +55,7 @@ __device__ __forceinline__ void ldmatrix_x4_t(uint32_t* r, const void* row_ptr) 
 }
 
 __device__ __forceinline__ void mma_f16(float* c, const uint32_t* a, uint32_t b0, uint32_t b1) {
-  asm volatile(
+  asm(
       "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
       : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
@@ -102,32 +102,31 @@ struct KdaIntraParams {
   int* status;
 };
 
-constexpr int KI_ELEM_WARPS = 16, KI_SOLVER_WARPS = 4;
+constexpr int KI_ELEM_WARPS = 16, KI_SOLVER_WARPS = 8;
 constexpr int KI_ELEM_THREADS = 32 * KI_ELEM_WARPS;                         // 512
-constexpr int KI_SOLVER_THREADS = 32 * KI_SOLVER_WARPS;                     // 128
-// 20 warps = 5 per scheduler: 96 registers per thread (a 21st warp would cut that to 80)
-constexpr int KI_THREADS = KI_ELEM_THREADS + KI_SOLVER_THREADS;             // 640
+constexpr int KI_SOLVER_THREADS = 32 * KI_SOLVER_WARPS;                     // 256
+// 24 warps = 6 per scheduler: 80 registers per thread
+constexpr int KI_THREADS = KI_ELEM_THREADS + KI_SOLVER_THREADS;             // 768
 constexpr int KI_IMG_BYTES = KD * KC * 2;                                   // one [128 channels][64 tokens] fp16 image: 16384
 constexpr int KI_IN_BYTES = KC * KD * 4 + 2 * KC * KD * 2;                  // g + q + k tiles: 65536
 constexpr int LDAKH = 72;
+constexpr int KI_SETS = 2;              // operand image sets in flight; divides the six levels of a chunk
 
 struct __align__(1024) KdaIntraSmem {
-  uint8_t img[2][2 * KI_IMG_BYTES];      // level operand images, two sets of (k image, q image); 128-byte swizzle
-  uint8_t ximg[KI_IMG_BYTES];            // (k e^G)^T image: A operand of W^T
-  uint8_t vtile[KI_IMG_BYTES];           // v tile as TMA leaves it (two [64 tokens][64 columns] boxes): A operand of U0^T
-  uint8_t t16[KC * 128], thi[KC * 128], tlo[KC * 128];   // T diag(beta): fp16, and bf16 high / low parts
+  uint8_t img[KI_SETS][2 * KI_IMG_BYTES];   // level operand images, a ring of sets of (k image, q image); 128-byte swizzle
   float g[KC][KD];                       // TMA destinations, plain rows
   __nv_bfloat16 q[KC][KD];
   __nv_bfloat16 k[KC][KD];
-  float akk[4][16][17];                  // beta * A_kk, the four diagonal 16 x 16 blocks in fp32
+  __nv_bfloat16 v[KC][KD];
+  __half xt[KD][LDT];                    // (k e^G)^T, fp16: right-hand side of the W solve
+  float akk_t[4][16][16];                // beta * A_kk, the four diagonal 16 x 16 blocks in fp32, column-major ([j][i])
   __half akh[KC][LDAKH];                 //              the whole lower triangle as fp16 operands
-  __half th[KC][LDT];                    // T = (I + A_kk)^-1, row-major
-  __half tht[KC][LDT];                   // T^T
+  __half th[KC][LDT];                    // the inverses of the diagonal blocks of I + A_kk, row-major, fp16
   float tot[4][KD];                      // product of the decays of each 16-token segment
   float rq[2][KC], rk[2][KC], beta[2][KC], qkd[2][KC];   // per-token scalars, double-buffered by chunk parity
-  float sbeta[KC], sqkd[KC];             // the solver's own copies
-  uint64_t in_full, v_full, x_full, x_empty, w_full;
-  uint64_t img_full[2], img_empty[2], d_full[6], d_empty[6];
+  float sbeta[KC];                       // the solver's own copy
+  uint64_t in_full, v_full, x_full, x_empty;
+  uint64_t img_full[KI_SETS], img_empty[KI_SETS], d_full[6], d_empty[6];
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -145,33 +144,41 @@ __device__ __forceinline__ void ki_coords(int w, int NC, int H, int& b, int& h, 
   b = bh / H;
 }
 
-// One level's operand images (this thread's 16 tokens of channel c) into the image set of the level's turn, then --
-// warp 0 only -- the level's Gram product once every element thread has delivered its share.
-__device__ __forceinline__ void ki_emit_level(KdaIntraSmem& sm, const float (&f)[16], const float (&kn)[16], const float (&qn)[16],
+__device__ __forceinline__ uint32_t hmul2_u32(uint32_t a, uint32_t b) {
+  uint32_t d;
+  asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+  return d;
+}
+
+// One level's operand images (this thread's 16 tokens of channel c; kn / qn hold them as fp16 pairs) into the image
+// set of the level's turn, then -- one warp per level, so that no warp falls far behind the others -- the level's
+// Gram product once every element thread has delivered its share.
+__device__ __forceinline__ void ki_emit_level(KdaIntraSmem& sm, const float (&f)[16], const uint32_t (&kn)[8], const uint32_t (&qn)[8],
                                               const bool write_q, const int c, const int seg, const int warp, const uint32_t leader,
                                               const uint32_t ci, uint32_t& n_img, bool& ok, const uint32_t tmem_base,
                                               const uint32_t g_lo0, const uint32_t g_hi, volatile int* abort_flag, int* status) {
   constexpr uint32_t idesc_g = umma_idesc_f16(128, KC, 1, 1);                   // A and B both token-contiguous (MN-major)
-  const uint32_t set = n_img & 1, use = n_img >> 1;
-  if (use >= 1) ok = mbar_wait(&sm.img_empty[set], (use - 1) & 1, abort_flag, status, 2) && ok;
+  const uint32_t set = n_img % KI_SETS, use = n_img / KI_SETS;
+  uint32_t fh[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) fh[i] = pack_h2(f[2 * i], f[2 * i + 1]);
+  if (use >= 1) ok = mbar_wait_long(&sm.img_empty[set], (use - 1) & 1, abort_flag, status, 2) && ok;
   uint8_t* kimg = sm.img[set];
 #pragma unroll
   for (int e = 0; e < 2; ++e) {
     const uint32_t off = sw128(c, 2 * seg + e);
-    *reinterpret_cast<uint4*>(kimg + off) =
-        make_uint4(pack_h2(kn[8 * e] * f[8 * e], kn[8 * e + 1] * f[8 * e + 1]), pack_h2(kn[8 * e + 2] * f[8 * e + 2], kn[8 * e + 3] * f[8 * e + 3]),
-                   pack_h2(kn[8 * e + 4] * f[8 * e + 4], kn[8 * e + 5] * f[8 * e + 5]), pack_h2(kn[8 * e + 6] * f[8 * e + 6], kn[8 * e + 7] * f[8 * e + 7]));
+    *reinterpret_cast<uint4*>(kimg + off) = make_uint4(hmul2_u32(kn[4 * e], fh[4 * e]), hmul2_u32(kn[4 * e + 1], fh[4 * e + 1]),
+                                                       hmul2_u32(kn[4 * e + 2], fh[4 * e + 2]), hmul2_u32(kn[4 * e + 3], fh[4 * e + 3]));
     if (write_q)
-      *reinterpret_cast<uint4*>(kimg + KI_IMG_BYTES + off) =
-          make_uint4(pack_h2(qn[8 * e] * f[8 * e], qn[8 * e + 1] * f[8 * e + 1]), pack_h2(qn[8 * e + 2] * f[8 * e + 2], qn[8 * e + 3] * f[8 * e + 3]),
-                     pack_h2(qn[8 * e + 4] * f[8 * e + 4], qn[8 * e + 5] * f[8 * e + 5]), pack_h2(qn[8 * e + 6] * f[8 * e + 6], qn[8 * e + 7] * f[8 * e + 7]));
+      *reinterpret_cast<uint4*>(kimg + KI_IMG_BYTES + off) = make_uint4(hmul2_u32(qn[4 * e], fh[4 * e]), hmul2_u32(qn[4 * e + 1], fh[4 * e + 1]),
+                                                                        hmul2_u32(qn[4 * e + 2], fh[4 * e + 2]), hmul2_u32(qn[4 * e + 3], fh[4 * e + 3]));
   }
   fence_proxy_async();
   mbar_arrive(&sm.img_full[set]);
-  if (warp == 0) {
-    const int li = (int)(n_img % 6u);
-    ok = mbar_wait(&sm.img_full[set], use & 1, abort_flag, status, 4) && ok;
-    if (ci >= 1) ok = mbar_wait(&sm.d_empty[li], (ci - 1) & 1, abort_flag, status, 5) && ok;
+  const int li = (int)(n_img % 6u);
+  if (warp == li) {                                                             // level li's product is issued by element warp li
+    ok = mbar_wait_long(&sm.img_full[set], use & 1, abort_flag, status, 4) && ok;
+    if (ci >= 1) ok = mbar_wait_long(&sm.d_empty[li], (ci - 1) & 1, abort_flag, status, 5) && ok;
     ok = __all_sync(0xffffffffu, ok);
     if (ok) {
       tc_fence_after();
@@ -214,16 +221,13 @@ kda_intra_kernel(const __grid_constant__ CUtensorMap tm_g, const __grid_constant
 
   if (tid == 0) {
     mbar_init(&sm.in_full, 1); mbar_init(&sm.v_full, 1);
-    mbar_init(&sm.x_full, KI_ELEM_THREADS); mbar_init(&sm.x_empty, 1); mbar_init(&sm.w_full, 1);
-    for (int i = 0; i < 2; ++i) { mbar_init(&sm.img_full[i], KI_ELEM_THREADS); mbar_init(&sm.img_empty[i], 1); }
+    mbar_init(&sm.x_full, KI_ELEM_THREADS); mbar_init(&sm.x_empty, 1);
+    for (int i = 0; i < KI_SETS; ++i) { mbar_init(&sm.img_full[i], KI_ELEM_THREADS); mbar_init(&sm.img_empty[i], 1); }
     for (int i = 0; i < 6; ++i) { mbar_init(&sm.d_full[i], 1); mbar_init(&sm.d_empty[i], KI_SOLVER_THREADS); }
     sm.abort_flag = 0;
     mbar_init_fence();
   }
-  // the T images keep zeros above the diagonal for the whole launch: only the lower triangle is ever rewritten
-  for (int i = tid; i < 3 * KC * 128 / 16; i += KI_THREADS) reinterpret_cast<uint4*>(sm.t16)[i] = make_uint4(0, 0, 0, 0);
   if (warp == 0) { tmem_alloc(&sm.tmem_base, 512); tmem_relinquish(); }
-  fence_proxy_async();
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -241,9 +245,10 @@ kda_intra_kernel(const __grid_constant__ CUtensorMap tm_g, const __grid_constant
       tma_load_4d(&sm.q[0][0], &tm_q, &sm.in_full, 0, chunk * KC, h, b);
       tma_load_4d(&sm.k[0][0], &tm_k, &sm.in_full, 0, chunk * KC, h, b);
     }
-    // warp 0 doubles as the issuer of the Gram products: after its own share of a level's images it waits for
-    // everybody else's (all element warps do the same work in step, so the wait is short) and issues the product
-    const uint32_t leader = (warp == 0 && elect_one()) ? 1u : 0u;
+    // warps 0..5 double as the issuers of the six Gram products (warp li issues level li): after its own share of
+    // the level's images the warp waits for everybody else's (all element warps do the same work in step, so the
+    // wait is short) and issues the product
+    const uint32_t leader = (warp < 6 && elect_one()) ? 1u : 0u;
     const uint64_t gd0 = umma_desc_sw128(smem_u32(sm.img[0]), KI_IMG_BYTES, 1024);
     const uint32_t g_lo0 = (uint32_t)gd0, g_hi = (uint32_t)(gd0 >> 32);
     uint32_t ci = 0, n_img = 0;
@@ -254,7 +259,7 @@ kda_intra_kernel(const __grid_constant__ CUtensorMap tm_g, const __grid_constant
       const int par = ci & 1;
       const int t0 = chunk * KC;
       uint8_t* rec = p.ws + (size_t)w * REC_BYTES;
-      ok = mbar_wait(&sm.in_full, ci & 1, abort_flag, p.status, 1) && ok;
+      ok = mbar_wait_long(&sm.in_full, ci & 1, abort_flag, p.status, 1) && ok;
 
       // ---- per-token scalars: 8 threads per row, 16 channels each
       {
@@ -282,15 +287,25 @@ kda_intra_kernel(const __grid_constant__ CUtensorMap tm_g, const __grid_constant
       if (named_bar_or(1, KI_ELEM_THREADS, !ok)) break;
 
       // ---- this thread's column of the chunk: 16 tokens of channel c
-      float pre[16], suf[16], kn[16], qn[16];
+      float pre[16], suf[16];
+      uint32_t kn[8], qn[8];                                                     // normalised k, q as fp16 pairs (tokens 2i, 2i + 1)
       {
         const int r0 = 16 * seg;
+        float rkv[16], rqv[16];
+#pragma unroll
+        for (int i = 0; i < 16; i += 4) {
+          *reinterpret_cast<float4*>(&rkv[i]) = *reinterpret_cast<const float4*>(&sm.rk[par][r0 + i]);
+          *reinterpret_cast<float4*>(&rqv[i]) = *reinterpret_cast<const float4*>(&sm.rq[par][r0 + i]);
+        }
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
           pre[i] = fast_exp2(sm.g[r0 + i][c] * 1.4426950408889634f);           // d_t = e^{g_t}
           suf[i] = 1.f;
-          kn[i] = __bfloat162float(sm.k[r0 + i][c]) * sm.rk[par][r0 + i];
-          qn[i] = __bfloat162float(sm.q[r0 + i][c]) * sm.rq[par][r0 + i];
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          kn[i] = pack_h2(__bfloat162float(sm.k[r0 + 2 * i][c]) * rkv[2 * i], __bfloat162float(sm.k[r0 + 2 * i + 1][c]) * rkv[2 * i + 1]);
+          qn[i] = pack_h2(__bfloat162float(sm.q[r0 + 2 * i][c]) * rqv[2 * i], __bfloat162float(sm.q[r0 + 2 * i + 1][c]) * rqv[2 * i + 1]);
         }
       }
       named_bar(1, KI_ELEM_THREADS);                                            // every read of the input tiles is done
@@ -346,83 +361,86 @@ kda_intra_kernel(const __grid_constant__ CUtensorMap tm_g, const __grid_constant
         }
       }
       // ---- pre = e^{G}, suf = e^{G_C - G}: the state-pass operands
-      if (ci >= 1) ok = mbar_wait(&sm.x_empty, (ci - 1) & 1, abort_flag, p.status, 3) && ok;
+      if (ci >= 1) ok = mbar_wait_long(&sm.x_empty, (ci - 1) & 1, abort_flag, p.status, 3) && ok;
 #pragma unroll
       for (int e = 0; e < 2; ++e) {
         float x[8], qt[8], kt[8];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          x[i] = kn[8 * e + i] * pre[8 * e + i];
-          qt[i] = qn[8 * e + i] * pre[8 * e + i] * p.scale;
-          kt[i] = kn[8 * e + i] * suf[8 * e + i];
+        for (int i = 0; i < 4; ++i) {
+          const float2 kf = unpack_h2(kn[4 * e + i]), qf = unpack_h2(qn[4 * e + i]);
+          const int t = 8 * e + 2 * i;
+          x[2 * i] = kf.x * pre[t]; x[2 * i + 1] = kf.y * pre[t + 1];
+          qt[2 * i] = qf.x * pre[t] * p.scale; qt[2 * i + 1] = qf.y * pre[t + 1] * p.scale;
+          kt[2 * i] = kf.x * suf[t]; kt[2 * i + 1] = kf.y * suf[t + 1];
         }
-        *reinterpret_cast<uint4*>(sm.ximg + sw128(c, 2 * seg + e)) =
+        *reinterpret_cast<uint4*>(&sm.xt[c][16 * seg + 8 * e]) =
             make_uint4(pack_h2(x[0], x[1]), pack_h2(x[2], x[3]), pack_h2(x[4], x[5]), pack_h2(x[6], x[7]));
         const size_t goff = ((size_t)c * LDT + 16 * seg + 8 * e) * 2;
         st_global16(rec + OFF_QT + goff, pack_h2(qt[0], qt[1]), pack_h2(qt[2], qt[3]), pack_h2(qt[4], qt[5]), pack_h2(qt[6], qt[7]));
         st_global16(rec + OFF_KT + goff, pack_h2(kt[0], kt[1]), pack_h2(kt[2], kt[3]), pack_h2(kt[4], kt[5]), pack_h2(kt[6], kt[7]));
       }
       if (seg == 3) reinterpret_cast<float*>(rec + OFF_D)[c] = pre[15];         // e^{G_C}
-      fence_proxy_async();
       mbar_arrive(&sm.x_full);
     }
   } else {
     // ================================================================== solver warps
-    const int ws = warp - KI_ELEM_WARPS, st = tid - KI_ELEM_THREADS;            // 0..3, 0..127
+    // Two warps share each quarter of the TMEM lanes (warp % 4): rows 32 hb .. 32 hb + 31 of the k (quarters 0, 1) or
+    // q (quarters 2, 3) products; `ch` splits a row's 32-column window into two halves of 16.
+    const int ws = warp - KI_ELEM_WARPS, st = tid - KI_ELEM_THREADS;            // 0..7, 0..255
     const int g8 = lane >> 2, t4 = lane & 3;
-    const bool is_qk = ws >= 2;                                                 // TMEM lanes 0-63: k rows, 64-127: q rows
-    const int hb = ws & 1;                                                      // which 32-token half this warp's rows are in
+    const int qt4 = ws & 3, ch = ws >> 2;
+    const bool is_qk = qt4 >= 2;
+    const int hb = qt4 & 1;
     const int row = 32 * hb + lane;
-    const uint32_t lane_base = tmem_base + ((uint32_t)(32 * ws) << 16);
+    const uint32_t lane_base = tmem_base + ((uint32_t)(32 * qt4) << 16);
     if (st == 0 && (int)blockIdx.x < p.total) {
       int b, h, chunk;
       ki_coords(blockIdx.x, p.NC, p.H, b, h, chunk);
       prefetch_tmap(&tm_v);
       mbar_expect_tx(&sm.v_full, KI_IMG_BYTES);
-      tma_load_4d(sm.vtile, &tm_v, &sm.v_full, 0, chunk * KC, h, b);
-      tma_load_4d(sm.vtile + KI_IMG_BYTES / 2, &tm_v, &sm.v_full, 64, chunk * KC, h, b);
+      tma_load_4d(&sm.v[0][0], &tm_v, &sm.v_full, 0, chunk * KC, h, b);
     }
     uint32_t ci = 0;
     bool ok = true;
     for (int w = blockIdx.x; w < p.total; w += gridDim.x, ++ci) {
       const int par = ci & 1;
       uint8_t* rec = p.ws + (size_t)w * REC_BYTES;
-      // ---- Gram entries out of TMEM.  acc[j] collects row `row`, columns 32 hb + j, level by level: the entry of
-      //      (row, column) lives in the level of the highest bit in which the two token indices differ.
-      float acc[32];
+      // ---- Gram entries out of TMEM.  acc[j] collects row `row`, column 32 hb + 16 ch + j, level by level: the
+      //      entry of (row, column) lives in the level of the highest bit in which the two token indices differ.
+      float acc[16];
 #pragma unroll
-      for (int j = 0; j < 32; ++j) acc[j] = 0.f;
+      for (int j = 0; j < 16; ++j) acc[j] = 0.f;
       float my_beta = 0.f, my_qkd = 0.f;
+#pragma unroll
       for (int li = 0; li < 6; ++li) {
-        ok = __all_sync(0xffffffffu, mbar_wait(&sm.d_full[li], ci & 1, abort_flag, p.status, 6)) && ok;
+        ok = __all_sync(0xffffffffu, mbar_wait_long(&sm.d_full[li], ci & 1, abort_flag, p.status, 6)) && ok;
         if (li == 0) {                                                          // the item's scalars are final once its first image exists
-          if (st < KC) { sm.sbeta[st] = sm.beta[par][st]; sm.sqkd[st] = sm.qkd[par][st]; }
+          if (st < KC) sm.sbeta[st] = sm.beta[par][st];
           my_beta = sm.beta[par][row]; my_qkd = sm.qkd[par][row];
         }
         tc_fence_after();
-        uint32_t r[32];
+        uint32_t r[16];
         if (li < 5) {
-          tmem_ld32(lane_base + 64 * li + 32 * hb, r);
+          tmem_ld16(lane_base + 64 * li + 32 * hb + 16 * ch, r);
           tc_wait_ld();
+          const uint32_t lx = (uint32_t)lane >> li;
 #pragma unroll
-          for (int j = 0; j < 32; ++j)
-            if ((((uint32_t)lane ^ (uint32_t)j) >> li) == 1u) acc[j] = __uint_as_float(r[j]);
+          for (int j = 0; j < 16; ++j)
+            if (lx == (uint32_t)((((16 * ch + j) >> li)) ^ 1)) acc[j] = __uint_as_float(r[j]);
         } else if (hb == 1) {                                                   // s = 32: rows 32..63 against columns 0..31, all of them
-          tmem_ld32(lane_base + 64 * 5, r);
+          tmem_ld16(lane_base + 64 * 5 + 16 * ch, r);
           tc_wait_ld();
           const float sc = is_qk ? p.scale : my_beta;
+          uint32_t pk[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) pk[j] = pack_h2(sc * __uint_as_float(r[2 * j]), sc * __uint_as_float(r[2 * j + 1]));
           if (is_qk) {
-            uint8_t* dst = rec + OFF_AQK + (size_t)row * LDT * 2;
-#pragma unroll
-            for (int j = 0; j < 32; j += 8)
-              st_global16(dst + j * 2, pack_h2(sc * __uint_as_float(r[j]), sc * __uint_as_float(r[j + 1])),
-                          pack_h2(sc * __uint_as_float(r[j + 2]), sc * __uint_as_float(r[j + 3])),
-                          pack_h2(sc * __uint_as_float(r[j + 4]), sc * __uint_as_float(r[j + 5])),
-                          pack_h2(sc * __uint_as_float(r[j + 6]), sc * __uint_as_float(r[j + 7])));
+            uint8_t* dst = rec + OFF_AQK + ((size_t)row * LDT + 16 * ch) * 2;
+            st_global16(dst, pk[0], pk[1], pk[2], pk[3]);
+            st_global16(dst + 16, pk[4], pk[5], pk[6], pk[7]);
           } else {
-#pragma unroll
-            for (int j = 0; j < 32; j += 2)
-              *reinterpret_cast<uint32_t*>(&sm.akh[row][j]) = pack_h2(sc * __uint_as_float(r[j]), sc * __uint_as_float(r[j + 1]));
+            *reinterpret_cast<uint4*>(&sm.akh[row][16 * ch]) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+            *reinterpret_cast<uint4*>(&sm.akh[row][16 * ch + 8]) = make_uint4(pk[4], pk[5], pk[6], pk[7]);
           }
         }
         tc_fence_before();
@@ -430,164 +448,130 @@ kda_intra_kernel(const __grid_constant__ CUtensorMap tm_g, const __grid_constant
       }
       {
         const float sc = is_qk ? p.scale : my_beta;
-        float v[32];
+        const int lj = lane - 16 * ch;                                          // this row's own column inside the 16 (if 0 <= lj < 16)
+        float v[16];
 #pragma unroll
-        for (int j = 0; j < 32; ++j) v[j] = (j < lane) ? sc * acc[j] : 0.f;
+        for (int j = 0; j < 16; ++j) v[j] = (j < lj) ? sc * acc[j] : 0.f;
+        uint32_t pk[8];
         if (is_qk) {
 #pragma unroll
-          for (int j = 0; j < 32; ++j) if (j == lane) v[j] = p.scale * my_qkd;  // the diagonal: q_i . k_i, no decay
-          uint8_t* dst = rec + OFF_AQK + ((size_t)row * LDT + 32 * hb) * 2;
+          for (int j = 0; j < 16; ++j) if (j == lj) v[j] = p.scale * my_qkd;    // the diagonal: q_i . k_i, no decay
+        }
 #pragma unroll
-          for (int j = 0; j < 32; j += 8)
-            st_global16(dst + j * 2, pack_h2(v[j], v[j + 1]), pack_h2(v[j + 2], v[j + 3]), pack_h2(v[j + 4], v[j + 5]), pack_h2(v[j + 6], v[j + 7]));
+        for (int j = 0; j < 8; ++j) pk[j] = pack_h2(v[2 * j], v[2 * j + 1]);
+        if (is_qk) {
+          uint8_t* dst = rec + OFF_AQK + ((size_t)row * LDT + 32 * hb + 16 * ch) * 2;
+          st_global16(dst, pk[0], pk[1], pk[2], pk[3]);
+          st_global16(dst + 16, pk[4], pk[5], pk[6], pk[7]);
         } else {
+          *reinterpret_cast<uint4*>(&sm.akh[row][32 * hb + 16 * ch]) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+          *reinterpret_cast<uint4*>(&sm.akh[row][32 * hb + 16 * ch + 8]) = make_uint4(pk[4], pk[5], pk[6], pk[7]);
+          if ((lane >> 4) == ch) {                                              // the row's diagonal 16 x 16 block, in fp32
+            const int blk = row >> 4;
 #pragma unroll
-          for (int j = 0; j < 32; j += 2) *reinterpret_cast<uint32_t*>(&sm.akh[row][32 * hb + j]) = pack_h2(v[j], v[j + 1]);
-          const int blk = row >> 4, jb = lane & 16;                              // the row's diagonal 16 x 16 block, in fp32
-#pragma unroll
-          for (int j = 0; j < 32; ++j)
-            if ((j & 16) == jb) sm.akk[blk][row & 15][j & 15] = v[j];
+            for (int j = 0; j < 16; ++j) sm.akk_t[blk][j][row & 15] = v[j];
+          }
         }
       }
       if (named_bar_or(2, KI_SOLVER_THREADS, !ok)) break;
 
-      // ---- T = (I + A_kk)^-1.  (a) the four 16x16 diagonal blocks by forward substitution in fp32
-      if (lane < 16) {
+      // ---- the four 16 x 16 diagonal blocks of I + A_kk inverted in fp32, one block per warp, lane = column: a column
+      //      sweep (once t_j is final every later row takes its update at once), so the chain is 16 steps deep
+      if (ws < 4 && lane < 16) {
         float t[16];
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          float s = (i == lane) ? 1.f : 0.f;
+        for (int i = 0; i < 16; ++i) t[i] = (i == lane) ? 1.f : 0.f;
 #pragma unroll
-          for (int j = 0; j < i; ++j) s = fmaf(-sm.akk[ws][i][j], t[j], s);
-          t[i] = s;
+        for (int j = 0; j < 15; ++j) {
+          float a[16];
+#pragma unroll
+          for (int i4 = (j + 1) & ~3; i4 < 16; i4 += 4)
+            *reinterpret_cast<float4*>(&a[i4]) = *reinterpret_cast<const float4*>(&sm.akk_t[ws][j][i4]);
+#pragma unroll
+          for (int i = j + 1; i < 16; ++i) t[i] = fmaf(-a[i], t[j], t[i]);
         }
         const int base = ws * 16;
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {                                 // t[i] = T[base + i][base + lane]
-          const __half thv = __float2half_rn(t[i]);
-          sm.th[base + i][base + lane] = thv;
-          sm.tht[base + lane][base + i] = thv;
-        }
+        for (int i = 0; i < 16; ++i) sm.th[base + i][base + lane] = __float2half_rn(t[i]);   // t[i] = T[base + i][base + lane]
       }
-      named_bar(2, KI_SOLVER_THREADS);
-      //      (b) block rows I = 1..3 on tensor cores, in transposed form so that the two products chain through
-      //          registers:  R = T^T,  R_{<I,I} = -(R_{<I,<I} A_{I,<I}^T) R_II.  Warp mt < I owns 16 rows of R_{<I,I};
-      //          the first product's accumulator pair is the second product's A fragment.
-#pragma unroll 1
-      for (int I = 1; I < 4; ++I) {
-        if (ws < I) {
-          const int mt = ws;
-          float acc1[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
-          for (int kb = mt; kb < I; ++kb) {                            // R is block upper triangular
-            uint32_t a[4];
-            const int kc = kb * 16 + 2 * t4;
-            a[0] = *reinterpret_cast<const uint32_t*>(&sm.tht[mt * 16 + g8][kc]);
-            a[1] = *reinterpret_cast<const uint32_t*>(&sm.tht[mt * 16 + g8 + 8][kc]);
-            a[2] = *reinterpret_cast<const uint32_t*>(&sm.tht[mt * 16 + g8][kc + 8]);
-            a[3] = *reinterpret_cast<const uint32_t*>(&sm.tht[mt * 16 + g8 + 8][kc + 8]);
+      ok = mbar_wait_long(&sm.x_full, ci & 1, abort_flag, p.status, 7) && ok;   // (k e^G)^T is in place
+      ok = mbar_wait_long(&sm.v_full, ci & 1, abort_flag, p.status, 8) && ok;   // and the v tile
+      if (named_bar_or(2, KI_SOLVER_THREADS, !ok)) break;
+
+      // ---- W and U0 by blocked forward substitution on the transposed systems
+      //          W^T (I + A)^T = (diag(beta) k e^G)^T,      U0^T (I + A)^T = (diag(beta) v)^T
+      //      A warp owns 32 of the 256 rows (channels of W^T: warps 0-3, value columns of U0^T: warps 4-7) for all
+      //      four 16-token block columns I, so there is nothing to exchange between warps:
+      //          Z_I = R_I - sum_{J<I} Z_J A_IJ^T,   then   Z_I <- Z_I T_II^T
+      //      with every product an m16n8k16 tile whose fp32 accumulators, rounded to fp16, are the A fragment of
+      //      the products that follow.  The two row tiles of a warp are independent chains issued side by side.
+      {
+        const bool is_w = ws < 4;
+        uint8_t* dst = rec + (is_w ? OFF_WT : OFF_UT);
+        uint32_t zf[2][3][4];                                                   // Z_J as fp16 A fragments: [row tile][J][4]
+#pragma unroll
+        for (int I = 0; I < 4; ++I) {
+          float acc1[2][2][4];
+#pragma unroll
+          for (int m = 0; m < 2; ++m)
+#pragma unroll
+            for (int nn = 0; nn < 2; ++nn) { acc1[m][nn][0] = acc1[m][nn][1] = acc1[m][nn][2] = acc1[m][nn][3] = 0.f; }
+#pragma unroll
+          for (int J = 0; J < I; ++J) {
 #pragma unroll
             for (int nn = 0; nn < 2; ++nn) {
-              const __half* arow = &sm.akh[I * 16 + nn * 8 + g8][kc];
-              mma_f16(acc1[nn], a, *reinterpret_cast<const uint32_t*>(arow), *reinterpret_cast<const uint32_t*>(arow + 8));
+              const __half* arow = &sm.akh[I * 16 + nn * 8 + g8][J * 16 + 2 * t4];
+              const uint32_t b0 = *reinterpret_cast<const uint32_t*>(arow), b1 = *reinterpret_cast<const uint32_t*>(arow + 8);
+#pragma unroll
+              for (int m = 0; m < 2; ++m) mma_f16(acc1[m][nn], zf[m][J], b0, b1);
             }
           }
-          uint32_t a2[4];
-          a2[0] = pack_h2(acc1[0][0], acc1[0][1]); a2[1] = pack_h2(acc1[0][2], acc1[0][3]);
-          a2[2] = pack_h2(acc1[1][0], acc1[1][1]); a2[3] = pack_h2(acc1[1][2], acc1[1][3]);
+          uint32_t a2[2][4];
 #pragma unroll
           for (int nn = 0; nn < 2; ++nn) {
-            float acc2[4] = {0.f, 0.f, 0.f, 0.f};
+            const int tk = I * 16 + nn * 8 + 2 * t4;                            // this thread's two tokens of the tile
+            const float2 bt = *reinterpret_cast<const float2*>(&sm.sbeta[tk]);
+#pragma unroll
+            for (int m = 0; m < 2; ++m) {
+              const int r0 = 16 * (2 * (ws & 3) + m) + g8;                      // row inside this matrix: channel or value column
+              float2 lo, hi;                                                    // right-hand side at rows r0 and r0 + 8
+              if (is_w) {
+                lo = unpack_h2(*reinterpret_cast<const uint32_t*>(&sm.xt[r0][tk]));
+                hi = unpack_h2(*reinterpret_cast<const uint32_t*>(&sm.xt[r0 + 8][tk]));
+              } else {
+                lo = make_float2(__bfloat162float(sm.v[tk][r0]), __bfloat162float(sm.v[tk + 1][r0]));
+                hi = make_float2(__bfloat162float(sm.v[tk][r0 + 8]), __bfloat162float(sm.v[tk + 1][r0 + 8]));
+              }
+              a2[m][2 * nn] = pack_h2(lo.x * bt.x - acc1[m][nn][0], lo.y * bt.y - acc1[m][nn][1]);
+              a2[m][2 * nn + 1] = pack_h2(hi.x * bt.x - acc1[m][nn][2], hi.y * bt.y - acc1[m][nn][3]);
+            }
+          }
+#pragma unroll
+          for (int nn = 0; nn < 2; ++nn) {
             const __half* trow = &sm.th[I * 16 + nn * 8 + g8][I * 16 + 2 * t4];
-            mma_f16(acc2, a2, *reinterpret_cast<const uint32_t*>(trow), *reinterpret_cast<const uint32_t*>(trow + 8));
-            // acc2[0..1] = R[mt*16 + g8][nn*8 + 2 t4 (+1)], acc2[2..3] the same for row g8 + 8;  T[i][j] = -R[j][i]
-            const int ti = I * 16 + nn * 8 + 2 * t4, tj = mt * 16 + g8;
-            const __half h0 = __float2half_rn(-acc2[0]), h1 = __float2half_rn(-acc2[1]);
-            const __half h2 = __float2half_rn(-acc2[2]), h3 = __float2half_rn(-acc2[3]);
-            sm.th[ti][tj] = h0; sm.th[ti + 1][tj] = h1; sm.th[ti][tj + 8] = h2; sm.th[ti + 1][tj + 8] = h3;
-            *reinterpret_cast<__half2*>(&sm.tht[tj][ti]) = __halves2half2(h0, h1);
-            *reinterpret_cast<__half2*>(&sm.tht[tj + 8][ti]) = __halves2half2(h2, h3);
+            const uint32_t b0 = *reinterpret_cast<const uint32_t*>(trow), b1 = *reinterpret_cast<const uint32_t*>(trow + 8);
+            const int tk = I * 16 + nn * 8 + 2 * t4;
+#pragma unroll
+            for (int m = 0; m < 2; ++m) {
+              float acc2[4] = {0.f, 0.f, 0.f, 0.f};
+              mma_f16(acc2, a2[m], b0, b1);
+              const uint32_t z_lo = pack_h2(acc2[0], acc2[1]), z_hi = pack_h2(acc2[2], acc2[3]);
+              if (I < 3) { zf[m][I][2 * nn] = z_lo; zf[m][I][2 * nn + 1] = z_hi; }
+              const int r0 = 16 * (2 * (ws & 3) + m) + g8;
+              *reinterpret_cast<uint32_t*>(dst + ((size_t)r0 * LDT + tk) * 2) = z_lo;
+              *reinterpret_cast<uint32_t*>(dst + ((size_t)(r0 + 8) * LDT + tk) * 2) = z_hi;
+            }
           }
         }
-        named_bar(2, KI_SOLVER_THREADS);
       }
-      // ---- operand images of T diag(beta) (lower triangle; everything above stays zero): fp16 for W^T, and a
-      //      bf16 high + low pair for U0^T, whose other operand is the bf16 v tile as it came from memory
-      {
-        const int i = st >> 1, j0 = (st & 1) * 32;
-#pragma unroll
-        for (int ch = 0; ch < 4; ++ch) {
-          const int j = j0 + 8 * ch;
-          if (j > i) continue;
-          float tv[8];
-          const uint4 raw = *reinterpret_cast<const uint4*>(&sm.th[i][j]);
-          const float2 a0 = unpack_h2(raw.x), a1 = unpack_h2(raw.y), a2 = unpack_h2(raw.z), a3 = unpack_h2(raw.w);
-          tv[0] = a0.x; tv[1] = a0.y; tv[2] = a1.x; tv[3] = a1.y; tv[4] = a2.x; tv[5] = a2.y; tv[6] = a3.x; tv[7] = a3.y;
-          float hi_[8], lo_[8];
-#pragma unroll
-          for (int e = 0; e < 8; ++e) {
-            tv[e] = (j + e <= i) ? tv[e] * sm.sbeta[j + e] : 0.f;
-            hi_[e] = __bfloat162float(__float2bfloat16_rn(tv[e]));
-            lo_[e] = tv[e] - hi_[e];
-          }
-          const uint32_t off = sw128(i, j >> 3);
-          *reinterpret_cast<uint4*>(sm.t16 + off) = make_uint4(pack_h2(tv[0], tv[1]), pack_h2(tv[2], tv[3]), pack_h2(tv[4], tv[5]), pack_h2(tv[6], tv[7]));
-          *reinterpret_cast<uint4*>(sm.thi + off) = pack8(hi_);
-          *reinterpret_cast<uint4*>(sm.tlo + off) = pack8(lo_);
-        }
-      }
-      fence_proxy_async();
-      if (named_bar_or(2, KI_SOLVER_THREADS, !ok)) break;
-      // ---- W^T = (k e^G)^T (T diag beta)^T  and  U0^T = v^T (T diag beta)^T, one thread issues both
+      if (named_bar_or(2, KI_SOLVER_THREADS, !ok)) break;                      // every warp is done with the X image and the v tile
       if (st == 0) {
-        bool go = mbar_wait(&sm.x_full, ci & 1, abort_flag, p.status, 7);
-        go = go && mbar_wait(&sm.v_full, ci & 1, abort_flag, p.status, 8);
-        if (go) {
-          tc_fence_after();
-          constexpr uint32_t idesc_w = umma_idesc_f16(128, KC, 0, 0);
-          constexpr uint32_t idesc_u = umma_idesc_bf16(128, KC, 1, 0);
-          const uint32_t xa = smem_u32(sm.ximg), va = smem_u32(sm.vtile);
-#pragma unroll
-          for (int ks = 0; ks < KC / 16; ++ks)
-            umma_ss(tmem_base + 384, umma_desc_sw128(xa + 32 * ks, 16, 1024), umma_desc_sw128(smem_u32(sm.t16) + 32 * ks, 16, 1024), idesc_w, ks > 0);
-#pragma unroll
-          for (int ks = 0; ks < KC / 16; ++ks) {
-            const uint64_t ad = umma_desc_sw128(va + 2048 * ks, KI_IMG_BYTES / 2, 1024);
-            umma_ss(tmem_base + 448, ad, umma_desc_sw128(smem_u32(sm.thi) + 32 * ks, 16, 1024), idesc_u, ks > 0);
-            umma_ss(tmem_base + 448, ad, umma_desc_sw128(smem_u32(sm.tlo) + 32 * ks, 16, 1024), idesc_u, 1u);
-          }
-        }
-        tc_commit(&sm.w_full);                                       // also arrives when nothing was issued, so no one is left waiting
-      }
-      ok = __all_sync(0xffffffffu, mbar_wait(&sm.w_full, ci & 1, abort_flag, p.status, 9)) && ok;
-      if (ok) {
-        tc_fence_after();
-        // lane = channel of W^T / value column of U0^T: one 128-byte row each
-#pragma unroll
-        for (int which = 0; which < 2; ++which) {
-          uint8_t* dst = rec + (which ? OFF_UT : OFF_WT) + (size_t)(32 * ws + lane) * LDT * 2;
-#pragma unroll
-          for (int half = 0; half < 2; ++half) {
-            uint32_t r[32];
-            tmem_ld32(lane_base + 384 + 64 * which + 32 * half, r);
-            tc_wait_ld();
-#pragma unroll
-            for (int j = 0; j < 32; j += 8)
-              st_global16(dst + (32 * half + j) * 2,
-                          pack_h2(__uint_as_float(r[j]), __uint_as_float(r[j + 1])), pack_h2(__uint_as_float(r[j + 2]), __uint_as_float(r[j + 3])),
-                          pack_h2(__uint_as_float(r[j + 4]), __uint_as_float(r[j + 5])), pack_h2(__uint_as_float(r[j + 6]), __uint_as_float(r[j + 7])));
-          }
-        }
-        tc_fence_before();
-      }
-      if (named_bar_or(2, KI_SOLVER_THREADS, !ok)) break;                      // every lane has read the two accumulators
-      if (st == 0) {
-        mbar_arrive(&sm.x_empty);                                               // the k e^G image and the v tile are free again
+        mbar_arrive(&sm.x_empty);
         if (w + (int)gridDim.x < p.total) {
           int nb, nh, nchunk;
           ki_coords(w + gridDim.x, p.NC, p.H, nb, nh, nchunk);
           mbar_expect_tx(&sm.v_full, KI_IMG_BYTES);
-          tma_load_4d(sm.vtile, &tm_v, &sm.v_full, 0, nchunk * KC, nh, nb);
-          tma_load_4d(sm.vtile + KI_IMG_BYTES / 2, &tm_v, &sm.v_full, 64, nchunk * KC, nh, nb);
+          tma_load_4d(&sm.v[0][0], &tm_v, &sm.v_full, 0, nchunk * KC, nh, nb);
         }
       }
     }
@@ -848,8 +832,7 @@ extern "C" int daisy_b200_kda_chunk_fwd(const void* q, const void* k, const void
   if ((trc = daisy_host::make_tmap_rows_bthd(&tg, g, 4, KD, T, H, B, KC)) != DAISY_OK) return trc;
   if ((trc = daisy_host::make_tmap_rows_bthd(&tq, q, 2, KD, T, H, B, KC)) != DAISY_OK) return trc;
   if ((trc = daisy_host::make_tmap_rows_bthd(&tk, k, 2, KD, T, H, B, KC)) != DAISY_OK) return trc;
-  // v keeps the 128-byte-swizzled form: its tile is a tensor-core operand as it lands
-  if ((trc = daisy_host::make_tmap_bf16_dthb(&tv, v, KD, T, H, B, (uint64_t)H * KD * 2, (uint64_t)KD * 2, (uint64_t)T * H * KD * 2, 64, KC)) != DAISY_OK) return trc;
+  if ((trc = daisy_host::make_tmap_rows_bthd(&tv, v, 2, KD, T, H, B, KC)) != DAISY_OK) return trc;
   KdaIntraParams ip;
   ip.beta = beta; ip.ws = (uint8_t*)workspace;
   ip.T = T; ip.H = H; ip.NC = NC; ip.total = B * H * NC;
