@@ -543,9 +543,13 @@ def run_decode(cfg, warmup, dist, rank, world, peaks, lean=False, extras=True):
         if rank == 0:
             full = DecodeCase(cfg, range(B), nq, dev)
             p1, g1, _ = full.time(warmup, nsteps, None)
-            same = bool(torch.equal(torch.cat(gathered, 0), full.out[warmup]))
+            # the split count follows the per-GPU batch, so the partial sums of a row are merged in a different
+            # order than on one GPU: equal up to fp32 reassociation, compared at one bf16 unit of the outputs
+            diff = (torch.cat(gathered, 0).float() - full.out[warmup].float()).abs().max().item()
+            same = bool(diff <= 2.0 ** -8 * max(1e-3, full.out[warmup].float().abs().max().item()))
             strong = strong_summary(min(p1, g1), per, world)
-            strong.update({"t1_plain_ms": p1, "t1_graph_ms": g1})
+            strong.update({"t1_plain_ms": p1, "t1_graph_ms": g1, "gathered_max_abs_diff": diff,
+                           "splits_single_gpu": full.splits, "splits_per_rank": splits})
             del full
             torch.cuda.empty_cache()
         strong["gathered_equals_single_gpu_result"] = same
