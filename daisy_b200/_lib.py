@@ -29,6 +29,8 @@ SIGNATURES = {
     "daisy_b200_sm_count": (_i, []),
     "daisy_b200_qkv_prep": (_i, [_vp] * 3 + [_i64] * 9 + [_vp] * 2 + [_vp] * 3 + [_vp] + [_i64] * 3 + [_vp] + [_i] * 4 + [_f, _u, _vp]),
     "daisy_b200_qkv_gemm": (_i, [_vp, _i64, _vp, _i64, _vp, _vp, _vp, _vp, _vp] + [_vp, _i64, _vp] + [_i] * 5 + [_f, _u, _vp, _vp]),
+    "daisy_b200_qkv_gemm_ring": (_i, [_vp, _i64, _vp, _i64, _vp, _vp, _vp, _vp, _vp] + [_vp, _i64, _vp] + [_vp, _vp, _i64, _i64, _i64, _i, _i] +
+                                 [_i] * 5 + [_f, _u, _vp, _vp]),
     "daisy_b200_gemm_nt": (_i, [_vp, _i64, _vp, _i64, _vp, _i64, _i, _i, _i, _vp, _vp]),
     "daisy_b200_swa_prefill_workspace_bytes": (_sz, [_i] * 4),
     "daisy_b200_swa_prefill_fwd": (_i, [_vp] * 3 + [_i64] * 9 + [_vp] * 2 + [_vp] + [_i64] * 3 + [_vp] * 2 +
@@ -42,6 +44,11 @@ SIGNATURES = {
     "daisy_b200_swa_decode_step_dev": (_i, [_vp] * 3 + [_i64] * 6 + [_vp] * 2 + [_i64] * 3 + [_vp, _i, _i] +
                                        [_vp] * 2 + [_i] + [_vp, _i64, _i64] + [_vp] * 2 + [_i] * 3 + [_f, _f, _u] +
                                        [_vp, _sz, _i, _vp, _vp]),
+    "daisy_b200_swa_decode_fused_workspace_bytes": (_sz, [_i] * 4),
+    "daisy_b200_swa_decode_step_fused": (_i, [_vp] * 3 + [_i64] * 6 + [_vp] * 2 + [_i64] * 3 + [_i64, _vp, _i, _i] +
+                                         [_vp] * 2 + [_i] + [_vp, _i64, _i64] + [_vp] * 2 + [_vp, _i64, _i64, _vp] +
+                                         [_i] * 3 + [_f, _f, _u] + [_vp, _sz, _i, _vp, _vp]),
+    "daisy_b200_gemm_skinny": (_i, [_vp, _i64, _vp, _i64, _vp, _i64, _i, _i, _i, _vp]),
     "daisy_b200_swa_decode_static_capacity": (_sz, []),
     "daisy_b200_swa_decode_step_static": (_i, [_vp] * 3 + [_i64] * 6 + [_vp] * 2 + [_i64] * 3 + [_i64, _i, _i] +
                                           [_vp] * 2 + [_vp, _i64, _i64] + [_vp] * 2 + [_i] * 3 + [_f, _f, _u] +

@@ -4,8 +4,9 @@ Same constructor, parameters (``qkvo_w [4, dim, dim]`` bf16, ``g_ve``), attribut
 ``AttentionProtocol`` entry points (models/daisy/attention_protocol.py:5-42).  ``forward`` and ``prefill``
 run on hand-written sm_100a kernels of ``libdaisy_b200.so`` only: the merged QKV projection with the RMS
 norm, RoPE and value-embedding gate in its epilogue, the windowed softmax attention, the output projection.
-The single-token ``step`` forms run the ring-cache decode kernels; their two skinny projections are
-``F.linear``.  There is no other code path and no switch that selects one: on a machine without the library
+The single-token ``step`` forms are three launches: the token's merged QKV projection (a weight-streaming
+kernel), the single-launch ring-cache decode (norm, RoPE, value-embedding gate, split-KV attention, merge, ring
+store) and the output projection.  There is no other code path and no switch that selects one: on a machine without the library
 or without a GPU the calls raise.
 
 Masking.  The kernels evaluate the reference's inference mask (models/daisy/daisy_core.py:53-69)
@@ -25,7 +26,6 @@ from typing import Optional
 
 import torch
 from torch import nn, Tensor
-import torch.nn.functional as F
 
 from . import ops
 from ._lib import NORM_Q, NORM_K, NORM_V, ROPE, QKV_DEFAULT
@@ -181,11 +181,17 @@ class B200CausalSelfAttention(nn.Module):
         self.last_k = None
 
     # ------------------------------------------------------------------ helpers
+    def _linear(self, x: Tensor, w: Tensor) -> Tensor:
+        """``F.linear(x, w)`` on this library's kernels: the weight-streaming one for the few rows of a decode step,
+        the tcgen05 GEMM otherwise."""
+        rows = x.numel() // x.size(-1)
+        return ops.gemm_skinny(x, w) if rows <= 64 else ops.gemm_nt(x, w)
+
     def _project(self, x: Tensor):
         self._no_autograd(x)
         B, T = x.size(0), x.size(1)
-        x = x.to(self.qkvo_w.dtype)
-        qkv = F.linear(x, self.qkvo_w[:3].flatten(end_dim=1)).view(B, T, 3 * self.num_heads, self.head_dim)
+        w = self.qkvo_w.detach()
+        qkv = self._linear(x.detach().to(w.dtype), w[:3].flatten(end_dim=1)).view(B, T, 3 * self.num_heads, self.head_dim)
         return qkv.chunk(3, dim=-2)                       # strided views, no copies
 
     @staticmethod
@@ -212,9 +218,10 @@ class B200CausalSelfAttention(nn.Module):
             raise NotImplementedError("daisy_b200 implements the forward pass only: call under torch.no_grad() / "
                                       "inference_mode(), or detach the input and freeze the parameters")
 
-    def _attend(self, x: Tensor, ve: Optional[Tensor], mask):
+    def _attend(self, x: Tensor, ve: Optional[Tensor], mask, ring=None, ring_first: int = 0):
         """Every kernel hand-written: QKV GEMM with norm + RoPE (+ the value-embedding gate) in its epilogue,
-        attention, output GEMM.  Returns ``(y, k', v', q')`` with k', v', q' shaped ``[B,H,T,D]``."""
+        attention, output GEMM.  Returns ``(y, k', v', q')`` with k', v', q' shaped ``[B,H,T,D]``.  ``ring``: one
+        layer of a KV ring the projection's epilogue also fills from position ``ring_first`` on."""
         self._no_autograd(x)
         window, doc_start = mask[0], mask[1]
         in_blocks = len(mask) > 2 and mask[2]
@@ -226,7 +233,7 @@ class B200CausalSelfAttention(nn.Module):
             torch._assert(ve is not None, "ve must be provided when receives_ve=True")
             ve_kw = dict(ve=ve.to(torch.bfloat16), ve_gate_logit=self.g_ve.detach().float().reshape(1))
         qp, kp, vp = ops.qkv_gemm(x.detach().to(w.dtype), w[:3].flatten(end_dim=1), cos, sin, self.num_heads, self.norm_eps,
-                                  **ve_kw)
+                                  ring=ring, ring_first=ring_first, **ve_kw)
         y = ops.swa_attend(qp, kp, vp, window, self.attn_scale, bounded_qk=True, doc_start=doc_start,   # q, k are RMS-normalised
                            window_in_blocks=in_blocks)
         y = ops.gemm_nt(y.view(B, T, self.m_dim), w[3])
@@ -252,6 +259,18 @@ class B200CausalSelfAttention(nn.Module):
             self.last_k = k.transpose(1, 2)
         return y, k, v
 
+    def prefill_ring(self, x: Tensor, ve: Optional[Tensor], cache: B200KVCache, layer: int, attn_mask=None):
+        """``prefill`` that fills layer ``layer`` of the ring cache itself: the projection kernel stores the rows
+        ``KVCache.bulk_write_packed`` would keep (the last ``min(T, W - 1)``, inference/kv_cache.py:57-68) into their
+        slots as it produces them, so the prompt's k, v are neither stacked (models/daisy/daisy_core.py:358-369) nor
+        copied afterwards.  The caller sets the cache position once after the last layer
+        (``cache.set_position(T)``).  Returns ``(y, k, v)`` like ``prefill``."""
+        T = x.size(1)
+        r = min(T, max(cache.W - 1, 0))
+        ring = cache.ring(layer) if r > 0 else None
+        y, k, v, _ = self._attend(x, ve, self._window_of(attn_mask), ring=ring, ring_first=T - r)
+        return y, k, v
+
     def step(self, x, k_ctx: Optional[Tensor], v_ctx: Optional[Tensor], pos: int, ve: Optional[Tensor],
              window: Optional[int]):
         """One token against a chronological context ``[B,n,H,D]`` (models/daisy/attention.py:181-202).
@@ -264,7 +283,7 @@ class B200CausalSelfAttention(nn.Module):
         if kc is not None and kc.dtype != torch.bfloat16:     # reference casts the context to q's dtype
             kc, vc = kc.to(torch.bfloat16), vc.to(torch.bfloat16)
         y, k_new, v_new = self._decode(q, k, v, kc, vc, n, n, pos, ve, window, write_ring=False)
-        y = F.linear(y.view(B, 1, self.m_dim), self.qkvo_w[3])
+        y = self._linear(y.view(B, 1, self.m_dim), self.qkvo_w.detach()[3])
         return y, k_new, v_new
 
     def step_ring(self, x, cache: B200KVCache, layer: int, pos: int, ve: Optional[Tensor], window: Optional[int]):
@@ -276,30 +295,44 @@ class B200CausalSelfAttention(nn.Module):
         kr, vr = cache.ring(layer)
         y, k_new, v_new = self._decode(q, k, v, kr, vr, cache.t, cache.W, pos, ve, window, write_ring=True)
         cache.mark_written(layer)
-        y = F.linear(y.view(B, 1, self.m_dim), self.qkvo_w[3])
+        y = self._linear(y.view(B, 1, self.m_dim), self.qkvo_w.detach()[3])
         return y, k_new, v_new
 
-    def step_ring_dev(self, x, cache: B200KVCache, layer: int, window: Optional[int], write_ring: bool = True):
+    def step_ring_dev(self, x, cache: B200KVCache, layer: int, window: Optional[int], write_ring: bool = True,
+                      ve: Optional[Tensor] = None):
         """``step_ring`` with the position read from ``cache.t_dev`` on the device: nothing in the launch
         sequence depends on the token index, so it can be captured once in a CUDA graph and replayed
-        (``StepRunner.capture_step``).  Position = tokens in the cache, as in ``Generator._step``."""
-        torch._assert(not self.receives_ve, "the graph step does not take value embeddings")
+        (``StepRunner.capture_step``).  Position = tokens in the cache, as in ``Generator._step``.  Three launches,
+        all of this library: the merged QKV projection of the token (weight-streaming kernel), the single-launch
+        ring decode (norm, RoPE, value-embedding gate, split-KV attention, merge, ring store), the output
+        projection."""
+        self._no_autograd(x)
         B = x.size(0)
-        q, k, v = self._project(x)
+        H, D = self.num_heads, self.head_dim
+        w = self.qkvo_w.detach()
+        qkv = ops.gemm_skinny(x.detach().to(w.dtype).view(B, self.m_dim), w[:3].flatten(end_dim=1)).view(B, 1, 3 * H, D)
+        q, k, v = qkv[:, :, :H], qkv[:, :, H:2 * H], qkv[:, :, 2 * H:]
         kr, vr = cache.ring(layer)
-        y = ops.swa_decode_step_dev(q, k, v, kr, vr, cache.t_dev, cache.W, window, self.rotary.cos, self.rotary.sin,
-                                    self.attn_scale, self.norm_eps, QKV_DEFAULT, write_ring=write_ring)
-        return F.linear(y.view(B, 1, self.m_dim), self.qkvo_w[3])
+        ve_kw = {}
+        if self.receives_ve:
+            torch._assert(ve is not None, "ve must be provided when receives_ve=True")
+            ve_kw = dict(ve=ve.to(torch.bfloat16), ve_gate_logit=self.g_ve.detach().float().reshape(1))
+        key = (B, cache.W, window)
+        if getattr(self, "_fused_ws_key", None) != key:                   # zeroed once; every call leaves the tickets zero
+            r = cache.W if not window else min(cache.W, window - 1)
+            self._fused_splits = ops.decode_splits(B, H, r)
+            self._fused_ws = ops.decode_fused_workspace(B, H, D, self._fused_splits, x.device)
+            self._fused_ws_key = key
+        y = ops.swa_decode_step_fused(q, k, v, kr, vr, cache.t_dev, cache.W, window, self.rotary.cos, self.rotary.sin,
+                                      self.attn_scale, self.norm_eps, QKV_DEFAULT, write_ring=write_ring,
+                                      splits=self._fused_splits, workspace=self._fused_ws, **ve_kw)
+        return ops.gemm_skinny(y.view(B, self.m_dim), w[3]).view(B, 1, self.m_dim)
 
     def _decode(self, q, k, v, kc, vc, t, cap, pos, ve, window, write_ring):
         cos, sin = self.rotary.tables(pos + 1)
-        flags = QKV_DEFAULT
+        ve_kw = {}
         if self.receives_ve:
             torch._assert(ve is not None, "ve must be provided when receives_ve=True")
-            vf = v.float()
-            vf = vf * torch.rsqrt(vf.pow(2).mean(-1, keepdim=True) + self.norm_eps)
-            g = torch.sigmoid(self.g_ve).float()
-            v = (g * vf + (1.0 - g) * ve.view_as(v).float()).to(torch.bfloat16)
-            flags = NORM_Q | NORM_K | ROPE
-        return ops.swa_decode_step(q, k, v, kc, vc, t, cap, window, cos[pos], sin[pos], self.attn_scale,
-                                   self.norm_eps, flags, write_ring=write_ring)
+            ve_kw = dict(ve=ve.to(torch.bfloat16), ve_gate_logit=self.g_ve.detach().float().reshape(1))
+        return ops.swa_decode_step_fused(q, k, v, kc, vc, int(t), cap, window, cos[pos], sin[pos], self.attn_scale,
+                                         self.norm_eps, QKV_DEFAULT, write_ring=write_ring, return_new_kv=True, **ve_kw)

@@ -16,6 +16,7 @@
 // (2 x BN columns) let the epilogue of tile i run under the main loop of tile i + 1.
 // All mbarrier waits are bounded (abort flag, DAISY_ETIMEOUT through the status word), as everywhere else.
 #include "common.cuh"
+#include <cuda_fp16.h>
 
 namespace daisy {
 
@@ -47,6 +48,11 @@ struct GemmParams {
   float eps;
   unsigned flags;
   int* status;
+  // optional ring-cache side output: rows t >= ring_first of k' (ring[0]) and v' (ring[1]) also go to slot t % cap of
+  // a [B,H,cap,128] ring with element strides (r_sb, r_sh, r_sr); bf16 or (ring_f16) float16 rows
+  void* ring[2];
+  int64_t r_sb, r_sh, r_sr;
+  int cap, ring_first, ring_f16;
 };
 
 struct GemmBars {
@@ -152,6 +158,7 @@ qkv_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant_
           mbar_arrive(&bars->acc_empty[buf]);
         }
         __nv_bfloat16* dst_row;                                    // this thread's output row (128 bf16)
+        uint8_t* ring_row = nullptr;
         if (p.epi == 1) {
           const int nh = (n0 + half * 128) >> 7;                   // head slot among 3 H
           const int which = nh / p.H, h = nh - which * p.H;
@@ -193,6 +200,11 @@ qkv_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant_
             }
           }
           dst_row = p.out[which] + ((size_t)m * p.H + h) * 128;
+          if (which >= 1 && p.ring[which - 1] && m < p.M) {        // this row's slot in the ring cache, if it is kept
+            const int b = m / p.T, t = m - b * p.T;
+            if (t >= p.ring_first)
+              ring_row = reinterpret_cast<uint8_t*>(p.ring[which - 1]) + ((int64_t)b * p.r_sb + (int64_t)h * p.r_sh + (int64_t)(t % p.cap) * p.r_sr) * 2;
+          }
         } else {
           dst_row = p.c + (size_t)m * p.ldc + n0 + half * 128;
         }
@@ -220,6 +232,21 @@ qkv_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant_
             const unsigned long long base = __shfl_sync(0xffffffffu, (unsigned long long)reinterpret_cast<uintptr_t>(dst_row), src_lane);
             const int mm = __shfl_sync(0xffffffffu, m, src_lane);
             if (mm < p.M) *reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(base) + (lane & 15) * 16) = val;
+            if (p.epi == 1 && p.ring[0]) {                         // warp-uniform: a ring is attached to this call
+              const unsigned long long rb = __shfl_sync(0xffffffffu, (unsigned long long)reinterpret_cast<uintptr_t>(ring_row), src_lane);
+              if (rb) {
+                uint4 rv = val;
+                if (p.ring_f16) {                                  // the ring keeps float16 rows
+                  float f[8];
+                  unpack8(val, f);
+                  const __half2 h0 = __floats2half2_rn(f[0], f[1]), h1 = __floats2half2_rn(f[2], f[3]);
+                  const __half2 h2 = __floats2half2_rn(f[4], f[5]), h3 = __floats2half2_rn(f[6], f[7]);
+                  rv = make_uint4(*reinterpret_cast<const uint32_t*>(&h0), *reinterpret_cast<const uint32_t*>(&h1),
+                                  *reinterpret_cast<const uint32_t*>(&h2), *reinterpret_cast<const uint32_t*>(&h3));
+                }
+                *reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(rb) + (lane & 15) * 16) = rv;
+              }
+            }
           }
           __syncwarp();
         }
@@ -287,10 +314,27 @@ extern "C" int daisy_b200_qkv_gemm(const void* x, int64_t ldx, const void* w_qkv
                                    const void* ve, int64_t ve_ld, const float* ve_gate_logit,
                                    int B, int T, int H, int D, int dim, float eps, unsigned flags,
                                    int* status_word, void* stream) {
+  return daisy_b200_qkv_gemm_ring(x, ldx, w_qkv, ldw, cos, sin, q_out, k_out, v_out, ve, ve_ld, ve_gate_logit,
+                                  nullptr, nullptr, 0, 0, 0, 0, 0, B, T, H, D, dim, eps, flags, status_word, stream);
+}
+
+extern "C" int daisy_b200_qkv_gemm_ring(const void* x, int64_t ldx, const void* w_qkv, int64_t ldw,
+                                        const float* cos, const float* sin,
+                                        void* q_out, void* k_out, void* v_out,
+                                        const void* ve, int64_t ve_ld, const float* ve_gate_logit,
+                                        void* ring_k, void* ring_v, int64_t r_sb, int64_t r_sh, int64_t r_sr,
+                                        int cap, int ring_first,
+                                        int B, int T, int H, int D, int dim, float eps, unsigned flags,
+                                        int* status_word, void* stream) {
   if (!q_out || !k_out || !v_out || B <= 0 || T <= 0 || H <= 0) return DAISY_EINVAL;
   if (D != DAISY_HEAD_DIM) return DAISY_EUNSUPPORTED;
   if ((int64_t)B * T >= (int64_t)1 << 31) return DAISY_EUNSUPPORTED;
-  if (flags & ~DAISY_QKV_DEFAULT) return DAISY_EINVAL;
+  if (flags & ~(DAISY_QKV_DEFAULT | DAISY_CACHE_FP16)) return DAISY_EINVAL;
+  if ((ring_k == nullptr) != (ring_v == nullptr)) return DAISY_EINVAL;
+  if (ring_k) {
+    if (cap <= 0 || ring_first < 0 || T - ring_first > cap) return DAISY_EINVAL;          // the kept rows would alias in the ring
+    if (!daisy_aligned16(ring_k) || !daisy_aligned16(ring_v) || ((r_sb | r_sh | r_sr) & 7)) return DAISY_EALIGN;
+  }
   if ((flags & DAISY_ROPE) && (!cos || !sin)) return DAISY_EINVAL;
   if ((flags & DAISY_ROPE) && (!daisy_aligned16(cos) || !daisy_aligned16(sin))) return DAISY_EALIGN;
   if (!daisy_aligned16(q_out) || !daisy_aligned16(k_out) || !daisy_aligned16(v_out)) return DAISY_EALIGN;
@@ -299,6 +343,8 @@ extern "C" int daisy_b200_qkv_gemm(const void* x, int64_t ldx, const void* w_qkv
   p.ve = (const __nv_bfloat16*)ve; p.ve_ld = ve_ld; p.ve_gate_logit = ve_gate_logit;
   p.M = B * T; p.N = 3 * H * D; p.K = dim; p.epi = 1;
   p.out[0] = (__nv_bfloat16*)q_out; p.out[1] = (__nv_bfloat16*)k_out; p.out[2] = (__nv_bfloat16*)v_out;
-  p.cos = cos; p.sin = sin; p.T = T; p.H = H; p.eps = eps; p.flags = flags; p.status = status_word;
+  p.cos = cos; p.sin = sin; p.T = T; p.H = H; p.eps = eps; p.flags = flags & DAISY_QKV_DEFAULT; p.status = status_word;
+  p.ring[0] = ring_k; p.ring[1] = ring_v; p.r_sb = r_sb; p.r_sh = r_sh; p.r_sr = r_sr;
+  p.cap = cap; p.ring_first = ring_first; p.ring_f16 = (flags & DAISY_CACHE_FP16) ? 1 : 0;
   return gemm_common(x, ldx, w_qkv, ldw, p, stream);
 }

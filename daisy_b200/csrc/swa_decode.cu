@@ -50,6 +50,13 @@ struct DecodeParams {
   const long long* t_dev;
   int window, table_rows;
   int* status;
+  // single-launch form: the last split CTA of a (batch, head) to finish merges the partials itself; `tickets` holds
+  // one counter per (batch, head), zero between calls
+  int* tickets;
+  // value-embedding gate on the new token's v (after the norm): v = g v + (1 - g) ve, g = sigmoid(*ve_gate)
+  const __nv_bfloat16* ve;
+  int64_t ve_sb, ve_sh;
+  const float* ve_gate;
 };
 
 // Row range and table rows of this step: the host's values, or derived from the device-side position.
@@ -79,6 +86,9 @@ __device__ __forceinline__ DecodeGeom decode_geom(const DecodeParams& p) {
 }
 
 template <bool DEV, bool F16>
+__device__ __forceinline__ void decode_combine_body(const DecodeParams& p, const DecodeGeom& g, int h, int b, bool coherent);
+
+template <bool DEV, bool F16, bool FUSED>
 __global__ void __launch_bounds__(128) swa_decode_partial_kernel(const DecodeParams p) {
   const int s = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, hw = lane >> 4, sub = lane & 15;
@@ -174,6 +184,24 @@ __global__ void __launch_bounds__(128) swa_decode_partial_kernel(const DecodePar
   const int64_t slot = ((int64_t)b * p.H + h) * p.splits + s;
   p.ws_acc[slot * DAISY_HEAD_DIM + d] = a;
   if (d == 0) { p.ws_ml[slot * 2] = M; p.ws_ml[slot * 2 + 1] = L; }
+  if (FUSED) {
+    // ticket per (batch, head): whoever draws the last one knows every other split's partials are in memory (each
+    // CTA fences its stores before drawing) and merges them; it also puts the counter back to zero for the next call
+    __shared__ int last;
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      int* tk = p.tickets + b * p.H + h;
+      const int drawn = atomicAdd(tk, 1);
+      last = (drawn == p.splits - 1);
+      if (last) *tk = 0;
+    }
+    __syncthreads();
+    if (last) {
+      __threadfence();
+      decode_combine_body<DEV, F16>(p, g, h, b, true);
+    }
+  }
 }
 
 __device__ __forceinline__ float block128_sum(float x, float* red) {
@@ -185,10 +213,12 @@ __device__ __forceinline__ float block128_sum(float x, float* red) {
   return (red[0] + red[1]) + (red[2] + red[3]);
 }
 
+// Merge of the split partials with the new token (thread = head-dim element, 128 threads): normalises / rotates the
+// new q, k, v, adds the new row's own score, writes the output row and stores the new k, v into the ring.
+// `coherent`: the partials were written by other SMs during this same launch -- read them past the L1.
 template <bool DEV, bool F16>
-__global__ void __launch_bounds__(128) swa_decode_combine_kernel(const DecodeParams p) {
-  const int h = blockIdx.x, b = blockIdx.y, d = threadIdx.x;
-  const DecodeGeom g = decode_geom<DEV>(p);
+__device__ __forceinline__ void decode_combine_body(const DecodeParams& p, const DecodeGeom& g, int h, int b, bool coherent) {
+  const int d = threadIdx.x;
   __shared__ float red[4];
   __shared__ float xq[DAISY_HEAD_DIM], xk[DAISY_HEAD_DIM];
   float q = __bfloat162float(p.q[b * p.q_sb + h * p.q_sh + d]);
@@ -198,6 +228,10 @@ __global__ void __launch_bounds__(128) swa_decode_combine_kernel(const DecodePar
   if (p.flags & DAISY_NORM_Q) q *= rsqrtf(block128_sum(q * q, red) * inv_d + p.eps);
   if (p.flags & DAISY_NORM_K) k *= rsqrtf(block128_sum(k * k, red) * inv_d + p.eps);
   if (p.flags & DAISY_NORM_V) v *= rsqrtf(block128_sum(v * v, red) * inv_d + p.eps);
+  if (p.ve) {
+    const float gate = 1.0f / (1.0f + __expf(-*p.ve_gate));
+    v = gate * v + (1.0f - gate) * __bfloat162float(p.ve[b * p.ve_sb + h * p.ve_sh + d]);
+  }
   if (p.flags & DAISY_ROPE) {
     xq[d] = q; xk[d] = k;
     __syncthreads();
@@ -214,14 +248,16 @@ __global__ void __launch_bounds__(128) swa_decode_combine_kernel(const DecodePar
   const float s_self = block128_sum(q * p.qscale * k, red);
 
   const int64_t base = ((int64_t)b * p.H + h) * p.splits;
+  auto ml = [&](int64_t i) { return coherent ? __ldcg(p.ws_ml + i) : p.ws_ml[i]; };
   float M = s_self;
-  for (int s = 0; s < p.splits; ++s) M = fmaxf(M, p.ws_ml[(base + s) * 2]);
+  for (int s = 0; s < p.splits; ++s) M = fmaxf(M, ml((base + s) * 2));
   float w = fast_exp2(s_self - M);
   float num = w * v, den = w;
   for (int s = 0; s < p.splits; ++s) {
-    const float f = fast_exp2(p.ws_ml[(base + s) * 2] - M);
-    num = fmaf(f, p.ws_acc[(base + s) * DAISY_HEAD_DIM + d], num);
-    den = fmaf(f, p.ws_ml[(base + s) * 2 + 1], den);
+    const float f = fast_exp2(ml((base + s) * 2) - M);
+    const float a = coherent ? __ldcg(p.ws_acc + (base + s) * DAISY_HEAD_DIM + d) : p.ws_acc[(base + s) * DAISY_HEAD_DIM + d];
+    num = fmaf(f, a, num);
+    den = fmaf(f, ml((base + s) * 2 + 1), den);
   }
   p.out[b * p.o_sb + h * p.o_sh + d] = __float2bfloat16_rn(num / den);
   const int64_t row = ((int64_t)b * p.H + h) * DAISY_HEAD_DIM + d;
@@ -232,6 +268,11 @@ __global__ void __launch_bounds__(128) swa_decode_combine_kernel(const DecodePar
     if (F16) { reinterpret_cast<__half*>(p.kc)[at] = kh; reinterpret_cast<__half*>(p.vc)[at] = vh; }
     else     { p.kc[at] = kb; p.vc[at] = vb; }
   }
+}
+
+template <bool DEV, bool F16>
+__global__ void __launch_bounds__(128) swa_decode_combine_kernel(const DecodeParams p) {
+  decode_combine_body<DEV, F16>(p, decode_geom<DEV>(p), blockIdx.x, blockIdx.y, false);
 }
 
 }  // namespace daisy
@@ -256,6 +297,14 @@ extern "C" size_t daisy_b200_swa_decode_workspace_bytes(int B, int H, int D, int
   return (size_t)B * H * splits * (D + 2) * sizeof(float);
 }
 
+extern "C" size_t daisy_b200_swa_decode_fused_workspace_bytes(int B, int H, int D, int splits) {
+  const size_t base = daisy_b200_swa_decode_workspace_bytes(B, H, D, splits);
+  if (!base) return 0;
+  return base + (((size_t)B * H * sizeof(int)) + 15) / 16 * 16;       // + one ticket per (batch, head)
+}
+
+struct DecodeExtras { bool fused; const void* ve; int64_t ve_sb, ve_sh; const float* ve_gate; };
+
 static int decode_launch(const void* q_new, const void* k_new, const void* v_new,
                          int64_t q_sb, int64_t q_sh, int64_t k_sb, int64_t k_sh, int64_t v_sb, int64_t v_sh,
                          void* kcache, void* vcache, int64_t c_sb, int64_t c_sh, int64_t c_sr,
@@ -263,7 +312,9 @@ static int decode_launch(const void* q_new, const void* k_new, const void* v_new
                          const float* cos_row, const float* sin_row,
                          void* out, int64_t o_sb, int64_t o_sh, void* k_new_out, void* v_new_out,
                          int B, int H, int D, float scale, float eps, unsigned flags,
-                         void* workspace, size_t workspace_bytes, int splits, int* status_word, void* stream) {
+                         void* workspace, size_t workspace_bytes, int splits, int* status_word, void* stream,
+                         const DecodeExtras ex = DecodeExtras{false, nullptr, 0, 0, nullptr}) {
+  const bool fused = ex.fused;
   if (!q_new || !k_new || !v_new || !out || B <= 0 || H <= 0 || t < 0 || cap < 0 || splits <= 0) return DAISY_EINVAL;
   if (D != DAISY_HEAD_DIM) return DAISY_EUNSUPPORTED;
   if (B > 65535 || H > 65535) return DAISY_EUNSUPPORTED;
@@ -275,7 +326,9 @@ static int decode_launch(const void* q_new, const void* k_new, const void* v_new
   if (window > 0 && r > (int64_t)window - 1) r = window - 1;
   if ((r > 0 || (flags & DAISY_WRITE_RING)) && (!kcache || !vcache)) return DAISY_EINVAL;
   if (!workspace) return DAISY_EINVAL;
-  if (workspace_bytes < daisy_b200_swa_decode_workspace_bytes(B, H, D, splits)) return DAISY_EWORKSPACE;
+  if (workspace_bytes < (fused ? daisy_b200_swa_decode_fused_workspace_bytes(B, H, D, splits) : daisy_b200_swa_decode_workspace_bytes(B, H, D, splits)))
+    return DAISY_EWORKSPACE;
+  if (ex.ve && (!ex.ve_gate || (flags & DAISY_NORM_V) == 0 || !daisy_aligned16(ex.ve) || ((ex.ve_sb | ex.ve_sh) & 7))) return DAISY_EINVAL;
   if (!daisy_aligned16(q_new) || !daisy_aligned16(k_new) || !daisy_aligned16(v_new) || !daisy_aligned16(workspace) ||
       ((q_sb | q_sh | k_sb | k_sh | v_sb | v_sh) & 7))
     return DAISY_EALIGN;
@@ -304,12 +357,20 @@ static int decode_launch(const void* q_new, const void* k_new, const void* v_new
   if (rps == 0) rps = 32;
   p.rows_per_split = rps;
   p.t_dev = (const long long*)t_dev; p.window = window; p.table_rows = table_rows; p.status = status_word;
+  p.tickets = fused ? reinterpret_cast<int*>(reinterpret_cast<char*>(workspace) + daisy_b200_swa_decode_workspace_bytes(B, H, D, splits)) : nullptr;
+  p.ve = (const __nv_bfloat16*)ex.ve; p.ve_sb = ex.ve_sb; p.ve_sh = ex.ve_sh; p.ve_gate = ex.ve_gate;
 
   cudaStream_t st = (cudaStream_t)stream;
   const bool f16 = (flags & DAISY_CACHE_FP16) != 0;
   const dim3 g1(splits, H, B), g2(H, B);
-  if (t_dev) { if (f16) swa_decode_partial_kernel<true, true><<<g1, 128, 0, st>>>(p); else swa_decode_partial_kernel<true, false><<<g1, 128, 0, st>>>(p); }
-  else       { if (f16) swa_decode_partial_kernel<false, true><<<g1, 128, 0, st>>>(p); else swa_decode_partial_kernel<false, false><<<g1, 128, 0, st>>>(p); }
+  if (fused) {                                                     // one launch: the last split CTA of a (batch, head) merges
+    if (t_dev) { if (f16) swa_decode_partial_kernel<true, true, true><<<g1, 128, 0, st>>>(p); else swa_decode_partial_kernel<true, false, true><<<g1, 128, 0, st>>>(p); }
+    else       { if (f16) swa_decode_partial_kernel<false, true, true><<<g1, 128, 0, st>>>(p); else swa_decode_partial_kernel<false, false, true><<<g1, 128, 0, st>>>(p); }
+    DAISY_CHECK_LAUNCH();
+    return DAISY_OK;
+  }
+  if (t_dev) { if (f16) swa_decode_partial_kernel<true, true, false><<<g1, 128, 0, st>>>(p); else swa_decode_partial_kernel<true, false, false><<<g1, 128, 0, st>>>(p); }
+  else       { if (f16) swa_decode_partial_kernel<false, true, false><<<g1, 128, 0, st>>>(p); else swa_decode_partial_kernel<false, false, false><<<g1, 128, 0, st>>>(p); }
   DAISY_CHECK_LAUNCH();
   if (t_dev) { if (f16) swa_decode_combine_kernel<true, true><<<g2, 128, 0, st>>>(p); else swa_decode_combine_kernel<true, false><<<g2, 128, 0, st>>>(p); }
   else       { if (f16) swa_decode_combine_kernel<false, true><<<g2, 128, 0, st>>>(p); else swa_decode_combine_kernel<false, false><<<g2, 128, 0, st>>>(p); }
@@ -348,6 +409,24 @@ extern "C" int daisy_b200_swa_decode_step_dev(const void* q_new, const void* k_n
   return decode_launch(q_new, k_new, v_new, q_sb, q_sh, k_sb, k_sh, v_sb, v_sh, kcache, vcache, c_sb, c_sh, c_sr,
                        0, t_dev, table_rows, cap, window, cos_table, sin_table, out, o_sb, o_sh, k_new_out, v_new_out,
                        B, H, D, scale, eps, flags, workspace, workspace_bytes, splits, status_word, stream);
+}
+
+extern "C" int daisy_b200_swa_decode_step_fused(const void* q_new, const void* k_new, const void* v_new,
+                                                int64_t q_sb, int64_t q_sh, int64_t k_sb, int64_t k_sh,
+                                                int64_t v_sb, int64_t v_sh,
+                                                void* kcache, void* vcache, int64_t c_sb, int64_t c_sh, int64_t c_sr,
+                                                int64_t t, const int64_t* t_dev, int cap, int window,
+                                                const float* cos, const float* sin, int table_rows,
+                                                void* out, int64_t o_sb, int64_t o_sh,
+                                                void* k_new_out, void* v_new_out,
+                                                const void* ve, int64_t ve_sb, int64_t ve_sh, const float* ve_gate_logit,
+                                                int B, int H, int D, float scale, float eps, unsigned flags,
+                                                void* workspace, size_t workspace_bytes, int splits,
+                                                int* status_word, void* stream) {
+  return decode_launch(q_new, k_new, v_new, q_sb, q_sh, k_sb, k_sh, v_sb, v_sh, kcache, vcache, c_sb, c_sh, c_sr,
+                       t_dev ? 0 : t, t_dev, t_dev ? table_rows : 0, cap, window, cos, sin, out, o_sb, o_sh, k_new_out, v_new_out,
+                       B, H, D, scale, eps, flags, workspace, workspace_bytes, splits, status_word, stream,
+                       DecodeExtras{true, ve, ve_sb, ve_sh, ve_gate_logit});
 }
 
 // ---------------------------------------------------------------------------------------------

@@ -1,7 +1,8 @@
 """Host orchestration of prefill and per-token steps over the ring cache.
 
 Mirror of the reference ``Generator._prefill`` / ``Generator._step`` (inference/generate.py:220-248) for a
-stack of attention layers: prefill fills the ring layer by layer (the rows ``bulk_write_packed`` would write); each step hands every
+stack of attention layers: prefill fills the ring layer by layer from inside the projection kernel (the rows
+``bulk_write_packed`` would write, no copy pass); each step hands every
 layer the ring itself (no per-layer chronological ``view`` copy, no separate ``write``) and advances once.
 Sampling, embeddings and the MLPs are outside this path; the runner works on hidden states.
 """
@@ -36,8 +37,8 @@ class StepRunner:
         the cache receives the rows ``Generator._prefill`` stores through ``bulk_write_packed``."""
         T = x.size(1)
         for i, a in enumerate(self.layers):
-            x, k, v = a.prefill(x, None, attn_mask=WindowMask(self.window))
-            self.cache.bulk_write_layer(i, k, v, T)               # same rows and slots as bulk_write_packed
+            # the projection's epilogue stores the rows bulk_write_packed keeps straight into their ring slots
+            x, _, _ = a.prefill_ring(x, None, self.cache, i, attn_mask=WindowMask(self.window))
         self.cache.set_position(T)
         return x
 

@@ -89,11 +89,14 @@ def qkv_prep(q, k, v, cos, sin, eps: float, flags: int = QKV_DEFAULT, bhtd: bool
 
 
 def qkv_gemm(x, w_qkv, cos, sin, num_heads: int, eps: float, flags: int = QKV_DEFAULT,
-             ve: Optional[torch.Tensor] = None, ve_gate_logit: Optional[torch.Tensor] = None):
+             ve: Optional[torch.Tensor] = None, ve_gate_logit: Optional[torch.Tensor] = None,
+             ring: Optional[Tuple[torch.Tensor, torch.Tensor]] = None, ring_first: int = 0):
     """``x [B,T,dim]`` times the merged ``w_qkv [3*H*128, dim]`` (``qkvo_w[:3].flatten(end_dim=1)``) with the RMS
     norm and RoPE applied in the GEMM epilogue: returns prepared ``q', k', v'`` as ``[B,T,H,128]`` contiguous.
     ``ve [B,T,H*128]`` (bf16) with ``ve_gate_logit`` (float32 scalar on the device) mixes the value embedding into
-    the normalised v: ``v' = g * norm(v) + (1 - g) * ve``."""
+    the normalised v: ``v' = g * norm(v) + (1 - g) * ve``.  ``ring = (k_ring, v_ring)``, one layer of a KV ring
+    ``[B,H,cap,128]`` (bf16 or float16): the epilogue also stores rows ``t >= ring_first`` of k', v' into slot
+    ``t % cap`` -- the rows ``KVCache.bulk_write_packed`` keeps when ``ring_first = T - min(T, cap - 1)``."""
     _req(x, "x"); _req(w_qkv, "w_qkv")
     B, T, dim = x.shape
     H, D = int(num_heads), 128
@@ -113,12 +116,21 @@ def qkv_gemm(x, w_qkv, cos, sin, num_heads: int, eps: float, flags: int = QKV_DE
         _req(ve2, "ve")
         ve_args = (ve2.data_ptr(), ve2.stride(0), ve_gate_logit.data_ptr())
     outs = [torch.empty(B, T, H, D, dtype=torch.bfloat16, device=x.device) for _ in range(3)]
-    rc = _lib.lib().daisy_b200_qkv_gemm(
+    ring_args = (None, None, 0, 0, 0, 0, 0)
+    if ring is not None:
+        rk, rv = ring
+        f16 = rk.dtype == torch.float16
+        _req(rk, "ring k", rk.dtype if f16 else torch.bfloat16); _req(rv, "ring v", rk.dtype)
+        if rk.shape != rv.shape or rk.stride() != rv.stride() or rk.shape[0] != B or rk.shape[1] != H or rk.shape[3] != D:
+            raise ValueError(f"ring tensors must both be [{B}, {H}, cap, {D}] with equal strides")
+        ring_args = (rk.data_ptr(), rv.data_ptr(), rk.stride(0), rk.stride(1), rk.stride(2), rk.shape[2], int(ring_first))
+        flags = flags | (_lib.CACHE_FP16 if f16 else 0)
+    rc = _lib.lib().daisy_b200_qkv_gemm_ring(
         x2.data_ptr(), x2.stride(0), w_qkv.data_ptr(), w_qkv.stride(0),
         cos.data_ptr() if cos is not None else None, sin.data_ptr() if sin is not None else None,
-        outs[0].data_ptr(), outs[1].data_ptr(), outs[2].data_ptr(), *ve_args, B, T, H, D, dim, eps, flags,
+        outs[0].data_ptr(), outs[1].data_ptr(), outs[2].data_ptr(), *ve_args, *ring_args, B, T, H, D, dim, eps, flags,
         status_word(x.device).data_ptr(), _stream(x))
-    _lib.check(rc, "daisy_b200_qkv_gemm")
+    _lib.check(rc, "daisy_b200_qkv_gemm_ring")
     return tuple(outs)
 
 
@@ -135,6 +147,23 @@ def gemm_nt(x, w):
                                        M, N, K, status_word(x.device).data_ptr(), _stream(x))
     _lib.check(rc, "daisy_b200_gemm_nt")
     return c.view(*x.shape[:-1], N)
+
+
+def gemm_skinny(x, w, out: Optional[torch.Tensor] = None):
+    """``F.linear(x, w)`` for at most 64 rows (a decode step's projections): weight-streaming kernel, bf16 in and out."""
+    _req(x, "x"); _req(w, "w")
+    K = x.shape[-1]
+    x2 = x.reshape(-1, K)
+    if x2.stride(1) != 1:
+        x2 = x2.contiguous()
+    M, N = x2.shape[0], w.shape[0]
+    if out is None:
+        out = torch.empty(*x.shape[:-1], N, dtype=torch.bfloat16, device=x.device)
+    y2 = out.view(M, N)
+    rc = _lib.lib().daisy_b200_gemm_skinny(x2.data_ptr(), x2.stride(0), w.data_ptr(), w.stride(0), y2.data_ptr(), y2.stride(0),
+                                           M, N, K, _stream(x))
+    _lib.check(rc, "daisy_b200_gemm_skinny")
+    return out
 
 
 def _doc_arg(doc_start: Optional[torch.Tensor], B: int, T: int, device):
@@ -307,6 +336,72 @@ def swa_decode_step_dev(q_new, k_new, v_new, kcache, vcache, t_dev: torch.Tensor
         status_word(q_new.device).data_ptr(), _stream(q_new))
     _lib.check(rc, "daisy_b200_swa_decode_step_dev")
     return out
+
+
+def decode_fused_workspace(B: int, H: int, D: int, splits: int, device) -> torch.Tensor:
+    """Workspace of :func:`swa_decode_step_fused`, zero-filled: its tail holds one ticket per (batch, head) that must
+    be zero before the first call (every call leaves it zero)."""
+    n = _lib.lib().daisy_b200_swa_decode_fused_workspace_bytes(B, H, D, splits)
+    return torch.zeros(n, dtype=torch.uint8, device=device)
+
+
+def swa_decode_step_fused(q_new, k_new, v_new, kcache, vcache, t, cap: int, window: Optional[int], cos, sin,
+                          scale: float = ATTN_SCALE, eps: float = 1.1920929e-07, flags: int = QKV_DEFAULT,
+                          write_ring: bool = True, splits: Optional[int] = None, workspace: Optional[torch.Tensor] = None,
+                          out: Optional[torch.Tensor] = None, ve: Optional[torch.Tensor] = None,
+                          ve_gate_logit: Optional[torch.Tensor] = None, return_new_kv: bool = False):
+    """The decode step as one launch.  ``t``: an int (``cos, sin`` are then the table rows of the position) or an
+    int64 CUDA tensor of one element (``cos, sin`` are whole tables, the kernels pick row ``t[0]``).  ``ve``
+    ``[B,1,H,D]`` with ``ve_gate_logit`` mixes the value embedding into the new token's normalised v.  ``workspace``
+    must come from :func:`decode_fused_workspace` (zeroed tickets).  ``kcache`` may be None (no context yet, nothing
+    to store).  Returns ``y [B,1,H,D]``, or ``(y, k', v')`` with ``return_new_kv``."""
+    for n, x in (("q_new", q_new), ("k_new", k_new), ("v_new", v_new)):
+        _req(x, n)
+    B, one, H, D = q_new.shape
+    assert one == 1
+    cache_f16 = kcache is not None and kcache.dtype == torch.float16
+    if kcache is not None:
+        _req(kcache, "kcache", kcache.dtype if cache_f16 else torch.bfloat16)
+        _req(vcache, "vcache", kcache.dtype if cache_f16 else torch.bfloat16)
+        assert kcache.shape == vcache.shape and kcache.stride() == vcache.stride()
+        c_args = (kcache.data_ptr(), vcache.data_ptr(), kcache.stride(0), kcache.stride(1), kcache.stride(2))
+    else:
+        c_args = (None, None, 0, 0, 0)
+    on_dev = isinstance(t, torch.Tensor)
+    if on_dev and not (t.is_cuda and t.dtype == torch.int64 and t.numel() == 1):
+        raise ValueError("a device-side position must be an int64 CUDA tensor with one element")
+    cos, sin = _f32c(cos, "cos"), _f32c(sin, "sin")
+    L = _lib.lib()
+    r = min(cap, int(t)) if not on_dev else cap
+    if window:
+        r = min(r, window - 1)
+    if splits is None:
+        splits = decode_splits(B, H, r)
+    if workspace is None:
+        workspace = decode_fused_workspace(B, H, D, splits, q_new.device)
+    if out is None:
+        out = torch.empty(B, 1, H, D, dtype=torch.bfloat16, device=q_new.device)
+    ve_args = (None, 0, 0, None)
+    if ve is not None:
+        ve = ve.view(B, 1, H, D)
+        _req(ve, "ve")
+        if ve_gate_logit is None or not (ve_gate_logit.is_cuda and ve_gate_logit.dtype == torch.float32 and ve_gate_logit.numel() == 1):
+            raise ValueError("ve needs ve_gate_logit, a float32 scalar CUDA tensor")
+        ve_args = (ve.data_ptr(), ve.stride(0), ve.stride(2), ve_gate_logit.data_ptr())
+    k_o = torch.empty(B, 1, H, D, dtype=torch.bfloat16, device=q_new.device) if return_new_kv else None
+    v_o = torch.empty(B, 1, H, D, dtype=torch.bfloat16, device=q_new.device) if return_new_kv else None
+    rc = L.daisy_b200_swa_decode_step_fused(
+        q_new.data_ptr(), k_new.data_ptr(), v_new.data_ptr(),
+        q_new.stride(0), q_new.stride(2), k_new.stride(0), k_new.stride(2), v_new.stride(0), v_new.stride(2),
+        *c_args,
+        0 if on_dev else int(t), t.data_ptr() if on_dev else None, int(cap), int(window or 0),
+        cos.data_ptr(), sin.data_ptr(), cos.shape[0] if on_dev else 0,
+        out.data_ptr(), out.stride(0), out.stride(2), k_o.data_ptr() if return_new_kv else None,
+        v_o.data_ptr() if return_new_kv else None, *ve_args,
+        B, H, D, scale, eps, flags | (WRITE_RING if write_ring else 0) | (_lib.CACHE_FP16 if cache_f16 else 0),
+        workspace.data_ptr(), workspace.numel(), splits, status_word(q_new.device).data_ptr(), _stream(q_new))
+    _lib.check(rc, "daisy_b200_swa_decode_step_fused")
+    return (out, k_o, v_o) if return_new_kv else out
 
 
 def ring_copy_rows(ring_bhcd, lin_bhnd, first_pos: int, to_ring: bool) -> None:

@@ -116,10 +116,31 @@ int daisy_b200_qkv_gemm(const void* x, int64_t ldx, const void* w_qkv, int64_t l
                         int B, int T, int H, int D, int dim, float eps, unsigned flags,
                         int* status_word, void* stream);
 
+/* The same projection for a prompt whose keys and values also enter the ring-buffer KV cache: besides k_out, v_out the
+ * epilogue stores rows t >= ring_first of k' and v' straight into slot t % cap of one layer of the ring (logical
+ * [B,H,cap,D], element strides r_sb, r_sh, r_sr; bf16 rows, or float16 with DAISY_CACHE_FP16 in flags).  Replaces the
+ * stacking of the per-layer k, v in DaisyCore.prefill (models/daisy/daisy_core.py:358-369) followed by
+ * KVCache.bulk_write_packed (inference/kv_cache.py:57-68), which keeps the last min(T, cap - 1) rows: pass
+ * ring_first = T - min(T, cap - 1).  T - ring_first must not exceed cap.  ring_k = ring_v = NULL: no ring output. */
+int daisy_b200_qkv_gemm_ring(const void* x, int64_t ldx, const void* w_qkv, int64_t ldw,
+                             const float* cos, const float* sin,
+                             void* q_out, void* k_out, void* v_out,
+                             const void* ve, int64_t ve_ld, const float* ve_gate_logit,
+                             void* ring_k, void* ring_v, int64_t r_sb, int64_t r_sh, int64_t r_sr,
+                             int cap, int ring_first,
+                             int B, int T, int H, int D, int dim, float eps, unsigned flags,
+                             int* status_word, void* stream);
+
 /* C[M,N] = X[M,K] W[N,K]^T, bf16 in and out, fp32 accumulation: F.linear(y, qkvo_w[3]), the output projection
  * (models/daisy/attention.py:149).  K a multiple of 64, N a multiple of 128; ld* are row strides in elements. */
 int daisy_b200_gemm_nt(const void* x, int64_t ldx, const void* w, int64_t ldw, void* c, int64_t ldc,
                        int M, int N, int K, int* status_word, void* stream);
+
+/* y[M,N] = x[M,K] W[N,K]^T for M <= 64 rows: the projections of a single decode token, F.linear(x, qkvo_w[:3]
+ * flattened) and F.linear(y, qkvo_w[3]) with x [B,1,dim] (models/daisy/attention.py:119,201).  bf16 in and out, fp32
+ * accumulation; weight-streaming (HBM-bound), no tensor cores.  K a multiple of 8; ld* are row strides in elements. */
+int daisy_b200_gemm_skinny(const void* x, int64_t ldx, const void* w, int64_t ldw, void* y, int64_t ldy,
+                           int M, int N, int K, void* stream);
 
 /* ---------------------------------------------------------------------------------------------
  * Sliding-window causal softmax attention, prefill form.
@@ -215,6 +236,31 @@ int daisy_b200_swa_decode_step_dev(const void* q_new, const void* k_new, const v
                                    int B, int H, int D, float scale, float eps, unsigned flags,
                                    void* workspace, size_t workspace_bytes, int splits,
                                    int* status_word, void* stream);
+
+/* The decode step as ONE launch: the last split CTA of a (batch, head) to finish merges that pair's partials itself
+ * (a ticket per pair in the workspace), so a decode layer is projection -> this -> projection.  Same arguments as
+ * daisy_b200_swa_decode_step plus:
+ *   t_dev        NULL: `t` is the position and cos / sin are the table ROWS of that position; non-NULL: the position is
+ *                read from *t_dev on the device and cos / sin are the table bases with table_rows rows (the form of
+ *                daisy_b200_swa_decode_step_dev, for CUDA-graph replays)
+ *   ve, ve_sb, ve_sh, ve_gate_logit   NULL, or the layer's value embedding for the new token, logical [B,1,H,D] bf16:
+ *                v = g * norm(v) + (1 - g) * ve, g = sigmoid(*ve_gate_logit) (models/daisy/attention.py:132-135); needs
+ *                DAISY_NORM_V in flags
+ *   workspace    daisy_b200_swa_decode_fused_workspace_bytes(B,H,D,splits) bytes; its last B*H ints (the tickets)
+ *                must be ZERO before the first call and are left zero by every call */
+size_t daisy_b200_swa_decode_fused_workspace_bytes(int B, int H, int D, int splits);
+int daisy_b200_swa_decode_step_fused(const void* q_new, const void* k_new, const void* v_new,
+                                     int64_t q_sb, int64_t q_sh, int64_t k_sb, int64_t k_sh,
+                                     int64_t v_sb, int64_t v_sh,
+                                     void* kcache, void* vcache, int64_t c_sb, int64_t c_sh, int64_t c_sr,
+                                     int64_t t, const int64_t* t_dev, int cap, int window,
+                                     const float* cos, const float* sin, int table_rows,
+                                     void* out, int64_t o_sb, int64_t o_sh,
+                                     void* k_new_out, void* v_new_out,
+                                     const void* ve, int64_t ve_sb, int64_t ve_sh, const float* ve_gate_logit,
+                                     int B, int H, int D, float scale, float eps, unsigned flags,
+                                     void* workspace, size_t workspace_bytes, int splits,
+                                     int* status_word, void* stream);
 
 /* The same decode step for callers that cannot allocate device memory (no counterpart in the reference;
  * it exists for embedders: code inside a stream capture, plugins under a pool allocator that forbids

@@ -93,3 +93,20 @@ def test_qkv_gemm_value_embedding_gate():
     g = torch.sigmoid(torch.tensor(-1.5163))
     ref = g * swa.rms_norm(v, swa.FP32_EPS) + (1 - g) * ve.float().cpu().view(B, T, H, D)
     assert_close_bf16(vp, ref, "ve gate in the epilogue")
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 6144, 2048), (2, 2048, 2048), (5, 392, 256), (8, 777, 1024), (17, 2048, 512), (64, 256, 2048)])
+def test_skinny_gemm_matches_fp32_reference(M, N, K):
+    """The weight-streaming projection of a decode step: F.linear for up to 64 rows."""
+    from daisy_b200 import ops
+    x = bf16_randn(M, K, seed=M + N)
+    w = bf16_randn(N, K, seed=K) * (K ** -0.5)
+    y = ops.gemm_skinny(x, w)
+    ref = x.float().cpu() @ w.float().cpu().t()
+    assert_close_bf16(y, ref, f"skinny {M}x{N}x{K}")
+    # a [B,1,K] input and a strided weight view (rows of a larger matrix), as the module passes them
+    big = bf16_randn(2 * N, K, seed=K + 1) * (K ** -0.5)
+    y3 = ops.gemm_skinny(x.view(M, 1, K), big[N:])
+    assert y3.shape == (M, 1, N)
+    assert_close_bf16(y3.view(M, N), x.float().cpu() @ big[N:].float().cpu().t(), "strided weight")
+    assert torch.equal(ops.gemm_skinny(x, w), y), "not run-to-run deterministic"

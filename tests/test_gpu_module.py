@@ -334,6 +334,31 @@ def test_step_through_cuda_graph_equals_eager_steps():
     assert torch.equal(graph.cache.k, eager.cache.k) and torch.equal(graph.cache.v, eager.cache.v)
 
 
+@pytest.mark.parametrize("T,cap,dtype", [(40, 32, torch.bfloat16), (300, 64, torch.bfloat16), (20, 64, torch.bfloat16),
+                                         (200, 48, torch.float16), (1, 8, torch.bfloat16)])
+def test_prefill_fills_the_ring_like_bulk_write_packed(T, cap, dtype):
+    """``prefill_ring``: the projection epilogue stores the prompt's last min(T, cap - 1) k', v' rows into their ring
+    slots; same ring contents, bit for bit, as ``prefill`` followed by ``KVCache.bulk_write_packed`` (the reference's
+    sequence, inference/generate.py:220-229), and the same outputs."""
+    from daisy_b200 import B200KVCache, WindowMask
+    B, H, D = 2, 2, 128
+    m = _module(H * D, H, D)
+    x = torch.randn(B, T, H * D, device="cuda", dtype=torch.bfloat16)
+    with torch.inference_mode():
+        y0, k0, v0 = m.prefill(x, None, attn_mask=WindowMask(24))
+        ref = B200KVCache(1, B, H, cap, D, "cuda", dtype)
+        ref.k.fill_(7.0); ref.v.fill_(7.0)                       # slots the fill must leave alone keep their contents
+        ref.bulk_write_packed(torch.stack([k0[None], v0[None]]), T)
+        got = B200KVCache(1, B, H, cap, D, "cuda", dtype)
+        got.k.fill_(7.0); got.v.fill_(7.0)
+        y1, k1, v1 = m.prefill_ring(x, None, got, 0, attn_mask=WindowMask(24))
+        got.set_position(T)
+    from daisy_b200 import ops
+    ops.check_device_status("cuda")
+    assert torch.equal(y1, y0) and torch.equal(k1, k0) and torch.equal(v1, v0)
+    assert torch.equal(got.k, ref.k) and torch.equal(got.v, ref.v) and got.t == ref.t == T
+
+
 def test_graph_capture_after_the_ring_wrapped_with_window_larger_than_capacity():
     """Capturing the graph step must leave the ring alone: with a window larger than the ring capacity the slot of
     the next token holds the oldest row the next step still attends to.  Eager steps first (so that slot holds a real
@@ -361,6 +386,31 @@ def test_graph_capture_after_the_ring_wrapped_with_window_larger_than_capacity()
         xi = x[:, P + E + i:P + E + i + 1]
         assert torch.equal(eager._step(xi), graph._step_graph(xi).clone()), f"step {i}"
     assert torch.equal(graph.cache.k, eager.cache.k) and torch.equal(graph.cache.v, eager.cache.v)
+
+
+def test_graph_step_with_value_embedding_layer():
+    """A layer that receives a value embedding through ``step_ring_dev`` (what the CUDA-graph step runs): same bits as
+    the eager ``step_ring``, and the step chain matches the windowed forward under the same embeddings."""
+    from daisy_b200 import B200CausalSelfAttention, B200KVCache, WindowMask
+    os.environ["DISABLE_O_ZERO_INIT"] = "1"
+    torch.manual_seed(3)
+    H, D, T, W, cap = 2, 128, 40, 16, 32
+    m = B200CausalSelfAttention(H * D, H, D, receives_ve=True, layer_idx=2, max_seq_len=128).cuda().eval()
+    m.norm_eps = swa.FP32_EPS
+    with torch.no_grad():
+        m.qkvo_w.mul_(4.0)
+    x = torch.randn(1, T, H * D, device="cuda", dtype=torch.bfloat16)
+    ve = torch.randn(1, T, H * D, device="cuda", dtype=torch.bfloat16)
+    with torch.inference_mode():
+        y_full = m.forward(x, ve, attn_mask=WindowMask(W))
+        ca, cb = B200KVCache(1, 1, H, cap, D, "cuda"), B200KVCache(1, 1, H, cap, D, "cuda")
+        for t in range(T):
+            ya, _, _ = m.step_ring(x[:, t:t + 1], ca, 0, ca.t, ve[:, t:t + 1], W)
+            yb = m.step_ring_dev(x[:, t:t + 1], cb, 0, W, ve=ve[:, t:t + 1])
+            ca.advance(); cb.advance()
+            assert torch.equal(ya, yb), f"token {t}"
+            assert_close_bf16(ya, y_full[:, t:t + 1].float().cpu(), f"token {t} vs forward", max_tol=6e-2, mean_tol=6e-3)
+    assert torch.equal(ca.k, cb.k) and torch.equal(ca.v, cb.v)
 
 
 def test_step_runner_with_float16_cache():
