@@ -6,7 +6,8 @@ from .kv_cache import B200KVCache, ring_segment                       # noqa: F4
 from .generate import StepRunner                                      # noqa: F401
 from .kda import B200KimiLinearSelfAttention, B200ShortConvolution, B200FusedRMSNormGated   # noqa: F401
 from . import ops                                                      # noqa: F401
+from .autograd import swa_attention                                   # noqa: F401
 
 __all__ = ["B200CausalSelfAttention", "B200KVCache", "WindowMask", "BlockWindowMask", "create_blockmasks", "doc_starts",
            "Rotary", "ring_segment", "StepRunner", "B200KimiLinearSelfAttention", "B200ShortConvolution",
-           "B200FusedRMSNormGated", "ops"]
+           "B200FusedRMSNormGated", "ops", "swa_attention"]

@@ -36,6 +36,10 @@ SIGNATURES = {
     "daisy_b200_swa_prefill_fwd": (_i, [_vp] * 3 + [_i64] * 9 + [_vp] * 2 + [_vp] + [_i64] * 3 + [_vp] * 2 +
                                    [_i] * 5 + [_f, _f, _vp, _i64, _u, _vp, _sz, _vp, _vp]),
     "daisy_b200_swa_attend": (_i, [_vp] * 3 + [_i64] * 9 + [_vp] + [_i64] * 3 + [_i] * 5 + [_f, _vp, _i64, _u, _vp, _vp]),
+    "daisy_b200_swa_attend_lse": (_i, [_vp] * 3 + [_i64] * 9 + [_vp] + [_i64] * 3 + [_vp] + [_i] * 5 + [_f, _vp, _i64, _u, _vp, _vp]),
+    "daisy_b200_swa_attend_bwd_workspace_bytes": (_sz, [_i] * 3),
+    "daisy_b200_swa_attend_bwd": (_i, [_vp] * 5 + [_i64] * 15 + [_vp] * 4 + [_i] * 5 + [_f, _vp, _i64, _u, _vp, _sz, _vp, _vp]),
+    "daisy_b200_qkv_prep_bwd": (_i, [_vp] * 3 + [_i64] * 9 + [_vp] * 2 + [_vp] * 6 + [_i] * 4 + [_f, _u, _vp]),
     "daisy_b200_swa_decode_splits": (_i, [_i] * 4),
     "daisy_b200_swa_decode_workspace_bytes": (_sz, [_i] * 4),
     "daisy_b200_swa_decode_step": (_i, [_vp] * 3 + [_i64] * 6 + [_vp] * 2 + [_i64] * 3 + [_i64, _i, _i] +

@@ -15,8 +15,10 @@ a ``WindowMask(window[, doc_start])``, an int, ``None`` (plain causal) -- or the
 ``[1,1,T,T]`` tensor, which is read once on the device to recover each row's first visible key
 (:func:`band_of_dense_mask`) and rejected if it is not such a band.
 
-Training.  The backward pass is not implemented: a call that would need gradients raises instead of
-returning a tensor autograd treats as a constant.
+Training.  When a call needs gradients (grad mode on and the input or a parameter requires them) ``forward``
+takes the differentiable route: ``F.linear`` projections (autograd supplies their gradients) around
+``daisy_b200.autograd.swa_attention``, whose backward is this library's tcgen05 backward kernels.  Layers that
+receive a value embedding, and the cache-writing ``prefill`` / ``step`` forms, have no backward and raise.
 """
 from __future__ import annotations
 
@@ -26,6 +28,7 @@ from typing import Optional
 
 import torch
 from torch import nn, Tensor
+import torch.nn.functional as F
 
 from . import ops
 from ._lib import NORM_Q, NORM_K, NORM_V, ROPE, QKV_DEFAULT
@@ -212,11 +215,27 @@ class B200CausalSelfAttention(nn.Module):
         raise TypeError("attn_mask must be None, an int window, WindowMask(window[, doc_start]) or the dense mask tensor of "
                         "build_attn_mask")
 
+    def _needs_grad(self, x: Tensor) -> bool:
+        return torch.is_grad_enabled() and (x.requires_grad or self.qkvo_w.requires_grad
+                                            or (self.g_ve is not None and self.g_ve.requires_grad))
+
     def _no_autograd(self, x: Tensor):
-        if torch.is_grad_enabled() and (x.requires_grad or self.qkvo_w.requires_grad
-                                        or (self.g_ve is not None and self.g_ve.requires_grad)):
-            raise NotImplementedError("daisy_b200 implements the forward pass only: call under torch.no_grad() / "
-                                      "inference_mode(), or detach the input and freeze the parameters")
+        if self._needs_grad(x):
+            raise NotImplementedError("this call has no backward pass (only forward() without a value embedding does): call "
+                                      "it under torch.no_grad() / inference_mode(), or detach the input and freeze the parameters")
+
+    def _attend_autograd(self, x: Tensor, mask):
+        """The differentiable forward: same arithmetic as ``_attend`` with the norm / RoPE as their own pass."""
+        from .autograd import swa_attention
+        window, doc_start = mask[0], mask[1]
+        in_blocks = len(mask) > 2 and mask[2]
+        B, T = x.size(0), x.size(1)
+        cos, sin = self.rotary.tables(T)
+        w = self.qkvo_w
+        qkv = F.linear(x.to(w.dtype), w[:3].flatten(end_dim=1)).view(B, T, 3 * self.num_heads, self.head_dim)
+        q, k, v = qkv.chunk(3, dim=-2)
+        y = swa_attention(q, k, v, cos, sin, window, self.attn_scale, self.norm_eps, QKV_DEFAULT, doc_start, in_blocks)
+        return F.linear(y.view(B, T, self.m_dim), w[3])
 
     def _attend(self, x: Tensor, ve: Optional[Tensor], mask, ring=None, ring_first: int = 0):
         """Every kernel hand-written: QKV GEMM with norm + RoPE (+ the value-embedding gate) in its epilogue,
@@ -246,9 +265,11 @@ class B200CausalSelfAttention(nn.Module):
         if block_mask is not None:
             torch._assert(isinstance(block_mask, BlockWindowMask), "block_mask must be a daisy_b200 BlockWindowMask")
             torch._assert(x.size(1) % WINDOW_BLOCK_SIZE == 0, "the block-granular mask needs T divisible by 128")
-            y, _, _, _ = self._attend(x, ve, self._window_of(block_mask))
-            return y
-        y, _, _, _ = self._attend(x, ve, self._window_of(attn_mask))
+            attn_mask = block_mask
+        mask = self._window_of(attn_mask)
+        if self._needs_grad(x) and not self.receives_ve:
+            return self._attend_autograd(x, mask)
+        y, _, _, _ = self._attend(x, ve, mask)
         return y
 
     def prefill(self, x: Tensor, ve: Optional[Tensor], attn_mask=None, debug: bool = False):

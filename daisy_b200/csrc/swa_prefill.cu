@@ -62,6 +62,9 @@ struct PrefillParams {
   const float* sin;
   float eps;
   int q_norm, q_rope;
+  // optional: log2 of each row's softmax denominator in the kernel's exp2 domain, [B,H,T] float32:
+  // P[q,k] = 2^(logit * log2(e) - lse2[q]).  What the backward pass rebuilds P from.
+  float* lse2;
 };
 
 struct PrefillBarriers {
@@ -435,6 +438,7 @@ swa_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       if (s == 0) asm volatile("bar.sync 1, 256;" ::: "memory");
       else        asm volatile("bar.sync 2, 256;" ::: "memory");
       if (half == 1) l = *lsum;
+      if (p.lse2 && half == 0 && q_row < T) p.lse2[((int64_t)g.b * p.H + g.h) * T + q_row] = __log2f(l);   // no reference maximum in this form
       if (ok) {
         ok = __all_sync(0xffffffffu, mbar_wait(&bars->o_full[s], n_o & 1, abort_flag, p.status, 7));
         ++n_o;
@@ -642,6 +646,7 @@ swa_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       if (ok) {
         tc_fence_after();
         const float inv = 1.0f / l;
+        if (p.lse2 && q_row < T) p.lse2[((int64_t)g.b * p.H + g.h) * T + q_row] = m_ref + __log2f(l);
         __nv_bfloat16* dst = p.out + g.b * p.o_sb + (int64_t)q_row * p.o_st + g.h * p.o_sh;
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
@@ -791,7 +796,8 @@ static int launch_attend(const void* q, const void* k, const void* v,
                          int64_t v_sb, int64_t v_st, int64_t v_sh,
                          void* out, int64_t o_sb, int64_t o_st, int64_t o_sh,
                          int B, int T, int H, int D, int window, float scale, const QTransform* qt, bool bounded_qk,
-                         const int* doc_start, int64_t doc_sb, bool window_in_blocks, int* status_word, void* stream) {
+                         const int* doc_start, int64_t doc_sb, bool window_in_blocks, int* status_word, void* stream,
+                         float* lse2 = nullptr) {
   if (!q || !k || !v || !out || B <= 0 || T <= 0 || H <= 0 || !(scale > 0.f)) return DAISY_EINVAL;
   if (D != DAISY_HEAD_DIM) return DAISY_EUNSUPPORTED;
   if (!daisy_aligned16(q) || !daisy_aligned16(k) || !daisy_aligned16(v) || !daisy_aligned16(out) || ((o_sb | o_st | o_sh) & 7) ||
@@ -821,6 +827,7 @@ static int launch_attend(const void* q, const void* k, const void* v,
   p.doc_start = doc_start; p.doc_sb = doc_sb;
   p.cos = qt ? qt->cos : nullptr; p.sin = qt ? qt->sin : nullptr;
   p.eps = qt ? qt->eps : 0.f; p.q_norm = qt ? qt->norm : 0; p.q_rope = qt ? qt->rope : 0;
+  p.lse2 = lse2;
   const int64_t items = (int64_t)((T + 2 * BM - 1) / (2 * BM)) * H * B;
   if (items >= (int64_t)1 << 31) return DAISY_EUNSUPPORTED;
   const int sms = daisy_host::sm_count_cached();
@@ -851,6 +858,21 @@ extern "C" int daisy_b200_swa_attend(const void* q, const void* k, const void* v
   return launch_attend(q, k, v, q_sb, q_st, q_sh, k_sb, k_st, k_sh, v_sb, v_st, v_sh, out, o_sb, o_st, o_sh,
                        B, T, H, D, window, scale, nullptr, (flags & DAISY_BOUNDED_QK) != 0, doc_start, doc_sb,
                        (flags & DAISY_WINDOW_BLOCKS) != 0, status_word, stream);
+}
+
+extern "C" int daisy_b200_swa_attend_lse(const void* q, const void* k, const void* v,
+                                         int64_t q_sb, int64_t q_st, int64_t q_sh,
+                                         int64_t k_sb, int64_t k_st, int64_t k_sh,
+                                         int64_t v_sb, int64_t v_st, int64_t v_sh,
+                                         void* out, int64_t o_sb, int64_t o_st, int64_t o_sh, float* lse2,
+                                         int B, int T, int H, int D, int window, float scale,
+                                         const int32_t* doc_start, int64_t doc_sb,
+                                         unsigned flags, int* status_word, void* stream) {
+  if (flags & ~(DAISY_BOUNDED_QK | DAISY_WINDOW_BLOCKS)) return DAISY_EINVAL;
+  if (!lse2 || (reinterpret_cast<uintptr_t>(lse2) & 3)) return DAISY_EINVAL;
+  return launch_attend(q, k, v, q_sb, q_st, q_sh, k_sb, k_st, k_sh, v_sb, v_st, v_sh, out, o_sb, o_st, o_sh,
+                       B, T, H, D, window, scale, nullptr, (flags & DAISY_BOUNDED_QK) != 0, doc_start, doc_sb,
+                       (flags & DAISY_WINDOW_BLOCKS) != 0, status_word, stream, lse2);
 }
 
 static size_t align1k(size_t x) { return (x + 1023) & ~size_t(1023); }

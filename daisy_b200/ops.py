@@ -182,12 +182,14 @@ def _doc_arg(doc_start: Optional[torch.Tensor], B: int, T: int, device):
 
 def swa_attend(q, k, v, window: Optional[int], scale: float = ATTN_SCALE,
                out: Optional[torch.Tensor] = None, bounded_qk: bool = False,
-               doc_start: Optional[torch.Tensor] = None, window_in_blocks: bool = False) -> torch.Tensor:
+               doc_start: Optional[torch.Tensor] = None, window_in_blocks: bool = False, return_lse: bool = False):
     """Windowed causal attention on prepared tensors of logical shape ``[B,T,H,D]`` (any batch / token /
     head strides, D contiguous); returns ``[B,T,H,D]``.  ``bounded_qk=True`` promises RMS-normalised q and k
     (every logit bounded), which selects the kernel without a running maximum.  ``doc_start`` (int, ``[T]`` or
     ``[B,T]``): first position of each token's document; keys before it are masked.  ``window_in_blocks``:
-    ``window`` counts blocks of 128 tokens (key block >= query block - window + 1), the training-form mask."""
+    ``window`` counts blocks of 128 tokens (key block >= query block - window + 1), the training-form mask.
+    ``return_lse``: also return ``lse2 [B,H,T]`` float32 (base-2 log of each row's softmax denominator), what
+    :func:`swa_attend_bwd` needs."""
     for n, t in (("q", q), ("k", k), ("v", v)):
         _req(t, n)
     B, T, H, D = q.shape
@@ -195,6 +197,17 @@ def swa_attend(q, k, v, window: Optional[int], scale: float = ATTN_SCALE,
     if out is None:
         out = torch.empty(B, T, H, D, dtype=torch.bfloat16, device=q.device)
     _doc, doc_ptr, doc_sb = _doc_arg(doc_start, B, T, q.device)
+    if return_lse:
+        lse = torch.empty(B, H, T, dtype=torch.float32, device=q.device)
+        rc = _lib.lib().daisy_b200_swa_attend_lse(
+            q.data_ptr(), k.data_ptr(), v.data_ptr(),
+            q.stride(0), q.stride(1), q.stride(2), k.stride(0), k.stride(1), k.stride(2),
+            v.stride(0), v.stride(1), v.stride(2), out.data_ptr(),
+            out.stride(0), out.stride(1), out.stride(2), lse.data_ptr(), B, T, H, D, int(window or 0), scale, doc_ptr, doc_sb,
+            (_lib.BOUNDED_QK if bounded_qk else 0) | (_lib.WINDOW_BLOCKS if window_in_blocks else 0),
+            status_word(q.device).data_ptr(), _stream(q))
+        _lib.check(rc, "daisy_b200_swa_attend_lse")
+        return out, lse
     rc = _lib.lib().daisy_b200_swa_attend(
         q.data_ptr(), k.data_ptr(), v.data_ptr(),
         q.stride(0), q.stride(1), q.stride(2), k.stride(0), k.stride(1), k.stride(2),
@@ -204,6 +217,49 @@ def swa_attend(q, k, v, window: Optional[int], scale: float = ATTN_SCALE,
         status_word(q.device).data_ptr(), _stream(q))
     _lib.check(rc, "daisy_b200_swa_attend")
     return out
+
+
+def swa_attend_bwd(q, k, v, o, d_o, lse2, window: Optional[int], scale: float = ATTN_SCALE,
+                   doc_start: Optional[torch.Tensor] = None, window_in_blocks: bool = False):
+    """Gradients of :func:`swa_attend` w.r.t. its prepared inputs: ``(dq, dk, dv)``, each ``[B,T,H,D]`` bf16 contiguous.
+    ``q, k, v, o, d_o`` logical ``[B,T,H,D]`` (any strides, D contiguous); ``lse2`` from ``swa_attend(...,
+    return_lse=True)``.  Deterministic (no atomics)."""
+    for n, t in (("q", q), ("k", k), ("v", v), ("o", o), ("d_o", d_o)):
+        _req(t, n)
+    B, T, H, D = q.shape
+    lse2 = _f32c(lse2, "lse2")
+    assert lse2.shape == (B, H, T)
+    dq, dk, dv = (torch.empty(B, T, H, D, dtype=torch.bfloat16, device=q.device) for _ in range(3))
+    L = _lib.lib()
+    ws = torch.empty(L.daisy_b200_swa_attend_bwd_workspace_bytes(B, T, H), dtype=torch.uint8, device=q.device)
+    _doc, doc_ptr, doc_sb = _doc_arg(doc_start, B, T, q.device)
+    st = lambda t: (t.stride(0), t.stride(1), t.stride(2))
+    rc = L.daisy_b200_swa_attend_bwd(
+        q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), d_o.data_ptr(), *st(q), *st(k), *st(v), *st(o), *st(d_o),
+        lse2.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), B, T, H, D, int(window or 0), scale, doc_ptr, doc_sb,
+        _lib.WINDOW_BLOCKS if window_in_blocks else 0, ws.data_ptr(), ws.numel(), status_word(q.device).data_ptr(), _stream(q))
+    _lib.check(rc, "daisy_b200_swa_attend_bwd")
+    return dq, dk, dv
+
+
+def qkv_prep_bwd(q, k, v, cos, sin, dq_p, dk_p, dv_p, eps: float, flags: int = QKV_DEFAULT):
+    """Backward of :func:`qkv_prep` (without a value embedding): raw ``q, k, v`` ``[B,T,H,D]`` (any strides) and the
+    gradients w.r.t. the prepared tensors (``[B,T,H,D]`` contiguous) -> gradients w.r.t. the raw tensors."""
+    for n, t in (("q", q), ("k", k), ("v", v), ("dq_p", dq_p), ("dk_p", dk_p), ("dv_p", dv_p)):
+        _req(t, n)
+    B, T, H, D = q.shape
+    for t in (dq_p, dk_p, dv_p):
+        assert t.shape == (B, T, H, D) and t.is_contiguous()
+    if flags & ROPE:
+        cos, sin = _f32c(cos, "cos"), _f32c(sin, "sin")
+    outs = [torch.empty(B, T, H, D, dtype=torch.bfloat16, device=q.device) for _ in range(3)]
+    st = lambda t: (t.stride(0), t.stride(1), t.stride(2))
+    rc = _lib.lib().daisy_b200_qkv_prep_bwd(
+        q.data_ptr(), k.data_ptr(), v.data_ptr(), *st(q), *st(k), *st(v), cos.data_ptr() if cos is not None else None,
+        sin.data_ptr() if sin is not None else None, dq_p.data_ptr(), dk_p.data_ptr(), dv_p.data_ptr(),
+        outs[0].data_ptr(), outs[1].data_ptr(), outs[2].data_ptr(), B, T, H, D, eps, flags, _stream(q))
+    _lib.check(rc, "daisy_b200_qkv_prep_bwd")
+    return tuple(outs)
 
 
 def swa_prefill(q, k, v, cos, sin, window: Optional[int], scale: float = ATTN_SCALE, eps: float = 1.1920929e-07,

@@ -185,6 +185,52 @@ int daisy_b200_swa_attend(const void* q, const void* k, const void* v,
                           const int32_t* doc_start, int64_t doc_sb,
                           unsigned flags, int* status_word, void* stream);
 
+/* The same attention core, also returning what the backward pass needs: lse2 [B,H,T] float32, the base-2 logarithm of
+ * each row's softmax denominator in the kernel's exp2 domain, P[q,k] = 2^(logit[q,k] * log2(e) - lse2[q]). */
+int daisy_b200_swa_attend_lse(const void* q, const void* k, const void* v,
+                              int64_t q_sb, int64_t q_st, int64_t q_sh,
+                              int64_t k_sb, int64_t k_st, int64_t k_sh,
+                              int64_t v_sb, int64_t v_st, int64_t v_sh,
+                              void* out, int64_t o_sb, int64_t o_st, int64_t o_sh, float* lse2,
+                              int B, int T, int H, int D, int window, float scale,
+                              const int32_t* doc_start, int64_t doc_sb,
+                              unsigned flags, int* status_word, void* stream);
+
+/* Backward pass of the attention core: what autograd computes for F.scaled_dot_product_attention /
+ * flex_attention inside CausalSelfAttention.forward during training (models/daisy/attention.py:141-162), for the same
+ * masks as the forward (window in tokens, or in 128-token blocks with DAISY_WINDOW_BLOCKS; documents).
+ *   q,k,v      the PREPARED tensors the forward consumed, o its output, d_o the incoming gradient: logical [B,T,H,D]
+ *              bf16 with strides (s_b, s_t, s_h) each (o: o_s*, d_o: g_s*)
+ *   lse2       [B,H,T] float32 from daisy_b200_swa_attend_lse
+ *   dq,dk,dv   gradients w.r.t. the prepared q, k, v: [B,T,H,D] bf16 contiguous
+ *   workspace  daisy_b200_swa_attend_bwd_workspace_bytes(B,T,H) bytes
+ * Three launches (row-wise delta = sum_d dO O; a key-block-stationary kernel for dK, dV; a query-block-stationary
+ * kernel for dQ); no atomics: results are bitwise reproducible. */
+size_t daisy_b200_swa_attend_bwd_workspace_bytes(int B, int T, int H);
+int daisy_b200_swa_attend_bwd(const void* q, const void* k, const void* v, const void* o, const void* d_o,
+                              int64_t q_sb, int64_t q_st, int64_t q_sh,
+                              int64_t k_sb, int64_t k_st, int64_t k_sh,
+                              int64_t v_sb, int64_t v_st, int64_t v_sh,
+                              int64_t o_sb, int64_t o_st, int64_t o_sh,
+                              int64_t g_sb, int64_t g_st, int64_t g_sh,
+                              const float* lse2, void* dq, void* dk, void* dv,
+                              int B, int T, int H, int D, int window, float scale,
+                              const int32_t* doc_start, int64_t doc_sb, unsigned flags,
+                              void* workspace, size_t workspace_bytes, int* status_word, void* stream);
+
+/* Backward of daisy_b200_qkv_prep (the norm / RoPE tail of _calc_qkv, models/daisy/attention.py:121-125, under
+ * autograd): q,k,v are the RAW projections the forward read (strides as there), d*_p the gradients w.r.t. the prepared
+ * tensors ([B,T,H,D] bf16 contiguous), d* receive the gradients w.r.t. the raw projections ([B,T,H,D] bf16 contiguous).
+ * Any of the three triples may be NULL together.  flags: DAISY_NORM_Q | DAISY_NORM_K | DAISY_NORM_V | DAISY_ROPE. */
+int daisy_b200_qkv_prep_bwd(const void* q, const void* k, const void* v,
+                            int64_t q_sb, int64_t q_st, int64_t q_sh,
+                            int64_t k_sb, int64_t k_st, int64_t k_sh,
+                            int64_t v_sb, int64_t v_st, int64_t v_sh,
+                            const float* cos, const float* sin,
+                            const void* dq_p, const void* dk_p, const void* dv_p,
+                            void* dq, void* dk, void* dv,
+                            int B, int T, int H, int D, float eps, unsigned flags, void* stream);
+
 /* ---------------------------------------------------------------------------------------------
  * Sliding-window decode step over a ring-buffer KV cache, split-KV.
  * Replaces CausalSelfAttention.step between the projections (models/daisy/attention.py:183-200)

@@ -271,6 +271,27 @@ def csa_prefill(x, qkvo_w, num_heads, head_dim, window, cos_td, sin_td, eps=FP32
     return y, kn, vn
 
 
+def csa_backward(x, qkvo_w, num_heads, head_dim, window, cos_td, sin_td, cot, eps=FP32_EPS, scale=ATTN_SCALE,
+                 doc_start=None):
+    """Gradients of ``sum(forward(x) * cot)`` with respect to ``x`` and the merged weights, by ``torch.autograd``
+    over :func:`csa_prefill` in fp32 -- what training computes through the reference module's forward
+    (models/daisy/attention.py:164-171).  Returns ``(y, dx, dw)``."""
+    x = x.detach().float().requires_grad_(True)
+    w = qkvo_w.detach().float().requires_grad_(True)
+    y, _, _ = csa_prefill(x, w, num_heads, head_dim, window, cos_td, sin_td, eps, scale, doc_start)
+    (y * cot.float()).sum().backward()
+    return y.detach(), x.grad, w.grad
+
+
+def attend_backward(q, k, v, d_out, window, scale=ATTN_SCALE, doc_start=None, window_blocks=None):
+    """Gradients of :func:`attend_windowed` with respect to its prepared inputs for the cotangent ``d_out``, by
+    ``torch.autograd`` in fp32.  Returns ``(out, dq, dk, dv)``."""
+    q, k, v = (t.detach().float().requires_grad_(True) for t in (q, k, v))
+    out = attend_windowed(q, k, v, window, scale, doc_start=doc_start, window_blocks=window_blocks)
+    (out * d_out.float()).sum().backward()
+    return out.detach(), q.grad, k.grad, v.grad
+
+
 def csa_step(x, qkvo_w, num_heads, head_dim, k_ctx, v_ctx, pos, window, cos_td, sin_td,
              eps=FP32_EPS, scale=ATTN_SCALE):
     """Whole ``CausalSelfAttention.step`` with ``ve=None`` (models/daisy/attention.py:181-202)."""

@@ -166,6 +166,28 @@ def doc_mask_case():
     print("doc_mask_small", tuple(y.shape))
 
 
+def csa_backward_case():
+    """The reference module's CPU SDPA path under autograd (the training form evaluated where flex-attention is not
+    available, models/daisy/attention.py:141-154,164-171): forward with the dense window + document mask, a fixed
+    cotangent, gradients with respect to the input and the merged weights."""
+    dim, heads, hd, T, window, eos = 256, 2, 128, 160, 48, 7
+    attn = make_attn(dim, heads, hd, seed=11)
+    g = torch.Generator().manual_seed(12)
+    seq = torch.randint(8, 100, (1, T), generator=g)
+    for p_ in (30, 31, 100):
+        seq[0, p_] = eos
+    x = torch.randn(1, T, dim, generator=g).requires_grad_(True)
+    cot = torch.randn(1, T, dim, generator=g)
+    mask = build_attn_mask(seq, window, eos)
+    y = attn(x, None, attn_mask=mask)
+    (y * cot).sum().backward()
+    np.savez_compressed(os.path.join(HERE, "csa_backward_small.npz"),
+                        seq=seq.numpy(), eos=np.int64(eos), window=np.int64(window), x=x.detach().numpy(), cot=cot.numpy(),
+                        qkvo_w=attn.qkvo_w.detach().numpy(), y=y.detach().numpy(), dx=x.grad.numpy(),
+                        dw=attn.qkvo_w.grad.numpy())
+    print("csa_backward_small", tuple(y.shape), float(x.grad.abs().max()), float(attn.qkvo_w.grad.abs().max()))
+
+
 def flex_blockmask_case():
     """Block lists of ``DaisyCore.create_blockmasks`` (daisy_core.py:182-229) for sequences with documents
     of many lengths: kv_num_blocks / kv_indices / full_kv_num_blocks / full_kv_indices of the long and the short
@@ -274,6 +296,7 @@ if __name__ == "__main__":
     kda_gate_case()
     kda_layer_case()
     doc_mask_case()
+    csa_backward_case()
     flex_blockmask_case()
     for f in sorted(os.listdir(HERE)):
         if f.endswith(".npz"):

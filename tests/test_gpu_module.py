@@ -276,9 +276,9 @@ def test_forward_with_eos_document_mask_matches_reference_fixture(golden_dir):
     for bad in (holed, future, torch.full_like(dense, float("-inf"))):
         with pytest.raises(ValueError, match="causal band"):
             band_of_dense_mask(bad)
-    # a call that would need gradients raises (the backward pass is not implemented)
-    with pytest.raises(NotImplementedError, match="forward pass only"):
-        attn(x.cuda().bfloat16(), None, attn_mask=mask)
+    # the cache-writing form has no backward pass: a call that would need gradients raises
+    with pytest.raises(NotImplementedError, match="no backward pass"):
+        attn.prefill(x.cuda().bfloat16(), None, attn_mask=mask)
 
 
 def test_forward_with_block_mask_training_form():

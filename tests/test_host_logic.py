@@ -48,9 +48,9 @@ def test_module_construction_and_mask_parsing(monkeypatch):
         m._window_of("causal")
     with pytest.raises(ValueError, match="CUDA tensor"):       # the dense mask is read on the device
         m._window_of(torch.zeros(1, 1, 4, 4))
-    # calls that would need gradients raise instead of returning a constant (the backward pass is not built)
-    with pytest.raises(NotImplementedError, match="forward pass only"):
-        m(torch.zeros(1, 4, 256, dtype=torch.bfloat16), None)
+    # calls without a backward pass that would need gradients raise instead of returning a constant
+    with pytest.raises(NotImplementedError, match="no backward pass"):
+        m.prefill(torch.zeros(1, 4, 256, dtype=torch.bfloat16), None)
     from daisy_b200.attention import create_blockmasks
     assert [bm.window_blocks for bm in create_blockmasks(torch.zeros(128, dtype=torch.long), 1, 3, 9)] == [1, 1, 1]
     with pytest.raises(Exception):

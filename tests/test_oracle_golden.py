@@ -149,6 +149,21 @@ def test_document_mask_against_reference_fixture(golden_dir):
     assert (y - torch.from_numpy(d["y"])).abs().max().item() < 1e-5
 
 
+def test_backward_against_reference_autograd_fixture(golden_dir):
+    """oracle ``csa_backward`` (autograd over the restatement) vs the reference module's own CPU SDPA path under
+    autograd, with the dense window + document mask: output, input gradient, weight gradient."""
+    d = np.load(os.path.join(golden_dir, "csa_backward_small.npz"))
+    seq = torch.from_numpy(d["seq"])[0]
+    T, W = seq.numel(), int(d["window"])
+    ds = swa.doc_starts(seq, int(d["eos"]))
+    cos, sin = swa.rope_tables(128, T)
+    y, dx, dw = swa.csa_backward(torch.from_numpy(d["x"]), torch.from_numpy(d["qkvo_w"]), 2, 128, W, cos, sin,
+                                 torch.from_numpy(d["cot"]), doc_start=ds)
+    for got, name in ((y, "y"), (dx, "dx"), (dw, "dw")):
+        ref = torch.from_numpy(d[name])
+        assert (got - ref).abs().max().item() <= 2e-5 * max(1.0, ref.abs().max().item()), name
+
+
 def test_flex_block_lists_against_reference_fixture(golden_dir):
     """The block lists of ``DaisyCore.create_blockmasks`` (models/daisy/daisy_core.py:182-229), produced by the
     reference itself for documents of many lengths and several window sizes, against the oracle's restatement;
