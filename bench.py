@@ -440,6 +440,41 @@ def run_prefill(cfg, steps, warmup, dist, rank, world, peaks, name, lean=False, 
     return res
 
 
+def run_prefill_bwd(cfg, steps, warmup, peaks):
+    """Backward of the windowed attention at the headline shape (training form): row-wise delta, the
+    key-block-stationary dK/dV kernel and the query-block-stationary dQ kernel.  FLOPs are counted as 2.5 x the forward's
+    (five products over the admitted pairs against the forward's two; the two recomputed score products of the
+    second kernel are not credited)."""
+    from daisy_b200 import ops
+    from daisy_b200 import accounting as acct
+    B, T, H, D, W = cfg["B"], cfg["T"], cfg["H"], cfg["D"], cfg["window"]
+    dev = torch.device("cuda", torch.cuda.current_device())
+    q, k, v = prefill_inputs(cfg, 77, dev)
+    cos, sin = rope_full(D, T, dev)
+    qp, kp, vp = ops.qkv_prep(q, k, v, cos, sin, acct.FP32_EPS)
+    del q, k, v
+    g = torch.Generator(device=dev).manual_seed(78)
+    d_o = torch.randn(B, T, H, D, device=dev, generator=g).bfloat16()
+    y, lse = ops.swa_attend(qp, kp, vp, W, bounded_qk=True, return_lse=True)
+    res = {}
+
+    def step():
+        res["g"] = ops.swa_attend_bwd(qp, kp, vp, y, d_o, lse, W)
+
+    ms = timed_steps(step, steps, warmup, None) / steps
+    ops.check_device_status(dev)
+    first = [t.clone() for t in res["g"]]
+    step()
+    same = all(torch.equal(a, b) for a, b in zip(first, res["g"]))
+    flops = 2.5 * acct.prefill_flops(B, T, H, D, W)
+    tf = flops / (ms * 1e-3) / 1e12
+    return {"ms_per_step": ms, "tflops": tf, "value": tf, "unit": "TFLOP/s", "steps": steps, "launches_per_step": 3,
+            "flops_counted": "2.5 x forward (dP, dV, dK, dQ and one score product over the admitted pairs)",
+            "frac_of_burst_peak": tf / peaks["bf16_tflops"], "finite": bool(all(torch.isfinite(t.float()).all() for t in res["g"])),
+            "bitwise_reproducible": bool(same),
+            "config": {"workload": f"prefill_bwd: B={B} T={T} H={H} D={D} window={W}, gradients w.r.t. prepared q, k, v"}}
+
+
 # ----------------------------------------------------------------------------- our arm: decode
 
 class DecodeCase:
@@ -939,7 +974,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--library-context", action="store_true",
                     help="also time the GPU library calls the reference makes for the same work (context, minutes)")
-    ap.add_argument("--workload", default="all", choices=["all", "prefill_c2", "prefill_c4", "decode_c3", "kda_c5", "prefill_small", "decode_small", "kda_small", "gemm_small", "kda_layer_small"])
+    ap.add_argument("--workload", default="all", choices=["all", "prefill_c2", "prefill_c4", "prefill_bwd", "decode_c3", "kda_c5", "prefill_small", "decode_small", "kda_small", "gemm_small", "kda_layer_small"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extras", action="store_true",
                     help="skip the measurements beside the workloads (projection GEMMs, generator-step latency, KDA layer "
@@ -981,6 +1016,14 @@ def main():
             res = c4
         else:
             extra["prefill_c4"] = c4
+    if want in ("all", "prefill_bwd") and rank == 0 and not (want == "all" and args.no_extras):
+        torch.cuda.empty_cache()
+        bw = run_prefill_bwd(PREFILL_C2, max(5, args.steps // 2), warm, peaks)
+        if res is None:
+            bw["name"] = "prefill_bwd"; bw["roofline"] = None; bw["e2e"] = None
+            res = bw
+        else:
+            extra["prefill_bwd"] = bw
     if want == "all" and rank == 0 and not args.no_extras:
         torch.cuda.empty_cache()
         extra["projection"] = run_projection(PREFILL_C2["B"], PREFILL_C2["T"], PREFILL_C2["H"], PREFILL_C2["D"],

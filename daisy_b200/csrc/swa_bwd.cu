@@ -14,8 +14,10 @@
 //   MODE 1  query block stationary:  item = 128 queries; Q_i, dO_i stay, the key blocks of the window stream
 //           (K_j, V_j);  S = Q_i K_j^T, dP = dO_i V_j^T (TMEM lane = query),  dQ += dZ K_j.
 // In both:  S = X0 Y0^T,  dP = X1 Y1^T  (X stationary, Y streamed),  acc1 += dZ Y0,  and MODE 0 also acc0 += P Y1.
-// Roles (192 threads): warps 0-3 rebuild P / dZ (thread = TMEM lane) and write the results, warp 4 TMA producer,
-// warp 5 MMA issuer.  TMEM: S [0,128) dP [128,256) acc0 [256,384) acc1 [384,512).
+// Roles (320 threads): warps 0-7 rebuild P / dZ -- two warpgroups, thread = TMEM lane, 64 of a tile's 128 columns
+// each (every warpgroup writes its bf16 results over the first 32 columns of its OWN 64, so nobody overwrites
+// columns somebody else still has to read) -- and write the results; warp 8 TMA producer, warp 9 MMA issuer.
+// TMEM: S [0,128) dP [128,256) acc0 [256,384) acc1 [384,512).
 // All mbarrier waits are bounded (abort flag, DAISY_ETIMEOUT through the status word).
 #include "common.cuh"
 
@@ -25,7 +27,8 @@ constexpr int WB = 128;                                   // block of queries / 
 constexpr int W_TILE = WB * DAISY_HEAD_DIM * 2;           // 32768
 constexpr int W_HALF = W_TILE / 2;
 constexpr int W_NST = 2;                                  // stages of streamed (Y0, Y1) tile pairs
-constexpr int BWD_THREADS = 192;
+constexpr int BWD_THREADS = 320;
+constexpr int BWD_WORKERS = 256;                          // threads of warps 0-7
 constexpr int BWD_SMEM = 1024 + 2 * W_TILE + W_NST * 2 * W_TILE + 2 * 3 * WB * 4 + 256;
 static_assert(BWD_SMEM <= 232448, "over the 227 KB a CTA may use");
 
@@ -87,17 +90,17 @@ swa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
   if (threadIdx.x == 0) {
     mbar_init(&bars->x_full, 1); mbar_init(&bars->x_empty, 1);
     for (int i = 0; i < W_NST; ++i) { mbar_init(&bars->y_full[i], 1); mbar_init(&bars->y_empty[i], 1); }
-    mbar_init(&bars->s_full, 1); mbar_init(&bars->p_full, 128); mbar_init(&bars->acc_full, 1);
+    mbar_init(&bars->s_full, 1); mbar_init(&bars->p_full, BWD_WORKERS); mbar_init(&bars->acc_full, 1);
     bars->abort_flag = 0;
     mbar_init_fence();
   }
-  if (warp == 5) { tmem_alloc(&bars->tmem_base, 512); tmem_relinquish(); }
+  if (warp == 9) { tmem_alloc(&bars->tmem_base, 512); tmem_relinquish(); }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = bars->tmem_base;
 
-  if (warp == 4) {
+  if (warp == 8) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
       prefetch_tmap(&tm_q); prefetch_tmap(&tm_k); prefetch_tmap(&tm_v); prefetch_tmap(&tm_do);
@@ -125,7 +128,7 @@ swa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         }
       }
     }
-  } else if (warp == 5) {
+  } else if (warp == 9) {
     // ------------------------------------------------------------------ MMA issuer
     const uint32_t leader = elect_one() ? 1u : 0u;
     constexpr uint32_t idesc_s = umma_idesc_bf16(WB, WB, 0, 0);                   // X Y^T: both K-major
@@ -167,20 +170,22 @@ swa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         if (MODE == 0) {
 #pragma unroll
           for (int k = 0; k < WB / 16; ++k)                                     // acc0 += P Y1   (dV += P^T dO)
-            umma_ts_lh_p(leader, a0_t, s_t + k * 8, ymn1 + k * (2048 >> 4), ymn_hi, idesc_a, (acc || k > 0) ? 1u : 0u);
+            umma_ts_lh_p(leader, a0_t, s_t + (k & 3) * 8 + (k >> 2) * 64, ymn1 + k * (2048 >> 4), ymn_hi, idesc_a, (acc || k > 0) ? 1u : 0u);
         }
 #pragma unroll
         for (int k = 0; k < WB / 16; ++k)                                       // acc1 += dZ Y0  (dK += dZ^T Q | dQ += dZ K)
-          umma_ts_lh_p(leader, a1_t, dp_t + k * 8, ymn0 + k * (2048 >> 4), ymn_hi, idesc_a, (acc || k > 0) ? 1u : 0u);
+          umma_ts_lh_p(leader, a1_t, dp_t + (k & 3) * 8 + (k >> 2) * 64, ymn0 + k * (2048 >> 4), ymn_hi, idesc_a, (acc || k > 0) ? 1u : 0u);
         tc_commit_p(leader, &bars->y_empty[st]);
         if (y == hi) { tc_commit_p(leader, &bars->acc_full); tc_commit_p(leader, &bars->x_empty); }
       }
     }
   } else {
     // ------------------------------------------------------------------ P / dZ rebuild and epilogue: thread = TMEM lane
-    const int row = warp * 32 + lane;
-    const uint32_t lane_off = (uint32_t)(warp * 32) << 16;
-    const uint32_t s_t = tmem_base + lane_off, dp_t = s_t + 128, a0_t = s_t + 256, a1_t = s_t + 384;
+    const int half = warp >> 2, quarter = warp & 3;                   // which 64 columns; which 32 TMEM lanes
+    const int row = quarter * 32 + lane;
+    const uint32_t lane_off = (uint32_t)(quarter * 32) << 16;
+    const uint32_t s_t = tmem_base + lane_off + 64 * half, dp_t = s_t + 128;       // this thread's 64 S and 64 dP columns
+    const uint32_t a0_t = tmem_base + lane_off + 256 + 64 * half, a1_t = a0_t + 128;   // and its 64 output columns of each accumulator
     const float c2 = p.scale_log2;
     uint32_t n = 0, it = 0;
     bool ok = true;
@@ -199,13 +204,15 @@ swa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       }
       for (int y = lo; y <= hi; ++y, ++n) {
         float* cf = col_f + (n & 1) * 3 * WB;
-        if (MODE == 0) {                                              // the streamed queries' scalars: one per thread, shared by all lanes
-          const int q = y * WB + row;
-          cf[row] = q < T ? p.lse2[rowbase + q] : 0.f;
-          cf[WB + row] = q < T ? p.delta[rowbase + q] : 0.f;
-          reinterpret_cast<int*>(cf)[2 * WB + row] = (doc_row && q < T) ? min(doc_row[q], q) : 0;
-          // the four warps leave together: a warp that gave up still comes here, and everybody learns of it
-          if (named_bar_or(1, 128, !ok)) { ok = false; break; }
+        if (MODE == 0) {                                              // the streamed queries' scalars, shared by all lanes
+          if (half == 0) {
+            const int q = y * WB + row;
+            cf[row] = q < T ? p.lse2[rowbase + q] : 0.f;
+            cf[WB + row] = q < T ? p.delta[rowbase + q] : 0.f;
+            reinterpret_cast<int*>(cf)[2 * WB + row] = (doc_row && q < T) ? min(doc_row[q], q) : 0;
+          }
+          // the eight warps leave together: a warp that gave up still comes here, and everybody learns of it
+          if (named_bar_or(1, BWD_WORKERS, !ok)) { ok = false; break; }
         }
         ok = __all_sync(0xffffffffu, mbar_wait(&bars->s_full, n & 1, abort_flag, p.status, 6));
         if (!ok) { if (MODE == 0) continue; else break; }
@@ -221,26 +228,33 @@ swa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                  (!doc_row || doc_row[min(blk * WB + WB - 1, T - 1)] <= y0);
         }
 #pragma unroll 1
-        for (int c = 0; c < 4; ++c) {                                 // 32 columns at a time; results go back behind the read pointer
+        for (int c = 0; c < 2; ++c) {                                 // 32 columns at a time; results go back behind the read pointer
           uint32_t rs[32], rd[32];
           tmem_ld32(s_t + 32 * c, rs);
           tmem_ld32(dp_t + 32 * c, rd);
           tc_wait_ld();
           uint32_t pp[16], pz[16];
 #pragma unroll
-          for (int i = 0; i < 32; i += 2) {
-            float pv[2], zv[2];
+          for (int i = 0; i < 32; i += 4) {
+            const int col0 = 64 * half + 32 * c + i;
+            float lse4[4], dl4[4];
+            int doc4[4] = {0, 0, 0, 0};
+            if (MODE == 0) {                                          // four columns' scalars per shared-memory load
+              *reinterpret_cast<float4*>(lse4) = *reinterpret_cast<const float4*>(cf + col0);
+              *reinterpret_cast<float4*>(dl4) = *reinterpret_cast<const float4*>(cf + WB + col0);
+              if (!full) *reinterpret_cast<int4*>(doc4) = *reinterpret_cast<const int4*>(reinterpret_cast<const int*>(cf) + 2 * WB + col0);
+            }
+            float pv[4], zv[4];
 #pragma unroll
-            for (int e = 0; e < 2; ++e) {
-              const int col = 32 * c + i + e;
+            for (int e = 0; e < 4; ++e) {
+              const int col = col0 + e;
               float lse, dl;
               bool vis = true;
               if (MODE == 0) {
-                lse = cf[col]; dl = cf[WB + col];
+                lse = lse4[e]; dl = dl4[e];
                 if (!full) {
                   const int q = y0 + col, k = xr;
-                  vis = (k <= q) && (q < T) && (p.window_blocks > 0 || p.window <= 0 || q - k < p.window) &&
-                        (k >= reinterpret_cast<const int*>(cf)[2 * WB + col]);
+                  vis = (k <= q) && (q < T) && (p.window_blocks > 0 || p.window <= 0 || q - k < p.window) && (k >= doc4[e]);
                 }
               } else {
                 lse = my_lse; dl = my_delta;
@@ -253,8 +267,8 @@ swa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
               pv[e] = pr;
               zv[e] = pr * (__uint_as_float(rd[i + e]) - dl);
             }
-            pp[i >> 1] = pack_bf16(pv[0], pv[1]);
-            pz[i >> 1] = pack_bf16(zv[0], zv[1]);
+            pp[i >> 1] = pack_bf16(pv[0], pv[1]); pp[(i >> 1) + 1] = pack_bf16(pv[2], pv[3]);
+            pz[i >> 1] = pack_bf16(zv[0], zv[1]); pz[(i >> 1) + 1] = pack_bf16(zv[2], zv[3]);
           }
           if (MODE == 0) tmem_st16(s_t + 16 * c, pp);
           tmem_st16(dp_t + 16 * c, pz);
@@ -271,10 +285,10 @@ swa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         tc_fence_after();
 #pragma unroll 1
         for (int which = (MODE == 0 ? 0 : 1); which < 2; ++which) {
-          __nv_bfloat16* dst = (which == 0 ? p.d0 : p.d1) + (((int64_t)b * T + xr) * p.H + h) * DAISY_HEAD_DIM;
+          __nv_bfloat16* dst = (which == 0 ? p.d0 : p.d1) + (((int64_t)b * T + xr) * p.H + h) * DAISY_HEAD_DIM + 64 * half;
           const float sc = which == 0 ? 1.f : p.scale;
 #pragma unroll 1
-          for (int c = 0; c < 4; ++c) {
+          for (int c = 0; c < 2; ++c) {
             uint32_t r[32];
             tmem_ld32((which == 0 ? a0_t : a1_t) + 32 * c, r);
             tc_wait_ld();
@@ -300,7 +314,7 @@ swa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
 
   tc_fence_before();
   __syncthreads();
-  if (warp == 5) { tc_fence_after(); tmem_dealloc(tmem_base, 512); }
+  if (warp == 9) { tc_fence_after(); tmem_dealloc(tmem_base, 512); }
 }
 
 // ---------------------------------------------------------------------------------------------
