@@ -54,6 +54,8 @@ NCU_TRAFFIC = {
                               "captured_at": "813cf57"},
     "decode_per_batch_row": {"bytes": 137.3e6 / 4, "profile": "profiles/swa_decode_partial_kernel__decode_small.md",
                              "captured_at": "c27d954"},
+    "kda_per_token_head": {"bytes": 526.8e6 / 131072, "profile": "profiles/kda_intra_kernel__kda_small.md + profiles/kda_state_kernel__kda_small.md",
+                           "captured_at": "601341c"},
 }
 ROPE_BASE = 10000.0     # the benchmark configs name base 10000 (the module default is 1024, half-truncated)
 
