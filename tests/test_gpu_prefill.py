@@ -108,6 +108,33 @@ def test_attend_bounded_qk_kernel_matches(T, window):
     assert_close_bf16(y_b, y_g.float().cpu(), "bounded vs general", max_tol=1e-2, mean_tol=1e-3)
 
 
+def test_bounded_qk_is_a_caller_promise():
+    """``DAISY_BOUNDED_QK`` promises |q.k| * scale * log2(e) <= 60 for every pair.  The entry point can only check
+    what it can see on the host -- the scale against the head dimension (RMS-normalised q and k give |q.k| <= D) --
+    and falls back to the general kernel when that bound is out of reach; the tensors themselves are not
+    inspected.  When the data break the promise, 2^x without a reference maximum overflows: the affected rows are
+    undefined (typically non-finite), rows whose logits stay in range are unaffected, and the general kernel
+    (the flag left off) gives the right answer for all of them.  The module path always normalises q and k."""
+    from daisy_b200 import ops
+    B, T, H, window = 1, 256, 1, 64
+    q, k, v = (bf16_randn(B, T, H, D, seed=60 + i) for i in range(3))
+    cos, sin = swa.rope_tables(D, T)
+    qp, kp, vp = ops.qkv_prep(q, k, v, cos.cuda(), sin.cuda(), swa.FP32_EPS)
+    y_ok = ops.swa_attend(qp, kp, vp, window, bounded_qk=True)
+    # (1) a scale the bound cannot cover: the flag is ignored, the general kernel runs -- same answer as without it
+    y_big_scale = ops.swa_attend(qp, kp, vp, window, scale=0.5, bounded_qk=True)      # 0.5 * 1.4427 * 128 > 60
+    assert torch.equal(y_big_scale, ops.swa_attend(qp, kp, vp, window, scale=0.5))
+    # (2) the promise broken by the data: rows 128.. of q are 40 x too large (logits up to ~ 40 * 128 * 0.12)
+    q_bad = qp.clone()
+    q_bad[:, 128:] *= 40.0
+    y_gen = ops.swa_attend(q_bad, kp, vp, window)
+    ref = swa.attend_windowed(q_bad.float().cpu(), kp.float().cpu(), vp.float().cpu(), window)
+    assert_close_bf16(y_gen, ref, "general kernel on out-of-bound logits", max_tol=4e-2, mean_tol=4e-3)
+    y_bad = ops.swa_attend(q_bad, kp, vp, window, bounded_qk=True)
+    ops.check_device_status("cuda")
+    assert torch.equal(y_bad[:, :128], y_ok[:, :128])                    # rows that keep the promise: untouched
+
+
 @pytest.mark.parametrize("T,window", [(5, 3), (300, 64), (513, 129), (1300, 512)])
 def test_q_prepared_in_kernel_matches(T, window):
     """DAISY_Q_IN_KERNEL: Q is normalised and rotated inside the attention kernel (in the swizzled tile, one
