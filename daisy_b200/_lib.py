@@ -60,6 +60,9 @@ SIGNATURES = {
     "daisy_b200_ring_copy_rows": (_i, [_vp] + [_i64] * 3 + [_vp] + [_i64] * 3 + [_i] * 4 + [_i64] + [_i] * 3 + [_vp]),
     "daisy_b200_kda_workspace_bytes": (_sz, [_i] * 5),
     "daisy_b200_kda_chunk_fwd": (_i, [_vp] * 8 + [_i] * 6 + [_f, _u, _vp, _sz, _vp, _vp]),
+    "daisy_b200_kda_varlen_workspace_bytes": (_sz, [_i] * 4),
+    "daisy_b200_kda_chunk_fwd_varlen": (_i, [_vp] * 8 + [_i] * 5 + [_f, _u, _vp, _i, _vp, _i, _vp, _sz, _vp, _vp]),
+    "daisy_b200_kda_short_conv_varlen": (_i, [_vp, _i64, _vp, _vp, _vp, _vp, _vp, _i64, _i, _i, _i, _vp, _u, _vp]),
     "daisy_b200_kda_recurrent_fwd": (_i, [_vp] * 8 + [_i] * 5 + [_f, _u, _vp]),
     "daisy_b200_kda_gate": (_i, [_vp, _i, _vp, _vp, _vp, _i64, _i, _i, _f, _f, _u, _vp]),
     "daisy_b200_kda_short_conv": (_i, [_vp, _i64, _i64, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i, _i, _i, _i, _u, _vp]),

@@ -100,6 +100,9 @@ struct KdaIntraParams {
   float scale;
   int l2norm;
   int* status;
+  // packed variable-length sequences (B = 1): chunk c of the packed row covers tokens chunk_tab[2c] .. + chunk_tab[2c+1]
+  // (1..64 of them; chunks never straddle a sequence boundary); null: chunk c covers tokens 64 c ..
+  const int* chunk_tab;
 };
 
 constexpr int KI_ELEM_WARPS = 16, KI_SOLVER_WARPS = 8;
@@ -142,6 +145,11 @@ __device__ __forceinline__ void ki_coords(int w, int NC, int H, int& b, int& h, 
   const int bh = w / NC;
   h = bh % H;
   b = bh / H;
+}
+// first token and number of tokens of a chunk
+__device__ __forceinline__ void ki_chunk_span(const int* chunk_tab, int chunk, int T, int& t0, int& rows) {
+  if (chunk_tab) { t0 = chunk_tab[2 * chunk]; rows = chunk_tab[2 * chunk + 1]; }
+  else { t0 = chunk * KC; rows = min(KC, T - t0); }
 }
 
 __device__ __forceinline__ uint32_t hmul2_u32(uint32_t a, uint32_t b) {
@@ -237,13 +245,14 @@ kda_intra_kernel(const __grid_constant__ CUtensorMap tm_g, const __grid_constant
     // ================================================================== element warps
     const int c = tid & (KD - 1), seg = tid >> 7;          // this thread's channel and 16-token segment (warp-uniform)
     if (tid == 0 && (int)blockIdx.x < p.total) {
-      int b, h, chunk;
+      int b, h, chunk, ft0, frows;
       ki_coords(blockIdx.x, p.NC, p.H, b, h, chunk);
+      ki_chunk_span(p.chunk_tab, chunk, p.T, ft0, frows);
       prefetch_tmap(&tm_g); prefetch_tmap(&tm_q); prefetch_tmap(&tm_k);
       mbar_expect_tx(&sm.in_full, KI_IN_BYTES);
-      tma_load_4d(&sm.g[0][0], &tm_g, &sm.in_full, 0, chunk * KC, h, b);
-      tma_load_4d(&sm.q[0][0], &tm_q, &sm.in_full, 0, chunk * KC, h, b);
-      tma_load_4d(&sm.k[0][0], &tm_k, &sm.in_full, 0, chunk * KC, h, b);
+      tma_load_4d(&sm.g[0][0], &tm_g, &sm.in_full, 0, ft0, h, b);
+      tma_load_4d(&sm.q[0][0], &tm_q, &sm.in_full, 0, ft0, h, b);
+      tma_load_4d(&sm.k[0][0], &tm_k, &sm.in_full, 0, ft0, h, b);
     }
     // warps 0..5 double as the issuers of the six Gram products (warp li issues level li): after its own share of
     // the level's images the warp waits for everybody else's (all element warps do the same work in step, so the
@@ -257,9 +266,21 @@ kda_intra_kernel(const __grid_constant__ CUtensorMap tm_g, const __grid_constant
       int b, h, chunk;
       ki_coords(w, p.NC, p.H, b, h, chunk);
       const int par = ci & 1;
-      const int t0 = chunk * KC;
+      int t0, rows;
+      ki_chunk_span(p.chunk_tab, chunk, p.T, t0, rows);
       uint8_t* rec = p.ws + (size_t)w * REC_BYTES;
       ok = mbar_wait_long(&sm.in_full, ci & 1, abort_flag, p.status, 1) && ok;
+      if (p.chunk_tab && rows < KC) {
+        // a sequence's last chunk: the rows after it belong to the next sequence (the tile load only zero-fills past
+        // the end of the tensor) -- blank them, so that they behave like padding: g = 0, k = q = 0 (beta = 0 below)
+        for (int i = tid; i < (KC - rows) * (KD / 4); i += KI_ELEM_THREADS) {
+          const int r = rows + i / (KD / 4), c4 = (i % (KD / 4)) * 4;
+          *reinterpret_cast<float4*>(&sm.g[r][c4]) = make_float4(0.f, 0.f, 0.f, 0.f);
+          *reinterpret_cast<uint2*>(&sm.q[r][c4]) = make_uint2(0u, 0u);
+          *reinterpret_cast<uint2*>(&sm.k[r][c4]) = make_uint2(0u, 0u);
+        }
+        named_bar(1, KI_ELEM_THREADS);
+      }
 
       // ---- per-token scalars: 8 threads per row, 16 channels each
       {
@@ -282,7 +303,7 @@ kda_intra_kernel(const __grid_constant__ CUtensorMap tm_g, const __grid_constant
           const float a = p.l2norm ? rsqrtf(sq + 1e-6f) : 1.f, cc = p.l2norm ? rsqrtf(sk + 1e-6f) : 1.f;
           sm.rq[par][r] = a; sm.rk[par][r] = cc; sm.qkd[par][r] = a * cc * dqk;
         }
-        if (tid < KC) sm.beta[par][tid] = (t0 + tid < p.T) ? p.beta[((size_t)b * p.T + t0 + tid) * p.H + h] : 0.f;
+        if (tid < KC) sm.beta[par][tid] = (tid < rows) ? p.beta[((size_t)b * p.T + t0 + tid) * p.H + h] : 0.f;
       }
       if (named_bar_or(1, KI_ELEM_THREADS, !ok)) break;
 
@@ -310,12 +331,13 @@ kda_intra_kernel(const __grid_constant__ CUtensorMap tm_g, const __grid_constant
       }
       named_bar(1, KI_ELEM_THREADS);                                            // every read of the input tiles is done
       if (tid == 0 && w + (int)gridDim.x < p.total) {                           // next item's inputs land under this item's work
-        int nb, nh, nchunk;
+        int nb, nh, nchunk, nt0, nrows;
         ki_coords(w + gridDim.x, p.NC, p.H, nb, nh, nchunk);
+        ki_chunk_span(p.chunk_tab, nchunk, p.T, nt0, nrows);
         mbar_expect_tx(&sm.in_full, KI_IN_BYTES);
-        tma_load_4d(&sm.g[0][0], &tm_g, &sm.in_full, 0, nchunk * KC, nh, nb);
-        tma_load_4d(&sm.q[0][0], &tm_q, &sm.in_full, 0, nchunk * KC, nh, nb);
-        tma_load_4d(&sm.k[0][0], &tm_k, &sm.in_full, 0, nchunk * KC, nh, nb);
+        tma_load_4d(&sm.g[0][0], &tm_g, &sm.in_full, 0, nt0, nh, nb);
+        tma_load_4d(&sm.q[0][0], &tm_q, &sm.in_full, 0, nt0, nh, nb);
+        tma_load_4d(&sm.k[0][0], &tm_k, &sm.in_full, 0, nt0, nh, nb);
       }
 
       // ---- six levels.  At level s token t is "upper" iff bit s of t is set; its factor is pre (upper) or suf (lower):
@@ -394,11 +416,12 @@ kda_intra_kernel(const __grid_constant__ CUtensorMap tm_g, const __grid_constant
     const int row = 32 * hb + lane;
     const uint32_t lane_base = tmem_base + ((uint32_t)(32 * qt4) << 16);
     if (st == 0 && (int)blockIdx.x < p.total) {
-      int b, h, chunk;
+      int b, h, chunk, ft0, frows;
       ki_coords(blockIdx.x, p.NC, p.H, b, h, chunk);
+      ki_chunk_span(p.chunk_tab, chunk, p.T, ft0, frows);
       prefetch_tmap(&tm_v);
       mbar_expect_tx(&sm.v_full, KI_IMG_BYTES);
-      tma_load_4d(&sm.v[0][0], &tm_v, &sm.v_full, 0, chunk * KC, h, b);
+      tma_load_4d(&sm.v[0][0], &tm_v, &sm.v_full, 0, ft0, h, b);
     }
     uint32_t ci = 0;
     bool ok = true;
@@ -568,10 +591,11 @@ kda_intra_kernel(const __grid_constant__ CUtensorMap tm_g, const __grid_constant
       if (st == 0) {
         mbar_arrive(&sm.x_empty);
         if (w + (int)gridDim.x < p.total) {
-          int nb, nh, nchunk;
+          int nb, nh, nchunk, nt0, nrows;
           ki_coords(w + gridDim.x, p.NC, p.H, nb, nh, nchunk);
+          ki_chunk_span(p.chunk_tab, nchunk, p.T, nt0, nrows);
           mbar_expect_tx(&sm.v_full, KI_IMG_BYTES);
-          tma_load_4d(&sm.v[0][0], &tm_v, &sm.v_full, 0, nchunk * KC, nh, nb);
+          tma_load_4d(&sm.v[0][0], &tm_v, &sm.v_full, 0, nt0, nh, nb);
         }
       }
     }
@@ -596,6 +620,10 @@ struct KdaStateParams {
   void* o;
   int T, H, NC, out_fp32;
   int* status;
+  // packed variable-length sequences (B = 1): blockIdx.y = sequence * H + head, the sequence's chunks are
+  // seq_ptr[s] .. seq_ptr[s + 1] - 1 of the packed row's NC chunks, chunk_tab as in the intra kernel; null: dense
+  const int* chunk_tab;
+  const int* seq_ptr;
 };
 
 constexpr int KDA_NST = 2;     // ring stages
@@ -621,10 +649,13 @@ __global__ void __launch_bounds__(32 * (NW + 1), 1) kda_state_kernel(const KdaSt
   volatile int* abort_flag = reinterpret_cast<volatile int*>(empty + KDA_NST);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g8 = lane >> 2, t4 = lane & 3;
-  const int vsl = blockIdx.x, bh = blockIdx.y;
-  const int b = bh / p.H, h = bh % p.H;
+  const int vsl = blockIdx.x, bh = blockIdx.y;              // bh also indexes h0 / hT
+  const int h = bh % p.H;
+  const int b = p.seq_ptr ? 0 : bh / p.H;
+  const int c_begin = p.seq_ptr ? p.seq_ptr[bh / p.H] : 0, c_end = p.seq_ptr ? p.seq_ptr[bh / p.H + 1] : p.NC;
   const int v_base = vsl * VS;
-  const uint8_t* recs = p.ws + (size_t)bh * p.NC * REC_BYTES;
+  const uint8_t* recs = p.ws + ((size_t)(b * p.H + h) * p.NC + c_begin) * REC_BYTES;    // this sequence's first record
+  const int n_chunks = c_end - c_begin;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < KDA_NST; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], NW); }
@@ -636,7 +667,7 @@ __global__ void __launch_bounds__(32 * (NW + 1), 1) kda_state_kernel(const KdaSt
   if (warp == NW) {
     // ------------------------------------------------------------ producer: bulk copies into the ring
     if (lane == 0) {
-      for (int c = 0; c < p.NC; ++c) {
+      for (int c = 0; c < n_chunks; ++c) {
         const int s = c % KDA_NST;
         if (!mbar_wait(&empty[s], ((c / KDA_NST) & 1) ^ 1, abort_flag, p.status, 1)) break;
         const uint8_t* rec = recs + (size_t)c * REC_BYTES;
@@ -663,7 +694,7 @@ __global__ void __launch_bounds__(32 * (NW + 1), 1) kda_state_kernel(const KdaSt
     }
   }
 
-  for (int c = 0; c < p.NC; ++c) {
+  for (int c = 0; c < n_chunks; ++c) {
     const int s = c % KDA_NST;
     const bool ok = __all_sync(0xffffffffu, mbar_wait(&full[s], (c / KDA_NST) & 1, abort_flag, p.status, 2));
     if (!ok) break;
@@ -751,12 +782,13 @@ __global__ void __launch_bounds__(32 * (NW + 1), 1) kda_state_kernel(const KdaSt
       o_stage[tok * L::O_LD + vr1] = ao[nt][2]; o_stage[(tok + 1) * L::O_LD + vr1] = ao[nt][3];
     }
     asm volatile("bar.sync 1, %0;" ::"n"(32 * NW) : "memory");
-    const int rows = min(KC, p.T - c * KC);
+    int t0, rows;
+    ki_chunk_span(p.chunk_tab, c_begin + c, p.T, t0, rows);
     for (int idx = threadIdx.x; idx < KC * (VS / 4); idx += 32 * NW) {
       const int tok = idx / (VS / 4), v4 = (idx % (VS / 4)) * 4;
       if (tok >= rows) continue;
       const float4 x = *reinterpret_cast<const float4*>(&o_stage[tok * L::O_LD + v4]);
-      const size_t off = (((size_t)b * p.T + (size_t)c * KC + tok) * p.H + h) * KD + v_base + v4;
+      const size_t off = (((size_t)b * p.T + (size_t)t0 + tok) * p.H + h) * KD + v_base + v4;
       if (p.out_fp32) {
         *reinterpret_cast<float4*>(reinterpret_cast<float*>(p.o) + off) = x;
       } else {
@@ -801,20 +833,21 @@ static int launch_state(const KdaStateParams& sp, int BH, cudaStream_t st) {
   return cudaGetLastError() == cudaSuccess ? DAISY_OK : DAISY_ECUDA;
 }
 
-extern "C" int daisy_b200_kda_chunk_fwd(const void* q, const void* k, const void* v, const float* g,
-                                        const float* beta, const float* h0, void* o, float* hT,
-                                        int B, int T, int H, int K, int V, int chunk, float scale,
-                                        unsigned flags, void* workspace, size_t workspace_bytes,
-                                        int* status_word, void* stream) {
-  if (!q || !k || !v || !g || !beta || !o || !workspace || B <= 0 || T <= 0 || H <= 0) return DAISY_EINVAL;
+// Shared launcher.  Dense: NC = ceil(T / 64) chunks per (batch, head) row, n_seq = B.  Packed variable-length (B = 1):
+// chunk_tab [NC][2] and seq_ptr [n_seq + 1] (both in device memory) say which tokens each chunk covers and which
+// chunks each sequence owns; h0 / hT are [n_seq, H, K, V].
+static int kda_launch(const void* q, const void* k, const void* v, const float* g, const float* beta, const float* h0, void* o,
+                      float* hT, int B, int T, int H, int K, int V, int chunk, float scale, unsigned flags,
+                      void* workspace, size_t workspace_bytes, int NC, int n_seq, const int* chunk_tab, const int* seq_ptr,
+                      int* status_word, void* stream) {
+  if (!q || !k || !v || !g || !beta || !o || !workspace || B <= 0 || T <= 0 || H <= 0 || NC <= 0 || n_seq <= 0) return DAISY_EINVAL;
   if (K != KD || V != KD || chunk != KC) return DAISY_EUNSUPPORTED;
-  if (B > 65535 || H > 65535 || (size_t)B * H > 65535) return DAISY_EUNSUPPORTED;
-  if (workspace_bytes < daisy_b200_kda_workspace_bytes(B, T, H, K, V)) return DAISY_EWORKSPACE;
+  if (B > 65535 || H > 65535 || (size_t)n_seq * H > 65535) return DAISY_EUNSUPPORTED;
+  if (workspace_bytes < (size_t)B * H * NC * REC_BYTES) return DAISY_EWORKSPACE;
   if (!daisy_aligned16(q) || !daisy_aligned16(k) || !daisy_aligned16(v) || !daisy_aligned16(g) || !daisy_aligned16(o) ||
       !daisy_aligned16(workspace) || (h0 && !daisy_aligned16(h0)) || (hT && !daisy_aligned16(hT)))
     return DAISY_EALIGN;
   cudaStream_t st = (cudaStream_t)stream;
-  const int NC = (T + KC - 1) / KC;
   static bool attr[daisy_host::MAX_DEVICES] = {};             // the attribute is per device
   const int dev = daisy_host::device_slot();
   if (dev < 0) return DAISY_ENODEV;
@@ -839,6 +872,7 @@ extern "C" int daisy_b200_kda_chunk_fwd(const void* q, const void* k, const void
   ip.scale = scale > 0.f ? scale : 1.0f / sqrtf((float)K);
   ip.l2norm = (flags & DAISY_KDA_L2NORM_QK) ? 1 : 0;
   ip.status = status_word;
+  ip.chunk_tab = chunk_tab;
   const int sms = daisy_host::sm_count_cached();
   if (sms <= 0) return DAISY_ENODEV;
   kda_intra_kernel<<<ip.total < sms ? ip.total : sms, KI_THREADS, intra_smem, st>>>(tg, tq, tk, tv, ip);
@@ -848,12 +882,39 @@ extern "C" int daisy_b200_kda_chunk_fwd(const void* q, const void* k, const void
   sp.ws = (const uint8_t*)workspace; sp.h0 = h0; sp.hT = hT; sp.o = o;
   sp.T = T; sp.H = H; sp.NC = NC; sp.out_fp32 = (flags & DAISY_KDA_OUT_FP32) ? 1 : 0;
   sp.status = status_word;
-  const int BH = B * H;
-  // V-slices: 64 rows (4 warps) fill the machine when B*H >= 64; fewer sequences take narrower slices
+  sp.chunk_tab = chunk_tab; sp.seq_ptr = seq_ptr;
+  const int BH = n_seq * H;
+  // V-slices: 64 rows (4 warps) fill the machine when there are >= 48 (sequence, head) pairs; fewer take narrower slices
   int rc;
   if (BH * 2 >= 96) rc = launch_state<4>(sp, BH, st);
   else if (BH * 4 >= 96) rc = launch_state<2>(sp, BH, st);
   else rc = launch_state<1>(sp, BH, st);
   if (rc != DAISY_OK) { (void)cudaGetLastError(); return rc; }
   return DAISY_OK;
+}
+
+extern "C" int daisy_b200_kda_chunk_fwd(const void* q, const void* k, const void* v, const float* g,
+                                        const float* beta, const float* h0, void* o, float* hT,
+                                        int B, int T, int H, int K, int V, int chunk, float scale,
+                                        unsigned flags, void* workspace, size_t workspace_bytes,
+                                        int* status_word, void* stream) {
+  if (T <= 0) return DAISY_EINVAL;
+  return kda_launch(q, k, v, g, beta, h0, o, hT, B, T, H, K, V, chunk, scale, flags, workspace, workspace_bytes,
+                    (T + KC - 1) / KC, B, nullptr, nullptr, status_word, stream);
+}
+
+extern "C" size_t daisy_b200_kda_varlen_workspace_bytes(int n_chunks, int H, int K, int V) {
+  if (n_chunks <= 0 || H <= 0 || K != KD || V != KD) return 0;
+  return (size_t)H * n_chunks * REC_BYTES;
+}
+
+extern "C" int daisy_b200_kda_chunk_fwd_varlen(const void* q, const void* k, const void* v, const float* g,
+                                               const float* beta, const float* h0, void* o, float* hT,
+                                               int T_total, int H, int K, int V, int chunk, float scale, unsigned flags,
+                                               const int32_t* chunk_tab, int n_chunks, const int32_t* seq_ptr, int n_seq,
+                                               void* workspace, size_t workspace_bytes, int* status_word, void* stream) {
+  if (!chunk_tab || !seq_ptr || n_chunks <= 0 || n_seq <= 0) return DAISY_EINVAL;
+  if ((reinterpret_cast<uintptr_t>(chunk_tab) & 7) || (reinterpret_cast<uintptr_t>(seq_ptr) & 3)) return DAISY_EALIGN;
+  return kda_launch(q, k, v, g, beta, h0, o, hT, 1, T_total, H, K, V, chunk, scale, flags, workspace, workspace_bytes,
+                    n_chunks, n_seq, chunk_tab, seq_ptr, status_word, stream);
 }

@@ -26,6 +26,8 @@ struct ShortConvParams {
   __nv_bfloat16* y;              // [B, T, C], strides y_st, y_sb
   long long x_sb, x_st, y_sb, y_st;
   int T, C, W, silu;
+  const int2* tok;               // packed sequences (B = 1): per token (first token of its sequence, sequence index), else null;
+                                 // s_in / s_out are then [n_seq, C, W]
 };
 
 __device__ __forceinline__ void unpack4(const uint2 u, float* f) {
@@ -54,7 +56,10 @@ __device__ __forceinline__ uint4 conv_state_row(const ShortConvParams& p, int b,
 // Phase 1: the CTA's tile of x (35 rows x 1 KB) goes to shared memory with coalesced 16-byte loads, all of a thread's
 // loads in flight before the first is used.  Phase 2: thread = 4 channels x 16 consecutive rows, sliding the taps'
 // window through registers, one 8-byte shared-memory read and one 8-byte store per row.
-template <bool SILU>
+// Packed sequences: the window never crosses a sequence's first token -- the inputs before it are that sequence's
+// carried state (or zeros), patched into the sliding registers at the first three rows of each sequence -- and the row
+// that ends a sequence leaves that sequence's state.
+template <bool SILU, bool VARLEN>
 __global__ void __launch_bounds__(SC_THREADS) kda_short_conv_kernel(const ShortConvParams p) {
   __shared__ uint4 tile[SC_TILE_ROWS][SC_COLS / 8];
   const int cblk = blockIdx.x * SC_COLS;                           // channel blocks vary fastest, then time blocks:
@@ -71,7 +76,7 @@ __global__ void __launch_bounds__(SC_THREADS) kda_short_conv_kernel(const ShortC
     v[i] = make_uint4(0, 0, 0, 0);
     if (r < SC_TILE_ROWS && c < p.C) {
       if (t >= 0) { if (t < t_end) v[i] = ld_stream16(xb + (long long)t * p.x_st + c); }
-      else v[i] = conv_state_row(p, b, t, c);
+      else if (!VARLEN) v[i] = conv_state_row(p, b, t, c);
     }
   }
 #pragma unroll
@@ -129,6 +134,21 @@ __global__ void __launch_bounds__(SC_THREADS) kda_short_conv_kernel(const ShortC
     const int t = tblk + r0 + i;
     float cur[SC_CH], o[SC_CH];
     unpack4(col[(r0 + 3 + i) * RS], cur);
+    int2 tk = make_int2(0, 0);
+    if (VARLEN && t < t_end) {
+      tk = __ldg(p.tok + t);
+      if (t - 3 < tk.x) {                                          // one of the three rows back lies before this sequence
+        const __nv_bfloat16* s = p.s_in ? p.s_in + ((long long)tk.y * p.C + c0) * p.W : nullptr;
+#pragma unroll
+        for (int e = 0; e < SC_CH; ++e) {
+          const int o1 = p.W + (t - 1 - tk.x), o2 = o1 - 1, o3 = o1 - 2;     // slot in the state of rows t-1, t-2, t-3
+          if (t - 1 < tk.x) h1[e] = (s && o1 >= 0) ? __bfloat162float(s[e * p.W + o1]) : 0.f;
+          if (t - 2 < tk.x) h2[e] = (s && o2 >= 0) ? __bfloat162float(s[e * p.W + o2]) : 0.f;
+          if (t - 3 < tk.x) h3[e] = (s && o3 >= 0) ? __bfloat162float(s[e * p.W + o3]) : 0.f;
+        }
+      }
+    }
+    float old3[SC_CH];
 #pragma unroll
     for (int e = 0; e < SC_CH; ++e) {
       float a = bs[e];
@@ -137,11 +157,21 @@ __global__ void __launch_bounds__(SC_THREADS) kda_short_conv_kernel(const ShortC
       a = fmaf(wt[e][2], h1[e], a);
       a = fmaf(wt[e][3], cur[e], a);
       o[e] = SILU ? a * fast_sigmoid(a) : a;
+      old3[e] = h3[e];
       h3[e] = h2[e]; h2[e] = h1[e]; h1[e] = cur[e];
     }
     if (t < t_end)
       *reinterpret_cast<uint2*>(yr + (long long)t * p.y_st) = make_uint2(pack_bf16(o[0], o[1]), pack_bf16(o[2], o[3]));
+    if (VARLEN && p.s_out && t < t_end && (t == p.T - 1 || __ldg(p.tok + t + 1).x == t + 1)) {
+      __nv_bfloat16* s = p.s_out + ((long long)tk.y * p.C + c0) * p.W;         // the sequence ends here: rows t-W+1 .. t
+#pragma unroll
+      for (int e = 0; e < SC_CH; ++e) {
+        const float last[4] = {old3[e], h3[e], h2[e], h1[e]};
+        for (int j = 0; j < p.W; ++j) s[e * p.W + j] = __float2bfloat16_rn(last[4 - p.W + j]);
+      }
+    }
   }
+  if (VARLEN) return;
 
   // the CTA that owns the last row leaves the state: the last W inputs, oldest first (tile row of input t: t - tblk + 3)
   if (p.s_out && t_end == p.T && slice == 0) {
@@ -277,9 +307,33 @@ extern "C" int daisy_b200_kda_short_conv(const void* x, int64_t x_sb, int64_t x_
   p.s_in = (const __nv_bfloat16*)state_in; p.s_out = (__nv_bfloat16*)state_out; p.y = (__nv_bfloat16*)y;
   p.x_sb = x_sb; p.x_st = x_st; p.y_sb = y_sb; p.y_st = y_st;
   p.T = T; p.C = C; p.W = W; p.silu = (flags & DAISY_KDA_CONV_SILU) ? 1 : 0;
+  p.tok = nullptr;
   const dim3 grid((C + SC_COLS - 1) / SC_COLS, (T + SC_ROWS - 1) / SC_ROWS, B);
-  if (p.silu) kda_short_conv_kernel<true><<<grid, SC_THREADS, 0, (cudaStream_t)stream>>>(p);
-  else        kda_short_conv_kernel<false><<<grid, SC_THREADS, 0, (cudaStream_t)stream>>>(p);
+  if (p.silu) kda_short_conv_kernel<true, false><<<grid, SC_THREADS, 0, (cudaStream_t)stream>>>(p);
+  else        kda_short_conv_kernel<false, false><<<grid, SC_THREADS, 0, (cudaStream_t)stream>>>(p);
+  DAISY_CHECK_LAUNCH();
+  return DAISY_OK;
+}
+
+extern "C" int daisy_b200_kda_short_conv_varlen(const void* x, int64_t x_st, const void* w, const void* bias,
+                                                const void* state_in, void* state_out, void* y, int64_t y_st,
+                                                int T, int C, int W, const int32_t* tok_tab, unsigned flags, void* stream) {
+  if (!x || !w || !y || !tok_tab || T <= 0 || C <= 0) return DAISY_EINVAL;
+  if (W < 1 || W > SC_MAX_W || C % 8 != 0 || (T + SC_ROWS - 1) / SC_ROWS > 65535) return DAISY_EUNSUPPORTED;
+  if (flags & ~DAISY_KDA_CONV_SILU) return DAISY_EINVAL;
+  if (!daisy_aligned16(x) || !daisy_aligned16(y) || !daisy_aligned16(w) || (bias && !daisy_aligned16(bias)) ||
+      x_st % 8 || y_st % 8 || (reinterpret_cast<uintptr_t>(tok_tab) & 7))
+    return DAISY_EALIGN;
+  if (state_in && state_in == state_out) return DAISY_EINVAL;     // sequences end in different CTAs
+  ShortConvParams p;
+  p.x = (const __nv_bfloat16*)x; p.w = (const __nv_bfloat16*)w; p.bias = (const __nv_bfloat16*)bias;
+  p.s_in = (const __nv_bfloat16*)state_in; p.s_out = (__nv_bfloat16*)state_out; p.y = (__nv_bfloat16*)y;
+  p.x_sb = 0; p.x_st = x_st; p.y_sb = 0; p.y_st = y_st;
+  p.T = T; p.C = C; p.W = W; p.silu = (flags & DAISY_KDA_CONV_SILU) ? 1 : 0;
+  p.tok = reinterpret_cast<const int2*>(tok_tab);
+  const dim3 grid((C + SC_COLS - 1) / SC_COLS, (T + SC_ROWS - 1) / SC_ROWS, 1);
+  if (p.silu) kda_short_conv_kernel<true, true><<<grid, SC_THREADS, 0, (cudaStream_t)stream>>>(p);
+  else        kda_short_conv_kernel<false, true><<<grid, SC_THREADS, 0, (cudaStream_t)stream>>>(p);
   DAISY_CHECK_LAUNCH();
   return DAISY_OK;
 }

@@ -30,18 +30,44 @@ RECURRENT_MAX_T = 4      # up to this many tokens the state is carried token by 
 
 def chunk_kda(q, k, v, g, beta, scale: Optional[float] = None, initial_state: Optional[torch.Tensor] = None,
               output_final_state: bool = False, use_qk_l2norm_in_kernel: bool = False, cu_seqlens=None,
-              out_fp32: bool = False):
-    if cu_seqlens is not None:
-        raise NotImplementedError("variable-length packing (cu_seqlens) is not implemented by the B200 KDA kernels")
+              out_fp32: bool = False, varlen_tables=None):
     q, k, v = (x.contiguous() if x.dtype == torch.bfloat16 else x.to(torch.bfloat16).contiguous() for x in (q, k, v))
     g = g.float().contiguous()
     beta = beta.float().contiguous()
     if initial_state is not None:
         initial_state = initial_state.float().contiguous()
+    if cu_seqlens is not None or varlen_tables is not None:
+        # packed sequences [1, T_total, ...]: states are per sequence, no chunk spans two of them
+        return ops.kda_chunk_fwd_varlen(q, k, v, g, beta, cu_seqlens, scale, initial_state, output_final_state,
+                                        l2norm_qk=use_qk_l2norm_in_kernel, out_fp32=out_fp32, tables=varlen_tables)
     fwd = ops.kda_recurrent_fwd if q.shape[1] <= RECURRENT_MAX_T else ops.kda_chunk_fwd
     o, hT = fwd(q, k, v, g, beta, scale, initial_state, output_final_state,
                 l2norm_qk=use_qk_l2norm_in_kernel, out_fp32=out_fp32)
     return o, hT
+
+
+def get_unpad_data(attention_mask: torch.Tensor):
+    """``(indices, cu_seqlens, max_len)`` of a ``[B, S]`` 0/1 mask, as the helper the reference imports
+    (models/daisy/attention_kimi.py:19, used at :150): the flat positions of the kept tokens, the N + 1 offsets of the
+    rows' kept counts, and the largest count."""
+    m = attention_mask.to(torch.bool)
+    lens = m.sum(dim=-1, dtype=torch.int32)
+    indices = torch.nonzero(m.flatten(), as_tuple=False).flatten()
+    cu = torch.nn.functional.pad(torch.cumsum(lens, 0, dtype=torch.int32), (1, 0))
+    return indices, cu, int(lens.max().item()) if lens.numel() else 0
+
+
+def index_first_axis(x: torch.Tensor, indices: torch.Tensor) -> torch.Tensor:
+    """Rows ``indices`` of ``x [(B S), ...]`` (attention_kimi.py:153)."""
+    return x.index_select(0, indices)
+
+
+def pad_input(x: torch.Tensor, indices: torch.Tensor, batch: int, seqlen: int) -> torch.Tensor:
+    """Inverse of :func:`index_first_axis`: ``x [T_total, ...]`` back to ``[batch, seqlen, ...]``, zeros at the dropped
+    positions (attention_kimi.py:193)."""
+    out = x.new_zeros(batch * seqlen, *x.shape[1:])
+    out.index_copy_(0, indices, x)
+    return out.view(batch, seqlen, *x.shape[1:])
 
 
 def fused_kda_gate(g, A_log, head_k_dim: int, g_bias=None, b=None, beta: float = 1.0, threshold: float = 20.0):
@@ -73,11 +99,15 @@ class B200ShortConvolution(torch.nn.Conv1d):
             raise ValueError(f"activation {activation!r} not supported")
         self.hidden_size, self.activation = hidden_size, activation
 
-    def forward(self, x, cache=None, output_final_state: bool = False, cu_seqlens=None, **_):
-        if cu_seqlens is not None:
-            raise NotImplementedError("variable-length packing (cu_seqlens) is not implemented by the B200 KDA kernels")
+    def forward(self, x, cache=None, output_final_state: bool = False, cu_seqlens=None, varlen_tables=None, **_):
         if cache is not None and cache.dtype != torch.bfloat16:
             cache = cache.to(torch.bfloat16)
+        if cu_seqlens is not None or varlen_tables is not None:
+            # packed sequences x [1, T_total, C]; cache and final state [N, C, W]
+            tabs = varlen_tables if varlen_tables is not None else ops.kda_varlen_tables(cu_seqlens, x.device)
+            return ops.kda_short_conv_varlen(x if x.dtype == torch.bfloat16 else x.to(torch.bfloat16), self.weight,
+                                             tabs[2], tabs[1].numel() - 1, self.bias, state=cache,
+                                             output_final_state=output_final_state, silu=self.activation is not None)
         step = cache is not None and x.shape[1] <= 32
         return ops.kda_short_conv(x if x.dtype == torch.bfloat16 else x.to(torch.bfloat16), self.weight, self.bias,
                                   state=cache, output_final_state=output_final_state or step,
@@ -117,8 +147,10 @@ class B200KimiLinearSelfAttention(torch.nn.Module):
     recurrent step for decode) -> gated norm (:135-137) -> output projection.  The reference's ``forward`` cannot
     run as written (it passes five arguments to a four-parameter ``_forward_core`` whose body then reads an
     undefined ``sa_lambdas``); this class implements what those lines evidently intend, with ``sa_lambdas``
-    threaded through.  The batch-size-1 assertion (:151) is lifted; ``attn_mask`` (varlen unpadding) is not
-    supported."""
+    threaded through.  The batch-size-1 assertion (:151) is lifted.  ``attn_mask [B, S_total]`` (1 = token, 0 =
+    padding) packs the kept tokens of the last ``T`` columns into one row, runs the convolutions and the KDA per
+    sequence (cu_seqlens, :150-162) and scatters the result back with zeros at the padding (:193); the cached states
+    are then one per batch row, so decode steps continue from them."""
 
     def __init__(self, dim: int, num_heads: int, max_seq_len: int, head_dim: int, expand_v: float = 1.0,
                  mode: str = "chunk", use_short_conv: bool = True, allow_neg_eigval: bool = False, conv_size: int = 4,
@@ -153,20 +185,28 @@ class B200KimiLinearSelfAttention(torch.nn.Module):
         self._recurrent_state, self._conv_state, self._seen = None, None, 0
 
     def _forward_core(self, x, ve, sa_lambdas, attn_mask, use_cache: bool):
-        if attn_mask is not None:
-            raise NotImplementedError("attn_mask (variable-length unpadding) is not implemented by the B200 KDA layer")
         if torch.is_grad_enabled() and (x.requires_grad or any(p.requires_grad for p in self.parameters())):
             # the kernels return tensors without a grad_fn: autograd would treat the layer as a constant
             raise NotImplementedError("daisy_b200 implements the forward pass only: call under torch.no_grad() / "
                                       "inference_mode(), or detach the input and freeze the parameters")
+        B0, T0, _ = x.shape
+        indices = tabs = None
+        if attn_mask is not None:                                          # attention_kimi.py:150-154
+            indices, cu_seqlens, _ = get_unpad_data(attn_mask[:, -T0:])
+            x = index_first_axis(x.reshape(B0 * T0, -1), indices).unsqueeze(0)
+            if ve is not None:
+                ve = index_first_axis(ve.reshape(B0 * T0, -1), indices).unsqueeze(0)
+            tabs = ops.kda_varlen_tables(cu_seqlens, x.device)
+            if x.shape[1] == 0:
+                return x.new_zeros(B0, T0, self.hidden_size)
         B, T, _ = x.shape
         H = self.num_heads
         q, k, v = _linear(x, self.q_proj.weight), _linear(x, self.k_proj.weight), _linear(x, self.v_proj.weight)
         if self.use_short_conv:
             cs = self._conv_state if (use_cache and self._conv_state is not None) else (None, None, None)
-            q, cs_q = self.q_conv1d(x=q, cache=cs[0], output_final_state=use_cache)
-            k, cs_k = self.k_conv1d(x=k, cache=cs[1], output_final_state=use_cache)
-            v, cs_v = self.v_conv1d(x=v, cache=cs[2], output_final_state=use_cache)
+            q, cs_q = self.q_conv1d(x=q, cache=cs[0], output_final_state=use_cache, varlen_tables=tabs)
+            k, cs_k = self.k_conv1d(x=k, cache=cs[1], output_final_state=use_cache, varlen_tables=tabs)
+            v, cs_v = self.v_conv1d(x=v, cache=cs[2], output_final_state=use_cache, varlen_tables=tabs)
             conv_state = (cs_q, cs_k, cs_v)
         else:
             q, k, v = (torch.nn.functional.silu(t) for t in (q, k, v))
@@ -179,19 +219,20 @@ class B200KimiLinearSelfAttention(torch.nn.Module):
         g = ops.kda_gate(g, self.A_log, self.head_k_dim, self.dt_bias, 1.0, 20.0)
         beta = torch.nn.functional.linear(x, self.b_proj.weight).sigmoid().float()
         rec = self._recurrent_state if use_cache else None
-        if rec is not None and T <= RECURRENT_MAX_T and rec.dtype == torch.float32 and rec.is_contiguous():
+        if tabs is None and rec is not None and T <= RECURRENT_MAX_T and rec.dtype == torch.float32 and rec.is_contiguous():
             # decode step: the cached state is updated where it lies (no allocation: the step can be graph-captured)
             o, rec = ops.kda_recurrent_fwd(q.contiguous(), k.contiguous(), v.contiguous(), g, beta, None, rec, True,
                                            l2norm_qk=True, state_in_place=True)
         else:
             o, rec = chunk_kda(q=q, k=k, v=v, g=g, beta=beta, initial_state=rec, output_final_state=use_cache,
-                               use_qk_l2norm_in_kernel=True)
+                               use_qk_l2norm_in_kernel=True, varlen_tables=tabs)
         gp = _linear(_linear(x, self.g_proj[0].weight), self.g_proj[1].weight)        # its bias is added in the norm kernel
         o = self.o_norm(o, gp.view(B, T, H, self.head_v_dim), self.g_proj[1].bias)
         if use_cache:
             self._recurrent_state, self._conv_state = rec, conv_state
-            self._seen += T
-        return _linear(o.view(B, T, self.value_dim), self.o_proj.weight)
+            self._seen += T0
+        y = _linear(o.view(B, T, self.value_dim), self.o_proj.weight)
+        return y if indices is None else pad_input(y.squeeze(0), indices, B0, T0)
 
     # ------------------------------------------------------------------ CUDA-graph decode step
     @torch.inference_mode()

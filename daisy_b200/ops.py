@@ -504,6 +504,66 @@ def kda_chunk_fwd(q, k, v, g, beta, scale: Optional[float] = None, initial_state
     return o, hT
 
 
+def kda_varlen_tables(cu_seqlens, device, chunk: int = 64):
+    """Chunk and token tables of a packed batch, from its ``cu_seqlens`` (N + 1 offsets, host integers or a tensor --
+    a tensor costs one device-to-host read, as the reference's own chunk-index preparation does).  Returns
+    ``(chunk_tab [n_chunks, 2], seq_ptr [N + 1], tok_tab [T_total, 2], n_chunks)`` as int32 device tensors: first token
+    and length of every chunk, the first chunk of every sequence, and for every token its sequence's first token and
+    number."""
+    cu = [int(c) for c in (cu_seqlens.tolist() if torch.is_tensor(cu_seqlens) else cu_seqlens)]
+    if len(cu) < 2 or cu[0] != 0 or any(b < a for a, b in zip(cu, cu[1:])):
+        raise ValueError("cu_seqlens must start at 0 and not decrease")
+    chunks, ptr, tok = [], [0], []
+    for n, (a, b) in enumerate(zip(cu, cu[1:])):
+        chunks.extend((t, min(chunk, b - t)) for t in range(a, b, chunk))
+        ptr.append(len(chunks))
+        tok.extend((a, n) for _ in range(b - a))
+    mk = lambda rows, w: torch.tensor(rows, dtype=torch.int32).reshape(-1, w).to(device)
+    return mk(chunks, 2), torch.tensor(ptr, dtype=torch.int32, device=device), mk(tok, 2), len(chunks)
+
+
+def kda_chunk_fwd_varlen(q, k, v, g, beta, cu_seqlens, scale: Optional[float] = None, initial_state=None,
+                         output_final_state: bool = False, l2norm_qk: bool = True, out_fp32: bool = False, tables=None):
+    """KDA chunked forward over packed sequences: ``q,k [1,T,H,K]``, ``v [1,T,H,V]`` bf16, ``g`` fp32, ``beta [1,T,H]``,
+    ``cu_seqlens`` the N + 1 sequence offsets; state ``[N,H,K,V]`` fp32.  ``tables``: the result of
+    :func:`kda_varlen_tables` when the caller already has it."""
+    for n, t in (("q", q), ("k", k), ("v", v)):
+        _req(t, n)
+        if not t.is_contiguous():
+            raise ValueError(f"{n} must be contiguous")
+    if q.shape[0] != 1:
+        raise ValueError("packed sequences come as one row: q must be [1, T_total, H, K]")
+    g, beta = _f32c(g, "g"), _f32c(beta, "beta")
+    _, T, H, K = q.shape
+    V = v.shape[-1]
+    chunk_tab, seq_ptr, _tok, n_chunks = tables if tables is not None else kda_varlen_tables(cu_seqlens, q.device)
+    N = seq_ptr.numel() - 1
+    if int(_tok.shape[0]) != T:
+        raise ValueError(f"cu_seqlens covers {int(_tok.shape[0])} tokens, the inputs hold {T}")
+    L = _lib.lib()
+    o = torch.empty(1, T, H, V, dtype=torch.float32 if out_fp32 else torch.bfloat16, device=q.device)
+    if initial_state is not None:
+        initial_state = _f32c(initial_state, "initial_state")
+        if tuple(initial_state.shape) != (N, H, K, V):
+            raise ValueError(f"initial_state must be [{N}, {H}, {K}, {V}]")
+    hT = torch.empty(N, H, K, V, dtype=torch.float32, device=q.device) if output_final_state else None
+    if T == 0 or n_chunks == 0:
+        if hT is not None:
+            hT.copy_(initial_state) if initial_state is not None else hT.zero_()
+        return o, hT
+    need = L.daisy_b200_kda_varlen_workspace_bytes(n_chunks, H, K, V)
+    ws = torch.empty(max(need, 16), dtype=torch.uint8, device=q.device)
+    flags = (KDA_L2NORM_QK if l2norm_qk else 0) | (KDA_OUT_FP32 if out_fp32 else 0)
+    rc = L.daisy_b200_kda_chunk_fwd_varlen(
+        q.data_ptr(), k.data_ptr(), v.data_ptr(), g.data_ptr(), beta.data_ptr(),
+        initial_state.data_ptr() if initial_state is not None else None, o.data_ptr(),
+        hT.data_ptr() if hT is not None else None, T, H, K, V, 64,
+        float(scale) if scale is not None else 0.0, flags, chunk_tab.data_ptr(), n_chunks, seq_ptr.data_ptr(), N,
+        ws.data_ptr(), ws.numel(), status_word(q.device).data_ptr(), _stream(q))
+    _lib.check(rc, "daisy_b200_kda_chunk_fwd_varlen")
+    return o, hT
+
+
 def kda_recurrent_fwd(q, k, v, g, beta, scale: Optional[float] = None, initial_state=None,
                       output_final_state: bool = False, l2norm_qk: bool = True, out_fp32: bool = False,
                       state_in_place: bool = False):
@@ -603,6 +663,43 @@ def kda_short_conv(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.T
                                               y.data_ptr(), y.stride(0), y.stride(1), B, T, C, W,
                                               _lib.KDA_CONV_SILU if silu else 0, _stream(x))
     _lib.check(rc, "daisy_b200_kda_short_conv")
+    return y, s_out
+
+
+def kda_short_conv_varlen(x: torch.Tensor, weight: torch.Tensor, tok_tab: torch.Tensor, n_seq: int,
+                          bias: Optional[torch.Tensor] = None, state: Optional[torch.Tensor] = None,
+                          output_final_state: bool = False, silu: bool = True):
+    """:func:`kda_short_conv` over packed sequences ``x [1, T_total, C]``: the window stops at each sequence's first
+    token.  ``tok_tab`` is the third table of :func:`kda_varlen_tables`; ``state`` and the returned final state are
+    ``[n_seq, C, W]``."""
+    _req(x, "x")
+    if x.dim() != 3 or x.shape[0] != 1:
+        raise ValueError("x must be [1, T_total, C]")
+    if x.stride(2) != 1:
+        x = x.contiguous()
+    _, T, C = x.shape
+    w = weight.reshape(C, -1)
+    w = (w if w.dtype == torch.bfloat16 else w.to(torch.bfloat16)).contiguous()
+    W = w.shape[1]
+    if tok_tab.dtype != torch.int32 or tuple(tok_tab.shape) != (T, 2) or not tok_tab.is_contiguous():
+        raise ValueError(f"tok_tab must be a contiguous int32 [{T}, 2] tensor")
+    if bias is not None:
+        bias = bias.to(device=x.device, dtype=torch.bfloat16).contiguous()
+    if state is not None and (tuple(state.shape) != (n_seq, C, W) or state.dtype != torch.bfloat16 or not state.is_contiguous()):
+        raise ValueError(f"state must be a contiguous bf16 [{n_seq}, {C}, {W}] tensor")
+    s_out = None
+    if output_final_state:       # sequences without tokens keep their state
+        s_out = state.clone() if state is not None else torch.zeros(n_seq, C, W, dtype=torch.bfloat16, device=x.device)
+    y = torch.empty(1, T, C, dtype=torch.bfloat16, device=x.device)
+    if T == 0:
+        return y, s_out
+    rc = _lib.lib().daisy_b200_kda_short_conv_varlen(x.data_ptr(), x.stride(1), w.data_ptr(),
+                                                     bias.data_ptr() if bias is not None else None,
+                                                     state.data_ptr() if state is not None else None,
+                                                     s_out.data_ptr() if s_out is not None else None,
+                                                     y.data_ptr(), y.stride(1), T, C, W, tok_tab.data_ptr(),
+                                                     _lib.KDA_CONV_SILU if silu else 0, _stream(x))
+    _lib.check(rc, "daisy_b200_kda_short_conv_varlen")
     return y, s_out
 
 

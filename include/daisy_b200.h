@@ -355,6 +355,22 @@ int daisy_b200_kda_chunk_fwd(const void* q, const void* k, const void* v, const 
                              unsigned flags, void* workspace, size_t workspace_bytes,
                              int* status_word, void* stream);
 
+/* Packed variable-length form of the same call: chunk_kda(..., cu_seqlens=cu_seqlens) at
+ * models/daisy/attention_kimi.py:133-134, with cu_seqlens from get_unpad_data (:150-154; helpers :19-33).  The
+ * sequences lie end to end in one row: q, k [1, T_total, H, K], v, o [1, T_total, H, V], g fp32, beta [1, T_total, H];
+ * h0 / hT [n_seq, H, K, V] float32 or null.  No chunk spans two sequences; the caller lists the chunks:
+ *   chunk_tab [n_chunks][2] int32 (device): first token and number of tokens (1..64) of each chunk, sequence after
+ *     sequence, each sequence cut into 64-token chunks from its own first token;
+ *   seq_ptr [n_seq + 1] int32 (device): sequence i owns chunks seq_ptr[i] .. seq_ptr[i+1]-1 (none for an empty
+ *     sequence, whose final state is its initial state).
+ * workspace: daisy_b200_kda_varlen_workspace_bytes(n_chunks, H, K, V).  Other arguments and errors as above. */
+size_t daisy_b200_kda_varlen_workspace_bytes(int n_chunks, int H, int K, int V);
+int daisy_b200_kda_chunk_fwd_varlen(const void* q, const void* k, const void* v, const float* g,
+                                    const float* beta, const float* h0, void* o, float* hT,
+                                    int T_total, int H, int K, int V, int chunk, float scale, unsigned flags,
+                                    const int32_t* chunk_tab, int n_chunks, const int32_t* seq_ptr, int n_seq,
+                                    void* workspace, size_t workspace_bytes, int* status_word, void* stream);
+
 /* The same recurrence token by token, for short inputs (decode steps; the reference calls chunk_kda with
  * T = 1 and the cached state, models/daisy/attention_kimi.py:144-149,175-180).  The state of one (batch, head)
  * stays in registers across the T tokens: read from h0 once (null = zero state), written to hT once (null =
@@ -385,6 +401,16 @@ int daisy_b200_kda_gate(const void* g, int g_is_bf16, const float* a_log, const 
 int daisy_b200_kda_short_conv(const void* x, int64_t x_sb, int64_t x_st, const void* w, const void* bias,
                               const void* state_in, void* state_out, void* y, int64_t y_sb, int64_t y_st,
                               int B, int T, int C, int W, unsigned flags, void* stream);
+
+/* The same convolution over packed sequences (the reference passes cu_seqlens to each ShortConvolution call,
+ * models/daisy/attention_kimi.py:160-162): x, y [T_total, C] with row strides; the window never crosses the first
+ * token of a sequence.  tok_tab [T_total][2] int32 (device): for each token the index of its sequence's first token
+ * and the sequence's number.  state_in / state_out [n_seq, C, W] or null; state_out is written for every sequence
+ * that has at least one token (fill it with state_in beforehand if empty sequences may occur) and must not alias
+ * state_in. */
+int daisy_b200_kda_short_conv_varlen(const void* x, int64_t x_st, const void* w, const void* bias,
+                                     const void* state_in, void* state_out, void* y, int64_t y_st,
+                                     int T, int C, int W, const int32_t* tok_tab, unsigned flags, void* stream);
 
 /* Gated RMS norm of the KDA output over the head dimension.  Replaces self.o_norm(o, gp) at
  * models/daisy/attention_kimi.py:137 (CompilableFusedRMSNormGated, :41-62; third-party fla rms_norm_gated):

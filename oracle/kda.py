@@ -56,6 +56,28 @@ def kda_recurrent(q, k, v, g, beta, scale: Optional[float] = None,
     return o, S
 
 
+def kda_recurrent_varlen(q, k, v, g, beta, cu_seqlens, scale: Optional[float] = None,
+                         initial_state: Optional[torch.Tensor] = None, l2norm_qk: bool = True,
+                         dtype=torch.float32) -> Tuple[torch.Tensor, torch.Tensor]:
+    """The packed form the reference reaches with an attention mask (``cu_seqlens`` from ``get_unpad_data``,
+    models/daisy/attention_kimi.py:150-154, passed to ``chunk_kda`` at :133-134): the sequences lie end to end in one
+    row ``[1, T_total, ...]`` and each runs the recurrence on its own, from its own initial state.  Returns
+    ``(o [1,T_total,H,V], final_state [N,H,K,V])``."""
+    cu = [int(c) for c in cu_seqlens]
+    N, H, K, V = len(cu) - 1, q.shape[2], q.shape[3], v.shape[3]
+    o = torch.zeros(1, q.shape[1], H, V, dtype=dtype)
+    S = torch.zeros(N, H, K, V, dtype=dtype)
+    for n, (a, b) in enumerate(zip(cu, cu[1:])):
+        h0 = initial_state[n:n + 1] if initial_state is not None else None
+        if b == a:
+            if h0 is not None:
+                S[n] = h0[0].to(dtype)
+            continue
+        o[:, a:b], S[n:n + 1] = kda_recurrent(q[:, a:b], k[:, a:b], v[:, a:b], g[:, a:b], beta[:, a:b], scale, h0,
+                                              l2norm_qk, dtype)
+    return o, S
+
+
 def kda_gate(g: torch.Tensor, A_log: torch.Tensor, head_k_dim: int, g_bias: Optional[torch.Tensor] = None,
              beta: float = 1.0, threshold: float = 20.0) -> torch.Tensor:
     """Log-decay gate of the KDA layer, ``[..., H*D] -> [..., H, D]`` in ``g.dtype``:
@@ -105,6 +127,25 @@ def short_conv(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tenso
     if activation in ("silu", "swish"):
         y = y * torch.sigmoid(y)
     return y, full[:, T:T + W].transpose(1, 2).contiguous()
+
+
+def short_conv_varlen(x: torch.Tensor, weight: torch.Tensor, cu_seqlens, bias: Optional[torch.Tensor] = None,
+                      state: Optional[torch.Tensor] = None, activation: Optional[str] = "silu"
+                      ) -> Tuple[torch.Tensor, torch.Tensor]:
+    """``short_conv`` over packed sequences ``x [1, T_total, C]`` (the ``cu_seqlens`` argument of the calls at
+    models/daisy/attention_kimi.py:160-162): every sequence is convolved on its own, preceded by its own state
+    ``state[n]`` (zeros when None).  Returns ``(y [1,T_total,C], final_state [N,C,W])``; an empty sequence keeps its
+    state."""
+    cu = [int(c) for c in cu_seqlens]
+    N, C = len(cu) - 1, x.shape[2]
+    W = weight.reshape(C, -1).shape[1]
+    y = torch.zeros(1, x.shape[1], C)
+    fin = state.float().clone() if state is not None else torch.zeros(N, C, W)
+    for n, (a, b) in enumerate(zip(cu, cu[1:])):
+        if b > a:
+            y[:, a:b], fin[n:n + 1] = short_conv(x[:, a:b], weight, bias, state[n:n + 1] if state is not None else None,
+                                                 activation)
+    return y, fin
 
 
 def gated_rms_norm(o: torch.Tensor, gate: torch.Tensor, weight: Optional[torch.Tensor] = None,
@@ -158,6 +199,26 @@ def kimi_layer_forward(x: torch.Tensor, params: dict, num_heads: int, head_dim: 
     o = gated_rms_norm(r(o), gp, P["o_norm.weight"], mode="swish_sigmoid")
     y = lin(r(o).reshape(B, T, num_heads * head_dim), P["o_proj.weight"])
     return y, {"rec": rec, "conv": tuple(conv_out)}
+
+
+def kimi_layer_forward_masked(x: torch.Tensor, params: dict, num_heads: int, head_dim: int, attn_mask: torch.Tensor,
+                              round_stages: bool = True):
+    """The layer with an attention mask (models/daisy/attention_kimi.py:150-154,193): the tokens a row's mask keeps
+    (its last T columns) form that row's sequence, the layer runs on each sequence alone, and the outputs return to
+    their positions with zeros at the padding.  Returns ``(y [B,T,dim], [state of row 0, state of row 1, ...])``."""
+    B, T, _ = x.shape
+    keep = attn_mask[:, -T:].bool()
+    y = torch.zeros(B, T, params["o_proj.weight"].shape[0])
+    states = []
+    for b in range(B):
+        idx = keep[b].nonzero().flatten()
+        if idx.numel() == 0:
+            states.append(None)
+            continue
+        yb, st = kimi_layer_forward(x[b:b + 1, idx], params, num_heads, head_dim, None, round_stages)
+        y[b, idx] = yb[0]
+        states.append(st)
+    return y, states
 
 
 def kda_bytes_per_token_head(K: int = 128, V: int = 128) -> int:

@@ -81,6 +81,17 @@ def test_argument_validation_without_gpu(lib):
     assert lib.daisy_b200_kda_chunk_fwd(a, a, a, a, a, None, a, None, 1, 100, 2, 64, 128, 64, 0.0, 1, a, kw, None, None) == _lib.EUNSUPPORTED
     assert lib.daisy_b200_kda_chunk_fwd(a, a, a, a, a, None, a, None, 1, 100, 2, 128, 128, 32, 0.0, 1, a, kw, None, None) == _lib.EUNSUPPORTED
     assert lib.daisy_b200_kda_chunk_fwd(a, a, a, a, a, None, a, None, 1, 100, 2, 128, 128, 64, 0.0, 1, a, kw - 1, None, None) == _lib.EWORKSPACE
+    # packed KDA: the same records per chunk; tables are required; then the dense checks apply
+    assert lib.daisy_b200_kda_varlen_workspace_bytes(2, 2, 128, 128) == kw
+    assert lib.daisy_b200_kda_varlen_workspace_bytes(0, 2, 128, 128) == 0
+    assert lib.daisy_b200_kda_chunk_fwd_varlen(a, a, a, a, a, None, a, None, 100, 2, 128, 128, 64, 0.0, 1, None, 2, a, 1,
+                                               a, kw, None, None) == _lib.EINVAL
+    assert lib.daisy_b200_kda_chunk_fwd_varlen(a, a, a, a, a, None, a, None, 100, 2, 128, 128, 64, 0.0, 1, a + 4, 2, a, 1,
+                                               a, kw, None, None) == _lib.EALIGN
+    assert lib.daisy_b200_kda_chunk_fwd_varlen(a, a, a, a, a, None, a, None, 100, 2, 128, 128, 64, 0.0, 1, a, 2, a, 1,
+                                               a, kw - 1, None, None) == _lib.EWORKSPACE
+    assert lib.daisy_b200_kda_short_conv_varlen(a, 256, a, None, None, None, a, 256, 8, 256, 4, None, 1, None) == _lib.EINVAL
+    assert lib.daisy_b200_kda_short_conv_varlen(a, 256, a, None, a, a, a, 256, 8, 256, 4, a, 1, None) == _lib.EINVAL
     # ring copy: n > cap, bad element size
     assert lib.daisy_b200_ring_copy_rows(a, 1024, 512, 128, a, 1024, 512, 128, 1, 2, 128, 4, 0, 5, 2, 1, None) == _lib.EINVAL
     assert lib.daisy_b200_ring_copy_rows(a, 1024, 512, 128, a, 1024, 512, 128, 1, 2, 128, 4, 0, 2, 3, 1, None) == _lib.EINVAL

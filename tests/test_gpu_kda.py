@@ -197,3 +197,72 @@ def test_chunk_kda_against_fla_triton():
     ours = ((o.float().cpu() - o_or).norm() / o_or.norm()).item()
     theirs = ((o_ref.float().cpu() - o_or).norm() / o_or.norm()).item()
     assert ours <= max(3e-3, 1.5 * theirs), (ours, theirs)
+
+
+# ------------------------------------------------------------------------------------ packed variable-length batches
+VARLEN_CASES = [[0, 64], [0, 1], [0, 5, 69], [0, 100, 100, 164, 421], [0, 64, 128, 192], [0, 63, 65, 130, 700],
+                [0, 0, 7], [0, 1000, 1001]]
+
+
+@pytest.mark.parametrize("cu", VARLEN_CASES)
+@pytest.mark.parametrize("with_state", [False, True])
+def test_kda_varlen_matches_per_sequence_recurrence(cu, with_state):
+    """chunk_kda(..., cu_seqlens=...): sequences of ragged lengths (one token, empty, chunk multiples, a partial last
+    chunk next to the following sequence's first tokens) packed into one row; each must equal the recurrence run on
+    it alone, from its own initial state."""
+    N, T, H = len(cu) - 1, cu[-1], 3
+    q, k, v, g, beta = _inputs(1, T, H, seed=11 + T + N)
+    h0 = torch.randn(N, H, 128, 128, generator=torch.Generator().manual_seed(5)) * 0.1 if with_state else None
+    o_ref, s_ref = okda.kda_recurrent_varlen(q.float(), k.float(), v.float(), g, beta, cu, None, h0)
+    o, s = _run(q, k, v, g, beta, cu_seqlens=torch.tensor(cu, dtype=torch.int32, device="cuda"),
+                initial_state=None if h0 is None else h0.cuda(), output_final_state=True, out_fp32=True)
+    assert o.shape == o_ref.shape and s.shape == s_ref.shape
+    assert _rel(o, o_ref) <= REL_TOL, f"o rel {_rel(o, o_ref)}"
+    assert _rel(s, s_ref) <= REL_TOL, f"state rel {_rel(s, s_ref)}"
+    for n, (a, b) in enumerate(zip(cu, cu[1:])):                    # per sequence, so that a short one cannot hide
+        if b > a:
+            assert _rel(o[:, a:b], o_ref[:, a:b]) <= 2 * REL_TOL, f"sequence {n}"
+        assert _rel(s[n], s_ref[n]) <= 2 * REL_TOL or s_ref[n].norm() == 0, f"state of sequence {n}"
+    if not with_state and 0 in [b - a for a, b in zip(cu, cu[1:])]:
+        n = [b - a for a, b in zip(cu, cu[1:])].index(0)
+        assert not s[n].any()
+
+
+def test_kda_varlen_equals_dense_per_sequence():
+    """A packed batch gives, sequence by sequence, the bits of the dense call on that sequence alone (the chunking
+    starts at each sequence's own first token)."""
+    cu = [0, 130, 194, 500]
+    q, k, v, g, beta = _inputs(1, cu[-1], 2, seed=41)
+    o, s = _run(q, k, v, g, beta, cu_seqlens=cu, output_final_state=True)
+    for n, (a, b) in enumerate(zip(cu, cu[1:])):
+        od, sd = _run(q[:, a:b].contiguous(), k[:, a:b].contiguous(), v[:, a:b].contiguous(), g[:, a:b].contiguous(),
+                      beta[:, a:b].contiguous(), output_final_state=True)
+        assert torch.equal(o[:, a:b], od) and torch.equal(s[n], sd[0]), f"sequence {n}"
+
+
+def test_kda_varlen_against_fla_triton():
+    """fla.ops.kda.chunk_kda with cu_seqlens on this GPU, the call the reference makes for a masked batch."""
+    try:
+        from fla.ops.kda import chunk_kda as fla_chunk_kda
+    except Exception as e:
+        pytest.skip(f"fla not importable: {e}")
+    from daisy_b200.kda import chunk_kda
+    cu, H, K = [0, 70, 333, 400], 4, 128
+    T, N = cu[-1], len(cu) - 1
+    g_ = torch.Generator(device="cuda").manual_seed(78)
+    q, k, v = (torch.randn(1, T, H, K, device="cuda", generator=g_).bfloat16() for _ in range(3))
+    g = torch.nn.functional.logsigmoid(torch.randn(1, T, H, K, device="cuda", generator=g_))
+    beta = torch.sigmoid(torch.randn(1, T, H, device="cuda", generator=g_))
+    h0 = torch.randn(N, H, K, K, device="cuda", generator=g_) * 0.1
+    cu_t = torch.tensor(cu, dtype=torch.int32, device="cuda")
+    try:
+        with torch.no_grad():
+            o_ref, s_ref = fla_chunk_kda(q=q, k=k, v=v, g=g, beta=beta, initial_state=h0.clone(), output_final_state=True,
+                                         use_qk_l2norm_in_kernel=True, cu_seqlens=cu_t.long())
+        torch.cuda.synchronize()
+    except Exception as e:
+        pytest.skip(f"fla's Triton kernels did not run here: {type(e).__name__}: {e}")
+    o, s = chunk_kda(q=q, k=k, v=v, g=g, beta=beta, initial_state=h0, output_final_state=True,
+                     use_qk_l2norm_in_kernel=True, cu_seqlens=cu_t)
+    assert ((o.float() - o_ref.float()).norm() / o_ref.float().norm()).item() <= 5e-3
+    assert ((s.float() - s_ref.float()).norm() / s_ref.float().norm()).item() <= 5e-3

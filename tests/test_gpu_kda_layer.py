@@ -246,3 +246,84 @@ def test_layer_step_graph_matches_eager():
         assert torch.equal(a, b)
     assert torch.equal(m._recurrent_state, rec_e) and all(torch.equal(a, b) for a, b in zip(m._conv_state, conv_e))
     assert m._seen == T0 + n
+
+
+# ------------------------------------------------------------------------------------ packed variable-length batches
+@pytest.mark.parametrize("W", [4, 2])
+@pytest.mark.parametrize("cu", [[0, 40], [0, 1, 2, 3, 4, 40], [0, 2, 2, 35, 67, 200], [0, 31, 32, 33, 96, 97]])
+def test_short_conv_varlen_matches_oracle(cu, W):
+    """The convolution over packed sequences: the window stops at each sequence's first token (sequences of 1 and 2
+    tokens, an empty one, boundaries on and next to the 32-row blocks of the kernel), with and without carried states;
+    each sequence gives the bits of the dense call on it alone."""
+    from daisy_b200 import ops
+    N, T, C = len(cu) - 1, cu[-1], 512
+    x, w, b = _conv_inputs(1, T, C, W, 21 + T + W, bias=True)
+    tabs = ops.kda_varlen_tables(cu, "cuda")
+    st = torch.randn(N, C, W, device="cuda").bfloat16()
+    for state in (None, st):
+        y, s = ops.kda_short_conv_varlen(x, w, tabs[2], N, b, state=state, output_final_state=True)
+        ref, s_ref = okda.short_conv_varlen(x.float().cpu(), w.float().cpu(), cu, b.float().cpu(),
+                                            None if state is None else state.float().cpu())
+        assert_close_bf16(y, ref, f"cu={cu} W={W}")
+        assert torch.equal(s.float().cpu(), s_ref)
+        for n, (a, e) in enumerate(zip(cu, cu[1:])):
+            if e > a:
+                yd, sd = ops.kda_short_conv(x[:, a:e], w, b, state=None if state is None else state[n:n + 1],
+                                            output_final_state=True)
+                assert torch.equal(y[:, a:e], yd) and torch.equal(s[n:n + 1], sd), f"sequence {n}"
+    assert s is not st
+
+
+def test_layer_attn_mask_matches_oracle_and_continues():
+    """forward / prefill with an attention mask (left padding, right padding, a hole, a full row): kept tokens match
+    the layer run on each row's kept tokens alone, padding positions return zeros, and the cached states are one per
+    row, so that the following single-token steps match the oracle's chained run."""
+    m = _layer(seed=13)
+    B, T, D = 4, 150, 256
+    x = torch.randn(B, T, D, device="cuda").bfloat16()
+    mask = torch.ones(B, T + 10, dtype=torch.long, device="cuda")         # longer than T: the last T columns count
+    mask[0, 10:10 + 37] = 0                                                # left padding
+    mask[1, -20:] = 0                                                      # right padding
+    mask[2, 60:75] = 0                                                     # a hole
+    with torch.inference_mode():
+        y = m(x, None, None, attn_mask=mask)
+        m.reset_history()
+        yp, _, _ = m.prefill(x, None, None, attn_mask=mask)
+    assert y.shape == x.shape and torch.equal(y, yp)
+    params = {n: p.detach().cpu() for n, p in m.named_parameters()}
+    y_ref, states = okda.kimi_layer_forward_masked(x.cpu(), params, 2, 128, mask.cpu())
+    keep = mask[:, -T:].bool().cpu()
+    assert not y.float().cpu()[~keep].any()
+    for b in range(B):
+        rel = ((y[b].float().cpu()[keep[b]] - y_ref[b][keep[b]]).norm() / y_ref[b][keep[b]].norm()).item()
+        assert rel <= 2e-2, (b, rel)
+    assert m._recurrent_state.shape == (B, 2, 128, 128) and m._conv_state[0].shape[0] == B
+    x1 = torch.randn(B, 1, D, device="cuda").bfloat16()
+    with torch.inference_mode():
+        y1, _, _ = m.step(x1, None, None, T, None, None, None)
+    for b in range(B):
+        r1, _ = okda.kimi_layer_forward(x1[b:b + 1].cpu(), params, 2, 128, state=states[b])
+        rel = ((y1[b].float().cpu() - r1[0]).norm() / r1[0].norm()).item()
+        assert rel <= 2e-2, (b, rel)
+
+
+def test_short_conv_varlen_against_fla_triton():
+    ShortConvolution, _ = _fla_or_skip()
+    from daisy_b200 import B200ShortConvolution
+    cu, C, W = [0, 3, 50, 51, 200], 256, 4
+    torch.manual_seed(2)
+    ref = ShortConvolution(C, W, bias=False, activation="silu").cuda().bfloat16()
+    ours = B200ShortConvolution(C, W, bias=False, activation="silu", dtype=torch.bfloat16).cuda()
+    ours.load_state_dict(ref.state_dict())
+    x = torch.randn(1, cu[-1], C, device="cuda").bfloat16()
+    cu_t = torch.tensor(cu, dtype=torch.int32, device="cuda")
+    try:
+        with torch.no_grad():
+            y_ref, s_ref = ref(x=x, cache=None, output_final_state=True, cu_seqlens=cu_t.long())
+        torch.cuda.synchronize()
+    except Exception as e:
+        pytest.skip(f"fla's Triton kernels did not run here: {type(e).__name__}: {e}")
+    with torch.no_grad():
+        y, s = ours(x=x, cache=None, output_final_state=True, cu_seqlens=cu_t)
+    assert_close_bf16(y, y_ref.float().cpu(), "varlen conv vs fla")
+    assert s.shape == s_ref.shape and torch.equal(s.float().cpu(), s_ref.float().cpu())

@@ -131,6 +131,55 @@ def test_kda_layer_module_has_the_reference_parameters(golden_dir):
     assert got == want
 
 
+def test_varlen_tables_and_unpad_helpers():
+    """Host side of the packed (cu_seqlens) KDA path: chunk / sequence / token tables, and the unpad helpers the
+    reference imports (models/daisy/attention_kimi.py:19, used at :150-154,193)."""
+    from daisy_b200 import ops
+    from daisy_b200.kda import get_unpad_data, index_first_axis, pad_input
+    chunk_tab, seq_ptr, tok_tab, n = ops.kda_varlen_tables([0, 5, 5, 135, 199], "cpu")
+    assert n == 5 and chunk_tab.tolist() == [[0, 5], [5, 64], [69, 64], [133, 2], [135, 64]]
+    assert seq_ptr.tolist() == [0, 1, 1, 4, 5]
+    assert tok_tab.shape == (199, 2) and tok_tab[4].tolist() == [0, 0] and tok_tab[5].tolist() == [5, 2]
+    assert tok_tab[198].tolist() == [135, 3] and chunk_tab.dtype == seq_ptr.dtype == tok_tab.dtype == torch.int32
+    t2 = ops.kda_varlen_tables(torch.tensor([0, 64]), "cpu")
+    assert t2[0].tolist() == [[0, 64]] and t2[3] == 1
+    for bad in ([1, 5], [0, 5, 3], [0]):
+        with pytest.raises(ValueError):
+            ops.kda_varlen_tables(bad, "cpu")
+    mask = torch.tensor([[0, 0, 1, 1, 1], [1, 1, 0, 1, 0], [0, 0, 0, 0, 0]])
+    idx, cu, mx = get_unpad_data(mask)
+    assert idx.tolist() == [2, 3, 4, 5, 6, 8] and cu.tolist() == [0, 3, 6, 6] and mx == 3 and cu.dtype == torch.int32
+    x = torch.arange(15 * 2, dtype=torch.float32).view(15, 2)
+    packed = index_first_axis(x, idx)
+    back = pad_input(packed, idx, 3, 5)
+    assert back.shape == (3, 5, 2) and torch.equal(back.view(15, 2)[idx], packed)
+    assert not back.view(15, 2)[[0, 1, 7, 9, 10, 14]].any()
+
+
+def test_oracle_varlen_is_the_per_sequence_recurrence(golden_dir):
+    """The packed restatements against the pinned dense ones: the third-party fixture's two batch rows laid end to end
+    (plus an empty sequence) give each row's fixture output and state; the convolution likewise."""
+    import os
+    import numpy as np
+    from oracle import kda as okda
+    z = np.load(os.path.join(golden_dir, "kda_naive_small.npz"))
+    q, k, v, g, beta, h0 = (torch.from_numpy(z[n]) for n in ("q", "k", "v", "g", "beta", "h0"))
+    B, T = q.shape[:2]
+    pack = lambda t: t.reshape(1, B * T, *t.shape[2:])
+    cu = [0] + [T * (i + 1) for i in range(B)]
+    cu = cu[:1] + cu[:1] + cu[1:]                                   # an empty sequence in front
+    h0e = torch.cat([torch.ones_like(h0[:1]), h0])
+    o, s = okda.kda_recurrent_varlen(pack(q), pack(k), pack(v), pack(g), pack(beta), cu, None, h0e)
+    o_d, s_d = okda.kda_recurrent(q, k, v, g, beta, None, h0)
+    assert torch.allclose(o.view_as(o_d), o_d, atol=1e-6) and torch.allclose(s[1:], s_d, atol=1e-6)
+    assert torch.equal(s[0], h0e[0])
+    x = torch.randn(2, 9, 16)
+    w, st = torch.randn(16, 4), torch.randn(2, 16, 4)
+    y, f = okda.short_conv_varlen(x.reshape(1, 18, 16), w, [0, 9, 18], None, st)
+    y_d, f_d = okda.short_conv(x, w, None, st)
+    assert torch.allclose(y.view_as(y_d), y_d, atol=1e-6) and torch.allclose(f, f_d)
+
+
 def test_accounting_matches_the_oracle_formulas():
     """The package's FLOP / byte counts (what bench.py's roofline figures use) equal the oracle's."""
     from daisy_b200 import accounting as a
