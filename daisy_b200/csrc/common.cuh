@@ -48,6 +48,28 @@ __device__ __forceinline__ uint4 ld_stream16(const void* p) {
   return r;
 }
 
+// 16-byte load served by L2 (no L1 line is created or used): for data another grid may have written while this one
+// was already resident
+__device__ __forceinline__ uint4 ld_cg16(const void* p) {
+  uint4 r;
+  asm volatile("ld.global.cg.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "l"(p) : "memory");
+  return r;
+}
+
+// ------------------------------------------------------------------ programmatic dependent launch
+// A kernel launched with launch_dependent() may become resident while the kernel before it in the stream is still
+// running.  Everything it does before grid_dep_wait() must be independent of that kernel: here that part only issues
+// L2 prefetch hints for the weights / cache rows it is about to stream, so the HBM pipe stays busy across the kernel
+// boundary.  grid_dep_wait() returns when the preceding grid has completed and its writes are visible; in a launch
+// without the attribute both instructions do nothing.
+__device__ __forceinline__ void grid_dep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_dep_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+// Hint: bring [p, p + bytes) into L2.  p 16-byte aligned, bytes a multiple of 16.  Never faults the kernel's results:
+// a prefetched line that is written afterwards is updated in L2 like any other.
+__device__ __forceinline__ void l2_prefetch_bulk(const void* p, uint32_t bytes) {
+  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p), "r"(bytes) : "memory");
+}
+
 // ------------------------------------------------------------------ shared memory / mbarrier
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
 
@@ -260,6 +282,66 @@ __device__ __forceinline__ void tc_commit_p(uint32_t leader, uint64_t* bar) {
       ::"r"(smem_u32(bar)), "r"(leader) : "memory");
 }
 
+// ------------------------------------------------------------------ CTA pairs (cta_group::2)
+// Two CTAs of a cluster (ranks 0 and 1) run one 256-row MMA: each holds its own 128 rows of A and one half of B in its
+// shared memory (same offsets in both), the tensor cores of both SMs read both halves of B, and each accumulates its
+// 128 rows in its own TMEM.  Rank 0 issues the MMAs and the commits; a commit can arrive on the mbarrier at the same
+// offset in both CTAs.
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// shared::cluster address of `cta_addr` (a shared::cta address valid in this CTA) in the CTA of rank `rank`
+__device__ __forceinline__ uint32_t mapa_shared(uint32_t cta_addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(cta_addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// TMA load into this CTA's shared memory whose completion bytes are counted on an mbarrier of either CTA of the pair
+// (bar_cluster_addr from mapa_shared); every CTA fetches what it keeps.
+__device__ __forceinline__ void tma_load_3d_pair(void* smem_dst, const CUtensorMap* m, uint32_t bar_cluster_addr, int x, int y, int z) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(smem_u32(smem_dst)), "l"(m), "r"(bar_cluster_addr), "r"(x), "r"(y), "r"(z) : "memory");
+}
+// TMEM allocation for a pair: the same warp of BOTH CTAs executes it, with the same shared-memory offset for the result
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t* smem_dst, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_dst)), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_pair() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+// D[tmem of both CTAs] (+)= A * B over the pair (M = 256 in the instruction descriptor); issued by rank 0 only
+__device__ __forceinline__ void umma_ss_pair_p(uint32_t leader, uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo,
+                                               uint32_t b_hi, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\t.reg .b64 da, db;\n\t"
+      "mov.b64 da, {%1, %2};\n\tmov.b64 db, {%3, %4};\n\t"
+      "setp.ne.b32 p, %6, 0;\n\tsetp.ne.b32 q, %7, 0;\n\t"
+      "@q tcgen05.mma.cta_group::2.kind::f16 [%0], da, db, %5, p;\n\t}"
+      ::"r"(d_tmem), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate), "r"(leader) : "memory");
+}
+// arrive, when the pair's MMAs issued so far have completed, on the mbarrier at this offset in BOTH CTAs of the pair
+// (two commits: one per CTA's barrier, addressed through the cluster window)
+__device__ __forceinline__ void tc_commit_pair_p(uint32_t leader, uint64_t* bar) {
+  const uint32_t a0 = mapa_shared(smem_u32(bar), 0), a1 = mapa_shared(smem_u32(bar), 1);
+  asm volatile(
+      "{\n\t.reg .pred q;\n\tsetp.ne.b32 q, %2, 0;\n\t"
+      "@q tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t"
+      "@q tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%1];\n\t}"
+      ::"r"(a0), "r"(a1), "r"(leader) : "memory");
+}
+
 // TMEM <-> registers, 32 lanes x 32-bit, N consecutive columns per thread (thread i of warp w
 // touches TMEM lane 32*(w%4)+i).
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* r) {
@@ -416,5 +498,19 @@ int make_tmap_bf16_dthb(CUtensorMap* m, const void* base, uint64_t D, uint64_t T
 // (D, rows, 1, 1), NO swizzle: whole token rows land one after another in shared memory, for element-wise readers.
 int make_tmap_rows_bthd(CUtensorMap* m, const void* base, int elem_bytes, uint64_t D, uint64_t T, uint64_t H, uint64_t B,
                         uint32_t rows);
+
+// <<<grid, block, smem, stream>>> with the programmatic-serialisation attribute: the kernel may start while its
+// predecessor in the stream drains (see grid_dep_wait).  Captured into a CUDA graph it becomes a programmatic edge.
+template <typename... KArgs, typename... Args>
+static inline cudaError_t launch_dependent(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
+                                           Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = st;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  at[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = at; cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
 
 }  // namespace daisy_host

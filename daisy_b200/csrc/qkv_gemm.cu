@@ -14,6 +14,10 @@
 // attention kernel; BN = 256 halves the shared-memory bytes read per flop against BN = 128 (the SS form of a
 // 128 x 128 x 16 MMA reads 8 KB per 64 cycles, all the shared-memory pipe has).  Two accumulators in TMEM
 // (2 x BN columns) let the epilogue of tile i run under the main loop of tile i + 1.
+// PAIR form (N a multiple of 256): clusters of two CTAs on 256 x 256 tiles with cta_group::2 MMAs.  Each CTA loads its
+// own 128 rows of X and its own 128 of the tile's 256 weight rows (plain per-CTA TMA loads), the pair's tensor cores
+// read both weight halves, so the shared-memory fill and operand reads per flop drop by a third against the single-CTA
+// 128 x 256 tile; rank 0 issues the MMAs, both CTAs run the epilogue on their own 128 accumulator rows.
 // All mbarrier waits are bounded (abort flag, DAISY_ETIMEOUT through the status word), as everywhere else.
 #include "common.cuh"
 #include <cuda_fp16.h>
@@ -26,11 +30,13 @@ constexpr int G_A_BYTES = GM * GK * 2;                 // 16 KB
 constexpr int G_STAGE_ROW = 256 + 16;                  // one staged output row (128 bf16) + pad: conflict-free 16-byte accesses
 constexpr int G_STAGING = 4 * 16 * G_STAGE_ROW;        // per warp 16 rows at a time
 
-template <int BN> struct GemmCfg {
-  static constexpr int B_BYTES = BN * GK * 2;
+template <int BN, bool PAIR> struct GemmCfg {
+  static constexpr int B_ROWS = PAIR ? BN / 2 : BN;    // weight rows this CTA keeps per stage
+  static constexpr int B_BYTES = B_ROWS * GK * 2;
   static constexpr int STAGE = G_A_BYTES + B_BYTES;
-  static constexpr int NST = BN == 256 ? 4 : 6;
+  static constexpr int NST = (BN == 256 && !PAIR) ? 4 : 6;
   static constexpr int SMEM = 1024 + NST * STAGE + G_STAGING + 256;
+  static constexpr int TILE_M = PAIR ? 2 * GM : GM;
 };
 
 struct GemmParams {
@@ -62,10 +68,10 @@ struct GemmBars {
   int abort_flag;
 };
 
-template <int BN>
+template <int BN, bool PAIR>
 __global__ void __launch_bounds__(G_THREADS, 1)
 qkv_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_w, const GemmParams p) {
-  using Cfg = GemmCfg<BN>;
+  using Cfg = GemmCfg<BN, PAIR>;
   extern __shared__ uint8_t gemm_smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(gemm_smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* stages = smem;
@@ -74,18 +80,25 @@ qkv_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant_
   volatile int* abort_flag = &bars->abort_flag;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int m_tiles = (p.M + GM - 1) / GM, n_tiles = p.N / BN, kb_n = p.K / GK;
+  const int m_tiles = (p.M + Cfg::TILE_M - 1) / Cfg::TILE_M, n_tiles = p.N / BN, kb_n = p.K / GK;
   const int tiles = m_tiles * n_tiles;
+  // PAIR: the work item belongs to the cluster; rank 0 issues the MMAs, rank r owns rows r * 128 .. of the tile
+  const uint32_t rank = PAIR ? cluster_ctarank() : 0u;
+  const int worker = PAIR ? (int)(blockIdx.x >> 1) : (int)blockIdx.x, workers = PAIR ? (int)(gridDim.x >> 1) : (int)gridDim.x;
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < Cfg::NST; ++i) { mbar_init(&bars->full[i], 1); mbar_init(&bars->empty[i], 1); }
-    for (int i = 0; i < 2; ++i) { mbar_init(&bars->acc_full[i], 1); mbar_init(&bars->acc_empty[i], 128); }
+    for (int i = 0; i < 2; ++i) { mbar_init(&bars->acc_full[i], 1); mbar_init(&bars->acc_empty[i], PAIR ? 256 : 128); }
     bars->abort_flag = 0;
     mbar_init_fence();
   }
-  if (warp == 5) { tmem_alloc(&bars->tmem_base, 2 * BN); tmem_relinquish(); }
+  if (warp == 5) {
+    if (PAIR) { tmem_alloc_pair(&bars->tmem_base, 2 * BN); tmem_relinquish_pair(); }
+    else { tmem_alloc(&bars->tmem_base, 2 * BN); tmem_relinquish(); }
+  }
   tc_fence_before();
-  __syncthreads();
+  if (PAIR) cluster_sync_all();                        // the peer's barriers exist before anything arrives on them
+  else __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = bars->tmem_base;
 
@@ -95,28 +108,36 @@ qkv_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant_
       prefetch_tmap(&tm_x); prefetch_tmap(&tm_w);
       uint32_t n = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
-        const int m0 = (tile / n_tiles) * GM, n0 = (tile % n_tiles) * BN;
+      for (int tile = worker; tile < tiles && ok; tile += workers) {
+        const int m0 = (tile / n_tiles) * Cfg::TILE_M + (int)rank * GM, n0 = (tile % n_tiles) * BN + (int)rank * Cfg::B_ROWS;
         for (int kb = 0; kb < kb_n; ++kb, ++n) {
           const int st = n % Cfg::NST;
           if (!mbar_wait(&bars->empty[st], ((n / Cfg::NST) & 1) ^ 1, abort_flag, p.status, 1)) { ok = false; break; }
           uint8_t* dst = stages + st * Cfg::STAGE;
-          mbar_expect_tx(&bars->full[st], Cfg::STAGE);
-          tma_load_3d(dst, &tm_x, &bars->full[st], kb * GK, m0, 0);
-          tma_load_3d(dst + G_A_BYTES, &tm_w, &bars->full[st], kb * GK, n0, 0);
+          if (PAIR) {
+            // both CTAs' bytes are counted on rank 0's barrier, which the MMA issuer waits on
+            const uint32_t full0 = mapa_shared(smem_u32(&bars->full[st]), 0);
+            if (rank == 0) mbar_expect_tx(&bars->full[st], 2 * Cfg::STAGE);
+            tma_load_3d_pair(dst, &tm_x, full0, kb * GK, m0, 0);
+            tma_load_3d_pair(dst + G_A_BYTES, &tm_w, full0, kb * GK, n0, 0);
+          } else {
+            mbar_expect_tx(&bars->full[st], Cfg::STAGE);
+            tma_load_3d(dst, &tm_x, &bars->full[st], kb * GK, m0, 0);
+            tma_load_3d(dst + G_A_BYTES, &tm_w, &bars->full[st], kb * GK, n0, 0);
+          }
         }
       }
     }
-  } else if (warp == 5) {
+  } else if (warp == 5 && rank == 0) {
     // ------------------------------------------------------------------ MMA issuer
     const uint32_t leader = elect_one() ? 1u : 0u;
-    constexpr uint32_t idesc = umma_idesc_bf16(GM, BN, 0, 0);
+    constexpr uint32_t idesc = umma_idesc_bf16(Cfg::TILE_M, BN, 0, 0);
     const uint64_t ad = umma_desc_sw128(smem_u32(stages), 16, 1024);
     const uint64_t bd = umma_desc_sw128(smem_u32(stages + G_A_BYTES), 16, 1024);
     const uint32_t a_lo0 = (uint32_t)ad, b_lo0 = (uint32_t)bd, hi = (uint32_t)(ad >> 32);
     uint32_t n = 0, it = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x, ++it) {
+    for (int tile = worker; tile < tiles && ok; tile += workers, ++it) {
       const uint32_t buf = it & 1;
       if (!mbar_wait(&bars->acc_empty[buf], ((it >> 1) & 1) ^ 1, abort_flag, p.status, 2)) { ok = false; break; }
       tc_fence_after();
@@ -127,22 +148,28 @@ qkv_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant_
         tc_fence_after();
         const uint32_t a_lo = a_lo0 + st * (Cfg::STAGE >> 4), b_lo = b_lo0 + st * (Cfg::STAGE >> 4);
 #pragma unroll
-        for (int k = 0; k < GK / 16; ++k)
-          umma_ss_lh_p(leader, d_tmem, a_lo + k * 2, hi, b_lo + k * 2, hi, idesc, (kb > 0 || k > 0) ? 1u : 0u);
-        tc_commit_p(leader, &bars->empty[st]);
+        for (int k = 0; k < GK / 16; ++k) {
+          if (PAIR) umma_ss_pair_p(leader, d_tmem, a_lo + k * 2, hi, b_lo + k * 2, hi, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          else umma_ss_lh_p(leader, d_tmem, a_lo + k * 2, hi, b_lo + k * 2, hi, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+        }
+        if (PAIR) tc_commit_pair_p(leader, &bars->empty[st]);       // both CTAs' producers may refill the stage
+        else tc_commit_p(leader, &bars->empty[st]);
       }
-      if (ok) tc_commit_p(leader, &bars->acc_full[buf]);
+      if (ok) {
+        if (PAIR) tc_commit_pair_p(leader, &bars->acc_full[buf]);
+        else tc_commit_p(leader, &bars->acc_full[buf]);
+      }
     }
-  } else {
+  } else if (warp < 4) {
     // ------------------------------------------------------------------ epilogue: thread = output row
     const int row = warp * 32 + lane;
     const uint32_t lane_off = (uint32_t)(warp * 32) << 16;
     uint8_t* stg = staging + warp * 16 * G_STAGE_ROW;
     uint32_t it = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x, ++it) {
+    for (int tile = worker; tile < tiles && ok; tile += workers, ++it) {
       const uint32_t buf = it & 1;
-      const int m0 = (tile / n_tiles) * GM, n0 = (tile % n_tiles) * BN;
+      const int m0 = (tile / n_tiles) * Cfg::TILE_M + (int)rank * GM, n0 = (tile % n_tiles) * BN;
       const int m = m0 + row;
       ok = __all_sync(0xffffffffu, mbar_wait(&bars->acc_full[buf], (it >> 1) & 1, abort_flag, p.status, 4));
       if (!ok) break;
@@ -155,7 +182,8 @@ qkv_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant_
         tc_wait_ld();
         if (half == BN / 128 - 1) {                                // accumulator read out: the MMA warp may refill it
           tc_fence_before();
-          mbar_arrive(&bars->acc_empty[buf]);
+          if (PAIR) mbar_arrive_cluster(mapa_shared(smem_u32(&bars->acc_empty[buf]), 0));   // the issuer waits for both CTAs
+          else mbar_arrive(&bars->acc_empty[buf]);
         }
         __nv_bfloat16* dst_row;                                    // this thread's output row (128 bf16)
         uint8_t* ring_row = nullptr;
@@ -255,33 +283,62 @@ qkv_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant_
   }
 
   tc_fence_before();
-  __syncthreads();
-  if (warp == 5) { tc_fence_after(); tmem_dealloc(tmem_base, 2 * BN); }
+  if (PAIR) cluster_sync_all();                        // neither CTA leaves while the other may still read its operands
+  else __syncthreads();
+  if (warp == 5) {
+    tc_fence_after();
+    if (PAIR) tmem_dealloc_pair(tmem_base, 2 * BN);
+    else tmem_dealloc(tmem_base, 2 * BN);
+  }
 }
 
 }  // namespace daisy
 
 using namespace daisy;
 
-template <int BN>
+template <int BN, bool PAIR>
 static int launch_gemm(const CUtensorMap& tx, const CUtensorMap& tw, const GemmParams& p, cudaStream_t st) {
-  using Cfg = GemmCfg<BN>;
+  using Cfg = GemmCfg<BN, PAIR>;
   static_assert(Cfg::SMEM <= 232448, "over the 227 KB a CTA may use");
   static bool attr[daisy_host::MAX_DEVICES] = {};
+  static int max_clusters[daisy_host::MAX_DEVICES] = {};
   const int dev = daisy_host::device_slot();
   if (dev < 0) return DAISY_ENODEV;
+  const int sms = daisy_host::sm_count_cached();
+  if (sms <= 0) return DAISY_ENODEV;
+  cudaLaunchConfig_t cfg = {};
+  cfg.blockDim = dim3(G_THREADS); cfg.dynamicSmemBytes = Cfg::SMEM; cfg.stream = st;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeClusterDimension;
+  at[0].val.clusterDim.x = 2; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
+  if (PAIR) { cfg.attrs = at; cfg.numAttrs = 1; }
   if (!attr[dev]) {
-    if (cudaFuncSetAttribute(qkv_gemm_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM) != cudaSuccess) {
+    if (cudaFuncSetAttribute(qkv_gemm_kernel<BN, PAIR>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM) != cudaSuccess) {
       (void)cudaGetLastError();
       return DAISY_ECUDA;
     }
+    if (PAIR) {                                          // how many CTA pairs the device can hold at once
+      cfg.gridDim = dim3((unsigned)(sms & ~1));
+      int n = 0;
+      if (cudaOccupancyMaxActiveClusters(&n, qkv_gemm_kernel<BN, PAIR>, &cfg) != cudaSuccess || n <= 0) {
+        (void)cudaGetLastError();
+        return DAISY_ECUDA;
+      }
+      max_clusters[dev] = n;
+    }
     attr[dev] = true;
   }
-  const int sms = daisy_host::sm_count_cached();
-  if (sms <= 0) return DAISY_ENODEV;
-  const int64_t tiles = (int64_t)((p.M + GM - 1) / GM) * (p.N / BN);
-  const unsigned grid = (unsigned)(tiles < sms ? tiles : sms);
-  qkv_gemm_kernel<BN><<<grid, G_THREADS, Cfg::SMEM, st>>>(tx, tw, p);
+  const int64_t tiles = (int64_t)((p.M + Cfg::TILE_M - 1) / Cfg::TILE_M) * (p.N / BN);
+  if (PAIR) {
+    const int64_t pairs = tiles < max_clusters[dev] ? tiles : max_clusters[dev];
+    cfg.gridDim = dim3((unsigned)(2 * pairs));
+  } else {
+    cfg.gridDim = dim3((unsigned)(tiles < sms ? tiles : sms));
+  }
+  if (cudaLaunchKernelEx(&cfg, qkv_gemm_kernel<BN, PAIR>, tx, tw, p) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return DAISY_ECUDA;
+  }
   DAISY_CHECK_LAUNCH();
   return DAISY_OK;
 }
@@ -290,12 +347,12 @@ static int gemm_common(const void* x, int64_t ldx, const void* w, int64_t ldw, G
   if (!x || !w || p.M <= 0 || p.N <= 0 || p.K <= 0) return DAISY_EINVAL;
   if (p.K % GK != 0 || p.N % 128 != 0) return DAISY_EUNSUPPORTED;
   if (!daisy_aligned16(x) || !daisy_aligned16(w) || (ldx & 7) || (ldw & 7) || ldx < p.K || ldw < p.K) return DAISY_EALIGN;
-  const int BN = (p.N % 256 == 0) ? 256 : 128;
+  const bool pair = p.N % 256 == 0 && p.M > GM;        // CTA pairs on 256 x 256 tiles; else one CTA per 128 x 128 tile
   CUtensorMap tx, tw;
   int rc;
   if ((rc = daisy_host::make_tmap_bf16_3d(&tx, x, p.K, p.M, 1, (uint64_t)ldx * 2, (uint64_t)ldx * 2 * p.M, GK, GM)) != DAISY_OK) return rc;
-  if ((rc = daisy_host::make_tmap_bf16_3d(&tw, w, p.K, p.N, 1, (uint64_t)ldw * 2, (uint64_t)ldw * 2 * p.N, GK, BN)) != DAISY_OK) return rc;
-  return BN == 256 ? launch_gemm<256>(tx, tw, p, (cudaStream_t)stream) : launch_gemm<128>(tx, tw, p, (cudaStream_t)stream);
+  if ((rc = daisy_host::make_tmap_bf16_3d(&tw, w, p.K, p.N, 1, (uint64_t)ldw * 2, (uint64_t)ldw * 2 * p.N, GK, 128)) != DAISY_OK) return rc;
+  return pair ? launch_gemm<256, true>(tx, tw, p, (cudaStream_t)stream) : launch_gemm<128, false>(tx, tw, p, (cudaStream_t)stream);
 }
 
 extern "C" int daisy_b200_gemm_nt(const void* x, int64_t ldx, const void* w, int64_t ldw, void* c, int64_t ldc,

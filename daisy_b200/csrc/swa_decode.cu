@@ -57,6 +57,7 @@ struct DecodeParams {
   const __nv_bfloat16* ve;
   int64_t ve_sb, ve_sh;
   const float* ve_gate;
+  int prefetch;    // single-launch form: hint the ring slice into L2 before waiting for the preceding kernel
 };
 
 // Row range and table rows of this step: the host's values, or derived from the device-side position.
@@ -88,14 +89,38 @@ __device__ __forceinline__ DecodeGeom decode_geom(const DecodeParams& p) {
 template <bool DEV, bool F16>
 __device__ __forceinline__ void decode_combine_body(const DecodeParams& p, const DecodeGeom& g, int h, int b, bool coherent);
 
-template <bool DEV, bool F16, bool FUSED>
+// PIPE: issue the next iteration's loads before the current one's arithmetic (twice the registers).  It pays when a CTA
+// has only a few iterations -- small batches, where the kernel is latency-bound -- and costs occupancy when the ring
+// traffic is large enough to saturate HBM anyway.
+template <bool DEV, bool F16, bool FUSED, bool PIPE = false>
 __global__ void __launch_bounds__(128) swa_decode_partial_kernel(const DecodeParams p) {
   const int s = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, hw = lane >> 4, sub = lane & 15;
 
+  if (FUSED) {
+    // Launched as a dependent grid (see grid_dep_wait): while the projection that produces q, k, v still runs, ask L2
+    // for this CTA's slice of the ring -- older tokens, which that projection does not touch.  Only a hint: the range
+    // comes from a position that may be stale and is clamped to the ring; everything is read again after the wait.
+    if (p.prefetch && threadIdx.x < 2) {
+      const DecodeGeom g0 = decode_geom<DEV>(p);
+      const int i0 = s * g0.rows_per_split, n = min(g0.r, i0 + g0.rows_per_split) - i0;
+      if (n > 0 && n <= p.cap && g0.start_slot >= 0 && g0.start_slot < p.cap) {
+        int s0 = g0.start_slot + i0;
+        if (s0 >= p.cap) s0 -= p.cap;
+        const int n1 = min(n, p.cap - s0);
+        const __nv_bfloat16* base = (threadIdx.x ? p.vc : p.kc) + b * p.c_sb + h * p.c_sh;
+        if (s0 >= 0 && s0 < p.cap) {
+          l2_prefetch_bulk(base + (int64_t)s0 * p.c_sr, (uint32_t)(((int64_t)(n1 - 1) * p.c_sr + DAISY_HEAD_DIM) * 2));
+          if (n > n1) l2_prefetch_bulk(base, (uint32_t)(((int64_t)(n - n1 - 1) * p.c_sr + DAISY_HEAD_DIM) * 2));
+        }
+      }
+    }
+    grid_dep_launch();
+    grid_dep_wait();
+  }
   const DecodeGeom g = decode_geom<DEV>(p);
   float qf[8];
-  unpack8(*reinterpret_cast<const uint4*>(p.q + b * p.q_sb + h * p.q_sh + 8 * sub), qf);
+  unpack8(ld_cg16(p.q + b * p.q_sb + h * p.q_sh + 8 * sub), qf);
   norm_rope_row8(qf, sub, p.flags & DAISY_NORM_Q, p.flags & DAISY_ROPE, p.eps, g.cos_row, g.sin_row);
 #pragma unroll
   for (int e = 0; e < 8; ++e) qf[e] *= p.qscale;
@@ -109,18 +134,21 @@ __global__ void __launch_bounds__(128) swa_decode_partial_kernel(const DecodePar
 #pragma unroll
   for (int e = 0; e < 8; ++e) acc[e] = 0.f;
 
-  for (int base = i0 + warp * 8; base < i1; base += 32) {
-    uint4 kk[4], vv[4];
-    bool valid[4];
+  // Rows come eight per warp iteration (four per half-warp).
+  auto fetch = [&](int base, uint4* kk, uint4* vv, unsigned& valid) {
+    valid = 0;
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       const int row = base + 2 * j + hw;
-      valid[j] = row < i1;
-      int slot = g.start_slot + (valid[j] ? row : i0);
+      const bool ok = row < i1;
+      valid |= ok ? (1u << j) : 0u;
+      int slot = g.start_slot + (ok ? row : i0);
       if (slot >= p.cap) slot -= p.cap;
       kk[j] = ld_stream16(kbase + (int64_t)slot * p.c_sr);
       vv[j] = ld_stream16(vbase + (int64_t)slot * p.c_sr);
     }
+  };
+  auto consume = [&](const uint4* kk, const uint4* vv, unsigned valid) {
     float sc[4];
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
@@ -130,7 +158,7 @@ __global__ void __launch_bounds__(128) swa_decode_partial_kernel(const DecodePar
 #pragma unroll
       for (int e = 0; e < 8; ++e) d = fmaf(qf[e], kf[e], d);
       d = halfwarp_sum(d);
-      sc[j] = valid[j] ? d : -INFINITY;
+      sc[j] = (valid >> j) & 1u ? d : -INFINITY;
     }
     const float mn = fmaxf(fmaxf(m, fmaxf(sc[0], sc[1])), fmaxf(sc[2], sc[3]));
     const float alpha = fast_exp2(m - mn);
@@ -148,6 +176,30 @@ __global__ void __launch_bounds__(128) swa_decode_partial_kernel(const DecodePar
       for (int e = 0; e < 8; ++e) acc[e] = fmaf(pj[j], vf[e], acc[e]);
     }
     m = mn;
+  };
+  if (!PIPE) {
+    for (int base = i0 + warp * 8; base < i1; base += 32) {
+      uint4 ka[4], va[4];
+      unsigned oka;
+      fetch(base, ka, va, oka);
+      consume(ka, va, oka);
+    }
+  } else {
+    uint4 ka[4], va[4], kb[4], vb[4];
+    unsigned oka = 0, okb = 0;
+    int base = i0 + warp * 8;
+    if (base < i1) fetch(base, ka, va, oka);
+    while (base < i1) {
+      const bool more_b = base + 32 < i1;
+      if (more_b) fetch(base + 32, kb, vb, okb);
+      consume(ka, va, oka);
+      if (!more_b) break;
+      const bool more_a = base + 64 < i1;
+      if (more_a) fetch(base + 64, ka, va, oka);
+      consume(kb, vb, okb);
+      if (!more_a) break;
+      base += 64;
+    }
   }
 
   // merge the two half-warps
@@ -359,13 +411,27 @@ static int decode_launch(const void* q_new, const void* k_new, const void* v_new
   p.t_dev = (const long long*)t_dev; p.window = window; p.table_rows = table_rows; p.status = status_word;
   p.tickets = fused ? reinterpret_cast<int*>(reinterpret_cast<char*>(workspace) + daisy_b200_swa_decode_workspace_bytes(B, H, D, splits)) : nullptr;
   p.ve = (const __nv_bfloat16*)ex.ve; p.ve_sb = ex.ve_sb; p.ve_sh = ex.ve_sh; p.ve_gate = ex.ve_gate;
+  // the ring slices of a small step fit L2 with room to spare; a large one would evict its own prefetches
+  p.prefetch = (fused && (size_t)B * H * (size_t)r * DAISY_HEAD_DIM * 4 <= ((size_t)48 << 20)) ? 1 : 0;
 
   cudaStream_t st = (cudaStream_t)stream;
   const bool f16 = (flags & DAISY_CACHE_FP16) != 0;
   const dim3 g1(splits, H, B), g2(H, B);
   if (fused) {                                                     // one launch: the last split CTA of a (batch, head) merges
-    if (t_dev) { if (f16) swa_decode_partial_kernel<true, true, true><<<g1, 128, 0, st>>>(p); else swa_decode_partial_kernel<true, false, true><<<g1, 128, 0, st>>>(p); }
-    else       { if (f16) swa_decode_partial_kernel<false, true, true><<<g1, 128, 0, st>>>(p); else swa_decode_partial_kernel<false, false, true><<<g1, 128, 0, st>>>(p); }
+    using daisy_host::launch_dependent;
+    cudaError_t le;
+    const int variant = (t_dev ? 4 : 0) | (f16 ? 2 : 0) | (p.prefetch ? 1 : 0);   // small steps: pipelined loads as well
+    switch (variant) {
+      case 0: le = launch_dependent(swa_decode_partial_kernel<false, false, true, false>, g1, dim3(128), 0, st, p); break;
+      case 1: le = launch_dependent(swa_decode_partial_kernel<false, false, true, true>, g1, dim3(128), 0, st, p); break;
+      case 2: le = launch_dependent(swa_decode_partial_kernel<false, true, true, false>, g1, dim3(128), 0, st, p); break;
+      case 3: le = launch_dependent(swa_decode_partial_kernel<false, true, true, true>, g1, dim3(128), 0, st, p); break;
+      case 4: le = launch_dependent(swa_decode_partial_kernel<true, false, true, false>, g1, dim3(128), 0, st, p); break;
+      case 5: le = launch_dependent(swa_decode_partial_kernel<true, false, true, true>, g1, dim3(128), 0, st, p); break;
+      case 6: le = launch_dependent(swa_decode_partial_kernel<true, true, true, false>, g1, dim3(128), 0, st, p); break;
+      default: le = launch_dependent(swa_decode_partial_kernel<true, true, true, true>, g1, dim3(128), 0, st, p); break;
+    }
+    if (le != cudaSuccess) { (void)cudaGetLastError(); return DAISY_ECUDA; }
     DAISY_CHECK_LAUNCH();
     return DAISY_OK;
   }
