@@ -81,7 +81,10 @@ swa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int T = p.T, nblk = (T + WB - 1) / WB;
-  const int n_items = nblk * p.H * p.B;
+  // blocks whose range is cut short by the sequence's end (MODE 0: the last key blocks) or start (MODE 1: the first
+  // query blocks) go last, longest first
+  const int span = p.window_blocks > 0 ? p.window_blocks * WB : p.window;
+  const BalancedWalk walk(nblk, p.H * p.B, span > 0 ? (span + WB - 1) / WB : nblk, MODE == 0);
   const CUtensorMap* tx0 = MODE == 0 ? &tm_k : &tm_q;
   const CUtensorMap* tx1 = MODE == 0 ? &tm_v : &tm_do;
   const CUtensorMap* ty0 = MODE == 0 ? &tm_q : &tm_k;
@@ -106,7 +109,7 @@ swa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       prefetch_tmap(&tm_q); prefetch_tmap(&tm_k); prefetch_tmap(&tm_v); prefetch_tmap(&tm_do);
       uint32_t n = 0, it = 0;
       bool ok = true;
-      for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x, ++it) {
+      for (int item; (item = walk.at((int)it)) >= 0 && ok; ++it) {
         const int blk = item % nblk, bh = item / nblk, h = bh % p.H, b = bh / p.H;
         int lo, hi;
         bwd_range<MODE>(blk, nblk, T, p.window, p.window_blocks, p.doc_start ? p.doc_start + b * p.doc_sb : nullptr, lo, hi);
@@ -141,7 +144,7 @@ swa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     const uint32_t s_t = tmem_base, dp_t = tmem_base + 128, a0_t = tmem_base + 256, a1_t = tmem_base + 384;
     uint32_t n = 0, it = 0, n_p = 0;
     bool ok = true;
-    for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x, ++it) {
+    for (int item; (item = walk.at((int)it)) >= 0 && ok; ++it) {
       const int blk = item % nblk, bh = item / nblk, b = bh / p.H;
       int lo, hi;
       bwd_range<MODE>(blk, nblk, T, p.window, p.window_blocks, p.doc_start ? p.doc_start + b * p.doc_sb : nullptr, lo, hi);
@@ -189,7 +192,7 @@ swa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     const float c2 = p.scale_log2;
     uint32_t n = 0, it = 0;
     bool ok = true;
-    for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x, ++it) {
+    for (int item; (item = walk.at((int)it)) >= 0 && ok; ++it) {
       const int blk = item % nblk, bh = item / nblk, h = bh % p.H, b = bh / p.H;
       const int* doc_row = p.doc_start ? p.doc_start + b * p.doc_sb : nullptr;
       int lo, hi;

@@ -164,8 +164,14 @@ __device__ __forceinline__ bool prepare_q_tile(PrefillBarriers* bars, uint8_t* q
   return true;
 }
 
-// Persistent: CTA c walks items c, c + gridDim.x, ...; item = (batch*H + head) * nq + q-pair, so the CTAs
-// running at any moment share a handful of (batch, head) K/V streams in L2.  Barrier phases are kept as
+// Persistent schedule: item = (batch*H + head) * nq + q-pair, walked in the balanced order of BalancedWalk (all
+// q-pairs that see a full window first, (batch, head)-major; then the causal-ramp q-pairs, longest first).
+__device__ __forceinline__ BalancedWalk prefill_walk(int nq, int BH, int window, int window_blocks) {
+  const int span = window > 0 ? window : (window_blocks > 0 ? window_blocks * BN : 0);       // keys a full row sees
+  return BalancedWalk(nq, BH, span > 0 ? (span + 2 * BM - 1) / (2 * BM) : nq, false);
+}
+
+// Barrier phases are kept as
 // running counters per role, so the K/V ring, the Q buffers and the TMEM accumulators carry over from
 // one item to the next: the producer prefetches the next item's Q and K while the softmax warps are
 // still writing the previous item's output.
@@ -191,7 +197,7 @@ swa_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int T = p.T, window = p.window;
   const int nq = (T + 2 * BM - 1) / (2 * BM);
-  const int n_items = nq * p.H * p.B;
+  const BalancedWalk walk = prefill_walk(nq, p.H * p.B, window, p.window_blocks);
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < 2; ++s) {
@@ -235,8 +241,8 @@ swa_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
           tma_load_4d(qdst + HALF_BYTES, &tm_q, &bars->q_full[s][qb], 64, gq.q0[s], gq.h, gq.b);
         }
       };
-      if ((int)blockIdx.x < n_items) load_q(blockIdx.x);
-      for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
+      if (walk.at(0) >= 0) load_q(walk.at(0));
+      for (int rd = 0, item; (item = walk.at(rd)) >= 0 && ok; ++rd) {
         const ItemGeom g = item_geom(item, nq, p.H, T, window, p.doc_start, p.doc_sb, p.window_blocks);
         for (int j = g.jlo; j <= g.jhi && ok; ++j) {
           for (int kv = 0; kv < 2; ++kv, ++n) {
@@ -251,7 +257,7 @@ swa_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
           }
           // next item's Q: after this item's first K/V tiles are on their way (its buffer was released when the
           // previous item issued its last Q K^T, which the ring has long passed by now)
-          if (j == (NQBUF > 1 ? g.jlo : g.jhi) && item + (int)gridDim.x < n_items) load_q(item + gridDim.x);
+          if (j == (NQBUF > 1 ? g.jlo : g.jhi) && walk.at(rd + 1) >= 0) load_q(walk.at(rd + 1));
         }
       }
     }
@@ -276,7 +282,7 @@ swa_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       uint32_t n_pv[2] = {0, 0};         // P tiles consumed so far per stream (phase of p_full)
       uint32_t n_q[2] = {0, 0};          // Q tiles consumed so far per stream (phase of q_full)
       bool ok = true;
-      for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
+      for (int rd = 0, item; (item = walk.at(rd)) >= 0 && ok; ++rd) {
         const ItemGeom g = item_geom(item, nq, p.H, T, window, p.doc_start, p.doc_sb, p.window_blocks);
         for (int j = g.jlo; j <= g.jhi + 1 && ok; ++j) {
 #pragma unroll
@@ -346,7 +352,7 @@ swa_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     uint32_t n_s = 0, n_o = 0, n_qs = 0;
     bool ok = true;
     bool q_prepared = false;                                       // raw-Q mode: the lower half prepares the stream's Q rows
-    for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
+    for (int rd = 0, item; (item = walk.at(rd)) >= 0 && ok; ++rd) {
       const ItemGeom g = item_geom(item, nq, p.H, T, window, p.doc_start, p.doc_sb, p.window_blocks);
       if (!g.valid[s]) continue;
       const int q0 = g.q0[s];
@@ -358,8 +364,8 @@ swa_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         // named barriers below, which need all 256 threads -- skip the tile loop and the epilogue instead
         if (!q_prepared) ok = prepare_q_tile(bars, q_tiles, s, row, n_qs, q_row, p, abort_flag);
         q_prepared = false;
-        const int item_next = item + gridDim.x;
-        if (item_next < n_items) {
+        const int item_next = walk.at(rd + 1);
+        if (item_next >= 0) {
           const ItemGeom gn = item_geom(item_next, nq, p.H, T, window, p.doc_start, p.doc_sb, p.window_blocks);
           next_valid = gn.valid[s];
           q_row_next = gn.q0[s] + row;
@@ -502,7 +508,7 @@ swa_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     uint32_t r[128];
     bool q_prepared = false;
     auto prepare_q = [&](int qrow) -> bool { return prepare_q_tile(bars, q_tiles, s, row, n_qs, qrow, p, abort_flag); };
-    for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
+    for (int rd = 0, item; (item = walk.at(rd)) >= 0 && ok; ++rd) {
       const ItemGeom g = item_geom(item, nq, p.H, T, window, p.doc_start, p.doc_sb, p.window_blocks);
       if (!g.valid[s]) continue;
       const int q0 = g.q0[s];
@@ -514,10 +520,10 @@ swa_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       q_prepared = false;
       // the next item's Q is prepared inside this item's loop (second iteration), in time these warps would
       // otherwise spend waiting for the tensor core
-      const int item_next = item + gridDim.x;
+      const int item_next = walk.at(rd + 1);
       bool next_valid = false;
       int q_row_next = 0;
-      if (QRAW && item_next < n_items) {
+      if (QRAW && item_next >= 0) {
         const ItemGeom gn = item_geom(item_next, nq, p.H, T, window, p.doc_start, p.doc_sb, p.window_blocks);
         next_valid = gn.valid[s];
         q_row_next = gn.q0[s] + row;
