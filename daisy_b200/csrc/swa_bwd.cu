@@ -14,9 +14,9 @@
 //   MODE 1  query block stationary:  item = 128 queries; Q_i, dO_i stay, the key blocks of the window stream
 //           (K_j, V_j);  S = Q_i K_j^T, dP = dO_i V_j^T (TMEM lane = query),  dQ += dZ K_j.
 // In both:  S = X0 Y0^T,  dP = X1 Y1^T  (X stationary, Y streamed),  acc1 += dZ Y0,  and MODE 0 also acc0 += P Y1.
-// Roles (320 threads): warps 0-7 rebuild P / dZ -- two warpgroups, thread = TMEM lane, 64 of a tile's 128 columns
-// each (every warpgroup writes its bf16 results over the first 32 columns of its OWN 64, so nobody overwrites
-// columns somebody else still has to read) -- and write the results; warp 8 TMA producer, warp 9 MMA issuer.
+// Roles (576 threads): warps 0-15 rebuild P / dZ -- four warpgroups, thread = TMEM lane, 32 of a tile's 128 columns
+// each (every warpgroup writes its bf16 results over the first 16 columns of its OWN 32, so nobody overwrites
+// columns somebody else still has to read) -- and write the results; warp 16 TMA producer, warp 17 MMA issuer.
 // TMEM: S [0,128) dP [128,256) acc0 [256,384) acc1 [384,512).
 // All mbarrier waits are bounded (abort flag, DAISY_ETIMEOUT through the status word).
 #include "common.cuh"
@@ -27,8 +27,8 @@ constexpr int WB = 128;                                   // block of queries / 
 constexpr int W_TILE = WB * DAISY_HEAD_DIM * 2;           // 32768
 constexpr int W_HALF = W_TILE / 2;
 constexpr int W_NST = 2;                                  // stages of streamed (Y0, Y1) tile pairs
-constexpr int BWD_THREADS = 320;
-constexpr int BWD_WORKERS = 256;                          // threads of warps 0-7
+constexpr int BWD_THREADS = 576;
+constexpr int BWD_WORKERS = 512;                          // threads of warps 0-15
 constexpr int BWD_SMEM = 1024 + 2 * W_TILE + W_NST * 2 * W_TILE + 2 * 3 * WB * 4 + 256;
 static_assert(BWD_SMEM <= 232448, "over the 227 KB a CTA may use");
 
@@ -44,7 +44,7 @@ struct BwdParams {
 };
 
 struct BwdBars {
-  uint64_t x_full, x_empty, y_full[W_NST], y_empty[W_NST], s_full, p_full, acc_full;
+  uint64_t x_full, x_empty, y_full[W_NST], y_empty[W_NST], s_full[2], p_full[2], acc_full, acc_empty;
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -93,17 +93,18 @@ swa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
   if (threadIdx.x == 0) {
     mbar_init(&bars->x_full, 1); mbar_init(&bars->x_empty, 1);
     for (int i = 0; i < W_NST; ++i) { mbar_init(&bars->y_full[i], 1); mbar_init(&bars->y_empty[i], 1); }
-    mbar_init(&bars->s_full, 1); mbar_init(&bars->p_full, BWD_WORKERS); mbar_init(&bars->acc_full, 1);
+    for (int i = 0; i < 2; ++i) { mbar_init(&bars->s_full[i], 1); mbar_init(&bars->p_full[i], BWD_WORKERS / 2); }
+    mbar_init(&bars->acc_full, 1); mbar_init(&bars->acc_empty, BWD_WORKERS);
     bars->abort_flag = 0;
     mbar_init_fence();
   }
-  if (warp == 9) { tmem_alloc(&bars->tmem_base, 512); tmem_relinquish(); }
+  if (warp == 17) { tmem_alloc(&bars->tmem_base, 512); tmem_relinquish(); }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = bars->tmem_base;
 
-  if (warp == 8) {
+  if (warp == 16) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
       prefetch_tmap(&tm_q); prefetch_tmap(&tm_k); prefetch_tmap(&tm_v); prefetch_tmap(&tm_do);
@@ -131,10 +132,17 @@ swa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         }
       }
     }
-  } else if (warp == 9) {
+  } else if (warp == 17) {
     // ------------------------------------------------------------------ MMA issuer
+    // The score tiles are formed and consumed in two halves of 64 streamed rows (= 64 TMEM columns), two worker
+    // warpgroups each, and the halves are software-pipelined: while the warpgroups of a half rebuild its P / dZ, the tensor core
+    // forms the other half's scores, accumulates the previous half's products and already forms the NEXT tile's
+    // scores of a half as soon as that half's columns have been consumed:
+    //   S0(y) S1(y) | wait P0(y): A0(y) S0(y+1) | wait P1(y): A1(y) S1(y+1) | wait P0(y+1): ...
+    // (S = both score products of a half, A = both accumulating products).  tcgen05 MMAs of one thread execute in
+    // order, so S_h(y+1) overwrites columns that A_h(y) has finished reading.
     const uint32_t leader = elect_one() ? 1u : 0u;
-    constexpr uint32_t idesc_s = umma_idesc_bf16(WB, WB, 0, 0);                   // X Y^T: both K-major
+    constexpr uint32_t idesc_s = umma_idesc_bf16(WB, WB / 2, 0, 0);               // X Y_half^T: both K-major, 64 streamed rows
     constexpr uint32_t idesc_a = umma_idesc_bf16(WB, DAISY_HEAD_DIM, 0, 1);       // (P | dZ from TMEM) x Y: Y as an MN-major operand
     const uint64_t xd = umma_desc_sw128(smem_u32(x_tiles), 16, 1024);
     const uint64_t yd = umma_desc_sw128(smem_u32(y_tiles), 16, 1024);
@@ -142,53 +150,75 @@ swa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     const uint32_t x_lo0 = (uint32_t)xd, y_lo0 = (uint32_t)yd, k_hi = (uint32_t)(xd >> 32);
     const uint32_t ymn_lo0 = (uint32_t)ymn, ymn_hi = (uint32_t)(ymn >> 32);
     const uint32_t s_t = tmem_base, dp_t = tmem_base + 128, a0_t = tmem_base + 256, a1_t = tmem_base + 384;
-    uint32_t n = 0, it = 0, n_p = 0;
+    uint32_t n = 0, it = 0;
     bool ok = true;
+    // both score products of half hf of the tile in stage st
+    auto scores = [&](int st, int hf) {
+      const uint32_t y0 = y_lo0 + st * ((2 * W_TILE) >> 4) + hf * ((64 * 128) >> 4), y1 = y0 + (W_TILE >> 4);
+#pragma unroll
+      for (int k = 0; k < DAISY_HEAD_DIM / 16; ++k) {                            // S = X0 Y0^T
+        const uint32_t off = ((k >> 2) * W_HALF + (k & 3) * 32) >> 4;
+        umma_ss_lh_p(leader, s_t + 64 * hf, x_lo0 + off, k_hi, y0 + off, k_hi, idesc_s, k > 0 ? 1u : 0u);
+      }
+#pragma unroll
+      for (int k = 0; k < DAISY_HEAD_DIM / 16; ++k) {                            // dP = X1 Y1^T
+        const uint32_t off = ((k >> 2) * W_HALF + (k & 3) * 32) >> 4;
+        umma_ss_lh_p(leader, dp_t + 64 * hf, x_lo0 + (W_TILE >> 4) + off, k_hi, y1 + off, k_hi, idesc_s, k > 0 ? 1u : 0u);
+      }
+      tc_commit_p(leader, &bars->s_full[hf]);
+    };
+    // both accumulating products over the 64 streamed rows of half hf
+    auto accumulate = [&](int st, int hf, uint32_t acc) {
+      const uint32_t ymn0 = ymn_lo0 + st * ((2 * W_TILE) >> 4), ymn1 = ymn0 + (W_TILE >> 4);
+      if (MODE == 0) {
+#pragma unroll
+        for (int k = 4 * hf; k < 4 * hf + 4; ++k)                               // acc0 += P Y1   (dV += P^T dO)
+          umma_ts_lh_p(leader, a0_t, s_t + (k & 1) * 8 + (k >> 1) * 32, ymn1 + k * (2048 >> 4), ymn_hi, idesc_a, (acc || k > 4 * hf) ? 1u : 0u);
+      }
+#pragma unroll
+      for (int k = 4 * hf; k < 4 * hf + 4; ++k)                                 // acc1 += dZ Y0  (dK += dZ^T Q | dQ += dZ K)
+        umma_ts_lh_p(leader, a1_t, dp_t + (k & 1) * 8 + (k >> 1) * 32, ymn0 + k * (2048 >> 4), ymn_hi, idesc_a, (acc || k > 4 * hf) ? 1u : 0u);
+    };
     for (int item; (item = walk.at((int)it)) >= 0 && ok; ++it) {
       const int blk = item % nblk, bh = item / nblk, b = bh / p.H;
       int lo, hi;
       bwd_range<MODE>(blk, nblk, T, p.window, p.window_blocks, p.doc_start ? p.doc_start + b * p.doc_sb : nullptr, lo, hi);
       if (!mbar_wait(&bars->x_full, it & 1, abort_flag, p.status, 3)) { ok = false; break; }
+      // the item's first tile
+      if (!mbar_wait(&bars->y_full[n % W_NST], (n / W_NST) & 1, abort_flag, p.status, 4)) { ok = false; break; }
+      tc_fence_after();
+      scores(n % W_NST, 0);
+      scores(n % W_NST, 1);
+      // its first accumulating products overwrite the accumulators: the workers have read out the previous item's
+      if (!mbar_wait(&bars->acc_empty, (it & 1) ^ 1, abort_flag, p.status, 8)) { ok = false; break; }
       for (int y = lo; y <= hi && ok; ++y, ++n) {
-        const int st = n % W_NST;
-        if (!mbar_wait(&bars->y_full[st], (n / W_NST) & 1, abort_flag, p.status, 4)) { ok = false; break; }
-        tc_fence_after();
-        const uint32_t y0 = y_lo0 + st * ((2 * W_TILE) >> 4), y1 = y0 + (W_TILE >> 4);
+        const int st = n % W_NST, st_next = (n + 1) % W_NST;
+        const bool more = y < hi;
 #pragma unroll
-        for (int k = 0; k < DAISY_HEAD_DIM / 16; ++k) {                          // S = X0 Y0^T
-          const uint32_t off = ((k >> 2) * W_HALF + (k & 3) * 32) >> 4;
-          umma_ss_lh_p(leader, s_t, x_lo0 + off, k_hi, y0 + off, k_hi, idesc_s, k > 0 ? 1u : 0u);
+        for (int hf = 0; hf < 2; ++hf) {
+          if (!mbar_wait(&bars->p_full[hf], n & 1, abort_flag, p.status, 5)) { ok = false; break; }
+          tc_fence_after();
+          accumulate(st, hf, (y == lo && hf == 0) ? 0u : 1u);
+          if (hf == 1) tc_commit_p(leader, &bars->y_empty[st]);
+          if (more) {
+            if (hf == 0) {
+              if (!mbar_wait(&bars->y_full[st_next], ((n + 1) / W_NST) & 1, abort_flag, p.status, 4)) { ok = false; break; }
+              tc_fence_after();
+            }
+            scores(st_next, hf);
+          }
         }
-#pragma unroll
-        for (int k = 0; k < DAISY_HEAD_DIM / 16; ++k) {                          // dP = X1 Y1^T
-          const uint32_t off = ((k >> 2) * W_HALF + (k & 3) * 32) >> 4;
-          umma_ss_lh_p(leader, dp_t, x_lo0 + (W_TILE >> 4) + off, k_hi, y1 + off, k_hi, idesc_s, k > 0 ? 1u : 0u);
-        }
-        tc_commit_p(leader, &bars->s_full);
-        if (!mbar_wait(&bars->p_full, n_p & 1, abort_flag, p.status, 5)) { ok = false; break; }
-        ++n_p;
-        tc_fence_after();
-        const uint32_t acc = (y == lo) ? 0u : 1u;                               // an item's first products overwrite its accumulators
-        const uint32_t ymn0 = ymn_lo0 + st * ((2 * W_TILE) >> 4), ymn1 = ymn0 + (W_TILE >> 4);
-        if (MODE == 0) {
-#pragma unroll
-          for (int k = 0; k < WB / 16; ++k)                                     // acc0 += P Y1   (dV += P^T dO)
-            umma_ts_lh_p(leader, a0_t, s_t + (k & 3) * 8 + (k >> 2) * 64, ymn1 + k * (2048 >> 4), ymn_hi, idesc_a, (acc || k > 0) ? 1u : 0u);
-        }
-#pragma unroll
-        for (int k = 0; k < WB / 16; ++k)                                       // acc1 += dZ Y0  (dK += dZ^T Q | dQ += dZ K)
-          umma_ts_lh_p(leader, a1_t, dp_t + (k & 3) * 8 + (k >> 2) * 64, ymn0 + k * (2048 >> 4), ymn_hi, idesc_a, (acc || k > 0) ? 1u : 0u);
-        tc_commit_p(leader, &bars->y_empty[st]);
-        if (y == hi) { tc_commit_p(leader, &bars->acc_full); tc_commit_p(leader, &bars->x_empty); }
+        if (ok && y == hi) { tc_commit_p(leader, &bars->acc_full); tc_commit_p(leader, &bars->x_empty); }
       }
     }
   } else {
     // ------------------------------------------------------------------ P / dZ rebuild and epilogue: thread = TMEM lane
-    const int half = warp >> 2, quarter = warp & 3;                   // which 64 columns; which 32 TMEM lanes
+    const int grp = warp >> 2, quarter = warp & 3;                    // which 32 columns; which 32 TMEM lanes
+    const int half = grp >> 1;                                        // the 64-column half whose barriers this warpgroup uses
     const int row = quarter * 32 + lane;
     const uint32_t lane_off = (uint32_t)(quarter * 32) << 16;
-    const uint32_t s_t = tmem_base + lane_off + 64 * half, dp_t = s_t + 128;       // this thread's 64 S and 64 dP columns
-    const uint32_t a0_t = tmem_base + lane_off + 256 + 64 * half, a1_t = a0_t + 128;   // and its 64 output columns of each accumulator
+    const uint32_t s_t = tmem_base + lane_off + 32 * grp, dp_t = s_t + 128;        // this thread's 32 S and 32 dP columns
+    const uint32_t a0_t = tmem_base + lane_off + 256 + 32 * grp, a1_t = a0_t + 128;    // and its 32 output columns of each accumulator
     const float c2 = p.scale_log2;
     uint32_t n = 0, it = 0;
     bool ok = true;
@@ -208,7 +238,7 @@ swa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       for (int y = lo; y <= hi; ++y, ++n) {
         float* cf = col_f + (n & 1) * 3 * WB;
         if (MODE == 0) {                                              // the streamed queries' scalars, shared by all lanes
-          if (half == 0) {
+          if (grp == 0) {
             const int q = y * WB + row;
             cf[row] = q < T ? p.lse2[rowbase + q] : 0.f;
             cf[WB + row] = q < T ? p.delta[rowbase + q] : 0.f;
@@ -217,7 +247,7 @@ swa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
           // the eight warps leave together: a warp that gave up still comes here, and everybody learns of it
           if (named_bar_or(1, BWD_WORKERS, !ok)) { ok = false; break; }
         }
-        ok = __all_sync(0xffffffffu, mbar_wait(&bars->s_full, n & 1, abort_flag, p.status, 6));
+        ok = __all_sync(0xffffffffu, mbar_wait(&bars->s_full[half], n & 1, abort_flag, p.status, 6));
         if (!ok) { if (MODE == 0) continue; else break; }
         tc_fence_after();
         const int y0 = y * WB;
@@ -230,16 +260,15 @@ swa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
           full = (y0 + WB - 1 <= blk * WB) && (p.window_blocks > 0 || p.window <= 0 || blk * WB + WB - 1 - y0 < p.window) &&
                  (!doc_row || doc_row[min(blk * WB + WB - 1, T - 1)] <= y0);
         }
-#pragma unroll 1
-        for (int c = 0; c < 2; ++c) {                                 // 32 columns at a time; results go back behind the read pointer
+        {                                                             // the results go back over the first 16 of the 32 columns
           uint32_t rs[32], rd[32];
-          tmem_ld32(s_t + 32 * c, rs);
-          tmem_ld32(dp_t + 32 * c, rd);
+          tmem_ld32(s_t, rs);
+          tmem_ld32(dp_t, rd);
           tc_wait_ld();
           uint32_t pp[16], pz[16];
 #pragma unroll
           for (int i = 0; i < 32; i += 4) {
-            const int col0 = 64 * half + 32 * c + i;
+            const int col0 = 32 * grp + i;
             float lse4[4], dl4[4];
             int doc4[4] = {0, 0, 0, 0};
             if (MODE == 0) {                                          // four columns' scalars per shared-memory load
@@ -248,37 +277,42 @@ swa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
               if (!full) *reinterpret_cast<int4*>(doc4) = *reinterpret_cast<const int4*>(reinterpret_cast<const int*>(cf) + 2 * WB + col0);
             }
             float pv[4], zv[4];
+            // two columns per packed instruction: x = S c2 - lse, then dZ = P (dP - delta)
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              const int col = col0 + e;
-              float lse, dl;
-              bool vis = true;
-              if (MODE == 0) {
-                lse = lse4[e]; dl = dl4[e];
-                if (!full) {
-                  const int q = y0 + col, k = xr;
-                  vis = (k <= q) && (q < T) && (p.window_blocks > 0 || p.window <= 0 || q - k < p.window) && (k >= doc4[e]);
-                }
-              } else {
-                lse = my_lse; dl = my_delta;
-                if (!full) {
-                  const int q = xr, k = y0 + col;
-                  vis = (k <= q) && (p.window_blocks > 0 || p.window <= 0 || q - k < p.window) && (k >= my_doc);
+            for (int e = 0; e < 4; e += 2) {
+              const float l0 = MODE == 0 ? lse4[e] : my_lse, l1 = MODE == 0 ? lse4[e + 1] : my_lse;
+              const float d0 = MODE == 0 ? dl4[e] : my_delta, d1 = MODE == 0 ? dl4[e + 1] : my_delta;
+              float x0, x1;
+              unpack2f(ffma2(pack2f(__uint_as_float(rs[i + e]), __uint_as_float(rs[i + e + 1])), pack2f(c2, c2), pack2f(-l0, -l1)), x0, x1);
+              float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
+              if (!full) {
+#pragma unroll
+                for (int u = 0; u < 2; ++u) {
+                  const int col = col0 + e + u;
+                  bool vis;
+                  if (MODE == 0) {
+                    const int q = y0 + col, k = xr;
+                    vis = (k <= q) && (q < T) && (p.window_blocks > 0 || p.window <= 0 || q - k < p.window) && (k >= doc4[e + u]);
+                  } else {
+                    const int q = xr, k = y0 + col;
+                    vis = (k <= q) && (p.window_blocks > 0 || p.window <= 0 || q - k < p.window) && (k >= my_doc);
+                  }
+                  if (!vis) { if (u == 0) p0 = 0.f; else p1 = 0.f; }
                 }
               }
-              const float pr = vis ? fast_exp2(fmaf(__uint_as_float(rs[i + e]), c2, -lse)) : 0.f;
-              pv[e] = pr;
-              zv[e] = pr * (__uint_as_float(rd[i + e]) - dl);
+              pv[e] = p0; pv[e + 1] = p1;
+              unpack2f(fmul2(pack2f(p0, p1), fadd2(pack2f(__uint_as_float(rd[i + e]), __uint_as_float(rd[i + e + 1])), pack2f(-d0, -d1))),
+                       zv[e], zv[e + 1]);
             }
             pp[i >> 1] = pack_bf16(pv[0], pv[1]); pp[(i >> 1) + 1] = pack_bf16(pv[2], pv[3]);
             pz[i >> 1] = pack_bf16(zv[0], zv[1]); pz[(i >> 1) + 1] = pack_bf16(zv[2], zv[3]);
           }
-          if (MODE == 0) tmem_st16(s_t + 16 * c, pp);
-          tmem_st16(dp_t + 16 * c, pz);
+          if (MODE == 0) tmem_st16(s_t, pp);
+          tmem_st16(dp_t, pz);
         }
         tc_wait_st();
         tc_fence_before();
-        mbar_arrive(&bars->p_full);
+        mbar_arrive(&bars->p_full[half]);
       }
       // ---- epilogue: the item's accumulators -> global rows (thread = row; 256 contiguous bytes each)
       if (ok) {
@@ -288,12 +322,11 @@ swa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         tc_fence_after();
 #pragma unroll 1
         for (int which = (MODE == 0 ? 0 : 1); which < 2; ++which) {
-          __nv_bfloat16* dst = (which == 0 ? p.d0 : p.d1) + (((int64_t)b * T + xr) * p.H + h) * DAISY_HEAD_DIM + 64 * half;
+          __nv_bfloat16* dst = (which == 0 ? p.d0 : p.d1) + (((int64_t)b * T + xr) * p.H + h) * DAISY_HEAD_DIM + 32 * grp;
           const float sc = which == 0 ? 1.f : p.scale;
-#pragma unroll 1
-          for (int c = 0; c < 2; ++c) {
+          {
             uint32_t r[32];
-            tmem_ld32((which == 0 ? a0_t : a1_t) + 32 * c, r);
+            tmem_ld32(which == 0 ? a0_t : a1_t, r);
             tc_wait_ld();
             if (xr < T) {
 #pragma unroll
@@ -303,21 +336,21 @@ swa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                 o.y = pack_bf16(__uint_as_float(r[i + 2]) * sc, __uint_as_float(r[i + 3]) * sc);
                 o.z = pack_bf16(__uint_as_float(r[i + 4]) * sc, __uint_as_float(r[i + 5]) * sc);
                 o.w = pack_bf16(__uint_as_float(r[i + 6]) * sc, __uint_as_float(r[i + 7]) * sc);
-                *reinterpret_cast<uint4*>(dst + 32 * c + i) = o;
+                *reinterpret_cast<uint4*>(dst + i) = o;
               }
             }
           }
         }
-        // the next item's first accumulating products are issued only after this thread has signalled that item's
-        // first P, i.e. after these loads: program order is the guard
+        // the next item's first accumulating products overwrite what was just read
         tc_fence_before();
       }
+      mbar_arrive(&bars->acc_empty);
     }
   }
 
   tc_fence_before();
   __syncthreads();
-  if (warp == 9) { tc_fence_after(); tmem_dealloc(tmem_base, 512); }
+  if (warp == 17) { tc_fence_after(); tmem_dealloc(tmem_base, 512); }
 }
 
 // ---------------------------------------------------------------------------------------------
