@@ -120,10 +120,13 @@ __global__ void __launch_bounds__(128) swa_decode_partial_kernel(const DecodePar
   }
   const DecodeGeom g = decode_geom<DEV>(p);
   float qf[8];
-  unpack8(ld_cg16(p.q + b * p.q_sb + h * p.q_sh + 8 * sub), qf);
-  norm_rope_row8(qf, sub, p.flags & DAISY_NORM_Q, p.flags & DAISY_ROPE, p.eps, g.cos_row, g.sin_row);
+  auto load_q = [&]() {
+    unpack8(ld_cg16(p.q + b * p.q_sb + h * p.q_sh + 8 * sub), qf);
+    norm_rope_row8(qf, sub, p.flags & DAISY_NORM_Q, p.flags & DAISY_ROPE, p.eps, g.cos_row, g.sin_row);
 #pragma unroll
-  for (int e = 0; e < 8; ++e) qf[e] *= p.qscale;
+    for (int e = 0; e < 8; ++e) qf[e] *= p.qscale;
+  };
+  if (!PIPE) load_q();                                  // PIPE: after the first ring rows are on their way
 
   const int i0 = s * g.rows_per_split;
   const int i1 = min(g.r, i0 + g.rows_per_split);
@@ -189,6 +192,7 @@ __global__ void __launch_bounds__(128) swa_decode_partial_kernel(const DecodePar
     unsigned oka = 0, okb = 0;
     int base = i0 + warp * 8;
     if (base < i1) fetch(base, ka, va, oka);
+    load_q();
     while (base < i1) {
       const bool more_b = base + 32 < i1;
       if (more_b) fetch(base + 32, kb, vb, okb);
@@ -265,6 +269,15 @@ __device__ __forceinline__ float block128_sum(float x, float* red) {
   return (red[0] + red[1]) + (red[2] + red[3]);
 }
 
+__device__ __forceinline__ float block128_max(float x, float* red) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) x = fmaxf(x, __shfl_xor_sync(0xffffffffu, x, o));
+  __syncthreads();
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = x;
+  __syncthreads();
+  return fmaxf(fmaxf(red[0], red[1]), fmaxf(red[2], red[3]));
+}
+
 // Merge of the split partials with the new token (thread = head-dim element, 128 threads): normalises / rotates the
 // new q, k, v, adds the new row's own score, writes the output row and stores the new k, v into the ring.
 // `coherent`: the partials were written by other SMs during this same launch -- read them past the L1.
@@ -301,15 +314,38 @@ __device__ __forceinline__ void decode_combine_body(const DecodeParams& p, const
 
   const int64_t base = ((int64_t)b * p.H + h) * p.splits;
   auto ml = [&](int64_t i) { return coherent ? __ldcg(p.ws_ml + i) : p.ws_ml[i]; };
-  float M = s_self;
-  for (int s = 0; s < p.splits; ++s) M = fmaxf(M, ml((base + s) * 2));
-  float w = fast_exp2(s_self - M);
-  float num = w * v, den = w;
-  for (int s = 0; s < p.splits; ++s) {
-    const float f = fast_exp2(ml((base + s) * 2) - M);
-    const float a = coherent ? __ldcg(p.ws_acc + (base + s) * DAISY_HEAD_DIM + d) : p.ws_acc[(base + s) * DAISY_HEAD_DIM + d];
-    num = fmaf(f, a, num);
-    den = fmaf(f, ml((base + s) * 2 + 1), den);
+  auto part = [&](int64_t s) { return coherent ? __ldcg(p.ws_acc + (base + s) * DAISY_HEAD_DIM + d) : p.ws_acc[(base + s) * DAISY_HEAD_DIM + d]; };
+  float num, den;
+  if (p.splits <= 128) {
+    // one round trip for all the (maximum, sum) pairs -- thread s takes split s -- and the partial rows in batches of
+    // eight loads in flight: a serial walk over the splits costs a memory latency per split, which at batch 1
+    // (31 splits) was a third of the whole step
+    __shared__ float wgt[128];
+    float m_s = DEC_NEG, l_s = 0.f;
+    if (d < p.splits) { m_s = ml((base + d) * 2); l_s = ml((base + d) * 2 + 1); }
+    const float M = fmaxf(block128_max(m_s, red), s_self);
+    const float f_s = d < p.splits ? fast_exp2(m_s - M) : 0.f;
+    wgt[d] = f_s;
+    const float w = fast_exp2(s_self - M);
+    den = block128_sum(f_s * l_s, red) + w;            // its barriers also publish wgt
+    num = w * v;
+    for (int s0 = 0; s0 < p.splits; s0 += 8) {
+      float a[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) a[j] = s0 + j < p.splits ? part(s0 + j) : 0.f;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) num = fmaf(s0 + j < p.splits ? wgt[s0 + j] : 0.f, a[j], num);
+    }
+  } else {
+    float M = s_self;
+    for (int s = 0; s < p.splits; ++s) M = fmaxf(M, ml((base + s) * 2));
+    const float w = fast_exp2(s_self - M);
+    num = w * v; den = w;
+    for (int s = 0; s < p.splits; ++s) {
+      const float f = fast_exp2(ml((base + s) * 2) - M);
+      num = fmaf(f, part(s), num);
+      den = fmaf(f, ml((base + s) * 2 + 1), den);
+    }
   }
   p.out[b * p.o_sb + h * p.o_sh + d] = __float2bfloat16_rn(num / den);
   const int64_t row = ((int64_t)b * p.H + h) * DAISY_HEAD_DIM + d;
