@@ -1013,7 +1013,9 @@ def main():
         res = run_kda_layer(dict(KDA_SMALL, B=4), args.steps, args.warmup, peaks, lean=True)
     if want in ("all", "prefill_c4"):
         torch.cuda.empty_cache()
-        c4 = run_prefill(PREFILL_C4, max(3, args.steps // 4), warm, dist, rank, world, peaks, "prefill_c4", shard_heads=True)
+        # a step shrinks with the number of ranks (heads are sharded): time as many more of them, so that the timed
+        # region stays several milliseconds long
+        c4 = run_prefill(PREFILL_C4, max(3, args.steps // 4) * world, warm, dist, rank, world, peaks, "prefill_c4", shard_heads=True)
         if res is None:
             res = c4
         else:

@@ -95,7 +95,8 @@ def test_qkv_gemm_value_embedding_gate():
     assert_close_bf16(vp, ref, "ve gate in the epilogue")
 
 
-@pytest.mark.parametrize("M,N,K", [(1, 6144, 2048), (2, 2048, 2048), (5, 392, 256), (8, 777, 1024), (17, 2048, 512), (64, 256, 2048)])
+@pytest.mark.parametrize("M,N,K", [(1, 6144, 2048), (2, 2048, 2048), (5, 392, 256), (8, 777, 1024), (17, 2048, 512), (64, 256, 2048),
+                                   (3, 512, 12288), (8, 130, 16384)])
 def test_skinny_gemm_matches_fp32_reference(M, N, K):
     """The weight-streaming projection of a decode step: F.linear for up to 64 rows."""
     from daisy_b200 import ops
