@@ -772,11 +772,15 @@ def run_kda(cfg, steps, warmup, dist, rank, world, peaks, lean=False):
                 full["o"], _ = ops.kda_chunk_fwd(*full_in, None, None, False, l2norm_qk=True)
 
             t1 = timed_steps(step1, steps, warmup, None) / steps
-            same = True
+            # fewer pairs per GPU run the state pass with its K dimension split over more warps (another summation
+            # order), so a shard equals the single-GPU result to bf16 rounding, not bit for bit
+            diff, mag = 0.0, float(full["o"].float().abs().max())
             for r, part in enumerate(gathered):
                 bl, bh_, hl, hh = unit_shard(B, H, world, r)
-                same = same and bool(torch.equal(part, full["o"][bl:bh_, :, hl:hh]))
+                diff = max(diff, float((part.float() - full["o"][bl:bh_, :, hl:hh].float()).abs().max()))
+            same = bool(diff <= mag * 2.0 ** -7)
             strong = strong_summary(t1, per, world)
+            strong["gathered_max_abs_diff"] = diff
             del full_in, full
         strong["gathered_equals_single_gpu_result"] = same
         del gathered

@@ -626,25 +626,39 @@ struct KdaStateParams {
   const int* seq_ptr;
 };
 
-constexpr int KDA_NST = 2;     // ring stages
 
-template <int NW>
+// NW V-slices of 16 rows per CTA, each owned by KS warps that split the K dimension of the state between them.
+// KS = 1: a warp keeps its 16 V-rows x 128 K-columns of S^T in accumulator registers and chains everything through
+// register fragments.  KS > 1 (few (batch, head) pairs per GPU, where the serial chain over the chunks -- 212
+// dependent mma.sync per chunk and warp -- is all that is left): warp kq holds K-columns [128 kq / KS, 128 (kq+1) / KS);
+// the two products that contract over K (S^T W^T and S^T q~^T) become partial sums that the slice's warps exchange
+// through shared memory once per chunk (fragment order, double-buffered, one named barrier), after which every warp
+// has the whole U^T, finishes the output for its own token tiles and updates its own K-columns of the state.
+template <int NW, int KS, int NST>
 struct KdaStateSmem {
   static constexpr int VS = 16 * NW;
+  static constexpr int CW = NW * KS;                     // compute warps
   static constexpr int U_BYTES = VS * LDT * 2;
   static constexpr int STAGE = SHARED_BYTES + U_BYTES;
   static constexpr int O_LD = VS + 4;                    // floats; staging of one chunk of output
-  static constexpr int BYTES = KDA_NST * STAGE + KC * O_LD * 4 + 64;
+  static constexpr int XCH_WARP = 2 * 8 * 32 * 16;       // one warp's two partial accumulators: 8 tiles x 32 lanes x float4
+  static constexpr int XCH = KS > 1 ? CW * XCH_WARP : 0;
+  static constexpr int BYTES = NST * STAGE + KC * O_LD * 4 + XCH + 64;
 };
 
-template <int NW>
-__global__ void __launch_bounds__(32 * (NW + 1), 1) kda_state_kernel(const KdaStateParams p) {
-  using L = KdaStateSmem<NW>;
-  constexpr int VS = L::VS;
+template <int NW, int KS, int NST>
+__global__ void __launch_bounds__(32 * (NW * KS + 1), 1) kda_state_kernel(const KdaStateParams p) {
+  using L = KdaStateSmem<NW, KS, NST>;
+  constexpr int KDA_NST = NST;                             // ring stages of chunk records
+  constexpr int VS = L::VS, CW = L::CW;
+  constexpr int NKT = 16 / KS;                             // this warp's 8-column tiles of the state
+  constexpr int NKS = 8 / KS;                              // and its 16-deep steps of the contractions over K
+  constexpr int TPW = 8 / KS;                              // token tiles whose output this warp finishes
   extern __shared__ __align__(128) uint8_t kda_smem_raw[];
   uint8_t* stages = kda_smem_raw;
   float* o_stage = reinterpret_cast<float*>(kda_smem_raw + KDA_NST * L::STAGE);
-  uint64_t* full = reinterpret_cast<uint64_t*>(kda_smem_raw + KDA_NST * L::STAGE + KC * L::O_LD * 4);
+  float4* xch = reinterpret_cast<float4*>(kda_smem_raw + KDA_NST * L::STAGE + KC * L::O_LD * 4);
+  uint64_t* full = reinterpret_cast<uint64_t*>(kda_smem_raw + KDA_NST * L::STAGE + KC * L::O_LD * 4 + L::XCH);
   uint64_t* empty = full + KDA_NST;
   volatile int* abort_flag = reinterpret_cast<volatile int*>(empty + KDA_NST);
 
@@ -658,13 +672,13 @@ __global__ void __launch_bounds__(32 * (NW + 1), 1) kda_state_kernel(const KdaSt
   const int n_chunks = c_end - c_begin;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < KDA_NST; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], NW); }
+    for (int s = 0; s < KDA_NST; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], CW); }
     *abort_flag = 0;
     mbar_init_fence();
   }
   __syncthreads();
 
-  if (warp == NW) {
+  if (warp == CW) {
     // ------------------------------------------------------------ producer: bulk copies into the ring
     if (lane == 0) {
       for (int c = 0; c < n_chunks; ++c) {
@@ -679,18 +693,19 @@ __global__ void __launch_bounds__(32 * (NW + 1), 1) kda_state_kernel(const KdaSt
     return;
   }
 
-  // ------------------------------------------------------------ compute warps: 16 V rows each
-  const int vr0 = warp * 16 + g8, vr1 = vr0 + 8;                   // rows inside the slice
-  float st[16][4];                                                 // S^T[v][k]: tile nt -> k = 8 nt + 2 t4 (+1)
+  // ------------------------------------------------------------ compute warps: 16 V rows, 128 / KS K columns each
+  const int vs = warp / KS, kq = warp % KS;
+  const int vr0 = vs * 16 + g8, vr1 = vr0 + 8;                     // rows inside the CTA's V range
+  float st[NKT][4];                                                // S^T[v][k]: tile j -> k = 8 (kq NKT + j) + 2 t4 (+1)
 #pragma unroll
-  for (int nt = 0; nt < 16; ++nt) {
+  for (int j = 0; j < NKT; ++j) {
     if (p.h0) {
       const float* hp = p.h0 + (size_t)bh * KD * KD;
-      const int k0 = nt * 8 + 2 * t4;
-      st[nt][0] = hp[(size_t)k0 * KD + v_base + vr0]; st[nt][1] = hp[(size_t)(k0 + 1) * KD + v_base + vr0];
-      st[nt][2] = hp[(size_t)k0 * KD + v_base + vr1]; st[nt][3] = hp[(size_t)(k0 + 1) * KD + v_base + vr1];
+      const int k0 = (kq * NKT + j) * 8 + 2 * t4;
+      st[j][0] = hp[(size_t)k0 * KD + v_base + vr0]; st[j][1] = hp[(size_t)(k0 + 1) * KD + v_base + vr0];
+      st[j][2] = hp[(size_t)k0 * KD + v_base + vr1]; st[j][3] = hp[(size_t)(k0 + 1) * KD + v_base + vr1];
     } else {
-      st[nt][0] = st[nt][1] = st[nt][2] = st[nt][3] = 0.f;
+      st[j][0] = st[j][1] = st[j][2] = st[j][3] = 0.f;
     }
   }
 
@@ -706,15 +721,16 @@ __global__ void __launch_bounds__(32 * (NW + 1), 1) kda_state_kernel(const KdaSt
     const float* dv = reinterpret_cast<const float*>(sb + OFF_D);
     const __half* Ut = reinterpret_cast<const __half*>(sb + SHARED_BYTES);
 
-    // (1) accU = S^T W^T   and   (2a) accO = S^T q~^T      [16 x 64 tokens each]
+    // (1) accU = S^T W^T   and   (2a) accO = S^T q~^T      [16 x 64 tokens each], over this warp's K columns
     float au[8][4], ao[8][4];
 #pragma unroll
     for (int nt = 0; nt < 8; ++nt) { au[nt][0] = au[nt][1] = au[nt][2] = au[nt][3] = 0.f; ao[nt][0] = ao[nt][1] = ao[nt][2] = ao[nt][3] = 0.f; }
 #pragma unroll
-    for (int ks = 0; ks < 8; ++ks) {
+    for (int ksl = 0; ksl < NKS; ++ksl) {
+      const int ks = kq * NKS + ksl;
       uint32_t a[4];
-      a[0] = pack_h2(st[2 * ks][0], st[2 * ks][1]); a[1] = pack_h2(st[2 * ks][2], st[2 * ks][3]);
-      a[2] = pack_h2(st[2 * ks + 1][0], st[2 * ks + 1][1]); a[3] = pack_h2(st[2 * ks + 1][2], st[2 * ks + 1][3]);
+      a[0] = pack_h2(st[2 * ksl][0], st[2 * ksl][1]); a[1] = pack_h2(st[2 * ksl][2], st[2 * ksl][3]);
+      a[2] = pack_h2(st[2 * ksl + 1][0], st[2 * ksl + 1][1]); a[3] = pack_h2(st[2 * ksl + 1][2], st[2 * ksl + 1][3]);
       // B fragments of two token tiles per transposing ldmatrix.x4 from the channel-major images: matrix m =
       // (k half m & 1, token tile nt + (m >> 1)); its stored rows are channels, its columns tokens
       const int lrow = ks * 16 + ((lane >> 3) & 1) * 8 + (lane & 7), lcol = (lane >> 4) * 8;
@@ -729,6 +745,40 @@ __global__ void __launch_bounds__(32 * (NW + 1), 1) kda_state_kernel(const KdaSt
         mma_f16(ao[nt + 1], a, bq[2], bq[3]);
       }
     }
+    if (KS > 1) {
+      // exchange: every warp of the slice needs the whole accU; accO only for the token tiles it finishes.  The sums
+      // run over the warps in a fixed order, so all of them hold the same bits.
+      float4* mine = xch + (size_t)warp * (L::XCH_WARP / 16);
+#pragma unroll
+      for (int nt = 0; nt < 8; ++nt) {
+        mine[nt * 32 + lane] = make_float4(au[nt][0], au[nt][1], au[nt][2], au[nt][3]);
+        mine[256 + nt * 32 + lane] = make_float4(ao[nt][0], ao[nt][1], ao[nt][2], ao[nt][3]);
+      }
+      named_bar(2 + vs, 32 * KS);
+      const float4* slice = xch + (size_t)(vs * KS) * (L::XCH_WARP / 16);
+#pragma unroll
+      for (int nt = 0; nt < 8; ++nt) {
+        float4 t = slice[nt * 32 + lane];
+#pragma unroll
+        for (int q = 1; q < KS; ++q) {
+          const float4 u = slice[q * (L::XCH_WARP / 16) + nt * 32 + lane];
+          t.x += u.x; t.y += u.y; t.z += u.z; t.w += u.w;
+        }
+        au[nt][0] = t.x; au[nt][1] = t.y; au[nt][2] = t.z; au[nt][3] = t.w;
+      }
+#pragma unroll
+      for (int nt = 0; nt < 8; ++nt) {
+        if (nt / TPW != kq) continue;                                // compile-time tile index, warp-uniform test
+        float4 t = slice[256 + nt * 32 + lane];
+#pragma unroll
+        for (int q = 1; q < KS; ++q) {
+          const float4 u = slice[q * (L::XCH_WARP / 16) + 256 + nt * 32 + lane];
+          t.x += u.x; t.y += u.y; t.z += u.z; t.w += u.w;
+        }
+        ao[nt][0] = t.x; ao[nt][1] = t.y; ao[nt][2] = t.z; ao[nt][3] = t.w;
+      }
+      named_bar(2 + vs, 32 * KS);                                    // everybody has read: the next chunk may overwrite
+    }
     // U^T = U0^T - accU, as fp16 A fragments over the token axis
     uint32_t ua[4][4];
 #pragma unroll
@@ -741,50 +791,52 @@ __global__ void __launch_bounds__(32 * (NW + 1), 1) kda_state_kernel(const KdaSt
       ua[nt >> 1][(nt & 1) * 2 + 0] = lo;
       ua[nt >> 1][(nt & 1) * 2 + 1] = hi;
     }
-    // (2b) accO += U^T A_qk^T
+    // (2b) accO += U^T A_qk^T, for the token tiles this warp finishes
 #pragma unroll
     for (int ks = 0; ks < 4; ++ks) {
       const int lrow = (lane >> 4) * 8 + (lane & 7), lcol = ks * 16 + ((lane >> 3) & 1) * 8;
 #pragma unroll
       for (int nt = 2 * ks; nt < 8; nt += 2) {                     // A_qk[i][j] = 0 for j > i: tiles below 2 ks are empty
+        if (KS > 1 && nt / TPW != kq) continue;
         uint32_t ba[4];
         ldmatrix_x4(ba, &Aq[(nt * 8 + lrow) * LDT + lcol]);
         mma_f16(ao[nt], ua[ks], ba[0], ba[1]);
         mma_f16(ao[nt + 1], ua[ks], ba[2], ba[3]);
       }
     }
-    // (3) S^T = S^T diag(e^{G_C}) + U^T k~
+    // (3) S^T = S^T diag(e^{G_C}) + U^T k~, this warp's K columns
 #pragma unroll
-    for (int nt = 0; nt < 16; ++nt) {
-      const float2 d2 = *reinterpret_cast<const float2*>(&dv[nt * 8 + 2 * t4]);
-      st[nt][0] *= d2.x; st[nt][1] *= d2.y; st[nt][2] *= d2.x; st[nt][3] *= d2.y;
+    for (int j = 0; j < NKT; ++j) {
+      const float2 d2 = *reinterpret_cast<const float2*>(&dv[(kq * NKT + j) * 8 + 2 * t4]);
+      st[j][0] *= d2.x; st[j][1] *= d2.y; st[j][2] *= d2.x; st[j][3] *= d2.y;
     }
 #pragma unroll
     for (int ks = 0; ks < 4; ++ks) {
       const int lrow = (lane >> 4) * 8 + (lane & 7), lcol = ks * 16 + ((lane >> 3) & 1) * 8;
 #pragma unroll
-      for (int nt = 0; nt < 16; nt += 2) {
+      for (int j = 0; j < NKT; j += 2) {
         uint32_t bk[4];
-        ldmatrix_x4(bk, &Kt[(nt * 8 + lrow) * LDT + lcol]);
-        mma_f16(st[nt], ua[ks], bk[0], bk[1]);
-        mma_f16(st[nt + 1], ua[ks], bk[2], bk[3]);
+        ldmatrix_x4(bk, &Kt[((kq * NKT + j) * 8 + lrow) * LDT + lcol]);
+        mma_f16(st[j], ua[ks], bk[0], bk[1]);
+        mma_f16(st[j + 1], ua[ks], bk[2], bk[3]);
       }
     }
     __syncwarp();
     if (lane == 0) mbar_arrive(&empty[s]);                         // this warp is done with the stage
 
     // output: stage [token][v] in shared memory, then coalesced rows
-    asm volatile("bar.sync 1, %0;" ::"n"(32 * NW) : "memory");    // previous chunk's copy-out finished
+    asm volatile("bar.sync 1, %0;" ::"n"(32 * CW) : "memory");    // previous chunk's copy-out finished
 #pragma unroll
     for (int nt = 0; nt < 8; ++nt) {
+      if (KS > 1 && nt / TPW != kq) continue;
       const int tok = nt * 8 + 2 * t4;
       o_stage[tok * L::O_LD + vr0] = ao[nt][0]; o_stage[(tok + 1) * L::O_LD + vr0] = ao[nt][1];
       o_stage[tok * L::O_LD + vr1] = ao[nt][2]; o_stage[(tok + 1) * L::O_LD + vr1] = ao[nt][3];
     }
-    asm volatile("bar.sync 1, %0;" ::"n"(32 * NW) : "memory");
+    asm volatile("bar.sync 1, %0;" ::"n"(32 * CW) : "memory");
     int t0, rows;
     ki_chunk_span(p.chunk_tab, c_begin + c, p.T, t0, rows);
-    for (int idx = threadIdx.x; idx < KC * (VS / 4); idx += 32 * NW) {
+    for (int idx = threadIdx.x; idx < KC * (VS / 4); idx += 32 * CW) {
       const int tok = idx / (VS / 4), v4 = (idx % (VS / 4)) * 4;
       if (tok >= rows) continue;
       const float4 x = *reinterpret_cast<const float4*>(&o_stage[tok * L::O_LD + v4]);
@@ -801,10 +853,10 @@ __global__ void __launch_bounds__(32 * (NW + 1), 1) kda_state_kernel(const KdaSt
   if (p.hT) {
     float* hp = p.hT + (size_t)bh * KD * KD;
 #pragma unroll
-    for (int nt = 0; nt < 16; ++nt) {
-      const int k0 = nt * 8 + 2 * t4;
-      hp[(size_t)k0 * KD + v_base + vr0] = st[nt][0]; hp[(size_t)(k0 + 1) * KD + v_base + vr0] = st[nt][1];
-      hp[(size_t)k0 * KD + v_base + vr1] = st[nt][2]; hp[(size_t)(k0 + 1) * KD + v_base + vr1] = st[nt][3];
+    for (int j = 0; j < NKT; ++j) {
+      const int k0 = (kq * NKT + j) * 8 + 2 * t4;
+      hp[(size_t)k0 * KD + v_base + vr0] = st[j][0]; hp[(size_t)(k0 + 1) * KD + v_base + vr0] = st[j][1];
+      hp[(size_t)k0 * KD + v_base + vr1] = st[j][2]; hp[(size_t)(k0 + 1) * KD + v_base + vr1] = st[j][3];
     }
   }
 }
@@ -819,17 +871,18 @@ extern "C" size_t daisy_b200_kda_workspace_bytes(int B, int T, int H, int K, int
   return (size_t)B * H * nc * REC_BYTES;
 }
 
-template <int NW>
+template <int NW, int KS, int NST>
 static int launch_state(const KdaStateParams& sp, int BH, cudaStream_t st) {
-  using L = KdaStateSmem<NW>;
+  using L = KdaStateSmem<NW, KS, NST>;
+  static_assert(L::BYTES <= 232448, "over the 227 KB a CTA may use");
   static bool attr[daisy_host::MAX_DEVICES] = {};             // the attribute is per device
   const int dev = daisy_host::device_slot();
   if (dev < 0) return DAISY_ENODEV;
   if (!attr[dev]) {
-    if (cudaFuncSetAttribute(kda_state_kernel<NW>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::BYTES) != cudaSuccess) return DAISY_ECUDA;
+    if (cudaFuncSetAttribute(kda_state_kernel<NW, KS, NST>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::BYTES) != cudaSuccess) return DAISY_ECUDA;
     attr[dev] = true;
   }
-  kda_state_kernel<NW><<<dim3(KD / L::VS, BH), 32 * (NW + 1), L::BYTES, st>>>(sp);
+  kda_state_kernel<NW, KS, NST><<<dim3(KD / L::VS, BH), 32 * (L::CW + 1), L::BYTES, st>>>(sp);
   return cudaGetLastError() == cudaSuccess ? DAISY_OK : DAISY_ECUDA;
 }
 
@@ -886,9 +939,9 @@ static int kda_launch(const void* q, const void* k, const void* v, const float* 
   const int BH = n_seq * H;
   // V-slices: 64 rows (4 warps) fill the machine when there are >= 48 (sequence, head) pairs; fewer take narrower slices
   int rc;
-  if (BH * 2 >= 96) rc = launch_state<4>(sp, BH, st);
-  else if (BH * 4 >= 96) rc = launch_state<2>(sp, BH, st);
-  else rc = launch_state<1>(sp, BH, st);
+  if (BH * 2 >= 96) rc = launch_state<4, 1, 2>(sp, BH, st);
+  else if (BH * 4 >= 96) rc = launch_state<2, 2, 2>(sp, BH, st);
+  else rc = launch_state<1, 2, 3>(sp, BH, st);
   if (rc != DAISY_OK) { (void)cudaGetLastError(); return rc; }
   return DAISY_OK;
 }

@@ -131,7 +131,9 @@ def test_kda_c5_full_size():
     # the shard one GPU of eight computes: heads 0..7 of batch row 2, as its own contiguous tensors
     shard = lambda x: x[b:b + 1, :, :8].contiguous()
     o_sh, s_sh = ops.kda_chunk_fwd(shard(q), shard(k), shard(v), shard(g), shard(beta), None, None, True, out_fp32=True)
-    assert torch.equal(o_sh, o[b:b + 1, :, :8]) and torch.equal(s_sh, s[b:b + 1, :8])
+    # (8 pairs per GPU run the state pass with the K dimension split over four warps: another summation order)
+    rel = lambda a, r: ((a - r).norm() / r.norm()).item()
+    assert rel(o_sh, o[b:b + 1, :, :8]) <= 1e-4 and rel(s_sh, s[b:b + 1, :8]) <= 1e-4
     half = T // 2
     cut = lambda x, a, b_: x[:, a:b_].contiguous()
     o1, s1 = ops.kda_chunk_fwd(cut(q, 0, half), cut(k, 0, half), cut(v, 0, half), cut(g, 0, half), cut(beta, 0, half),
