@@ -111,3 +111,23 @@ def test_skinny_gemm_matches_fp32_reference(M, N, K):
     assert y3.shape == (M, 1, N)
     assert_close_bf16(y3.view(M, N), x.float().cpu() @ big[N:].float().cpu().t(), "strided weight")
     assert torch.equal(ops.gemm_skinny(x, w), y), "not run-to-run deterministic"
+
+
+def test_skinny_gemm_after_a_kernel_that_writes_its_operands():
+    """The skinny projection is launched as a dependent grid and hints its weight rows into L2 before it waits for the
+    preceding kernel.  Both operands are produced by kernels launched immediately before it on the same stream, again
+    and again with new values: every result must see the latest ones."""
+    from daisy_b200 import ops
+    M, N, K = 2, 2048, 2048
+    w = torch.empty(N, K, device="cuda", dtype=torch.bfloat16)
+    x = torch.empty(M, K, device="cuda", dtype=torch.bfloat16)
+    g = torch.Generator(device="cuda").manual_seed(5)
+    srcs = [((torch.randn(N, K, device="cuda", generator=g) * K ** -0.5).bfloat16(),
+             torch.randn(M, K, device="cuda", generator=g).bfloat16()) for _ in range(6)]
+    outs = []
+    for ws, xs in srcs:
+        w.copy_(ws)                                               # a kernel that writes the weights ...
+        x.copy_(xs)                                               # ... and one that writes the rows, right before the call
+        outs.append(ops.gemm_skinny(x, w).clone())
+    for (ws, xs), y in zip(srcs, outs):
+        assert_close_bf16(y, xs.float().cpu() @ ws.float().cpu().t(), "operands written by the preceding kernels")
