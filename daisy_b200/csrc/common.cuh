@@ -469,7 +469,7 @@ __device__ __forceinline__ bool elect_one() {
 // sequence (causal attention: the first query blocks see fewer keys, the last key blocks are seen by fewer queries).
 // The items are laid out in an order in which the cost never increases -- first the full-cost ones, bh-major with
 // consecutive blocks adjacent, so CTAs running at the same moment share K/V streams in L2; then the ramp, longest
-// first -- and dealt to the CTAs in rounds of alternating direction (round 0: CTA 0 .. G-1, round 1: G-1 .. 0, ...), so
+// first in bands of four blocks -- and dealt to the CTAs in rounds of alternating direction (round 0: CTA 0 .. G-1, round 1: G-1 .. 0, ...), so
 // every CTA's total stays within one item of the mean.  (The plain c, c + G, ... walk left the CTAs that drew few ramp
 // items 5-7 % above the mean at 8 x 16 heads, T = 8192, window 2048.)  at() returns bh * nblk + blk.
 struct BalancedWalk {
@@ -487,8 +487,13 @@ struct BalancedWalk {
       bh = (int)pos / nf;
       blk = (ramp_at_end ? 0 : nr) + (int)pos % nf;
     } else {
-      const int e = (int)pos - nfull, k = e / BH;           // k-th longest ramp block
-      bh = e % BH;
+      // ramp: bands of RB consecutive blocks, longest band first; inside a band bh-major again, so that neighbours in
+      // the order still share a (batch, head) (the costs inside a band differ by at most RB - 1 tiles)
+      constexpr int RB = 4;
+      const int e = (int)pos - nfull, band = e / (BH * RB), r = e - band * BH * RB;
+      const int width = min(RB, nr - band * RB);
+      bh = r / width;
+      const int k = band * RB + r % width;                  // k-th longest ramp block
       blk = ramp_at_end ? nf + k : nr - 1 - k;
     }
     return bh * nblk + blk;
