@@ -9,7 +9,7 @@
 // Two kernels:
 //  * kda_intra_kernel  -- everything that does not depend on the state, all chunks in parallel, on tcgen05 tensor
 //    cores: a persistent CTA per SM walks (batch, head, chunk) work items; 16 "element" warps turn the TMA-staged
-//    inputs into fp16 operand images and issue the Gram products on them, 4 "solver" warps pull the Gram entries
+//    inputs into fp16 operand images and issue the Gram products on them, 8 "solver" warps pull the Gram entries
 //    out of TMEM and solve (I + A_kk) W = beta k e^G, (I + A_kk) U0 = beta v block by block with register-chained
 //    mma.sync tiles -- two pipelines that overlap across consecutive chunks.  Per chunk it writes a record of fp16 operand images (rows padded so that fragment loads
 //    are bank-conflict free): W^T, (scale q e^G)^T, (k e^{G_C-G})^T, U0^T as [128][72], A_qk as [64][72], e^{G_C}.
@@ -17,7 +17,8 @@
 //    bulk-copies the images of chunk c+1.. into a shared-memory ring while the compute warps hold their
 //    slice of S^T (16 V-rows x 128 K-columns per warp) in fp32 accumulator registers and chain the
 //    three products through register-resident fragments (an accumulator tile pair is exactly the next
-//    product's A fragment), so the state never leaves the register file between chunks.
+//    product's A fragment), so the state never leaves the register file between chunks.  With few (batch, head)
+//    pairs per GPU two warps share a slice, each holding half of the K-columns.
 // Tensor-core operands are fp16 (10-bit mantissa, every decay factor and operand here is <= O(1)):
 // measured relative error of o against the fp32 token recurrence is ~4e-4, bf16 operands give ~3e-3.
 #include <cuda_fp16.h>
