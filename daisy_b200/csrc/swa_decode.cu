@@ -373,10 +373,15 @@ extern "C" int daisy_b200_swa_decode_splits(int B, int H, int ctx_rows, int sm_c
   const int64_t bh = (int64_t)B * H;
   const int64_t target = (int64_t)sm_count * 16;            // 16 CTAs of 128 threads fit on one SM
   int64_t splits = (target + bh - 1) / bh;
-  const int64_t max_by_rows = ctx_rows / 128 > 0 ? ctx_rows / 128 : 1;   // >= 4 loop trips per CTA
+  const int64_t max_by_rows = ctx_rows >= 128 ? (ctx_rows + 127) / 128 : 1;   // about 4 loop trips per CTA at least
   if (splits > max_by_rows) splits = max_by_rows;
   if (splits > 64) splits = 64;
   if (splits < 1) splits = 1;
+  // a split covers a whole number of 32-row iterations: drop the splits that rounding would leave without rows
+  // (4095 rows in 31 splits are 160 rows each, i.e. 26 splits of five iterations and five idle ones; 32 splits are
+  // 128 rows each, four iterations, nobody idle)
+  const int64_t rps = ((ctx_rows + splits - 1) / splits + 31) / 32 * 32;
+  splits = (ctx_rows + rps - 1) / rps;
   return (int)splits;
 }
 
