@@ -469,7 +469,7 @@ __device__ __forceinline__ bool elect_one() {
 // sequence (causal attention: the first query blocks see fewer keys, the last key blocks are seen by fewer queries).
 // The items are laid out in an order in which the cost never increases -- first the full-cost ones, bh-major with
 // consecutive blocks adjacent, so CTAs running at the same moment share K/V streams in L2; then the ramp, longest
-// first in bands of four blocks -- and dealt to the CTAs in rounds of alternating direction (round 0: CTA 0 .. G-1, round 1: G-1 .. 0, ...), so
+// first in bands of four blocks -- and dealt to the CTAs in passes of alternating direction (first pass: CTA 0 .. G-1, second: G-1 .. 0, ...), so
 // every CTA's total stays within one item of the mean.  (The plain c, c + G, ... walk left the CTAs that drew few ramp
 // items 5-7 % above the mean at 8 x 16 heads, T = 8192, window 2048.)  at() returns bh * nblk + blk.
 struct BalancedWalk {
@@ -477,9 +477,9 @@ struct BalancedWalk {
   __device__ BalancedWalk(int nblk_, int BH_, int nr_, bool ramp_at_end_)
       : c((int)blockIdx.x), G((int)gridDim.x), n_items(nblk_ * BH_), nblk(nblk_), nr(min(max(nr_, 0), nblk_)), BH(BH_),
         ramp_at_end(ramp_at_end_ ? 1 : 0) {}
-  // the item of this CTA's round-th turn, or -1 when its turns are over
-  __device__ int at(int round) const {
-    const long long pos = (long long)round * G + ((round & 1) ? G - 1 - c : c);
+  // the item of this CTA's turn-th turn, or -1 when its turns are over
+  __device__ int at(int turn) const {
+    const long long pos = (long long)turn * G + ((turn & 1) ? G - 1 - c : c);
     if (pos >= n_items) return -1;
     const int nf = nblk - nr, nfull = BH * nf;
     int bh, blk;
