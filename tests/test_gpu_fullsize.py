@@ -143,3 +143,32 @@ def test_kda_c5_full_size():
     assert torch.equal(o1, o[:, :half])                            # chunks are independent of what follows
     assert ((o2 - o[:, half:]).norm() / o[:, half:].norm()).item() <= 1e-6
     assert ((s2 - s).norm() / s.norm()).item() <= 1e-6
+
+
+def test_backward_c2_full_size():
+    """The attention backward at the headline shape (B=8, T=8192, 16 heads, window 2048): dq, dk, dv of sampled
+    (batch, head) pairs against ``torch.autograd`` over the fp32 oracle run on that pair's whole sequence; one batch row
+    computed alone gives the same bits; two runs give the same bits."""
+    from daisy_b200 import ops
+    B, T, H, W = 8, 8192, 16, 2048
+    q, k, v = (_randn_bf16((B, T, H, D), 60 + i) for i in range(3))
+    cos, sin = _rope(T)
+    qp, kp, vp = ops.qkv_prep(q, k, v, cos, sin, swa.FP32_EPS)
+    d_o = _randn_bf16((B, T, H, D), 64)
+    y, lse = ops.swa_attend(qp, kp, vp, W, bounded_qk=True, return_lse=True)
+    dq, dk, dv = ops.swa_attend_bwd(qp, kp, vp, y, d_o, lse, W)
+    ops.check_device_status("cuda")
+    assert all(torch.isfinite(t.float()).all() for t in (dq, dk, dv))
+    for b, h in ((0, 0), (6, 13)):
+        sl = lambda x: x[b:b + 1, :, h:h + 1].float().cpu()
+        y_ref, *ref = swa.attend_backward(sl(qp), sl(kp), sl(vp), sl(d_o), W)
+        assert_close_bf16(y[b:b + 1, :, h:h + 1], y_ref, f"y[{b},{h}]")
+        for got, r, n in zip((dq, dk, dv), ref, ("dq", "dk", "dv")):
+            g = got[b:b + 1, :, h:h + 1]
+            assert_close_bf16(g, r, f"{n}[{b},{h}]")
+            rel = ((g.float().cpu() - r).norm() / r.norm()).item()
+            assert rel <= 2e-2, f"{n}[{b},{h}]: relative L2 {rel}"
+    again = ops.swa_attend_bwd(qp, kp, vp, y, d_o, lse, W)
+    assert all(torch.equal(a, b_) for a, b_ in zip((dq, dk, dv), again))
+    row = ops.swa_attend_bwd(qp[2:3], kp[2:3], vp[2:3], y[2:3], d_o[2:3], lse[2:3], W)
+    assert all(torch.equal(a[0], b_[2]) for a, b_ in zip(row, (dq, dk, dv)))
