@@ -17,8 +17,9 @@ a ``WindowMask(window[, doc_start])``, an int, ``None`` (plain causal) -- or the
 
 Training.  When a call needs gradients (grad mode on and the input or a parameter requires them) ``forward``
 takes the differentiable route: ``F.linear`` projections (autograd supplies their gradients) around
-``daisy_b200.autograd.swa_attention``, whose backward is this library's tcgen05 backward kernels.  Layers that
-receive a value embedding, and the cache-writing ``prefill`` / ``step`` forms, have no backward and raise.
+``daisy_b200.autograd.swa_attention``, whose backward is this library's tcgen05 backward kernels.  In a layer that
+receives a value embedding the norm of v and the gate are torch operations on that route, so the gate parameter and
+``ve`` get their gradients too.  The cache-writing ``prefill`` / ``step`` forms have no backward and raise.
 """
 from __future__ import annotations
 
@@ -221,11 +222,14 @@ class B200CausalSelfAttention(nn.Module):
 
     def _no_autograd(self, x: Tensor):
         if self._needs_grad(x):
-            raise NotImplementedError("this call has no backward pass (only forward() without a value embedding does): call "
+            raise NotImplementedError("this call has no backward pass (only forward() does): call "
                                       "it under torch.no_grad() / inference_mode(), or detach the input and freeze the parameters")
 
-    def _attend_autograd(self, x: Tensor, mask):
-        """The differentiable forward: same arithmetic as ``_attend`` with the norm / RoPE as their own pass."""
+    def _attend_autograd(self, x: Tensor, ve: Optional[Tensor], mask):
+        """The differentiable forward: same arithmetic as ``_attend`` with the norm / RoPE as their own pass.  In a layer
+        with a value embedding the norm of v and the gate ``v = s(g_ve) norm(v) + (1 - s(g_ve)) ve``
+        (models/daisy/attention.py:125,132-135) are torch operations, so autograd supplies the gradients of ``g_ve`` and
+        ``ve`` as well, and the kernels get a v they must not normalise again."""
         from .autograd import swa_attention
         window, doc_start = mask[0], mask[1]
         in_blocks = len(mask) > 2 and mask[2]
@@ -234,7 +238,14 @@ class B200CausalSelfAttention(nn.Module):
         w = self.qkvo_w
         qkv = F.linear(x.to(w.dtype), w[:3].flatten(end_dim=1)).view(B, T, 3 * self.num_heads, self.head_dim)
         q, k, v = qkv.chunk(3, dim=-2)
-        y = swa_attention(q, k, v, cos, sin, window, self.attn_scale, self.norm_eps, QKV_DEFAULT, doc_start, in_blocks)
+        flags = QKV_DEFAULT
+        if self.receives_ve:
+            torch._assert(ve is not None, "ve must be provided when receives_ve=True")
+            vn = F.rms_norm(v.float(), (self.head_dim,), eps=self.norm_eps)
+            g = torch.sigmoid(self.g_ve.float())
+            v = (g * vn + (1.0 - g) * ve.view_as(v).float()).to(q.dtype)
+            flags = QKV_DEFAULT & ~NORM_V
+        y = swa_attention(q, k, v, cos, sin, window, self.attn_scale, self.norm_eps, flags, doc_start, in_blocks)
         return F.linear(y.view(B, T, self.m_dim), w[3])
 
     def _attend(self, x: Tensor, ve: Optional[Tensor], mask, ring=None, ring_first: int = 0):
@@ -267,8 +278,8 @@ class B200CausalSelfAttention(nn.Module):
             torch._assert(x.size(1) % WINDOW_BLOCK_SIZE == 0, "the block-granular mask needs T divisible by 128")
             attn_mask = block_mask
         mask = self._window_of(attn_mask)
-        if self._needs_grad(x) and not self.receives_ve:
-            return self._attend_autograd(x, mask)
+        if self._needs_grad(x) or (ve is not None and torch.is_grad_enabled() and ve.requires_grad):
+            return self._attend_autograd(x, ve, mask)
         y, _, _, _ = self._attend(x, ve, mask)
         return y
 

@@ -137,3 +137,43 @@ def test_module_forward_under_autograd_matches_reference_fixture(golden_dir):
     with torch.inference_mode():
         y_inf = attn(x.detach(), None, attn_mask=mask)
     assert_close_bf16(y_inf, y.detach().float().cpu(), "inference vs training forward", max_tol=3e-2, mean_tol=3e-3)
+
+
+def test_value_embedding_layer_under_autograd():
+    """A layer that receives a value embedding, trained: the gate ``v = s(g_ve) norm(v) + (1 - s(g_ve)) ve``
+    (models/daisy/attention.py:132-135) sits between the norm and the attention, and ``loss.backward()`` must reach x, the
+    merged weights, the gate parameter and ve.  Compared with ``torch.autograd`` over the fp32 oracle functions."""
+    from daisy_b200 import B200CausalSelfAttention, WindowMask
+    os.environ["DISABLE_O_ZERO_INIT"] = "1"
+    torch.manual_seed(3)
+    H, T, W = 2, 200, 64
+    m = B200CausalSelfAttention(H * D, H, D, receives_ve=True, layer_idx=2).cuda()
+    m.norm_eps = swa.FP32_EPS
+    x = torch.randn(1, T, H * D, device="cuda").bfloat16().requires_grad_(True)
+    ve = torch.randn(1, T, H * D, device="cuda").bfloat16().requires_grad_(True)
+    cot = torch.randn(1, T, H * D, device="cuda")
+    y = m(x, ve, attn_mask=WindowMask(W))
+    assert y.requires_grad
+    (y.float() * cot).sum().backward()
+    # oracle: the same computation in fp32 on the CPU
+    xo = x.detach().float().cpu().requires_grad_(True)
+    vo = ve.detach().float().cpu().requires_grad_(True)
+    wo = m.qkvo_w.detach().float().cpu().requires_grad_(True)
+    go = m.g_ve.detach().float().cpu().requires_grad_(True)
+    q, k, v = swa.project_qkv(xo, wo, H, D)
+    cos, sin = swa.rope_tables(D, T)
+    qn, kn, vn = swa.qkv_transform(q, k, v, cos, sin, swa.FP32_EPS)
+    gate = torch.sigmoid(go)
+    vn = gate * vn + (1 - gate) * vo.view_as(vn)
+    yo = swa.attend_windowed(qn, kn, vn, W).reshape(1, T, H * D) @ wo[3].t()
+    (yo * cot.cpu()).sum().backward()
+    assert_close_bf16(y.detach(), yo.detach(), "y", max_tol=4e-2, mean_tol=4e-3)
+    assert_close_bf16(x.grad, xo.grad, "dx", max_tol=4e-2, mean_tol=4e-3)
+    assert_close_bf16(ve.grad, vo.grad, "d ve", max_tol=4e-2, mean_tol=4e-3)
+    assert_close_bf16(m.qkvo_w.grad, wo.grad, "dw", max_tol=4e-2, mean_tol=4e-3)
+    g_got, g_ref = m.g_ve.grad.float().cpu().reshape(-1), go.grad.reshape(-1)
+    assert torch.allclose(g_got, g_ref, rtol=5e-2, atol=5e-2 * float(g_ref.abs().max()) + 1e-3), (g_got, g_ref)
+    # the inference route computes the same forward
+    with torch.inference_mode():
+        y_inf = m(x.detach(), ve.detach(), attn_mask=WindowMask(W))
+    assert_close_bf16(y_inf, y.detach().float().cpu(), "inference vs training forward", max_tol=3e-2, mean_tol=3e-3)
