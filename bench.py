@@ -1022,7 +1022,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--library-context", action="store_true",
                     help="also time the GPU library calls the reference makes for the same work (context, minutes)")
-    ap.add_argument("--workload", default="all", choices=["all", "prefill_c2", "prefill_c4", "prefill_bwd", "decode_c3", "kda_c5", "prefill_small", "decode_small", "kda_small", "gemm_small", "kda_layer_small"])
+    ap.add_argument("--workload", default="all", choices=["all", "prefill_c2", "prefill_c4", "prefill_bwd", "decode_c3", "kda_c5", "prefill_small", "bwd_small", "decode_small", "kda_small", "gemm_small", "kda_layer_small"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extras", action="store_true",
                     help="skip the measurements beside the workloads (projection GEMMs, generator-step latency, KDA layer "
@@ -1049,6 +1049,9 @@ def main():
                           sustained=(want == "all" and not args.no_extras))
     if want == "prefill_small":
         res = run_prefill(PREFILL_SMALL, args.steps, args.warmup, dist, rank, world, peaks, "prefill_small", lean=True)
+    if want == "bwd_small":                                  # the backward on the reduced case (profiler captures)
+        res = run_prefill_bwd(PREFILL_SMALL, args.steps, args.warmup, peaks)
+        res.update({"name": "prefill_bwd", "roofline": None, "e2e": None, "clocks": None})
     if want == "gemm_small":
         res = run_projection(1, 8192, 16, 128, args.steps, args.warmup, lean=True)
     if want == "decode_small":
